@@ -1,0 +1,152 @@
+/*
+ * light_b200.h -- C ABI of the B200 (sm_100a) quantized-weight matmul library.
+ *
+ * Every entry point replaces one CUDA launcher of the reference (sushvibez/light), i.e. one
+ * key of its kernel registry (internal/registry/registry.go:12-62) on device kind CUDA.  The
+ * contract is the reference launchers' contract:
+ *
+ *   - all pointers are DEVICE pointers into buffers the caller owns, output included; the
+ *     library never allocates, frees or copies to the host on these paths;
+ *   - work is enqueued on `stream` (0 = the legacy default stream) of device `device` and the
+ *     call returns without synchronising, so calls can be captured into a CUDA graph;
+ *   - the return value is 0 on success, a positive cudaError_t when the CUDA runtime refused
+ *     something, or a negative LB200_E_* code when the arguments are rejected; shape
+ *     violations are returned, never asserted; light_b200_last_error() gives the text;
+ *   - tensors are contiguous, row-major, offset 0.
+ *
+ * Quantized GGUF weights are passed in their on-disk block layout, (N, K) row-major, a row
+ * being K / block_elems consecutive blocks (reference gguf/reader.go:237-251, quant/q4_k.go:14-24,
+ * quant/q6_k.go:11-32, quant/q8_0.go:11-17).
+ */
+#ifndef LIGHT_B200_H
+#define LIGHT_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LIGHT_B200_ABI_VERSION 1
+
+/* ggml on-disk type codes (reference gguf/types.go:39-58) of the formats with a fused kernel
+ * (reference kernels/cuda/matmul_q.go:17-24). */
+enum {
+  LB200_Q4_0 = 2,
+  LB200_Q5_0 = 6,
+  LB200_Q8_0 = 8,
+  LB200_Q4_K = 12,
+  LB200_Q5_K = 13,
+  LB200_Q6_K = 14
+};
+
+/* Activation / output element types. */
+enum { LB200_F32 = 0, LB200_BF16 = 1, LB200_F16 = 2 };
+
+/* Argument errors (negative so they cannot collide with cudaError_t). */
+enum {
+  LB200_E_DTYPE = -1,     /* unknown or unsupported element / block type            */
+  LB200_E_SHAPE = -2,     /* a dimension is negative, zero where it may not be, or   */
+                          /* not a multiple of what the layout needs                 */
+  LB200_E_NULL = -3,      /* a required pointer is null                              */
+  LB200_E_ALIGN = -4,     /* a pointer is less aligned than the layout guarantees    */
+  LB200_E_DEVICE = -5,    /* no such device, or not an sm_100 device                 */
+  LB200_E_TOO_LARGE = -6  /* beyond a documented maximum                             */
+};
+
+/* Binds the library to `device` (makes its primary context current on the calling thread,
+ * checks the compute capability, sets kernel attributes).  Every other entry point does this
+ * lazily, so calling it is optional; it mirrors cudart.SetDevice + module load in the
+ * reference launchers (kernels/cuda/matmul_q.go:52-58, kernels/cuda/loader.go:99-196). */
+int light_b200_init(int device);
+
+/* Copies the calling thread's last error text into buf (NUL terminated); returns its length.
+ * Reference: the `cudart: <op>: <msg> (code N)` errors of internal/cudart/runtime.go:335-363. */
+int light_b200_last_error(char *buf, size_t n);
+
+int light_b200_abi_version(void);
+
+/* Number of kernels this library has launched on any stream since load (monotonic). */
+unsigned long long light_b200_launch_count(void);
+
+/* Block geometry: elements / bytes per block, 0 for an unknown type
+ * (reference dtype/dtype.go:53-102 blockInfo, BlockElems, BlockBytes). */
+int light_b200_block_elems(int ggml_type);
+int light_b200_block_bytes(int ggml_type);
+
+/* Registry key {matmul_q, CUDA, <w dtype>} (reference kernels/cuda/matmul_q.go:44-91,
+ * ops/matmul_q.go:27-75):  out (M,N) f32 = x (M,K) f32 . dequant(w (N,K) blocks)^T.
+ * K must be a multiple of the block size.  Any M >= 0 is taken (the reference routes M >= 8 to
+ * dequantize + SGEMM; here one call covers decode and prefill). */
+int light_b200_matmul_q(int ggml_type, const float *x, const void *w, float *out, int M, int N, int K, int device,
+                        void *stream);
+
+/* The CUDA dequantize hook, quant.RegisterCUDADequant (reference quant/cuda_hook.go:13-46,
+ * kernels/cuda/dequant.go:15-75):  dst f32 [n_elems] = dequant(src blocks).  n_elems must be a
+ * whole number of blocks.  Bit-identical to the reference's CPU decoders. */
+int light_b200_dequant(int ggml_type, const void *src, float *dst, int64_t n_elems, int device, void *stream);
+
+/* Registry key {int4_dequant, CUDA, F32|BF16} (reference kernels/cuda/int4.go:43-69):
+ * canonical 4-bit layout (reference quant/int4.go:12-31) codes u32 (N,K/8), scales and zeros
+ * f32 (N,K/G) -> out (N,K) at out_dtype, written `offset` ELEMENTS into `out`;
+ * W = s * (code - z) formed in f32 and rounded once.  G % 8 == 0. */
+int light_b200_int4_dequant(const uint32_t *codes, const float *scales, const float *zeros, void *out, int out_dtype,
+                            int N, int K, int group, int64_t offset, int device, void *stream);
+
+/* Registry key {int4_gemv, CUDA, F32|BF16} (reference kernels/cuda/int4.go:76-101):
+ * y (M,N) at act_dtype = x (M,K) at act_dtype . W^T.  K % 32 == 0, G % 32 == 0.  The reference
+ * kernel stops at M = 8 (ops/int4.go:58-59); this one takes any M >= 0. */
+int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *scales, const float *zeros, void *y,
+                         int act_dtype, int M, int N, int K, int group, int device, void *stream);
+
+/* Registry key {fp8_block_dequant, CUDA, F32|BF16} (reference kernels/cuda/fp8_block.go:44-69):
+ * w e4m3fn codes (R,C), scale f32 (R/bR, C/bC) -> out (R,C) = f32(w) * scale, rounded once.
+ * C % 4 == 0, bC % 4 == 0, R % bR == 0, C % bC == 0. */
+int light_b200_fp8_block_dequant(const uint8_t *w, const float *scale, void *out, int out_dtype, int R, int C,
+                                 int block_r, int block_c, int device, void *stream);
+
+/* Registry key {fp8_block_gemv, CUDA, F32|BF16} (reference kernels/cuda/fp8_block.go:76-105):
+ * y (M,N) = x (M,K) . (w * scale)^T.  K % 16 == 0, bC % 16 == 0.  Any M >= 0 (reference: M <= 8). */
+int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N,
+                              int K, int block_r, int block_c, int device, void *stream);
+
+/* Arguments of the grouped expert matmuls.  Mirrors the Inputs / Attrs of the reference
+ * launchers (kernels/cuda/moe.go:21-141; kernel contract kernels/cuda/src/moe.cu:1-24):
+ *
+ *   out[p, :] = w(p) * input[row(p), :] . weights[e, :, :]^T   for each sorted pair
+ *
+ * sorted_pairs[i] is the pair id p = token * topk + slot of the i-th pair in expert order and
+ * expert_ids[i] its expert (non-decreasing); row(p) = p when row_per_pair, else p / topk;
+ * w(p) = topk_weights[p], or 1 when topk_weights is null.  counts (E) and offsets (E+1) are
+ * int32 SCRATCH the caller provides; the call fills them (offsets = exclusive prefix sum of the
+ * per-expert pair counts) and they are valid outputs afterwards.  Rows of `out` whose pair id
+ * does not appear (or is outside [0, size_m)) are left untouched. */
+typedef struct lb200_moe_args {
+  const void *input;          /* (rows, K) at dtype (moe_gemm) or f32 (moe_gemm_q)          */
+  const void *weights;        /* (E, N, K) at dtype, or GGUF blocks of ggml_type            */
+  const int64_t *sorted_pairs; /* (M)                                                        */
+  const int64_t *expert_ids;  /* (M)                                                        */
+  int32_t *counts;            /* (E) scratch                                                */
+  int32_t *offsets;           /* (E+1) scratch                                              */
+  const float *topk_weights;  /* (size_m) or null                                           */
+  void *out;                  /* (size_m, N) at dtype, or f32 (moe_gemm_q)                  */
+  int64_t M;                  /* number of sorted pairs                                     */
+  int64_t size_m;             /* rows of out                                                */
+  int32_t E, N, K;
+  int32_t topk;
+  int32_t row_per_pair;
+  int32_t dtype;              /* LB200_F32 / BF16 / F16 (moe_gemm); ggml type (moe_gemm_q)  */
+} lb200_moe_args;
+
+/* Registry key {moe_gemm, CUDA, F32|BF16|F16} (reference kernels/cuda/moe.go:21-97). */
+int light_b200_moe_gemm(const lb200_moe_args *args, int device, void *stream);
+
+/* Registry key {moe_gemm_q, CUDA, <w dtype>} (reference kernels/cuda/moe.go:99-141):
+ * x f32, GGUF block-quantized experts, out f32. */
+int light_b200_moe_gemm_q(const lb200_moe_args *args, int device, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIGHT_B200_H */

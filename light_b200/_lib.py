@@ -1,0 +1,88 @@
+"""ctypes binding of liblight_b200.so -- the C ABI declared in include/light_b200.h.
+
+There is no fallback: if the shared library is missing or a call fails, an exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "liblight_b200.so")
+
+F32, BF16, F16 = 0, 1, 2
+Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 6, 8, 12, 13, 14
+
+
+class Light200Error(RuntimeError):
+    """A call into liblight_b200.so returned non-zero; .code is the return value."""
+
+    def __init__(self, code: int, msg: str):
+        super().__init__(msg)
+        self.code = code
+
+
+class MoeArgs(C.Structure):
+    _fields_ = [
+        ("input", C.c_void_p), ("weights", C.c_void_p), ("sorted_pairs", C.c_void_p), ("expert_ids", C.c_void_p),
+        ("counts", C.c_void_p), ("offsets", C.c_void_p), ("topk_weights", C.c_void_p), ("out", C.c_void_p),
+        ("M", C.c_int64), ("size_m", C.c_int64), ("E", C.c_int32), ("N", C.c_int32), ("K", C.c_int32),
+        ("topk", C.c_int32), ("row_per_pair", C.c_int32), ("dtype", C.c_int32),
+    ]
+
+
+# name -> (restype, argtypes): every symbol include/light_b200.h declares
+SYMBOLS = {
+    "light_b200_init": (C.c_int, [C.c_int]),
+    "light_b200_last_error": (C.c_int, [C.c_char_p, C.c_size_t]),
+    "light_b200_abi_version": (C.c_int, []),
+    "light_b200_launch_count": (C.c_ulonglong, []),
+    "light_b200_block_elems": (C.c_int, [C.c_int]),
+    "light_b200_block_bytes": (C.c_int, [C.c_int]),
+    "light_b200_matmul_q": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                      C.c_void_p]),
+    "light_b200_dequant": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
+    "light_b200_int4_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                          C.c_int, C.c_int64, C.c_int, C.c_void_p]),
+    "light_b200_int4_gemv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                       C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_fp8_block_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                               C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_fp8_block_gemv": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                            C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_moe_gemm": (C.c_int, [C.POINTER(MoeArgs), C.c_int, C.c_void_p]),
+    "light_b200_moe_gemm_q": (C.c_int, [C.POINTER(MoeArgs), C.c_int, C.c_void_p]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """Loads liblight_b200.so (built by light_b200/build.py); raises if it is absent."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise Light200Error(-100, f"{LIB_PATH} is missing: run `python -m light_b200.build` (needs nvcc); "
+                                      "there is no CPU or PyTorch fallback")
+        l = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(l, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = l
+    return _lib
+
+
+def last_error() -> str:
+    buf = C.create_string_buffer(512)
+    lib().light_b200_last_error(buf, 512)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(rc: int) -> None:
+    if rc != 0:
+        raise Light200Error(rc, last_error() or f"light_b200 call failed with code {rc}")
+
+
+def launch_count() -> int:
+    return int(lib().light_b200_launch_count())

@@ -1,0 +1,212 @@
+// extern "C" entry points: argument checks, device binding, dispatch.  No kernel lives here.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace lb {
+
+static thread_local char g_err[512];
+static std::atomic<unsigned long long> g_launches{0};
+
+int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  int n = vsnprintf(g_err, sizeof(g_err) - 32, fmt, ap);
+  va_end(ap);
+  if (n < 0) n = 0;
+  if ((size_t)n > sizeof(g_err) - 32) n = sizeof(g_err) - 32;
+  snprintf(g_err + n, 32, " (code %d)", code);
+  return code;
+}
+
+int launched(const char *what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail((int)e, "light_b200: %s: %s", what, cudaGetErrorString(e));
+  return 0;
+}
+
+static std::mutex g_mu;
+static bool g_ready[64];
+
+static int bind(int device) {
+  if (device < 0 || device >= 64) return fail(LB200_E_DEVICE, "light_b200: device ordinal %d out of range", device);
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: cudaSetDevice(%d): %s", device, cudaGetErrorString(e));
+  if (g_ready[device]) return 0;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (g_ready[device]) return 0;
+  int major = 0;
+  e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: device %d: %s", device, cudaGetErrorString(e));
+  if (major != 10)
+    return fail(LB200_E_DEVICE, "light_b200: device %d has compute capability %d.x; this library holds sm_100a code only",
+                device, major);
+  int rc = gguf_gemv_fast_init(device);
+  if (rc) return rc;
+  g_ready[device] = true;
+  return 0;
+}
+
+static bool aligned(const void *p, size_t a) { return ((uintptr_t)p & (a - 1)) == 0; }
+
+}  // namespace lb
+
+using namespace lb;
+
+#define REQUIRE_PTR(p, op) \
+  if (!(p)) return fail(LB200_E_NULL, "light_b200: " op ": null pointer for " #p)
+
+extern "C" {
+
+int light_b200_init(int device) { return bind(device); }
+
+int light_b200_last_error(char *buf, size_t n) {
+  size_t len = strlen(g_err);
+  if (buf && n) {
+    size_t c = len < n - 1 ? len : n - 1;
+    memcpy(buf, g_err, c);
+    buf[c] = 0;
+  }
+  return (int)len;
+}
+
+int light_b200_abi_version(void) { return LIGHT_B200_ABI_VERSION; }
+unsigned long long light_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+int light_b200_block_elems(int t) { return block_elems(t); }
+int light_b200_block_bytes(int t) { return block_bytes(t); }
+
+int light_b200_matmul_q(int t, const float *x, const void *w, float *out, int M, int N, int K, int device, void *stream) {
+  const int be = block_elems(t);
+  if (!be) return fail(LB200_E_DTYPE, "light_b200: matmul_q: ggml type %d has no fused kernel", t);
+  if (M < 0 || N < 0 || K <= 0) return fail(LB200_E_SHAPE, "light_b200: matmul_q: bad shape M=%d N=%d K=%d", M, N, K);
+  if (K % be) return fail(LB200_E_SHAPE, "light_b200: matmul_q: K=%d not a multiple of the block size %d", K, be);
+  if (M == 0 || N == 0) return 0;
+  REQUIRE_PTR(x, "matmul_q");
+  REQUIRE_PTR(w, "matmul_q");
+  REQUIRE_PTR(out, "matmul_q");
+  if (!aligned(x, 16) || !aligned(out, 4) || !aligned(w, 2))
+    return fail(LB200_E_ALIGN, "light_b200: matmul_q: x must be 16-byte, out 4-byte, w 2-byte aligned");
+  if (int rc = bind(device)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  int took = gguf_gemv_fast(t, x, w, out, M, N, K, st);
+  if (took < 0) return took;
+  if (took) return 0;
+  return gguf_matmul_generic(t, x, w, out, M, N, K, st);
+}
+
+int light_b200_dequant(int t, const void *src, float *dst, int64_t n, int device, void *stream) {
+  const int be = block_elems(t);
+  if (!be) return fail(LB200_E_DTYPE, "light_b200: dequant: ggml type %d has no kernel", t);
+  if (n < 0 || n % be) return fail(LB200_E_SHAPE, "light_b200: dequant: %lld elements is not a whole number of %d-element blocks", (long long)n, be);
+  if (n == 0) return 0;
+  REQUIRE_PTR(src, "dequant");
+  REQUIRE_PTR(dst, "dequant");
+  if (!aligned(dst, 16)) return fail(LB200_E_ALIGN, "light_b200: dequant: dst must be 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return gguf_dequant(t, src, dst, n, (cudaStream_t)stream);
+}
+
+static int act_ok(int dt) { return dt == LB200_F32 || dt == LB200_BF16; }
+
+int light_b200_int4_dequant(const uint32_t *codes, const float *s, const float *z, void *out, int out_dtype, int N,
+                            int K, int G, int64_t offset, int device, void *stream) {
+  if (!act_ok(out_dtype)) return fail(LB200_E_DTYPE, "light_b200: int4_dequant: output type %d, want F32 or BF16", out_dtype);
+  if (N < 0 || K < 0 || G <= 0 || K % 8 || G % 8 || K % G || offset < 0)
+    return fail(LB200_E_SHAPE, "light_b200: int4_dequant: bad shape N=%d K=%d group=%d offset=%lld", N, K, G, (long long)offset);
+  if (N == 0 || K == 0) return 0;
+  REQUIRE_PTR(codes, "int4_dequant");
+  REQUIRE_PTR(s, "int4_dequant");
+  REQUIRE_PTR(z, "int4_dequant");
+  REQUIRE_PTR(out, "int4_dequant");
+  size_t esz = out_dtype == LB200_F32 ? 4 : 2;
+  if (!aligned((const char *)out + offset * esz, 16))
+    return fail(LB200_E_ALIGN, "light_b200: int4_dequant: out + offset must be 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return int4_dequant(codes, s, z, out, out_dtype, N, K, G, offset, (cudaStream_t)stream);
+}
+
+int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype,
+                         int M, int N, int K, int G, int device, void *stream) {
+  if (!act_ok(act_dtype)) return fail(LB200_E_DTYPE, "light_b200: int4_gemv: activation type %d, want F32 or BF16", act_dtype);
+  if (M < 0 || N < 0 || K <= 0 || G <= 0 || K % 32 || G % 32 || K % G)
+    return fail(LB200_E_SHAPE, "light_b200: int4_gemv: bad shape M=%d N=%d K=%d group=%d (K and group must be multiples of 32)", M, N, K, G);
+  if (M == 0 || N == 0) return 0;
+  REQUIRE_PTR(x, "int4_gemv");
+  REQUIRE_PTR(codes, "int4_gemv");
+  REQUIRE_PTR(s, "int4_gemv");
+  REQUIRE_PTR(z, "int4_gemv");
+  REQUIRE_PTR(y, "int4_gemv");
+  if (!aligned(codes, 16) || !aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: int4_gemv: x and codes must be 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return int4_gemv(x, codes, s, z, y, act_dtype, M, N, K, G, (cudaStream_t)stream);
+}
+
+int light_b200_fp8_block_dequant(const uint8_t *w, const float *s, void *out, int out_dtype, int R, int C, int bR,
+                                 int bC, int device, void *stream) {
+  if (!act_ok(out_dtype)) return fail(LB200_E_DTYPE, "light_b200: fp8_block_dequant: output type %d, want F32 or BF16", out_dtype);
+  if (R < 0 || C < 0 || bR <= 0 || bC <= 0 || R % bR || C % bC || C % 4 || bC % 4)
+    return fail(LB200_E_SHAPE, "light_b200: fp8_block_dequant: (%d, %d) not a multiple of block (%d, %d), or columns not a multiple of 4", R, C, bR, bC);
+  if (R == 0 || C == 0) return 0;
+  REQUIRE_PTR(w, "fp8_block_dequant");
+  REQUIRE_PTR(s, "fp8_block_dequant");
+  REQUIRE_PTR(out, "fp8_block_dequant");
+  if (!aligned(w, 4) || !aligned(out, 16)) return fail(LB200_E_ALIGN, "light_b200: fp8_block_dequant: w must be 4-byte, out 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return fp8_block_dequant(w, s, out, out_dtype, R, C, bR, bC, (cudaStream_t)stream);
+}
+
+int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *s, void *y, int act_dtype, int M, int N,
+                              int K, int bR, int bC, int device, void *stream) {
+  if (!act_ok(act_dtype)) return fail(LB200_E_DTYPE, "light_b200: fp8_block_gemv: activation type %d, want F32 or BF16", act_dtype);
+  if (M < 0 || N < 0 || K <= 0 || bR <= 0 || bC <= 0 || K % 16 || bC % 16 || N % bR || K % bC)
+    return fail(LB200_E_SHAPE, "light_b200: fp8_block_gemv: bad shape M=%d N=%d K=%d block (%d, %d)", M, N, K, bR, bC);
+  if (M == 0 || N == 0) return 0;
+  REQUIRE_PTR(x, "fp8_block_gemv");
+  REQUIRE_PTR(w, "fp8_block_gemv");
+  REQUIRE_PTR(s, "fp8_block_gemv");
+  REQUIRE_PTR(y, "fp8_block_gemv");
+  if (!aligned(w, 16) || !aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: fp8_block_gemv: x and w must be 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return fp8_block_gemv(x, w, s, y, act_dtype, M, N, K, bR, bC, (cudaStream_t)stream);
+}
+
+static int moe_check(const lb200_moe_args *a, const char *op, bool quant) {
+  if (!a) return fail(LB200_E_NULL, "light_b200: %s: null argument block", op);
+  if (a->M < 0 || a->size_m < 0 || a->E <= 0 || a->N < 0 || a->K <= 0 || a->topk < 1)
+    return fail(LB200_E_SHAPE, "light_b200: %s: bad shape M=%lld size_m=%lld E=%d N=%d K=%d topk=%d", op, (long long)a->M,
+                (long long)a->size_m, a->E, a->N, a->K, a->topk);
+  if (quant) {
+    int be = block_elems(a->dtype);
+    if (!be) return fail(LB200_E_DTYPE, "light_b200: %s: ggml type %d has no fused kernel", op, a->dtype);
+    if (a->K % be) return fail(LB200_E_SHAPE, "light_b200: %s: K=%d not a multiple of the block size %d", op, a->K, be);
+  } else {
+    if (a->dtype != LB200_F32 && a->dtype != LB200_BF16 && a->dtype != LB200_F16)
+      return fail(LB200_E_DTYPE, "light_b200: %s: element type %d, want F32, BF16 or F16", op, a->dtype);
+    if (a->K % 8) return fail(LB200_E_SHAPE, "light_b200: %s: K=%d must be a multiple of 8", op, a->K);
+  }
+  if (!a->counts || !a->offsets) return fail(LB200_E_NULL, "light_b200: %s: counts / offsets scratch missing", op);
+  if (a->M > 0 && (!a->input || !a->weights || !a->sorted_pairs || !a->expert_ids || !a->out))
+    return fail(LB200_E_NULL, "light_b200: %s: null tensor pointer", op);
+  if (a->M > 0 && (!aligned(a->input, 16) || !aligned(a->weights, quant ? 2 : 16)))
+    return fail(LB200_E_ALIGN, "light_b200: %s: input and weights must be 16-byte aligned", op);
+  return 0;
+}
+
+int light_b200_moe_gemm(const lb200_moe_args *a, int device, void *stream) {
+  if (int rc = moe_check(a, "moe_gemm", false)) return rc;
+  if (int rc = bind(device)) return rc;
+  return moe_gemm(a, (cudaStream_t)stream);
+}
+
+int light_b200_moe_gemm_q(const lb200_moe_args *a, int device, void *stream) {
+  if (int rc = moe_check(a, "moe_gemm_q", true)) return rc;
+  if (int rc = bind(device)) return rc;
+  return moe_gemm_q(a, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,64 @@
+// Shared declarations of the sm_100a quantized-matmul library.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/light_b200.h"
+
+namespace lb {
+
+// Records the message light_b200_last_error() returns (thread local) and hands back `code`.
+int fail(int code, const char *fmt, ...);
+// Maps the launch status of the kernel just enqueued (no synchronisation).
+int launched(const char *what);
+
+// Block geometry of the GGUF formats with a fused kernel (reference dtype/dtype.go:53-60).
+__host__ __device__ constexpr int block_elems(int t) {
+  return (t == LB200_Q4_0 || t == LB200_Q5_0 || t == LB200_Q8_0) ? 32
+         : (t == LB200_Q4_K || t == LB200_Q5_K || t == LB200_Q6_K) ? 256
+                                                                    : 0;
+}
+__host__ __device__ constexpr int block_bytes(int t) {
+  return t == LB200_Q4_0 ? 18 : t == LB200_Q5_0 ? 22 : t == LB200_Q8_0 ? 34 : t == LB200_Q4_K ? 144
+         : t == LB200_Q5_K ? 176 : t == LB200_Q6_K ? 210 : 0;
+}
+
+__device__ __forceinline__ float f16_bits_to_f32(uint16_t u) {
+  __half_raw r;
+  r.x = u;
+  return __half2float(__half(r));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// activation element access at either f32 or bf16
+__device__ __forceinline__ float ld_act(const float *p, long long i) { return p[i]; }
+__device__ __forceinline__ float ld_act(const __nv_bfloat16 *p, long long i) { return __bfloat162float(p[i]); }
+__device__ __forceinline__ void st_act(float *p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void st_act(__nv_bfloat16 *p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// ---- per-file launch entry points (host side), called from abi.cu ----
+int gguf_dequant(int type, const void *src, float *dst, long long n, cudaStream_t st);
+int gguf_matmul_generic(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
+// returns 1 when a fast decode kernel took the call, 0 when the shape is not covered, <0 on error
+int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
+int gguf_gemv_fast_init(int device);
+
+int int4_dequant(const uint32_t *codes, const float *s, const float *z, void *out, int out_dtype, int N, int K, int G,
+                 long long offset, cudaStream_t st);
+int int4_gemv(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N,
+              int K, int G, cudaStream_t st);
+int fp8_block_dequant(const uint8_t *w, const float *s, void *out, int out_dtype, int R, int C, int bR, int bC,
+                      cudaStream_t st);
+int fp8_block_gemv(const void *x, const uint8_t *w, const float *s, void *y, int act_dtype, int M, int N, int K, int bR,
+                   int bC, cudaStream_t st);
+int moe_gemm(const lb200_moe_args *a, cudaStream_t st);
+int moe_gemm_q(const lb200_moe_args *a, cudaStream_t st);
+
+}  // namespace lb

@@ -1,0 +1,183 @@
+// Grouped expert matmul over routed (token, slot) pairs (contract: reference
+// kernels/cuda/src/moe.cu:1-24, ops/moe.go:96-107):
+//
+//   out[p, :] = w(p) * input[row(p), :] . weights[e, :, :]^T      for every sorted pair
+//
+// Pairs arrive sorted by expert, so expert e owns the index range offsets[e] .. offsets[e+1].
+// The ranges come from boundary detection on the sorted expert ids (no atomics, deterministic);
+// every output row is written by exactly one warp lane set, so the result is deterministic too.
+#include "gguf_decode.cuh"
+
+namespace lb {
+
+// offsets[e] = first sorted index whose expert id is >= e; offsets[E] = M.
+__global__ void moe_offsets_kernel(const int64_t *__restrict__ ids, int32_t *__restrict__ offsets, long long M, int E) {
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (M == 0) {
+    if (i <= E) offsets[i] = 0;
+    return;
+  }
+  if (i >= M) return;
+  long long cur = ids[i], prev = i == 0 ? -1 : ids[i - 1];
+  if (cur >= E) cur = E - 1;  // ids are validated by the caller; clamp so no store leaves the array
+  for (long long e = prev + 1; e <= cur; e++) offsets[e] = (int32_t)i;
+  if (i == M - 1)
+    for (long long e = cur + 1; e <= E; e++) offsets[e] = (int32_t)M;
+}
+
+__global__ void moe_counts_kernel(const int32_t *__restrict__ offsets, int32_t *__restrict__ counts, int E) {
+  int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e < E) counts[e] = offsets[e + 1] - offsets[e];
+}
+
+__device__ __forceinline__ void load8(const float *p, float v[8]) {
+  float4 a = __ldg(reinterpret_cast<const float4 *>(p)), b = __ldg(reinterpret_cast<const float4 *>(p) + 1);
+  v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16 *p, float v[8]) {
+  uint4 u = __ldg(reinterpret_cast<const uint4 *>(p));
+  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float2 f = __bfloat1622float2(h[i]);
+    v[2 * i] = f.x, v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void load8(const __half *p, float v[8]) {
+  uint4 u = __ldg(reinterpret_cast<const uint4 *>(p));
+  const __half2 *h = reinterpret_cast<const __half2 *>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; i++) {
+    float2 f = __half22float2(h[i]);
+    v[2 * i] = f.x, v[2 * i + 1] = f.y;
+  }
+}
+__device__ __forceinline__ void st_out(float *p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void st_out(__nv_bfloat16 *p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void st_out(__half *p, long long i, float v) { p[i] = __float2half_rn(v); }
+
+constexpr int MOE_MT = 8;     // sorted pairs per tile
+constexpr int MOE_WARPS = 8;  // output columns per CTA
+
+// Weight row fetchers: eight consecutive K elements of row n of expert e as f32.
+template <typename T>
+struct DenseRow {
+  const T *row;
+  __device__ DenseRow(const void *w, long long e, int n, int N, int K) : row((const T *)w + ((size_t)e * N + n) * K) {}
+  __device__ __forceinline__ void get(int k, float v[8]) const { load8(row + k, v); }
+};
+template <int QT>
+struct QuantRow {
+  const uint8_t *row;
+  __device__ QuantRow(const void *w, long long e, int n, int N, int K)
+      : row((const uint8_t *)w + ((size_t)e * N + n) * (size_t)(K / block_elems(QT)) * block_bytes(QT)) {}
+  __device__ __forceinline__ void get(int k, float v[8]) const {
+    int b = k / block_elems(QT);
+    decode8<QT>(row + (size_t)b * block_bytes(QT), k - b * block_elems(QT), v);
+  }
+};
+
+// One warp: one output column n, the pairs of one tile.  A tile may straddle experts; each run
+// of equal expert id inside it is handled with that expert's weight row.
+template <typename TI, typename TO, typename Row>
+__global__ void __launch_bounds__(MOE_WARPS * 32) moe_gemm_kernel(
+    const TI *__restrict__ in, const void *__restrict__ w, const int64_t *__restrict__ pairs,
+    const int64_t *__restrict__ ids, const int32_t *__restrict__ offsets, const float *__restrict__ topkw,
+    TO *__restrict__ out, long long M, long long sizeM, int E, int N, int K, int topk, int rowPerPair) {
+  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5);
+  if (n >= N) return;
+  const long long t0 = (long long)blockIdx.y * MOE_MT, t1 = t0 + MOE_MT < M ? t0 + MOE_MT : M;
+  long long i = t0;
+  while (i < t1) {
+    const long long e = ids[i];
+    if (e < 0 || e >= E) {  // not an expert: the pair is skipped, as an out-of-range pair id is
+      i++;
+      continue;
+    }
+    long long r1 = offsets[e + 1];
+    if (r1 > t1) r1 = t1;
+    if (r1 <= i) r1 = i + 1;  // unsorted input: still make progress
+    const int cnt = (int)(r1 - i);
+    const TI *xrow[MOE_MT];
+    long long pr[MOE_MT];
+#pragma unroll
+    for (int m = 0; m < MOE_MT; m++) {
+      long long p = m < cnt ? pairs[i + m] : -1;
+      if (p < 0 || p >= sizeM) p = -1;
+      pr[m] = p;
+      xrow[m] = p < 0 ? nullptr : in + (size_t)(rowPerPair ? p : p / topk) * K;
+    }
+    float acc[MOE_MT];
+#pragma unroll
+    for (int m = 0; m < MOE_MT; m++) acc[m] = 0.f;
+    Row wr(w, e, n, N, K);
+    for (int k = lane * 8; k < K; k += 256) {
+      float wv[8];
+      wr.get(k, wv);
+#pragma unroll
+      for (int m = 0; m < MOE_MT; m++) {
+        if (xrow[m]) {
+          float xv[8];
+          load8(xrow[m] + k, xv);
+#pragma unroll
+          for (int j = 0; j < 8; j++) acc[m] = fmaf(wv[j], xv[j], acc[m]);
+        }
+      }
+    }
+#pragma unroll
+    for (int m = 0; m < MOE_MT; m++) {
+      float v = warp_sum(acc[m]);
+      if (lane == 0 && pr[m] >= 0) st_out(out, pr[m] * N + n, topkw ? v * topkw[pr[m]] : v);
+    }
+    i = r1;
+  }
+}
+
+static int prep(const lb200_moe_args *a, cudaStream_t st) {
+  long long work = a->M > a->E + 1 ? a->M : a->E + 1;
+  moe_offsets_kernel<<<(unsigned)((work + 255) / 256), 256, 0, st>>>(a->expert_ids, a->offsets, a->M, a->E);
+  int rc = launched("moe expert offsets");
+  if (rc) return rc;
+  moe_counts_kernel<<<(a->E + 255) / 256, 256, 0, st>>>(a->offsets, a->counts, a->E);
+  return launched("moe expert counts");
+}
+
+template <typename TI, typename TO, typename Row>
+static int run(const lb200_moe_args *a, cudaStream_t st) {
+  if (a->M == 0 || a->N == 0) return 0;
+  dim3 grid((a->N + MOE_WARPS - 1) / MOE_WARPS, (unsigned)((a->M + MOE_MT - 1) / MOE_MT));
+  if ((a->M + MOE_MT - 1) / MOE_MT > 65535)
+    return fail(LB200_E_TOO_LARGE, "moe_gemm: %lld pairs exceed the kernel's grid", (long long)a->M);
+  moe_gemm_kernel<TI, TO, Row><<<grid, MOE_WARPS * 32, 0, st>>>(
+      (const TI *)a->input, a->weights, a->sorted_pairs, a->expert_ids, a->offsets, a->topk_weights, (TO *)a->out, a->M,
+      a->size_m, a->E, a->N, a->K, a->topk, a->row_per_pair);
+  return launched("moe_gemm");
+}
+
+int moe_gemm(const lb200_moe_args *a, cudaStream_t st) {
+  int rc = prep(a, st);
+  if (rc) return rc;
+  switch (a->dtype) {
+    case LB200_F32: return run<float, float, DenseRow<float>>(a, st);
+    case LB200_BF16: return run<__nv_bfloat16, __nv_bfloat16, DenseRow<__nv_bfloat16>>(a, st);
+    case LB200_F16: return run<__half, __half, DenseRow<__half>>(a, st);
+  }
+  return fail(LB200_E_DTYPE, "moe_gemm: element type %d has no kernel", a->dtype);
+}
+
+int moe_gemm_q(const lb200_moe_args *a, cudaStream_t st) {
+  int rc = prep(a, st);
+  if (rc) return rc;
+  switch (a->dtype) {
+    case LB200_Q4_0: return run<float, float, QuantRow<LB200_Q4_0>>(a, st);
+    case LB200_Q5_0: return run<float, float, QuantRow<LB200_Q5_0>>(a, st);
+    case LB200_Q8_0: return run<float, float, QuantRow<LB200_Q8_0>>(a, st);
+    case LB200_Q4_K: return run<float, float, QuantRow<LB200_Q4_K>>(a, st);
+    case LB200_Q5_K: return run<float, float, QuantRow<LB200_Q5_K>>(a, st);
+    case LB200_Q6_K: return run<float, float, QuantRow<LB200_Q6_K>>(a, st);
+  }
+  return fail(LB200_E_DTYPE, "moe_gemm_q: ggml type %d has no kernel", a->dtype);
+}
+
+}  // namespace lb

@@ -1,0 +1,302 @@
+"""Host side of the operator API for the quantized-weight matmul path.
+
+Mirrors the reference's `ops` package for this path -- same names, argument meaning and error
+behaviour (ops/matmul_q.go, ops/int4.go, ops/fp8_block.go, ops/moe.go) -- on top of the C ABI in
+include/light_b200.h.  Tensors are torch CUDA tensors used only as device buffers; every op
+allocates its output, as the reference ops do, and enqueues on torch's current stream.
+
+There is no CPU path and no PyTorch fallback: a tensor that is not on a CUDA device is an
+error, and so is a missing shared library.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import BF16, F16, F32, Q4_0, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, Light200Error, MoeArgs  # noqa: F401
+
+GGUF_NAMES = {Q4_0: "Q4_0", Q5_0: "Q5_0", Q8_0: "Q8_0", Q4_K: "Q4_K", Q5_K: "Q5_K", Q6_K: "Q6_K"}
+_ACT = {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16}
+
+
+def block_elems(ggml_type: int) -> int:
+    """dtype.DType.BlockElems (dtype/dtype.go:76-83)."""
+    return _lib.lib().light_b200_block_elems(ggml_type)
+
+
+def block_bytes(ggml_type: int) -> int:
+    """dtype.DType.BlockBytes (dtype/dtype.go:85-91)."""
+    return _lib.lib().light_b200_block_bytes(ggml_type)
+
+
+@dataclass
+class QTensor:
+    """A GGUF block-quantized tensor kept in its on-disk layout: `data` is uint8 with the rows'
+    blocks back to back; `shape` is the logical (N, K) or (E, N, K) (gguf/reader.go:237-251)."""
+    data: torch.Tensor
+    ggml_type: int
+    shape: tuple
+
+    def __post_init__(self):
+        be, bb = block_elems(self.ggml_type), block_bytes(self.ggml_type)
+        if be == 0:
+            raise ValueError(f"QTensor: ggml type {self.ggml_type} is not a supported quantized dtype")
+        n = 1
+        for d in self.shape:
+            n *= d
+        if self.shape[-1] % be:
+            raise ValueError(f"QTensor: inner dim {self.shape[-1]} not a multiple of {GGUF_NAMES[self.ggml_type]} "
+                             f"block size {be}")
+        if self.data.dtype != torch.uint8 or self.data.numel() != n // be * bb:
+            raise ValueError(f"QTensor: {self.data.numel()} bytes of {self.data.dtype} for shape {self.shape}, "
+                             f"expected {n // be * bb} uint8")
+
+    @property
+    def device(self):
+        return self.data.device
+
+
+@dataclass
+class Int4:
+    """quant.Int4 (quant/int4.go:12-31): codes u32 (N, K/8) held as int32, scales / zeros f32
+    (N, K/G), group G, optional act-order permutation (K,) int64."""
+    codes: torch.Tensor
+    scales: torch.Tensor
+    zeros: torch.Tensor
+    group: int
+    perm: Optional[torch.Tensor] = None
+
+    def N(self) -> int:
+        return self.codes.shape[0]
+
+    def K(self) -> int:
+        return self.codes.shape[1] * 8
+
+
+@dataclass
+class MoERouting:
+    """ops.MoERouting (ops/moe.go:13-22)."""
+    topk_ids: torch.Tensor      # (T, topk) int64
+    weights: torch.Tensor       # (M,) f32
+    sorted_pairs: torch.Tensor  # (M,) int64, pair ids in expert order
+    sorted_expts: torch.Tensor  # (M,) int64, non-decreasing
+
+
+def _dev(t: torch.Tensor, what: str) -> int:
+    if not t.is_cuda:
+        raise ValueError(f"{what}: tensor is on {t.device}; this library has CUDA kernels only")
+    return t.device.index if t.device.index is not None else torch.cuda.current_device()
+
+
+def _stream(device: int) -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+# --------------------------------------------------------------------------- GGUF
+
+def MatMulQ(x: torch.Tensor, w: QTensor) -> torch.Tensor:
+    """ops.MatMulQ (ops/matmul_q.go:27-75): out (M, N) f32 = x (M, K) f32 . dequant(w (N, K))^T."""
+    if x.dim() != 2 or len(w.shape) != 2:
+        raise ValueError(f"MatMulQ: want x (M,K) and w (N,K); got {tuple(x.shape)}, {tuple(w.shape)}")
+    if x.dtype != torch.float32:
+        raise ValueError(f"MatMulQ: x must be F32, got {x.dtype}")
+    if x.device != w.device:
+        raise ValueError(f"MatMulQ: x on {x.device}, w on {w.device}")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise ValueError(f"MatMulQ: inner dim mismatch (x K={K}, w K={w.shape[1]})")
+    dev = _dev(x, "MatMulQ")
+    xc = x.contiguous()
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().light_b200_matmul_q(w.ggml_type, _ptr(xc), _ptr(w.data), _ptr(out), M, N, K, dev,
+                                              _stream(dev)))
+    return out
+
+
+def Dequantize(w: QTensor) -> torch.Tensor:
+    """quant.Dequantize on a CUDA tensor (quant/cuda_hook.go:28-46): blocks -> f32, same shape."""
+    dev = _dev(w.data, "Dequantize")
+    n = 1
+    for d in w.shape:
+        n *= d
+    out = torch.empty(w.shape, dtype=torch.float32, device=w.device)
+    _lib.check(_lib.lib().light_b200_dequant(w.ggml_type, _ptr(w.data), _ptr(out), n, dev, _stream(dev)))
+    return out
+
+
+# --------------------------------------------------------------------------- int4
+
+def DequantizeInt4(w: Int4, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None, offset: int = 0) -> torch.Tensor:
+    """ops.DequantizeInt4 / dequantizeInt4At (ops/int4.go:13-57): (N, K) at F32 or BF16; with
+    `out` given, writes `offset` elements into it (one slot of a stacked buffer)."""
+    if w.group <= 0 or w.K() % w.group:
+        raise ValueError(f"ops.DequantizeInt4: group {w.group} does not divide K {w.K()}")
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.DequantizeInt4: output {out_dtype}, want F32 or BF16")
+    dev = _dev(w.codes, "DequantizeInt4")
+    if out is None:
+        out = torch.zeros((w.N(), w.K()), dtype=out_dtype, device=w.codes.device)
+    _lib.check(_lib.lib().light_b200_int4_dequant(_ptr(w.codes.contiguous()), _ptr(w.scales.contiguous()),
+                                                  _ptr(w.zeros.contiguous()), _ptr(out), _ACT[out_dtype], w.N(), w.K(),
+                                                  w.group, offset, dev, _stream(dev)))
+    return out
+
+
+def MatMulInt4(x: torch.Tensor, w: Int4) -> torch.Tensor:
+    """ops.MatMulInt4 (ops/int4.go:66-127): x (M, K) F32 or BF16 -> (M, N) at x's dtype."""
+    if x.dim() != 2 or x.shape[1] != w.K():
+        raise ValueError(f"ops.MatMulInt4: x {tuple(x.shape)}, weight ({w.N()}, {w.K()})")
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.MatMulInt4: activations {x.dtype}, want F32 or BF16")
+    dev = _dev(x, "MatMulInt4")
+    xc = x.contiguous()
+    if w.perm is not None:  # act-order GPTQ: gather x's columns into the weight's K order
+        xc = xc.index_select(1, w.perm).contiguous()
+    M, N = x.shape[0], w.N()
+    out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().light_b200_int4_gemv(_ptr(xc), _ptr(w.codes.contiguous()), _ptr(w.scales.contiguous()),
+                                               _ptr(w.zeros.contiguous()), _ptr(out), _ACT[x.dtype], M, N, w.K(),
+                                               w.group, dev, _stream(dev)))
+    return out
+
+
+# --------------------------------------------------------------------------- block-scaled FP8
+
+def DequantizeF8Block(w: torch.Tensor, scale: torch.Tensor, block_r: int, block_c: int,
+                      out_dtype: torch.dtype) -> torch.Tensor:
+    """ops.DequantizeF8Block (ops/fp8_block.go:13-60): e4m3 codes (R, C) (uint8 or float8_e4m3fn),
+    f32 scale (R/bR, C/bC) -> (R, C) at F32 or BF16."""
+    if w.dim() != 2 or scale.dim() != 2:
+        raise ValueError("ops.DequantizeF8Block: rank-2 weight and scale expected")
+    R, Cc = w.shape
+    if block_r <= 0 or block_c <= 0 or R % block_r or Cc % block_c or tuple(scale.shape) != (R // block_r, Cc // block_c):
+        raise ValueError(f"ops.DequantizeF8Block: weight {tuple(w.shape)}, scale {tuple(scale.shape)}, "
+                         f"block ({block_r}, {block_c}) inconsistent")
+    dev = _dev(w, "DequantizeF8Block")
+    out = torch.empty((R, Cc), dtype=out_dtype, device=w.device)
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.DequantizeF8Block: output {out_dtype}, want F32 or BF16")
+    _lib.check(_lib.lib().light_b200_fp8_block_dequant(_ptr(w.contiguous()), _ptr(scale.contiguous()), _ptr(out),
+                                                       _ACT[out_dtype], R, Cc, block_r, block_c, dev, _stream(dev)))
+    return out
+
+
+def MatMulF8Block(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, block_r: int, block_c: int) -> torch.Tensor:
+    """ops.MatMulF8Block (ops/fp8_block.go:165-233): x (M, K) F32 or BF16 -> (M, N) at x's dtype."""
+    if x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1]:
+        raise ValueError(f"ops.MatMulF8Block: x {tuple(x.shape)}, w {tuple(w.shape)}")
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.MatMulF8Block: activations {x.dtype}, want F32 or BF16")
+    M, K = x.shape
+    N = w.shape[0]
+    dev = _dev(x, "MatMulF8Block")
+    out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
+    _lib.check(_lib.lib().light_b200_fp8_block_gemv(_ptr(x.contiguous()), _ptr(w.contiguous()),
+                                                    _ptr(scale.contiguous()), _ptr(out), _ACT[x.dtype], M, N, K,
+                                                    block_r, block_c, dev, _stream(dev)))
+    return out
+
+
+# --------------------------------------------------------------------------- MoE
+
+def MoERouteFromIDs(ids: torch.Tensor, weights: torch.Tensor, T: int, topk: int) -> MoERouting:
+    """ops.MoERouteFromIDs (ops/moe.go:73-99): explicit top-k selection -> expert-sorted pairs."""
+    if ids.numel() != T * topk or weights.numel() != T * topk:
+        raise ValueError(f"moe_route: {ids.numel()} ids / {weights.numel()} weights for {T} x {topk}")
+    flat = ids.reshape(T * topk).to(torch.int64)
+    sorted_expts, sorted_pairs = torch.sort(flat, stable=True)
+    return MoERouting(ids.reshape(T, topk), weights.reshape(T * topk).float(), sorted_pairs, sorted_expts)
+
+
+def MoERoute(probs: torch.Tensor, topk: int, normalize: bool) -> MoERouting:
+    """ops.MoERoute (ops/moe.go:24-71): top-k of router probabilities (T, E), optional renorm."""
+    if probs.dim() != 2 or probs.dtype != torch.float32:
+        raise ValueError(f"moe_route: probs must be (T, E) F32, got {tuple(probs.shape)} {probs.dtype}")
+    T, E = probs.shape
+    if topk < 1 or topk > E:
+        raise ValueError(f"moe_route: topk {topk} out of range [1, {E}]")
+    vals, ids = torch.topk(probs, topk, dim=1)
+    if normalize:
+        vals = vals / vals.sum(dim=1, keepdim=True)
+    return MoERouteFromIDs(ids, vals.contiguous(), T, topk)
+
+
+def _moe_dispatch(op: str, key_dtype: int, quant: bool, inp: torch.Tensor, weights, wshape, routing: MoERouting,
+                  topk_weights: Optional[torch.Tensor], topk: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """moeGemmDispatch (ops/moe.go:124-204)."""
+    if inp.dim() != 2 or len(wshape) != 3:
+        raise ValueError(f"{op}: input (rows, K) and weights (E, N, K) required, got {tuple(inp.shape)} / {tuple(wshape)}")
+    E, N, K = wshape
+    if inp.shape[1] != K:
+        raise ValueError(f"{op}: input K {inp.shape[1]} != weights K {K}")
+    M = routing.sorted_pairs.shape[0]
+    if routing.sorted_expts.shape[0] != M or routing.sorted_pairs.dtype != torch.int64 or \
+            routing.sorted_expts.dtype != torch.int64:
+        raise ValueError(f"{op}: routing must hold M I64 pair ids and M I64 expert ids")
+    if inp.shape[0] == M:
+        row_per_pair = True
+    elif inp.shape[0] == M // topk:
+        row_per_pair = False
+    else:
+        raise ValueError(f"{op}: input rows {inp.shape[0]} must be M={M} (per pair) or M/topk={M // topk} (per token)")
+    if topk_weights is not None and (topk_weights.dtype != torch.float32 or topk_weights.numel() != M):
+        raise ValueError(f"{op}: topkWeights must be F32 with {M} elements")
+    dev = _dev(inp, op)
+    inc = inp.contiguous()
+    counts = torch.zeros(E, dtype=torch.int32, device=inp.device)
+    offsets = torch.zeros(E + 1, dtype=torch.int32, device=inp.device)
+    out = torch.zeros((M, N), dtype=out_dtype, device=inp.device)
+    a = MoeArgs(input=inc.data_ptr(), weights=weights.data_ptr(), sorted_pairs=routing.sorted_pairs.contiguous().data_ptr(),
+                expert_ids=routing.sorted_expts.contiguous().data_ptr(), counts=counts.data_ptr(),
+                offsets=offsets.data_ptr(),
+                topk_weights=0 if topk_weights is None else topk_weights.contiguous().data_ptr(), out=out.data_ptr(),
+                M=M, size_m=M, E=E, N=N, K=K, topk=topk, row_per_pair=int(row_per_pair), dtype=key_dtype)
+    fn = _lib.lib().light_b200_moe_gemm_q if quant else _lib.lib().light_b200_moe_gemm
+    _lib.check(fn(C.byref(a), dev, _stream(dev)))
+    return out
+
+
+def MoEGemm(inp: torch.Tensor, weights: torch.Tensor, routing: MoERouting, topk_weights: Optional[torch.Tensor],
+            topk: int) -> torch.Tensor:
+    """ops.MoEGemm (ops/moe.go:101-122): dense stacked experts (E, N, K) at input's dtype."""
+    if inp.dim() != 2 or weights.dim() != 3:
+        raise ValueError(f"moe_gemm: input (rows, K) and weights (E, N, K) required, got {tuple(inp.shape)} / "
+                         f"{tuple(weights.shape)}")
+    if inp.dtype != weights.dtype:
+        raise ValueError(f"moe_gemm: input {inp.dtype} / weights {weights.dtype} dtype mismatch")
+    if inp.dtype not in _ACT:
+        raise ValueError(f"moe_gemm: unsupported dtype {inp.dtype}")
+    return _moe_dispatch("moe_gemm", _ACT[inp.dtype], False, inp, weights.contiguous(), tuple(weights.shape), routing,
+                         topk_weights, topk, inp.dtype)
+
+
+def MoEGemmQ(x: torch.Tensor, w: QTensor, routing: MoERouting, topk_weights: Optional[torch.Tensor],
+             topk: int) -> torch.Tensor:
+    """ops.MoEGemmQ (ops/moe.go:242-265): GGUF block-quantized experts (E, N, K), x f32, out f32."""
+    if x.dtype != torch.float32:
+        raise ValueError(f"moe_gemm_q: x must be F32, got {x.dtype}")
+    if len(w.shape) != 3:
+        raise ValueError(f"moe_gemm_q: w must be a quantized (E, N, K) tensor, got {tuple(w.shape)}")
+    return _moe_dispatch("moe_gemm_q", w.ggml_type, True, x, w.data, tuple(w.shape), routing, topk_weights, topk,
+                         torch.float32)
+
+
+def MoECombine(pair_out: torch.Tensor, topk: int) -> torch.Tensor:
+    """ops.MoECombine (ops/moe.go:206-240): sum of the topk slot rows, (M, N) -> (T, N), slot 0 first."""
+    M, N = pair_out.shape
+    if M % topk:
+        raise ValueError(f"moe_combine: {M} rows not divisible by topk {topk}")
+    v = pair_out.contiguous().reshape(M // topk, topk, N)
+    acc = v[:, 0, :]
+    for s in range(1, topk):
+        acc = acc + v[:, s, :]
+    return acc.contiguous()

@@ -1,0 +1,233 @@
+"""ctypes binding of the CPU oracle (oracle/light_oracle.c).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by ``__graft_entry__.smoke()`` and by the
+``cpu_baseline`` / ``--impl reference`` legs of bench.py -- never by the ``light_b200``
+package.  Arrays are numpy, contiguous, little-endian.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "liblight_oracle.so")
+
+# ggml on-disk type codes (gguf/types.go:39-58 of the reference)
+Q4_0, Q5_0, Q8_0, Q4_K, Q5_K, Q6_K = 2, 6, 8, 12, 13, 14
+GGUF_TYPES = {"q4_0": Q4_0, "q5_0": Q5_0, "q8_0": Q8_0, "q4_k": Q4_K, "q5_k": Q5_K, "q6_k": Q6_K}
+
+
+def build(force: bool = False) -> None:
+    """Compile liblight_oracle.so (and, when the reference checkout is present, its CUDA
+    kernels into oracle/_ref/)."""
+    if force and os.path.exists(LIB_PATH):
+        os.remove(LIB_PATH)
+    subprocess.run(["make", "-s", "-C", HERE], check=True)
+
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        src = os.path.join(HERE, "light_oracle.c")
+        if not os.path.exists(LIB_PATH) or os.path.getmtime(LIB_PATH) < os.path.getmtime(src):
+            build()
+        _lib = C.CDLL(LIB_PATH)
+        _lib.lo_f16_to_f32.restype = C.c_float
+        _lib.lo_f16_to_f32.argtypes = [C.c_uint16]
+        _lib.lo_f32_to_f16.restype = C.c_uint16
+        _lib.lo_f32_to_f16.argtypes = [C.c_float]
+        _lib.lo_f32_to_bf16.restype = C.c_uint16
+        _lib.lo_f32_to_bf16.argtypes = [C.c_float]
+        _lib.lo_bf16_to_f32.restype = C.c_float
+        _lib.lo_bf16_to_f32.argtypes = [C.c_uint16]
+        _lib.lo_e4m3_to_f32.restype = C.c_float
+        _lib.lo_e4m3_to_f32.argtypes = [C.c_uint8]
+        _lib.lo_f32_to_e4m3.restype = C.c_uint8
+        _lib.lo_f32_to_e4m3.argtypes = [C.c_float]
+    return _lib
+
+
+def _p(a: np.ndarray | None):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"]
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _chk(rc: int, what: str) -> None:
+    if rc != 0:
+        raise ValueError(f"oracle {what}: rejected arguments (rc={rc})")
+
+
+def block_elems(dt: int) -> int:
+    return lib().lo_block_elems(dt)
+
+
+def block_bytes(dt: int) -> int:
+    return lib().lo_block_bytes(dt)
+
+
+def f16_to_f32(h: int) -> float:
+    return lib().lo_f16_to_f32(h)
+
+
+def f32_to_f16(f: float) -> int:
+    return lib().lo_f32_to_f16(f)
+
+
+def f32_to_bf16(f: float) -> int:
+    return lib().lo_f32_to_bf16(f)
+
+
+def bf16_to_f32(b: int) -> float:
+    return lib().lo_bf16_to_f32(b)
+
+
+def e4m3_to_f32(c: int) -> float:
+    return lib().lo_e4m3_to_f32(c)
+
+
+def f32_to_e4m3(f: float) -> int:
+    return lib().lo_f32_to_e4m3(f)
+
+
+def e4m3_table() -> np.ndarray:
+    return np.array([e4m3_to_f32(i) for i in range(256)], dtype=np.float32)
+
+
+def dequant(dt: int, raw: np.ndarray, n_elems: int) -> np.ndarray:
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    out = np.empty(n_elems, dtype=np.float32)
+    _chk(lib().lo_dequant(dt, _p(raw), _p(out), C.c_int64(n_elems)), "dequant")
+    return out
+
+
+def quantize_q8_0(src: np.ndarray) -> np.ndarray:
+    src = np.ascontiguousarray(src, dtype=np.float32).ravel()
+    out = np.empty(src.size // 32 * 34, dtype=np.uint8)
+    _chk(lib().lo_quantize_q8_0(_p(src), _p(out), C.c_int64(src.size)), "quantize_q8_0")
+    return out
+
+
+def matmul_q(dt: int, x: np.ndarray, w: np.ndarray, N: int, threads: int = 1) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    M, K = x.shape
+    out = np.empty((M, N), dtype=np.float32)
+    _chk(lib().lo_matmul_q(dt, _p(x), _p(w), _p(out), M, N, K, threads), "matmul_q")
+    return out
+
+
+def int4_dequant(codes, s, z, G: int, bf16: bool = False) -> np.ndarray:
+    codes = np.ascontiguousarray(codes, dtype=np.uint32)
+    s = np.ascontiguousarray(s, dtype=np.float32)
+    z = np.ascontiguousarray(z, dtype=np.float32)
+    N, K = codes.shape[0], codes.shape[1] * 8
+    out = np.empty((N, K), dtype=np.uint16 if bf16 else np.float32)
+    _chk(lib().lo_int4_dequant(_p(codes), _p(s), _p(z), _p(out), N, K, G, int(bf16)), "int4_dequant")
+    return out
+
+
+def int4_matmul(x, codes, s, z, G: int, threads: int = 1) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    codes = np.ascontiguousarray(codes, dtype=np.uint32)
+    s = np.ascontiguousarray(s, dtype=np.float32)
+    z = np.ascontiguousarray(z, dtype=np.float32)
+    M, K = x.shape
+    N = codes.shape[0]
+    out = np.empty((M, N), dtype=np.float32)
+    _chk(lib().lo_int4_matmul(_p(x), _p(codes), _p(s), _p(z), _p(out), M, N, K, G, threads), "int4_matmul")
+    return out
+
+
+def int4_from_gptq(qweight, qzeros, scales, group: int, v2: bool = False):
+    qweight = np.ascontiguousarray(qweight).view(np.uint32)
+    qzeros = np.ascontiguousarray(qzeros).view(np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    K, N = qweight.shape[0] * 8, qweight.shape[1]
+    G = K // group
+    codes = np.empty((N, K // 8), np.uint32)
+    sc = np.empty((N, G), np.float32)
+    zr = np.empty((N, G), np.float32)
+    _chk(lib().lo_int4_from_gptq(_p(qweight), _p(qzeros), _p(scales), K, N, group, int(v2), _p(codes), _p(sc), _p(zr)),
+         "int4_from_gptq")
+    return codes, sc, zr
+
+
+def int4_from_awq(qweight, qzeros, scales, group: int):
+    qweight = np.ascontiguousarray(qweight).view(np.uint32)
+    qzeros = np.ascontiguousarray(qzeros).view(np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float32)
+    K, N = qweight.shape[0], qweight.shape[1] * 8
+    G = K // group
+    codes = np.empty((N, K // 8), np.uint32)
+    sc = np.empty((N, G), np.float32)
+    zr = np.empty((N, G), np.float32)
+    _chk(lib().lo_int4_from_awq(_p(qweight), _p(qzeros), _p(scales), K, N, group, _p(codes), _p(sc), _p(zr)),
+         "int4_from_awq")
+    return codes, sc, zr
+
+
+def fp8_block_dequant(w, s, bR: int, bC: int, bf16: bool = False) -> np.ndarray:
+    w = np.ascontiguousarray(w, dtype=np.uint8)
+    s = np.ascontiguousarray(s, dtype=np.float32)
+    R, Cc = w.shape
+    out = np.empty((R, Cc), dtype=np.uint16 if bf16 else np.float32)
+    _chk(lib().lo_fp8_block_dequant(_p(w), _p(s), _p(out), R, Cc, bR, bC, int(bf16)), "fp8_block_dequant")
+    return out
+
+
+def matmul_f32_tb(x, w, threads: int = 1) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    M, K = x.shape
+    N = w.shape[0]
+    out = np.empty((M, N), dtype=np.float32)
+    _chk(lib().lo_matmul_f32_tb(_p(x), _p(w), _p(out), M, N, K, threads), "matmul_f32_tb")
+    return out
+
+
+def moe_sort_pairs(ids, E: int):
+    ids = np.ascontiguousarray(ids, dtype=np.int64).ravel()
+    sp = np.empty_like(ids)
+    se = np.empty_like(ids)
+    _chk(lib().lo_moe_sort_pairs(_p(ids), C.c_int64(ids.size), E, _p(sp), _p(se)), "moe_sort_pairs")
+    return sp, se
+
+
+def moe_gemm_f32(inp, w, pairs, expts, topkw, sizeM: int, topk: int, row_per_pair: bool, threads: int = 1,
+                 out: np.ndarray | None = None) -> np.ndarray:
+    inp = np.ascontiguousarray(inp, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    pairs = np.ascontiguousarray(pairs, dtype=np.int64)
+    expts = np.ascontiguousarray(expts, dtype=np.int64)
+    if topkw is not None:
+        topkw = np.ascontiguousarray(topkw, dtype=np.float32)
+    E, N, K = w.shape
+    if out is None:
+        out = np.zeros((sizeM, N), dtype=np.float32)
+    _chk(lib().lo_moe_gemm_f32(_p(inp), _p(w), _p(pairs), _p(expts), _p(topkw), _p(out), C.c_int64(pairs.size),
+                               C.c_int64(sizeM), N, K, topk, int(row_per_pair), threads), "moe_gemm_f32")
+    return out
+
+
+def deepseek_route_sigmoid(logits, bias, topk: int, norm_topk: bool = True):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=np.float32)
+    T, E = logits.shape
+    ids = np.empty((T, topk), np.int64)
+    ws = np.empty((T, topk), np.float32)
+    _chk(lib().lo_deepseek_route_sigmoid(_p(logits), _p(bias), T, E, topk, int(norm_topk), _p(ids), _p(ws)),
+         "deepseek_route")
+    return ids, ws
+
+
+def has_avx2() -> bool:
+    return bool(lib().lo_has_avx2())
