@@ -1,0 +1,353 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-weight matmul path: Llama-3-8B-shape decode at GGUF Q4_K_M.
+
+One step = one decode step's worth of quantized linears for M tokens: 32 layers x
+{q, k, v, o, gate, up as Q4_K; down as Q6_K} plus the Q6_K lm_head, 225 fused dequant-matmul
+launches reading 4.84 GB of block-quantized weights once.  Weights are random-init from a seed
+(N(0, 0.02) before quantization) directly in HBM; activations are N(0, 1).
+
+    python bench.py --gpus N --steps K --warmup W            # this library, rank-per-GPU
+    python bench.py --impl reference ...                     # the CPU port of the reference path
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from light_b200 import _lib, ops, synth  # noqa: E402
+
+HID, FFN, NKV, VOCAB, LAYERS = 4096, 14336, 1024, 128256, 32
+# (name, N, K, ggml type) of one decoder layer's linears, in call order
+LAYER = [("q", HID, HID, ops.Q4_K), ("k", NKV, HID, ops.Q4_K), ("v", NKV, HID, ops.Q4_K), ("o", HID, HID, ops.Q4_K),
+         ("gate", FFN, HID, ops.Q4_K), ("up", FFN, HID, ops.Q4_K), ("down", HID, FFN, ops.Q6_K)]
+HEAD = ("lm_head", VOCAB, HID, ops.Q6_K)
+
+
+def weight_bytes(N, K, dt):
+    return N * synth.row_bytes(dt, K)
+
+
+def algorithmic_bytes(N, K, dt, M):
+    """weights once + activations in + outputs out."""
+    return weight_bytes(N, K, dt) + M * K * 4 + M * N * 4
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(index).uuid)
+                self.h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": 0x8, "sw_power_cap": 0x4, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                get = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+                r = get(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def __enter__(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["nvml unavailable"]}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+class Chain:
+    """The quantized linears of one decode step on one GPU, each weight row-split over `world` ranks."""
+
+    def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0):
+        self.device, self.M, self.rank, self.world = device, M, rank, world
+        self.lin = []  # (name, N_local, N, K, dt, weight bytes tensor)
+        for l in range(layers):
+            for i, (name, N, K, dt) in enumerate(LAYER):
+                self.lin.append(self._make(f"l{l}.{name}", N, K, dt, seed * 100003 + l * 16 + i))
+        self.lin.append(self._make(*HEAD, seed * 100003 + 99991))
+        g = torch.Generator(device=device)
+        g.manual_seed(seed + 7)
+        self.x = {HID: torch.randn(M, HID, generator=g, device=device), FFN: torch.randn(M, FFN, generator=g, device=device)}
+        self.out = [torch.empty(M, e[2], device=device) for e in self.lin]  # full-width outputs (gathered when world > 1)
+        self.local = [torch.empty(M, e[1], device=device) for e in self.lin] if world > 1 else self.out
+        self.dev_index = device.index or 0
+
+    def _make(self, name, N, K, dt, seed):
+        assert N % self.world == 0
+        nl = N // self.world
+        # every rank draws only its own rows (a row split is a byte slice of the block layout)
+        w = synth.gaussian_weight(seed * 8 + self.rank, dt, nl, K, device=self.device)
+        return (name, nl, N, K, dt, w)
+
+    def launch(self, i, stream):
+        name, nl, N, K, dt, w = self.lin[i]
+        _lib.check(_lib.lib().light_b200_matmul_q(dt, C.c_void_p(self.x[K].data_ptr()), C.c_void_p(w.data_ptr()),
+                                                  C.c_void_p(self.local[i].data_ptr()), self.M, nl, K, self.dev_index,
+                                                  C.c_void_p(stream)))
+
+    def step(self, only=None):
+        import torch.distributed as dist
+
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        n = 0
+        for i, e in enumerate(self.lin):
+            if only is not None and e[4] != only:
+                continue
+            self.launch(i, st)
+            n += 1
+            if self.world > 1:
+                if self.M == 1:
+                    dist.all_gather_into_tensor(self.out[i].view(-1), self.local[i].view(-1))
+                else:  # rank slices are column blocks of (M, N): gather then interleave
+                    tmp = torch.empty(self.world, self.M, e[1], device=self.device)
+                    dist.all_gather_into_tensor(tmp, self.local[i])
+                    self.out[i].view(self.M, self.world, e[1]).copy_(tmp.permute(1, 0, 2))
+        return n
+
+    def bytes_per_step(self, only=None):
+        return sum(algorithmic_bytes(e[1], e[3], e[4], self.M) for e in self.lin if only is None or e[4] == only)
+
+    def launches(self, only=None):
+        return sum(1 for e in self.lin if only is None or e[4] == only)
+
+
+def capture(fn, device):
+    """Warm up on a side stream, then capture fn() into a CUDA graph (as the reference's decode loop
+    replays its step, models/decode_graph.go:58-205)."""
+    s = torch.cuda.Stream(device)
+    s.wait_stream(torch.cuda.current_stream(device))
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            fn()
+    torch.cuda.current_stream(device).wait_stream(s)
+    torch.cuda.synchronize(device)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
+
+
+def timed(replay, steps, warmup, device, barrier):
+    for _ in range(warmup):
+        replay()
+    torch.cuda.synchronize(device)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        replay()
+    e1.record()
+    torch.cuda.synchronize(device)
+    barrier()
+    return e0.elapsed_time(e1)  # ms
+
+
+def cpu_reference(M, threads, steps, warmup):
+    """The reference's CPU implementation of the path (kernels/cpu/quant_matmul.go matmulQCPU), as
+    restated in oracle/light_oracle.c, on a bounded sample: one decoder layer (7 linears) + nothing
+    else per timed step; the whole-step time is 32 x that + one lm_head pass timed once."""
+    from oracle import binding as ob
+
+    rng = np.random.Generator(np.random.Philox(5))
+    xs = {HID: rng.standard_normal((M, HID)).astype(np.float32), FFN: rng.standard_normal((M, FFN)).astype(np.float32)}
+    # decode time does not depend on the code values: random blocks stand in for quantized Gaussians here
+    ws = [(N, K, dt, synth.random_blocks(900 + i, dt, N, K)) for i, (_, N, K, dt) in enumerate(LAYER)]
+
+    def layer():
+        for N, K, dt, w in ws:
+            ob.matmul_q(dt, xs[K], w, N, threads=threads)
+
+    for _ in range(max(1, min(warmup, 2))):
+        layer()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        layer()
+    t_layer = (time.perf_counter() - t0) / steps
+    _, N, K, dt = HEAD
+    head = synth.random_blocks(999, dt, N, K)
+    ob.matmul_q(dt, xs[K], head, N, threads=threads)
+    t0 = time.perf_counter()
+    ob.matmul_q(dt, xs[K], head, N, threads=threads)
+    t_head = time.perf_counter() - t0
+    t_step = LAYERS * t_layer + t_head
+    return M / t_step, t_step, f"{steps} x one decoder layer (7 linears, 137.8 MB) + 1 x lm_head (430.9 MB), " \
+                               f"scaled to 32 layers + lm_head; M={M}"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="light_b200", choices=["light_b200", "reference"])
+    ap.add_argument("--tokens", type=int, default=1, help="tokens per decode step (M)")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers (default: the full 32)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    M = args.tokens
+    metric, unit = "llama3_8b_q4_k_m_decode_tokens_per_s", "tok/s"
+    workload = (f"configs[1]: Llama-3-8B-shape decoder at GGUF Q4_K_M, batched decode M={M}, the 225 quantized "
+                f"linears of one step (32 x [q,k,v,o,gate,up Q4_K; down Q6_K] + Q6_K lm_head), linear chain only")
+
+    if args.impl == "reference":
+        if rank != 0:
+            return 0
+        threads = os.cpu_count() or 1
+        steps = max(1, min(args.steps, 5))
+        v, t_step, sample = cpu_reference(M, threads, steps, args.warmup)
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload, "timed_steps_of_sample": steps},
+            "cpu_baseline": {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return 0
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+        barrier = lambda: dist.barrier()  # noqa: E731
+    else:
+        barrier = lambda: None  # noqa: E731
+    _lib.check(_lib.lib().light_b200_init(local))
+
+    chain = Chain(device, M, rank, world, layers=args.layers)
+    torch.cuda.synchronize(device)
+    launches_per_step = chain.launches()
+    graph = capture(chain.step, device)
+
+    with ClockSampler(local) as clk:
+        ms = timed(graph.replay, args.steps, args.warmup, device, barrier)
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = M / (ms_per_step * 1e-3)
+
+    # ---- roofline of the dominant kernel: the Q4_K decode GEMV, alone in a graph of its own
+    peak, peak_kind = load_peaks()
+    g4 = capture(lambda: chain.step(only=ops.Q4_K), device)
+    ms4 = timed(g4.replay, args.steps, max(3, args.warmup), device, barrier)
+    n4 = chain.launches(ops.Q4_K)
+    b4 = chain.bytes_per_step(ops.Q4_K) / n4
+    us4 = ms4 * 1e3 / (args.steps * n4)
+    achieved = b4 / (us4 * 1e-6) / 1e9
+    g6 = capture(lambda: chain.step(only=ops.Q6_K), device)
+    ms6 = timed(g6.replay, args.steps, max(3, args.warmup), device, barrier)
+    n6 = chain.launches(ops.Q6_K)
+    gbs6 = chain.bytes_per_step(ops.Q6_K) / (ms6 * 1e-3 / args.steps) / 1e9
+    roofline = {"bound": "hbm", "kernel": "q4k_gemv_mma_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_source": f"of {peak_kind}", "traffic": None,
+                "bytes_per_launch": b4, "us_per_launch": us4, "launches_per_step": n4,
+                "q6k_gemv_gbs": gbs6, "q6k_launches_per_step": n6,
+                "whole_step_gbs": chain.bytes_per_step() / (ms_per_step * 1e-3) / 1e9}
+
+    # ---- end to end: host activations in, logits out, every step
+    hx = {k: v.cpu().pin_memory() for k, v in chain.x.items()}
+    hlog = torch.empty(M, VOCAB).pin_memory()
+    h2d = sum(v.numel() * 4 for v in hx.values())
+    d2h = hlog.numel() * 4
+
+    def e2e_step():
+        for k in hx:
+            chain.x[k].copy_(hx[k], non_blocking=True)
+        graph.replay()
+        hlog.copy_(chain.out[-1], non_blocking=True)
+        torch.cuda.current_stream(device).synchronize()
+
+    ms_e = timed(e2e_step, args.steps, max(3, args.warmup), device, barrier)
+    te = torch.tensor([ms_e], device=device)
+    if world > 1:
+        dist.all_reduce(te, op=dist.ReduceOp.MAX)
+    e2e_val = M / (float(te.item()) / args.steps * 1e-3)
+
+    line = {
+        "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32 activations x Q4_K/Q6_K weights, f32 accumulate", "data": "synthetic",
+        "config": {"workload": workload, "tokens_per_step": M, "layers": args.layers,
+                   "weights_bytes_per_step": sum(weight_bytes(e[2], e[3], e[4]) for e in chain.lin),
+                   "parallelism": f"rows of every weight split over {world} GPU(s)" + (", NCCL all-gather per linear" if world > 1 else ""),
+                   "l2": "inputs (4.84 GB of weights per step) exceed the 126 MB L2", "launch": "CUDA graph replay"},
+        "roofline": roofline,
+        "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clk.summary(),
+    }
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            threads = os.cpu_count() or 1
+            v, t_step, sample = cpu_reference(M, threads, 3, 1)
+            line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

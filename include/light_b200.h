@@ -30,6 +30,12 @@ extern "C" {
 
 #define LIGHT_B200_ABI_VERSION 1
 
+#if defined(__GNUC__)
+#define LB200_API __attribute__((visibility("default")))
+#else
+#define LB200_API
+#endif
+
 /* ggml on-disk type codes (reference gguf/types.go:39-58) of the formats with a fused kernel
  * (reference kernels/cuda/matmul_q.go:17-24). */
 enum {
@@ -59,56 +65,56 @@ enum {
  * checks the compute capability, sets kernel attributes).  Every other entry point does this
  * lazily, so calling it is optional; it mirrors cudart.SetDevice + module load in the
  * reference launchers (kernels/cuda/matmul_q.go:52-58, kernels/cuda/loader.go:99-196). */
-int light_b200_init(int device);
+LB200_API int light_b200_init(int device);
 
 /* Copies the calling thread's last error text into buf (NUL terminated); returns its length.
  * Reference: the `cudart: <op>: <msg> (code N)` errors of internal/cudart/runtime.go:335-363. */
-int light_b200_last_error(char *buf, size_t n);
+LB200_API int light_b200_last_error(char *buf, size_t n);
 
-int light_b200_abi_version(void);
+LB200_API int light_b200_abi_version(void);
 
 /* Number of kernels this library has launched on any stream since load (monotonic). */
-unsigned long long light_b200_launch_count(void);
+LB200_API unsigned long long light_b200_launch_count(void);
 
 /* Block geometry: elements / bytes per block, 0 for an unknown type
  * (reference dtype/dtype.go:53-102 blockInfo, BlockElems, BlockBytes). */
-int light_b200_block_elems(int ggml_type);
-int light_b200_block_bytes(int ggml_type);
+LB200_API int light_b200_block_elems(int ggml_type);
+LB200_API int light_b200_block_bytes(int ggml_type);
 
 /* Registry key {matmul_q, CUDA, <w dtype>} (reference kernels/cuda/matmul_q.go:44-91,
  * ops/matmul_q.go:27-75):  out (M,N) f32 = x (M,K) f32 . dequant(w (N,K) blocks)^T.
  * K must be a multiple of the block size.  Any M >= 0 is taken (the reference routes M >= 8 to
  * dequantize + SGEMM; here one call covers decode and prefill). */
-int light_b200_matmul_q(int ggml_type, const float *x, const void *w, float *out, int M, int N, int K, int device,
+LB200_API int light_b200_matmul_q(int ggml_type, const float *x, const void *w, float *out, int M, int N, int K, int device,
                         void *stream);
 
 /* The CUDA dequantize hook, quant.RegisterCUDADequant (reference quant/cuda_hook.go:13-46,
  * kernels/cuda/dequant.go:15-75):  dst f32 [n_elems] = dequant(src blocks).  n_elems must be a
  * whole number of blocks.  Bit-identical to the reference's CPU decoders. */
-int light_b200_dequant(int ggml_type, const void *src, float *dst, int64_t n_elems, int device, void *stream);
+LB200_API int light_b200_dequant(int ggml_type, const void *src, float *dst, int64_t n_elems, int device, void *stream);
 
 /* Registry key {int4_dequant, CUDA, F32|BF16} (reference kernels/cuda/int4.go:43-69):
  * canonical 4-bit layout (reference quant/int4.go:12-31) codes u32 (N,K/8), scales and zeros
  * f32 (N,K/G) -> out (N,K) at out_dtype, written `offset` ELEMENTS into `out`;
  * W = s * (code - z) formed in f32 and rounded once.  G % 8 == 0. */
-int light_b200_int4_dequant(const uint32_t *codes, const float *scales, const float *zeros, void *out, int out_dtype,
+LB200_API int light_b200_int4_dequant(const uint32_t *codes, const float *scales, const float *zeros, void *out, int out_dtype,
                             int N, int K, int group, int64_t offset, int device, void *stream);
 
 /* Registry key {int4_gemv, CUDA, F32|BF16} (reference kernels/cuda/int4.go:76-101):
  * y (M,N) at act_dtype = x (M,K) at act_dtype . W^T.  K % 32 == 0, G % 32 == 0.  The reference
  * kernel stops at M = 8 (ops/int4.go:58-59); this one takes any M >= 0. */
-int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *scales, const float *zeros, void *y,
+LB200_API int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *scales, const float *zeros, void *y,
                          int act_dtype, int M, int N, int K, int group, int device, void *stream);
 
 /* Registry key {fp8_block_dequant, CUDA, F32|BF16} (reference kernels/cuda/fp8_block.go:44-69):
  * w e4m3fn codes (R,C), scale f32 (R/bR, C/bC) -> out (R,C) = f32(w) * scale, rounded once.
  * C % 4 == 0, bC % 4 == 0, R % bR == 0, C % bC == 0. */
-int light_b200_fp8_block_dequant(const uint8_t *w, const float *scale, void *out, int out_dtype, int R, int C,
+LB200_API int light_b200_fp8_block_dequant(const uint8_t *w, const float *scale, void *out, int out_dtype, int R, int C,
                                  int block_r, int block_c, int device, void *stream);
 
 /* Registry key {fp8_block_gemv, CUDA, F32|BF16} (reference kernels/cuda/fp8_block.go:76-105):
  * y (M,N) = x (M,K) . (w * scale)^T.  K % 16 == 0, bC % 16 == 0.  Any M >= 0 (reference: M <= 8). */
-int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N,
+LB200_API int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N,
                               int K, int block_r, int block_c, int device, void *stream);
 
 /* Arguments of the grouped expert matmuls.  Mirrors the Inputs / Attrs of the reference
@@ -140,11 +146,11 @@ typedef struct lb200_moe_args {
 } lb200_moe_args;
 
 /* Registry key {moe_gemm, CUDA, F32|BF16|F16} (reference kernels/cuda/moe.go:21-97). */
-int light_b200_moe_gemm(const lb200_moe_args *args, int device, void *stream);
+LB200_API int light_b200_moe_gemm(const lb200_moe_args *args, int device, void *stream);
 
 /* Registry key {moe_gemm_q, CUDA, <w dtype>} (reference kernels/cuda/moe.go:99-141):
  * x f32, GGUF block-quantized experts, out f32. */
-int light_b200_moe_gemm_q(const lb200_moe_args *args, int device, void *stream);
+LB200_API int light_b200_moe_gemm_q(const lb200_moe_args *args, int device, void *stream);
 
 #ifdef __cplusplus
 }

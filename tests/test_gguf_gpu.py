@@ -1,0 +1,187 @@
+"""GPU parity of the GGUF path (matmul_q, dequant) through the C ABI, against the CPU oracle and
+against the reference's own CUDA kernels compiled for sm_100a (oracle/_ref)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import RefCuda, max_rel, rel_l2
+from light_b200 import ops, synth
+
+pytestmark = pytest.mark.gpu
+
+FORMATS = {"q4_0": ops.Q4_0, "q5_0": ops.Q5_0, "q8_0": ops.Q8_0, "q4_k": ops.Q4_K, "q5_k": ops.Q5_K, "q6_k": ops.Q6_K}
+TOL_REL_L2 = 1e-3  # stated bound on f32 outputs vs the reference's CUDA path and vs the f64 oracle
+
+
+def _qt(raw: np.ndarray, dt, shape, dev):
+    return ops.QTensor(torch.from_numpy(raw.reshape(-1)).to(dev), dt, shape)
+
+
+@pytest.mark.parametrize("name", list(FORMATS))
+def test_dequant_bit_exact(cuda, oracle, name):
+    """quant/dequant_cuda_test.go:15-62 asks for 1e-5; here the bar is bit equality with the CPU
+    decoders, on random blocks (every code value) and on Gaussian weights."""
+    dt = FORMATS[name]
+    N, K = 7, 1024
+    raws = [synth.random_blocks(21, dt, N, K)]
+    if dt in synth.QUANTIZERS:
+        raws.append(synth.gaussian_weight(22, dt, N, K).numpy())
+    for raw in raws:
+        got = ops.Dequantize(_qt(raw, dt, (N, K), cuda)).cpu().numpy()
+        want = oracle.dequant(dt, raw.reshape(-1), N * K).reshape(N, K)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_dequant_rejects_partial_block(cuda):
+    from light_b200 import _lib
+
+    buf = torch.zeros(1024, dtype=torch.uint8, device=cuda)
+    out = torch.zeros(1024, device=cuda)
+    rc = _lib.lib().light_b200_dequant(ops.Q4_K, C.c_void_p(buf.data_ptr()), C.c_void_p(out.data_ptr()), 100, 0, None)
+    assert rc == -2
+
+
+@pytest.mark.parametrize("name", list(FORMATS))
+@pytest.mark.parametrize("K", [1024, 1792])
+def test_matmul_q_reference_shapes(cuda, oracle, name, K):
+    """ops/matmul_q_test.go:105-146: M in {1, 4, 9} (plus 2, 3, 5) x K in {1024, 1792}, N = 13,
+    random bytes with pinned f16 scales, max-rel <= 2e-4; plus the 1e-3 rel-L2 bound."""
+    dt = FORMATS[name]
+    N = 13
+    raw = synth.random_blocks(31, dt, N, K)
+    deq = oracle.dequant(dt, raw.reshape(-1), N * K).reshape(N, K).astype(np.float64)
+    w = _qt(raw, dt, (N, K), cuda)
+    g = torch.Generator().manual_seed(32)
+    for M in (1, 2, 3, 4, 5, 9):
+        x = torch.randn(M, K, generator=g)
+        got = ops.MatMulQ(x.to(cuda), w).cpu().numpy()
+        want = x.numpy().astype(np.float64) @ deq.T
+        scale = np.abs(want).max()
+        assert np.max(np.abs(got - want)) / scale <= 2e-4, (name, K, M)
+        assert rel_l2(got, want) <= TOL_REL_L2
+
+
+@pytest.mark.parametrize("name,N,K", [("q4_k", 16, 256), ("q4_k", 37, 2048), ("q4_k", 1, 4096), ("q4_k", 100, 14336),
+                                      ("q6_k", 16, 512), ("q6_k", 37, 2048), ("q6_k", 5, 14336), ("q6_k", 9, 768),
+                                      ("q8_0", 33, 4096)])
+def test_matmul_q_decode_kernels(cuda, oracle, name, N, K):
+    """The decode kernels (M <= 4) on ragged N, one-block and long rows, both weight kinds; the
+    output buffer sits between canaries that must survive."""
+    dt = FORMATS[name]
+    for seed, raw in ((41, synth.random_blocks(41, dt, N, K)), (42, synth.gaussian_weight(42, dt, N, K).numpy())):
+        deq = oracle.dequant(dt, raw.reshape(-1), N * K).reshape(N, K).astype(np.float64)
+        wdev = torch.from_numpy(raw.reshape(-1)).to(cuda)
+        g = torch.Generator().manual_seed(seed)
+        for M in (1, 2, 3, 4):
+            x = torch.randn(M, K, generator=g)
+            xd = x.to(cuda)
+            buf = torch.full((M * N + 64,), 777.0, device=cuda)
+            out = buf[32:32 + M * N]
+            from light_b200 import _lib
+
+            _lib.check(_lib.lib().light_b200_matmul_q(dt, C.c_void_p(xd.data_ptr()), C.c_void_p(wdev.data_ptr()),
+                                                      C.c_void_p(out.data_ptr()), M, N, K, 0,
+                                                      C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            torch.cuda.synchronize()
+            host = buf.cpu().numpy()
+            assert np.all(host[:32] == 777.0) and np.all(host[32 + M * N:] == 777.0), "wrote outside the output"
+            want = x.numpy().astype(np.float64) @ deq.T
+            assert rel_l2(host[32:32 + M * N].reshape(M, N), want) <= 1e-4, (name, N, K, M, seed)
+
+
+def test_matmul_q_large_activations(cuda, oracle):
+    """Activations beyond f16 range go through the exact power-of-two prescale."""
+    N, K = 32, 2048
+    raw = synth.random_blocks(51, ops.Q4_K, N, K)
+    deq = oracle.dequant(ops.Q4_K, raw.reshape(-1), N * K).reshape(N, K).astype(np.float64)
+    x = torch.randn(1, K, generator=torch.Generator().manual_seed(52)) * 3e5
+    x[0, 7] = 2.5e7
+    got = ops.MatMulQ(x.to(cuda), _qt(raw, ops.Q4_K, (N, K), cuda)).cpu().numpy()
+    assert rel_l2(got, x.numpy().astype(np.float64) @ deq.T) <= 1e-4
+
+
+def test_matmul_q_empty_and_errors(cuda):
+    w = _qt(synth.random_blocks(1, ops.Q4_K, 4, 256), ops.Q4_K, (4, 256), cuda)
+    assert ops.MatMulQ(torch.zeros(0, 256, device=cuda), w).shape == (0, 4)
+    with pytest.raises(ValueError, match="inner dim mismatch"):
+        ops.MatMulQ(torch.zeros(1, 512, device=cuda), w)
+
+
+REF_MV = {"q8_0": "matmul_q8_0_f32_mv", "q4_k": "matmul_q4_k_f32_mv", "q5_k": "matmul_q5_k_f32_mv",
+          "q6_k": "matmul_q6_k_f32_mv"}
+
+
+@pytest.mark.parametrize("name", list(FORMATS))
+def test_matmul_q_vs_reference_cuda(cuda, name):
+    """Same seeded inputs through the reference's own kernels (kernels/cuda/src/matmul_q.cu,
+    launch shapes of kernels/cuda/matmul_q.go:60-89): outputs within 1e-3 relative L2."""
+    if not RefCuda.available("matmul_q"):
+        pytest.skip("oracle/_ref/matmul_q.cubin not built")
+    ref = RefCuda()
+    dt = FORMATS[name]
+    N, K = 264, 4096
+    raw = synth.random_blocks(61, dt, N, K)
+    wdev = torch.from_numpy(raw.reshape(-1)).to(cuda)
+    w = ops.QTensor(wdev, dt, (N, K))
+    g = torch.Generator().manual_seed(62)
+    for M in (1, 4, 7):
+        x = torch.randn(M, K, generator=g).to(cuda)
+        mine = ops.MatMulQ(x, w)
+        theirs = torch.zeros(M, N, device=cuda)
+        if M == 1 and name in REF_MV:
+            ref.launch("matmul_q", REF_MV[name], ((N + 7) // 8,), (256,),
+                       [C.c_void_p(x.data_ptr()), C.c_void_p(wdev.data_ptr()), C.c_void_p(theirs.data_ptr()),
+                        C.c_int(N), C.c_int(K)])
+        else:
+            ref.launch("matmul_q", f"matmul_{name}_f32", ((N + 7) // 8, (M + 3) // 4), (256,),
+                       [C.c_void_p(x.data_ptr()), C.c_void_p(wdev.data_ptr()), C.c_void_p(theirs.data_ptr()),
+                        C.c_int(M), C.c_int(N), C.c_int(K)])
+        torch.cuda.synchronize()
+        assert rel_l2(mine.cpu().numpy(), theirs.cpu().numpy()) <= TOL_REL_L2, (name, M)
+
+
+@pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0"])
+def test_dequant_vs_reference_cuda(cuda, name):
+    """Reference dequant kernels (kernels/cuda/src/dequant.cu; one thread per element, 256 threads):
+    Q8_0 and Q6_K bit-identical; Q4_K within 1 ulp-scale error (the reference build contracts
+    d*sc*q - dmin*m into an FMA under -use_fast_math, its own test allows 1e-5)."""
+    if not RefCuda.available("dequant"):
+        pytest.skip("oracle/_ref/dequant.cubin not built")
+    ref = RefCuda()
+    dt = FORMATS[name]
+    n = 64 * 1024
+    raw = synth.random_blocks(71, dt, 64, 1024)
+    src = torch.from_numpy(raw.reshape(-1)).to(cuda)
+    mine = ops.Dequantize(ops.QTensor(src, dt, (64, 1024)))
+    theirs = torch.zeros(n, device=cuda)
+    ref.launch("dequant", f"dequant_{name}_f32", ((n + 255) // 256,), (256,),
+               [C.c_void_p(src.data_ptr()), C.c_void_p(theirs.data_ptr()), C.c_ulong(n)])
+    torch.cuda.synchronize()
+    a, b = mine.cpu().numpy().ravel(), theirs.cpu().numpy()
+    if name == "q4_k":
+        assert np.max(np.abs(a - b)) <= 1e-5
+    else:
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+
+
+def test_config1_full_size_properties(cuda, oracle):
+    """BASELINE config 1 at full size (N = K = 4096, Q4_K from N(0, 0.02) weights, x ~ N(0, 1)):
+    parity with the threaded CPU oracle, linearity, and row-slice consistency (a row split is a
+    byte slice, which is what the multi-GPU column split relies on)."""
+    N = K = 4096
+    raw = synth.gaussian_weight(1, ops.Q4_K, N, K)
+    w = ops.QTensor(raw.reshape(-1).to(cuda), ops.Q4_K, (N, K))
+    g = torch.Generator().manual_seed(2)
+    x1, x2 = torch.randn(1, K, generator=g), torch.randn(1, K, generator=g)
+    y1 = ops.MatMulQ(x1.to(cuda), w).cpu().numpy()
+    want = oracle.matmul_q(ops.Q4_K, x1.numpy(), raw.numpy(), N, threads=8)
+    assert rel_l2(y1, want) <= 1e-5
+    y2 = ops.MatMulQ(x2.to(cuda), w).cpu().numpy()
+    y12 = ops.MatMulQ((x1 + x2).to(cuda), w).cpu().numpy()
+    assert rel_l2(y12, y1.astype(np.float64) + y2) <= 1e-5
+    rb = synth.row_bytes(ops.Q4_K, K)
+    part = ops.QTensor(raw[1000:1512].reshape(-1).to(cuda), ops.Q4_K, (512, K))
+    assert rel_l2(ops.MatMulQ(x1.to(cuda), part).cpu().numpy(), y1[:, 1000:1512]) <= 1e-6
+    assert rb == 2304
