@@ -1,19 +1,18 @@
 // Decode (few activation rows) fused dequant-matmul for Q4_K and Q6_K: HBM-bound GEMV.
 //
-// The weights are read exactly once, with 16-byte (Q4_K) or 4-byte aligned (Q6_K, whose 210-byte
-// blocks allow no more) coalesced loads, and never expanded to f32.  The arithmetic runs on the
-// tensor cores although this is a matrix-vector product:
+// The weights are read exactly once, coalesced, and never expanded to f32.  The arithmetic runs
+// on the tensor cores although this is a matrix-vector product:
 //
-//   * a warp owns 16 weight rows (the M of mma.m16n8k16) and a contiguous range of K;
+//   * a warp owns one 256-element K block and walks down RT tiles of 16 weight rows (the M of
+//     mma.m16n8k16), so the activations of its block are converted once and reused;
 //   * the packed integer codes become exact f16 values with one LOP3 / PRMT per pair of weights
-//     ((code bits) | magic exponent = offset + code), and form the A fragment directly in
-//     registers -- there is no int -> float conversion, no per-weight scale multiply and no FMA
-//     on the CUDA cores;
+//     ((code bits) | magic exponent = offset + code) and form the A fragment directly in
+//     registers -- no int -> float conversion, no per-weight scale multiply, no CUDA-core FMA;
 //   * the eight columns of the MMA are not eight tokens but EIGHT SUB-BLOCKS: the B fragment
 //     holds the activations block-diagonally, B[k][c] = x[k] if element k lies in sub-block c,
 //     else 0.  D[row][c] is then sum_{k in sub-block c} (offset + code) * x[k], the per-sub-block
-//     integer dot product that a scale applies to -- accumulated over the whole 256-element
-//     block by the tensor core, so the CUDA cores touch each (row, sub-block) once:
+//     integer dot product that a scale applies to, accumulated over the whole 256-element block
+//     by the tensor core.  The CUDA cores touch each (row, sub-block) once:
 //         acc += (d*sc) * (D - offset * Sx) - (dmin*m) * Sx,     Sx = sum of x over the sub-block;
 //   * lane (g, t) of the warp ends up holding exactly the D columns whose scales it decoded
 //     (sub-blocks 2t and 2t+1 of rows g and g+8), so there is no cross-lane traffic until the
@@ -21,17 +20,21 @@
 //   * activations stay f32-accurate: x is split as f16 hi + f16 lo (two MMAs into the same
 //     accumulator) after an exact power-of-two prescale that keeps it inside f16 range.
 //
-// Per 256 weights of a row a lane issues ~2 instructions per weight-byte instead of ~8, which is
-// what lets one SM keep up with its share of 6.5 TB/s.
+// A CTA covers 16*RT rows and all of K (its warps take K blocks round-robin and reduce through
+// shared memory), so every output element is written once, deterministically, without atomics.
+// The kernels are launched with programmatic dependent launch: the first weight tile is
+// requested before griddepcontrol.wait, so the head of each launch overlaps the tail of the one
+// before it in the stream -- a decode step is a chain of a few hundred such launches.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace lb {
 
 namespace {
 
-constexpr int WARPS = 4;        // warps per CTA, splitting K
-constexpr int ROWS = 16;        // weight rows per CTA (one m16 tile)
-constexpr int ZERO_BYTES = 512; // zero page read by lanes whose B fragment is structurally zero
+constexpr int WARPS = 8;  // warps per CTA, taking K blocks round-robin
+constexpr int ROWS = 16;  // weight rows per tile (one m16 MMA tile)
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -46,57 +49,93 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
   return v;
 }
-
-// Shared memory layout, per activation row m (stride tok_stride bytes):
-//   xh: K halves, hi part of the prescaled x, in natural element order except that inside each
-//       group of four the order is (0, 2, 1, 3), so that one 8-byte load yields both B registers
-//       of an MMA whose A fragment was cut from four consecutive code bytes;
-//   xl: K halves, lo part, same order;
-//   sx: K/SUB floats, sum of the prescaled x over each sub-block of SUB elements.
-// Then ZERO_BYTES of zeros, then the cross-warp reduction buffer.
-template <int SUB>
-__host__ __device__ constexpr int tok_bytes(int K) {
-  return 4 * K + 4 * (K / SUB);
+__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
+  asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(addr), "r"(a), "r"(b));
 }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
-// Each warp converts the K range it will consume: [e0, e1), multiples of 256.
-// Returns the power of two by which the warp's partial sums must be multiplied back.
+// Per-warp activation slab for one 256-element K block, SUB elements per sub-block:
+//   hi[256/SUB sub-blocks][SUB halves + pad]  lo[...same...]  sx[256/SUB floats]
+// Inside each group of four elements the order is (0, 2, 1, 3), so that one 8-byte load yields
+// both B registers of an MMA whose A fragment was cut from four consecutive code bytes.  The pad
+// (8 bytes per sub-block) spreads the live lanes of a B-fragment load over distinct banks.
 template <int SUB>
-__device__ __forceinline__ float stage_x(const float *__restrict__ x, unsigned char *tok, int K, int e0, int e1,
-                                         int lane) {
-  float amax = 0.f;
-  for (int e = e0 + lane * 4; e < e1; e += 128) {
-    float4 v = __ldg(reinterpret_cast<const float4 *>(x + e));
-    amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-  }
+struct Slab {
+  static constexpr int NSUB = 256 / SUB;
+  static constexpr int SUB_BYTES = SUB * 2 + 8;
+  static constexpr int LO_OFF = NSUB * SUB_BYTES;
+  static constexpr int SX_OFF = 2 * LO_OFF;
+  static constexpr int BYTES = SX_OFF + NSUB * 4;
+  static constexpr int ZERO_BYTES = LO_OFF + SUB_BYTES * NSUB;  // a zero page as large as hi + lo
+};
+
+// Converts one block's activations (two float4 per lane, already loaded) into the warp's slab.
+// Returns the power of two the block's partial sums must be multiplied by (exact prescale that
+// keeps |x| inside f16 range; 1 unless some |x| >= 2^15).
+template <int SUB>
+__device__ __forceinline__ float stage_block(const float4 (&xv)[2], uint32_t slab, int lane) {
+  using S = Slab<SUB>;
+  uint32_t m = 0;
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  // exact power-of-two prescale: only when |x| would leave f16 range
-  int ex = ((__float_as_int(amax) >> 23) & 0xff) - 127;
-  int sh = ex > 14 ? ex - 14 : 0;
-  if (sh > 100) sh = 100;
-  const float down = __int_as_float((127 - sh) << 23), up = __int_as_float((127 + sh) << 23);
-  __half *xh = reinterpret_cast<__half *>(tok);
-  __half *xl = xh + K;
-  float *sx = reinterpret_cast<float *>(tok + 4 * K);
-  constexpr int LANES_PER_SUB = SUB / 4;
-  for (int e = e0 + lane * 4; e < e1; e += 128) {
-    float4 v = __ldg(reinterpret_cast<const float4 *>(x + e));
-    v.x *= down, v.y *= down, v.z *= down, v.w *= down;
+  for (int i = 0; i < 2; i++) {
+    m = max(m, __float_as_uint(xv[i].x) & 0x7fffffffu);
+    m = max(m, __float_as_uint(xv[i].y) & 0x7fffffffu);
+    m = max(m, __float_as_uint(xv[i].z) & 0x7fffffffu);
+    m = max(m, __float_as_uint(xv[i].w) & 0x7fffffffu);
+  }
+  m = __reduce_max_sync(0xffffffffu, m);
+  int sh = (int)(m >> 23) - 127 - 14;
+  sh = sh < 0 ? 0 : (sh > 100 ? 100 : sh);
+  const float down = __uint_as_float((uint32_t)(127 - sh) << 23), up = __uint_as_float((uint32_t)(127 + sh) << 23);
+  constexpr int LPS = SUB / 4;  // lanes per sub-block
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    float4 v = xv[i];
+    if (sh) v.x *= down, v.y *= down, v.z *= down, v.w *= down;
     __half2 h02 = __floats2half2_rn(v.x, v.z), h13 = __floats2half2_rn(v.y, v.w);
     float2 f02 = __half22float2(h02), f13 = __half22float2(h13);
     __half2 l02 = __floats2half2_rn(v.x - f02.x, v.z - f02.y), l13 = __floats2half2_rn(v.y - f13.x, v.w - f13.y);
-    uint2 hv, lv;
-    hv.x = *reinterpret_cast<uint32_t *>(&h02), hv.y = *reinterpret_cast<uint32_t *>(&h13);
-    lv.x = *reinterpret_cast<uint32_t *>(&l02), lv.y = *reinterpret_cast<uint32_t *>(&l13);
-    *reinterpret_cast<uint2 *>(xh + e) = hv;
-    *reinterpret_cast<uint2 *>(xl + e) = lv;
+    const int e = i * 128 + lane * 4;  // element index inside the block
+    const uint32_t a = slab + (e / SUB) * S::SUB_BYTES + (e % SUB) * 2;
+    sts64(a, *reinterpret_cast<uint32_t *>(&h02), *reinterpret_cast<uint32_t *>(&h13));
+    sts64(a + S::LO_OFF, *reinterpret_cast<uint32_t *>(&l02), *reinterpret_cast<uint32_t *>(&l13));
     float s = (v.x + v.y) + (v.z + v.w);
 #pragma unroll
-    for (int o = 1; o < LANES_PER_SUB; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if ((lane & (LANES_PER_SUB - 1)) == 0) sx[e / SUB] = s;
+    for (int o = 1; o < LPS; o <<= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((lane & (LPS - 1)) == 0)
+      asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(slab + S::SX_OFF + (e / SUB) * 4), "f"(s));
   }
   return up;
+}
+
+constexpr int MAX_RT = 8;  // row tiles per CTA, upper bound (sizes the reduction buffer)
+
+// Adds one tile's per-lane partial sums (rows g and g+8) into the warp's private reduction row:
+// the four t-lanes of a row are summed with shuffles, lane t == 0 does the shared-memory update.
+__device__ __forceinline__ void tile_accumulate(float v0, float v1, float *red_warp, int rt, int lane) {
+  const int g = lane >> 2, t = lane & 3;
+  v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+  v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+  v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+  v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+  if (t == 0) {
+    red_warp[rt * ROWS + g] += v0;
+    red_warp[rt * ROWS + g + 8] += v1;
+  }
+}
+
+// Sums the warps of the CTA and stores out[n0 .. n0 + 16*RT).
+__device__ __forceinline__ void reduce_store(const float *red, float *__restrict__ out, int n0, int N, int RT) {
+  __syncthreads();
+  for (int i = threadIdx.x; i < RT * ROWS; i += WARPS * 32) {
+    if (n0 + i < N) {
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) v += red[wq * (MAX_RT * ROWS) + i];
+      out[n0 + i] = v;
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------ Q4_K
@@ -105,19 +144,20 @@ __device__ __forceinline__ float stage_x(const float *__restrict__ x, unsigned c
 // 64p + l (low nibble, sub-block 2p) and 64p + 32 + l (high nibble, sub-block 2p+1).
 // Lane (g, t) loads the 32 qs bytes of pair p = t of rows g and g+8 (two 16-byte loads each)
 // and the 16-byte header of both rows.  Code word i (bytes 4i..4i+3) feeds two MMAs:
-//   even sub-block 2t: a0 = codes(b0.lo, b2.lo)  a2 = codes(b1.lo, b3.lo)   (k slots 2t,2t+1 | 2t+8,2t+9)
+//   even sub-block 2t:   a0 = codes(b0.lo, b2.lo)  a2 = codes(b1.lo, b3.lo)  (k slots 2t,2t+1 | 2t+8,2t+9)
 //   odd  sub-block 2t+1: the same with the high nibbles.
-// All four come out as f16 (64 + code): (word >> {-4,0,4,8}) & 0x00F000F0 | 0x54005400.
-// The B lane (col c, tid) is non-zero only when c == 2*tid (even MMA) or c == 2*tid+1 (odd MMA).
+// All four come out as f16 (64 + code): (word >> {-4, 4, 0, 8}) & 0x00F000F0 | 0x54005400.
+// The B lane (col c, tid) is non-zero only when c == 2*tid (even MMA) or c == 2*tid+1 (odd MMA);
+// all other lanes read a page of zeros.
 
-struct Q4KBlk {
+struct Q4KTile {
   uint4 hdr[2];   // rows g, g+8
   uint4 q[2][2];  // [row][half of the 32 bytes]
 };
 
-__device__ __forceinline__ Q4KBlk q4k_load(const uint4 *rg, const uint4 *rg8, int b, int t) {
-  Q4KBlk k;
-  const uint4 *pg = rg + b * 9, *pg8 = rg8 + b * 9;
+__device__ __forceinline__ Q4KTile q4k_load(const uint4 *w, size_t row_u4, int rg, int rg8, int b, int t) {
+  Q4KTile k;
+  const uint4 *pg = w + (size_t)rg * row_u4 + b * 9, *pg8 = w + (size_t)rg8 * row_u4 + b * 9;
   k.hdr[0] = __ldg(pg);
   k.hdr[1] = __ldg(pg8);
   k.q[0][0] = __ldg(pg + 1 + 2 * t);
@@ -142,56 +182,61 @@ __device__ __forceinline__ void q4k_scales(const uint4 &h, int t, float (&dsc)[2
   dmn[1] = dmin * (float)((mnw >> (sh + 8)) & 0xFFu);
 }
 
-template <int MT, bool LO>
-__global__ void __launch_bounds__(WARPS * 32) q4k_gemv_mma_kernel(const float *__restrict__ x,
-                                                                  const uint8_t *__restrict__ w,
-                                                                  float *__restrict__ out, int M, int N, int K) {
-  extern __shared__ __align__(16) unsigned char smem[];
+__global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_mma_kernel(const float *__restrict__ x,
+                                                                    const uint8_t *__restrict__ w,
+                                                                    float *__restrict__ out, int N, int K, int RT) {
+  using S = Slab<32>;
+  __shared__ __align__(16) unsigned char slabs[WARPS][S::BYTES];
+  __shared__ __align__(16) unsigned char zero[S::ZERO_BYTES];
+  __shared__ float red[WARPS * MAX_RT * ROWS];
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int nb = K >> 8;
-  const int b0 = warp * nb / WARPS, b1 = (warp + 1) * nb / WARPS;
-  const int tokb = tok_bytes<32>(K);
-  unsigned char *zero = smem + MT * tokb;
-  float *red = reinterpret_cast<float *>(zero + ZERO_BYTES);
-
-  for (int i = threadIdx.x; i < ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-  float up[MT];
-#pragma unroll
-  for (int m = 0; m < MT; m++)
-    up[m] = m < M ? stage_x<32>(x + (size_t)m * K, smem + m * tokb, K, b0 * 256, b1 * 256, lane) : 0.f;
-  __syncthreads();  // zero page; each warp reads back only what it staged itself
-
-  const int n0 = blockIdx.x * ROWS;
-  const int rg = min(n0 + g, N - 1), rg8 = min(n0 + g + 8, N - 1);
+  const int n0 = blockIdx.x * (ROWS * RT);
   const size_t row_u4 = (size_t)nb * 9;
-  const uint4 *wg = reinterpret_cast<const uint4 *>(w) + (size_t)rg * row_u4;
-  const uint4 *wg8 = reinterpret_cast<const uint4 *>(w) + (size_t)rg8 * row_u4;
+  const uint4 *w4 = reinterpret_cast<const uint4 *>(w);
+  for (int i = threadIdx.x; i < S::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
 
-  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem), szero = (uint32_t)__cvta_generic_to_shared(zero);
+  float *red_warp = red + warp * (MAX_RT * ROWS);
+  for (int i = lane; i < MAX_RT * ROWS; i += 32) red_warp[i] = 0.f;
+  const int last = N - 1;
+  const int r0 = n0 + g;  // row g of tile rt is min(r0 + 16 rt, last); row g+8 likewise
+
+  const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
+  const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
   // B addresses: even MMA live iff g == 2t, odd MMA live iff g == 2t+1; sub-block index == g.
-  const bool live_e = g == 2 * t, live_o = g == 2 * t + 1;
-  uint32_t pe = live_e ? sbase + b0 * 512 + g * 64 : szero;
-  uint32_t po = live_o ? sbase + b0 * 512 + g * 64 : szero;
-  const uint32_t adv_e = live_e ? 512u : 0u, adv_o = live_o ? 512u : 0u;
-  const uint32_t lo_e = live_e ? (uint32_t)(2 * K) : 0u, lo_o = live_o ? (uint32_t)(2 * K) : 0u;
-  const uint32_t tok_e = live_e ? (uint32_t)tokb : 0u, tok_o = live_o ? (uint32_t)tokb : 0u;
-
-  float acc[MT][2];
-#pragma unroll
-  for (int m = 0; m < MT; m++) acc[m][0] = acc[m][1] = 0.f;
+  const uint32_t pe = g == 2 * t ? slab + g * S::SUB_BYTES : szero;
+  const uint32_t po = g == 2 * t + 1 ? slab + g * S::SUB_BYTES : szero;
 
   constexpr uint32_t MASK = 0x00F000F0u, MAGIC = 0x54005400u;  // f16 (64 + nibble)
-  if (b0 < b1) {
-    Q4KBlk cur = q4k_load(wg, wg8, b0, t);
-    for (int b = b0; b < b1; b++) {
-      Q4KBlk nxt;
-      if (b + 1 < b1) nxt = q4k_load(wg, wg8, b + 1, t);
+  Q4KTile cur;
+  if (warp < nb) cur = q4k_load(w4, row_u4, min(r0, last), min(r0 + 8, last), warp, t);  // weights do not depend on x
+  pdl_wait();                                                                  // x does
+  __syncthreads();                                                             // zero page
+  float4 xn[2];
+  if (warp < nb) {
+    xn[0] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256) + lane);
+    xn[1] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256 + 128) + lane);
+  }
+  for (int b = warp; b < nb; b += WARPS) {
+    const float up = stage_block<32>(xn, slab, lane);
+    const int bn = b + WARPS;
+    if (bn < nb) {
+      xn[0] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256) + lane);
+      xn[1] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256 + 128) + lane);
+    }
+    __syncwarp();
+    const float2 sx = *reinterpret_cast<const float2 *>(slabs[warp] + S::SX_OFF + 8 * t);
+    for (int rt = 0; rt < RT; rt++) {
+      Q4KTile nxt;
+      if (rt + 1 < RT)
+        nxt = q4k_load(w4, row_u4, min(r0 + (rt + 1) * ROWS, last), min(r0 + (rt + 1) * ROWS + 8, last), b, t);
+      else if (bn < nb)
+        nxt = q4k_load(w4, row_u4, min(r0, last), min(r0 + 8, last), bn, t);
       float dsc[2][2], dmn[2][2];
       q4k_scales(cur.hdr[0], t, dsc[0], dmn[0]);
       q4k_scales(cur.hdr[1], t, dsc[1], dmn[1]);
-      float d[MT][4];
-#pragma unroll
-      for (int m = 0; m < MT; m++) d[m][0] = d[m][1] = d[m][2] = d[m][3] = 0.f;
+      float de[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};  // even / odd sub-block chains
       const uint32_t qg[8] = {cur.q[0][0].x, cur.q[0][0].y, cur.q[0][0].z, cur.q[0][0].w,
                               cur.q[0][1].x, cur.q[0][1].y, cur.q[0][1].z, cur.q[0][1].w};
       const uint32_t qh[8] = {cur.q[1][0].x, cur.q[1][0].y, cur.q[1][0].z, cur.q[1][0].w,
@@ -203,254 +248,234 @@ __global__ void __launch_bounds__(WARPS * 32) q4k_gemv_mma_kernel(const float *_
         const uint32_t e2 = ((vg >> 4) & MASK) | MAGIC, e3 = ((vh >> 4) & MASK) | MAGIC;
         const uint32_t o0 = (vg & MASK) | MAGIC, o1 = (vh & MASK) | MAGIC;
         const uint32_t o2 = ((vg >> 8) & MASK) | MAGIC, o3 = ((vh >> 8) & MASK) | MAGIC;
-#pragma unroll
-        for (int m = 0; m < MT; m++) {
-          uint2 be = lds64(pe + m * tok_e + i * 8);
-          mma16816(d[m], e0, e1, e2, e3, be.x, be.y);
-          uint2 bo = lds64(po + m * tok_o + i * 8);
-          mma16816(d[m], o0, o1, o2, o3, bo.x, bo.y);
-          if (LO) {
-            uint2 bel = lds64(pe + m * tok_e + lo_e + i * 8);
-            mma16816(d[m], e0, e1, e2, e3, bel.x, bel.y);
-            uint2 bol = lds64(po + m * tok_o + lo_o + i * 8);
-            mma16816(d[m], o0, o1, o2, o3, bol.x, bol.y);
-          }
-        }
+        const uint2 be = lds64(pe + i * 8), bo = lds64(po + i * 8);
+        mma16816(de, e0, e1, e2, e3, be.x, be.y);
+        mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
+        const uint2 bel = lds64(pe + S::LO_OFF + i * 8), bol = lds64(po + S::LO_OFF + i * 8);
+        mma16816(de, e0, e1, e2, e3, bel.x, bel.y);
+        mma16816(dq, o0, o1, o2, o3, bol.x, bol.y);
       }
-      // lane (g, t): d[.][0], d[.][1] = row g, sub-blocks 2t, 2t+1;  d[.][2], d[.][3] = row g+8.
+      // lane (g, t): de[0] / dq[1] = row g, sub-blocks 2t / 2t+1;  de[2] / dq[3] = row g+8.
+      float vr[2];
 #pragma unroll
-      for (int m = 0; m < MT; m++) {
-        const float2 sx = *reinterpret_cast<const float2 *>(smem + m * tokb + 4 * K + (b * 8 + 2 * t) * 4);
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-          float v = dsc[r][0] * d[m][2 * r] - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
-          v += dsc[r][1] * d[m][2 * r + 1] - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
-          acc[m][r] += v;
-        }
+      for (int r = 0; r < 2; r++) {
+        float v = dsc[r][0] * de[2 * r] - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
+        v += dsc[r][1] * dq[2 * r + 1] - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
+        vr[r] = v * up;
       }
-      pe += adv_e;
-      po += adv_o;
+      tile_accumulate(vr[0], vr[1], red_warp, rt, lane);
       cur = nxt;
     }
+    __syncwarp();  // the slab is rewritten by the next block's staging
   }
-  // sum the four t-lanes of each row, undo the prescale, then the warps of the CTA
-#pragma unroll
-  for (int m = 0; m < MT; m++)
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-      float v = acc[m][r];
-      v += __shfl_xor_sync(0xffffffffu, v, 1);
-      v += __shfl_xor_sync(0xffffffffu, v, 2);
-      if (t == 0) red[(warp * MT + m) * ROWS + g + 8 * r] = v * up[m];
-    }
-  __syncthreads();
-  for (int i = threadIdx.x; i < MT * ROWS; i += WARPS * 32) {
-    const int m = i / ROWS, r = i % ROWS;
-    if (m < M && n0 + r < N) {
-      float v = 0.f;
-#pragma unroll
-      for (int wq = 0; wq < WARPS; wq++) v += red[(wq * MT + m) * ROWS + r];
-      out[(size_t)m * N + n0 + r] = v;
-    }
-  }
+  reduce_store(red, out, n0, N, RT);
 }
 
 // ------------------------------------------------------------------------------------ Q6_K
 //
 // Block (210 B): [ql[128] | qh[64] | int8 sc[16] | f16 d]; element e = 128h + 32q + l
-// (half h, group q, l < 32) has low nibble in ql[64h + 32(q&1) + l] (high nibble when q >= 2) and
-// bits 2q..2q+1 of qh[32h + l]; its sub-block of 16 is s = e / 16 = 8h + 2q + l/16.
-// Lane (g, t) takes group q = t of rows g and g+8.  For each (h, u = l/16) it needs the 16 ql
-// bytes at 64h + 32(t&1) + 16u and the 16 qh bytes at 128 + 32h + 16u.  Blocks are only 2-byte
-// aligned, so each run is fetched as five aligned 32-bit words and funnel-shifted by 0 or 16.
-// Code word i (l = 16u + 4i .. +3) becomes four 6-bit bytes, then two f16x2 (1024 + code)
-// with PRMT, and feeds ONE MMA (all 16 k slots of it belong to sub-block 8h + 2t + u):
-//   column = sub-block mod 8 = 2t + u -> B lane (col c, tid) live iff c == 2*tid + u, as for Q4_K.
-// One accumulator fragment per half h.
+// (half h, group q, l < 32) has its low nibble in ql[64h + 32(q&1) + l] (high nibble when q >= 2)
+// and bits 2q..2q+1 of qh[32h + l]; its sub-block of 16 is s = e / 16 = 8h + 2q + l/16.
+// For each (h, u = l/16), lane (g, t) takes l = 16u + 4t .. +3 of rows g and g+8: one word of
+// ql[64h + l], one of ql[64h + 32 + l] and one of qh[32h + l] -- every byte of the block is
+// loaded by exactly one lane.  Blocks are only 2-byte aligned, so a word is fetched as two
+// aligned 32-bit words funnel-shifted by 0 or 16 bits.  From the three words come the four
+// groups' 6-bit codes as bytes, then f16x2 (1024 + code) with PRMT, and group q feeds ONE MMA
+// whose 16 k slots are exactly sub-block 8h + 2q + u, live column 2q + u.
 
-__device__ __forceinline__ void ld_run16(const uint8_t *p, uint32_t (&v)[4]) {
+__device__ __forceinline__ uint32_t ld_u32_2aligned(const uint8_t *p) {
   const uint32_t sh = ((uint32_t)(uintptr_t)p & 2u) * 8u;  // 0 or 16
   const uint32_t *a = reinterpret_cast<const uint32_t *>((uintptr_t)p & ~(uintptr_t)3);
-  uint32_t r[5];
-#pragma unroll
-  for (int i = 0; i < 5; i++) r[i] = __ldg(a + i);
-#pragma unroll
-  for (int i = 0; i < 4; i++) v[i] = __funnelshift_r(r[i], r[i + 1], sh);
+  return __funnelshift_r(__ldg(a), __ldg(a + 1), sh);
 }
 
-template <int MT, bool LO>
-__global__ void __launch_bounds__(WARPS * 32) q6k_gemv_mma_kernel(const float *__restrict__ x,
-                                                                  const uint8_t *__restrict__ w,
-                                                                  float *__restrict__ out, int M, int N, int K) {
-  extern __shared__ __align__(16) unsigned char smem[];
+struct Q6KTile {
+  uint32_t wa[2][4], wc[2][4], wh[2][4];  // [row][(h, u)]: ql[64h + l], ql[64h + 32 + l], qh[32h + l]
+  uint32_t sc[2];                         // [row]: scales 2t, 2t+1 (h = 0) | 8+2t, 8+2t+1 (h = 1), one byte each
+  uint16_t d[2];
+};
+
+__device__ __forceinline__ Q6KTile q6k_load(const uint8_t *w, size_t row_bytes, int rg, int rg8, int b, int t) {
+  Q6KTile k;
+  const uint8_t *blk[2] = {w + (size_t)rg * row_bytes + (size_t)b * 210, w + (size_t)rg8 * row_bytes + (size_t)b * 210};
+#pragma unroll
+  for (int r = 0; r < 2; r++) {
+#pragma unroll
+    for (int hu = 0; hu < 4; hu++) {
+      const int h = hu >> 1, u = hu & 1, l = 16 * u + 4 * t;
+      k.wa[r][hu] = ld_u32_2aligned(blk[r] + 64 * h + l);
+      k.wc[r][hu] = ld_u32_2aligned(blk[r] + 64 * h + 32 + l);
+      k.wh[r][hu] = ld_u32_2aligned(blk[r] + 128 + 32 * h + l);
+    }
+    const uint32_t s0 = __ldg(reinterpret_cast<const uint16_t *>(blk[r] + 192 + 2 * t));
+    const uint32_t s1 = __ldg(reinterpret_cast<const uint16_t *>(blk[r] + 200 + 2 * t));
+    k.sc[r] = s0 | (s1 << 16);
+    k.d[r] = __ldg(reinterpret_cast<const uint16_t *>(blk[r] + 208));
+  }
+  return k;
+}
+
+__global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float *__restrict__ x,
+                                                                    const uint8_t *__restrict__ w,
+                                                                    float *__restrict__ out, int N, int K, int RT) {
+  using S = Slab<16>;
+  __shared__ __align__(16) unsigned char slabs[WARPS][S::BYTES];
+  __shared__ __align__(16) unsigned char zero[S::ZERO_BYTES];
+  __shared__ float red[WARPS * MAX_RT * ROWS];
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int nb = K >> 8;
-  const int b0 = warp * nb / WARPS, b1 = (warp + 1) * nb / WARPS;
-  const int tokb = tok_bytes<16>(K);
-  unsigned char *zero = smem + MT * tokb;
-  float *red = reinterpret_cast<float *>(zero + ZERO_BYTES);
-
-  for (int i = threadIdx.x; i < ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-  float up[MT];
-#pragma unroll
-  for (int m = 0; m < MT; m++)
-    up[m] = m < M ? stage_x<16>(x + (size_t)m * K, smem + m * tokb, K, b0 * 256, b1 * 256, lane) : 0.f;
-  __syncthreads();
-
-  const int n0 = blockIdx.x * ROWS;
+  const int n0 = blockIdx.x * (ROWS * RT);
   const size_t row_bytes = (size_t)nb * 210;
-  const uint8_t *wr[2] = {w + (size_t)min(n0 + g, N - 1) * row_bytes, w + (size_t)min(n0 + g + 8, N - 1) * row_bytes};
+  for (int i = threadIdx.x; i < S::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
 
-  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(smem), szero = (uint32_t)__cvta_generic_to_shared(zero);
-  const bool live0 = g == 2 * t, live1 = g == 2 * t + 1;  // u = 0 / u = 1 MMAs
-  uint32_t p0 = live0 ? sbase + b0 * 512 + g * 32 : szero;
-  uint32_t p1 = live1 ? sbase + b0 * 512 + g * 32 : szero;
-  const uint32_t adv0 = live0 ? 512u : 0u, adv1 = live1 ? 512u : 0u;
-  const uint32_t lo0 = live0 ? (uint32_t)(2 * K) : 0u, lo1 = live1 ? (uint32_t)(2 * K) : 0u;
-  const uint32_t tok0 = live0 ? (uint32_t)tokb : 0u, tok1 = live1 ? (uint32_t)tokb : 0u;
-  const uint32_t half0 = live0 ? 256u : 0u, half1 = live1 ? 256u : 0u;  // +128 elements for h = 1
+  float *red_warp = red + warp * (MAX_RT * ROWS);
+  for (int i = lane; i < MAX_RT * ROWS; i += 32) red_warp[i] = 0.f;
+  const int last = N - 1;
+  const int r0 = n0 + g;  // row g of tile rt is min(r0 + 16 rt, last); row g+8 likewise
 
-  const int sA = (t >> 1) * 4, sH = 2 * t;
-  float acc[MT][2];
+  const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
+  const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
+  // B address of the MMA of (group q, u): live iff this lane's column g == 2q + u; then the lane
+  // reads elements 4t..4t+3 of sub-block 8h + g (h adds an immediate).
+  uint32_t pb[4][2];
 #pragma unroll
-  for (int m = 0; m < MT; m++) acc[m][0] = acc[m][1] = 0.f;
-
-  for (int b = b0; b < b1; b++) {
-    // scales of sub-blocks 8h + 2t + u and the block scale d, for both rows
-    float ds[2][2][2];  // [row][h][u]
+  for (int q = 0; q < 4; q++)
 #pragma unroll
-    for (int r = 0; r < 2; r++) {
-      const uint8_t *blk = wr[r] + (size_t)b * 210;
-      const uint16_t s0 = __ldg(reinterpret_cast<const uint16_t *>(blk + 192 + 2 * t));
-      const uint16_t s1 = __ldg(reinterpret_cast<const uint16_t *>(blk + 200 + 2 * t));
-      const float d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(blk + 208)));
-      ds[r][0][0] = d * (float)(int8_t)(s0 & 0xff);
-      ds[r][0][1] = d * (float)(int8_t)(s0 >> 8);
-      ds[r][1][0] = d * (float)(int8_t)(s1 & 0xff);
-      ds[r][1][1] = d * (float)(int8_t)(s1 >> 8);
+    for (int u = 0; u < 2; u++) pb[q][u] = g == 2 * q + u ? slab + g * S::SUB_BYTES + 8 * t : szero;
+
+  Q6KTile cur;
+  if (warp < nb) cur = q6k_load(w, row_bytes, min(r0, last), min(r0 + 8, last), warp, t);
+  pdl_wait();
+  __syncthreads();
+  float4 xn[2];
+  if (warp < nb) {
+    xn[0] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256) + lane);
+    xn[1] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256 + 128) + lane);
+  }
+  for (int b = warp; b < nb; b += WARPS) {
+    const float up = stage_block<16>(xn, slab, lane);
+    const int bn = b + WARPS;
+    if (bn < nb) {
+      xn[0] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256) + lane);
+      xn[1] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256 + 128) + lane);
     }
+    __syncwarp();
+    float2 sx[2];  // sums of x over sub-blocks 8h + 2t, 8h + 2t + 1
+    sx[0] = *reinterpret_cast<const float2 *>(slabs[warp] + S::SX_OFF + (2 * t) * 4);
+    sx[1] = *reinterpret_cast<const float2 *>(slabs[warp] + S::SX_OFF + (8 + 2 * t) * 4);
+    for (int rt = 0; rt < RT; rt++) {
+      Q6KTile nxt;
+      if (rt + 1 < RT)
+        nxt = q6k_load(w, row_bytes, min(r0 + (rt + 1) * ROWS, last), min(r0 + (rt + 1) * ROWS + 8, last), b, t);
+      else if (bn < nb)
+        nxt = q6k_load(w, row_bytes, min(r0, last), min(r0 + 8, last), bn, t);
+      float vr[2] = {0.f, 0.f};
 #pragma unroll
-    for (int h = 0; h < 2; h++) {
-      float d[MT][4];
+      for (int h = 0; h < 2; h++) {
+        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // u = 0 / u = 1 chains
 #pragma unroll
-      for (int m = 0; m < MT; m++) d[m][0] = d[m][1] = d[m][2] = d[m][3] = 0.f;
+        for (int u = 0; u < 2; u++) {
+          const int hu = 2 * h + u;
 #pragma unroll
-      for (int u = 0; u < 2; u++) {
-        uint32_t ql[2][4], qh[2][4];
+          for (int q = 0; q < 4; q++) {
+            uint32_t a[4];
 #pragma unroll
-        for (int r = 0; r < 2; r++) {
-          const uint8_t *blk = wr[r] + (size_t)b * 210;
-          ld_run16(blk + 64 * h + 32 * (t & 1) + 16 * u, ql[r]);
-          ld_run16(blk + 128 + 32 * h + 16 * u, qh[r]);
-        }
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-          uint32_t a[4];
-#pragma unroll
-          for (int r = 0; r < 2; r++) {
-            const uint32_t v = ((ql[r][i] >> sA) & 0x0F0F0F0Fu) | (((qh[r][i] >> sH) << 4) & 0x30303030u);
-            a[r] = __byte_perm(v, 0x64646464u, 0x4240);      // (1024 + b0, 1024 + b2)
-            a[2 + r] = __byte_perm(v, 0x64646464u, 0x4341);  // (1024 + b1, 1024 + b3)
-          }
-          const uint32_t pu = u ? p1 : p0, toku = u ? tok1 : tok0, lou = u ? lo1 : lo0, hu = u ? half1 : half0;
-#pragma unroll
-          for (int m = 0; m < MT; m++) {
-            uint2 bb = lds64(pu + m * toku + h * hu + i * 8);
-            mma16816(d[m], a[0], a[1], a[2], a[3], bb.x, bb.y);
-            if (LO) {
-              uint2 bl = lds64(pu + m * toku + lou + h * hu + i * 8);
-              mma16816(d[m], a[0], a[1], a[2], a[3], bl.x, bl.y);
+            for (int r = 0; r < 2; r++) {
+              const uint32_t lo4 = (q & 1) ? cur.wc[r][hu] : cur.wa[r][hu];
+              const uint32_t nib = (q >> 1) ? (lo4 >> 4) : lo4;
+              const uint32_t hi2 = q == 0 ? (cur.wh[r][hu] << 4) : q == 1 ? (cur.wh[r][hu] << 2)
+                                   : q == 2 ? cur.wh[r][hu] : (cur.wh[r][hu] >> 2);
+              const uint32_t v = (nib & 0x0F0F0F0Fu) | (hi2 & 0x30303030u);
+              a[r] = __byte_perm(v, 0x64646464u, 0x4240);      // f16x2 (1024 + b0, 1024 + b2)
+              a[2 + r] = __byte_perm(v, 0x64646464u, 0x4341);  // f16x2 (1024 + b1, 1024 + b3)
+            }
+            const uint32_t p = pb[q][u] + h * (8 * S::SUB_BYTES);
+            const uint2 bh = lds64(p), bl = lds64(p + S::LO_OFF);
+            if (u == 0) {
+              mma16816(d0, a[0], a[1], a[2], a[3], bh.x, bh.y);
+              mma16816(d0, a[0], a[1], a[2], a[3], bl.x, bl.y);
+            } else {
+              mma16816(d1, a[0], a[1], a[2], a[3], bh.x, bh.y);
+              mma16816(d1, a[0], a[1], a[2], a[3], bl.x, bl.y);
             }
           }
         }
+        // lane (g, t): d0[0] / d1[1] = row g, sub-blocks 8h+2t / 8h+2t+1;  d0[2] / d1[3] = row g+8
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          const float d = f16_bits_to_f32(cur.d[r]);
+          const float s0 = d * (float)(int8_t)((cur.sc[r] >> (16 * h)) & 0xff);
+          const float s1 = d * (float)(int8_t)((cur.sc[r] >> (16 * h + 8)) & 0xff);
+          vr[r] += (s0 * (d0[2 * r] - 1056.f * sx[h].x) + s1 * (d1[2 * r + 1] - 1056.f * sx[h].y)) * up;
+        }
       }
-      // lane (g, t): d[.][0], d[.][1] = row g, sub-blocks 8h+2t, 8h+2t+1;  d[.][2], d[.][3] = row g+8
-#pragma unroll
-      for (int m = 0; m < MT; m++) {
-        const float2 sx = *reinterpret_cast<const float2 *>(smem + m * tokb + 4 * K + (b * 16 + 8 * h + 2 * t) * 4);
-#pragma unroll
-        for (int r = 0; r < 2; r++)
-          acc[m][r] += ds[r][h][0] * (d[m][2 * r] - 1056.f * sx.x) + ds[r][h][1] * (d[m][2 * r + 1] - 1056.f * sx.y);
-      }
+      tile_accumulate(vr[0], vr[1], red_warp, rt, lane);
+      cur = nxt;
     }
-    p0 += adv0;
-    p1 += adv1;
+    __syncwarp();
   }
-#pragma unroll
-  for (int m = 0; m < MT; m++)
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-      float v = acc[m][r];
-      v += __shfl_xor_sync(0xffffffffu, v, 1);
-      v += __shfl_xor_sync(0xffffffffu, v, 2);
-      if (t == 0) red[(warp * MT + m) * ROWS + g + 8 * r] = v * up[m];
-    }
-  __syncthreads();
-  for (int i = threadIdx.x; i < MT * ROWS; i += WARPS * 32) {
-    const int m = i / ROWS, r = i % ROWS;
-    if (m < M && n0 + r < N) {
-      float v = 0.f;
-#pragma unroll
-      for (int wq = 0; wq < WARPS; wq++) v += red[(wq * MT + m) * ROWS + r];
-      out[(size_t)m * N + n0 + r] = v;
-    }
-  }
+  reduce_store(red, out, n0, N, RT);
 }
 
-constexpr int MAX_SMEM = 200 * 1024;
-
-template <int SUB>
-size_t smem_bytes(int MT, int K) {
-  return (size_t)MT * tok_bytes<SUB>(K) + ZERO_BYTES + (size_t)WARPS * MT * ROWS * 4;
+template <typename... Args>
+int launch_pdl(void (*kern)(Args...), unsigned grid, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(WARPS * 32);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, args...);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode): %s", cudaGetErrorString(e));
+  return 0;
 }
 
-template <typename Kern>
-int set_smem(Kern k) {
-  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, MAX_SMEM);
-  return e == cudaSuccess ? 0 : fail((int)e, "light_b200: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+// Row tiles per CTA: enough CTAs to fill the 148 SMs a few times over, as many tiles as that
+// allows (each tile reuses the block's converted activations).
+int g_rt_override = 0;  // LIGHT_B200_GEMV_RT: tuning knob, 0 = choose by shape
+int pick_rt(int N) {
+  if (g_rt_override > 0) return g_rt_override < MAX_RT ? g_rt_override : MAX_RT;
+  const int tiles = (N + ROWS - 1) / ROWS;
+  if (tiles >= 148 * 16) return 8;
+  if (tiles >= 148 * 8) return 4;
+  if (tiles >= 148 * 4) return 2;
+  return 1;
 }
 
 }  // namespace
 
 int gguf_gemv_fast_init(int) {
-  int rc = 0;
-  if ((rc = set_smem(q4k_gemv_mma_kernel<1, true>))) return rc;
-  if ((rc = set_smem(q4k_gemv_mma_kernel<2, true>))) return rc;
-  if ((rc = set_smem(q4k_gemv_mma_kernel<4, true>))) return rc;
-  if ((rc = set_smem(q6k_gemv_mma_kernel<1, true>))) return rc;
-  if ((rc = set_smem(q6k_gemv_mma_kernel<2, true>))) return rc;
-  if ((rc = set_smem(q6k_gemv_mma_kernel<4, true>))) return rc;
+  if (const char *e = getenv("LIGHT_B200_GEMV_RT")) g_rt_override = atoi(e);
   return 0;
 }
 
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
   if (M < 1 || M > 4 || K % 256) return 0;
-  const int MT = M == 1 ? 1 : M == 2 ? 2 : 4;
-  const unsigned grid = (unsigned)((N + ROWS - 1) / ROWS);
-  if (type == LB200_Q4_K) {
-    if ((uintptr_t)w & 15) return 0;
-    size_t sm = smem_bytes<32>(MT, K);
-    if (sm > (size_t)MAX_SMEM) return 0;
-    const uint8_t *wb = (const uint8_t *)w;
-    if (MT == 1) q4k_gemv_mma_kernel<1, true><<<grid, WARPS * 32, sm, st>>>(x, wb, out, M, N, K);
-    else if (MT == 2) q4k_gemv_mma_kernel<2, true><<<grid, WARPS * 32, sm, st>>>(x, wb, out, M, N, K);
-    else q4k_gemv_mma_kernel<4, true><<<grid, WARPS * 32, sm, st>>>(x, wb, out, M, N, K);
-    int rc = launched("matmul_q (Q4_K decode)");
-    return rc ? rc : 1;
+  if (type != LB200_Q4_K && type != LB200_Q6_K) return 0;
+  if (type == LB200_Q4_K && ((uintptr_t)w & 15)) return 0;
+  // Q6_K rows must start 4-byte aligned for the aligned-word loads: (K/256)*210 % 4 == 0
+  if (type == LB200_Q6_K && (((uintptr_t)w & 3) || ((size_t)(K >> 8) * 210) % 4)) return 0;
+  const int rt = pick_rt(N);
+  const unsigned grid = (unsigned)((N + ROWS * rt - 1) / (ROWS * rt));
+  const uint8_t *wb = (const uint8_t *)w;
+  for (int m = 0; m < M; m++) {  // one launch per activation row: the weights of a decode-sized
+    const float *xm = x + (size_t)m * K;  // matrix stay in the 126 MB L2 between the launches
+    float *om = out + (size_t)m * N;
+    int rc;
+    if (type == LB200_Q4_K)
+      rc = launch_pdl(q4k_gemv_mma_kernel, grid, st, xm, wb, om, N, K, rt);
+    else
+      rc = launch_pdl(q6k_gemv_mma_kernel, grid, st, xm, wb, om, N, K, rt);
+    if (rc) return rc;
+    rc = launched("matmul_q (decode)");
+    if (rc) return rc;
   }
-  if (type == LB200_Q6_K) {
-    // rows must start 4-byte aligned for the aligned-word loads: (K/256)*210 % 4 == 0
-    if (((uintptr_t)w & 3) || ((size_t)(K >> 8) * 210) % 4) return 0;
-    size_t sm = smem_bytes<16>(MT, K);
-    if (sm > (size_t)MAX_SMEM) return 0;
-    const uint8_t *wb = (const uint8_t *)w;
-    if (MT == 1) q6k_gemv_mma_kernel<1, true><<<grid, WARPS * 32, sm, st>>>(x, wb, out, M, N, K);
-    else if (MT == 2) q6k_gemv_mma_kernel<2, true><<<grid, WARPS * 32, sm, st>>>(x, wb, out, M, N, K);
-    else q6k_gemv_mma_kernel<4, true><<<grid, WARPS * 32, sm, st>>>(x, wb, out, M, N, K);
-    int rc = launched("matmul_q (Q6_K decode)");
-    return rc ? rc : 1;
-  }
-  return 0;
+  return 1;
 }
 
 }  // namespace lb
