@@ -44,6 +44,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// (a & b) | c in one LOP3 (b and c live in registers; the compiler does not fuse two immediates)
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+  return d;
+}
+
 __device__ __forceinline__ uint2 lds64(uint32_t addr) {
   uint2 v;
   asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
@@ -109,30 +116,32 @@ __device__ __forceinline__ float stage_block(const float4 (&xv)[2], uint32_t sla
   return up;
 }
 
-constexpr int MAX_RT = 8;  // row tiles per CTA, upper bound (sizes the reduction buffer)
+constexpr int MAX_RT = 4;  // row tiles per CTA, upper bound (sizes the reduction buffer)
 
-// Adds one tile's per-lane partial sums (rows g and g+8) into the warp's private reduction row:
-// the four t-lanes of a row are summed with shuffles, lane t == 0 does the shared-memory update.
-__device__ __forceinline__ void tile_accumulate(float v0, float v1, float *red_warp, int rt, int lane) {
-  const int g = lane >> 2, t = lane & 3;
-  v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
-  v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
-  v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
-  v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
-  if (t == 0) {
-    red_warp[rt * ROWS + g] += v0;
-    red_warp[rt * ROWS + g + 8] += v1;
-  }
+// Per-lane partial sums of (rows g, g+8) of tile rt, kept in the warp's private part of shared
+// memory so that the row-tile loop needs no registers per tile: one 8-byte read-modify-write.
+__device__ __forceinline__ void tile_accumulate(float v0, float v1, uint32_t red_lane, int rt) {
+  const uint32_t a = red_lane + rt * (32 * 8);
+  float2 o;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(o.x), "=f"(o.y) : "r"(a));
+  o.x += v0, o.y += v1;
+  asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(a), "f"(o.x), "f"(o.y));
 }
 
-// Sums the warps of the CTA and stores out[n0 .. n0 + 16*RT).
-__device__ __forceinline__ void reduce_store(const float *red, float *__restrict__ out, int n0, int N, int RT) {
+// red[warp][rt][lane] (float2: rows g, g+8).  Sums the four t-lanes of a row and the warps of the
+// CTA in a fixed order and stores out[n0 .. n0 + 16*RT).
+__device__ __forceinline__ void reduce_store(const float2 *red, float *__restrict__ out, int n0, int N, int RT) {
   __syncthreads();
   for (int i = threadIdx.x; i < RT * ROWS; i += WARPS * 32) {
     if (n0 + i < N) {
+      const int rt = i >> 4, row = i & 15, g = row & 7, hi = row >> 3;
       float v = 0.f;
 #pragma unroll
-      for (int wq = 0; wq < WARPS; wq++) v += red[wq * (MAX_RT * ROWS) + i];
+      for (int wq = 0; wq < WARPS; wq++) {
+        const float2 *p = red + (wq * MAX_RT + rt) * 32 + g * 4;
+#pragma unroll
+        for (int t = 0; t < 4; t++) v += hi ? p[t].y : p[t].x;
+      }
       out[n0 + i] = v;
     }
   }
@@ -150,123 +159,109 @@ __device__ __forceinline__ void reduce_store(const float *red, float *__restrict
 // The B lane (col c, tid) is non-zero only when c == 2*tid (even MMA) or c == 2*tid+1 (odd MMA);
 // all other lanes read a page of zeros.
 
-struct Q4KTile {
-  uint4 hdr[2];   // rows g, g+8
-  uint4 q[2][2];  // [row][half of the 32 bytes]
-};
-
-__device__ __forceinline__ Q4KTile q4k_load(const uint4 *w, size_t row_u4, int rg, int rg8, int b, int t) {
-  Q4KTile k;
-  const uint4 *pg = w + (size_t)rg * row_u4 + b * 9, *pg8 = w + (size_t)rg8 * row_u4 + b * 9;
-  k.hdr[0] = __ldg(pg);
-  k.hdr[1] = __ldg(pg8);
-  k.q[0][0] = __ldg(pg + 1 + 2 * t);
-  k.q[0][1] = __ldg(pg + 2 + 2 * t);
-  k.q[1][0] = __ldg(pg8 + 1 + 2 * t);
-  k.q[1][1] = __ldg(pg8 + 2 + 2 * t);
-  return k;
+// (d*sc, dmin*m) of sub-blocks 2t and 2t+1 from one header; `hi` = t >= 2, sh = 16 * (t & 1).
+__device__ __forceinline__ void q4k_scales(const uint4 &h, bool hi, int sh, float (&dsc)[2], float (&dmn)[2]) {
+  const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
+  const float2 df = __half22float2(dd);  // (d, dmin)
+  // packed 6-bit fields as one byte each: sub-blocks 0..3 (lo words) or 4..7 (hi words)
+  const uint32_t scw = hi ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
+  const uint32_t mnw = hi ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
+  const uint32_t s2 = scw >> sh, m2 = mnw >> sh;
+  dsc[0] = df.x * (float)(s2 & 0xFFu);
+  dsc[1] = df.x * (float)((s2 >> 8) & 0xFFu);
+  dmn[0] = df.y * (float)(m2 & 0xFFu);
+  dmn[1] = df.y * (float)((m2 >> 8) & 0xFFu);
 }
 
-// (d*sc, dmin*m) of sub-blocks 2t and 2t+1 from one header.
-__device__ __forceinline__ void q4k_scales(const uint4 &h, int t, float (&dsc)[2], float (&dmn)[2]) {
-  const float d = f16_bits_to_f32((uint16_t)(h.x & 0xffffu)), dmin = f16_bits_to_f32((uint16_t)(h.x >> 16));
-  // packed 6-bit fields as one byte each: sub-blocks 0..3 and 4..7
-  const uint32_t sc_lo = h.y & 0x3F3F3F3Fu, mn_lo = h.z & 0x3F3F3F3Fu;
-  const uint32_t sc_hi = (h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u);
-  const uint32_t mn_hi = ((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u);
-  const uint32_t scw = t < 2 ? sc_lo : sc_hi, mnw = t < 2 ? mn_lo : mn_hi;
-  const int sh = (t & 1) * 16;
-  dsc[0] = d * (float)((scw >> sh) & 0xFFu);
-  dsc[1] = d * (float)((scw >> (sh + 8)) & 0xFFu);
-  dmn[0] = dmin * (float)((mnw >> sh) & 0xFFu);
-  dmn[1] = dmin * (float)((mnw >> (sh + 8)) & 0xFFu);
-}
-
-__global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_mma_kernel(const float *__restrict__ x,
+__global__ void __launch_bounds__(WARPS * 32, 3) q4k_gemv_mma_kernel(const float *__restrict__ x,
                                                                     const uint8_t *__restrict__ w,
                                                                     float *__restrict__ out, int N, int K, int RT) {
   using S = Slab<32>;
   __shared__ __align__(16) unsigned char slabs[WARPS][S::BYTES];
   __shared__ __align__(16) unsigned char zero[S::ZERO_BYTES];
-  __shared__ float red[WARPS * MAX_RT * ROWS];
+  __shared__ __align__(16) float2 red[WARPS * MAX_RT * 32];
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int nb = K >> 8;
   const int n0 = blockIdx.x * (ROWS * RT);
-  const size_t row_u4 = (size_t)nb * 9;
+  const uint32_t row_u4 = (uint32_t)nb * 9;
   const uint4 *w4 = reinterpret_cast<const uint4 *>(w);
   for (int i = threadIdx.x; i < S::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-
-  float *red_warp = red + warp * (MAX_RT * ROWS);
-  for (int i = lane; i < MAX_RT * ROWS; i += 32) red_warp[i] = 0.f;
-  const int last = N - 1;
-  const int r0 = n0 + g;  // row g of tile rt is min(r0 + 16 rt, last); row g+8 likewise
+  for (int i = lane; i < MAX_RT * 32; i += 32) red[warp * MAX_RT * 32 + i] = make_float2(0.f, 0.f);
 
   const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
   const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
-  // B addresses: even MMA live iff g == 2t, odd MMA live iff g == 2t+1; sub-block index == g.
-  const uint32_t pe = g == 2 * t ? slab + g * S::SUB_BYTES : szero;
-  const uint32_t po = g == 2 * t + 1 ? slab + g * S::SUB_BYTES : szero;
+  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(red + warp * MAX_RT * 32 + lane);
+  // B addresses.  The even MMA works on sub-block 2t of A-lane t: its column 2t carries the hi
+  // half of x and the otherwise unused column 2t+1 the lo half, so one MMA does both.  The odd MMA
+  // (sub-block 2t+1) has hi in column 2t+1 and lo in column 2t.  Every other column reads zeros.
+  const bool mine = (g >> 1) == t;
+  const uint32_t pe = mine ? slab + (2 * t) * S::SUB_BYTES + ((g & 1) ? S::LO_OFF : 0) : szero;
+  const uint32_t po = mine ? slab + (2 * t + 1) * S::SUB_BYTES + ((g & 1) ? 0 : S::LO_OFF) : szero;
+  const bool hdr_hi = t >= 2;
+  const int hdr_sh = (t & 1) * 16;
+  const int last = N - 1;
+  const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
 
-  constexpr uint32_t MASK = 0x00F000F0u, MAGIC = 0x54005400u;  // f16 (64 + nibble)
-  Q4KTile cur;
-  if (warp < nb) cur = q4k_load(w4, row_u4, min(r0, last), min(r0 + 8, last), warp, t);  // weights do not depend on x
-  pdl_wait();                                                                  // x does
-  __syncthreads();                                                             // zero page
-  float4 xn[2];
-  if (warp < nb) {
-    xn[0] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256) + lane);
-    xn[1] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256 + 128) + lane);
-  }
+  bool first = true;
   for (int b = warp; b < nb; b += WARPS) {
-    const float up = stage_block<32>(xn, slab, lane);
-    const int bn = b + WARPS;
-    if (bn < nb) {
-      xn[0] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256) + lane);
-      xn[1] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256 + 128) + lane);
-    }
-    __syncwarp();
-    const float2 sx = *reinterpret_cast<const float2 *>(slabs[warp] + S::SX_OFF + 8 * t);
+    float up = 1.f;
+    float2 sx = make_float2(0.f, 0.f);
     for (int rt = 0; rt < RT; rt++) {
-      Q4KTile nxt;
-      if (rt + 1 < RT)
-        nxt = q4k_load(w4, row_u4, min(r0 + (rt + 1) * ROWS, last), min(r0 + (rt + 1) * ROWS + 8, last), b, t);
-      else if (bn < nb)
-        nxt = q4k_load(w4, row_u4, min(r0, last), min(r0 + 8, last), bn, t);
+      // this tile's packed weights: header + the 32 code bytes of pair t, rows g and g+8
+      const int rg = min(n0 + rt * ROWS + g, last), rg8 = min(n0 + rt * ROWS + g + 8, last);
+      const uint4 *pg = w4 + (size_t)((uint32_t)rg * row_u4 + (uint32_t)b * 9u);
+      const uint4 *pg8 = w4 + (size_t)((uint32_t)rg8 * row_u4 + (uint32_t)b * 9u);
+      const uint4 h0 = __ldg(pg), h1 = __ldg(pg8);
+      const uint4 qa0 = __ldg(pg + 1 + 2 * t), qa1 = __ldg(pg + 2 + 2 * t);
+      const uint4 qb0 = __ldg(pg8 + 1 + 2 * t), qb1 = __ldg(pg8 + 2 + 2 * t);
+      if (rt == 0) {
+        // the block's activations, requested after the weights so that both are in flight
+        if (first) {
+          pdl_wait();  // x is the previous launch's output; the weights above are not
+          __syncthreads();
+          first = false;
+        }
+        float4 xv[2];
+        xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+        xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+        __syncwarp();  // every lane is done reading the previous block's slab
+        up = stage_block<32>(xv, slab, lane);
+        __syncwarp();
+        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + S::SX_OFF + 8 * t));
+      }
       float dsc[2][2], dmn[2][2];
-      q4k_scales(cur.hdr[0], t, dsc[0], dmn[0]);
-      q4k_scales(cur.hdr[1], t, dsc[1], dmn[1]);
+      q4k_scales(h0, hdr_hi, hdr_sh, dsc[0], dmn[0]);
+      q4k_scales(h1, hdr_hi, hdr_sh, dsc[1], dmn[1]);
       float de[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};  // even / odd sub-block chains
-      const uint32_t qg[8] = {cur.q[0][0].x, cur.q[0][0].y, cur.q[0][0].z, cur.q[0][0].w,
-                              cur.q[0][1].x, cur.q[0][1].y, cur.q[0][1].z, cur.q[0][1].w};
-      const uint32_t qh[8] = {cur.q[1][0].x, cur.q[1][0].y, cur.q[1][0].z, cur.q[1][0].w,
-                              cur.q[1][1].x, cur.q[1][1].y, cur.q[1][1].z, cur.q[1][1].w};
+      const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+      const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
 #pragma unroll
       for (int i = 0; i < 8; i++) {
         const uint32_t vg = qg[i], vh = qh[i];
-        const uint32_t e0 = ((vg << 4) & MASK) | MAGIC, e1 = ((vh << 4) & MASK) | MAGIC;
-        const uint32_t e2 = ((vg >> 4) & MASK) | MAGIC, e3 = ((vh >> 4) & MASK) | MAGIC;
-        const uint32_t o0 = (vg & MASK) | MAGIC, o1 = (vh & MASK) | MAGIC;
-        const uint32_t o2 = ((vg >> 8) & MASK) | MAGIC, o3 = ((vh >> 8) & MASK) | MAGIC;
+        const uint32_t e0 = and_or(vg << 4, mask, magic), e1 = and_or(vh << 4, mask, magic);
+        const uint32_t e2 = and_or(vg >> 4, mask, magic), e3 = and_or(vh >> 4, mask, magic);
+        const uint32_t o0 = and_or(vg, mask, magic), o1 = and_or(vh, mask, magic);
+        const uint32_t o2 = and_or(vg >> 8, mask, magic), o3 = and_or(vh >> 8, mask, magic);
         const uint2 be = lds64(pe + i * 8), bo = lds64(po + i * 8);
         mma16816(de, e0, e1, e2, e3, be.x, be.y);
         mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
-        const uint2 bel = lds64(pe + S::LO_OFF + i * 8), bol = lds64(po + S::LO_OFF + i * 8);
-        mma16816(de, e0, e1, e2, e3, bel.x, bel.y);
-        mma16816(dq, o0, o1, o2, o3, bol.x, bol.y);
       }
-      // lane (g, t): de[0] / dq[1] = row g, sub-blocks 2t / 2t+1;  de[2] / dq[3] = row g+8.
+      // lane (g, t): de[0] + de[1] = row g, sub-block 2t (hi + lo parts of x); dq[0] + dq[1] = row g,
+      // sub-block 2t+1; [2], [3] the same for row g+8.
       float vr[2];
 #pragma unroll
       for (int r = 0; r < 2; r++) {
-        float v = dsc[r][0] * de[2 * r] - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
-        v += dsc[r][1] * dq[2 * r + 1] - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
+        float v = dsc[r][0] * (de[2 * r] + de[2 * r + 1]) - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
+        v += dsc[r][1] * (dq[2 * r] + dq[2 * r + 1]) - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
         vr[r] = v * up;
       }
-      tile_accumulate(vr[0], vr[1], red_warp, rt, lane);
-      cur = nxt;
+      tile_accumulate(vr[0], vr[1], red_lane, rt);
     }
-    __syncwarp();  // the slab is rewritten by the next block's staging
+  }
+  if (first) {  // a warp without a K block still joins the CTA's barriers
+    pdl_wait();
+    __syncthreads();
   }
   reduce_store(red, out, n0, N, RT);
 }
@@ -283,137 +278,130 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_mma_kernel(const float
 // groups' 6-bit codes as bytes, then f16x2 (1024 + code) with PRMT, and group q feeds ONE MMA
 // whose 16 k slots are exactly sub-block 8h + 2q + u, live column 2q + u.
 
-__device__ __forceinline__ uint32_t ld_u32_2aligned(const uint8_t *p) {
-  const uint32_t sh = ((uint32_t)(uintptr_t)p & 2u) * 8u;  // 0 or 16
-  const uint32_t *a = reinterpret_cast<const uint32_t *>((uintptr_t)p & ~(uintptr_t)3);
-  return __funnelshift_r(__ldg(a), __ldg(a + 1), sh);
+// 32-bit load from a 2-byte aligned address: `a` is the address rounded down to 4 bytes, sh is
+// 0 (already aligned; the second word is then not fetched) or 16.
+__device__ __forceinline__ uint32_t ld_u32_sh(const uint32_t *a, uint32_t sh) {
+  const uint32_t lo = __ldg(a);
+  uint32_t hi = 0;
+  if (sh) hi = __ldg(a + 1);
+  return __funnelshift_r(lo, hi, sh);
 }
 
-struct Q6KTile {
-  uint32_t wa[2][4], wc[2][4], wh[2][4];  // [row][(h, u)]: ql[64h + l], ql[64h + 32 + l], qh[32h + l]
-  uint32_t sc[2];                         // [row]: scales 2t, 2t+1 (h = 0) | 8+2t, 8+2t+1 (h = 1), one byte each
-  uint16_t d[2];
-};
-
-__device__ __forceinline__ Q6KTile q6k_load(const uint8_t *w, size_t row_bytes, int rg, int rg8, int b, int t) {
-  Q6KTile k;
-  const uint8_t *blk[2] = {w + (size_t)rg * row_bytes + (size_t)b * 210, w + (size_t)rg8 * row_bytes + (size_t)b * 210};
-#pragma unroll
-  for (int r = 0; r < 2; r++) {
-#pragma unroll
-    for (int hu = 0; hu < 4; hu++) {
-      const int h = hu >> 1, u = hu & 1, l = 16 * u + 4 * t;
-      k.wa[r][hu] = ld_u32_2aligned(blk[r] + 64 * h + l);
-      k.wc[r][hu] = ld_u32_2aligned(blk[r] + 64 * h + 32 + l);
-      k.wh[r][hu] = ld_u32_2aligned(blk[r] + 128 + 32 * h + l);
-    }
-    const uint32_t s0 = __ldg(reinterpret_cast<const uint16_t *>(blk[r] + 192 + 2 * t));
-    const uint32_t s1 = __ldg(reinterpret_cast<const uint16_t *>(blk[r] + 200 + 2 * t));
-    k.sc[r] = s0 | (s1 << 16);
-    k.d[r] = __ldg(reinterpret_cast<const uint16_t *>(blk[r] + 208));
-  }
-  return k;
-}
-
-__global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float *__restrict__ x,
+__global__ void __launch_bounds__(WARPS * 32, 3) q6k_gemv_mma_kernel(const float *__restrict__ x,
                                                                     const uint8_t *__restrict__ w,
                                                                     float *__restrict__ out, int N, int K, int RT) {
   using S = Slab<16>;
   __shared__ __align__(16) unsigned char slabs[WARPS][S::BYTES];
   __shared__ __align__(16) unsigned char zero[S::ZERO_BYTES];
-  __shared__ float red[WARPS * MAX_RT * ROWS];
+  __shared__ __align__(16) float2 red[WARPS * MAX_RT * 32];
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int nb = K >> 8;
   const int n0 = blockIdx.x * (ROWS * RT);
-  const size_t row_bytes = (size_t)nb * 210;
+  const uint32_t row_bytes = (uint32_t)nb * 210u;  // a multiple of 4 (checked by the launcher)
   for (int i = threadIdx.x; i < S::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-
-  float *red_warp = red + warp * (MAX_RT * ROWS);
-  for (int i = lane; i < MAX_RT * ROWS; i += 32) red_warp[i] = 0.f;
-  const int last = N - 1;
-  const int r0 = n0 + g;  // row g of tile rt is min(r0 + 16 rt, last); row g+8 likewise
+  for (int i = lane; i < MAX_RT * 32; i += 32) red[warp * MAX_RT * 32 + i] = make_float2(0.f, 0.f);
 
   const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
   const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
-  // B address of the MMA of (group q, u): live iff this lane's column g == 2q + u; then the lane
-  // reads elements 4t..4t+3 of sub-block 8h + g (h adds an immediate).
+  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(red + warp * MAX_RT * 32 + lane);
+  // B address of the MMA of (group q, u), which works on sub-block 8h + 2q + u: column 2q + u
+  // carries the hi half of x, the neighbouring column 2q + 1 - u (unused in this accumulator) the
+  // lo half; a lane of those columns reads elements 4t..4t+3 (h adds an immediate).  All other
+  // columns read zeros.
   uint32_t pb[4][2];
 #pragma unroll
   for (int q = 0; q < 4; q++)
 #pragma unroll
-    for (int u = 0; u < 2; u++) pb[q][u] = g == 2 * q + u ? slab + g * S::SUB_BYTES + 8 * t : szero;
+    for (int u = 0; u < 2; u++)
+      pb[q][u] = (g >> 1) == q ? slab + (2 * q + u) * S::SUB_BYTES + 8 * t + ((g & 1) == u ? 0 : S::LO_OFF) : szero;
+  const int last = N - 1;
+  const uint32_t m0f = 0x0F0F0F0Fu;
 
-  Q6KTile cur;
-  if (warp < nb) cur = q6k_load(w, row_bytes, min(r0, last), min(r0 + 8, last), warp, t);
-  pdl_wait();
-  __syncthreads();
-  float4 xn[2];
-  if (warp < nb) {
-    xn[0] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256) + lane);
-    xn[1] = __ldg(reinterpret_cast<const float4 *>(x + warp * 256 + 128) + lane);
-  }
+  bool first = true;
   for (int b = warp; b < nb; b += WARPS) {
-    const float up = stage_block<16>(xn, slab, lane);
-    const int bn = b + WARPS;
-    if (bn < nb) {
-      xn[0] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256) + lane);
-      xn[1] = __ldg(reinterpret_cast<const float4 *>(x + bn * 256 + 128) + lane);
-    }
-    __syncwarp();
-    float2 sx[2];  // sums of x over sub-blocks 8h + 2t, 8h + 2t + 1
-    sx[0] = *reinterpret_cast<const float2 *>(slabs[warp] + S::SX_OFF + (2 * t) * 4);
-    sx[1] = *reinterpret_cast<const float2 *>(slabs[warp] + S::SX_OFF + (8 + 2 * t) * 4);
+    float up = 1.f;
+    float2 sx[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+    const uint32_t sh = (b & 1) * 16u;             // odd blocks start 2 bytes past a 4-byte boundary
+    const uint32_t boff = (uint32_t)b * 210u - (b & 1) * 2u;  // block start rounded down to 4 bytes
     for (int rt = 0; rt < RT; rt++) {
-      Q6KTile nxt;
-      if (rt + 1 < RT)
-        nxt = q6k_load(w, row_bytes, min(r0 + (rt + 1) * ROWS, last), min(r0 + (rt + 1) * ROWS + 8, last), b, t);
-      else if (bn < nb)
-        nxt = q6k_load(w, row_bytes, min(r0, last), min(r0 + 8, last), bn, t);
+      const int rg[2] = {min(n0 + rt * ROWS + g, last), min(n0 + rt * ROWS + g + 8, last)};
+      const uint32_t *blk[2];
+      uint32_t scw[2];
+      float dd[2];
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        const uint8_t *base = w + (size_t)rg[r] * row_bytes + boff;
+        blk[r] = reinterpret_cast<const uint32_t *>(base);
+        const uint8_t *bb = base + (sh >> 3);  // true block start
+        const uint32_t s0 = __ldg(reinterpret_cast<const uint16_t *>(bb + 192 + 2 * t));
+        const uint32_t s1 = __ldg(reinterpret_cast<const uint16_t *>(bb + 200 + 2 * t));
+        scw[r] = s0 | (s1 << 16);  // scales 2t, 2t+1 (h = 0) | 8+2t, 8+2t+1 (h = 1)
+        dd[r] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(bb + 208)));
+      }
+      if (rt == 0) {
+        if (first) {
+          pdl_wait();
+          __syncthreads();
+          first = false;
+        }
+        float4 xv[2];
+        xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+        xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+        __syncwarp();
+        up = stage_block<16>(xv, slab, lane);
+        __syncwarp();
+        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[0].x), "=f"(sx[0].y) : "r"(slab + S::SX_OFF + 8 * t));
+        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[1].x), "=f"(sx[1].y) : "r"(slab + S::SX_OFF + 32 + 8 * t));
+      }
       float vr[2] = {0.f, 0.f};
 #pragma unroll
       for (int h = 0; h < 2; h++) {
         float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // u = 0 / u = 1 chains
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-          const int hu = 2 * h + u;
+          uint32_t wa[2], wc[2], wh[2];  // ql[64h + l], ql[64h + 32 + l], qh[32h + l], l = 16u + 4t
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            wa[r] = ld_u32_sh(blk[r] + 16 * h + 4 * u + t, sh);
+            wc[r] = ld_u32_sh(blk[r] + 16 * h + 8 + 4 * u + t, sh);
+            wh[r] = ld_u32_sh(blk[r] + 32 + 8 * h + 4 * u + t, sh);
+          }
 #pragma unroll
           for (int q = 0; q < 4; q++) {
             uint32_t a[4];
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-              const uint32_t lo4 = (q & 1) ? cur.wc[r][hu] : cur.wa[r][hu];
+              const uint32_t lo4 = (q & 1) ? wc[r] : wa[r];
               const uint32_t nib = (q >> 1) ? (lo4 >> 4) : lo4;
-              const uint32_t hi2 = q == 0 ? (cur.wh[r][hu] << 4) : q == 1 ? (cur.wh[r][hu] << 2)
-                                   : q == 2 ? cur.wh[r][hu] : (cur.wh[r][hu] >> 2);
-              const uint32_t v = (nib & 0x0F0F0F0Fu) | (hi2 & 0x30303030u);
+              const uint32_t hi2 = q == 0 ? (wh[r] << 4) : q == 1 ? (wh[r] << 2) : q == 2 ? wh[r] : (wh[r] >> 2);
+              const uint32_t v = and_or(nib, m0f, hi2 & 0x30303030u);
               a[r] = __byte_perm(v, 0x64646464u, 0x4240);      // f16x2 (1024 + b0, 1024 + b2)
               a[2 + r] = __byte_perm(v, 0x64646464u, 0x4341);  // f16x2 (1024 + b1, 1024 + b3)
             }
             const uint32_t p = pb[q][u] + h * (8 * S::SUB_BYTES);
-            const uint2 bh = lds64(p), bl = lds64(p + S::LO_OFF);
-            if (u == 0) {
+            const uint2 bh = lds64(p);
+            if (u == 0)
               mma16816(d0, a[0], a[1], a[2], a[3], bh.x, bh.y);
-              mma16816(d0, a[0], a[1], a[2], a[3], bl.x, bl.y);
-            } else {
+            else
               mma16816(d1, a[0], a[1], a[2], a[3], bh.x, bh.y);
-              mma16816(d1, a[0], a[1], a[2], a[3], bl.x, bl.y);
-            }
           }
         }
-        // lane (g, t): d0[0] / d1[1] = row g, sub-blocks 8h+2t / 8h+2t+1;  d0[2] / d1[3] = row g+8
+        // lane (g, t): d0[0] + d0[1] = row g, sub-block 8h+2t; d1[0] + d1[1] = row g, sub-block 8h+2t+1;
+        // [2], [3] the same for row g+8
 #pragma unroll
         for (int r = 0; r < 2; r++) {
-          const float d = f16_bits_to_f32(cur.d[r]);
-          const float s0 = d * (float)(int8_t)((cur.sc[r] >> (16 * h)) & 0xff);
-          const float s1 = d * (float)(int8_t)((cur.sc[r] >> (16 * h + 8)) & 0xff);
-          vr[r] += (s0 * (d0[2 * r] - 1056.f * sx[h].x) + s1 * (d1[2 * r + 1] - 1056.f * sx[h].y)) * up;
+          const float s0 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h)) & 0xff);
+          const float s1 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h + 8)) & 0xff);
+          vr[r] += s0 * (d0[2 * r] + d0[2 * r + 1] - 1056.f * sx[h].x) + s1 * (d1[2 * r] + d1[2 * r + 1] - 1056.f * sx[h].y);
         }
       }
-      tile_accumulate(vr[0], vr[1], red_warp, rt, lane);
-      cur = nxt;
+      tile_accumulate(vr[0] * up, vr[1] * up, red_lane, rt);
     }
-    __syncwarp();
+  }
+  if (first) {
+    pdl_wait();
+    __syncthreads();
   }
   reduce_store(red, out, n0, N, RT);
 }
@@ -441,7 +429,6 @@ int g_rt_override = 0;  // LIGHT_B200_GEMV_RT: tuning knob, 0 = choose by shape
 int pick_rt(int N) {
   if (g_rt_override > 0) return g_rt_override < MAX_RT ? g_rt_override : MAX_RT;
   const int tiles = (N + ROWS - 1) / ROWS;
-  if (tiles >= 148 * 16) return 8;
   if (tiles >= 148 * 8) return 4;
   if (tiles >= 148 * 4) return 2;
   return 1;
