@@ -148,6 +148,30 @@ typedef struct lb200_moe_args {
 /* Registry key {moe_gemm, CUDA, F32|BF16|F16} (reference kernels/cuda/moe.go:21-97). */
 LB200_API int light_b200_moe_gemm(const lb200_moe_args *args, int device, void *stream);
 
+/* Largest expert count light_b200_moe_gemm_static_scratch accepts. */
+#define LB200_MOE_STATIC_MAX_EXPERTS 1024
+
+/* light_b200_moe_gemm for callers that cannot hand over scratch memory.  (No counterpart in the
+ * reference: its launcher always receives counts / offsets tensors from the Go tensor pool.)
+ *
+ * Some callers of a C ABI have nothing to allocate with at the call site: a thin FFI stub that
+ * only forwards the pointers it was given, a serving loop that has handed all device memory to
+ * its own pool, or code that must not call cudaMalloc because it can synchronise the device and
+ * can fail late.  For them this variant keeps the per-expert counts and offsets in a fixed device
+ * array inside the library (8 KiB + 8 B per GPU that loads the library, held until the process
+ * exits); args->counts and args->offsets are ignored and may be null.  Everything else -- inputs,
+ * weights, routing, output -- is still the caller's memory, and the result is the same as
+ * light_b200_moe_gemm's.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *
+ *   - args->E must not exceed LB200_MOE_STATIC_MAX_EXPERTS, else LB200_E_TOO_LARGE.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call before any stream capture begins.
+ *   - Every call on a device shares the one array, which keeps the previous call's contents.
+ *     Each call overwrites all E counts and E + 1 offsets before reading them, so nothing has to
+ *     be cleared -- but two calls that overlap on the GPU (different streams, or graphs replayed
+ *     concurrently) race on it.  Serialise them, or use light_b200_moe_gemm with own scratch. */
+LB200_API int light_b200_moe_gemm_static_scratch(const lb200_moe_args *args, int device, void *stream);
+
 /* Registry key {moe_gemm_q, CUDA, <w dtype>} (reference kernels/cuda/moe.go:99-141):
  * x f32, GGUF block-quantized experts, out f32. */
 LB200_API int light_b200_moe_gemm_q(const lb200_moe_args *args, int device, void *stream);

@@ -175,7 +175,7 @@ int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *s, v
   return fp8_block_gemv(x, w, s, y, act_dtype, M, N, K, bR, bC, (cudaStream_t)stream);
 }
 
-static int moe_check(const lb200_moe_args *a, const char *op, bool quant) {
+static int moe_check(const lb200_moe_args *a, const char *op, bool quant, bool need_scratch = true) {
   if (!a) return fail(LB200_E_NULL, "light_b200: %s: null argument block", op);
   if (a->M < 0 || a->size_m < 0 || a->E <= 0 || a->N < 0 || a->K <= 0 || a->topk < 1)
     return fail(LB200_E_SHAPE, "light_b200: %s: bad shape M=%lld size_m=%lld E=%d N=%d K=%d topk=%d", op, (long long)a->M,
@@ -189,7 +189,8 @@ static int moe_check(const lb200_moe_args *a, const char *op, bool quant) {
       return fail(LB200_E_DTYPE, "light_b200: %s: element type %d, want F32, BF16 or F16", op, a->dtype);
     if (a->K % 8) return fail(LB200_E_SHAPE, "light_b200: %s: K=%d must be a multiple of 8", op, a->K);
   }
-  if (!a->counts || !a->offsets) return fail(LB200_E_NULL, "light_b200: %s: counts / offsets scratch missing", op);
+  if (need_scratch && (!a->counts || !a->offsets))
+    return fail(LB200_E_NULL, "light_b200: %s: counts / offsets scratch missing", op);
   if (a->M > 0 && (!a->input || !a->weights || !a->sorted_pairs || !a->expert_ids || !a->out))
     return fail(LB200_E_NULL, "light_b200: %s: null tensor pointer", op);
   if (a->M > 0 && (!aligned(a->input, 16) || !aligned(a->weights, quant ? 2 : 16)))
@@ -201,6 +202,12 @@ int light_b200_moe_gemm(const lb200_moe_args *a, int device, void *stream) {
   if (int rc = moe_check(a, "moe_gemm", false)) return rc;
   if (int rc = bind(device)) return rc;
   return moe_gemm(a, (cudaStream_t)stream);
+}
+
+int light_b200_moe_gemm_static_scratch(const lb200_moe_args *a, int device, void *stream) {
+  if (int rc = moe_check(a, "moe_gemm_static_scratch", false, false)) return rc;
+  if (int rc = bind(device)) return rc;
+  return moe_gemm_static_scratch(a, device, (cudaStream_t)stream);
 }
 
 int light_b200_moe_gemm_q(const lb200_moe_args *a, int device, void *stream) {

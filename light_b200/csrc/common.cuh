@@ -60,5 +60,6 @@ int fp8_block_gemv(const void *x, const uint8_t *w, const float *s, void *y, int
                    int bC, cudaStream_t st);
 int moe_gemm(const lb200_moe_args *a, cudaStream_t st);
 int moe_gemm_q(const lb200_moe_args *a, cudaStream_t st);
+int moe_gemm_static_scratch(const lb200_moe_args *a, int device, cudaStream_t st);
 
 }  // namespace lb

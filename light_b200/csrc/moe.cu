@@ -6,6 +6,8 @@
 // Pairs arrive sorted by expert, so expert e owns the index range offsets[e] .. offsets[e+1].
 // The ranges come from boundary detection on the sorted expert ids (no atomics, deterministic);
 // every output row is written by exactly one warp lane set, so the result is deterministic too.
+#include <mutex>
+
 #include "gguf_decode.cuh"
 
 namespace lb {
@@ -164,6 +166,39 @@ int moe_gemm(const lb200_moe_args *a, cudaStream_t st) {
     case LB200_F16: return run<__half, __half, DenseRow<__half>>(a, st);
   }
   return fail(LB200_E_DTYPE, "moe_gemm: element type %d has no kernel", a->dtype);
+}
+
+// ---- grouped matmul whose expert counts / offsets live in this library's own device memory.
+//
+// The scratch is one file-scope device array, so the entry point needs no allocation by anyone:
+// not by the caller, not by this library, not by a tensor pool.  In host code the array's name
+// is only a stand-in for the device symbol, so its device address is looked up once per device
+// (with that device current) and that address is what the kernels are given.
+static __device__ __align__(256) int32_t g_moe_static_scratch[2 * LB200_MOE_STATIC_MAX_EXPERTS + 2];
+static int32_t *g_moe_static_ptr[64];
+static std::mutex g_moe_static_mu;
+
+int moe_gemm_static_scratch(const lb200_moe_args *a, int device, cudaStream_t st) {
+  if (a->E > LB200_MOE_STATIC_MAX_EXPERTS)
+    return fail(LB200_E_TOO_LARGE, "light_b200: moe_gemm_static_scratch: %d experts exceed the built-in scratch (max %d)",
+                a->E, LB200_MOE_STATIC_MAX_EXPERTS);
+  int32_t *base;
+  {
+    std::lock_guard<std::mutex> lk(g_moe_static_mu);
+    base = g_moe_static_ptr[device];
+    if (!base) {  // first call on this device: resolve the symbol's device address
+      cudaError_t e = cudaGetSymbolAddress((void **)&base, g_moe_static_scratch);
+      if (e != cudaSuccess)
+        return fail((int)e, "light_b200: moe_gemm_static_scratch: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      g_moe_static_ptr[device] = base;
+    }
+  }
+  lb200_moe_args b = *a;
+  b.counts = base;                                      // E entries
+  b.offsets = base + LB200_MOE_STATIC_MAX_EXPERTS + 1;  // E + 1 entries
+  // Both ranges are fully overwritten by the offsets / counts kernels before the matmul reads
+  // them, so what an earlier call left behind never matters and nothing needs clearing.
+  return moe_gemm(&b, st);
 }
 
 int moe_gemm_q(const lb200_moe_args *a, cudaStream_t st) {
