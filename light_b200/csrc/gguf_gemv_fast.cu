@@ -159,6 +159,10 @@ __device__ __forceinline__ void reduce_store(const float2 *red, float *__restric
 // The B lane (col c, tid) is non-zero only when c == 2*tid (even MMA) or c == 2*tid+1 (odd MMA);
 // all other lanes read a page of zeros.
 
+struct Q4KTile {
+  uint4 h0, h1, qa0, qa1, qb0, qb1;  // headers of rows g, g+8; the 32 code bytes of pair t of each
+};
+
 // (d*sc, dmin*m) of sub-blocks 2t and 2t+1 from one header; `hi` = t >= 2, sh = 16 * (t & 1).
 __device__ __forceinline__ void q4k_scales(const uint4 &h, bool hi, int sh, float (&dsc)[2], float (&dmn)[2]) {
   const __half2 dd = *reinterpret_cast<const __half2 *>(&h.x);
@@ -173,7 +177,7 @@ __device__ __forceinline__ void q4k_scales(const uint4 &h, bool hi, int sh, floa
   dmn[1] = df.y * (float)((m2 >> 8) & 0xFFu);
 }
 
-__global__ void __launch_bounds__(WARPS * 32, 3) q4k_gemv_mma_kernel(const float *__restrict__ x,
+__global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_mma_kernel(const float *__restrict__ x,
                                                                     const uint8_t *__restrict__ w,
                                                                     float *__restrict__ out, int N, int K, int RT) {
   using S = Slab<32>;
@@ -203,61 +207,79 @@ __global__ void __launch_bounds__(WARPS * 32, 3) q4k_gemv_mma_kernel(const float
   const int last = N - 1;
   const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
 
+  // Units of work of this warp, in order: (its K blocks) x (the CTA's RT row tiles).  The packed
+  // weights of unit u+1 are requested before unit u is computed (two register sets, alternating),
+  // and the first unit's before griddepcontrol.wait, so loads of the next tile -- and of the next
+  // launch -- are in flight while this one computes.
+  const int nbw = warp < nb ? (nb - warp + WARPS - 1) / WARPS : 0;
+  const int rt_shift = RT == 4 ? 2 : RT == 2 ? 1 : 0;
+  const int U = nbw << rt_shift;
   bool first = true;
-  for (int b = warp; b < nb; b += WARPS) {
-    float up = 1.f;
-    float2 sx = make_float2(0.f, 0.f);
-    for (int rt = 0; rt < RT; rt++) {
-      // this tile's packed weights: header + the 32 code bytes of pair t, rows g and g+8
-      const int rg = min(n0 + rt * ROWS + g, last), rg8 = min(n0 + rt * ROWS + g + 8, last);
-      const uint4 *pg = w4 + (size_t)((uint32_t)rg * row_u4 + (uint32_t)b * 9u);
-      const uint4 *pg8 = w4 + (size_t)((uint32_t)rg8 * row_u4 + (uint32_t)b * 9u);
-      const uint4 h0 = __ldg(pg), h1 = __ldg(pg8);
-      const uint4 qa0 = __ldg(pg + 1 + 2 * t), qa1 = __ldg(pg + 2 + 2 * t);
-      const uint4 qb0 = __ldg(pg8 + 1 + 2 * t), qb1 = __ldg(pg8 + 2 + 2 * t);
-      if (rt == 0) {
-        // the block's activations, requested after the weights so that both are in flight
-        if (first) {
-          pdl_wait();  // x is the previous launch's output; the weights above are not
-          __syncthreads();
-          first = false;
-        }
-        float4 xv[2];
-        xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
-        xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
-        __syncwarp();  // every lane is done reading the previous block's slab
-        up = stage_block<32>(xv, slab, lane);
-        __syncwarp();
-        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + S::SX_OFF + 8 * t));
+  float up = 1.f;
+  float2 sx = make_float2(0.f, 0.f);
+
+  auto issue = [&](Q4KTile &T, int u) {
+    const int b = warp + (u >> rt_shift) * WARPS, rt = u & (RT - 1);
+    const int rg = min(n0 + rt * ROWS + g, last), rg8 = min(n0 + rt * ROWS + g + 8, last);
+    const uint4 *pg = w4 + (size_t)((uint32_t)rg * row_u4 + (uint32_t)b * 9u);
+    const uint4 *pg8 = w4 + (size_t)((uint32_t)rg8 * row_u4 + (uint32_t)b * 9u);
+    T.h0 = __ldg(pg), T.h1 = __ldg(pg8);
+    T.qa0 = __ldg(pg + 1 + 2 * t), T.qa1 = __ldg(pg + 2 + 2 * t);
+    T.qb0 = __ldg(pg8 + 1 + 2 * t), T.qb1 = __ldg(pg8 + 2 + 2 * t);
+  };
+  auto process = [&](const Q4KTile &T, int u) {
+    const int b = warp + (u >> rt_shift) * WARPS, rt = u & (RT - 1);
+    if (rt == 0) {
+      if (first) {
+        pdl_wait();  // x is the previous launch's output; the weights requested above are not
+        __syncthreads();
+        first = false;
       }
-      float dsc[2][2], dmn[2][2];
-      q4k_scales(h0, hdr_hi, hdr_sh, dsc[0], dmn[0]);
-      q4k_scales(h1, hdr_hi, hdr_sh, dsc[1], dmn[1]);
-      float de[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};  // even / odd sub-block chains
-      const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
-      const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-#pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const uint32_t vg = qg[i], vh = qh[i];
-        const uint32_t e0 = and_or(vg << 4, mask, magic), e1 = and_or(vh << 4, mask, magic);
-        const uint32_t e2 = and_or(vg >> 4, mask, magic), e3 = and_or(vh >> 4, mask, magic);
-        const uint32_t o0 = and_or(vg, mask, magic), o1 = and_or(vh, mask, magic);
-        const uint32_t o2 = and_or(vg >> 8, mask, magic), o3 = and_or(vh >> 8, mask, magic);
-        const uint2 be = lds64(pe + i * 8), bo = lds64(po + i * 8);
-        mma16816(de, e0, e1, e2, e3, be.x, be.y);
-        mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
-      }
-      // lane (g, t): de[0] + de[1] = row g, sub-block 2t (hi + lo parts of x); dq[0] + dq[1] = row g,
-      // sub-block 2t+1; [2], [3] the same for row g+8.
-      float vr[2];
-#pragma unroll
-      for (int r = 0; r < 2; r++) {
-        float v = dsc[r][0] * (de[2 * r] + de[2 * r + 1]) - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
-        v += dsc[r][1] * (dq[2 * r] + dq[2 * r + 1]) - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
-        vr[r] = v * up;
-      }
-      tile_accumulate(vr[0], vr[1], red_lane, rt);
+      float4 xv[2];
+      xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+      xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+      __syncwarp();  // every lane is done reading the previous block's slab
+      up = stage_block<32>(xv, slab, lane);
+      __syncwarp();
+      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + S::SX_OFF + 8 * t));
     }
+    float dsc[2][2], dmn[2][2];
+    q4k_scales(T.h0, hdr_hi, hdr_sh, dsc[0], dmn[0]);
+    q4k_scales(T.h1, hdr_hi, hdr_sh, dsc[1], dmn[1]);
+    float de[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};  // even / odd sub-block chains
+    const uint32_t qg[8] = {T.qa0.x, T.qa0.y, T.qa0.z, T.qa0.w, T.qa1.x, T.qa1.y, T.qa1.z, T.qa1.w};
+    const uint32_t qh[8] = {T.qb0.x, T.qb0.y, T.qb0.z, T.qb0.w, T.qb1.x, T.qb1.y, T.qb1.z, T.qb1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const uint32_t vg = qg[i], vh = qh[i];
+      const uint32_t e0 = and_or(vg << 4, mask, magic), e1 = and_or(vh << 4, mask, magic);
+      const uint32_t e2 = and_or(vg >> 4, mask, magic), e3 = and_or(vh >> 4, mask, magic);
+      const uint32_t o0 = and_or(vg, mask, magic), o1 = and_or(vh, mask, magic);
+      const uint32_t o2 = and_or(vg >> 8, mask, magic), o3 = and_or(vh >> 8, mask, magic);
+      const uint2 be = lds64(pe + i * 8), bo = lds64(po + i * 8);
+      mma16816(de, e0, e1, e2, e3, be.x, be.y);
+      mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
+    }
+    // lane (g, t): de[0] + de[1] = row g, sub-block 2t (hi + lo parts of x); dq[0] + dq[1] = row g,
+    // sub-block 2t+1; [2], [3] the same for row g+8.
+    float vr[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      float v = dsc[r][0] * (de[2 * r] + de[2 * r + 1]) - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
+      v += dsc[r][1] * (dq[2 * r] + dq[2 * r + 1]) - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
+      vr[r] = v * up;
+    }
+    tile_accumulate(vr[0], vr[1], red_lane, rt);
+  };
+
+  Q4KTile ta, tb;
+  if (U > 0) issue(ta, 0);
+  for (int u = 0; u < U; u += 2) {
+    if (u + 1 < U) issue(tb, u + 1);
+    process(ta, u);
+    if (u + 1 >= U) break;
+    if (u + 2 < U) issue(ta, u + 2);
+    process(tb, u + 1);
   }
   if (first) {  // a warp without a K block still joins the CTA's barriers
     pdl_wait();
@@ -338,6 +360,20 @@ __global__ void __launch_bounds__(WARPS * 32, 3) q6k_gemv_mma_kernel(const float
         const uint32_t s1 = __ldg(reinterpret_cast<const uint16_t *>(bb + 200 + 2 * t));
         scw[r] = s0 | (s1 << 16);  // scales 2t, 2t+1 (h = 0) | 8+2t, 8+2t+1 (h = 1)
         dd[r] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(bb + 208)));
+      }
+      {
+        // pull the next unit's rows towards L2 while this one is being worked on: the three cache
+        // lines a 210-byte block can touch, one per lane t < 3, for both rows
+        const bool more_rt = rt + 1 < RT;
+        const int bn = more_rt ? b : b + WARPS, rtn = more_rt ? rt + 1 : 0;
+        if (bn < nb && t < 3) {
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            const int rn = min(n0 + rtn * ROWS + g + 8 * r, last);
+            const uint8_t *pn = w + (size_t)rn * row_bytes + (uint32_t)bn * 210u + t * 104 + (t >> 1);
+            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(pn));
+          }
+        }
       }
       if (rt == 0) {
         if (first) {
@@ -427,7 +463,7 @@ int launch_pdl(void (*kern)(Args...), unsigned grid, cudaStream_t st, Args... ar
 // allows (each tile reuses the block's converted activations).
 int g_rt_override = 0;  // LIGHT_B200_GEMV_RT: tuning knob, 0 = choose by shape
 int pick_rt(int N) {
-  if (g_rt_override > 0) return g_rt_override < MAX_RT ? g_rt_override : MAX_RT;
+  if (g_rt_override > 0) return g_rt_override >= 4 ? 4 : g_rt_override >= 2 ? 2 : 1;
   const int tiles = (N + ROWS - 1) / ROWS;
   if (tiles >= 148 * 8) return 4;
   if (tiles >= 148 * 4) return 2;
