@@ -309,7 +309,7 @@ __device__ __forceinline__ uint32_t ld_u32_sh(const uint32_t *a, uint32_t sh) {
   return __funnelshift_r(lo, hi, sh);
 }
 
-__global__ void __launch_bounds__(WARPS * 32, 3) q6k_gemv_mma_kernel(const float *__restrict__ x,
+__global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float *__restrict__ x,
                                                                     const uint8_t *__restrict__ w,
                                                                     float *__restrict__ out, int N, int K, int RT) {
   using S = Slab<16>;
@@ -361,6 +361,18 @@ __global__ void __launch_bounds__(WARPS * 32, 3) q6k_gemv_mma_kernel(const float
         scw[r] = s0 | (s1 << 16);  // scales 2t, 2t+1 (h = 0) | 8+2t, 8+2t+1 (h = 1)
         dd[r] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(bb + 208)));
       }
+      // all code words of the tile are requested up front: [row][(h, u)] = ql[64h + l], ql[64h + 32 + l],
+      // qh[32h + l] for l = 16u + 4t
+      uint32_t wa[2][4], wc[2][4], wh[2][4];
+#pragma unroll
+      for (int r = 0; r < 2; r++)
+#pragma unroll
+        for (int hu = 0; hu < 4; hu++) {
+          const int h = hu >> 1, u = hu & 1;
+          wa[r][hu] = ld_u32_sh(blk[r] + 16 * h + 4 * u + t, sh);
+          wc[r][hu] = ld_u32_sh(blk[r] + 16 * h + 8 + 4 * u + t, sh);
+          wh[r][hu] = ld_u32_sh(blk[r] + 32 + 8 * h + 4 * u + t, sh);
+        }
       {
         // pull the next unit's rows towards L2 while this one is being worked on: the three cache
         // lines a 210-byte block can touch, one per lane t < 3, for both rows
@@ -396,21 +408,15 @@ __global__ void __launch_bounds__(WARPS * 32, 3) q6k_gemv_mma_kernel(const float
         float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // u = 0 / u = 1 chains
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-          uint32_t wa[2], wc[2], wh[2];  // ql[64h + l], ql[64h + 32 + l], qh[32h + l], l = 16u + 4t
-#pragma unroll
-          for (int r = 0; r < 2; r++) {
-            wa[r] = ld_u32_sh(blk[r] + 16 * h + 4 * u + t, sh);
-            wc[r] = ld_u32_sh(blk[r] + 16 * h + 8 + 4 * u + t, sh);
-            wh[r] = ld_u32_sh(blk[r] + 32 + 8 * h + 4 * u + t, sh);
-          }
+          const int hu = 2 * h + u;
 #pragma unroll
           for (int q = 0; q < 4; q++) {
             uint32_t a[4];
 #pragma unroll
             for (int r = 0; r < 2; r++) {
-              const uint32_t lo4 = (q & 1) ? wc[r] : wa[r];
+              const uint32_t lo4 = (q & 1) ? wc[r][hu] : wa[r][hu];
               const uint32_t nib = (q >> 1) ? (lo4 >> 4) : lo4;
-              const uint32_t hi2 = q == 0 ? (wh[r] << 4) : q == 1 ? (wh[r] << 2) : q == 2 ? wh[r] : (wh[r] >> 2);
+              const uint32_t hi2 = q == 0 ? (wh[r][hu] << 4) : q == 1 ? (wh[r][hu] << 2) : q == 2 ? wh[r][hu] : (wh[r][hu] >> 2);
               const uint32_t v = and_or(nib, m0f, hi2 & 0x30303030u);
               a[r] = __byte_perm(v, 0x64646464u, 0x4240);      // f16x2 (1024 + b0, 1024 + b2)
               a[2 + r] = __byte_perm(v, 0x64646464u, 0x4341);  // f16x2 (1024 + b1, 1024 + b3)
