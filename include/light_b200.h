@@ -76,6 +76,19 @@ LB200_API int light_b200_abi_version(void);
 /* Number of kernels this library has launched on any stream since load (monotonic). */
 LB200_API unsigned long long light_b200_launch_count(void);
 
+/* Hands the library a per-device workspace it may use between calls on that device (device
+ * memory, 1024-byte aligned, owned by the caller, valid until replaced; ptr = NULL withdraws it).
+ * The reference keeps the same kind of buffer, one reusable weight scratch per device
+ * (ops/fp8_block.go:105-154 weightScratch).  Here it holds the f16 copy of the activations that the
+ * tensor-core prefill path streams by TMA: matmul_q with M > 64 needs M * K * 2 bytes; without a
+ * large enough workspace such calls run the slower shape-generic kernel.  Calls that use the
+ * workspace must not overlap on the GPU. */
+LB200_API int light_b200_set_workspace(int device, void *ptr, size_t bytes);
+
+/* 0 if no bounded device-side wait of the tensor-core kernels ever gave up on this device, 1 if one
+ * did (the affected call's output is then incomplete).  Synchronises with the device. */
+LB200_API int light_b200_prefill_status(int device);
+
 /* Block geometry: elements / bytes per block, 0 for an unknown type
  * (reference dtype/dtype.go:53-102 blockInfo, BlockElems, BlockBytes). */
 LB200_API int light_b200_block_elems(int ggml_type);

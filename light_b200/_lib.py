@@ -37,6 +37,8 @@ SYMBOLS = {
     "light_b200_last_error": (C.c_int, [C.c_char_p, C.c_size_t]),
     "light_b200_abi_version": (C.c_int, []),
     "light_b200_launch_count": (C.c_ulonglong, []),
+    "light_b200_set_workspace": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t]),
+    "light_b200_prefill_status": (C.c_int, [C.c_int]),
     "light_b200_block_elems": (C.c_int, [C.c_int]),
     "light_b200_block_bytes": (C.c_int, [C.c_int]),
     "light_b200_matmul_q": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,

@@ -76,6 +76,16 @@ int light_b200_last_error(char *buf, size_t n) {
 }
 
 int light_b200_abi_version(void) { return LIGHT_B200_ABI_VERSION; }
+
+int light_b200_set_workspace(int device, void *ptr, size_t bytes) {
+  if (int rc = bind(device)) return rc;
+  return set_workspace(device, ptr, bytes);
+}
+
+int light_b200_prefill_status(int device) {
+  if (int rc = bind(device)) return rc;
+  return prefill_status(device);
+}
 unsigned long long light_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 int light_b200_block_elems(int t) { return block_elems(t); }
 int light_b200_block_bytes(int t) { return block_bytes(t); }
@@ -96,6 +106,8 @@ int light_b200_matmul_q(int t, const float *x, const void *w, float *out, int M,
   int took = gguf_gemv_fast(t, x, w, out, M, N, K, st);
   if (took < 0) return took;
   if (took) return 0;
+  took = gguf_prefill(t, x, w, out, M, N, K, device, st);
+  if (took != 0) return took == 1 ? 0 : took;
   return gguf_matmul_generic(t, x, w, out, M, N, K, st);
 }
 

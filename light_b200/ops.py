@@ -100,6 +100,28 @@ def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
     return C.c_void_p(0 if t is None else t.data_ptr())
 
 
+# --------------------------------------------------------------------------- workspace
+
+_workspaces = {}  # device index -> torch uint8 buffer handed to the library
+
+
+def ensure_workspace(device_index: int, nbytes: int) -> None:
+    """Keeps one reusable device buffer per GPU registered with the library (the counterpart of the
+    reference's per-device weight scratch, ops/fp8_block.go:105-154); grows it when a call needs more."""
+    cur = _workspaces.get(device_index)
+    if cur is not None and cur.numel() >= nbytes:
+        return
+    buf = torch.empty(max(nbytes, 1 << 20) + 1024, dtype=torch.uint8, device=torch.device("cuda", device_index))
+    off = (-buf.data_ptr()) % 1024
+    _lib.check(_lib.lib().light_b200_set_workspace(device_index, C.c_void_p(buf.data_ptr() + off), buf.numel() - 1024))
+    _workspaces[device_index] = buf
+
+
+def prefill_status(device_index: int = 0) -> int:
+    """0 unless a bounded wait inside a tensor-core kernel gave up on this device."""
+    return _lib.lib().light_b200_prefill_status(device_index)
+
+
 # --------------------------------------------------------------------------- GGUF
 
 def MatMulQ(x: torch.Tensor, w: QTensor) -> torch.Tensor:
@@ -116,6 +138,8 @@ def MatMulQ(x: torch.Tensor, w: QTensor) -> torch.Tensor:
         raise ValueError(f"MatMulQ: inner dim mismatch (x K={K}, w K={w.shape[1]})")
     dev = _dev(x, "MatMulQ")
     xc = x.contiguous()
+    if M > 64:  # the tensor-core prefill path streams an f16 copy of x from the workspace
+        ensure_workspace(dev, M * K * 2)
     out = torch.empty((M, N), dtype=torch.float32, device=x.device)
     _lib.check(_lib.lib().light_b200_matmul_q(w.ggml_type, _ptr(xc), _ptr(w.data), _ptr(out), M, N, K, dev,
                                               _stream(dev)))
