@@ -59,7 +59,7 @@ __device__ __forceinline__ void expand4(uint32_t bytes, float s, float m, uint32
 // load(): fetch the block into registers.  step(j, ...): write the 64 weights k = 64j .. 64j+63 of
 // the block as 8 swizzled 16-byte chunks of row `r` of the B tile at shared address `tile`.
 struct Q4KRow {
-  static constexpr int BLOCK_BYTES = 144;
+  static constexpr int BLOCK_BYTES = 144, STEPS = 4;  // one load() = one 256-element block = 4 steps
   uint4 h, q[8];
   __device__ __forceinline__ void load(const uint8_t *row, int kb) {
     const uint4 *p = reinterpret_cast<const uint4 *>(row) + (size_t)kb * 9;
@@ -92,6 +92,55 @@ struct Q4KRow {
       expand4((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, s1, m1, hi.z, hi.w);
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(tile + swz(r, c)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w));
       asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(tile + swz(r, c + 4)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w));
+    }
+  }
+};
+
+// Q6_K (210 B): [ql[128] | qh[64] | int8 sc[16] | f16 d].  One load() fetches a 128-element half h:
+// ql[64h .. 64h+63], qh[32h .. 32h+31], sc[8h .. 8h+7], d.  Step j (k = 64j .. 64j+63 of the half)
+// covers groups q = 2j, 2j+1: code = (ql[64h + 32(q&1) + l] >> 4j) & 15 | ((qh[32h + l] >> 2q) & 3) << 4,
+// weight = d * sc[8h + 4j + k/16] * (code - 32).  Blocks are only 2-byte aligned: each word is two
+// aligned 32-bit loads funnel-shifted by 0 or 16 bits (rows start 4-byte aligned, checked on the host).
+struct Q6KRow {
+  static constexpr int BLOCK_BYTES = 210, STEPS = 2;
+  uint32_t ql[16], qh[8], sc[2];
+  float d;
+  __device__ __forceinline__ static uint32_t ld(const uint32_t *a, uint32_t sh) {
+    const uint32_t lo = __ldg(a);
+    uint32_t hi = 0;
+    if (sh) hi = __ldg(a + 1);
+    return __funnelshift_r(lo, hi, sh);
+  }
+  __device__ __forceinline__ void load(const uint8_t *row, int unit) {
+    const int b = unit >> 1, h = unit & 1;
+    const uint32_t sh = (b & 1) * 16u;
+    const uint8_t *blk = row + (size_t)b * 210;
+    const uint32_t *a = reinterpret_cast<const uint32_t *>(blk - (b & 1) * 2);  // rounded down to 4 bytes
+#pragma unroll
+    for (int i = 0; i < 16; i++) ql[i] = ld(a + 16 * h + i, sh);
+#pragma unroll
+    for (int i = 0; i < 8; i++) qh[i] = ld(a + 32 + 8 * h + i, sh);
+    sc[0] = ld(a + 48 + 2 * h, sh), sc[1] = ld(a + 49 + 2 * h, sh);
+    d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(blk + 208)));
+  }
+  __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
+#pragma unroll
+    for (int c = 0; c < 8; c++) {  // chunk c: k = 8c .. 8c+7 -> group q = 2j + c/4, l = 8 (c%4) ..
+      const int q = 2 * j + (c >> 2), li = 2 * (c & 3);
+      const float ds = d * (float)(int8_t)((sc[j] >> (8 * (c >> 1))) & 0xff);
+      const float m = 32.f * ds;
+      uint4 o;
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const uint32_t wq = ql[8 * (c >> 2) + li + e] >> (4 * j), wh = qh[li + e];
+        const uint32_t hi2 = q == 0 ? (wh << 4) : q == 1 ? (wh << 2) : q == 2 ? wh : (wh >> 2);
+        const uint32_t v = (wq & 0x0F0F0F0Fu) | (hi2 & 0x30303030u);
+        if (e == 0)
+          expand4(v, ds, m, o.x, o.y);
+        else
+          expand4(v, ds, m, o.z, o.w);
+      }
+      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(tile + swz(r, c)), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w));
     }
   }
 };
@@ -186,12 +235,13 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
     Row cur;
     cur.load(row, 0);
     bool ok = true;
-    for (int blk = 0; blk < K / 256 && ok; blk++) {
+    const int units = K / (BK * Row::STEPS);
+    for (int u = 0; u < units && ok; u++) {
       Row nxt;
-      if (blk + 1 < K / 256) nxt.load(row, blk + 1);
+      if (u + 1 < units) nxt.load(row, u + 1);
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const int kb = blk * 4 + j, s = kb % SB;
+      for (int j = 0; j < Row::STEPS; j++) {
+        const int kb = u * Row::STEPS + j, s = kb % SB;
         if (kb >= SB) {  // lane 0 waits for the stage to be free, the warp follows its verdict
           int got = 1;
           if (lane == 0) got = mbar_wait(b_empty + 8 * s, ((kb / SB) - 1) & 1, abort);
@@ -317,14 +367,21 @@ int set_workspace(int device, void *ptr, size_t bytes) {
 
 // returns 1 when the tensor-core prefill kernel took the call, 0 when the shape is not covered
 int gguf_prefill(int type, const float *x, const void *w, float *out, int M, int N, int K, int device, cudaStream_t st) {
-  if (type != LB200_Q4_K || M < 65 || K % 256 || ((uintptr_t)w & 15)) return 0;
+  if (M < 65 || K % 256) return 0;
+  if (type == LB200_Q4_K) {
+    if ((uintptr_t)w & 15) return 0;
+  } else if (type == LB200_Q6_K) {
+    if (((uintptr_t)w & 3) || ((size_t)(K >> 8) * 210) % 4) return 0;  // rows must start 4-byte aligned
+  } else {
+    return 0;
+  }
   Workspace ws;
   {
     std::lock_guard<std::mutex> lk(g_mu);
     ws = g_ws[device];
   }
   if (!ws.ptr || ws.bytes < (size_t)M * K * 2) return 0;
-  int rc = launch<Q4KRow>(x, w, out, M, N, K, ws.ptr, st);
+  int rc = type == LB200_Q4_K ? launch<Q4KRow>(x, w, out, M, N, K, ws.ptr, st) : launch<Q6KRow>(x, w, out, M, N, K, ws.ptr, st);
   return rc ? rc : 1;
 }
 

@@ -50,3 +50,13 @@ def test_prefill_without_workspace_still_correct(cuda, oracle):
     check(lib().light_b200_matmul_q(ops.Q4_K, C.c_void_p(xd.data_ptr()), C.c_void_p(wd.data_ptr()),
                                     C.c_void_p(out.data_ptr()), M, N, K, 0, None))
     assert rel_l2(out.cpu().numpy(), x.numpy().astype(np.float64) @ deq.T) <= 1e-5
+
+
+@pytest.mark.parametrize("M,N,K", [(65, 256, 512), (200, 300, 1024), (256, 512, 2048), (1024, 1024, 14336), (70, 40, 768)])
+def test_q6k_prefill_matches_f64_oracle(cuda, oracle, M, N, K):
+    """Q6_K through the same kernel (K = 768 has rows that are not 4-byte aligned and takes the
+    shape-generic kernel instead)."""
+    for seed, bf16_x in ((321, True), (322, True), (323, False)):
+        err = _case(ops.Q6_K, M, N, K, seed, cuda, oracle, bf16_x)
+        assert err <= (5e-4 if bf16_x else 1e-3), (M, N, K, seed, err)
+    assert ops.prefill_status(0) == 0
