@@ -49,6 +49,8 @@ int gguf_matmul_generic(int type, const float *x, const void *w, float *out, int
 // returns 1 when a fast decode kernel took the call, 0 when the shape is not covered, <0 on error
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
 int gguf_gemv_fast_init(int device);
+// batched decode (2..64 rows): 1 = took the call, 0 = not covered, other = error
+int gguf_gemv_batch(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
 // tensor-core prefill: 1 = took the call, 0 = shape / workspace not covered, other = error
 int gguf_prefill(int type, const float *x, const void *w, float *out, int M, int N, int K, int device, cudaStream_t st);
 int set_workspace(int device, void *ptr, size_t bytes);

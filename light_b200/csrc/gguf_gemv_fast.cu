@@ -28,6 +28,7 @@
 #include <cstdlib>
 
 #include "common.cuh"
+#include "mma_sync.cuh"
 
 namespace lb {
 
@@ -35,32 +36,6 @@ namespace {
 
 constexpr int WARPS = 8;  // warps per CTA, taking K blocks round-robin
 constexpr int ROWS = 16;  // weight rows per tile (one m16 MMA tile)
-
-__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
-// (a & b) | c in one LOP3 (b and c live in registers; the compiler does not fuse two immediates)
-__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t b, uint32_t c) {
-  uint32_t d;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;\n" : "=r"(d) : "r"(a), "r"(b), "r"(c));
-  return d;
-}
-
-__device__ __forceinline__ uint2 lds64(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
-  asm volatile("st.shared.v2.u32 [%0], {%1,%2};\n" ::"r"(addr), "r"(a), "r"(b));
-}
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
-__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 
 // Per-warp activation slab for one 256-element K block, SUB elements per sub-block:
 //   hi[256/SUB sub-blocks][SUB halves + pad]  lo[...same...]  sx[256/SUB floats]
@@ -484,7 +459,7 @@ int gguf_gemv_fast_init(int) {
 }
 
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
-  if (M < 1 || M > 4 || K % 256) return 0;
+  if (M != 1 || K % 256) return 0;
   if (type != LB200_Q4_K && type != LB200_Q6_K) return 0;
   if (type == LB200_Q4_K && ((uintptr_t)w & 15)) return 0;
   // Q6_K rows must start 4-byte aligned for the aligned-word loads: (K/256)*210 % 4 == 0
