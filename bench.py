@@ -137,8 +137,13 @@ class Chain:
                                                   C.c_void_p(self.local[i].data_ptr()), self.M, nl, K, self.dev_index,
                                                   C.c_void_p(stream)))
 
+    # Outputs the next operator needs in full on every rank (the rest stay row-local): the attention
+    # output (q stands in for it here: k, v and the heads they feed are rank-local), o, the MLP
+    # activation (gate stands in for silu(gate) * up), down, and the logits.
+    GATHERED = ("q", "o", "gate", "down", "lm_head")
+
     def step(self, only=None):
-        import torch.distributed as dist
+        from light_b200 import tp
 
         st = torch.cuda.current_stream(self.device).cuda_stream
         n = 0
@@ -147,13 +152,8 @@ class Chain:
                 continue
             self.launch(i, st)
             n += 1
-            if self.world > 1:
-                if self.M == 1:
-                    dist.all_gather_into_tensor(self.out[i].view(-1), self.local[i].view(-1))
-                else:  # rank slices are column blocks of (M, N): gather then interleave
-                    tmp = torch.empty(self.world, self.M, e[1], device=self.device)
-                    dist.all_gather_into_tensor(tmp, self.local[i])
-                    self.out[i].view(self.M, self.world, e[1]).copy_(tmp.permute(1, 0, 2))
+            if self.world > 1 and only is None and e[0].split(".")[-1] in self.GATHERED:
+                tp.all_gather_columns(self.local[i], self.out[i])
         return n
 
     def bytes_per_step(self, only=None):
@@ -330,7 +330,7 @@ def main():
         "dtype": "f32 activations x Q4_K/Q6_K weights, f32 accumulate", "data": "synthetic",
         "config": {"workload": workload, "tokens_per_step": M, "layers": args.layers,
                    "weights_bytes_per_step": sum(weight_bytes(e[2], e[3], e[4]) for e in chain.lin),
-                   "parallelism": f"rows of every weight split over {world} GPU(s)" + (", NCCL all-gather per linear" if world > 1 else ""),
+                   "parallelism": f"rows of every weight split over {world} GPU(s)" + (", NCCL all-gather of the attention output, o, the MLP activation, down and the logits (129 per step)" if world > 1 else ""),
                    "l2": "inputs (4.84 GB of weights per step) exceed the 126 MB L2", "launch": "CUDA graph replay"},
         "roofline": roofline,
         "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -342,10 +342,15 @@ def main():
             threads = os.cpu_count() or 1
             v, t_step, sample = cpu_reference(M, threads, 3, 1)
             line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample}
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
     if world > 1:
+        # Graphs that captured NCCL kernels must be gone before the communicator is torn down; and a
+        # communicator that will not finish tearing down must not keep the job alive.
+        del graph
+        torch.cuda.synchronize(device)
         dist.barrier()
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        os._exit(0)
     return 0
 
 

@@ -1,0 +1,73 @@
+"""Row-split (tensor-parallel) placement of quantized weights over the GPUs of one node.
+
+The reference is single-GPU (STATUS.md:474), so the contract here is "same numbers as one GPU".
+Every weight layout on this path is row-major with whole blocks per row (GGUF: K/256 blocks of 144
+or 210 bytes; int4: codes / scales / zeros all (N, .); fp8-block: split on multiples of the block
+height), so giving rank r the rows [r*N/P, (r+1)*N/P) is a plain slice with no repacking -- the same
+property the reference's loader uses when it permutes and concatenates rows at byte level
+(models/llama_gguf.go:344-382).  Each rank computes its (M, N/P) slice of the output; where the
+next operator needs the whole row, the slices are all-gathered.
+
+Only host-side logic lives here (it is exercised on CPU with the gloo backend); the matmuls themselves
+are the single-GPU kernels.
+"""
+from __future__ import annotations
+
+import torch
+
+
+def row_range(N: int, rank: int, world: int) -> tuple[int, int]:
+    """Rows of an (N, K) weight owned by `rank`; N must divide evenly so that every rank runs the
+    same launch shape."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError(f"row_range: rank {rank} outside world of {world}")
+    if N % world:
+        raise ValueError(f"row_range: {N} rows do not split evenly over {world} ranks")
+    per = N // world
+    return rank * per, (rank + 1) * per
+
+
+def shard_rows(w: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """The rank's rows of a weight held as a 2-D tensor whose first dimension is N (block bytes, codes,
+    scales or zeros alike).  A view, not a copy."""
+    lo, hi = row_range(w.shape[0], rank, world)
+    return w[lo:hi]
+
+
+def shard_fp8_block(w: torch.Tensor, scale: torch.Tensor, block_r: int, rank: int, world: int):
+    """Block-scaled FP8: rows split on multiples of the block height so that scale rows split with them."""
+    lo, hi = row_range(w.shape[0], rank, world)
+    if lo % block_r or hi % block_r:
+        raise ValueError(f"shard_fp8_block: {w.shape[0]} rows over {world} ranks does not fall on {block_r}-row blocks")
+    return w[lo:hi], scale[lo // block_r:hi // block_r]
+
+
+def all_gather_columns(local: torch.Tensor, out: torch.Tensor | None = None, group=None) -> torch.Tensor:
+    """(M, N/P) slices -> (M, N): rank r's slice becomes columns [r*N/P, (r+1)*N/P).  One collective."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    M, n = local.shape
+    if out is None:
+        out = torch.empty(M, n * world, dtype=local.dtype, device=local.device)
+    if M == 1:
+        dist.all_gather_into_tensor(out.view(-1), local.contiguous().view(-1), group=group)
+        return out
+    tmp = torch.empty(world, M, n, dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(tmp.view(-1), local.contiguous().view(-1), group=group)
+    out.view(M, world, n).copy_(tmp.permute(1, 0, 2))
+    return out
+
+
+def expert_range(E: int, rank: int, world: int) -> tuple[int, int]:
+    """Experts owned by `rank` under expert parallelism (contiguous blocks of E / P)."""
+    return row_range(E, rank, world)
+
+
+def split_pairs_by_rank(sorted_expts: torch.Tensor, E: int, world: int) -> torch.Tensor:
+    """Number of routed pairs each rank receives: because pairs are already sorted by expert
+    (ops.MoERoute), rank r's pairs are one contiguous run of the sorted list.  Returns (world + 1)
+    offsets into it."""
+    per = E // world
+    bounds = torch.arange(0, world + 1, device=sorted_expts.device, dtype=sorted_expts.dtype) * per
+    return torch.searchsorted(sorted_expts.contiguous(), bounds)
