@@ -53,6 +53,10 @@ int gguf_gemv_fast_init(int device);
 int gguf_gemv_batch(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
 // tensor-core prefill: 1 = took the call, 0 = shape / workspace not covered, other = error
 int gguf_prefill(int type, const float *x, const void *w, float *out, int M, int N, int K, int device, cudaStream_t st);
+int int4_prefill(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N,
+                 int K, int G, int device, cudaStream_t st);
+int fp8_prefill(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR,
+                int bC, int device, cudaStream_t st);
 int set_workspace(int device, void *ptr, size_t bytes);
 int prefill_status(int device);
 

@@ -15,6 +15,7 @@
 // f16 (not bf16) operands: the reference multiplies f32 weights by f32 activations; rounding the
 // weights to bf16 alone costs 1.7e-3 relative L2, to f16 2e-4.
 #include <cuda.h>
+#include <cuda_fp8.h>
 
 #include <mutex>
 
@@ -45,28 +46,48 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t *>(&h);
 }
-// four code bytes (each 0..63) -> four f16 weights w = code * s - m, as two packed registers
+// two f32 -> one register of two f16 (BF16 = false) or two bf16 (BF16 = true), round to nearest even
+template <bool BF16>
+__device__ __forceinline__ uint32_t pack2(float a, float b) {
+  if (BF16) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t *>(&h);
+  }
+  return pack_h2(a, b);
+}
+// byte i of `bytes` as f32 (0 .. 255), exact, without the conversion pipe
+__device__ __forceinline__ float byte_f32(uint32_t bytes, int i) {
+  return __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7650 + i)) - 8388608.f;
+}
+// four code bytes -> four weights code * s - m (one f32 FMA, one rounding), as two packed registers
+template <bool BF16>
 __device__ __forceinline__ void expand4(uint32_t bytes, float s, float m, uint32_t &o0, uint32_t &o1) {
-  const float f0 = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7650)) - 8388608.f;
-  const float f1 = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7651)) - 8388608.f;
-  const float f2 = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7652)) - 8388608.f;
-  const float f3 = __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7653)) - 8388608.f;
-  o0 = pack_h2(fmaf(f0, s, -m), fmaf(f1, s, -m));
-  o1 = pack_h2(fmaf(f2, s, -m), fmaf(f3, s, -m));
+  o0 = pack2<BF16>(fmaf(byte_f32(bytes, 0), s, -m), fmaf(byte_f32(bytes, 1), s, -m));
+  o1 = pack2<BF16>(fmaf(byte_f32(bytes, 2), s, -m), fmaf(byte_f32(bytes, 3), s, -m));
+}
+__device__ __forceinline__ void st_chunk(uint32_t addr, const uint4 &v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w));
 }
 
 // ---- per-format row expanders: one thread, one weight row, one 256-element block at a time.
 // load(): fetch the block into registers.  step(j, ...): write the 64 weights k = 64j .. 64j+63 of
 // the block as 8 swizzled 16-byte chunks of row `r` of the B tile at shared address `tile`.
+struct GgufCtx {
+  const uint8_t *w;
+};
 struct Q4KRow {
-  static constexpr int BLOCK_BYTES = 144, STEPS = 4;  // one load() = one 256-element block = 4 steps
+  using Ctx = GgufCtx;
+  static constexpr int STEPS = 4;  // one load() = one 256-element block = 4 steps of 64
+  const uint8_t *row;
   uint4 h, q[8];
-  __device__ __forceinline__ void load(const uint8_t *row, int kb) {
+  __device__ __forceinline__ void init(const Ctx &c, int n, int K) { row = c.w + (size_t)n * (size_t)(K / 256) * 144; }
+  __device__ __forceinline__ void load(int kb) {
     const uint4 *p = reinterpret_cast<const uint4 *>(row) + (size_t)kb * 9;
     h = __ldg(p);
 #pragma unroll
     for (int i = 0; i < 8; i++) q[i] = __ldg(p + 1 + i);
   }
+  template <bool BF16>
   __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
     // sub-blocks 2j (low nibbles of qs[32j .. 32j+31]) and 2j+1 (high nibbles)
     const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
@@ -86,12 +107,12 @@ struct Q4KRow {
 #pragma unroll
     for (int c = 0; c < 4; c++) {  // chunk c: k = 8c..8c+7 (low nibbles); chunk c+4: k = 32+8c.. (high nibbles)
       uint4 lo, hi;
-      expand4(w[2 * c] & 0x0F0F0F0Fu, s0, m0, lo.x, lo.y);
-      expand4(w[2 * c + 1] & 0x0F0F0F0Fu, s0, m0, lo.z, lo.w);
-      expand4((w[2 * c] >> 4) & 0x0F0F0F0Fu, s1, m1, hi.x, hi.y);
-      expand4((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, s1, m1, hi.z, hi.w);
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(tile + swz(r, c)), "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w));
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(tile + swz(r, c + 4)), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w));
+      expand4<BF16>(w[2 * c] & 0x0F0F0F0Fu, s0, m0, lo.x, lo.y);
+      expand4<BF16>(w[2 * c + 1] & 0x0F0F0F0Fu, s0, m0, lo.z, lo.w);
+      expand4<BF16>((w[2 * c] >> 4) & 0x0F0F0F0Fu, s1, m1, hi.x, hi.y);
+      expand4<BF16>((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, s1, m1, hi.z, hi.w);
+      st_chunk(tile + swz(r, c), lo);
+      st_chunk(tile + swz(r, c + 4), hi);
     }
   }
 };
@@ -102,16 +123,19 @@ struct Q4KRow {
 // weight = d * sc[8h + 4j + k/16] * (code - 32).  Blocks are only 2-byte aligned: each word is two
 // aligned 32-bit loads funnel-shifted by 0 or 16 bits (rows start 4-byte aligned, checked on the host).
 struct Q6KRow {
-  static constexpr int BLOCK_BYTES = 210, STEPS = 2;
+  using Ctx = GgufCtx;
+  static constexpr int STEPS = 2;
+  const uint8_t *row;
   uint32_t ql[16], qh[8], sc[2];
   float d;
+  __device__ __forceinline__ void init(const Ctx &c, int n, int K) { row = c.w + (size_t)n * (size_t)(K / 256) * 210; }
   __device__ __forceinline__ static uint32_t ld(const uint32_t *a, uint32_t sh) {
     const uint32_t lo = __ldg(a);
     uint32_t hi = 0;
     if (sh) hi = __ldg(a + 1);
     return __funnelshift_r(lo, hi, sh);
   }
-  __device__ __forceinline__ void load(const uint8_t *row, int unit) {
+  __device__ __forceinline__ void load(int unit) {
     const int b = unit >> 1, h = unit & 1;
     const uint32_t sh = (b & 1) * 16u;
     const uint8_t *blk = row + (size_t)b * 210;
@@ -123,6 +147,7 @@ struct Q6KRow {
     sc[0] = ld(a + 48 + 2 * h, sh), sc[1] = ld(a + 49 + 2 * h, sh);
     d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(blk + 208)));
   }
+  template <bool BF16>
   __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
 #pragma unroll
     for (int c = 0; c < 8; c++) {  // chunk c: k = 8c .. 8c+7 -> group q = 2j + c/4, l = 8 (c%4) ..
@@ -136,11 +161,99 @@ struct Q6KRow {
         const uint32_t hi2 = q == 0 ? (wh << 4) : q == 1 ? (wh << 2) : q == 2 ? wh : (wh >> 2);
         const uint32_t v = (wq & 0x0F0F0F0Fu) | (hi2 & 0x30303030u);
         if (e == 0)
-          expand4(v, ds, m, o.x, o.y);
+          expand4<BF16>(v, ds, m, o.x, o.y);
         else
-          expand4(v, ds, m, o.z, o.w);
+          expand4<BF16>(v, ds, m, o.z, o.w);
       }
-      asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};\n" ::"r"(tile + swz(r, c)), "r"(o.x), "r"(o.y), "r"(o.z), "r"(o.w));
+      st_chunk(tile + swz(r, c), o);
+    }
+  }
+};
+
+// Group-quantized int4 in the reference's canonical layout (quant/int4.go:12-31): codes u32 (N, K/8),
+// nibble i of word c = element 8c + i; scales / zeros f32 (N, K/G).  W = fl(s * fl(code - z)): the two
+// f32 roundings of the reference's dequantize kernel (kernels/cuda/src/int4.cu:16-41), then one
+// rounding to the operand type, so a bf16 operand equals the reference's bf16 weight bit for bit.
+// One load() = 256 elements (32 code words); requires G % 64 == 0.
+struct Int4Ctx {
+  const uint32_t *codes;
+  const float *s, *z;
+  int G;
+};
+struct Int4Row {
+  using Ctx = Int4Ctx;
+  static constexpr int STEPS = 4;
+  const uint4 *row;
+  const float *sr, *zr;
+  int G, unit;
+  uint4 q[8];
+  __device__ __forceinline__ void init(const Ctx &c, int n, int K) {
+    row = reinterpret_cast<const uint4 *>(c.codes + (size_t)n * (K / 8));
+    sr = c.s + (size_t)n * (K / c.G), zr = c.z + (size_t)n * (K / c.G), G = c.G;
+  }
+  __device__ __forceinline__ void load(int u) {
+    unit = u;
+#pragma unroll
+    for (int i = 0; i < 8; i++) q[i] = __ldg(row + (size_t)u * 8 + i);
+  }
+  template <bool BF16>
+  __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
+    const int grp = (unit * 256 + j * 64) / G;
+    const float sc = __ldg(sr + grp), z = __ldg(zr + grp);
+    const uint32_t w[8] = {q[2 * j].x, q[2 * j].y, q[2 * j].z, q[2 * j].w, q[2 * j + 1].x, q[2 * j + 1].y, q[2 * j + 1].z, q[2 * j + 1].w};
+#pragma unroll
+    for (int c = 0; c < 8; c++) {  // chunk c = code word c: nibbles 0..7 in element order
+      const uint32_t lo = w[c] & 0x0F0F0F0Fu, hi = (w[c] >> 4) & 0x0F0F0F0Fu;  // even / odd nibbles
+      uint4 o;
+      o.x = pack2<BF16>(__fmul_rn(sc, __fsub_rn(byte_f32(lo, 0), z)), __fmul_rn(sc, __fsub_rn(byte_f32(hi, 0), z)));
+      o.y = pack2<BF16>(__fmul_rn(sc, __fsub_rn(byte_f32(lo, 1), z)), __fmul_rn(sc, __fsub_rn(byte_f32(hi, 1), z)));
+      o.z = pack2<BF16>(__fmul_rn(sc, __fsub_rn(byte_f32(lo, 2), z)), __fmul_rn(sc, __fsub_rn(byte_f32(hi, 2), z)));
+      o.w = pack2<BF16>(__fmul_rn(sc, __fsub_rn(byte_f32(lo, 3), z)), __fmul_rn(sc, __fsub_rn(byte_f32(hi, 3), z)));
+      st_chunk(tile + swz(r, c), o);
+    }
+  }
+};
+
+// Block-scaled FP8: e4m3fn codes (N, K), one f32 scale per (bR x bC) block; W = fl(f32(code) * scale)
+// (kernels/cuda/src/fp8_block.cu:34-62), then one rounding to the operand type.  One load() = 128
+// elements; requires bC % 64 == 0.
+struct Fp8Ctx {
+  const uint8_t *w;
+  const float *scale;
+  int bR, bC;
+};
+struct Fp8Row {
+  using Ctx = Fp8Ctx;
+  static constexpr int STEPS = 2;
+  const uint4 *row;
+  const float *sr;
+  int bC, unit;
+  uint4 q[8];
+  __device__ __forceinline__ void init(const Ctx &c, int n, int K) {
+    row = reinterpret_cast<const uint4 *>(c.w + (size_t)n * K);
+    sr = c.scale + (size_t)(n / c.bR) * (K / c.bC), bC = c.bC;
+  }
+  __device__ __forceinline__ void load(int u) {
+    unit = u;
+#pragma unroll
+    for (int i = 0; i < 8; i++) q[i] = __ldg(row + (size_t)u * 8 + i);
+  }
+  template <bool BF16>
+  __device__ __forceinline__ static uint2 four(uint32_t v, float sc) {
+    __half2_raw a = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xFFFFu), __NV_E4M3);
+    __half2_raw b = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v >> 16), __NV_E4M3);
+    const float2 fa = __half22float2(__half2(a)), fb = __half22float2(__half2(b));
+    return make_uint2(pack2<BF16>(__fmul_rn(fa.x, sc), __fmul_rn(fa.y, sc)), pack2<BF16>(__fmul_rn(fb.x, sc), __fmul_rn(fb.y, sc)));
+  }
+  template <bool BF16>
+  __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
+    const float sc = __ldg(sr + (unit * 128 + j * 64) / bC);
+#pragma unroll
+    for (int c = 0; c < 4; c++) {  // 16 bytes = two chunks of 8 codes
+      const uint4 v = q[4 * j + c];
+      const uint2 a = four<BF16>(v.x, sc), b = four<BF16>(v.y, sc), e = four<BF16>(v.z, sc), f = four<BF16>(v.w, sc);
+      st_chunk(tile + swz(r, 2 * c), make_uint4(a.x, a.y, b.x, b.y));
+      st_chunk(tile + swz(r, 2 * c + 1), make_uint4(e.x, e.y, f.x, f.y));
     }
   }
 };
@@ -149,10 +262,10 @@ struct Q6KRow {
 //   warps 0-7  expand weights (thread r <-> weight row n0 + r), then run the epilogue
 //   warp  8    TMA producer of the x tiles (one lane)
 //   warp  9    owns tensor memory and issues the MMAs (one lane)
-template <typename Row>
-__global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                                                                      const uint8_t *__restrict__ w,
-                                                                      float *__restrict__ out, int M, int N, int K) {
+template <typename Row, bool BF16, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
+                                                                 const typename Row::Ctx ctx, OutT *__restrict__ out,
+                                                                 int M, int N, int K) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = base, sB = base + SA * A_STAGE, sBar = sB + SB * B_STAGE;
@@ -164,6 +277,7 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
   const int nkb = K / BK;
+  const bool two = m0 + 128 < M;  // the second 128-token tile holds real tokens
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -195,9 +309,9 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
       for (int kb = 0; kb < nkb; kb++) {
         const int s = kb % SA;
         if (kb >= SA && !mbar_wait(a_empty + 8 * s, ((kb / SA) - 1) & 1, abort)) break;
-        mbar_arrive_expect_tx(a_full + 8 * s, A_STAGE);
+        mbar_arrive_expect_tx(a_full + 8 * s, two ? A_STAGE : A_STAGE / 2);
         tma_load_2d(sA + s * A_STAGE, &tmap_x, a_full + 8 * s, kb * BK, m0);
-        tma_load_2d(sA + s * A_STAGE + A_STAGE / 2, &tmap_x, a_full + 8 * s, kb * BK, m0 + 128);
+        if (two) tma_load_2d(sA + s * A_STAGE + A_STAGE / 2, &tmap_x, a_full + 8 * s, kb * BK, m0 + 128);
         issued = kb + 1;
       }
       if (*abort)  // give the loads still in flight a bounded time to land before the CTA retires
@@ -207,7 +321,7 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
     }
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_f16(128, BN, false);
+      constexpr uint32_t idesc = idesc_f16(128, BN, BF16);
       for (int kb = 0; kb < nkb; kb++) {
         const int sa = kb % SA, sb = kb % SB;
         if (!mbar_wait(a_full + 8 * sa, (kb / SA) & 1, abort)) break;
@@ -220,7 +334,7 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
           const uint64_t a1 = smem_desc_sw128(sA + sa * A_STAGE + A_STAGE / 2 + k4 * 32);
           const uint32_t acc = (kb | k4) ? 1u : 0u;
           mma_f16(tmem_base, a0, bd, idesc, acc);
-          mma_f16(tmem_base + 256, a1, bd, idesc, acc);
+          if (two) mma_f16(tmem_base + 256, a1, bd, idesc, acc);
         }
         mma_commit(a_empty + 8 * sa);
         mma_commit(b_empty + 8 * sb);
@@ -231,14 +345,14 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
     // ---- weight expansion: thread r owns row n0 + r (clamped; rows past N are never stored)
     const int r = threadIdx.x;
     const int n = min(n0 + r, N - 1);
-    const uint8_t *row = w + (size_t)n * (size_t)(K / 256) * Row::BLOCK_BYTES;
     Row cur;
-    cur.load(row, 0);
+    cur.init(ctx, n, K);
+    cur.load(0);
     bool ok = true;
     const int units = K / (BK * Row::STEPS);
     for (int u = 0; u < units && ok; u++) {
-      Row nxt;
-      if (u + 1 < units) nxt.load(row, u + 1);
+      Row nxt = cur;
+      if (u + 1 < units) nxt.load(u + 1);
 #pragma unroll
       for (int j = 0; j < Row::STEPS; j++) {
         const int kb = u * Row::STEPS + j, s = kb % SB;
@@ -250,7 +364,7 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
             break;
           }
         }
-        cur.step(j, sB + s * B_STAGE, r);
+        cur.template step<BF16>(j, sB + s * B_STAGE, r);
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) mbar_arrive(b_full + 8 * s);
@@ -264,7 +378,7 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
       tc_fence_after();
       const int quad = warp & 3, chalf = warp >> 2;
 #pragma unroll 1
-      for (int a = 0; a < 2; a++) {
+      for (int a = 0; a < (two ? 2 : 1); a++) {
         const int m = m0 + a * 128 + quad * 32 + lane;
 #pragma unroll 1
         for (int c = 0; c < 4; c++) {
@@ -273,16 +387,26 @@ __global__ void __launch_bounds__(THREADS, 1) gguf_prefill_umma_kernel(const __g
           tmem_ld_wait();
           const int nc = n0 + chalf * 128 + c * 32;
           if (m < M) {
-            float *o = out + (size_t)m * N + nc;
-            if (nc + 32 <= N && (N & 3) == 0) {
+            OutT *o = out + (size_t)m * N + nc;
+            if (nc + 32 <= N && (N & 7) == 0) {
+              if constexpr (sizeof(OutT) == 4) {
 #pragma unroll
-              for (int i = 0; i < 8; i++)
-                reinterpret_cast<float4 *>(o)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                               __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+                for (int i = 0; i < 8; i++)
+                  reinterpret_cast<float4 *>(o)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
+                                                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+              } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+                  reinterpret_cast<uint4 *>(o)[i] = make_uint4(
+                      pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                      pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                      pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                      pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
+              }
             } else {
 #pragma unroll
               for (int i = 0; i < 32; i++)
-                if (nc + i < N) o[i] = __uint_as_float(v[i]);
+                if (nc + i < N) st_act(o, i, __uint_as_float(v[i]));
             }
           }
         }
@@ -327,32 +451,62 @@ int ensure_encode() {
   return 0;
 }
 
-template <typename Row>
-int launch(const float *x, const void *w, float *out, int M, int N, int K, void *ws, cudaStream_t st) {
+// x f32 -> f16 in the workspace, or bf16 x used as it is; then the tensor map over it.
+int make_x_map(CUtensorMap *tm, const void *x, int act_dtype, int M, int K, void *ws, cudaStream_t st) {
   if (int rc = ensure_encode()) return rc;
-  const long long n4 = (long long)M * K / 4;
-  long long blocks = (n4 + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
-  x_to_f16_kernel<<<(unsigned)blocks, 256, 0, st>>>((const float4 *)x, (uint2 *)ws, n4);
-  if (int rc = launched("matmul_q (prefill, x to f16)")) return rc;
-  CUtensorMap tm;
+  const void *src = x;
+  CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (act_dtype == LB200_F32) {
+    const long long n4 = (long long)M * K / 4;
+    long long blocks = (n4 + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    x_to_f16_kernel<<<(unsigned)blocks, 256, 0, st>>>((const float4 *)x, (uint2 *)ws, n4);
+    if (int rc = launched("prefill: activations to f16")) return rc;
+    src = ws;
+    dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  }
   const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)M};
   const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
   const cuuint32_t box[2] = {BK, 128};
   const cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ws, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  CUresult r = g_encode(tm, dt, 2, const_cast<void *>(src), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(LB200_E_SHAPE, "light_b200: matmul_q (prefill): cuTensorMapEncodeTiled failed (%d)", (int)r);
-  auto kern = gguf_prefill_umma_kernel<Row>;
+  if (r != CUDA_SUCCESS) return fail(LB200_E_SHAPE, "light_b200: prefill: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return 0;
+}
+
+template <typename Row, bool BF16, typename OutT>
+int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, OutT *out, int M, int N, int K, cudaStream_t st) {
+  auto kern = prefill_umma_kernel<Row, BF16, OutT>;
   static bool attr_done = false;
   if (!attr_done) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (prefill): %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
     attr_done = true;
   }
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, (const uint8_t *)w, out, M, N, K);
-  return launched("matmul_q (prefill)");
+  kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, out, M, N, K);
+  return launched("prefill (tcgen05)");
+}
+
+// f32 activations run with f16 operands and f32 output, bf16 activations with bf16 operands and output
+template <typename Row>
+int launch_by_act(const void *x, int act_dtype, const typename Row::Ctx &ctx, void *out, int M, int N, int K, void *ws,
+                  cudaStream_t st) {
+  CUtensorMap tm;
+  if (int rc = make_x_map(&tm, x, act_dtype, M, K, ws, st)) return rc;
+  if (act_dtype == LB200_F32) return launch<Row, false, float>(tm, ctx, (float *)out, M, N, K, st);
+  return launch<Row, true, __nv_bfloat16>(tm, ctx, (__nv_bfloat16 *)out, M, N, K, st);
+}
+
+// workspace for an f32 activation matrix; bf16 needs none.  Returns false if there is not enough.
+bool get_ws(int device, int act_dtype, int M, int K, void **ws) {
+  *ws = nullptr;
+  if (act_dtype != LB200_F32) return true;
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_ws[device].ptr || g_ws[device].bytes < (size_t)M * K * 2) return false;
+  *ws = g_ws[device].ptr;
+  return true;
 }
 
 }  // namespace
@@ -365,9 +519,12 @@ int set_workspace(int device, void *ptr, size_t bytes) {
   return 0;
 }
 
-// returns 1 when the tensor-core prefill kernel took the call, 0 when the shape is not covered
+constexpr int PREFILL_MIN_M = 65;
+
+// Each returns 1 when the tensor-core prefill kernel took the call, 0 when the shape (or the workspace)
+// does not allow it, any other value is an error.
 int gguf_prefill(int type, const float *x, const void *w, float *out, int M, int N, int K, int device, cudaStream_t st) {
-  if (M < 65 || K % 256) return 0;
+  if (M < PREFILL_MIN_M || K % 256) return 0;
   if (type == LB200_Q4_K) {
     if ((uintptr_t)w & 15) return 0;
   } else if (type == LB200_Q6_K) {
@@ -375,13 +532,31 @@ int gguf_prefill(int type, const float *x, const void *w, float *out, int M, int
   } else {
     return 0;
   }
-  Workspace ws;
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    ws = g_ws[device];
-  }
-  if (!ws.ptr || ws.bytes < (size_t)M * K * 2) return 0;
-  int rc = type == LB200_Q4_K ? launch<Q4KRow>(x, w, out, M, N, K, ws.ptr, st) : launch<Q6KRow>(x, w, out, M, N, K, ws.ptr, st);
+  void *ws;
+  if (!get_ws(device, LB200_F32, M, K, &ws)) return 0;
+  GgufCtx ctx{(const uint8_t *)w};
+  int rc = type == LB200_Q4_K ? launch_by_act<Q4KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st)
+                              : launch_by_act<Q6KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st);
+  return rc ? rc : 1;
+}
+
+int int4_prefill(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N,
+                 int K, int G, int device, cudaStream_t st) {
+  if (M < PREFILL_MIN_M || K % 256 || G % 64 || ((uintptr_t)codes & 15) || ((uintptr_t)x & 15)) return 0;
+  void *ws;
+  if (!get_ws(device, act_dtype, M, K, &ws)) return 0;
+  Int4Ctx ctx{codes, s, z, G};
+  int rc = launch_by_act<Int4Row>(x, act_dtype, ctx, y, M, N, K, ws, st);
+  return rc ? rc : 1;
+}
+
+int fp8_prefill(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR,
+                int bC, int device, cudaStream_t st) {
+  if (M < PREFILL_MIN_M || K % 128 || bC % 64 || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
+  void *ws;
+  if (!get_ws(device, act_dtype, M, K, &ws)) return 0;
+  Fp8Ctx ctx{w, scale, bR, bC};
+  int rc = launch_by_act<Fp8Row>(x, act_dtype, ctx, y, M, N, K, ws, st);
   return rc ? rc : 1;
 }
 

@@ -186,6 +186,8 @@ def MatMulInt4(x: torch.Tensor, w: Int4) -> torch.Tensor:
     if w.perm is not None:  # act-order GPTQ: gather x's columns into the weight's K order
         xc = xc.index_select(1, w.perm).contiguous()
     M, N = x.shape[0], w.N()
+    if M > 64 and x.dtype == torch.float32:  # tensor-core path: f16 copy of x in the workspace
+        ensure_workspace(dev, M * w.K() * 2)
     out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
     _lib.check(_lib.lib().light_b200_int4_gemv(_ptr(xc), _ptr(w.codes.contiguous()), _ptr(w.scales.contiguous()),
                                                _ptr(w.zeros.contiguous()), _ptr(out), _ACT[x.dtype], M, N, w.K(),
@@ -223,6 +225,8 @@ def MatMulF8Block(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, block_r
     M, K = x.shape
     N = w.shape[0]
     dev = _dev(x, "MatMulF8Block")
+    if M > 64 and x.dtype == torch.float32:
+        ensure_workspace(dev, M * K * 2)
     out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
     _lib.check(_lib.lib().light_b200_fp8_block_gemv(_ptr(x.contiguous()), _ptr(w.contiguous()),
                                                     _ptr(scale.contiguous()), _ptr(out), _ACT[x.dtype], M, N, K,

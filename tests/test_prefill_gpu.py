@@ -60,3 +60,45 @@ def test_q6k_prefill_matches_f64_oracle(cuda, oracle, M, N, K):
         err = _case(ops.Q6_K, M, N, K, seed, cuda, oracle, bf16_x)
         assert err <= (5e-4 if bf16_x else 1e-3), (M, N, K, seed, err)
     assert ops.prefill_status(0) == 0
+
+
+def _bf16_round(a: np.ndarray) -> np.ndarray:
+    return torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
+
+
+@pytest.mark.parametrize("M,N,K,G", [(65, 256, 256, 128), (256, 512, 1024, 128), (300, 200, 512, 64), (1024, 4608, 3584, 128)])
+def test_int4_prefill(cuda, oracle, M, N, K, G):
+    """GPTQ/AWQ int4 on the tensor cores (config 4 shapes at the end).  bf16 activations: operands are
+    the reference's bf16 weight (bit-identical dequantization) and x itself, so only accumulation order
+    and the bf16 rounding of the output differ (reference tolerance 3e-2, ops/int4_test.go:80-145);
+    f32 activations: f16 operands, 1e-3 relative L2 against the f64 oracle."""
+    codes, s, z = synth.random_int4(331, N, K, G)
+    w = ops.Int4(torch.from_numpy(codes.view(np.int32)).to(cuda), torch.from_numpy(s).to(cuda),
+                 torch.from_numpy(z).to(cuda), G)
+    deq = oracle.int4_dequant(codes, s, z, G).astype(np.float64)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(332))
+    got = ops.MatMulInt4(x.to(cuda), w).cpu().numpy()
+    assert rel_l2(got, x.numpy().astype(np.float64) @ deq.T) <= 1e-3
+    xb = x.to(torch.bfloat16)
+    got16 = ops.MatMulInt4(xb.to(cuda), w)
+    assert got16.dtype == torch.bfloat16
+    want16 = xb.float().numpy().astype(np.float64) @ _bf16_round(deq).T
+    assert rel_l2(got16.float().cpu().numpy(), want16) <= 4e-3  # one bf16 rounding of the output
+    assert ops.prefill_status(0) == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(65, 256, 256), (200, 384, 512), (512, 4096, 7168)])
+def test_fp8_block_prefill(cuda, oracle, M, N, K):
+    """Block-scaled FP8 (128 x 128 blocks; the last shape is a DeepSeek-V3 expert's gate_up) on the
+    tensor cores, bf16 and f32 activations."""
+    b = 128
+    codes, scale = synth.random_fp8_block(341, N, K, b, b)
+    deq = oracle.fp8_block_dequant(codes.numpy(), scale.numpy(), b, b).astype(np.float64)
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(342))
+    got = ops.MatMulF8Block(x.to(cuda), codes.to(cuda), scale.to(cuda), b, b).cpu().numpy()
+    assert rel_l2(got, x.numpy().astype(np.float64) @ deq.T) <= 1e-3
+    xb = x.to(torch.bfloat16)
+    got16 = ops.MatMulF8Block(xb.to(cuda), codes.to(cuda), scale.to(cuda), b, b)
+    want16 = xb.float().numpy().astype(np.float64) @ _bf16_round(deq).T
+    assert got16.dtype == torch.bfloat16 and rel_l2(got16.float().cpu().numpy(), want16) <= 4e-3
+    assert ops.prefill_status(0) == 0
