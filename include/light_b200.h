@@ -161,6 +161,15 @@ typedef struct lb200_moe_args {
 /* Registry key {moe_gemm, CUDA, F32|BF16|F16} (reference kernels/cuda/moe.go:21-97). */
 LB200_API int light_b200_moe_gemm(const lb200_moe_args *args, int device, void *stream);
 
+/* Grouped matmul over block-scaled FP8 experts: weights = e4m3fn codes (E, N, K), w_scale f32
+ * (E, N / block_r, K / block_c); args->dtype = activation and output type (LB200_F32 or LB200_BF16);
+ * everything else as light_b200_moe_gemm.  The reference has no grouped kernel for FP8 experts: its
+ * models loop over experts on the host, one ops.MatMulF8Block per expert plus gather / scatter
+ * (models/moe_routed.go:34-79); this entry point is that loop as one launch.  Needs a workspace of
+ * M * K * 2 bytes (light_b200_set_workspace), M >= 256, K % 128 == 0, block_c % 64 == 0. */
+LB200_API int light_b200_moe_gemm_f8block(const lb200_moe_args *args, const float *w_scale, int block_r, int block_c,
+                                          int device, void *stream);
+
 /* Largest expert count light_b200_moe_gemm_static_scratch accepts. */
 #define LB200_MOE_STATIC_MAX_EXPERTS 1024
 

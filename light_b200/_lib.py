@@ -54,6 +54,7 @@ SYMBOLS = {
                                             C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_moe_gemm": (C.c_int, [C.POINTER(MoeArgs), C.c_int, C.c_void_p]),
     "light_b200_moe_gemm_q": (C.c_int, [C.POINTER(MoeArgs), C.c_int, C.c_void_p]),
+    "light_b200_moe_gemm_f8block": (C.c_int, [C.POINTER(MoeArgs), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_moe_gemm_static_scratch": (C.c_int, [C.POINTER(MoeArgs), C.c_int, C.c_void_p]),
 }
 

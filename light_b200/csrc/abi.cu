@@ -217,7 +217,7 @@ static int moe_check(const lb200_moe_args *a, const char *op, bool quant, bool n
 int light_b200_moe_gemm(const lb200_moe_args *a, int device, void *stream) {
   if (int rc = moe_check(a, "moe_gemm", false)) return rc;
   if (int rc = bind(device)) return rc;
-  return moe_gemm(a, (cudaStream_t)stream);
+  return moe_gemm(a, device, (cudaStream_t)stream);
 }
 
 int light_b200_moe_gemm_static_scratch(const lb200_moe_args *a, int device, void *stream) {
@@ -226,10 +226,25 @@ int light_b200_moe_gemm_static_scratch(const lb200_moe_args *a, int device, void
   return moe_gemm_static_scratch(a, device, (cudaStream_t)stream);
 }
 
+int light_b200_moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int block_r, int block_c, int device,
+                                 void *stream) {
+  if (!a) return fail(LB200_E_NULL, "light_b200: moe_gemm_f8block: null argument block");
+  if (a->M < 0 || a->size_m < 0 || a->E <= 0 || a->N < 0 || a->K <= 0 || a->topk < 1 || block_r <= 0 || block_c <= 0)
+    return fail(LB200_E_SHAPE, "light_b200: moe_gemm_f8block: bad shape");
+  if (a->dtype != LB200_F32 && a->dtype != LB200_BF16)
+    return fail(LB200_E_DTYPE, "light_b200: moe_gemm_f8block: activation type %d, want F32 or BF16", a->dtype);
+  if (!a->counts || !a->offsets || !w_scale) return fail(LB200_E_NULL, "light_b200: moe_gemm_f8block: counts / offsets / scale missing");
+  if (a->M > 0 && (!a->input || !a->weights || !a->sorted_pairs || !a->expert_ids || !a->out))
+    return fail(LB200_E_NULL, "light_b200: moe_gemm_f8block: null tensor pointer");
+  if (int rc = bind(device)) return rc;
+  if (a->M == 0) return 0;
+  return moe_gemm_f8block(a, w_scale, block_r, block_c, device, (cudaStream_t)stream);
+}
+
 int light_b200_moe_gemm_q(const lb200_moe_args *a, int device, void *stream) {
   if (int rc = moe_check(a, "moe_gemm_q", true)) return rc;
   if (int rc = bind(device)) return rc;
-  return moe_gemm_q(a, (cudaStream_t)stream);
+  return moe_gemm_q(a, device, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -68,8 +68,10 @@ int fp8_block_dequant(const uint8_t *w, const float *s, void *out, int out_dtype
                       cudaStream_t st);
 int fp8_block_gemv(const void *x, const uint8_t *w, const float *s, void *y, int act_dtype, int M, int N, int K, int bR,
                    int bC, cudaStream_t st);
-int moe_gemm(const lb200_moe_args *a, cudaStream_t st);
-int moe_gemm_q(const lb200_moe_args *a, cudaStream_t st);
+int moe_gemm(const lb200_moe_args *a, int device, cudaStream_t st);
+int moe_gemm_q(const lb200_moe_args *a, int device, cudaStream_t st);
+int moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int bR, int bC, int device, cudaStream_t st);
+int moe_umma(const lb200_moe_args *a, int kind, const float *w_scale, int bR, int bC, int device, cudaStream_t st);
 int moe_gemm_static_scratch(const lb200_moe_args *a, int device, cudaStream_t st);
 
 }  // namespace lb

@@ -157,9 +157,10 @@ static int run(const lb200_moe_args *a, cudaStream_t st) {
   return launched("moe_gemm");
 }
 
-int moe_gemm(const lb200_moe_args *a, cudaStream_t st) {
+int moe_gemm(const lb200_moe_args *a, int device, cudaStream_t st) {
   int rc = prep(a, st);
   if (rc) return rc;
+  if (int took = moe_umma(a, 0, nullptr, 0, 0, device, st)) return took == 1 ? 0 : took;
   switch (a->dtype) {
     case LB200_F32: return run<float, float, DenseRow<float>>(a, st);
     case LB200_BF16: return run<__nv_bfloat16, __nv_bfloat16, DenseRow<__nv_bfloat16>>(a, st);
@@ -198,12 +199,24 @@ int moe_gemm_static_scratch(const lb200_moe_args *a, int device, cudaStream_t st
   b.offsets = base + LB200_MOE_STATIC_MAX_EXPERTS + 1;  // E + 1 entries
   // Both ranges are fully overwritten by the offsets / counts kernels before the matmul reads
   // them, so what an earlier call left behind never matters and nothing needs clearing.
-  return moe_gemm(&b, st);
+  return moe_gemm(&b, device, st);
 }
 
-int moe_gemm_q(const lb200_moe_args *a, cudaStream_t st) {
+int moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int bR, int bC, int device, cudaStream_t st) {
   int rc = prep(a, st);
   if (rc) return rc;
+  int took = moe_umma(a, 2, w_scale, bR, bC, device, st);
+  if (took == 1) return 0;
+  if (took) return took;
+  return fail(LB200_E_SHAPE,
+              "light_b200: moe_gemm_f8block: needs M >= 256 pairs, K %% 128 == 0, block_c %% 64 == 0, 16-byte aligned "
+              "tensors and a workspace of M * K * 2 bytes (light_b200_set_workspace)");
+}
+
+int moe_gemm_q(const lb200_moe_args *a, int device, cudaStream_t st) {
+  int rc = prep(a, st);
+  if (rc) return rc;
+  if (int took = moe_umma(a, 1, nullptr, 0, 0, device, st)) return took == 1 ? 0 : took;
   switch (a->dtype) {
     case LB200_Q4_0: return run<float, float, QuantRow<LB200_Q4_0>>(a, st);
     case LB200_Q5_0: return run<float, float, QuantRow<LB200_Q5_0>>(a, st);

@@ -80,7 +80,9 @@ struct Q4KRow {
   static constexpr int STEPS = 4;  // one load() = one 256-element block = 4 steps of 64
   const uint8_t *row;
   uint4 h, q[8];
-  __device__ __forceinline__ void init(const Ctx &c, int n, int K) { row = c.w + (size_t)n * (size_t)(K / 256) * 144; }
+  __device__ __forceinline__ void init(const Ctx &c, int e, int n, int N, int K) {
+    row = c.w + ((size_t)e * N + n) * (size_t)(K / 256) * 144;
+  }
   __device__ __forceinline__ void load(int kb) {
     const uint4 *p = reinterpret_cast<const uint4 *>(row) + (size_t)kb * 9;
     h = __ldg(p);
@@ -128,7 +130,9 @@ struct Q6KRow {
   const uint8_t *row;
   uint32_t ql[16], qh[8], sc[2];
   float d;
-  __device__ __forceinline__ void init(const Ctx &c, int n, int K) { row = c.w + (size_t)n * (size_t)(K / 256) * 210; }
+  __device__ __forceinline__ void init(const Ctx &c, int e, int n, int N, int K) {
+    row = c.w + ((size_t)e * N + n) * (size_t)(K / 256) * 210;
+  }
   __device__ __forceinline__ static uint32_t ld(const uint32_t *a, uint32_t sh) {
     const uint32_t lo = __ldg(a);
     uint32_t hi = 0;
@@ -187,9 +191,10 @@ struct Int4Row {
   const float *sr, *zr;
   int G, unit;
   uint4 q[8];
-  __device__ __forceinline__ void init(const Ctx &c, int n, int K) {
-    row = reinterpret_cast<const uint4 *>(c.codes + (size_t)n * (K / 8));
-    sr = c.s + (size_t)n * (K / c.G), zr = c.z + (size_t)n * (K / c.G), G = c.G;
+  __device__ __forceinline__ void init(const Ctx &c, int e, int n, int N, int K) {
+    const size_t r = (size_t)e * N + n;
+    row = reinterpret_cast<const uint4 *>(c.codes + r * (K / 8));
+    sr = c.s + r * (K / c.G), zr = c.z + r * (K / c.G), G = c.G;
   }
   __device__ __forceinline__ void load(int u) {
     unit = u;
@@ -229,9 +234,9 @@ struct Fp8Row {
   const float *sr;
   int bC, unit;
   uint4 q[8];
-  __device__ __forceinline__ void init(const Ctx &c, int n, int K) {
-    row = reinterpret_cast<const uint4 *>(c.w + (size_t)n * K);
-    sr = c.scale + (size_t)(n / c.bR) * (K / c.bC), bC = c.bC;
+  __device__ __forceinline__ void init(const Ctx &c, int e, int n, int N, int K) {
+    row = reinterpret_cast<const uint4 *>(c.w + ((size_t)e * N + n) * K);
+    sr = c.scale + ((size_t)e * (N / c.bR) + n / c.bR) * (K / c.bC), bC = c.bC;
   }
   __device__ __forceinline__ void load(int u) {
     unit = u;
@@ -258,14 +263,48 @@ struct Fp8Row {
   }
 };
 
+// Dense 16-bit weights (bf16 with bf16 operands, f16 with f16 operands): the row is copied as it is.
+struct DenseCtx {
+  const uint16_t *w;
+};
+struct DenseRow {
+  using Ctx = DenseCtx;
+  static constexpr int STEPS = 1;
+  const uint4 *row;
+  uint4 q[8];
+  __device__ __forceinline__ void init(const Ctx &c, int e, int n, int N, int K) {
+    row = reinterpret_cast<const uint4 *>(c.w + ((size_t)e * N + n) * K);
+  }
+  __device__ __forceinline__ void load(int u) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) q[i] = __ldg(row + (size_t)u * 8 + i);
+  }
+  template <bool BF16>
+  __device__ __forceinline__ void step(int, uint32_t tile, int r) const {
+#pragma unroll
+    for (int c = 0; c < 8; c++) st_chunk(tile + swz(r, c), q[c]);
+  }
+};
+
+// Grouped (mixture-of-experts) mode: the token rows of the A operand have been gathered into expert
+// order, expert e owns rows offsets[e] .. offsets[e+1] of it; output row i goes to pair sorted_pairs[i],
+// scaled by its routing weight.  offsets == nullptr selects the plain (one weight) mode.
+struct Group {
+  const int32_t *offsets;
+  const int64_t *pairs;
+  const float *topkw;
+  long long size_m;
+  int E;
+};
+
 // ---- the kernel.  grid = (ceil(N / 256), ceil(M / 256)); 320 threads:
 //   warps 0-7  expand weights (thread r <-> weight row n0 + r), then run the epilogue
 //   warp  8    TMA producer of the x tiles (one lane)
 //   warp  9    owns tensor memory and issues the MMAs (one lane)
 template <typename Row, bool BF16, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
-                                                                 const typename Row::Ctx ctx, OutT *__restrict__ out,
-                                                                 int M, int N, int K) {
+                                                                 const typename Row::Ctx ctx, const Group grp,
+                                                                 OutT *__restrict__ out, int M, int N, int K) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = base, sB = base + SA * A_STAGE, sBar = sB + SB * B_STAGE;
@@ -275,9 +314,29 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_base_sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
+  const int n0 = blockIdx.x * BN;
+  int m0 = blockIdx.y * BM, m_end = M, expert = 0;
+  if (grp.offsets) {
+    // which (expert, tile of its rows) is this CTA's?  Tiles are numbered expert by expert.
+    __shared__ int tile_info[3];
+    if (threadIdx.x == 0) {
+      int y = blockIdx.y, e = 0;
+      tile_info[0] = -1;
+      for (; e < grp.E; e++) {
+        const int lo = grp.offsets[e], hi = grp.offsets[e + 1], t = (hi - lo + BM - 1) / BM;
+        if (y < t) {
+          tile_info[0] = e, tile_info[1] = lo + y * BM, tile_info[2] = hi;
+          break;
+        }
+        y -= t;
+      }
+    }
+    __syncthreads();
+    if (tile_info[0] < 0) return;  // beyond the last tile: the grid is sized for the worst case
+    expert = tile_info[0], m0 = tile_info[1], m_end = tile_info[2];
+  }
   const int nkb = K / BK;
-  const bool two = m0 + 128 < M;  // the second 128-token tile holds real tokens
+  const bool two = m0 + 128 < m_end;  // the second 128-row tile holds real rows
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -346,7 +405,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
     const int r = threadIdx.x;
     const int n = min(n0 + r, N - 1);
     Row cur;
-    cur.init(ctx, n, K);
+    cur.init(ctx, expert, n, N, K);
     cur.load(0);
     bool ok = true;
     const int units = K / (BK * Row::STEPS);
@@ -379,14 +438,26 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
       const int quad = warp & 3, chalf = warp >> 2;
 #pragma unroll 1
       for (int a = 0; a < (two ? 2 : 1); a++) {
-        const int m = m0 + a * 128 + quad * 32 + lane;
+        const int mi = m0 + a * 128 + quad * 32 + lane;  // row of the A operand
+        long long m = mi;                                 // row of the output
+        float wgt = 1.f;
+        bool live = mi < m_end;
+        if (grp.offsets && live) {
+          m = grp.pairs[mi];
+          live = m >= 0 && m < grp.size_m;
+          if (live && grp.topkw) wgt = grp.topkw[m];
+        }
 #pragma unroll 1
         for (int c = 0; c < 4; c++) {
           uint32_t v[32];
           tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + a * 256 + chalf * 128 + c * 32, v);
           tmem_ld_wait();
           const int nc = n0 + chalf * 128 + c * 32;
-          if (m < M) {
+          if (live) {
+            if (grp.topkw) {
+#pragma unroll
+              for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
+            }
             OutT *o = out + (size_t)m * N + nc;
             if (nc + 32 <= N && (N & 7) == 0) {
               if constexpr (sizeof(OutT) == 4) {
@@ -476,7 +547,8 @@ int make_x_map(CUtensorMap *tm, const void *x, int act_dtype, int M, int K, void
 }
 
 template <typename Row, bool BF16, typename OutT>
-int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, OutT *out, int M, int N, int K, cudaStream_t st) {
+int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp, OutT *out, int M, int N, int K,
+           cudaStream_t st) {
   auto kern = prefill_umma_kernel<Row, BF16, OutT>;
   static bool attr_done = false;
   if (!attr_done) {
@@ -484,8 +556,9 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, OutT *out, int M
     if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
     attr_done = true;
   }
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, out, M, N, K);
+  // grouped: at most ceil(M / BM) + E tiles (every expert can end with one partial tile)
+  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM + (grp.offsets ? grp.E : 0));
+  kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K);
   return launched("prefill (tcgen05)");
 }
 
@@ -495,8 +568,9 @@ int launch_by_act(const void *x, int act_dtype, const typename Row::Ctx &ctx, vo
                   cudaStream_t st) {
   CUtensorMap tm;
   if (int rc = make_x_map(&tm, x, act_dtype, M, K, ws, st)) return rc;
-  if (act_dtype == LB200_F32) return launch<Row, false, float>(tm, ctx, (float *)out, M, N, K, st);
-  return launch<Row, true, __nv_bfloat16>(tm, ctx, (__nv_bfloat16 *)out, M, N, K, st);
+  const Group none{nullptr, nullptr, nullptr, 0, 0};
+  if (act_dtype == LB200_F32) return launch<Row, false, float>(tm, ctx, none, (float *)out, M, N, K, st);
+  return launch<Row, true, __nv_bfloat16>(tm, ctx, none, (__nv_bfloat16 *)out, M, N, K, st);
 }
 
 // workspace for an f32 activation matrix; bf16 needs none.  Returns false if there is not enough.
@@ -557,6 +631,95 @@ int fp8_prefill(const void *x, const uint8_t *w, const float *scale, void *y, in
   if (!get_ws(device, act_dtype, M, K, &ws)) return 0;
   Fp8Ctx ctx{w, scale, bR, bC};
   int rc = launch_by_act<Fp8Row>(x, act_dtype, ctx, y, M, N, K, ws, st);
+  return rc ? rc : 1;
+}
+
+namespace {
+
+// ---- grouped (mixture-of-experts) matmul on the same kernel.
+// Rows of the A operand in expert order: dst[i] = in[row(sorted_pairs[i])], converted to the operand type
+// (f32 -> f16 clamped, 16-bit types copied); rows of pairs outside [0, size_m) are zero.
+template <typename TI>
+__global__ void __launch_bounds__(256) gather_rows_kernel(const TI *__restrict__ in, const int64_t *__restrict__ pairs,
+                                                          uint16_t *__restrict__ dst, long long Mp, int K, int topk,
+                                                          int row_per_pair, long long size_m) {
+  const int lane = threadIdx.x & 31;
+  for (long long i = (long long)blockIdx.x * 8 + (threadIdx.x >> 5); i < Mp; i += (long long)gridDim.x * 8) {
+    const long long p = pairs[i];
+    const bool ok = p >= 0 && p < size_m;
+    const TI *src = in + (size_t)(row_per_pair ? p : p / topk) * K;
+    for (int k = lane * 8; k < K; k += 256) {
+      uint4 o = make_uint4(0, 0, 0, 0);
+      if (ok) {
+        if constexpr (sizeof(TI) == 4) {
+          const float4 a = __ldg(reinterpret_cast<const float4 *>(src + k)), b = __ldg(reinterpret_cast<const float4 *>(src + k) + 1);
+          auto cl = [](float v) { return fminf(fmaxf(v, -65504.f), 65504.f); };
+          o = make_uint4(pack_h2(cl(a.x), cl(a.y)), pack_h2(cl(a.z), cl(a.w)), pack_h2(cl(b.x), cl(b.y)), pack_h2(cl(b.z), cl(b.w)));
+        } else {
+          o = __ldg(reinterpret_cast<const uint4 *>(src + k));
+        }
+      }
+      *reinterpret_cast<uint4 *>(dst + (size_t)i * K + k) = o;
+    }
+  }
+}
+
+template <typename Row, bool BF16, typename OutT, typename TI>
+int moe_launch(const lb200_moe_args *a, const typename Row::Ctx &ctx, void *ws, cudaStream_t st) {
+  if (int rc = ensure_encode()) return rc;
+  long long blocks = (a->M + 7) / 8;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  gather_rows_kernel<TI><<<(unsigned)blocks, 256, 0, st>>>((const TI *)a->input, a->sorted_pairs, (uint16_t *)ws, a->M, a->K,
+                                                          a->topk, a->row_per_pair, a->size_m);
+  if (int rc = launched("moe: gather rows")) return rc;
+  CUtensorMap tm;
+  const cuuint64_t dims[2] = {(cuuint64_t)a->K, (cuuint64_t)a->M};
+  const cuuint64_t strides[1] = {(cuuint64_t)a->K * 2};
+  const cuuint32_t box[2] = {BK, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(&tm, BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, ws, dims, strides, box,
+                        estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LB200_E_SHAPE, "light_b200: moe: cuTensorMapEncodeTiled failed (%d)", (int)r);
+  const Group grp{a->offsets, a->sorted_pairs, a->topk_weights, a->size_m, a->E};
+  return launch<Row, BF16, OutT>(tm, ctx, grp, (OutT *)a->out, (int)a->M, a->N, a->K, st);
+}
+
+}  // namespace
+
+// Grouped matmul on the tensor cores; the expert offsets must already be in a->offsets.  kind: 0 dense
+// (a->dtype = BF16 only), 1 GGUF (a->dtype = Q4_K / Q6_K, x f32), 2 block-scaled FP8 (a->dtype = F32 / BF16
+// activations).  Returns 1 when taken, 0 when not covered, other values are errors.
+int moe_umma(const lb200_moe_args *a, int kind, const float *w_scale, int bR, int bC, int device, cudaStream_t st) {
+  if (a->M < 256 || a->M > 0x7fffffffLL || ((uintptr_t)a->input & 15) || ((uintptr_t)a->weights & 15) || a->K % 64) return 0;
+  void *ws;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!g_ws[device].ptr || g_ws[device].bytes < (size_t)a->M * a->K * 2) return 0;
+    ws = g_ws[device].ptr;
+  }
+  int rc = 0;
+  if (kind == 0) {
+    if (a->dtype != LB200_BF16) return 0;
+    rc = moe_launch<DenseRow, true, __nv_bfloat16, __nv_bfloat16>(a, DenseCtx{(const uint16_t *)a->weights}, ws, st);
+  } else if (kind == 1) {
+    if (a->K % 256) return 0;
+    if (a->dtype == LB200_Q4_K)
+      rc = moe_launch<Q4KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
+    else if (a->dtype == LB200_Q6_K && ((size_t)(a->K >> 8) * 210) % 4 == 0)
+      rc = moe_launch<Q6KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
+    else
+      return 0;
+  } else {
+    if (a->K % 128 || bC % 64 || bR <= 0 || a->N % bR || a->K % bC) return 0;
+    const Fp8Ctx ctx{(const uint8_t *)a->weights, w_scale, bR, bC};
+    if (a->dtype == LB200_BF16)
+      rc = moe_launch<Fp8Row, true, __nv_bfloat16, __nv_bfloat16>(a, ctx, ws, st);
+    else if (a->dtype == LB200_F32)
+      rc = moe_launch<Fp8Row, false, float, float>(a, ctx, ws, st);
+    else
+      return 0;
+  }
   return rc ? rc : 1;
 }
 

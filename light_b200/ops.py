@@ -259,7 +259,7 @@ def MoERoute(probs: torch.Tensor, topk: int, normalize: bool) -> MoERouting:
 
 
 def _moe_dispatch(op: str, key_dtype: int, quant: bool, inp: torch.Tensor, weights, wshape, routing: MoERouting,
-                  topk_weights: Optional[torch.Tensor], topk: int, out_dtype: torch.dtype) -> torch.Tensor:
+                  topk_weights: Optional[torch.Tensor], topk: int, out_dtype: torch.dtype, f8=None) -> torch.Tensor:
     """moeGemmDispatch (ops/moe.go:124-204)."""
     if inp.dim() != 2 or len(wshape) != 3:
         raise ValueError(f"{op}: input (rows, K) and weights (E, N, K) required, got {tuple(inp.shape)} / {tuple(wshape)}")
@@ -280,6 +280,8 @@ def _moe_dispatch(op: str, key_dtype: int, quant: bool, inp: torch.Tensor, weigh
         raise ValueError(f"{op}: topkWeights must be F32 with {M} elements")
     dev = _dev(inp, op)
     inc = inp.contiguous()
+    if M >= 256:  # tensor-core grouped path: the token rows are gathered into the workspace in expert order
+        ensure_workspace(dev, M * K * 2)
     counts = torch.zeros(E, dtype=torch.int32, device=inp.device)
     offsets = torch.zeros(E + 1, dtype=torch.int32, device=inp.device)
     out = torch.zeros((M, N), dtype=out_dtype, device=inp.device)
@@ -288,6 +290,10 @@ def _moe_dispatch(op: str, key_dtype: int, quant: bool, inp: torch.Tensor, weigh
                 offsets=offsets.data_ptr(),
                 topk_weights=0 if topk_weights is None else topk_weights.contiguous().data_ptr(), out=out.data_ptr(),
                 M=M, size_m=M, E=E, N=N, K=K, topk=topk, row_per_pair=int(row_per_pair), dtype=key_dtype)
+    if f8 is not None:
+        scale, bR, bC = f8
+        _lib.check(_lib.lib().light_b200_moe_gemm_f8block(C.byref(a), _ptr(scale.contiguous()), bR, bC, dev, _stream(dev)))
+        return out
     fn = _lib.lib().light_b200_moe_gemm_q if quant else _lib.lib().light_b200_moe_gemm
     _lib.check(fn(C.byref(a), dev, _stream(dev)))
     return out
@@ -316,6 +322,25 @@ def MoEGemmQ(x: torch.Tensor, w: QTensor, routing: MoERouting, topk_weights: Opt
         raise ValueError(f"moe_gemm_q: w must be a quantized (E, N, K) tensor, got {tuple(w.shape)}")
     return _moe_dispatch("moe_gemm_q", w.ggml_type, True, x, w.data, tuple(w.shape), routing, topk_weights, topk,
                          torch.float32)
+
+
+def MoEGemmF8Block(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, block_r: int, block_c: int,
+                   routing: MoERouting, topk_weights: Optional[torch.Tensor], topk: int) -> torch.Tensor:
+    """Grouped matmul over block-scaled FP8 experts: w e4m3 codes (E, N, K) (uint8 or float8_e4m3fn), scale
+    f32 (E, N/bR, K/bC), x F32 or BF16 (rows per token or per pair), output (M, N) at x's dtype.  The
+    reference runs this as a host loop over experts (models/moe_routed.go:34-79: IndexSelect, one
+    ops.MatMulF8Block per expert, scatter); the contract per pair is the same as MoEGemm's."""
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"moe_gemm_f8block: activations {x.dtype}, want F32 or BF16")
+    if w.dim() != 3 or scale.dim() != 3:
+        raise ValueError(f"moe_gemm_f8block: w (E, N, K) and scale (E, N/bR, K/bC) required, got {tuple(w.shape)} / "
+                         f"{tuple(scale.shape)}")
+    E, N, K = w.shape
+    if block_r <= 0 or block_c <= 0 or N % block_r or K % block_c or tuple(scale.shape) != (E, N // block_r, K // block_c):
+        raise ValueError(f"moe_gemm_f8block: weight {tuple(w.shape)}, scale {tuple(scale.shape)}, block ({block_r}, {block_c}) "
+                         "inconsistent")
+    return _moe_dispatch("moe_gemm_f8block", _ACT[x.dtype], False, x, w.contiguous(), (E, N, K), routing, topk_weights, topk,
+                         x.dtype, f8=(scale, block_r, block_c))
 
 
 def MoECombine(pair_out: torch.Tensor, topk: int) -> torch.Tensor:

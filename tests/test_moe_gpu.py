@@ -123,3 +123,66 @@ def test_moe_vs_reference_cuda(cuda):
                 C.c_int(topk), C.c_ulong(T * topk), C.c_ulong(N), C.c_ulong(K), C.c_int(0)])
     torch.cuda.synchronize()
     assert rel_l2(mine.cpu().numpy(), theirs.cpu().numpy()) <= 1e-3
+
+
+def _skewed_routing(seed, T, E, topk, dev):
+    """Biased router (per-expert bias ~ N(0, 1.5)): some experts get several tiles, some get nothing."""
+    g = torch.Generator().manual_seed(seed)
+    logits = torch.randn(T, E, generator=g) + torch.randn(E, generator=g) * 1.5
+    logits[:, E - 1] = -1e9  # the last expert never routed
+    return ops.MoERoute(torch.softmax(logits, dim=1).to(dev), topk, True)
+
+
+def test_moe_grouped_tensor_core_dense_bf16(cuda, oracle):
+    """M >= 256 pairs takes the tcgen05 grouped kernel (bf16 operands): same contract, bf16 tolerance."""
+    T, E, topk, N, K = 300, 8, 2, 320, 128
+    r = _skewed_routing(131, T, E, topk, cuda)
+    g = torch.Generator().manual_seed(132)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, N, K, generator=g) * 0.1).to(torch.bfloat16)
+    got = ops.MoEGemm(x.to(cuda), w.to(cuda), r, r.weights, topk)
+    want = oracle.moe_gemm_f32(x.float().numpy(), w.float().numpy(), r.sorted_pairs.cpu().numpy(),
+                               r.sorted_expts.cpu().numpy(), r.weights.cpu().numpy(), T * topk, topk, False)
+    assert got.dtype == torch.bfloat16 and rel_l2(got.float().cpu().numpy(), want) <= 4e-3
+    assert ops.prefill_status(0) == 0
+
+
+@pytest.mark.parametrize("name", ["q4_k", "q6_k"])
+def test_moe_grouped_tensor_core_gguf(cuda, oracle, name):
+    dt = {"q4_k": ops.Q4_K, "q6_k": ops.Q6_K}[name]
+    T, E, topk, N, K = 400, 6, 2, 264, 512
+    r = _skewed_routing(141, T, E, topk, cuda)
+    raw = synth.random_blocks(142, dt, E * N, K)
+    deq = oracle.dequant(dt, raw.reshape(-1), E * N * K).reshape(E, N, K)
+    x = torch.randn(T, K, generator=torch.Generator().manual_seed(143))
+    w = ops.QTensor(torch.from_numpy(raw.reshape(-1)).to(cuda), dt, (E, N, K))
+    got = ops.MoEGemmQ(x.to(cuda), w, r, r.weights, topk).cpu().numpy()
+    want = oracle.moe_gemm_f32(x.numpy(), deq, r.sorted_pairs.cpu().numpy(), r.sorted_expts.cpu().numpy(),
+                               r.weights.cpu().numpy(), T * topk, topk, False)
+    assert rel_l2(got, want) <= 1e-3
+    # second GEMM of a layer: one input row per pair, no routing weights
+    h = torch.randn(T * topk, K, generator=torch.Generator().manual_seed(144))
+    got2 = ops.MoEGemmQ(h.to(cuda), w, r, None, topk).cpu().numpy()
+    want2 = oracle.moe_gemm_f32(h.numpy(), deq, r.sorted_pairs.cpu().numpy(), r.sorted_expts.cpu().numpy(), None,
+                                T * topk, topk, True)
+    assert rel_l2(got2, want2) <= 1e-3
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-3), (torch.bfloat16, 4e-3)])
+def test_moe_gemm_f8block(cuda, oracle, dtype, tol):
+    """Block-scaled FP8 experts (128 x 128 blocks) against the per-expert loop the reference runs:
+    dequantize each expert (oracle) and take the pair-wise dot products."""
+    T, E, topk, N, K, b = 350, 8, 2, 256, 384, 128
+    r = _skewed_routing(151, T, E, topk, cuda)
+    codes, scale = synth.random_fp8_block(152, E * N, K, b, b)
+    deq = oracle.fp8_block_dequant(codes.numpy(), scale.numpy(), b, b).reshape(E, N, K)
+    if dtype == torch.bfloat16:
+        deq = torch.from_numpy(deq).to(torch.bfloat16).float().numpy()
+    x = torch.randn(T, K, generator=torch.Generator().manual_seed(153)).to(dtype)
+    got = ops.MoEGemmF8Block(x.to(cuda), codes.reshape(E, N, K).to(cuda), scale.reshape(E, N // b, K // b).to(cuda), b, b, r,
+                             r.weights, topk)
+    want = oracle.moe_gemm_f32(x.float().numpy(), deq, r.sorted_pairs.cpu().numpy(), r.sorted_expts.cpu().numpy(),
+                               r.weights.cpu().numpy(), T * topk, topk, False)
+    assert got.dtype == dtype and rel_l2(got.float().cpu().numpy(), want) <= tol
+    # rows of the never-routed expert and of pairs that do not exist stay zero
+    assert ops.prefill_status(0) == 0
