@@ -110,19 +110,38 @@ class ClockSampler:
 class Chain:
     """The quantized linears of one decode step on one GPU, each weight row-split over `world` ranks."""
 
-    def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0):
+    def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0, share=None):
         self.device, self.M, self.rank, self.world = device, M, rank, world
         self.lin = []  # (name, N_local, N, K, dt, weight bytes tensor)
-        for l in range(layers):
-            for i, (name, N, K, dt) in enumerate(LAYER):
-                self.lin.append(self._make(f"l{l}.{name}", N, K, dt, seed * 100003 + l * 16 + i))
-        self.lin.append(self._make(*HEAD, seed * 100003 + 99991))
+        if share is not None:  # same weights, another token count
+            self.lin = share.lin
+        else:
+            for l in range(layers):
+                for i, (name, N, K, dt) in enumerate(LAYER):
+                    self.lin.append(self._make(f"l{l}.{name}", N, K, dt, seed * 100003 + l * 16 + i))
+            self.lin.append(self._make(*HEAD, seed * 100003 + 99991))
         g = torch.Generator(device=device)
         g.manual_seed(seed + 7)
         self.x = {HID: torch.randn(M, HID, generator=g, device=device), FFN: torch.randn(M, FFN, generator=g, device=device)}
         self.out = [torch.empty(M, e[2], device=device) for e in self.lin]  # full-width outputs (gathered when world > 1)
         self.local = [torch.empty(M, e[1], device=device) for e in self.lin] if world > 1 else self.out
         self.dev_index = device.index or 0
+        self.peer, self.gather_kind = None, "none"
+        if world > 1:
+            self.gidx = [i for i, e in enumerate(self.lin) if e[0].split(".")[-1] in self.GATHERED]
+            self.gather_kind = "nccl"
+            if os.environ.get("LIGHT_B200_TP_GATHER", "peer") == "peer":
+                try:
+                    from light_b200 import tp
+
+                    self.peer = tp.PeerGather(device)
+                    outs = self.peer.plan([(M, self.lin[i][2]) for i in self.gidx])
+                    for j, i in enumerate(self.gidx):
+                        self.out[i] = outs[j]
+                    self.gather_kind = "peer"
+                except Exception as e:  # noqa: BLE001  (no peer mapping on this box: NCCL does the gathers)
+                    print(f"[bench] peer-memory gather unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+                    self.peer = None
 
     def _make(self, name, N, K, dt, seed):
         assert N % self.world == 0
@@ -147,13 +166,18 @@ class Chain:
 
         st = torch.cuda.current_stream(self.device).cuda_stream
         n = 0
+        if self.peer is not None and only is None:
+            self.peer.step_begin()
         for i, e in enumerate(self.lin):
             if only is not None and e[4] != only:
                 continue
             self.launch(i, st)
             n += 1
             if self.world > 1 and only is None and e[0].split(".")[-1] in self.GATHERED:
-                tp.all_gather_columns(self.local[i], self.out[i])
+                if self.peer is not None:
+                    self.peer.gather(self.gidx.index(i), self.local[i])
+                else:
+                    tp.all_gather_columns(self.local[i], self.out[i])
         return n
 
     def bytes_per_step(self, only=None):
@@ -226,6 +250,40 @@ def cpu_reference(M, threads, steps, warmup):
                                f"scaled to 32 layers + lm_head; M={M}"
 
 
+def extras(chain, device, args):
+    """Side measurements on the same weights, reported next to the headline (not part of `value`):
+    batched decode at the other token counts of configs[1], and the prefill matmuls of configs[2]."""
+    out = {"decode_tokens_per_s": {}, "prefill_m2048": {}}
+    steps = max(5, min(20, args.steps))
+    for M in (8, 32, 64):
+        c = Chain(device, M, share=chain)
+        g = capture(c.step, device)
+        ms = timed(g.replay, steps, 3, device, lambda: None) / steps
+        out["decode_tokens_per_s"][str(M)] = {"ms_per_step": ms, "tok_s": M / (ms * 1e-3),
+                                              "weights_gbs": c.bytes_per_step() / (ms * 1e-3) / 1e9}
+        del g, c
+    M = 2048
+    by = {e[0]: e for e in chain.lin}
+    qkv = torch.cat([by["l0.q"][5], by["l0.k"][5], by["l0.v"][5]])          # fused rows: a byte concatenation
+    gate_up = torch.cat([by["l0.gate"][5], by["l0.up"][5]])
+    shapes = [("qkv", qkv, HID + 2 * NKV, HID, ops.Q4_K), ("o", by["l0.o"][5], HID, HID, ops.Q4_K),
+              ("gate_up", gate_up, 2 * FFN, HID, ops.Q4_K), ("down", by["l0.down"][5], HID, FFN, ops.Q6_K)]
+    for name, w, N, K, dt in shapes:
+        x = torch.randn(M, K, device=device).to(torch.bfloat16).float()
+        qt = ops.QTensor(w.reshape(-1), dt, (N, K))
+        ops.MatMulQ(x, qt)
+        ms = timed(lambda: ops.MatMulQ(x, qt), 10, 3, device, lambda: None) / 10
+        out["prefill_m2048"][name] = {"ms": ms, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12}
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    if "bf16_tflops_sustained" in peaks:
+        tot_f = sum(2.0 * M * N * K for _, _, N, K, _ in shapes)
+        tot_t = sum(v["ms"] for v in out["prefill_m2048"].values()) * 1e-3
+        out["prefill_m2048"]["all_four"] = {"tflops": tot_f / tot_t / 1e12,
+                                            "frac_of_measured_sustained_bf16": tot_f / tot_t / 1e12 / peaks["bf16_tflops_sustained"]}
+    out["tensor_core_status"] = ops.prefill_status(device.index or 0)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -235,6 +293,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=1, help="tokens per decode step (M)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers (default: the full 32)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the batched-decode and prefill side measurements")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -275,6 +334,7 @@ def main():
 
     chain = Chain(device, M, rank, world, layers=args.layers)
     torch.cuda.synchronize(device)
+    barrier()
     launches_per_step = chain.launches()
     graph = capture(chain.step, device)
 
@@ -330,19 +390,23 @@ def main():
         "dtype": "f32 activations x Q4_K/Q6_K weights, f32 accumulate", "data": "synthetic",
         "config": {"workload": workload, "tokens_per_step": M, "layers": args.layers,
                    "weights_bytes_per_step": sum(weight_bytes(e[2], e[3], e[4]) for e in chain.lin),
-                   "parallelism": f"rows of every weight split over {world} GPU(s)" + (", NCCL all-gather of the attention output, o, the MLP activation, down and the logits (129 per step)" if world > 1 else ""),
+                   "parallelism": f"rows of every weight split over {world} GPU(s)" + (f", all-gather ({chain.gather_kind}) of the attention output, o, the MLP activation, down and the logits (129 per step)" if world > 1 else ""),
                    "l2": "inputs (4.84 GB of weights per step) exceed the 126 MB L2", "launch": "CUDA graph replay"},
         "roofline": roofline,
         "e2e": {"value": e2e_val, "unit": unit, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
         "clocks": clk.summary(),
     }
+    if world == 1 and not args.no_extras:
+        line["extras"] = extras(chain, device, args)
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             v, t_step, sample = cpu_reference(M, threads, 3, 1)
             line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
+    if world > 1 and chain.peer is not None and chain.peer.status() != 0:
+        print("[bench] a bounded wait on a peer gave up: the N-GPU number above is not valid", file=sys.stderr)
     if world > 1:
         # Graphs that captured NCCL kernels must be gone before the communicator is torn down; and a
         # communicator that will not finish tearing down must not keep the job alive.

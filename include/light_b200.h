@@ -170,6 +170,33 @@ LB200_API int light_b200_moe_gemm(const lb200_moe_args *args, int device, void *
 LB200_API int light_b200_moe_gemm_f8block(const lb200_moe_args *args, const float *w_scale, int block_r, int block_c,
                                           int device, void *stream);
 
+/* ---- multi-GPU: all-gather of row-split outputs over NVLink peer memory (no counterpart in the
+ * reference, which is single-GPU: STATUS.md:474).  Each rank r of `world` (<= LB200_MAX_PEERS) GPUs of one
+ * node owns rows [r N/P, (r+1) N/P) of a weight and so produces an (M, N/P) column block of the output.
+ * slots[p] is rank p's receive buffer for THIS gathered operator: 2 * M * N slots of 8 bytes ({f32, u32 tag};
+ * two sets, used on alternating steps), 8-byte aligned, in memory every rank can address (peer-mapped / symmetric memory; the caller sets that
+ * up), zeroed once. */
+#define LB200_MAX_PEERS 8
+typedef struct lb200_peers {
+  void *slots[LB200_MAX_PEERS];
+  int32_t world, rank;
+} lb200_peers;
+
+/* Once per step (one pass over the model), before its first gather: bumps the step word (device memory of
+ * this rank, zeroed once) that tags everything sent during the step. */
+LB200_API int light_b200_comm_step_begin(uint32_t *step, int device, void *stream);
+
+/* Writes `local` (M, n_local) f32, tagged with the step, into its slots in every peer's receive buffer and
+ * into columns [rank * n_local, (rank + 1) * n_local) of `out` (M, n_local * world, this rank's own memory);
+ * then fills the other columns of `out` from this rank's receive buffer as the peers' elements of the same
+ * step arrive.  A slot that does not arrive within about 50 ms is given up (status: light_b200_comm_status).
+ * Every rank must issue the same sequence of gathers each step, each operator with its own slots. */
+LB200_API int light_b200_allgather_ll(const float *local, float *out, const lb200_peers *peers, int M, int n_local,
+                                      const uint32_t *step, int device, void *stream);
+
+/* 0, or 1 if a bounded wait on a peer ever gave up on this device.  Synchronises with the device. */
+LB200_API int light_b200_comm_status(int device);
+
 /* Largest expert count light_b200_moe_gemm_static_scratch accepts. */
 #define LB200_MOE_STATIC_MAX_EXPERTS 1024
 

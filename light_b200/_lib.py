@@ -22,6 +22,10 @@ class Light200Error(RuntimeError):
         self.code = code
 
 
+class Peers(C.Structure):
+    _fields_ = [("slots", C.c_void_p * 8), ("world", C.c_int32), ("rank", C.c_int32)]
+
+
 class MoeArgs(C.Structure):
     _fields_ = [
         ("input", C.c_void_p), ("weights", C.c_void_p), ("sorted_pairs", C.c_void_p), ("expert_ids", C.c_void_p),
@@ -37,6 +41,9 @@ SYMBOLS = {
     "light_b200_last_error": (C.c_int, [C.c_char_p, C.c_size_t]),
     "light_b200_abi_version": (C.c_int, []),
     "light_b200_launch_count": (C.c_ulonglong, []),
+    "light_b200_comm_step_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "light_b200_allgather_ll": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Peers), C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
+    "light_b200_comm_status": (C.c_int, [C.c_int]),
     "light_b200_set_workspace": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t]),
     "light_b200_prefill_status": (C.c_int, [C.c_int]),
     "light_b200_block_elems": (C.c_int, [C.c_int]),

@@ -82,6 +82,35 @@ int light_b200_set_workspace(int device, void *ptr, size_t bytes) {
   return set_workspace(device, ptr, bytes);
 }
 
+int light_b200_comm_step_begin(uint32_t *step, int device, void *stream) {
+  REQUIRE_PTR(step, "comm_step_begin");
+  if (int rc = bind(device)) return rc;
+  return comm_step_begin(step, (cudaStream_t)stream);
+}
+
+int light_b200_allgather_ll(const float *local, float *out, const lb200_peers *peers, int M, int n_local, const uint32_t *step,
+                            int device, void *stream) {
+  REQUIRE_PTR(local, "allgather_ll");
+  REQUIRE_PTR(out, "allgather_ll");
+  REQUIRE_PTR(peers, "allgather_ll");
+  REQUIRE_PTR(step, "allgather_ll");
+  if (peers->world < 1 || peers->world > LB200_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->world)
+    return fail(LB200_E_SHAPE, "light_b200: allgather_ll: rank %d of %d (at most %d peers)", peers->rank, peers->world,
+                LB200_MAX_PEERS);
+  if (M < 1 || n_local < 1 || (long long)M * n_local * peers->world > 0x7fffffffLL)
+    return fail(LB200_E_SHAPE, "light_b200: allgather_ll: bad shape M=%d n_local=%d", M, n_local);
+  for (int i = 0; i < peers->world; i++)
+    if (!peers->slots[i] || !aligned(peers->slots[i], 8))
+      return fail(LB200_E_NULL, "light_b200: allgather_ll: peer %d has no (8-byte aligned) receive buffer", i);
+  if (int rc = bind(device)) return rc;
+  return allgather_ll(local, out, peers, M, n_local, step, (cudaStream_t)stream);
+}
+
+int light_b200_comm_status(int device) {
+  if (int rc = bind(device)) return rc;
+  return comm_status();
+}
+
 int light_b200_prefill_status(int device) {
   if (int rc = bind(device)) return rc;
   return prefill_status(device);

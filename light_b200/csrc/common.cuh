@@ -58,6 +58,10 @@ int int4_prefill(const void *x, const uint32_t *codes, const float *s, const flo
 int fp8_prefill(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR,
                 int bC, int device, cudaStream_t st);
 int set_workspace(int device, void *ptr, size_t bytes);
+int comm_step_begin(unsigned int *step, cudaStream_t st);
+int allgather_ll(const float *local, float *out, const lb200_peers *peers, int M, int n_local, const unsigned int *step,
+                 cudaStream_t st);
+int comm_status();
 int prefill_status(int device);
 
 int int4_dequant(const uint32_t *codes, const float *s, const float *z, void *out, int out_dtype, int N, int K, int G,

@@ -71,3 +71,79 @@ def split_pairs_by_rank(sorted_expts: torch.Tensor, E: int, world: int) -> torch
     per = E // world
     bounds = torch.arange(0, world + 1, device=sorted_expts.device, dtype=sorted_expts.dtype) * per
     return torch.searchsorted(sorted_expts.contiguous(), bounds)
+
+
+class PeerGather:
+    """All-gather of row-split f32 outputs through NVLink peer stores (light_b200_allgather_ll).
+
+    One symmetric-memory arena per rank holds a receive buffer (8 bytes per output element) for every
+    gathered operator; `plan(shapes)` lays them out identically on all ranks.  Symmetric memory comes from
+    torch.distributed._symmetric_memory (plumbing only); the data path is this library's kernel.  Raises if
+    the ranks cannot map each other's memory -- callers then fall back to NCCL.
+    """
+
+    def __init__(self, device: torch.device, group=None):
+        import torch.distributed as dist
+
+        self.device, self.group = device, group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+
+    def plan(self, shapes: list[tuple[int, int]]) -> list[torch.Tensor]:
+        """shapes: (M, N) of each gathered output, in the order they are gathered every step.  Returns the
+        full-width output tensors (ordinary local memory)."""
+        import ctypes as C
+
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import _lib
+
+        offs, total = [], 0
+        for M, N in shapes:
+            offs.append(total)
+            total += (2 * M * N * 8 + 255) // 256 * 256  # two sets of slots, alternating by step
+        arena = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        arena.zero_()
+        try:
+            hdl = symm_mem.rendezvous(arena, self.group)
+        except TypeError:
+            hdl = symm_mem.rendezvous(arena, self.group.group_name)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self.arena, self.handle = arena, hdl
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self.peers = []
+        for off in offs:
+            p = _lib.Peers(world=self.world, rank=self.rank)
+            for r in range(self.world):
+                p.slots[r] = ptrs[r] + off
+            self.peers.append(p)
+        self.step = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.outs = [torch.empty(M, N, dtype=torch.float32, device=self.device) for M, N in shapes]
+        self._C = C
+        return self.outs
+
+    def step_begin(self) -> None:
+        from . import _lib
+
+        dev = self.device.index or 0
+        _lib.check(_lib.lib().light_b200_comm_step_begin(self._C.c_void_p(self.step.data_ptr()), dev,
+                                                         self._C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+
+    def gather(self, index: int, local: torch.Tensor) -> torch.Tensor:
+        """Sends this rank's (M, N/P) block of gathered output `index` and receives the others; the returned
+        full-width tensor is complete for whatever runs next on the stream."""
+        from . import _lib
+
+        C = self._C
+        dev = self.device.index or 0
+        M, n = local.shape
+        _lib.check(_lib.lib().light_b200_allgather_ll(C.c_void_p(local.data_ptr()), C.c_void_p(self.outs[index].data_ptr()),
+                                                      C.byref(self.peers[index]), M, n, C.c_void_p(self.step.data_ptr()), dev,
+                                                      C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+        return self.outs[index]
+
+    def status(self) -> int:
+        from . import _lib
+
+        return _lib.lib().light_b200_comm_status(self.device.index or 0)
