@@ -304,7 +304,7 @@ struct Group {
 template <typename Row, bool BF16, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                  const typename Row::Ctx ctx, const Group grp,
-                                                                 OutT *__restrict__ out, int M, int N, int K) {
+                                                                 OutT *__restrict__ out, int M, int N, int K, int bm) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = base, sB = base + SA * A_STAGE, sBar = sB + SB * B_STAGE;
@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
   __shared__ uint32_t tmem_base_sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
-  int m0 = blockIdx.y * BM, m_end = M, expert = 0;
+  int m0 = blockIdx.y * bm, m_end = M, expert = 0;  // bm = 256, or 128 when that fills the SMs better
   if (grp.offsets) {
     // which (expert, tile of its rows) is this CTA's?  Tiles are numbered expert by expert.
     __shared__ int tile_info[3];
@@ -323,9 +323,9 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
       int y = blockIdx.y, e = 0;
       tile_info[0] = -1;
       for (; e < grp.E; e++) {
-        const int lo = grp.offsets[e], hi = grp.offsets[e + 1], t = (hi - lo + BM - 1) / BM;
+        const int lo = grp.offsets[e], hi = grp.offsets[e + 1], t = (hi - lo + bm - 1) / bm;
         if (y < t) {
-          tile_info[0] = e, tile_info[1] = lo + y * BM, tile_info[2] = hi;
+          tile_info[0] = e, tile_info[1] = lo + y * bm, tile_info[2] = hi;
           break;
         }
         y -= t;
@@ -336,7 +336,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
     expert = tile_info[0], m0 = tile_info[1], m_end = tile_info[2];
   }
   const int nkb = K / BK;
-  const bool two = m0 + 128 < m_end;  // the second 128-row tile holds real rows
+  const bool two = bm > 128 && m0 + 128 < m_end;  // the second 128-row tile holds real rows
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
@@ -556,9 +556,18 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
     if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
     attr_done = true;
   }
-  // grouped: at most ceil(M / BM) + E tiles (every expert can end with one partial tile)
-  dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM + (grp.offsets ? grp.E : 0));
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K);
+  // Token-tile height: 256 amortises the weight expansion best, but when the grid of 256-row tiles leaves
+  // the last wave of the 148 SMs mostly empty, 128-row tiles (twice as many CTAs) finish sooner.
+  const long long nt = (N + BN - 1) / BN;
+  auto waves_cost = [&](int bm_) {  // time in units of one 256-row tile
+    const long long ctas = nt * ((M + bm_ - 1) / bm_);
+    return (double)((ctas + 147) / 148) * (bm_ == 256 ? 1.0 : 0.85);
+  };
+  // (measured: a 128-row tile takes 0.85 of a 256-row tile, the weight expansion dominates)
+  const int bm = (!grp.offsets && waves_cost(128) < waves_cost(256)) ? 128 : 256;
+  // grouped: at most ceil(M / bm) + E tiles (every expert can end with one partial tile)
+  dim3 grid((unsigned)nt, (M + bm - 1) / bm + (grp.offsets ? grp.E : 0));
+  kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, bm);
   return launched("prefill (tcgen05)");
 }
 
