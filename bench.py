@@ -2,8 +2,10 @@
 """Benchmark of the quantized-weight matmul path: Llama-3-8B-shape decode at GGUF Q4_K_M.
 
 One step = one decode step's worth of quantized linears for M tokens: 32 layers x
-{q, k, v, o, gate, up as Q4_K; down as Q6_K} plus the Q6_K lm_head, 225 fused dequant-matmul
-launches reading 4.84 GB of block-quantized weights once.  Weights are random-init from a seed
+{q, k, v, o, gate, up as Q4_K; down as Q6_K} plus the Q6_K lm_head, 225 fused dequant-matmuls
+reading 4.84 GB of block-quantized weights once.  At M = 1 the q/k/v trio and the gate/up pair,
+which share their input row, go out as one launch each (matmul_q_multi: 129 launches per step);
+--launches single issues all 225 separately.  Weights are random-init from a seed
 (N(0, 0.02) before quantization) directly in HBM; activations are N(0, 1).
 
     python bench.py --gpus N --steps K --warmup W            # this library, rank-per-GPU
@@ -110,8 +112,15 @@ class ClockSampler:
 class Chain:
     """The quantized linears of one decode step on one GPU, each weight row-split over `world` ranks."""
 
-    def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0, share=None):
+    # Linears that share their input row and are issued as ONE launch at M = 1, as the reference's
+    # decode step does for BF16 weights (ops.LinearMulti for q/k/v, models/llama.go:1085; gate and
+    # up, models/llama.go:1300): keyed by the first member's name.
+    GROUPS = {"q": ("q", "k", "v"), "gate": ("gate", "up")}
+
+    def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0, share=None, fused=True):
         self.device, self.M, self.rank, self.world = device, M, rank, world
+        self.fused = fused and M == 1
+        self._multi = {}
         self.lin = []  # (name, N_local, N, K, dt, weight bytes tensor)
         if share is not None:  # same weights, another token count
             self.lin = share.lin
@@ -156,6 +165,33 @@ class Chain:
                                                   C.c_void_p(self.local[i].data_ptr()), self.M, nl, K, self.dev_index,
                                                   C.c_void_p(stream)))
 
+    def launch_multi(self, idx, stream):
+        """The linears idx (same x, same type) in one matmul_q_multi launch."""
+        key = idx[0]
+        if key not in self._multi:
+            n = len(idx)
+            self._multi[key] = ((C.c_void_p * n)(*[self.lin[i][5].data_ptr() for i in idx]),
+                                (C.c_void_p * n)(*[self.local[i].data_ptr() for i in idx]),
+                                (C.c_int32 * n)(*[self.lin[i][1] for i in idx]))
+        wp, op, nn = self._multi[key]
+        _, _, _, K, dt, _ = self.lin[key]
+        _lib.check(_lib.lib().light_b200_matmul_q_multi(dt, C.c_void_p(self.x[K].data_ptr()), wp, op, nn, len(idx), K,
+                                                        self.dev_index, C.c_void_p(stream)))
+
+    def plan(self, only=None):
+        """The launches of one step: lists of indices into self.lin, one list per launch."""
+        out, i = [], 0
+        while i < len(self.lin):
+            e = self.lin[i]
+            if only is not None and e[4] != only:
+                i += 1
+                continue
+            grp = self.GROUPS.get(e[0].split(".")[-1]) if self.fused else None
+            k = len(grp) if grp else 1
+            out.append(list(range(i, i + k)))
+            i += k
+        return out
+
     # Outputs the next operator needs in full on every rank (the rest stay row-local): the attention
     # output (q stands in for it here: k, v and the heads they feed are rank-local), o, the MLP
     # activation (gate stands in for silu(gate) * up), down, and the logits.
@@ -168,23 +204,25 @@ class Chain:
         n = 0
         if self.peer is not None and only is None:
             self.peer.step_begin()
-        for i, e in enumerate(self.lin):
-            if only is not None and e[4] != only:
-                continue
-            self.launch(i, st)
+        for idx in self.plan(only):
+            if len(idx) > 1:
+                self.launch_multi(idx, st)
+            else:
+                self.launch(idx[0], st)
             n += 1
-            if self.world > 1 and only is None and e[0].split(".")[-1] in self.GATHERED:
-                if self.peer is not None:
-                    self.peer.gather(self.gidx.index(i), self.local[i])
-                else:
-                    tp.all_gather_columns(self.local[i], self.out[i])
+            for i in idx:
+                if self.world > 1 and only is None and self.lin[i][0].split(".")[-1] in self.GATHERED:
+                    if self.peer is not None:
+                        self.peer.gather(self.gidx.index(i), self.local[i])
+                    else:
+                        tp.all_gather_columns(self.local[i], self.out[i])
         return n
 
     def bytes_per_step(self, only=None):
         return sum(algorithmic_bytes(e[1], e[3], e[4], self.M) for e in self.lin if only is None or e[4] == only)
 
     def launches(self, only=None):
-        return sum(1 for e in self.lin if only is None or e[4] == only)
+        return len(self.plan(only))
 
 
 def capture(fn, device):
@@ -255,6 +293,12 @@ def extras(chain, device, args):
     batched decode at the other token counts of configs[1], and the prefill matmuls of configs[2]."""
     out = {"decode_tokens_per_s": {}, "prefill_m2048": {}}
     steps = max(5, min(20, args.steps))
+    if chain.fused:  # the same step with one launch per linear
+        c = Chain(device, 1, share=chain, fused=False)
+        g = capture(c.step, device)
+        ms = timed(g.replay, steps, 3, device, lambda: None) / steps
+        out["decode_m1_one_launch_per_linear"] = {"launches": c.launches(), "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3)}
+        del g, c
     for M in (8, 32, 64):
         c = Chain(device, M, share=chain)
         g = capture(c.step, device)
@@ -292,6 +336,8 @@ def main():
     ap.add_argument("--impl", default="light_b200", choices=["light_b200", "reference"])
     ap.add_argument("--tokens", type=int, default=1, help="tokens per decode step (M)")
     ap.add_argument("--layers", type=int, default=LAYERS, help="decoder layers (default: the full 32)")
+    ap.add_argument("--launches", default="fused", choices=["fused", "single"],
+                    help="fused: q/k/v and gate/up of a layer as one launch each at M=1; single: one launch per linear")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the batched-decode and prefill side measurements")
     args = ap.parse_args()
@@ -301,7 +347,8 @@ def main():
     M = args.tokens
     metric, unit = "llama3_8b_q4_k_m_decode_tokens_per_s", "tok/s"
     workload = (f"configs[1]: Llama-3-8B-shape decoder at GGUF Q4_K_M, batched decode M={M}, the 225 quantized "
-                f"linears of one step (32 x [q,k,v,o,gate,up Q4_K; down Q6_K] + Q6_K lm_head), linear chain only")
+                f"linears of one step (32 x [q,k,v,o,gate,up Q4_K; down Q6_K] + Q6_K lm_head), linear chain only"
+                + ("; q,k,v and gate,up of a layer issued as one launch each" if args.launches == "fused" and M == 1 else ""))
 
     if args.impl == "reference":
         if rank != 0:
@@ -332,7 +379,7 @@ def main():
         barrier = lambda: None  # noqa: E731
     _lib.check(_lib.lib().light_b200_init(local))
 
-    chain = Chain(device, M, rank, world, layers=args.layers)
+    chain = Chain(device, M, rank, world, layers=args.layers, fused=args.launches == "fused")
     torch.cuda.synchronize(device)
     barrier()
     launches_per_step = chain.launches()
@@ -362,6 +409,7 @@ def main():
     roofline = {"bound": "hbm", "kernel": "q4k_gemv_mma_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_source": f"of {peak_kind}", "traffic": None,
                 "bytes_per_launch": b4, "us_per_launch": us4, "launches_per_step": n4,
+                "timed": "all Q4_K launches of a step in a graph of their own",
                 "q6k_gemv_gbs": gbs6, "q6k_launches_per_step": n6,
                 "whole_step_gbs": chain.bytes_per_step() / (ms_per_step * 1e-3) / 1e9}
 

@@ -101,6 +101,23 @@ LB200_API int light_b200_block_bytes(int ggml_type);
 LB200_API int light_b200_matmul_q(int ggml_type, const float *x, const void *w, float *out, int M, int N, int K, int device,
                         void *stream);
 
+/* Decode-time fused launches over quantized weights, the quantized twins of the reference's
+ * ops.LinearMulti / registry key gemv_multi (ops/gemv.go:21-78, kernels/cuda/gemv.go:15-94) and
+ * ops.GatedLinear / gemv_gated (ops/gemv.go:80-140), which the reference applies to the q/k/v trio
+ * and to gate/up (models/llama.go:1085,1300; gate models/fused_linear.go:16-47) but only for BF16
+ * weights.  x is ONE f32 activation row (K).
+ *
+ * matmul_q_multi:  out[i] (n[i]) f32 = x . dequant(w[i] (n[i],K))^T for i < count <= 4, all w of one
+ *   ggml type; one launch when a fused kernel applies, else one matmul per matrix.
+ * matmul_q_gated:  out (N) f32 = act(x . dequant(wg)^T) * (x . dequant(wu)^T), act 1 = SiLU,
+ *   2 = GELU (erf), the two products held in f32.  Needs the fused kernel (Q4_K, K a multiple of
+ *   256, N >= 16, 16-byte aligned weights); otherwise LB200_E_SHAPE / LB200_E_DTYPE and the caller
+ *   keeps its unfused sequence, as the reference does when gemv_gated does not apply. */
+LB200_API int light_b200_matmul_q_multi(int ggml_type, const float *x, const void *const *w, float *const *out,
+                                        const int32_t *n, int count, int K, int device, void *stream);
+LB200_API int light_b200_matmul_q_gated(int ggml_type, const float *x, const void *wg, const void *wu, float *out, int N,
+                                        int K, int act, int device, void *stream);
+
 /* The CUDA dequantize hook, quant.RegisterCUDADequant (reference quant/cuda_hook.go:13-46,
  * kernels/cuda/dequant.go:15-75):  dst f32 [n_elems] = dequant(src blocks).  n_elems must be a
  * whole number of blocks.  Bit-identical to the reference's CPU decoders. */

@@ -50,6 +50,10 @@ SYMBOLS = {
     "light_b200_block_bytes": (C.c_int, [C.c_int]),
     "light_b200_matmul_q": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
                                       C.c_void_p]),
+    "light_b200_matmul_q_multi": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                            C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_matmul_q_gated": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                            C.c_int, C.c_int, C.c_void_p]),
     "light_b200_dequant": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "light_b200_int4_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_int64, C.c_int, C.c_void_p]),

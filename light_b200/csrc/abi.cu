@@ -142,6 +142,54 @@ int light_b200_matmul_q(int t, const float *x, const void *w, float *out, int M,
   return gguf_matmul_generic(t, x, w, out, M, N, K, st);
 }
 
+int light_b200_matmul_q_multi(int t, const float *x, const void *const *w, float *const *out, const int32_t *n, int count,
+                              int K, int device, void *stream) {
+  const int be = block_elems(t);
+  if (!be) return fail(LB200_E_DTYPE, "light_b200: matmul_q_multi: ggml type %d has no fused kernel", t);
+  if (count < 1 || count > 4) return fail(LB200_E_SHAPE, "light_b200: matmul_q_multi: %d matrices, want 1..4", count);
+  if (K <= 0 || K % be) return fail(LB200_E_SHAPE, "light_b200: matmul_q_multi: K=%d not a multiple of the block size %d", K, be);
+  REQUIRE_PTR(x, "matmul_q_multi");
+  REQUIRE_PTR(w, "matmul_q_multi");
+  REQUIRE_PTR(out, "matmul_q_multi");
+  REQUIRE_PTR(n, "matmul_q_multi");
+  for (int i = 0; i < count; i++) {
+    if (n[i] <= 0) return fail(LB200_E_SHAPE, "light_b200: matmul_q_multi: matrix %d has %d rows", i, n[i]);
+    if (!w[i] || !out[i]) return fail(LB200_E_NULL, "light_b200: matmul_q_multi: null pointer for matrix %d", i);
+    if (!aligned(out[i], 4) || !aligned(w[i], 2))
+      return fail(LB200_E_ALIGN, "light_b200: matmul_q_multi: out must be 4-byte, w 2-byte aligned (matrix %d)", i);
+  }
+  if (!aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: matmul_q_multi: x must be 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  int took = gguf_gemv_multi(t, x, w, out, n, count, 0, K, st);
+  if (took != 0) return took == 1 ? 0 : took;
+  for (int i = 0; i < count; i++)
+    if (int rc = light_b200_matmul_q(t, x, w[i], out[i], 1, n[i], K, device, stream)) return rc;
+  return 0;
+}
+
+int light_b200_matmul_q_gated(int t, const float *x, const void *wg, const void *wu, float *out, int N, int K, int act,
+                              int device, void *stream) {
+  if (t != LB200_Q4_K) return fail(LB200_E_DTYPE, "light_b200: matmul_q_gated: ggml type %d has no gated kernel", t);
+  if (act != 1 && act != 2) return fail(LB200_E_SHAPE, "light_b200: matmul_q_gated: act %d, want 1 (SiLU) or 2 (GELU)", act);
+  if (N < 16 || K <= 0 || K % 256)
+    return fail(LB200_E_SHAPE, "light_b200: matmul_q_gated: N=%d K=%d (N >= 16, K a multiple of 256)", N, K);
+  REQUIRE_PTR(x, "matmul_q_gated");
+  REQUIRE_PTR(wg, "matmul_q_gated");
+  REQUIRE_PTR(wu, "matmul_q_gated");
+  REQUIRE_PTR(out, "matmul_q_gated");
+  if (!aligned(x, 16) || !aligned(out, 4) || !aligned(wg, 16) || !aligned(wu, 16))
+    return fail(LB200_E_ALIGN, "light_b200: matmul_q_gated: x, wg, wu must be 16-byte, out 4-byte aligned");
+  if (int rc = bind(device)) return rc;
+  const void *w[2] = {wg, wu};
+  float *o[2] = {out, out};
+  const int n[2] = {N, N};
+  const int took = gguf_gemv_multi(t, x, w, o, n, 2, act, K, (cudaStream_t)stream);
+  if (took == 1) return 0;
+  if (took == 0) return fail(LB200_E_SHAPE, "light_b200: matmul_q_gated: K=%d is too long for the fused kernel", K);
+  return took;
+}
+
 int light_b200_dequant(int t, const void *src, float *dst, int64_t n, int device, void *stream) {
   const int be = block_elems(t);
   if (!be) return fail(LB200_E_DTYPE, "light_b200: dequant: ggml type %d has no kernel", t);

@@ -152,115 +152,222 @@ __device__ __forceinline__ void q4k_scales(const uint4 &h, bool hi, int sh, floa
   dmn[1] = df.y * (float)((m2 >> 8) & 0xFFu);
 }
 
-__global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_mma_kernel(const float *__restrict__ x,
-                                                                    const uint8_t *__restrict__ w,
-                                                                    float *__restrict__ out, int N, int K, int RT) {
-  using S = Slab<32>;
-  __shared__ __align__(16) unsigned char slabs[WARPS][S::BYTES];
-  __shared__ __align__(16) unsigned char zero[S::ZERO_BYTES];
-  __shared__ __align__(16) float2 red[WARPS * MAX_RT * 32];
+
+// Up to four weight matrices that share one activation row and one K, served by ONE launch: the
+// row tiles of all of them form one list, which the CTAs split evenly.  With act != 0 there are
+// two matrices of equal height (gate, up), their tiles alternate in the list, and the launch
+// stores act(gate . x) * (up . x) into out[0].
+struct MultiArgs {
+  const uint8_t *w[4];
+  float *out[4];
+  int n[4];     // rows of each matrix (>= 16)
+  int tend[4];  // running total of row tiles (not used when act != 0)
+  int count;
+  int act;      // 0: plain outputs, 1: SiLU gate, 2: GELU (erf) gate
+};
+
+// Which matrix and which first row tile T of the list stands for.  A tile that would run past the
+// last row is pulled back to n - 16: it recomputes rows of the tile before it, and the duplicate
+// stores write identical values.
+__device__ __forceinline__ void resolve_tile(const MultiArgs &a, int T, int &j, int &r0) {
+  if (a.act) {
+    j = T & 1;
+    r0 = min((T >> 1) * ROWS, a.n[0] - ROWS);
+    return;
+  }
+  j = 0;
+  int base = 0;
+#pragma unroll
+  for (int i = 1; i < 4; i++)
+    if (i < a.count && T >= a.tend[i - 1]) j = i, base = a.tend[i - 1];
+  r0 = min((T - base) * ROWS, a.n[j] - ROWS);
+}
+
+__device__ __forceinline__ float gate_act(float v, int act) {
+  return act == 1 ? v / (1.f + expf(-v)) : 0.5f * v * (1.f + erff(v * 0.70710678118654752f));
+}
+
+constexpr int Q4K_TILE_BYTES = ROWS * 144;  // one K block of 16 rows, dense in shared memory
+constexpr int GROUP = 4;                    // row tiles whose partial sums a CTA holds at a time
+constexpr int Q4K_SLAB = Slab<32>::BYTES + 16;  // a block's activations + its prescale factor
+
+// One CTA per SM slot walks a contiguous range of row tiles (a balanced share of N/16), GROUP tiles
+// at a time; its warps take the K blocks round-robin and meet once per group to add up their parts.
+//
+// The packed tiles travel global -> shared with 16-byte asynchronous copies into a ring of S tiles
+// per warp, requested S tiles ahead of their use: the bytes in flight per SM (what hides the DRAM
+// latency) are set by the ring, not by registers, and the ring keeps filling across group
+// boundaries.  Each of the 144 chunks of a tile is fetched once (lane l takes chunks l, l+32, ...).
+// Row r of a tile sits at r*144 in its slot: 16-byte reads of lanes (g, t) at g*144 + 16 + 32t fall
+// into distinct banks.
+//
+// The grid never exceeds the SM count and a CTA takes less than half of an SM, so under
+// programmatic dependent launch the NEXT launch of the stream is resident beside this one: its
+// rings fill with its own weights (requested before griddepcontrol.wait) while this launch
+// computes, and HBM stays busy through the dependency bubble between two launches.
+//
+// All activations are converted once per CTA (warp w converts the blocks it will use), so the
+// tile loop holds no activation traffic at all.
+template <int S, int MINB>
+__global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const float *__restrict__ x,
+                                                                       const __grid_constant__ MultiArgs a,
+                                                                       int tiles, int K) {
+  using SL = Slab<32>;
+  extern __shared__ __align__(16) unsigned char dyn[];  // [ring: WARPS x S tiles][slabs: K/256]
+  __shared__ __align__(16) unsigned char zero[SL::ZERO_BYTES];
+  __shared__ __align__(16) float2 red[2][WARPS * GROUP * 32];  // by group parity
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int nb = K >> 8;
-  const int n0 = blockIdx.x * (ROWS * RT);
-  const uint32_t row_u4 = (uint32_t)nb * 9;
-  const uint4 *w4 = reinterpret_cast<const uint4 *>(w);
-  for (int i = threadIdx.x; i < S::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-  for (int i = lane; i < MAX_RT * 32; i += 32) red[warp * MAX_RT * 32 + i] = make_float2(0.f, 0.f);
+  const uint32_t row_bytes = (uint32_t)nb * 144u;
+  for (int i = threadIdx.x; i < SL::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
+  for (int i = threadIdx.x; i < 2 * WARPS * GROUP * 32; i += WARPS * 32) (&red[0][0])[i] = make_float2(0.f, 0.f);
 
-  const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + warp * (S * Q4K_TILE_BYTES);
+  const uint32_t slabs = (uint32_t)__cvta_generic_to_shared(dyn) + WARPS * S * Q4K_TILE_BYTES;
   const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
-  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(red + warp * MAX_RT * 32 + lane);
-  // B addresses.  The even MMA works on sub-block 2t of A-lane t: its column 2t carries the hi
-  // half of x and the otherwise unused column 2t+1 the lo half, so one MMA does both.  The odd MMA
-  // (sub-block 2t+1) has hi in column 2t+1 and lo in column 2t.  Every other column reads zeros.
+  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(&red[0][warp * GROUP * 32 + lane]);
+  constexpr uint32_t RED_PARITY = WARPS * GROUP * 32 * 8;
+  // B addresses inside a slab.  The even MMA works on sub-block 2t of A-lane t: its column 2t
+  // carries the hi half of x and the otherwise unused column 2t+1 the lo half, so one MMA does
+  // both.  The odd MMA (sub-block 2t+1) has hi in column 2t+1 and lo in column 2t.  Every other
+  // column reads zeros.
   const bool mine = (g >> 1) == t;
-  const uint32_t pe = mine ? slab + (2 * t) * S::SUB_BYTES + ((g & 1) ? S::LO_OFF : 0) : szero;
-  const uint32_t po = mine ? slab + (2 * t + 1) * S::SUB_BYTES + ((g & 1) ? 0 : S::LO_OFF) : szero;
+  const uint32_t pe_off = (2 * t) * SL::SUB_BYTES + ((g & 1) ? SL::LO_OFF : 0);
+  const uint32_t po_off = (2 * t + 1) * SL::SUB_BYTES + ((g & 1) ? 0 : SL::LO_OFF);
   const bool hdr_hi = t >= 2;
   const int hdr_sh = (t & 1) * 16;
-  const int last = N - 1;
   const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
 
-  // Units of work of this warp, in order: (its K blocks) x (the CTA's RT row tiles).  The packed
-  // weights of unit u+1 are requested before unit u is computed (two register sets, alternating),
-  // and the first unit's before griddepcontrol.wait, so loads of the next tile -- and of the next
-  // launch -- are in flight while this one computes.
-  const int nbw = warp < nb ? (nb - warp + WARPS - 1) / WARPS : 0;
-  const int rt_shift = RT == 4 ? 2 : RT == 2 ? 1 : 0;
-  const int U = nbw << rt_shift;
-  bool first = true;
-  float up = 1.f;
-  float2 sx = make_float2(0.f, 0.f);
+  // this CTA's share [t0, t1) of the tile list (whole gate/up pairs when act != 0)
+  const int unit = a.act ? 2 : 1, lt = tiles / unit;
+  const int t0 = (int)(((long long)lt * blockIdx.x) / gridDim.x) * unit,
+            t1 = (int)(((long long)lt * (blockIdx.x + 1)) / gridDim.x) * unit;
 
-  auto issue = [&](Q4KTile &T, int u) {
-    const int b = warp + (u >> rt_shift) * WARPS, rt = u & (RT - 1);
-    const int rg = min(n0 + rt * ROWS + g, last), rg8 = min(n0 + rt * ROWS + g + 8, last);
-    const uint4 *pg = w4 + (size_t)((uint32_t)rg * row_u4 + (uint32_t)b * 9u);
-    const uint4 *pg8 = w4 + (size_t)((uint32_t)rg8 * row_u4 + (uint32_t)b * 9u);
-    T.h0 = __ldg(pg), T.h1 = __ldg(pg8);
-    T.qa0 = __ldg(pg + 1 + 2 * t), T.qa1 = __ldg(pg + 2 + 2 * t);
-    T.qb0 = __ldg(pg8 + 1 + 2 * t), T.qb1 = __ldg(pg8 + 2 + 2 * t);
-  };
-  auto process = [&](const Q4KTile &T, int u) {
-    const int b = warp + (u >> rt_shift) * WARPS, rt = u & (RT - 1);
-    if (rt == 0) {
-      if (first) {
-        pdl_wait();  // x is the previous launch's output; the weights requested above are not
-        __syncthreads();
-        first = false;
+  // source offsets of this lane's chunks, relative to the tile's first byte (row 0, this block)
+  uint32_t soff[5];
+#pragma unroll
+  for (int i = 0; i < 5; i++) {
+    const uint32_t c = lane + 32 * i, row = c / 9u;
+    soff[i] = row * row_bytes + (c - 9u * row) * 16u;
+  }
+  const uint32_t ld_off = g * 144u + 32u * t;
+  // The requests run S units ahead of the arithmetic; both walk (group, block, tile) in this order.
+  int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_gt < t1 && warp < nb) {
+      int j, r0;
+      resolve_tile(a, i_gt + i_rt, j, r0);
+      const uint8_t *base = a.w[j] + ((size_t)r0 * row_bytes + (uint32_t)i_b * 144u);
+      const uint32_t dst = ring + i_slot * Q4K_TILE_BYTES + lane * 16;
+#pragma unroll
+      for (int i = 0; i < 4; i++) cp_async16(dst + i * 512, base + soff[i]);
+      if (lane < 16) cp_async16(dst + 2048, base + soff[4]);
+      i_slot = (i_slot + 1) & (S - 1);
+      if (++i_rt == i_gs) {
+        i_rt = 0, i_b += WARPS;
+        if (i_b >= nb) i_b = warp, i_gt += i_gs, i_gs = min(GROUP, t1 - i_gt);
       }
-      float4 xv[2];
-      xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
-      xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
-      __syncwarp();  // every lane is done reading the previous block's slab
-      up = stage_block<32>(xv, slab, lane);
-      __syncwarp();
-      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + S::SX_OFF + 8 * t));
     }
-    float dsc[2][2], dmn[2][2];
-    q4k_scales(T.h0, hdr_hi, hdr_sh, dsc[0], dmn[0]);
-    q4k_scales(T.h1, hdr_hi, hdr_sh, dsc[1], dmn[1]);
-    float de[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};  // even / odd sub-block chains
-    const uint32_t qg[8] = {T.qa0.x, T.qa0.y, T.qa0.z, T.qa0.w, T.qa1.x, T.qa1.y, T.qa1.z, T.qa1.w};
-    const uint32_t qh[8] = {T.qb0.x, T.qb0.y, T.qb0.z, T.qb0.w, T.qb1.x, T.qb1.y, T.qb1.z, T.qb1.w};
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const uint32_t vg = qg[i], vh = qh[i];
-      const uint32_t e0 = and_or(vg << 4, mask, magic), e1 = and_or(vh << 4, mask, magic);
-      const uint32_t e2 = and_or(vg >> 4, mask, magic), e3 = and_or(vh >> 4, mask, magic);
-      const uint32_t o0 = and_or(vg, mask, magic), o1 = and_or(vh, mask, magic);
-      const uint32_t o2 = and_or(vg >> 8, mask, magic), o3 = and_or(vh >> 8, mask, magic);
-      const uint2 be = lds64(pe + i * 8), bo = lds64(po + i * 8);
-      mma16816(de, e0, e1, e2, e3, be.x, be.y);
-      mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
-    }
-    // lane (g, t): de[0] + de[1] = row g, sub-block 2t (hi + lo parts of x); dq[0] + dq[1] = row g,
-    // sub-block 2t+1; [2], [3] the same for row g+8.
-    float vr[2];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-      float v = dsc[r][0] * (de[2 * r] + de[2 * r + 1]) - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
-      v += dsc[r][1] * (dq[2 * r] + dq[2 * r + 1]) - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
-      vr[r] = v * up;
-    }
-    tile_accumulate(vr[0], vr[1], red_lane, rt);
+    cp_async_commit();
   };
-
-  Q4KTile ta, tb;
-  if (U > 0) issue(ta, 0);
-  for (int u = 0; u < U; u += 2) {
-    if (u + 1 < U) issue(tb, u + 1);
-    process(ta, u);
-    if (u + 1 >= U) break;
-    if (u + 2 < U) issue(ta, u + 2);
-    process(tb, u + 1);
+#pragma unroll
+  for (int p = 0; p < S; p++) issue();
+  pdl_wait();  // x is the previous launch's output; the weights requested above are not
+  for (int b = warp; b < nb; b += WARPS) {
+    float4 xv[2];
+    xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+    xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+    const uint32_t slab = slabs + b * Q4K_SLAB;
+    const float up = stage_block<32>(xv, slab, lane);
+    if (lane == 0) asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(slab + SL::BYTES), "f"(up));
   }
-  if (first) {  // a warp without a K block still joins the CTA's barriers
-    pdl_wait();
-    __syncthreads();
+  __syncthreads();
+  int slot = 0, parity = 0;
+  for (int gt = t0; gt < t1; gt += GROUP, parity ^= 1) {
+    const int gs = min(GROUP, t1 - gt);
+    const uint32_t red_g = red_lane + parity * RED_PARITY;
+    for (int b = warp; b < nb; b += WARPS) {
+      const uint32_t slab = slabs + b * Q4K_SLAB;
+      const uint32_t pe = mine ? slab + pe_off : szero, po = mine ? slab + po_off : szero;
+      float2 sx;
+      float up;
+      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + SL::SX_OFF + 8 * t));
+      asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(up) : "r"(slab + SL::BYTES));
+      for (int rt = 0; rt < gs; rt++) {
+        cp_async_wait<S - 1>();  // this lane's chunks of the tile have landed ...
+        __syncwarp();            // ... and so have the other lanes'
+        const uint32_t sb = ring + slot * Q4K_TILE_BYTES + ld_off;
+        slot = (slot + 1) & (S - 1);
+        const uint4 h0 = lds128(sb - 32u * t), h1 = lds128(sb - 32u * t + 8 * 144);
+        const uint4 qa0 = lds128(sb + 16), qa1 = lds128(sb + 32);
+        const uint4 qb0 = lds128(sb + 8 * 144 + 16), qb1 = lds128(sb + 8 * 144 + 32);
+        __syncwarp();  // the slot is free again
+        issue();
+        float dsc[2][2], dmn[2][2];
+        q4k_scales(h0, hdr_hi, hdr_sh, dsc[0], dmn[0]);
+        q4k_scales(h1, hdr_hi, hdr_sh, dsc[1], dmn[1]);
+        float de[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};  // even / odd sub-block chains
+        const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+        const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const uint32_t vg = qg[i], vh = qh[i];
+          const uint32_t e0 = and_or(vg << 4, mask, magic), e1 = and_or(vh << 4, mask, magic);
+          const uint32_t e2 = and_or(vg >> 4, mask, magic), e3 = and_or(vh >> 4, mask, magic);
+          const uint32_t o0 = and_or(vg, mask, magic), o1 = and_or(vh, mask, magic);
+          const uint32_t o2 = and_or(vg >> 8, mask, magic), o3 = and_or(vh >> 8, mask, magic);
+          const uint2 be = lds64(pe + i * 8), bo = lds64(po + i * 8);
+          mma16816(de, e0, e1, e2, e3, be.x, be.y);
+          mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
+        }
+        // lane (g, t): de[0] + de[1] = row g, sub-block 2t (hi + lo parts of x); dq[0] + dq[1] =
+        // row g, sub-block 2t+1; [2], [3] the same for row g+8.
+        float vr[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          float v = dsc[r][0] * (de[2 * r] + de[2 * r + 1]) - (64.f * dsc[r][0] + dmn[r][0]) * sx.x;
+          v += dsc[r][1] * (dq[2 * r] + dq[2 * r + 1]) - (64.f * dsc[r][1] + dmn[r][1]) * sx.y;
+          vr[r] = v * up;
+        }
+        // the warp's first block of a group overwrites what an earlier group left behind
+        const uint32_t ra = red_g + rt * (32 * 8);
+        float2 o = make_float2(0.f, 0.f);
+        if (b != warp) asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(o.x), "=f"(o.y) : "r"(ra));
+        asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(ra), "f"(o.x + vr[0]), "f"(o.y + vr[1]));
+      }
+    }
+    // red[parity][warp][rt][lane] (float2: rows g, g+8): sum the four t-lanes of a row and the
+    // warps in a fixed order.
+    __syncthreads();  // also orders this group's reads of red[parity] before its reuse two groups on
+    auto row_sum = [&](int rt, int row) {
+      const int gg = row & 7, hi = row >> 3;
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) {
+        const float2 *p = &red[parity][(wq * GROUP + rt) * 32 + gg * 4];
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;
+      }
+      return v;
+    };
+    if (a.act) {
+      for (int i = threadIdx.x; i < (gs >> 1) * ROWS; i += WARPS * 32) {
+        const int pr = i >> 4, row = i & 15;
+        int j, r0;
+        resolve_tile(a, gt + 2 * pr, j, r0);
+        a.out[0][r0 + row] = gate_act(row_sum(2 * pr, row), a.act) * row_sum(2 * pr + 1, row);
+      }
+    } else {
+      for (int i = threadIdx.x; i < gs * ROWS; i += WARPS * 32) {
+        const int rt = i >> 4, row = i & 15;
+        int j, r0;
+        resolve_tile(a, gt + rt, j, r0);
+        a.out[j][r0 + row] = row_sum(rt, row);
+      }
+    }
   }
-  reduce_store(red, out, n0, N, RT);
+  cp_async_wait<0>();
 }
 
 // ------------------------------------------------------------------------------------ Q6_K
@@ -424,11 +531,11 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
 }
 
 template <typename... Args>
-int launch_pdl(void (*kern)(Args...), unsigned grid, cudaStream_t st, Args... args) {
+int launch_pdl(void (*kern)(Args...), unsigned grid, size_t dyn_smem, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(WARPS * 32);
-  cfg.dynamicSmemBytes = 0;
+  cfg.dynamicSmemBytes = dyn_smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -440,8 +547,8 @@ int launch_pdl(void (*kern)(Args...), unsigned grid, cudaStream_t st, Args... ar
   return 0;
 }
 
-// Row tiles per CTA: enough CTAs to fill the 148 SMs a few times over, as many tiles as that
-// allows (each tile reuses the block's converted activations).
+// Row tiles per CTA of the Q6_K kernel: enough CTAs to fill the SMs a few times over, as many
+// tiles as that allows (each tile reuses the block's converted activations).
 int g_rt_override = 0;  // LIGHT_B200_GEMV_RT: tuning knob, 0 = choose by shape
 int pick_rt(int N) {
   if (g_rt_override > 0) return g_rt_override >= 4 ? 4 : g_rt_override >= 2 ? 2 : 1;
@@ -451,35 +558,77 @@ int pick_rt(int N) {
   return 1;
 }
 
+int g_sms = 148;       // SMs of the bound device
+int g_waves = 2;       // LIGHT_B200_GEMV_WAVES: CTAs per SM of the persistent kernels' grids (1 or 2)
+int g_q4k_stages = 4;  // LIGHT_B200_Q4K_STAGES: ring depth (2 or 4)
+constexpr size_t MAX_DYN_SMEM = 96 * 1024;  // keeps two launches resident per SM
+
 }  // namespace
 
-int gguf_gemv_fast_init(int) {
+int gguf_gemv_fast_init(int device) {
   if (const char *e = getenv("LIGHT_B200_GEMV_RT")) g_rt_override = atoi(e);
+  if (const char *e = getenv("LIGHT_B200_GEMV_WAVES")) g_waves = atoi(e) == 1 ? 1 : 2;
+  if (const char *e = getenv("LIGHT_B200_Q4K_STAGES")) g_q4k_stages = atoi(e) == 2 ? 2 : 4;
+  cudaError_t err = cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, device);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+  if (err != cudaSuccess) return fail((int)err, "light_b200: init (decode): %s", cudaGetErrorString(err));
   return 0;
 }
 
+// One launch over up to four Q4_K matrices that share x (M = 1).  Returns 1 if launched, 0 if this
+// path does not apply, < 0 or a CUDA code on error.
+static int q4k_launch(const float *x, const MultiArgs &a, int tiles, int K, cudaStream_t st) {
+  const size_t dyn = (size_t)WARPS * g_q4k_stages * Q4K_TILE_BYTES + (size_t)(K >> 8) * Q4K_SLAB;
+  if (dyn > MAX_DYN_SMEM) return 0;  // very long rows: the activations do not fit beside the rings
+  const int lt = a.act ? tiles / 2 : tiles;
+  const unsigned grid = (unsigned)(lt < g_sms * g_waves ? lt : g_sms * g_waves);
+  int rc = g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 2>, grid, dyn, st, x, a, tiles, K)
+                             : launch_pdl(q4k_gemv_mma_kernel<4, 2>, grid, dyn, st, x, a, tiles, K);
+  if (rc) return rc;
+  rc = launched("matmul_q (decode)");
+  return rc ? rc : 1;
+}
+
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
-  if (M != 1 || K % 256) return 0;
+  if (M != 1 || K % 256 || N < ROWS) return 0;
   if (type != LB200_Q4_K && type != LB200_Q6_K) return 0;
   if (type == LB200_Q4_K && ((uintptr_t)w & 15)) return 0;
   // Q6_K rows must start 4-byte aligned for the aligned-word loads: (K/256)*210 % 4 == 0
   if (type == LB200_Q6_K && (((uintptr_t)w & 3) || ((size_t)(K >> 8) * 210) % 4)) return 0;
+  const uint8_t *wb = (const uint8_t *)w;
+  const int tiles = (N + ROWS - 1) / ROWS;
+  if (type == LB200_Q4_K) {
+    MultiArgs a = {};
+    a.w[0] = wb, a.out[0] = out, a.n[0] = N, a.tend[0] = tiles, a.count = 1;
+    return q4k_launch(x, a, tiles, K, st);
+  }
   const int rt = pick_rt(N);
   const unsigned grid = (unsigned)((N + ROWS * rt - 1) / (ROWS * rt));
-  const uint8_t *wb = (const uint8_t *)w;
-  for (int m = 0; m < M; m++) {  // one launch per activation row: the weights of a decode-sized
-    const float *xm = x + (size_t)m * K;  // matrix stay in the 126 MB L2 between the launches
-    float *om = out + (size_t)m * N;
-    int rc;
-    if (type == LB200_Q4_K)
-      rc = launch_pdl(q4k_gemv_mma_kernel, grid, st, xm, wb, om, N, K, rt);
-    else
-      rc = launch_pdl(q6k_gemv_mma_kernel, grid, st, xm, wb, om, N, K, rt);
-    if (rc) return rc;
-    rc = launched("matmul_q (decode)");
-    if (rc) return rc;
+  int rc = launch_pdl(q6k_gemv_mma_kernel, grid, (size_t)0, st, x, wb, out, N, K, rt);
+  if (rc) return rc;
+  rc = launched("matmul_q (decode)");
+  return rc ? rc : 1;
+}
+
+// Several matrices of one type against one activation row in one launch (act == 0), or the gated
+// pair act(w[0] x) * (w[1] x) -> out[0] (act 1 = SiLU, 2 = GELU).  Returns 1 if launched, 0 if no
+// single-launch kernel applies (the caller then issues one matmul per matrix), else an error.
+int gguf_gemv_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int act,
+                    int K, cudaStream_t st) {
+  if (type != LB200_Q4_K || K % 256 || count < 1 || count > 4) return 0;
+  if (act && (count != 2 || n[0] != n[1])) return 0;
+  MultiArgs a = {};
+  int tiles = 0;
+  for (int i = 0; i < count; i++) {
+    if (n[i] < ROWS || ((uintptr_t)w[i] & 15)) return 0;
+    tiles += (n[i] + ROWS - 1) / ROWS;
+    a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
   }
-  return 1;
+  a.count = count, a.act = act;
+  return q4k_launch(x, a, tiles, K, st);
 }
 
 }  // namespace lb

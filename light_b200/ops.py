@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -143,6 +143,57 @@ def MatMulQ(x: torch.Tensor, w: QTensor) -> torch.Tensor:
     out = torch.empty((M, N), dtype=torch.float32, device=x.device)
     _lib.check(_lib.lib().light_b200_matmul_q(w.ggml_type, _ptr(xc), _ptr(w.data), _ptr(out), M, N, K, dev,
                                               _stream(dev)))
+    return out
+
+
+def _one_row(x: torch.Tensor, op: str) -> int:
+    if x.dtype != torch.float32:
+        raise ValueError(f"{op}: x must be F32, got {x.dtype}")
+    K = x.shape[-1]
+    if x.numel() != K:
+        raise ValueError(f"{op}: x must be one row, got {tuple(x.shape)}")
+    return K
+
+
+def MatMulQMulti(x: torch.Tensor, ws: Sequence[QTensor], outs: Optional[Sequence[torch.Tensor]] = None) -> list:
+    """The quantized twin of ops.LinearMulti (ops/gemv.go:21-78): one f32 activation row against up to
+    four quantized weights of one type that share K (the q/k/v trio, gate and up), in one launch.
+    Returns one (..., N_i) f32 tensor per weight (written into `outs` when given)."""
+    if not 1 <= len(ws) <= 4:
+        raise ValueError(f"MatMulQMulti: {len(ws)} weights, want 1..4")
+    K = _one_row(x, "MatMulQMulti")
+    for i, w in enumerate(ws):
+        if len(w.shape) != 2 or w.shape[1] != K or w.ggml_type != ws[0].ggml_type or w.device != x.device:
+            raise ValueError(f"MatMulQMulti: weight {i} must be (N, {K}) of type {ws[0].ggml_type} on {x.device}")
+    dev = _dev(x, "MatMulQMulti")
+    xc = x.contiguous()
+    lead = tuple(x.shape[:-1])
+    if outs is None:
+        outs = [torch.empty(lead + (w.shape[0],), dtype=torch.float32, device=x.device) for w in ws]
+    n = len(ws)
+    wp = (C.c_void_p * n)(*[w.data.data_ptr() for w in ws])
+    op = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    nn = (C.c_int32 * n)(*[w.shape[0] for w in ws])
+    _lib.check(_lib.lib().light_b200_matmul_q_multi(ws[0].ggml_type, _ptr(xc), wp, op, nn, n, K, dev, _stream(dev)))
+    return list(outs)
+
+
+def MatMulQGated(x: torch.Tensor, wg: QTensor, wu: QTensor, gelu: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The quantized twin of ops.GatedLinear (ops/gemv.go:80-140): act(x . wg^T) * (x . wu^T) for one
+    f32 activation row, act = SiLU or (gelu) GELU-erf, in one launch.  Raises when the fused kernel
+    does not apply; the caller then runs MatMulQ twice and the activation itself, as the reference
+    does without gemv_gated."""
+    K = _one_row(x, "MatMulQGated")
+    for w in (wg, wu):
+        if len(w.shape) != 2 or w.shape[1] != K or w.shape[0] != wg.shape[0] or w.ggml_type != wg.ggml_type or w.device != x.device:
+            raise ValueError(f"MatMulQGated: weights must be (N, {K}) of one type on {x.device}")
+    dev = _dev(x, "MatMulQGated")
+    xc = x.contiguous()
+    N = wg.shape[0]
+    if out is None:
+        out = torch.empty(tuple(x.shape[:-1]) + (N,), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().light_b200_matmul_q_gated(wg.ggml_type, _ptr(xc), _ptr(wg.data), _ptr(wu.data), _ptr(out), N, K,
+                                                    2 if gelu else 1, dev, _stream(dev)))
     return out
 
 

@@ -1,0 +1,92 @@
+"""GPU parity of the fused decode launches over quantized weights (matmul_q_multi, matmul_q_gated),
+the quantized twins of the reference's ops.LinearMulti / ops.GatedLinear (ops/gemv.go:21-140).
+The reference tests those against separate Linear calls (ops/gemv_test.go); here the bar is the same
+plus the f64 oracle: a fused launch must return what one MatMulQ per weight returns."""
+import ctypes as C
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import rel_l2
+from light_b200 import _lib, ops, synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _qt(raw, dt, shape, dev):
+    t = raw if isinstance(raw, torch.Tensor) else torch.from_numpy(raw)
+    return ops.QTensor(t.reshape(-1).to(dev), dt, shape)
+
+
+def _deq(oracle, dt, raw, N, K):
+    r = raw.numpy() if isinstance(raw, torch.Tensor) else raw
+    return oracle.dequant(dt, r.reshape(-1), N * K).reshape(N, K).astype(np.float64)
+
+
+@pytest.mark.parametrize("Ns,K", [((4096, 1024, 1024), 4096), ((16, 17, 4097, 33), 1024), ((48,), 256), ((1000, 24), 2048)])
+def test_multi_matches_single_and_oracle(cuda, oracle, Ns, K):
+    """q/k/v-shaped trio and ragged heights (tiles that are pulled back to the last 16 rows, one K
+    block only, four weights): bit-identical to one MatMulQ per weight, <= 1e-5 rel-L2 vs f64."""
+    dt = ops.Q4_K
+    raws = [synth.random_blocks(500 + i, dt, N, K) for i, N in enumerate(Ns)]
+    ws = [_qt(r, dt, (N, K), cuda) for r, N in zip(raws, Ns)]
+    x = torch.randn(1, K, generator=torch.Generator().manual_seed(9))
+    outs = ops.MatMulQMulti(x.to(cuda), ws)
+    for o, w, r, N in zip(outs, ws, raws, Ns):
+        single = ops.MatMulQ(x.to(cuda), w)
+        assert o.shape == (1, N)
+        assert torch.equal(o, single)
+        want = x.numpy().astype(np.float64) @ _deq(oracle, dt, r, N, K).T
+        assert rel_l2(o.cpu().numpy(), want) <= 1e-5
+
+
+def test_multi_falls_back_for_other_types(cuda, oracle):
+    """Types without a fused multi kernel are served by one matmul per weight, same results."""
+    K = 1024
+    for dt in (ops.Q8_0, ops.Q6_K):
+        raws = [synth.random_blocks(520 + i, dt, N, K) for i, N in enumerate((40, 24))]
+        ws = [_qt(r, dt, (N, K), cuda) for r, N in zip(raws, (40, 24))]
+        x = torch.randn(K, generator=torch.Generator().manual_seed(10))
+        outs = ops.MatMulQMulti(x.to(cuda), ws)
+        for o, w in zip(outs, ws):
+            assert o.shape == (w.shape[0],)
+            assert torch.equal(o.reshape(1, -1), ops.MatMulQ(x.reshape(1, K).to(cuda), w))
+
+
+@pytest.mark.parametrize("N,K,gelu", [(14336, 4096, False), (40, 512, False), (1000, 1024, True)])
+def test_gated_matches_unfused_and_oracle(cuda, oracle, N, K, gelu):
+    """act(gate . x) * (up . x) with Gaussian Q4_K weights (the gate/up shape of the decoder) and
+    ragged heights; vs the unfused sequence on the GPU and vs f64."""
+    dt = ops.Q4_K
+    rg, ru = synth.gaussian_weight(61, dt, N, K), synth.gaussian_weight(62, dt, N, K)
+    wg, wu = _qt(rg, dt, (N, K), cuda), _qt(ru, dt, (N, K), cuda)
+    x = torch.randn(1, K, generator=torch.Generator().manual_seed(11))
+    got = ops.MatMulQGated(x.to(cuda), wg, wu, gelu=gelu)
+    g, u = ops.MatMulQ(x.to(cuda), wg), ops.MatMulQ(x.to(cuda), wu)
+    act = torch.nn.functional.gelu(g) if gelu else torch.nn.functional.silu(g)
+    assert rel_l2(got.cpu().numpy(), (act * u).cpu().numpy()) <= 1e-6
+    g64 = x.numpy().astype(np.float64) @ _deq(oracle, dt, rg, N, K).T
+    u64 = x.numpy().astype(np.float64) @ _deq(oracle, dt, ru, N, K).T
+    a64 = 0.5 * g64 * (1 + np.vectorize(math.erf)(g64 / math.sqrt(2))) if gelu else g64 / (1 + np.exp(-g64))
+    assert rel_l2(got.cpu().numpy(), a64 * u64) <= 1e-5
+
+
+def test_multi_and_gated_errors(cuda):
+    L = _lib.lib()
+    K = 512
+    raw = synth.random_blocks(70, ops.Q4_K, 32, K)
+    w = _qt(raw, ops.Q4_K, (32, K), cuda)
+    x = torch.randn(1, K, device=cuda)
+    with pytest.raises(ValueError):
+        ops.MatMulQMulti(x, [w] * 5)
+    with pytest.raises(ValueError):
+        ops.MatMulQMulti(torch.randn(2, K, device=cuda), [w])
+    w6 = _qt(synth.random_blocks(71, ops.Q6_K, 32, K), ops.Q6_K, (32, K), cuda)
+    with pytest.raises(ops.Light200Error):
+        ops.MatMulQGated(x, w6, w6)
+    out = torch.empty(32, device=cuda)
+    rc = L.light_b200_matmul_q_gated(ops.Q4_K, C.c_void_p(x.data_ptr()), C.c_void_p(w.data.data_ptr()),
+                                     C.c_void_p(w.data.data_ptr()), C.c_void_p(out.data_ptr()), 32, K, 3, 0, None)
+    assert rc != 0
