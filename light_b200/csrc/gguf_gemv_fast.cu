@@ -26,6 +26,7 @@
 // requested before griddepcontrol.wait, so the head of each launch overlaps the tail of the one
 // before it in the stream -- a decode step is a chain of a few hundred such launches.
 #include <cstdlib>
+#include <type_traits>
 
 #include "common.cuh"
 #include "mma_sync.cuh"
@@ -89,37 +90,6 @@ __device__ __forceinline__ float stage_block(const float4 (&xv)[2], uint32_t sla
       asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(slab + S::SX_OFF + (e / SUB) * 4), "f"(s));
   }
   return up;
-}
-
-constexpr int MAX_RT = 4;  // row tiles per CTA, upper bound (sizes the reduction buffer)
-
-// Per-lane partial sums of (rows g, g+8) of tile rt, kept in the warp's private part of shared
-// memory so that the row-tile loop needs no registers per tile: one 8-byte read-modify-write.
-__device__ __forceinline__ void tile_accumulate(float v0, float v1, uint32_t red_lane, int rt) {
-  const uint32_t a = red_lane + rt * (32 * 8);
-  float2 o;
-  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(o.x), "=f"(o.y) : "r"(a));
-  o.x += v0, o.y += v1;
-  asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(a), "f"(o.x), "f"(o.y));
-}
-
-// red[warp][rt][lane] (float2: rows g, g+8).  Sums the four t-lanes of a row and the warps of the
-// CTA in a fixed order and stores out[n0 .. n0 + 16*RT).
-__device__ __forceinline__ void reduce_store(const float2 *red, float *__restrict__ out, int n0, int N, int RT) {
-  __syncthreads();
-  for (int i = threadIdx.x; i < RT * ROWS; i += WARPS * 32) {
-    if (n0 + i < N) {
-      const int rt = i >> 4, row = i & 15, g = row & 7, hi = row >> 3;
-      float v = 0.f;
-#pragma unroll
-      for (int wq = 0; wq < WARPS; wq++) {
-        const float2 *p = red + (wq * MAX_RT + rt) * 32 + g * 4;
-#pragma unroll
-        for (int t = 0; t < 4; t++) v += hi ? p[t].y : p[t].x;
-      }
-      out[n0 + i] = v;
-    }
-  }
 }
 
 // ------------------------------------------------------------------------------------ Q4_K
@@ -377,38 +347,60 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
 // and bits 2q..2q+1 of qh[32h + l]; its sub-block of 16 is s = e / 16 = 8h + 2q + l/16.
 // For each (h, u = l/16), lane (g, t) takes l = 16u + 4t .. +3 of rows g and g+8: one word of
 // ql[64h + l], one of ql[64h + 32 + l] and one of qh[32h + l] -- every byte of the block is
-// loaded by exactly one lane.  Blocks are only 2-byte aligned, so a word is fetched as two
-// aligned 32-bit words funnel-shifted by 0 or 16 bits.  From the three words come the four
+// read by exactly one lane.  From the three words come the four
 // groups' 6-bit codes as bytes, then f16x2 (1024 + code) with PRMT, and group q feeds ONE MMA
 // whose 16 k slots are exactly sub-block 8h + 2q + u, live column 2q + u.
 
-// 32-bit load from a 2-byte aligned address: `a` is the address rounded down to 4 bytes, sh is
-// 0 (already aligned; the second word is then not fetched) or 16.
-__device__ __forceinline__ uint32_t ld_u32_sh(const uint32_t *a, uint32_t sh) {
-  const uint32_t lo = __ldg(a);
-  uint32_t hi = 0;
-  if (sh) hi = __ldg(a + 1);
-  return __funnelshift_r(lo, hi, sh);
+// The tiles travel through a per-warp ring of shared memory like the Q4_K ones.  A 16-byte
+// asynchronous copy keeps the byte offset inside its 16-byte granule, and a 210-byte block starts
+// anywhere on a 2-byte grid: each row's block is copied as the 14 granules that cover it (224 B,
+// to a 240-byte pitch that spreads the rows over the banks), and the block begins `skew` = (its
+// byte offset & 15) bytes into the row's slot.  With an even number of blocks per row the skew is
+// the same for rows g and g+8, and it is a multiple of 4 for even blocks and 2 mod 4 for odd
+// ones, where a word is two aligned words funnel-shifted by 16 bits.
+constexpr int Q6K_PITCH = 240;
+constexpr int Q6K_TILE_BYTES = ROWS * Q6K_PITCH;
+constexpr int Q6K_STAGES = 2;
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+  uint16_t v;
+  asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
+  return v;
+}
+// word at a 2-byte aligned shared address: odd == false -> 4-byte aligned
+template <bool ODD>
+__device__ __forceinline__ uint32_t lds32_skew(uint32_t addr) {
+  if constexpr (!ODD) return lds32(addr);
+  return __funnelshift_r(lds32(addr - 2), lds32(addr + 2), 16);
 }
 
+template <int S>
 __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float *__restrict__ x,
                                                                     const uint8_t *__restrict__ w,
-                                                                    float *__restrict__ out, int N, int K, int RT) {
-  using S = Slab<16>;
-  __shared__ __align__(16) unsigned char slabs[WARPS][S::BYTES];
-  __shared__ __align__(16) unsigned char zero[S::ZERO_BYTES];
-  __shared__ __align__(16) float2 red[WARPS * MAX_RT * 32];
+                                                                    float *__restrict__ out, int N, int K) {
+  using SL = Slab<16>;
+  extern __shared__ __align__(16) unsigned char dyn[];  // ring: WARPS x S tiles
+  __shared__ __align__(16) unsigned char slabs[WARPS][SL::BYTES];
+  __shared__ __align__(16) unsigned char zero[SL::ZERO_BYTES];
+  __shared__ __align__(16) float2 red[2][WARPS * GROUP * 32];  // by group parity
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
   const int nb = K >> 8;
-  const int n0 = blockIdx.x * (ROWS * RT);
-  const uint32_t row_bytes = (uint32_t)nb * 210u;  // a multiple of 4 (checked by the launcher)
-  for (int i = threadIdx.x; i < S::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-  for (int i = lane; i < MAX_RT * 32; i += 32) red[warp * MAX_RT * 32 + i] = make_float2(0.f, 0.f);
+  const uint32_t row_bytes = (uint32_t)nb * 210u;  // a multiple of 4 (nb is even: checked by the launcher)
+  const uint8_t *w_end = w + (size_t)N * row_bytes;
+  for (int i = threadIdx.x; i < SL::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
+  for (int i = threadIdx.x; i < 2 * WARPS * GROUP * 32; i += WARPS * 32) (&red[0][0])[i] = make_float2(0.f, 0.f);
 
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + warp * (S * Q6K_TILE_BYTES);
   const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
   const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
-  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(red + warp * MAX_RT * 32 + lane);
+  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(&red[0][warp * GROUP * 32 + lane]);
+  constexpr uint32_t RED_PARITY = WARPS * GROUP * 32 * 8;
   // B address of the MMA of (group q, u), which works on sub-block 8h + 2q + u: column 2q + u
   // carries the hi half of x, the neighbouring column 2q + 1 - u (unused in this accumulator) the
   // lo half; a lane of those columns reads elements 4t..4t+3 (h adds an immediate).  All other
@@ -418,116 +410,168 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
   for (int q = 0; q < 4; q++)
 #pragma unroll
     for (int u = 0; u < 2; u++)
-      pb[q][u] = (g >> 1) == q ? slab + (2 * q + u) * S::SUB_BYTES + 8 * t + ((g & 1) == u ? 0 : S::LO_OFF) : szero;
-  const int last = N - 1;
+      pb[q][u] = (g >> 1) == q ? slab + (2 * q + u) * SL::SUB_BYTES + 8 * t + ((g & 1) == u ? 0 : SL::LO_OFF) : szero;
   const uint32_t m0f = 0x0F0F0F0Fu;
 
-  bool first = true;
-  for (int b = warp; b < nb; b += WARPS) {
-    float up = 1.f;
-    float2 sx[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-    const uint32_t sh = (b & 1) * 16u;             // odd blocks start 2 bytes past a 4-byte boundary
-    const uint32_t boff = (uint32_t)b * 210u - (b & 1) * 2u;  // block start rounded down to 4 bytes
-    for (int rt = 0; rt < RT; rt++) {
-      const int rg[2] = {min(n0 + rt * ROWS + g, last), min(n0 + rt * ROWS + g + 8, last)};
-      const uint32_t *blk[2];
-      uint32_t scw[2];
-      float dd[2];
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const int t0 = (int)(((long long)tiles * blockIdx.x) / gridDim.x), t1 = (int)(((long long)tiles * (blockIdx.x + 1)) / gridDim.x);
+
+  // requests: lanes 0..13 / 16..29 copy the 14 granules of rows 2i / 2i+1, i = 0..7
+  const uint32_t c_rsub = lane >> 4, c_piece = lane & 15;
+  int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_gt < t1 && warp < nb) {
+      const int r0 = min((i_gt + i_rt) * ROWS, N - ROWS);
+      uint32_t ro = (uint32_t)r0 * row_bytes + (uint32_t)i_b * 210u + c_rsub * row_bytes;
+      uint32_t dst = ring + i_slot * Q6K_TILE_BYTES + c_rsub * Q6K_PITCH + c_piece * 16;
+      if (c_piece < 14) {
+        if (r0 + ROWS < N) {
 #pragma unroll
-      for (int r = 0; r < 2; r++) {
-        const uint8_t *base = w + (size_t)rg[r] * row_bytes + boff;
-        blk[r] = reinterpret_cast<const uint32_t *>(base);
-        const uint8_t *bb = base + (sh >> 3);  // true block start
-        const uint32_t s0 = __ldg(reinterpret_cast<const uint16_t *>(bb + 192 + 2 * t));
-        const uint32_t s1 = __ldg(reinterpret_cast<const uint16_t *>(bb + 200 + 2 * t));
-        scw[r] = s0 | (s1 << 16);  // scales 2t, 2t+1 (h = 0) | 8+2t, 8+2t+1 (h = 1)
-        dd[r] = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(bb + 208)));
-      }
-      // all code words of the tile are requested up front: [row][(h, u)] = ql[64h + l], ql[64h + 32 + l],
-      // qh[32h + l] for l = 16u + 4t
-      uint32_t wa[2][4], wc[2][4], wh[2][4];
+          for (int i = 0; i < 8; i++) {
+            cp_async16(dst, w + ((ro & ~15u) + c_piece * 16));
+            ro += 2 * row_bytes, dst += 2 * Q6K_PITCH;
+          }
+        } else {  // the last rows of the matrix: never read past its end
 #pragma unroll
-      for (int r = 0; r < 2; r++)
-#pragma unroll
-        for (int hu = 0; hu < 4; hu++) {
-          const int h = hu >> 1, u = hu & 1;
-          wa[r][hu] = ld_u32_sh(blk[r] + 16 * h + 4 * u + t, sh);
-          wc[r][hu] = ld_u32_sh(blk[r] + 16 * h + 8 + 4 * u + t, sh);
-          wh[r][hu] = ld_u32_sh(blk[r] + 32 + 8 * h + 4 * u + t, sh);
+          for (int i = 0; i < 8; i++) {
+            const uint8_t *src = w + ((ro & ~15u) + c_piece * 16);
+            const long long left = w_end - src;
+            if (left >= 16)
+              cp_async16(dst, src);
+            else if (left > 0)
+              cp_async16_part(dst, src, (uint32_t)left);
+            ro += 2 * row_bytes, dst += 2 * Q6K_PITCH;
+          }
         }
-      {
-        // pull the next unit's rows towards L2 while this one is being worked on: the three cache
-        // lines a 210-byte block can touch, one per lane t < 3, for both rows
-        const bool more_rt = rt + 1 < RT;
-        const int bn = more_rt ? b : b + WARPS, rtn = more_rt ? rt + 1 : 0;
-        if (bn < nb && t < 3) {
+      }
+      i_slot = (i_slot + 1) & (S - 1);
+      if (++i_rt == i_gs) {
+        i_rt = 0, i_b += WARPS;
+        if (i_b >= nb) i_b = warp, i_gt += i_gs, i_gs = min(GROUP, t1 - i_gt);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int p = 0; p < S; p++) issue();
+
+  pdl_wait();  // x is the previous launch's output; the weights requested above are not
+  __syncthreads();
+  float4 xn[2];  // the activations of the block this warp stages next, requested one block ahead
+  auto load_x = [&](int b) {
+    xn[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+    xn[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+  };
+  if (warp < nb) load_x(warp);
+
+  // one unit: rows g, g+8 of one tile x one K block, out of ring slot `sb`
+  auto unit = [&](auto odd_tag, uint32_t sb, uint32_t skew, const float2 (&sx)[2], float up, float (&vr)[2]) {
+    constexpr bool ODD = decltype(odd_tag)::value;
+    uint32_t wa[2][4], wc[2][4], wh[2][4], scw[2];
+    float dd[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const uint32_t blk = sb + (g + 8 * r) * Q6K_PITCH + skew;  // the block's first byte
+#pragma unroll
+      for (int hu = 0; hu < 4; hu++) {
+        const int h = hu >> 1, u = hu & 1;
+        wa[r][hu] = lds32_skew<ODD>(blk + 4 * (16 * h + 4 * u + t));
+        wc[r][hu] = lds32_skew<ODD>(blk + 4 * (16 * h + 8 + 4 * u + t));
+        wh[r][hu] = lds32_skew<ODD>(blk + 4 * (32 + 8 * h + 4 * u + t));
+      }
+      scw[r] = lds16(blk + 192 + 2 * t) | (lds16(blk + 200 + 2 * t) << 16);  // scales 2t, 2t+1 | 8+2t, 8+2t+1
+      dd[r] = f16_bits_to_f32((uint16_t)lds16(blk + 208));
+    }
+    __syncwarp();  // the slot is free again
+    issue();
+    vr[0] = vr[1] = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // u = 0 / u = 1 chains
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const int hu = 2 * h + u;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          uint32_t a[4];
 #pragma unroll
           for (int r = 0; r < 2; r++) {
-            const int rn = min(n0 + rtn * ROWS + g + 8 * r, last);
-            const uint8_t *pn = w + (size_t)rn * row_bytes + (uint32_t)bn * 210u + t * 104 + (t >> 1);
-            asm volatile("prefetch.global.L2 [%0];\n" ::"l"(pn));
+            const uint32_t lo4 = (q & 1) ? wc[r][hu] : wa[r][hu];
+            const uint32_t nib = (q >> 1) ? (lo4 >> 4) : lo4;
+            const uint32_t hi2 = q == 0 ? (wh[r][hu] << 4) : q == 1 ? (wh[r][hu] << 2) : q == 2 ? wh[r][hu] : (wh[r][hu] >> 2);
+            const uint32_t v = and_or(nib, m0f, hi2 & 0x30303030u);
+            a[r] = __byte_perm(v, 0x64646464u, 0x4240);      // f16x2 (1024 + b0, 1024 + b2)
+            a[2 + r] = __byte_perm(v, 0x64646464u, 0x4341);  // f16x2 (1024 + b1, 1024 + b3)
           }
+          const uint2 bh = lds64(pb[q][u] + h * (8 * SL::SUB_BYTES));
+          if (u == 0)
+            mma16816(d0, a[0], a[1], a[2], a[3], bh.x, bh.y);
+          else
+            mma16816(d1, a[0], a[1], a[2], a[3], bh.x, bh.y);
         }
       }
-      if (rt == 0) {
-        if (first) {
-          pdl_wait();
-          __syncthreads();
-          first = false;
-        }
-        float4 xv[2];
-        xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
-        xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
-        __syncwarp();
-        up = stage_block<16>(xv, slab, lane);
-        __syncwarp();
-        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[0].x), "=f"(sx[0].y) : "r"(slab + S::SX_OFF + 8 * t));
-        asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[1].x), "=f"(sx[1].y) : "r"(slab + S::SX_OFF + 32 + 8 * t));
+      // lane (g, t): d0[0] + d0[1] = row g, sub-block 8h+2t; d1[0] + d1[1] = row g, sub-block 8h+2t+1;
+      // [2], [3] the same for row g+8
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        const float s0 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h)) & 0xff);
+        const float s1 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h + 8)) & 0xff);
+        vr[r] += s0 * (d0[2 * r] + d0[2 * r + 1] - 1056.f * sx[h].x) + s1 * (d1[2 * r] + d1[2 * r + 1] - 1056.f * sx[h].y);
       }
-      float vr[2] = {0.f, 0.f};
-#pragma unroll
-      for (int h = 0; h < 2; h++) {
-        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // u = 0 / u = 1 chains
-#pragma unroll
-        for (int u = 0; u < 2; u++) {
-          const int hu = 2 * h + u;
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            uint32_t a[4];
-#pragma unroll
-            for (int r = 0; r < 2; r++) {
-              const uint32_t lo4 = (q & 1) ? wc[r][hu] : wa[r][hu];
-              const uint32_t nib = (q >> 1) ? (lo4 >> 4) : lo4;
-              const uint32_t hi2 = q == 0 ? (wh[r][hu] << 4) : q == 1 ? (wh[r][hu] << 2) : q == 2 ? wh[r][hu] : (wh[r][hu] >> 2);
-              const uint32_t v = and_or(nib, m0f, hi2 & 0x30303030u);
-              a[r] = __byte_perm(v, 0x64646464u, 0x4240);      // f16x2 (1024 + b0, 1024 + b2)
-              a[2 + r] = __byte_perm(v, 0x64646464u, 0x4341);  // f16x2 (1024 + b1, 1024 + b3)
-            }
-            const uint32_t p = pb[q][u] + h * (8 * S::SUB_BYTES);
-            const uint2 bh = lds64(p);
-            if (u == 0)
-              mma16816(d0, a[0], a[1], a[2], a[3], bh.x, bh.y);
-            else
-              mma16816(d1, a[0], a[1], a[2], a[3], bh.x, bh.y);
-          }
-        }
-        // lane (g, t): d0[0] + d0[1] = row g, sub-block 8h+2t; d1[0] + d1[1] = row g, sub-block 8h+2t+1;
-        // [2], [3] the same for row g+8
-#pragma unroll
-        for (int r = 0; r < 2; r++) {
-          const float s0 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h)) & 0xff);
-          const float s1 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h + 8)) & 0xff);
-          vr[r] += s0 * (d0[2 * r] + d0[2 * r + 1] - 1056.f * sx[h].x) + s1 * (d1[2 * r] + d1[2 * r + 1] - 1056.f * sx[h].y);
-        }
+    }
+    vr[0] *= up, vr[1] *= up;
+  };
+
+  int slot = 0, parity = 0;
+  for (int gt = t0; gt < t1; gt += GROUP, parity ^= 1) {
+    const int gs = min(GROUP, t1 - gt);
+    const uint32_t red_g = red_lane + parity * RED_PARITY;
+    for (int b = warp; b < nb; b += WARPS) {
+      // this block's activations into the warp's slab; the next block's are requested meanwhile
+      const float4 xv[2] = {xn[0], xn[1]};
+      {
+        const int bn = b + WARPS < nb ? b + WARPS : warp;
+        if (b + WARPS < nb || gt + GROUP < t1) load_x(bn);
       }
-      tile_accumulate(vr[0] * up, vr[1] * up, red_lane, rt);
+      __syncwarp();  // every lane is done reading the previous block's slab
+      const float up = stage_block<16>(xv, slab, lane);
+      __syncwarp();
+      float2 sx[2];
+      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[0].x), "=f"(sx[0].y) : "r"(slab + SL::SX_OFF + 8 * t));
+      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[1].x), "=f"(sx[1].y) : "r"(slab + SL::SX_OFF + 32 + 8 * t));
+      for (int rt = 0; rt < gs; rt++) {
+        cp_async_wait<S - 1>();  // this lane's granules of the tile have landed ...
+        __syncwarp();            // ... and so have the other lanes'
+        const uint32_t sb = ring + slot * Q6K_TILE_BYTES;
+        slot = (slot + 1) & (S - 1);
+        const int r0 = min((gt + rt) * ROWS, N - ROWS);
+        const uint32_t skew = ((uint32_t)r0 * row_bytes + (uint32_t)b * 210u + (uint32_t)g * row_bytes) & 15u;
+        float vr[2];
+        if (b & 1)
+          unit(std::true_type{}, sb, skew, sx, up, vr);
+        else
+          unit(std::false_type{}, sb, skew, sx, up, vr);
+        // the warp's first block of a group overwrites what an earlier group left behind
+        const uint32_t ra = red_g + rt * (32 * 8);
+        float2 o = make_float2(0.f, 0.f);
+        if (b != warp) asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(o.x), "=f"(o.y) : "r"(ra));
+        asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(ra), "f"(o.x + vr[0]), "f"(o.y + vr[1]));
+      }
+    }
+    __syncthreads();  // also orders this group's reads of red[parity] before its reuse two groups on
+    for (int i = threadIdx.x; i < gs * ROWS; i += WARPS * 32) {
+      const int rt = i >> 4, row = i & 15, gg = row & 7, hi = row >> 3;
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) {
+        const float2 *p = &red[parity][(wq * GROUP + rt) * 32 + gg * 4];
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;
+      }
+      out[min((gt + rt) * ROWS, N - ROWS) + row] = v;
     }
   }
-  if (first) {
-    pdl_wait();
-    __syncthreads();
-  }
-  reduce_store(red, out, n0, N, RT);
+  cp_async_wait<0>();
 }
 
 template <typename... Args>
@@ -547,17 +591,6 @@ int launch_pdl(void (*kern)(Args...), unsigned grid, size_t dyn_smem, cudaStream
   return 0;
 }
 
-// Row tiles per CTA of the Q6_K kernel: enough CTAs to fill the SMs a few times over, as many
-// tiles as that allows (each tile reuses the block's converted activations).
-int g_rt_override = 0;  // LIGHT_B200_GEMV_RT: tuning knob, 0 = choose by shape
-int pick_rt(int N) {
-  if (g_rt_override > 0) return g_rt_override >= 4 ? 4 : g_rt_override >= 2 ? 2 : 1;
-  const int tiles = (N + ROWS - 1) / ROWS;
-  if (tiles >= 148 * 8) return 4;
-  if (tiles >= 148 * 4) return 2;
-  return 1;
-}
-
 int g_sms = 148;       // SMs of the bound device
 int g_waves = 2;       // LIGHT_B200_GEMV_WAVES: CTAs per SM of the persistent kernels' grids (1 or 2)
 int g_q4k_stages = 4;  // LIGHT_B200_Q4K_STAGES: ring depth (2 or 4)
@@ -566,7 +599,6 @@ constexpr size_t MAX_DYN_SMEM = 96 * 1024;  // keeps two launches resident per S
 }  // namespace
 
 int gguf_gemv_fast_init(int device) {
-  if (const char *e = getenv("LIGHT_B200_GEMV_RT")) g_rt_override = atoi(e);
   if (const char *e = getenv("LIGHT_B200_GEMV_WAVES")) g_waves = atoi(e) == 1 ? 1 : 2;
   if (const char *e = getenv("LIGHT_B200_Q4K_STAGES")) g_q4k_stages = atoi(e) == 2 ? 2 : 4;
   cudaError_t err = cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, device);
@@ -574,6 +606,9 @@ int gguf_gemv_fast_init(int device) {
     err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               WARPS * Q6K_STAGES * Q6K_TILE_BYTES);
   if (err != cudaSuccess) return fail((int)err, "light_b200: init (decode): %s", cudaGetErrorString(err));
   return 0;
 }
@@ -595,9 +630,10 @@ static int q4k_launch(const float *x, const MultiArgs &a, int tiles, int K, cuda
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
   if (M != 1 || K % 256 || N < ROWS) return 0;
   if (type != LB200_Q4_K && type != LB200_Q6_K) return 0;
-  if (type == LB200_Q4_K && ((uintptr_t)w & 15)) return 0;
-  // Q6_K rows must start 4-byte aligned for the aligned-word loads: (K/256)*210 % 4 == 0
-  if (type == LB200_Q6_K && (((uintptr_t)w & 3) || ((size_t)(K >> 8) * 210) % 4)) return 0;
+  if ((uintptr_t)w & 15) return 0;
+  // Q6_K: an even number of blocks per row keeps every row's skew equal for rows 8 apart and
+  // word-aligned for even blocks; byte offsets are 32-bit
+  if (type == LB200_Q6_K && (((K >> 8) & 1) || (unsigned long long)N * (K >> 8) * 210ull >= (1ull << 32))) return 0;
   const uint8_t *wb = (const uint8_t *)w;
   const int tiles = (N + ROWS - 1) / ROWS;
   if (type == LB200_Q4_K) {
@@ -605,9 +641,8 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
     a.w[0] = wb, a.out[0] = out, a.n[0] = N, a.tend[0] = tiles, a.count = 1;
     return q4k_launch(x, a, tiles, K, st);
   }
-  const int rt = pick_rt(N);
-  const unsigned grid = (unsigned)((N + ROWS * rt - 1) / (ROWS * rt));
-  int rc = launch_pdl(q6k_gemv_mma_kernel, grid, (size_t)0, st, x, wb, out, N, K, rt);
+  const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
+  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x, wb, out, N, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
   return rc ? rc : 1;
