@@ -191,7 +191,6 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
   const int nb = K >> 8;
   const uint32_t row_bytes = (uint32_t)nb * 144u;
   for (int i = threadIdx.x; i < SL::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-  for (int i = threadIdx.x; i < 2 * WARPS * GROUP * 32; i += WARPS * 32) (&red[0][0])[i] = make_float2(0.f, 0.f);
 
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + warp * (S * Q4K_TILE_BYTES);
   const uint32_t slabs = (uint32_t)__cvta_generic_to_shared(dyn) + WARPS * S * Q4K_TILE_BYTES;
@@ -211,8 +210,8 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
 
   // this CTA's share [t0, t1) of the tile list (whole gate/up pairs when act != 0)
   const int unit = a.act ? 2 : 1, lt = tiles / unit;
-  const int t0 = (int)(((long long)lt * blockIdx.x) / gridDim.x) * unit,
-            t1 = (int)(((long long)lt * (blockIdx.x + 1)) / gridDim.x) * unit;
+  const int t0 = (int)((uint32_t)lt * blockIdx.x / gridDim.x) * unit,  // lt * gridDim.x < 2^32 (launcher)
+            t1 = (int)((uint32_t)lt * (blockIdx.x + 1) / gridDim.x) * unit;
 
   // source offsets of this lane's chunks, relative to the tile's first byte (row 0, this block)
   uint32_t soff[5];
@@ -241,7 +240,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
     }
     cp_async_commit();
   };
-#pragma unroll
+#pragma unroll 1
   for (int p = 0; p < S; p++) issue();
   pdl_wait();  // x is the previous launch's output; the weights requested above are not
   for (int b = warp; b < nb; b += WARPS) {
@@ -315,6 +314,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
       float v = 0.f;
 #pragma unroll
       for (int wq = 0; wq < WARPS; wq++) {
+        if (wq >= nb) break;  // a warp without a K block never wrote its part
         const float2 *p = &red[parity][(wq * GROUP + rt) * 32 + gg * 4];
 #pragma unroll
         for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;
@@ -394,7 +394,6 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
   const uint32_t row_bytes = (uint32_t)nb * 210u;  // a multiple of 4 (nb is even: checked by the launcher)
   const uint8_t *w_end = w + (size_t)N * row_bytes;
   for (int i = threadIdx.x; i < SL::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
-  for (int i = threadIdx.x; i < 2 * WARPS * GROUP * 32; i += WARPS * 32) (&red[0][0])[i] = make_float2(0.f, 0.f);
 
   const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + warp * (S * Q6K_TILE_BYTES);
   const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
@@ -414,7 +413,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
   const uint32_t m0f = 0x0F0F0F0Fu;
 
   const int tiles = (N + ROWS - 1) / ROWS;
-  const int t0 = (int)(((long long)tiles * blockIdx.x) / gridDim.x), t1 = (int)(((long long)tiles * (blockIdx.x + 1)) / gridDim.x);
+  const int t0 = (int)((uint32_t)tiles * blockIdx.x / gridDim.x), t1 = (int)((uint32_t)tiles * (blockIdx.x + 1) / gridDim.x);
 
   // requests: lanes 0..13 / 16..29 copy the 14 granules of rows 2i / 2i+1, i = 0..7
   const uint32_t c_rsub = lane >> 4, c_piece = lane & 15;
@@ -452,7 +451,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
     }
     cp_async_commit();
   };
-#pragma unroll
+#pragma unroll 1
   for (int p = 0; p < S; p++) issue();
 
   pdl_wait();  // x is the previous launch's output; the weights requested above are not
@@ -564,6 +563,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
       float v = 0.f;
 #pragma unroll
       for (int wq = 0; wq < WARPS; wq++) {
+        if (wq >= nb) break;  // a warp without a K block never wrote its part
         const float2 *p = &red[parity][(wq * GROUP + rt) * 32 + gg * 4];
 #pragma unroll
         for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;

@@ -20,6 +20,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "mma_sync.cuh"
 #include "umma.cuh"
 
 namespace lb {
@@ -75,9 +76,17 @@ __device__ __forceinline__ void st_chunk(uint32_t addr, const uint4 &v) {
 struct GgufCtx {
   const uint8_t *w;
 };
+// The expansion runs on packed f16 pairs.  One LOP3 turns two nibbles of a code word into the f16
+// pair (1024 + q, 1024 + q') (low nibbles of bytes 0 and 2) or (64 + q, 64 + q') (high nibbles); one
+// HFMA2 with the sub-block's 6-bit scale gives q * sc exactly (an integer below 2048), and a second
+// one d * (q * sc) - dmin * m with a single rounding of the weight (dmin * m itself is rounded to
+// f16 once per sub-block).  A code word yields the pairs (0, 2) and (1, 3) of its four bytes, so
+// the activations are stored with every four consecutive k in the order 0, 2, 1, 3 (KPERM) and no
+// instruction is spent on putting the weights back in order.
 struct Q4KRow {
   using Ctx = GgufCtx;
   static constexpr int STEPS = 4;  // one load() = one 256-element block = 4 steps of 64
+  static constexpr bool KPERM = true;
   const uint8_t *row;
   uint4 h, q[8];
   __device__ __forceinline__ void init(const Ctx &c, int e, int n, int N, int K) {
@@ -89,10 +98,12 @@ struct Q4KRow {
 #pragma unroll
     for (int i = 0; i < 8; i++) q[i] = __ldg(p + 1 + i);
   }
+  __device__ __forceinline__ static uint32_t h2u(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+  __device__ __forceinline__ static __half2 u2h(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
   template <bool BF16>
   __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
     // sub-blocks 2j (low nibbles of qs[32j .. 32j+31]) and 2j+1 (high nibbles)
-    const float2 dd = __half22float2(*reinterpret_cast<const __half2 *>(&h.x));
+    const __half2 dd = u2h(h.x);  // (d, dmin)
     uint32_t sc0, mn0, sc1, mn1;
     if (j < 2) {
       sc0 = (h.y >> (16 * j)) & 63, sc1 = (h.y >> (16 * j + 8)) & 63;
@@ -104,17 +115,20 @@ struct Q4KRow {
       mn0 = ((h.w >> (s + 4)) & 0xF) | (((h.z >> (s + 6)) & 3) << 4);
       mn1 = ((h.w >> (s + 12)) & 0xF) | (((h.z >> (s + 14)) & 3) << 4);
     }
-    const float s0 = dd.x * (float)sc0, m0 = dd.y * (float)mn0, s1 = dd.x * (float)sc1, m1 = dd.y * (float)mn1;
+    const __half2 d2 = __low2half2(dd);
+    const float dmin = __high2float(dd);
+    const __half2 s0 = __half2half2(__uint2half_rn(sc0)), s1 = __half2half2(__uint2half_rn(sc1));
+    const __half2 c0 = __hmul2(s0, __float2half2_rn(-1024.f)), c1 = __hmul2(s1, __float2half2_rn(-64.f));  // exact
+    const __half2 nm0 = __float2half2_rn(-dmin * (float)mn0), nm1 = __float2half2_rn(-dmin * (float)mn1);
+    const uint32_t mlo = 0x000F000Fu, glo = 0x64006400u, mhi = 0x00F000F0u, ghi = 0x54005400u;
     const uint32_t w[8] = {q[2 * j].x, q[2 * j].y, q[2 * j].z, q[2 * j].w, q[2 * j + 1].x, q[2 * j + 1].y, q[2 * j + 1].z, q[2 * j + 1].w};
+    auto lo2 = [&](uint32_t v) { return h2u(__hfma2(__hfma2(u2h(and_or(v, mlo, glo)), s0, c0), d2, nm0)); };
+    auto hi2 = [&](uint32_t v) { return h2u(__hfma2(__hfma2(u2h(and_or(v, mhi, ghi)), s1, c1), d2, nm1)); };
 #pragma unroll
     for (int c = 0; c < 4; c++) {  // chunk c: k = 8c..8c+7 (low nibbles); chunk c+4: k = 32+8c.. (high nibbles)
-      uint4 lo, hi;
-      expand4<BF16>(w[2 * c] & 0x0F0F0F0Fu, s0, m0, lo.x, lo.y);
-      expand4<BF16>(w[2 * c + 1] & 0x0F0F0F0Fu, s0, m0, lo.z, lo.w);
-      expand4<BF16>((w[2 * c] >> 4) & 0x0F0F0F0Fu, s1, m1, hi.x, hi.y);
-      expand4<BF16>((w[2 * c + 1] >> 4) & 0x0F0F0F0Fu, s1, m1, hi.z, hi.w);
-      st_chunk(tile + swz(r, c), lo);
-      st_chunk(tile + swz(r, c + 4), hi);
+      const uint32_t a = w[2 * c], b = w[2 * c + 1], a8 = a >> 8, b8 = b >> 8;
+      st_chunk(tile + swz(r, c), make_uint4(lo2(a), lo2(a8), lo2(b), lo2(b8)));
+      st_chunk(tile + swz(r, c + 4), make_uint4(hi2(a), hi2(a8), hi2(b), hi2(b8)));
     }
   }
 };
@@ -126,6 +140,7 @@ struct Q4KRow {
 // aligned 32-bit loads funnel-shifted by 0 or 16 bits (rows start 4-byte aligned, checked on the host).
 struct Q6KRow {
   using Ctx = GgufCtx;
+  static constexpr bool KPERM = false;
   static constexpr int STEPS = 2;
   const uint8_t *row;
   uint32_t ql[16], qh[8], sc[2];
@@ -186,6 +201,7 @@ struct Int4Ctx {
 };
 struct Int4Row {
   using Ctx = Int4Ctx;
+  static constexpr bool KPERM = false;
   static constexpr int STEPS = 4;
   const uint4 *row;
   const float *sr, *zr;
@@ -229,6 +245,7 @@ struct Fp8Ctx {
 };
 struct Fp8Row {
   using Ctx = Fp8Ctx;
+  static constexpr bool KPERM = false;
   static constexpr int STEPS = 2;
   const uint4 *row;
   const float *sr;
@@ -269,6 +286,7 @@ struct DenseCtx {
 };
 struct DenseRow {
   using Ctx = DenseCtx;
+  static constexpr bool KPERM = false;
   static constexpr int STEPS = 1;
   const uint4 *row;
   uint4 q[8];
@@ -490,13 +508,15 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-// x f32 (M, K) -> f16, clamped to the f16 range so that an outlier cannot become an infinity
+// x f32 (M, K) -> f16, clamped to the f16 range so that an outlier cannot become an infinity.
+// PERM: every four consecutive k are stored in the order 0, 2, 1, 3 (what a KPERM row expander pairs them with).
+template <bool PERM>
 __global__ void __launch_bounds__(256) x_to_f16_kernel(const float4 *__restrict__ x, uint2 *__restrict__ y, long long n4) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     float4 v = __ldg(x + i);
     v.x = fminf(fmaxf(v.x, -65504.f), 65504.f), v.y = fminf(fmaxf(v.y, -65504.f), 65504.f);
     v.z = fminf(fmaxf(v.z, -65504.f), 65504.f), v.w = fminf(fmaxf(v.w, -65504.f), 65504.f);
-    y[i] = make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
+    y[i] = PERM ? make_uint2(pack_h2(v.x, v.z), pack_h2(v.y, v.w)) : make_uint2(pack_h2(v.x, v.y), pack_h2(v.z, v.w));
   }
 }
 
@@ -523,7 +543,7 @@ int ensure_encode() {
 }
 
 // x f32 -> f16 in the workspace, or bf16 x used as it is; then the tensor map over it.
-int make_x_map(CUtensorMap *tm, const void *x, int act_dtype, int M, int K, void *ws, cudaStream_t st) {
+int make_x_map(CUtensorMap *tm, const void *x, int act_dtype, int M, int K, void *ws, bool perm, cudaStream_t st) {
   if (int rc = ensure_encode()) return rc;
   const void *src = x;
   CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -531,7 +551,10 @@ int make_x_map(CUtensorMap *tm, const void *x, int act_dtype, int M, int K, void
     const long long n4 = (long long)M * K / 4;
     long long blocks = (n4 + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
-    x_to_f16_kernel<<<(unsigned)blocks, 256, 0, st>>>((const float4 *)x, (uint2 *)ws, n4);
+    if (perm)
+      x_to_f16_kernel<true><<<(unsigned)blocks, 256, 0, st>>>((const float4 *)x, (uint2 *)ws, n4);
+    else
+      x_to_f16_kernel<false><<<(unsigned)blocks, 256, 0, st>>>((const float4 *)x, (uint2 *)ws, n4);
     if (int rc = launched("prefill: activations to f16")) return rc;
     src = ws;
     dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -576,10 +599,13 @@ template <typename Row>
 int launch_by_act(const void *x, int act_dtype, const typename Row::Ctx &ctx, void *out, int M, int N, int K, void *ws,
                   cudaStream_t st) {
   CUtensorMap tm;
-  if (int rc = make_x_map(&tm, x, act_dtype, M, K, ws, st)) return rc;
+  if (Row::KPERM && act_dtype != LB200_F32)
+    return fail(LB200_E_DTYPE, "light_b200: prefill: this weight format takes f32 activations only");
+  if (int rc = make_x_map(&tm, x, act_dtype, M, K, ws, Row::KPERM, st)) return rc;
   const Group none{nullptr, nullptr, nullptr, 0, 0};
   if (act_dtype == LB200_F32) return launch<Row, false, float>(tm, ctx, none, (float *)out, M, N, K, st);
-  return launch<Row, true, __nv_bfloat16>(tm, ctx, none, (__nv_bfloat16 *)out, M, N, K, st);
+  if constexpr (!Row::KPERM) return launch<Row, true, __nv_bfloat16>(tm, ctx, none, (__nv_bfloat16 *)out, M, N, K, st);
+  return LB200_E_DTYPE;
 }
 
 // workspace for an f32 activation matrix; bf16 needs none.  Returns false if there is not enough.
@@ -648,7 +674,7 @@ namespace {
 // ---- grouped (mixture-of-experts) matmul on the same kernel.
 // Rows of the A operand in expert order: dst[i] = in[row(sorted_pairs[i])], converted to the operand type
 // (f32 -> f16 clamped, 16-bit types copied); rows of pairs outside [0, size_m) are zero.
-template <typename TI>
+template <typename TI, bool PERM>
 __global__ void __launch_bounds__(256) gather_rows_kernel(const TI *__restrict__ in, const int64_t *__restrict__ pairs,
                                                           uint16_t *__restrict__ dst, long long Mp, int K, int topk,
                                                           int row_per_pair, long long size_m) {
@@ -663,7 +689,8 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const TI *__restrict__
         if constexpr (sizeof(TI) == 4) {
           const float4 a = __ldg(reinterpret_cast<const float4 *>(src + k)), b = __ldg(reinterpret_cast<const float4 *>(src + k) + 1);
           auto cl = [](float v) { return fminf(fmaxf(v, -65504.f), 65504.f); };
-          o = make_uint4(pack_h2(cl(a.x), cl(a.y)), pack_h2(cl(a.z), cl(a.w)), pack_h2(cl(b.x), cl(b.y)), pack_h2(cl(b.z), cl(b.w)));
+          o = PERM ? make_uint4(pack_h2(cl(a.x), cl(a.z)), pack_h2(cl(a.y), cl(a.w)), pack_h2(cl(b.x), cl(b.z)), pack_h2(cl(b.y), cl(b.w)))
+                   : make_uint4(pack_h2(cl(a.x), cl(a.y)), pack_h2(cl(a.z), cl(a.w)), pack_h2(cl(b.x), cl(b.y)), pack_h2(cl(b.z), cl(b.w)));
         } else {
           o = __ldg(reinterpret_cast<const uint4 *>(src + k));
         }
@@ -678,7 +705,7 @@ int moe_launch(const lb200_moe_args *a, const typename Row::Ctx &ctx, void *ws, 
   if (int rc = ensure_encode()) return rc;
   long long blocks = (a->M + 7) / 8;
   if (blocks > 148 * 32) blocks = 148 * 32;
-  gather_rows_kernel<TI><<<(unsigned)blocks, 256, 0, st>>>((const TI *)a->input, a->sorted_pairs, (uint16_t *)ws, a->M, a->K,
+  gather_rows_kernel<TI, Row::KPERM && sizeof(TI) == 4><<<(unsigned)blocks, 256, 0, st>>>((const TI *)a->input, a->sorted_pairs, (uint16_t *)ws, a->M, a->K,
                                                           a->topk, a->row_per_pair, a->size_m);
   if (int rc = launched("moe: gather rows")) return rc;
   CUtensorMap tm;
