@@ -17,6 +17,7 @@
 #include <cuda.h>
 #include <cuda_fp8.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -140,7 +141,7 @@ struct Q4KRow {
 // aligned 32-bit loads funnel-shifted by 0 or 16 bits (rows start 4-byte aligned, checked on the host).
 struct Q6KRow {
   using Ctx = GgufCtx;
-  static constexpr bool KPERM = false;
+  static constexpr bool KPERM = true;
   static constexpr int STEPS = 2;
   const uint8_t *row;
   uint32_t ql[16], qh[8], sc[2];
@@ -166,25 +167,27 @@ struct Q6KRow {
     sc[0] = ld(a + 48 + 2 * h, sh), sc[1] = ld(a + 49 + 2 * h, sh);
     d = f16_bits_to_f32(__ldg(reinterpret_cast<const uint16_t *>(blk + 208)));
   }
+  // Packed f16 arithmetic as in the Q4_K expander: PRMT builds (1024 + code) pairs of bytes (0, 2)
+  // and (1, 3), one HADD2 takes 1056 off (code - 32, exact), one HMUL2 applies d * sc rounded to f16.
   template <bool BF16>
   __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
+    const __half2 off = __float2half2_rn(-1056.f);
 #pragma unroll
     for (int c = 0; c < 8; c++) {  // chunk c: k = 8c .. 8c+7 -> group q = 2j + c/4, l = 8 (c%4) ..
       const int q = 2 * j + (c >> 2), li = 2 * (c & 3);
-      const float ds = d * (float)(int8_t)((sc[j] >> (8 * (c >> 1))) & 0xff);
-      const float m = 32.f * ds;
-      uint4 o;
+      const __half2 ds = __float2half2_rn(d * (float)(int8_t)((sc[j] >> (8 * (c >> 1))) & 0xff));
+      uint32_t o[4];
 #pragma unroll
       for (int e = 0; e < 2; e++) {
         const uint32_t wq = ql[8 * (c >> 2) + li + e] >> (4 * j), wh = qh[li + e];
         const uint32_t hi2 = q == 0 ? (wh << 4) : q == 1 ? (wh << 2) : q == 2 ? wh : (wh >> 2);
-        const uint32_t v = (wq & 0x0F0F0F0Fu) | (hi2 & 0x30303030u);
-        if (e == 0)
-          expand4<BF16>(v, ds, m, o.x, o.y);
-        else
-          expand4<BF16>(v, ds, m, o.z, o.w);
+        const uint32_t v = and_or(wq, 0x0F0F0F0Fu, hi2 & 0x30303030u);
+        const uint32_t p02 = __byte_perm(v, 0x64646464u, 0x4240), p13 = __byte_perm(v, 0x64646464u, 0x4341);
+        const __half2 w02 = __hmul2(__hadd2(*reinterpret_cast<const __half2 *>(&p02), off), ds);
+        const __half2 w13 = __hmul2(__hadd2(*reinterpret_cast<const __half2 *>(&p13), off), ds);
+        o[2 * e] = *reinterpret_cast<const uint32_t *>(&w02), o[2 * e + 1] = *reinterpret_cast<const uint32_t *>(&w13);
       }
-      st_chunk(tile + swz(r, c), o);
+      st_chunk(tile + swz(r, c), make_uint4(o[0], o[1], o[2], o[3]));
     }
   }
 };
@@ -584,10 +587,11 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
   const long long nt = (N + BN - 1) / BN;
   auto waves_cost = [&](int bm_) {  // time in units of one 256-row tile
     const long long ctas = nt * ((M + bm_ - 1) / bm_);
-    return (double)((ctas + 147) / 148) * (bm_ == 256 ? 1.0 : 0.85);
+    return (double)((ctas + 147) / 148) * (bm_ == 256 ? 1.0 : 0.75);
   };
-  // (measured: a 128-row tile takes 0.85 of a 256-row tile, the weight expansion dominates)
-  const int bm = (!grp.offsets && waves_cost(128) < waves_cost(256)) ? 128 : 256;
+  // (measured: a 128-row tile takes 0.75 of a 256-row tile)
+  int bm = (!grp.offsets && waves_cost(128) < waves_cost(256)) ? 128 : 256;
+  if (const char *e = getenv("LIGHT_B200_PREFILL_BM")) bm = (atoi(e) == 128 && !grp.offsets) ? 128 : atoi(e) == 256 ? 256 : bm;
   // grouped: at most ceil(M / bm) + E tiles (every expert can end with one partial tile)
   dim3 grid((unsigned)nt, (M + bm - 1) / bm + (grp.offsets ? grp.E : 0));
   kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, bm);
