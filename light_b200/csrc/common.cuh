@@ -65,6 +65,12 @@ int allgather_ll(const float *local, float *out, const lb200_peers *peers, int M
                  cudaStream_t st);
 int comm_status();
 int prefill_status(int device);
+int decode_umma_status();
+int gguf_decode_umma(int type, const float *x, const void *w, float *out, int M, int N, int K, int device, cudaStream_t st);
+int int4_decode_umma(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N,
+                     int K, int G, int device, cudaStream_t st);
+int fp8_decode_umma(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR,
+                    int bC, int device, cudaStream_t st);
 
 int int4_dequant(const uint32_t *codes, const float *s, const float *z, void *out, int out_dtype, int N, int K, int G,
                  long long offset, cudaStream_t st);
