@@ -37,6 +37,9 @@ HID, FFN, NKV, VOCAB, LAYERS = 4096, 14336, 1024, 128256, 32
 LAYER = [("q", HID, HID, ops.Q4_K), ("k", NKV, HID, ops.Q4_K), ("v", NKV, HID, ops.Q4_K), ("o", HID, HID, ops.Q4_K),
          ("gate", FFN, HID, ops.Q4_K), ("up", FFN, HID, ops.Q4_K), ("down", HID, FFN, ops.Q6_K)]
 HEAD = ("lm_head", VOCAB, HID, ops.Q6_K)
+# DRAM traffic of the Q4_K decode kernel per algorithmic byte, from the ncu capture summarised in
+# profiles/q4k_gemv_mma_kernel__llama8b_decode_small_case.md (every weight byte is fetched once)
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 89.78 / 89.86
 
 
 def weight_bytes(N, K, dt):
@@ -407,7 +410,9 @@ def main():
     n6 = chain.launches(ops.Q6_K)
     gbs6 = chain.bytes_per_step(ops.Q6_K) / (ms6 * 1e-3 / args.steps) / 1e9
     roofline = {"bound": "hbm", "kernel": "q4k_gemv_mma_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                "frac": achieved / peak, "peak_source": f"of {peak_kind}", "traffic": None,
+                "frac": achieved / peak, "peak_source": f"of {peak_kind}", "traffic": b4 * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE,
+                "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of this kernel's three launch shapes on the "
+                                  "1-layer case (89.78 MB) over their algorithmic bytes (89.86 MB), scaled to the mean launch",
                 "bytes_per_launch": b4, "us_per_launch": us4, "launches_per_step": n4,
                 "timed": "all Q4_K launches of a step in a graph of their own",
                 "q6k_gemv_gbs": gbs6, "q6k_launches_per_step": n6,
