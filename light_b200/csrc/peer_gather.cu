@@ -30,6 +30,10 @@ struct Slots {
 __global__ void __launch_bounds__(256) allgather_ll_kernel(const float *__restrict__ local, float *__restrict__ out,
                                                            Slots slots, int world, int rank, int M, int n_local,
                                                            const unsigned int *__restrict__ step) {
+  // programmatic dependent launch on both sides: the matmul after this gather may start (and request
+  // its weights) at once, and this kernel's own launch overlapped the tail of the matmul before it
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");  // `local` and the step word are the predecessors' outputs
   const unsigned int tag = *step;
   const int N = n_local * world, mine = M * n_local, total = M * N;
   const int tid = blockIdx.x * blockDim.x + threadIdx.x, nthr = gridDim.x * blockDim.x;
@@ -87,7 +91,17 @@ int allgather_ll(const float *local, float *out, const lb200_peers *peers, int M
   int grid = (total + 1023) / 1024;  // about four elements per thread
   if (grid < 1) grid = 1;
   if (grid > 148) grid = 148;
-  allgather_ll_kernel<<<grid, 256, 0, st>>>(local, out, s, peers->world, peers->rank, M, n_local, step);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(256);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, allgather_ll_kernel, local, out, s, peers->world, peers->rank, M, n_local, step);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: allgather_ll: %s", cudaGetErrorString(e));
   return launched("allgather_ll");
 }
 
