@@ -147,3 +147,70 @@ class PeerGather:
         from . import _lib
 
         return _lib.lib().light_b200_comm_status(self.device.index or 0)
+
+
+class ExpertParallel:
+    """Mixture-of-experts layer with the experts sharded over the ranks (E / P contiguous experts each)
+    and a token all-to-all on either side of the local grouped matmuls -- the multi-GPU form of the
+    reference's single-GPU sparse block (nn/moe.go:121-237: route, grouped GEMMs in expert order,
+    combine).  Every rank brings its own tokens.
+
+        dispatch : pairs (token, slot) sorted by expert are one contiguous run per destination rank
+                   (split_pairs_by_rank); their hidden rows and expert ids go out in one all-to-all each
+        local    : the receiver regroups the rows it got (from all ranks) by local expert and runs
+                   `ffn(rows, routing_local)` -- on a GPU the grouped tensor-core matmuls of this
+                   library (ops.MoEGemm / MoEGemmQ / MoEGemmF8Block with row_per_pair), on CPU whatever
+                   the test injects
+        combine  : results travel back with the split sizes reversed, and each token sums its top-k
+                   rows with the routing weights (ops.MoECombine's arithmetic)
+
+    The exchange is torch.distributed.all_to_all_single (NCCL over NVLink on GPUs, gloo in the CPU
+    tests): a real exchange step, the one place on this path where a collective is the right tool.
+    """
+
+    def __init__(self, num_experts: int, group=None):
+        import torch.distributed as dist
+
+        self.group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        self.E = num_experts
+        self.lo, self.hi = expert_range(num_experts, self.rank, self.world)
+
+    def plan(self, topk_ids: torch.Tensor):
+        """Routing of this rank's tokens: (sorted_pairs, sorted_expts, send_counts, recv_counts)."""
+        import torch.distributed as dist
+
+        T, topk = topk_ids.shape
+        flat = topk_ids.reshape(T * topk).to(torch.int64)
+        if flat.numel() and (int(flat.min()) < 0 or int(flat.max()) >= self.E):
+            raise ValueError(f"ExpertParallel: expert id outside [0, {self.E})")
+        sorted_expts, sorted_pairs = torch.sort(flat, stable=True)
+        offs = split_pairs_by_rank(sorted_expts, self.E, self.world)
+        send = (offs[1:] - offs[:-1]).to(torch.int64)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=self.group)
+        return sorted_pairs, sorted_expts, send.tolist(), recv.tolist()
+
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, ffn) -> torch.Tensor:
+        """x (T, H) this rank's tokens, topk_ids / topk_weights (T, topk); ffn(rows (R, H), order (R,) int64,
+        local_expert_of_order (R,) int64 non-decreasing) -> (R, H_out) rows in the order it was given them.
+        Returns (T, H_out) f32."""
+        import torch.distributed as dist
+
+        T, topk = topk_ids.shape
+        sorted_pairs, sorted_expts, send, recv = self.plan(topk_ids)
+        rows = x.index_select(0, sorted_pairs // topk).contiguous()
+        R = sum(recv)
+        got_rows = torch.empty(R, x.shape[1], dtype=x.dtype, device=x.device)
+        got_expts = torch.empty(R, dtype=torch.int64, device=x.device)
+        dist.all_to_all_single(got_rows, rows, output_split_sizes=recv, input_split_sizes=send, group=self.group)
+        dist.all_to_all_single(got_expts, sorted_expts.contiguous(), output_split_sizes=recv, input_split_sizes=send, group=self.group)
+        # what arrived is sorted by expert inside each source rank's run: regroup over all runs
+        local_sorted, order = torch.sort(got_expts - self.lo, stable=True)
+        done = ffn(got_rows, order, local_sorted)
+        back = torch.empty(rows.shape[0], done.shape[1], dtype=done.dtype, device=x.device)
+        dist.all_to_all_single(back, done.contiguous(), output_split_sizes=send, input_split_sizes=recv, group=self.group)
+        w = topk_weights.reshape(T * topk).float().index_select(0, sorted_pairs)
+        out = torch.zeros(T, done.shape[1], dtype=torch.float32, device=x.device)
+        out.index_add_(0, sorted_pairs // topk, back.float() * w[:, None])
+        return out

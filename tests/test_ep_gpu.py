@@ -1,0 +1,87 @@
+"""Expert parallelism on two or more GPUs, one process per GPU: tokens of every rank are dispatched by
+all-to-all to the rank that owns their experts, run through this library's grouped matmuls there
+(SwiGLU expert: gate_up, SiLU * up, down), and come back; the result must equal the same sparse block
+computed on one GPU with all experts.  Skipped on a single-GPU box."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from light_b200 import ops, tp
+
+        E, H, I, topk = 4 * world, 256, 128, 2
+        g = torch.Generator().manual_seed(5)
+        W1 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        W2 = (torch.randn(E, H, I, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+        ep = tp.ExpertParallel(E)
+
+        def expert_block(rows, order, expts, w1, w2):
+            r = ops.MoERouting(None, None, order.contiguous(), expts.contiguous())
+            h = ops.MoEGemm(rows, w1, r, None, 1)
+            act = (torch.nn.functional.silu(h[:, :I].float()) * h[:, I:].float()).to(torch.bfloat16)
+            return ops.MoEGemm(act, w2, r, None, 1)
+
+        for T in (48, 300):
+            gt = torch.Generator().manual_seed(10 * T + rank)
+            x = torch.randn(T, H, generator=gt).to(torch.bfloat16).to(dev)
+            logits = torch.randn(T, E, generator=gt)
+            w, ids = torch.topk(torch.softmax(logits, 1), topk, dim=1)
+            w, ids = w.to(dev), ids.to(dev)
+            got = ep.forward(x, ids, w, lambda rows, order, le: expert_block(rows, order, le, W1[ep.lo:ep.hi], W2[ep.lo:ep.hi]))
+            # one GPU, all experts, same tokens
+            flat = ids.reshape(-1)
+            se, sp = torch.sort(flat, stable=True)
+            rows = x.index_select(0, sp // topk)
+            order = torch.arange(rows.shape[0], device=dev)
+            y = expert_block(rows, order, se, W1, W2)
+            want = torch.zeros(T, H, device=dev)
+            want.index_add_(0, sp // topk, y.float() * w.reshape(-1).index_select(0, sp)[:, None])
+            torch.cuda.synchronize(dev)
+            err = ((got - want).norm() / want.norm()).item()
+            assert err <= 1e-3, f"rank {rank} T={T} rel err {err}"
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, repr(e)))
+    finally:
+        dist.barrier()
+        torch.cuda.synchronize(dev)
+        os._exit(0)
+
+
+def test_expert_parallel_matches_single_gpu():
+    world = torch.cuda.device_count()
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    world = min(world, 4)
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(60)
+    assert res == {r: "ok" for r in range(world)}, res
