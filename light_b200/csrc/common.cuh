@@ -49,6 +49,7 @@ int gguf_matmul_generic(int type, const float *x, const void *w, float *out, int
 // returns 1 when a fast decode kernel took the call, 0 when the shape is not covered, <0 on error
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
 int gguf_gemv_fast_init(int device);
+int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
 int gguf_gemv_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int act,
                     int K, cudaStream_t st);
 // batched decode (2..64 rows): 1 = took the call, 0 = not covered, other = error

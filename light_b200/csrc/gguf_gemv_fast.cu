@@ -340,6 +340,211 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
   cp_async_wait<0>();
 }
 
+// ------------------------------------------------------------------------------------ Q4_K, 2 .. 8 rows of x
+//
+// The same persistent, ring-fed decomposition as q4k_gemv_mma_kernel, with the eight MMA columns
+// given to eight TOKENS.  A lane then needs weights that carry their sub-block scale, because one
+// accumulator sums over the whole 256-element block:
+//   * codes -> f16 (64 + q) by LOP3 as before, then ONE HFMA2 with the 6-bit scale: (64 + q) * sc
+//     - 64 * sc = q * sc, exact (an integer below 2048).  D = sum_k (q * sc)_k x_k over the block,
+//     accumulated by the tensor core; once per block and row, acc += d * D.
+//   * the minimum term -dmin * m_s * sum_{k in s} x_k is a second tiny contraction over the eight
+//     sub-blocks: A' = -dmin * m split into f16 hi + lo (k slots 0-7 and 8-15), B' = the
+//     per-sub-block sums of x as f16 hi (both k halves), then A' = hi only against the lo half of
+//     the sums: two MMAs per block, straight into the running accumulator.
+// x is rounded to f16 (no hi/lo split of the activations themselves): 2^-11 relative per element,
+// about 2e-4 relative L2 on the output, inside the 1e-3 bound for M >= 2.
+// A warp converts its K block's x for all tokens into a private slab (token stride 544 B: the
+// 8-byte B-fragment loads of lanes (token g, t) fall into distinct banks), once per group of four
+// row tiles.
+constexpr int TOK = 8;                       // tokens per launch (MMA N)
+constexpr int TOK_PITCH = 544;               // bytes per token in a warp's slab
+constexpr int TOK_SX = TOK * TOK_PITCH;      // then per token: 8 sub-block sums as f16 hi | 8 as f16 lo
+constexpr int TOK_SLAB = TOK_SX + TOK * 32;
+constexpr int Q4K_TOK_STAGES = 3;
+constexpr int Q4K_TOK_SMEM = WARPS * Q4K_TOK_STAGES * Q4K_TILE_BYTES + WARPS * TOK_SLAB + WARPS * GROUP * 32 * 16;
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
+
+template <int S>
+__global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float *__restrict__ x, const uint8_t *__restrict__ w,
+                                                                    float *__restrict__ out, int M, int N, int K) {
+  extern __shared__ __align__(16) unsigned char dyn[];  // [ring: WARPS x S tiles][slabs: WARPS][red: WARPS x GROUP x 32 float4]
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int nb = K >> 8;
+  const uint32_t row_bytes = (uint32_t)nb * 144u;
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dyn);
+  const uint32_t ring = sbase + warp * (S * Q4K_TILE_BYTES);
+  const uint32_t slab = sbase + WARPS * S * Q4K_TILE_BYTES + warp * TOK_SLAB;
+  const uint32_t red = sbase + WARPS * S * Q4K_TILE_BYTES + WARPS * TOK_SLAB;
+  const uint32_t red_lane = red + (uint32_t)((warp * GROUP) * 32 + lane) * 16u;
+  const bool hdr_hi = t >= 2;
+  const int hdr_sh = (t & 1) * 16;
+  const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
+
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const int t0 = (int)((uint32_t)tiles * blockIdx.x / gridDim.x), t1 = (int)((uint32_t)tiles * (blockIdx.x + 1) / gridDim.x);
+  uint32_t soff[5];
+#pragma unroll
+  for (int i = 0; i < 5; i++) {
+    const uint32_t c = lane + 32 * i, row = c / 9u;
+    soff[i] = row * row_bytes + (c - 9u * row) * 16u;
+  }
+  const uint32_t ld_off = g * 144u + 32u * t;
+
+  int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_gt < t1 && warp < nb) {
+      const int r0 = min((i_gt + i_rt) * ROWS, N - ROWS);
+      const uint8_t *base = w + ((size_t)r0 * row_bytes + (uint32_t)i_b * 144u);
+      const uint32_t dst = ring + i_slot * Q4K_TILE_BYTES + lane * 16;
+#pragma unroll
+      for (int i = 0; i < 4; i++) cp_async16(dst + i * 512, base + soff[i]);
+      if (lane < 16) cp_async16(dst + 2048, base + soff[4]);
+      i_slot = i_slot + 1 == S ? 0 : i_slot + 1;
+      if (++i_rt == i_gs) {
+        i_rt = 0, i_b += WARPS;
+        if (i_b >= nb) i_b = warp, i_gt += i_gs, i_gs = min(GROUP, t1 - i_gt);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int p = 0; p < S; p++) issue();
+  pdl_wait();  // x is the previous launch's output; the weights requested above are not
+
+  int slot = 0;
+  for (int gt = t0; gt < t1; gt += GROUP) {
+    const int gs = min(GROUP, t1 - gt);
+    float acc[GROUP][4];
+#pragma unroll
+    for (int r = 0; r < GROUP; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+    for (int b = warp; b < nb; b += WARPS) {
+      // ---- this block's activations, all tokens, into the warp's slab.  A token's 256 values are 64
+      // float4: lane l takes float4 l and l + 32 (coalesced), i.e. four values of sub-block l / 8 (+ 4).
+      __syncwarp();  // every lane is done reading the previous block's slab
+#pragma unroll 4
+      for (int tk = 0; tk < TOK; tk++) {
+        const float4 *xp = reinterpret_cast<const float4 *>(x + (size_t)tk * K + b * 256);
+        float4 v[2];
+        v[0] = v[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tk < M) v[0] = __ldg(xp + lane), v[1] = __ldg(xp + lane + 32);
+        float s[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          const int F = lane + 32 * j;  // elements 4F .. 4F+3 = 64 (F / 16) + 32 ((F / 8) & 1) + 4 (F & 7) + 0..3
+          const __half2 lim = __float2half2_rn(65504.f);
+          const __half2 h02 = __hmax2(__hmin2(__floats2half2_rn(v[j].x, v[j].z), lim), __hneg2(lim));
+          const __half2 h13 = __hmax2(__hmin2(__floats2half2_rn(v[j].y, v[j].w), lim), __hneg2(lim));
+          sts64(slab + tk * TOK_PITCH + (uint32_t)((((F >> 3) & 1) * 8 + (F & 7)) * 4 + (F >> 4)) * 8u, h2_as_u32(h02), h2_as_u32(h13));
+          // the sums are those of the ROUNDED values, the ones the tensor core multiplies
+          const float2 a = __half22float2(h02), c = __half22float2(h13);
+          float p = (a.x + a.y) + (c.x + c.y);
+          p += __shfl_xor_sync(0xffffffffu, p, 1), p += __shfl_xor_sync(0xffffffffu, p, 2), p += __shfl_xor_sync(0xffffffffu, p, 4);
+          s[j] = p;  // sub-block (lane / 8) + 4 j
+        }
+        // lanes 0 and 16 (j = 0: sub-blocks 0,1 / 2,3; j = 1: 4,5 / 6,7) write the hi | lo pairs
+        const float n0 = __shfl_down_sync(0xffffffffu, s[0], 8), n1 = __shfl_down_sync(0xffffffffu, s[1], 8);
+        if ((lane & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < 2; j++) {
+            const float a0 = s[j], a1 = j ? n1 : n0;
+            const __half2 hi = __floats2half2_rn(a0, a1);
+            const float2 hf = __half22float2(hi);
+            const __half2 lo = __floats2half2_rn(a0 - hf.x, a1 - hf.y);
+            const uint32_t at = slab + TOK_SX + tk * 32 + 4 * ((lane >> 4) + 2 * j);
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at), "r"(h2_as_u32(hi)));
+            asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at + 16), "r"(h2_as_u32(lo)));
+          }
+        }
+      }
+      __syncwarp();
+      const uint32_t bx = slab + g * TOK_PITCH + t * 8;  // B fragments of token g
+      const uint32_t sx_hi = lds32(slab + TOK_SX + g * 32 + 4 * t), sx_lo = lds32(slab + TOK_SX + g * 32 + 16 + 4 * t);
+#pragma unroll
+      for (int rt = 0; rt < GROUP; rt++) {
+        if (rt < gs) {
+          cp_async_wait<S - 1>();  // this lane's chunks of the tile have landed ...
+          __syncwarp();            // ... and so have the other lanes'
+          const uint32_t sb = ring + slot * Q4K_TILE_BYTES + ld_off;
+          slot = slot + 1 == S ? 0 : slot + 1;
+          const uint4 h0 = lds128(sb - 32u * t), h1 = lds128(sb - 32u * t + 8 * 144);
+          const uint4 qa0 = lds128(sb + 16), qa1 = lds128(sb + 32);
+          const uint4 qb0 = lds128(sb + 8 * 144 + 16), qb1 = lds128(sb + 8 * 144 + 32);
+          __syncwarp();  // the slot is free again
+          issue();
+          // 6-bit scales and minima of sub-blocks 2t, 2t+1 of rows g (h0) and g+8 (h1)
+          __half2 s2[2][2], c2[2][2];
+          uint32_t dmh[2], dml[2];
+          float dd[2];
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            const uint4 &h = r ? h1 : h0;
+            const float2 df = __half22float2(u32_as_h2(h.x));  // (d, dmin)
+            const uint32_t scw = hdr_hi ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
+            const uint32_t mnw = hdr_hi ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
+            const uint32_t sc = scw >> hdr_sh, mn = mnw >> hdr_sh;
+            s2[r][0] = __half2half2(__uint2half_rn(sc & 0xFFu)), s2[r][1] = __half2half2(__uint2half_rn((sc >> 8) & 0xFFu));
+            c2[r][0] = __hmul2(s2[r][0], __float2half2_rn(-64.f)), c2[r][1] = __hmul2(s2[r][1], __float2half2_rn(-64.f));
+            const float m0 = -df.y * (float)(mn & 0xFFu), m1 = -df.y * (float)((mn >> 8) & 0xFFu);
+            const __half2 mh = __floats2half2_rn(m0, m1);
+            const float2 mf = __half22float2(mh);
+            dmh[r] = h2_as_u32(mh), dml[r] = h2_as_u32(__floats2half2_rn(m0 - mf.x, m1 - mf.y));
+            dd[r] = df.x;
+          }
+          float dq[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+          const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+          auto scl = [](uint32_t raw, __half2 s, __half2 c) { return h2_as_u32(__hfma2(u32_as_h2(raw), s, c)); };
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const uint32_t vg = qg[i], vh = qh[i];
+            const uint32_t e0 = scl(and_or(vg << 4, mask, magic), s2[0][0], c2[0][0]), e1 = scl(and_or(vh << 4, mask, magic), s2[1][0], c2[1][0]);
+            const uint32_t e2 = scl(and_or(vg >> 4, mask, magic), s2[0][0], c2[0][0]), e3 = scl(and_or(vh >> 4, mask, magic), s2[1][0], c2[1][0]);
+            const uint32_t o0 = scl(and_or(vg, mask, magic), s2[0][1], c2[0][1]), o1 = scl(and_or(vh, mask, magic), s2[1][1], c2[1][1]);
+            const uint32_t o2 = scl(and_or(vg >> 8, mask, magic), s2[0][1], c2[0][1]), o3 = scl(and_or(vh >> 8, mask, magic), s2[1][1], c2[1][1]);
+            const uint2 be = lds64(bx + i * 32), bo = lds64(bx + (8 + i) * 32);
+            mma16816(dq, e0, e1, e2, e3, be.x, be.y);
+            mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
+          }
+          acc[rt][0] = fmaf(dd[0], dq[0], acc[rt][0]), acc[rt][1] = fmaf(dd[0], dq[1], acc[rt][1]);
+          acc[rt][2] = fmaf(dd[1], dq[2], acc[rt][2]), acc[rt][3] = fmaf(dd[1], dq[3], acc[rt][3]);
+          mma16816(acc[rt], dmh[0], dmh[1], dml[0], dml[1], sx_hi, sx_hi);
+          mma16816(acc[rt], dmh[0], dmh[1], 0u, 0u, sx_lo, 0u);
+        }
+      }
+    }
+    // ---- add up the warps' parts: lane (g, t) of tile rt holds rows g, g+8 x tokens 2t, 2t+1
+    __syncthreads();  // the previous group's sums have been read
+#pragma unroll
+    for (int rt = 0; rt < GROUP; rt++)
+      asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"r"(red_lane + rt * 512), "f"(acc[rt][0]), "f"(acc[rt][1]),
+                   "f"(acc[rt][2]), "f"(acc[rt][3]));
+    __syncthreads();
+    for (int i = threadIdx.x; i < gs * ROWS * TOK; i += WARPS * 32) {
+      const int row = i & 15, tok = (i >> 4) & 7, rt = i >> 7;
+      const uint32_t a = red + (uint32_t)(rt * 32 + (row & 7) * 4 + (tok >> 1)) * 16u + (uint32_t)((row >> 3) * 2 + (tok & 1)) * 4u;
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) {
+        if (wq >= nb) break;  // a warp without a K block holds zeros it never stored
+        float p;
+        asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(p) : "r"(a + wq * (GROUP * 512)));
+        v += p;
+      }
+      if (tok < M) out[(size_t)tok * N + min((gt + rt) * ROWS, N - ROWS) + row] = v;
+    }
+  }
+  cp_async_wait<0>();
+}
+
 // ------------------------------------------------------------------------------------ Q6_K
 //
 // Block (210 B): [ql[128] | qh[64] | int8 sc[16] | f16 d]; element e = 128h + 32q + l
@@ -362,11 +567,6 @@ constexpr int Q6K_PITCH = 240;
 constexpr int Q6K_TILE_BYTES = ROWS * Q6K_PITCH;
 constexpr int Q6K_STAGES = 2;
 
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
@@ -609,6 +809,8 @@ int gguf_gemv_fast_init(int device) {
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                WARPS * Q6K_STAGES * Q6K_TILE_BYTES);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q4K_TOK_SMEM);
   if (err != cudaSuccess) return fail((int)err, "light_b200: init (decode): %s", cudaGetErrorString(err));
   return 0;
 }
@@ -645,6 +847,18 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
   int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x, wb, out, N, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
+  return rc ? rc : 1;
+}
+
+// 2 .. 8 activation rows against one Q4_K matrix, tokens as MMA columns.  Returns 1 if launched, 0 if
+// the shape is not covered.
+int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
+  if (type != LB200_Q4_K || M < 2 || M > TOK || K % 256 || N < ROWS || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const unsigned grid = (unsigned)(tiles < g_sms * 2 ? tiles : g_sms * 2);
+  int rc = launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, (const uint8_t *)w, out, M, N, K);
+  if (rc) return rc;
+  rc = launched("matmul_q (decode, 2-8 rows)");
   return rc ? rc : 1;
 }
 
