@@ -138,11 +138,11 @@ int light_b200_matmul_q(int t, const float *x, const void *w, float *out, int M,
   if (took) return 0;
   took = gguf_gemv_tok(t, x, w, out, M, N, K, st);
   if (took != 0) return took == 1 ? 0 : took;
+  took = gguf_prefill(t, x, w, out, M, N, K, device, st);
+  if (took != 0) return took == 1 ? 0 : took;
   took = gguf_decode_umma(t, x, w, out, M, N, K, device, st);
   if (took != 0) return took == 1 ? 0 : took;
   took = gguf_gemv_batch(t, x, w, out, M, N, K, st);
-  if (took != 0) return took == 1 ? 0 : took;
-  took = gguf_prefill(t, x, w, out, M, N, K, device, st);
   if (took != 0) return took == 1 ? 0 : took;
   return gguf_matmul_generic(t, x, w, out, M, N, K, st);
 }
@@ -239,8 +239,8 @@ int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *s, c
   REQUIRE_PTR(y, "int4_gemv");
   if (!aligned(codes, 16) || !aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: int4_gemv: x and codes must be 16-byte aligned");
   if (int rc = bind(device)) return rc;
-  if (int took = int4_decode_umma(x, codes, s, z, y, act_dtype, M, N, K, G, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = int4_prefill(x, codes, s, z, y, act_dtype, M, N, K, G, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
+  if (int took = int4_decode_umma(x, codes, s, z, y, act_dtype, M, N, K, G, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   return int4_gemv(x, codes, s, z, y, act_dtype, M, N, K, G, (cudaStream_t)stream);
 }
 
@@ -270,8 +270,8 @@ int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *s, v
   REQUIRE_PTR(y, "fp8_block_gemv");
   if (!aligned(w, 16) || !aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: fp8_block_gemv: x and w must be 16-byte aligned");
   if (int rc = bind(device)) return rc;
-  if (int took = fp8_decode_umma(x, w, s, y, act_dtype, M, N, K, bR, bC, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = fp8_prefill(x, w, s, y, act_dtype, M, N, K, bR, bC, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
+  if (int took = fp8_decode_umma(x, w, s, y, act_dtype, M, N, K, bR, bC, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   return fp8_block_gemv(x, w, s, y, act_dtype, M, N, K, bR, bC, (cudaStream_t)stream);
 }
 

@@ -40,7 +40,8 @@ constexpr int NUM_DEQ_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = SA * A_STAGE + SB * B_STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
 
-__device__ int g_prefill_status;  // non-zero: a bounded wait gave up (sticky, read by the host on demand)
+__device__ int g_prefill_status;
+int g_sm_count_pf = 148;  // SMs of the device (set on first use)  // non-zero: a bounded wait gave up (sticky, read by the host on demand)
 
 // Grouped (mixture-of-experts) mode: the token rows of the A operand have been gathered into expert
 // order, expert e owns rows offsets[e] .. offsets[e+1] of it; output row i goes to pair sorted_pairs[i],
@@ -91,7 +92,11 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
     if (tile_info[0] < 0) return;  // beyond the last tile: the grid is sized for the worst case
     expert = tile_info[0], m0 = tile_info[1], m_end = tile_info[2];
   }
-  const int nkb = K / BK;
+  // K split (few tokens only): gridDim.z CTAs form a cluster, each takes a contiguous run of 256-element
+  // blocks; the partial tiles are added up through distributed shared memory at the end
+  const int KS = gridDim.z, krank = blockIdx.z;
+  const int kb0 = KS > 1 ? ((K >> 8) * krank / KS) * 4 : 0, kb1 = KS > 1 ? ((K >> 8) * (krank + 1) / KS) * 4 : K / BK;
+  const int nkb = kb1 - kb0;
   const bool two = bm > 128 && m0 + 128 < m_end;  // the second 128-row tile holds real rows
 
   if (threadIdx.x == 0) {
@@ -125,8 +130,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
         const int s = kb % SA;
         if (kb >= SA && !mbar_wait(a_empty + 8 * s, ((kb / SA) - 1) & 1, abort)) break;
         mbar_arrive_expect_tx(a_full + 8 * s, two ? A_STAGE : A_STAGE / 2);
-        tma_load_2d(sA + s * A_STAGE, &tmap_x, a_full + 8 * s, kb * BK, m0);
-        if (two) tma_load_2d(sA + s * A_STAGE + A_STAGE / 2, &tmap_x, a_full + 8 * s, kb * BK, m0 + 128);
+        tma_load_2d(sA + s * A_STAGE, &tmap_x, a_full + 8 * s, (kb0 + kb) * BK, m0);
+        if (two) tma_load_2d(sA + s * A_STAGE + A_STAGE / 2, &tmap_x, a_full + 8 * s, (kb0 + kb) * BK, m0 + 128);
         issued = kb + 1;
       }
       if (*abort)  // give the loads still in flight a bounded time to land before the CTA retires
@@ -154,7 +159,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
         mma_commit(a_empty + 8 * sa);
         mma_commit(b_empty + 8 * sb);
       }
-      mma_commit(d_full);
+      if (nkb > 0) mma_commit(d_full);
     }
   } else {
     // ---- weight expansion: thread r owns row n0 + r (clamped; rows past N are never stored)
@@ -162,15 +167,15 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
     const int n = min(n0 + r, N - 1);
     Row cur;
     cur.init(ctx, expert, n, N, K);
-    cur.load(0);
+    const int u0 = kb0 / Row::STEPS, units = kb1 / Row::STEPS;
+    if (u0 < units) cur.load(u0);
     bool ok = true;
-    const int units = K / (BK * Row::STEPS);
-    for (int u = 0; u < units && ok; u++) {
+    for (int u = u0; u < units && ok; u++) {
       Row nxt = cur;
       if (u + 1 < units) nxt.load(u + 1);
 #pragma unroll
       for (int j = 0; j < Row::STEPS; j++) {
-        const int kb = u * Row::STEPS + j, s = kb % SB;
+        const int kb = u * Row::STEPS + j - kb0, s = kb % SB;
         if (kb >= SB) {  // lane 0 waits for the stage to be free, the warp follows its verdict
           int got = 1;
           if (lane == 0) got = mbar_wait(b_empty + 8 * s, ((kb / SB) - 1) & 1, abort);
@@ -188,8 +193,28 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
     }
     // ---- epilogue: warp w reads TMEM lanes 32 (w % 4) .. +31 (tokens) and columns 128 (w / 4) .. +127
     int done = 0;
-    if (ok && lane == 0) done = mbar_wait(d_full, 0, abort);
-    if (__shfl_sync(0xffffffffu, done, 0)) {
+    if (ok && lane == 0) done = nkb > 0 ? (int)mbar_wait(d_full, 0, abort) : 1;
+    done = __shfl_sync(0xffffffffu, done, 0);
+    if (KS > 1) {
+      // partial[token][column] (257 floats per token: a warp writes one column of 32 tokens at a time)
+      // over the now idle stages; rows of the cluster's sum are shared out below
+      if (done) tc_fence_after();
+      const int quad = warp & 3, chalf = warp >> 2;
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t v[32];
+#pragma unroll
+        for (int i = 0; i < 32; i++) v[i] = 0u;
+        if (done && nkb > 0) {
+          tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + chalf * 128 + c * 32, v);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i++)
+          asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(base + (uint32_t)((quad * 32 + lane) * 257 + chalf * 128 + c * 32 + i) * 4u),
+                       "r"(v[i]));
+      }
+    } else if (done) {
       tc_fence_after();
       const int quad = warp & 3, chalf = warp >> 2;
 #pragma unroll 1
@@ -240,9 +265,26 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
       }
     }
   }
+  __syncwarp();
   if (abort_flag && threadIdx.x == 0) g_prefill_status = 1;
   tc_fence_before();
-  __syncthreads();
+  if (KS > 1) {
+    cluster_sync();
+    const int rows_per = 128 / KS;  // tokens of the tile this CTA adds up and stores
+    if (threadIdx.x < BN) {
+      const int col = threadIdx.x;
+      for (int tt = 0; tt < rows_per; tt++) {
+        const int tok = krank * rows_per + tt;
+        const uint32_t a = base + (uint32_t)(tok * 257 + col) * 4u;
+        float v = 0.f;
+        for (int p = 0; p < KS; p++) v += ld_cluster_f32(map_to_rank(a, (uint32_t)p));
+        if (m0 + tok < m_end && n0 + col < N) st_act(out, (long long)(m0 + tok) * N + n0 + col, v);
+      }
+    }
+    cluster_sync();  // nobody leaves while a peer still reads its partials
+  } else {
+    __syncthreads();
+  }
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
@@ -327,9 +369,32 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
   // (measured: a 128-row tile takes 0.75 of a 256-row tile)
   int bm = (!grp.offsets && waves_cost(128) < waves_cost(256)) ? 128 : 256;
   if (const char *e = getenv("LIGHT_B200_PREFILL_BM")) bm = (atoi(e) == 128 && !grp.offsets) ? 128 : atoi(e) == 256 ? 256 : bm;
+  // Few tokens (one 128-row tile) and few weight-row tiles: split K over a cluster of up to 8 CTAs so that
+  // every SM has one, the smallest power of two that does
+  int ks = 1;
+  if (!grp.offsets && M <= 128 && K % 256 == 0) {
+    bm = 128;
+    const int nblk = K >> 8;
+    while (ks < 8 && ks * 2 <= nblk && nt * ks < g_sm_count_pf) ks *= 2;
+  }
   // grouped: at most ceil(M / bm) + E tiles (every expert can end with one partial tile)
-  dim3 grid((unsigned)nt, (M + bm - 1) / bm + (grp.offsets ? grp.E : 0));
-  kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, bm);
+  dim3 grid((unsigned)nt, (M + bm - 1) / bm + (grp.offsets ? grp.E : 0), (unsigned)ks);
+  if (ks == 1) {
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, bm);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = (unsigned)ks;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm, ctx, grp, out, M, N, K, bm);
+    if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
+  }
   return launched("prefill (tcgen05)");
 }
 
@@ -367,7 +432,16 @@ int set_workspace(int device, void *ptr, size_t bytes) {
   return 0;
 }
 
-constexpr int PREFILL_MIN_M = 65;
+int g_prefill_min_m = 65;  // LIGHT_B200_PREFILL_MIN_M (tuning knob): fewest activation rows this kernel takes
+bool g_pf_knobs = false;
+void pf_knobs() {
+  if (g_pf_knobs) return;
+  if (const char *e = getenv("LIGHT_B200_PREFILL_MIN_M")) g_prefill_min_m = atoi(e) < 1 ? 1 : atoi(e);
+  int dev = 0, v = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) g_sm_count_pf = v;
+  g_pf_knobs = true;
+}
+#define PREFILL_MIN_M (pf_knobs(), g_prefill_min_m)
 
 // Each returns 1 when the tensor-core prefill kernel took the call, 0 when the shape (or the workspace)
 // does not allow it, any other value is an error.

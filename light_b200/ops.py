@@ -138,7 +138,7 @@ def MatMulQ(x: torch.Tensor, w: QTensor) -> torch.Tensor:
         raise ValueError(f"MatMulQ: inner dim mismatch (x K={K}, w K={w.shape[1]})")
     dev = _dev(x, "MatMulQ")
     xc = x.contiguous()
-    if M > 64:  # the tensor-core prefill path streams an f16 copy of x from the workspace
+    if M > 8:  # the tensor-core paths stream an f16 copy of x from the workspace
         ensure_workspace(dev, M * K * 2)
     out = torch.empty((M, N), dtype=torch.float32, device=x.device)
     _lib.check(_lib.lib().light_b200_matmul_q(w.ggml_type, _ptr(xc), _ptr(w.data), _ptr(out), M, N, K, dev,
