@@ -211,6 +211,25 @@ LB200_API int light_b200_comm_step_begin(uint32_t *step, int device, void *strea
 LB200_API int light_b200_allgather_ll(const float *local, float *out, const lb200_peers *peers, int M, int n_local,
                                       const uint32_t *step, int device, void *stream);
 
+/* Row-split decode matmul with the exchange INSIDE the launch (one activation row; Q4_K: up to four
+ * matrices that share it, Q6_K: one).  Rank `rank` of `world` holds rows [rank n[i], (rank + 1) n[i]) of
+ * output i.  For an output the next operator needs in full, out_slots[i][p] is rank p's receive buffer for it
+ * (2 * world * n[i] slots of 8 bytes, two step parities, peer-addressable, zeroed once): the launch's epilogue
+ * stores every value it owns there as {f32, step tag}, on every rank.  out_slots[i][*] all NULL keeps output
+ * i local (out[i], n[i] f32, is written in either case).  The activations come either as plain f32 (x, K
+ * values; x_slots NULL) or as this rank's receive buffer of the launch that produced them (x_slots, 2 * K
+ * slots; x ignored): the kernel polls the slots until they carry the step's tag (about 50 ms at most, then
+ * light_b200_comm_status reports it), so no gather launch stands between two matmuls.  `step` as for
+ * light_b200_allgather_ll.  Fails with LB200_E_SHAPE when no single-launch kernel covers the shape. */
+typedef struct lb200_tp {
+  const void *x_slots;
+  void *out_slots[4][LB200_MAX_PEERS];
+  const uint32_t *step;
+  int32_t world, rank;
+} lb200_tp;
+LB200_API int light_b200_matmul_q_tp(int ggml_type, const float *x, const void *const *w, float *const *out,
+                                     const int32_t *n, int count, int K, const lb200_tp *tp, int device, void *stream);
+
 /* 0, or 1 if a bounded wait on a peer ever gave up on this device.  Synchronises with the device. */
 LB200_API int light_b200_comm_status(int device);
 

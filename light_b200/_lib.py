@@ -26,6 +26,12 @@ class Peers(C.Structure):
     _fields_ = [("slots", C.c_void_p * 8), ("world", C.c_int32), ("rank", C.c_int32)]
 
 
+class TpArgs(C.Structure):
+    """lb200_tp: activations as a receive buffer (or NULL), per-output receive buffers of every rank, step word."""
+    _fields_ = [("x_slots", C.c_void_p), ("out_slots", (C.c_void_p * 8) * 4), ("step", C.c_void_p),
+                ("world", C.c_int32), ("rank", C.c_int32)]
+
+
 class MoeArgs(C.Structure):
     _fields_ = [
         ("input", C.c_void_p), ("weights", C.c_void_p), ("sorted_pairs", C.c_void_p), ("expert_ids", C.c_void_p),
@@ -42,6 +48,8 @@ SYMBOLS = {
     "light_b200_abi_version": (C.c_int, []),
     "light_b200_launch_count": (C.c_ulonglong, []),
     "light_b200_comm_step_begin": (C.c_int, [C.c_void_p, C.c_int, C.c_void_p]),
+    "light_b200_matmul_q_tp": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int32),
+                                         C.c_int, C.c_int, C.POINTER(TpArgs), C.c_int, C.c_void_p]),
     "light_b200_allgather_ll": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(Peers), C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]),
     "light_b200_comm_status": (C.c_int, [C.c_int]),
     "light_b200_set_workspace": (C.c_int, [C.c_int, C.c_void_p, C.c_size_t]),

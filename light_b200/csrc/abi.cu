@@ -108,7 +108,31 @@ int light_b200_allgather_ll(const float *local, float *out, const lb200_peers *p
 
 int light_b200_comm_status(int device) {
   if (int rc = bind(device)) return rc;
-  return comm_status();
+  const int a = comm_status(), b = gemv_tp_status();
+  return a ? a : b;
+}
+
+int light_b200_matmul_q_tp(int t, const float *x, const void *const *w, float *const *out, const int32_t *n, int count,
+                           int K, const lb200_tp *tp, int device, void *stream) {
+  if (t != LB200_Q4_K && t != LB200_Q6_K) return fail(LB200_E_DTYPE, "light_b200: matmul_q_tp: ggml type %d has no row-split kernel", t);
+  if (count < 1 || count > 4) return fail(LB200_E_SHAPE, "light_b200: matmul_q_tp: %d matrices, want 1..4", count);
+  if (K <= 0 || K % 256) return fail(LB200_E_SHAPE, "light_b200: matmul_q_tp: K=%d not a multiple of 256", K);
+  REQUIRE_PTR(w, "matmul_q_tp");
+  REQUIRE_PTR(out, "matmul_q_tp");
+  REQUIRE_PTR(n, "matmul_q_tp");
+  REQUIRE_PTR(tp, "matmul_q_tp");
+  if (!tp->x_slots) REQUIRE_PTR(x, "matmul_q_tp");
+  REQUIRE_PTR(tp->step, "matmul_q_tp");
+  if (tp->world < 1 || tp->world > LB200_MAX_PEERS || tp->rank < 0 || tp->rank >= tp->world)
+    return fail(LB200_E_SHAPE, "light_b200: matmul_q_tp: rank %d of %d", tp->rank, tp->world);
+  for (int i = 0; i < count; i++)
+    if (n[i] <= 0 || !w[i] || !out[i]) return fail(LB200_E_NULL, "light_b200: matmul_q_tp: matrix %d: null pointer or no rows", i);
+  if (int rc = bind(device)) return rc;
+  const int took = gguf_gemv_tp(t, x, tp->x_slots, w, out, n, count, K, (void *const *)tp->out_slots, tp->step, tp->world,
+                                tp->rank, (cudaStream_t)stream);
+  if (took == 1) return 0;
+  if (took == 0) return fail(LB200_E_SHAPE, "light_b200: matmul_q_tp: no single-launch kernel for this shape or alignment");
+  return took;
 }
 
 int light_b200_prefill_status(int device) {

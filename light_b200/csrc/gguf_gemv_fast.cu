@@ -123,6 +123,46 @@ __device__ __forceinline__ void q4k_scales(const uint4 &h, bool hi, int sh, floa
 }
 
 
+// ---- row-split execution over several GPUs, with the exchange inside the matmul launches.
+// A rank computes rows [rank n, (rank + 1) n) of an output of `world` n rows.  Instead of a gather
+// launch between two matmuls, the PRODUCER's epilogue stores every value it owns, as an 8-byte
+// {value, step tag} slot, into the receive buffer of every rank (plain NVLink peer stores; its own
+// rank included), and the CONSUMER's activation load polls its own receive buffer until the slots
+// carry the current step's tag: the data is its own arrival flag, there is no fence and no extra
+// launch.  Receive buffers hold two sets of slots, used on alternating steps.
+struct TpArgs {
+  const uint2 *x_slots;                // this launch's activations as 2 K slots (two step parities); nullptr: plain f32 x
+  uint2 *peer[4][LB200_MAX_PEERS];     // per matrix: every rank's receive buffer for its output; peer[j][0] == nullptr: not exchanged
+  const unsigned int *step;            // device step word: the tag
+  int world, rank;
+};
+
+__device__ int g_tp_status;  // non-zero: a bounded wait for a peer's activations gave up (sticky)
+
+// four consecutive slots -> four activations, once all four carry `tag` (bounded: about 50 ms)
+__device__ __forceinline__ float4 ld_slots4(const uint2 *s, unsigned int tag, unsigned long long t0, bool &gave_up) {
+  uint4 a, b;
+  for (unsigned int it = 0;; it++) {
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(s) : "memory");
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(s + 2) : "memory");
+    if ((a.y == tag && a.w == tag && b.y == tag && b.w == tag) || gave_up) break;
+    if ((it & 255u) == 255u) {
+      unsigned long long t1;
+      asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t1));
+      if (t1 - t0 > 50000000ull) {  // a peer is gone or a step behind for good
+        g_tp_status = 1;
+        gave_up = true;
+      }
+    }
+  }
+  return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+}
+// one output value of row `e` of the full-height output to every rank
+__device__ __forceinline__ void st_slots(uint2 *const (&peer)[LB200_MAX_PEERS], int world, size_t e, float v, unsigned int tag) {
+  for (int p = 0; p < world; p++)
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(peer[p] + e), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+
 // Up to four weight matrices that share one activation row and one K, served by ONE launch: the
 // row tiles of all of them form one list, which the CTAs split evenly.  With act != 0 there are
 // two matrices of equal height (gate, up), their tiles alternate in the list, and the launch
@@ -181,7 +221,7 @@ constexpr int Q4K_SLAB = Slab<32>::BYTES + 16;  // a block's activations + its p
 template <int S, int MINB>
 __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const float *__restrict__ x,
                                                                        const __grid_constant__ MultiArgs a,
-                                                                       int tiles, int K) {
+                                                                       const __grid_constant__ TpArgs tp, int tiles, int K) {
   using SL = Slab<32>;
   extern __shared__ __align__(16) unsigned char dyn[];  // [ring: WARPS x S tiles][slabs: K/256]
   __shared__ __align__(16) unsigned char zero[SL::ZERO_BYTES];
@@ -243,10 +283,21 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
 #pragma unroll 1
   for (int p = 0; p < S; p++) issue();
   pdl_wait();  // x is the previous launch's output; the weights requested above are not
+  unsigned int tag = 0;
+  if (tp.step) tag = *reinterpret_cast<const volatile unsigned int *>(tp.step);
+  unsigned long long tp_t0 = 0;
+  bool tp_gave_up = false;
+  if (tp.x_slots) asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(tp_t0));
   for (int b = warp; b < nb; b += WARPS) {
     float4 xv[2];
-    xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
-    xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+    if (tp.x_slots) {  // the peers' parts of x arrive as tagged slots
+      const uint2 *xs = tp.x_slots + (size_t)(tag & 1u) * K + b * 256 + lane * 4;
+      xv[0] = ld_slots4(xs, tag, tp_t0, tp_gave_up);
+      xv[1] = ld_slots4(xs + 128, tag, tp_t0, tp_gave_up);
+    } else {
+      xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+      xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+    }
     const uint32_t slab = slabs + b * Q4K_SLAB;
     const float up = stage_block<32>(xv, slab, lane);
     if (lane == 0) asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(slab + SL::BYTES), "f"(up));
@@ -326,14 +377,18 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
         const int pr = i >> 4, row = i & 15;
         int j, r0;
         resolve_tile(a, gt + 2 * pr, j, r0);
-        a.out[0][r0 + row] = gate_act(row_sum(2 * pr, row), a.act) * row_sum(2 * pr + 1, row);
+        const float v = gate_act(row_sum(2 * pr, row), a.act) * row_sum(2 * pr + 1, row);
+        a.out[0][r0 + row] = v;
+        if (tp.peer[0][0]) st_slots(tp.peer[0], tp.world, (size_t)(tag & 1u) * a.n[0] * tp.world + (size_t)tp.rank * a.n[0] + r0 + row, v, tag);
       }
     } else {
       for (int i = threadIdx.x; i < gs * ROWS; i += WARPS * 32) {
         const int rt = i >> 4, row = i & 15;
         int j, r0;
         resolve_tile(a, gt + rt, j, r0);
-        a.out[j][r0 + row] = row_sum(rt, row);
+        const float v = row_sum(rt, row);
+        a.out[j][r0 + row] = v;
+        if (tp.peer[j][0]) st_slots(tp.peer[j], tp.world, (size_t)(tag & 1u) * a.n[j] * tp.world + (size_t)tp.rank * a.n[j] + r0 + row, v, tag);
       }
     }
   }
@@ -582,7 +637,8 @@ __device__ __forceinline__ uint32_t lds32_skew(uint32_t addr) {
 template <int S>
 __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float *__restrict__ x,
                                                                     const uint8_t *__restrict__ w,
-                                                                    float *__restrict__ out, int N, int K) {
+                                                                    float *__restrict__ out, const __grid_constant__ TpArgs tp,
+                                                                    int N, int K) {
   using SL = Slab<16>;
   extern __shared__ __align__(16) unsigned char dyn[];  // ring: WARPS x S tiles
   __shared__ __align__(16) unsigned char slabs[WARPS][SL::BYTES];
@@ -657,9 +713,20 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
   pdl_wait();  // x is the previous launch's output; the weights requested above are not
   __syncthreads();
   float4 xn[2];  // the activations of the block this warp stages next, requested one block ahead
+  unsigned int tag = 0;
+  if (tp.step) tag = *reinterpret_cast<const volatile unsigned int *>(tp.step);
+  unsigned long long tp_t0 = 0;
+  bool tp_gave_up = false;
+  if (tp.x_slots) asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(tp_t0));
   auto load_x = [&](int b) {
-    xn[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
-    xn[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+    if (tp.x_slots) {  // the peers' parts of x arrive as tagged slots
+      const uint2 *xs = tp.x_slots + (size_t)(tag & 1u) * K + b * 256 + lane * 4;
+      xn[0] = ld_slots4(xs, tag, tp_t0, tp_gave_up);
+      xn[1] = ld_slots4(xs + 128, tag, tp_t0, tp_gave_up);
+    } else {
+      xn[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+      xn[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+    }
   };
   if (warp < nb) load_x(warp);
 
@@ -768,7 +835,9 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
 #pragma unroll
         for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;
       }
-      out[min((gt + rt) * ROWS, N - ROWS) + row] = v;
+      const int orow = min((gt + rt) * ROWS, N - ROWS) + row;
+      out[orow] = v;
+      if (tp.peer[0][0]) st_slots(tp.peer[0], tp.world, (size_t)(tag & 1u) * N * tp.world + (size_t)tp.rank * N + orow, v, tag);
     }
   }
   cp_async_wait<0>();
@@ -817,17 +886,19 @@ int gguf_gemv_fast_init(int device) {
 
 // One launch over up to four Q4_K matrices that share x (M = 1).  Returns 1 if launched, 0 if this
 // path does not apply, < 0 or a CUDA code on error.
-static int q4k_launch(const float *x, const MultiArgs &a, int tiles, int K, cudaStream_t st) {
+static int q4k_launch(const float *x, const MultiArgs &a, const TpArgs &tp, int tiles, int K, cudaStream_t st) {
   const size_t dyn = (size_t)WARPS * g_q4k_stages * Q4K_TILE_BYTES + (size_t)(K >> 8) * Q4K_SLAB;
   if (dyn > MAX_DYN_SMEM) return 0;  // very long rows: the activations do not fit beside the rings
   const int lt = a.act ? tiles / 2 : tiles;
   const unsigned grid = (unsigned)(lt < g_sms * g_waves ? lt : g_sms * g_waves);
-  int rc = g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 2>, grid, dyn, st, x, a, tiles, K)
-                             : launch_pdl(q4k_gemv_mma_kernel<4, 2>, grid, dyn, st, x, a, tiles, K);
+  int rc = g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 2>, grid, dyn, st, x, a, tp, tiles, K)
+                             : launch_pdl(q4k_gemv_mma_kernel<4, 2>, grid, dyn, st, x, a, tp, tiles, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
   return rc ? rc : 1;
 }
+
+static const TpArgs NO_TP = {};
 
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
   if (M != 1 || K % 256 || N < ROWS) return 0;
@@ -841,10 +912,10 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
   if (type == LB200_Q4_K) {
     MultiArgs a = {};
     a.w[0] = wb, a.out[0] = out, a.n[0] = N, a.tend[0] = tiles, a.count = 1;
-    return q4k_launch(x, a, tiles, K, st);
+    return q4k_launch(x, a, NO_TP, tiles, K, st);
   }
   const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
-  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x, wb, out, N, K);
+  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x, wb, out, NO_TP, N, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
   return rc ? rc : 1;
@@ -877,7 +948,50 @@ int gguf_gemv_multi(int type, const float *x, const void *const *w, float *const
     a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
   }
   a.count = count, a.act = act;
-  return q4k_launch(x, a, tiles, K, st);
+  return q4k_launch(x, a, NO_TP, tiles, K, st);
+}
+
+// Row-split matmul with the exchange inside the launch (see TpArgs): `count` matrices of one type that
+// share x; x comes as plain f32 (x) or as this rank's receive buffer of the producing launch (x_slots);
+// out_slots[i * LB200_MAX_PEERS + p] is rank p's receive buffer for output i, or all null for an output that
+// stays local.  Returns 1 if launched, 0 if no kernel covers the shape, else an error.
+int gguf_gemv_tp(int type, const float *x, const void *x_slots, const void *const *w, float *const *out, const int *n,
+                 int count, int K, void *const *out_slots, const unsigned int *step, int world, int rank, cudaStream_t st) {
+  if (K % 256 || count < 1 || count > 4 || world < 1 || world > LB200_MAX_PEERS || rank < 0 || rank >= world) return 0;
+  if (((uintptr_t)x_slots & 31) || (x && ((uintptr_t)x & 15))) return 0;
+  TpArgs tp = {};
+  tp.x_slots = (const uint2 *)x_slots, tp.step = step, tp.world = world, tp.rank = rank;
+  for (int i = 0; i < count; i++)
+    for (int p = 0; p < world; p++) {
+      tp.peer[i][p] = (uint2 *)out_slots[i * LB200_MAX_PEERS + p];
+      if ((tp.peer[i][p] == nullptr) != (tp.peer[i][0] == nullptr) || ((uintptr_t)tp.peer[i][p] & 7)) return 0;
+    }
+  if (type == LB200_Q4_K) {
+    MultiArgs a = {};
+    int tiles = 0;
+    for (int i = 0; i < count; i++) {
+      if (n[i] < ROWS || ((uintptr_t)w[i] & 15)) return 0;
+      tiles += (n[i] + ROWS - 1) / ROWS;
+      a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
+    }
+    a.count = count;
+    return q4k_launch(x, a, tp, tiles, K, st);
+  }
+  if (type != LB200_Q6_K || count != 1 || n[0] < ROWS || ((uintptr_t)w[0] & 15)) return 0;
+  if (((K >> 8) & 1) || (unsigned long long)n[0] * (K >> 8) * 210ull >= (1ull << 32)) return 0;
+  const int tiles = (n[0] + ROWS - 1) / ROWS;
+  const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
+  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x,
+                      (const uint8_t *)w[0], out[0], tp, n[0], K);
+  if (rc) return rc;
+  rc = launched("matmul_q (decode, row-split)");
+  return rc ? rc : 1;
+}
+
+int gemv_tp_status() {
+  int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_tp_status, sizeof(int));
+  return e == cudaSuccess ? v : -(int)e;
 }
 
 }  // namespace lb

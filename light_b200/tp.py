@@ -149,6 +149,95 @@ class PeerGather:
         return _lib.lib().light_b200_comm_status(self.device.index or 0)
 
 
+class FusedExchange:
+    """Row-split decode with the exchange inside the matmul launches (light_b200_matmul_q_tp): the
+    producing launch stores every value it owns, tagged with the step, into every rank's receive buffer
+    for that output, and the consuming launch polls its own receive buffer while it loads its activations.
+    No gather launch, no collective, no fence.
+
+    plan(widths) lays out one receive buffer (2 * N slots of 8 bytes) per exchanged output identically on
+    all ranks in symmetric memory (torch.distributed._symmetric_memory: plumbing only).
+    """
+
+    def __init__(self, device: torch.device, group=None):
+        import torch.distributed as dist
+
+        self.device, self.group = device, group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+
+    def plan(self, widths: list[int]) -> None:
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        offs, total = [], 0
+        for N in widths:
+            offs.append(total)
+            total += (2 * N * 8 + 255) // 256 * 256
+        arena = symm_mem.empty(max(total, 256), dtype=torch.uint8, device=self.device)
+        arena.zero_()
+        try:
+            hdl = symm_mem.rendezvous(arena, self.group)
+        except TypeError:
+            hdl = symm_mem.rendezvous(arena, self.group.group_name)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+        self.arena, self.handle = arena, hdl
+        ptrs = [int(p) for p in hdl.buffer_ptrs]
+        self.slots = [[ptrs[r] + off for r in range(self.world)] for off in offs]  # [output][rank] -> address
+        self.step = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def step_begin(self) -> None:
+        import ctypes as C
+
+        from . import _lib
+
+        dev = self.device.index or 0
+        _lib.check(_lib.lib().light_b200_comm_step_begin(C.c_void_p(self.step.data_ptr()), dev,
+                                                         C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+
+    def args(self, x_from: int | None, outs_to: list[int | None]):
+        """lb200_tp for one launch: activations from exchanged output `x_from` (None: plain x), output i to
+        exchanged output outs_to[i] (None: stays local)."""
+        from . import _lib
+
+        a = _lib.TpArgs()
+        a.x_slots = self.slots[x_from][self.rank] if x_from is not None else None
+        for i, o in enumerate(outs_to):
+            if o is not None:
+                for r in range(self.world):
+                    a.out_slots[i][r] = self.slots[o][r]
+        a.step = self.step.data_ptr()
+        a.world, a.rank = self.world, self.rank
+        return a
+
+    def matmul(self, ggml_type: int, x: torch.Tensor | None, ws: list[torch.Tensor], outs: list[torch.Tensor], K: int, args) -> None:
+        """One row-split launch: ws are this rank's row slices (block bytes), outs its local (n_i,) f32 outputs."""
+        import ctypes as C
+
+        from . import _lib
+
+        n = len(ws)
+        wp = (C.c_void_p * n)(*[w.data_ptr() for w in ws])
+        op = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+        nn = (C.c_int32 * n)(*[o.numel() for o in outs])
+        dev = self.device.index or 0
+        _lib.check(_lib.lib().light_b200_matmul_q_tp(ggml_type, C.c_void_p(x.data_ptr() if x is not None else 0), wp, op, nn, n, K,
+                                                     C.byref(args), dev, C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
+
+    def read(self, index: int, N: int) -> torch.Tensor:
+        """The exchanged output `index` of the step just run, as (N,) f32 (test helper: synchronises)."""
+        torch.cuda.synchronize(self.device)
+        par = int(self.step.item()) & 1
+        off = self.slots[index][self.rank] - int(self.handle.buffer_ptrs[self.rank])
+        sl = self.arena[off + par * N * 8: off + (par + 1) * N * 8].view(torch.float32).view(N, 2)
+        return sl[:, 0].clone()
+
+    def status(self) -> int:
+        from . import _lib
+
+        return _lib.lib().light_b200_comm_status(self.device.index or 0)
+
+
 class ExpertParallel:
     """Mixture-of-experts layer with the experts sharded over the ranks (E / P contiguous experts each)
     and a token all-to-all on either side of the local grouped matmuls -- the multi-GPU form of the
