@@ -138,22 +138,52 @@ class Chain:
         self.out = [torch.empty(M, e[2], device=device) for e in self.lin]  # full-width outputs (gathered when world > 1)
         self.local = [torch.empty(M, e[1], device=device) for e in self.lin] if world > 1 else self.out
         self.dev_index = device.index or 0
-        self.peer, self.gather_kind = None, "none"
+        self.peer, self.fx, self.gather_kind = None, None, "none"
         if world > 1:
+            from light_b200 import tp
+
             self.gidx = [i for i, e in enumerate(self.lin) if e[0].split(".")[-1] in self.GATHERED]
             self.gather_kind = "nccl"
-            if os.environ.get("LIGHT_B200_TP_GATHER", "peer") == "peer":
+            mode = os.environ.get("LIGHT_B200_TP_GATHER", "fused")
+            if mode in ("fused", "peer"):
                 try:
-                    from light_b200 import tp
-
+                    fused = mode == "fused" and self.fused  # the in-launch exchange serves one activation row
+                    pidx = [i for i in self.gidx if not fused or self.lin[i][0] == HEAD[0]]  # gathered by the gather kernel
                     self.peer = tp.PeerGather(device)
-                    outs = self.peer.plan([(M, self.lin[i][2]) for i in self.gidx])
-                    for j, i in enumerate(self.gidx):
+                    outs = self.peer.plan([(M, self.lin[i][2]) for i in pidx])
+                    for j, i in enumerate(pidx):
                         self.out[i] = outs[j]
+                    self.pidx = pidx
                     self.gather_kind = "peer"
+                    if fused:
+                        self._plan_fused(tp)
+                        self.gather_kind = "fused into the matmul launches (logits: peer-store gather kernel)"
                 except Exception as e:  # noqa: BLE001  (no peer mapping on this box: NCCL does the gathers)
-                    print(f"[bench] peer-memory gather unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
-                    self.peer = None
+                    print(f"[bench] peer-memory exchange unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+                    self.peer, self.fx = None, None
+                    self.gather_kind = "nccl"
+
+    def _plan_fused(self, tp):
+        """Receive buffers and per-launch arguments of the in-launch exchange: every launch but the first
+        takes its activations from the exchanged output before it (a real dependent chain: q -> o -> gate ->
+        down -> next layer's q ... -> lm_head), the logits are gathered by the gather kernel."""
+        fidx = [i for i in self.gidx if self.lin[i][0] != HEAD[0]]
+        fx = tp.FusedExchange(self.device)
+        fx.plan([self.lin[i][2] for i in fidx])
+        self.launch_args, prev = [], None
+        for idx in self.plan():
+            K = self.lin[idx[0]][3]
+            x_from = prev if prev is not None and self.lin[fidx[prev]][2] == K else None
+            outs_to = [fidx.index(i) if i in fidx else None for i in idx]
+            n = len(idx)
+            self.launch_args.append((fx.args(x_from, outs_to), x_from is None,
+                                     (C.c_void_p * n)(*[self.lin[i][5].data_ptr() for i in idx]),
+                                     (C.c_void_p * n)(*[self.local[i].data_ptr() for i in idx]),
+                                     (C.c_int32 * n)(*[self.lin[i][1] for i in idx])))
+            for o in outs_to:
+                if o is not None:
+                    prev = o
+        self.fx = fx
 
     def _make(self, name, N, K, dt, seed):
         assert N % self.world == 0
@@ -207,17 +237,24 @@ class Chain:
         n = 0
         if self.peer is not None and only is None:
             self.peer.step_begin()
-        for idx in self.plan(only):
-            if len(idx) > 1:
+        if self.fx is not None and only is None:
+            self.fx.step_begin()
+        for li, idx in enumerate(self.plan(only)):
+            if self.fx is not None and only is None:
+                args, plain_x, wp, op, nn = self.launch_args[li]
+                _, _, _, K, dt, _ = self.lin[idx[0]]
+                _lib.check(_lib.lib().light_b200_matmul_q_tp(dt, C.c_void_p(self.x[K].data_ptr() if plain_x else 0), wp, op, nn,
+                                                             len(idx), K, C.byref(args), self.dev_index, C.c_void_p(st)))
+            elif len(idx) > 1:
                 self.launch_multi(idx, st)
             else:
                 self.launch(idx[0], st)
             n += 1
             for i in idx:
                 if self.world > 1 and only is None and self.lin[i][0].split(".")[-1] in self.GATHERED:
-                    if self.peer is not None:
-                        self.peer.gather(self.gidx.index(i), self.local[i])
-                    else:
+                    if self.peer is not None and i in self.pidx:
+                        self.peer.gather(self.pidx.index(i), self.local[i])
+                    elif self.peer is None:
                         tp.all_gather_columns(self.local[i], self.out[i])
         return n
 
@@ -458,7 +495,7 @@ def main():
             v, t_step, sample = cpu_reference(M, threads, 3, 1)
             line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
-    if world > 1 and chain.peer is not None and chain.peer.status() != 0:
+    if world > 1 and chain.peer is not None and chain.peer.status() != 0:  # (one status word covers both exchanges)
         print("[bench] a bounded wait on a peer gave up: the N-GPU number above is not valid", file=sys.stderr)
     if world > 1:
         # Graphs that captured NCCL kernels must be gone before the communicator is torn down; and a
