@@ -346,6 +346,18 @@ def extras(chain, device, args):
         out["decode_tokens_per_s"][str(M)] = {"ms_per_step": ms, "tok_s": M / (ms * 1e-3),
                                               "weights_gbs": c.bytes_per_step() / (ms * 1e-3) / 1e9}
         del g, c
+    # the Q4_K decode kernel on one matrix large enough that the cost of a launch does not matter (the vocabulary
+    # projection's shape, 295 MB as Q4_K): its streaming rate, next to the launch-bound average of a step
+    big = synth.gaussian_weight(4242, ops.Q4_K, VOCAB, HID, device=device)
+    qt = ops.QTensor(big.reshape(-1), ops.Q4_K, (VOCAB, HID))
+    xb = chain.x[HID][:1]
+    ops.MatMulQ(xb, qt)
+    ms = timed(lambda: ops.MatMulQ(xb, qt), 20, 3, device, lambda: None) / 20
+    nbytes = algorithmic_bytes(VOCAB, HID, ops.Q4_K, 1)
+    peak, _ = load_peaks()
+    out["q4k_gemv_one_large_matrix"] = {"shape": [VOCAB, HID], "bytes": nbytes, "us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9,
+                                        "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peak}
+    del big, qt
     M = 2048
     by = {e[0]: e for e in chain.lin}
     qkv = torch.cat([by["l0.q"][5], by["l0.k"][5], by["l0.v"][5]])          # fused rows: a byte concatenation

@@ -843,6 +843,183 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
   cp_async_wait<0>();
 }
 
+// ------------------------------------------------------------------------------------ Q6_K, 2 .. 8 rows of x
+//
+// Tokens as MMA columns, as in q4k_gemv_tok_kernel.  The 16 k slots of an MMA are one 16-element
+// sub-block here, so every MMA has ONE int8 scale per row: the codes become (code - 32) exactly (PRMT to
+// 1024 + code, HADD2 -1056), one HMUL2 applies the scale ((code - 32) * sc is an integer of at most
+// 4096: exact up to 2048, rounded to even above, 2.4e-4 relative at worst), and one accumulator sums the
+// whole block; once per block and row, acc += d * D.  There is no minimum term.  Float4 F of a token's
+// 256 activations is exactly what lane F & 3 feeds to MMA F >> 2, so the slab is x in its own order with
+// the (0, 2, 1, 3) pairing inside each four.
+constexpr int Q6K_TOK_STAGES = 2;
+constexpr int Q6K_TOK_SLAB = TOK * TOK_PITCH;
+constexpr int Q6K_TOK_SMEM = WARPS * Q6K_TOK_STAGES * Q6K_TILE_BYTES + WARPS * Q6K_TOK_SLAB + WARPS * GROUP * 32 * 16;
+
+template <int S>
+__global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_tok_kernel(const float *__restrict__ x, const uint8_t *__restrict__ w,
+                                                                    float *__restrict__ out, int M, int N, int K) {
+  extern __shared__ __align__(16) unsigned char dyn[];  // [ring: WARPS x S tiles][slabs: WARPS][red: WARPS x GROUP x 32 float4]
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int nb = K >> 8;
+  const uint32_t row_bytes = (uint32_t)nb * 210u;  // a multiple of 4 (nb is even: checked by the launcher)
+  const uint8_t *w_end = w + (size_t)N * row_bytes;
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dyn);
+  const uint32_t ring = sbase + warp * (S * Q6K_TILE_BYTES);
+  const uint32_t slab = sbase + WARPS * S * Q6K_TILE_BYTES + warp * Q6K_TOK_SLAB;
+  const uint32_t red = sbase + WARPS * S * Q6K_TILE_BYTES + WARPS * Q6K_TOK_SLAB;
+  const uint32_t red_lane = red + (uint32_t)((warp * GROUP) * 32 + lane) * 16u;
+  const uint32_t m0f = 0x0F0F0F0Fu;
+
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const int t0 = (int)((uint32_t)tiles * blockIdx.x / gridDim.x), t1 = (int)((uint32_t)tiles * (blockIdx.x + 1) / gridDim.x);
+  const uint32_t c_rsub = lane >> 4, c_piece = lane & 15;
+  int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_gt < t1 && warp < nb) {
+      const int r0 = min((i_gt + i_rt) * ROWS, N - ROWS);
+      uint32_t ro = (uint32_t)r0 * row_bytes + (uint32_t)i_b * 210u + c_rsub * row_bytes;
+      uint32_t dst = ring + i_slot * Q6K_TILE_BYTES + c_rsub * Q6K_PITCH + c_piece * 16;
+      if (c_piece < 14) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const uint8_t *src = w + ((ro & ~15u) + c_piece * 16);
+          const long long left = w_end - src;  // the last rows of the matrix: never read past its end
+          if (left >= 16)
+            cp_async16(dst, src);
+          else if (left > 0)
+            cp_async16_part(dst, src, (uint32_t)left);
+          ro += 2 * row_bytes, dst += 2 * Q6K_PITCH;
+        }
+      }
+      i_slot = i_slot + 1 == S ? 0 : i_slot + 1;
+      if (++i_rt == i_gs) {
+        i_rt = 0, i_b += WARPS;
+        if (i_b >= nb) i_b = warp, i_gt += i_gs, i_gs = min(GROUP, t1 - i_gt);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int p = 0; p < S; p++) issue();
+  pdl_wait();  // x is the previous launch's output; the weights requested above are not
+
+  // one unit: rows g, g+8 of one tile x one K block out of ring slot `sb`, all tokens of the slab
+  auto unit = [&](auto odd_tag, uint32_t sb, uint32_t skew, float (&accr)[4]) {
+    constexpr bool ODD = decltype(odd_tag)::value;
+    uint32_t wa[2][4], wc[2][4], wh[2][4], scw[2][4];
+    float dd[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const uint32_t blk = sb + (g + 8 * r) * Q6K_PITCH + skew;  // the block's first byte
+#pragma unroll
+      for (int hu = 0; hu < 4; hu++) {
+        const int h = hu >> 1, u = hu & 1;
+        wa[r][hu] = lds32_skew<ODD>(blk + 4 * (16 * h + 4 * u + t));
+        wc[r][hu] = lds32_skew<ODD>(blk + 4 * (16 * h + 8 + 4 * u + t));
+        wh[r][hu] = lds32_skew<ODD>(blk + 4 * (32 + 8 * h + 4 * u + t));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; i++) scw[r][i] = lds32_skew<ODD>(blk + 192 + 4 * i) ^ 0x80808080u;  // sc + 128, four per word
+      dd[r] = f16_bits_to_f32((uint16_t)lds16(blk + 208));
+    }
+    __syncwarp();  // the slot is free again
+    issue();
+    float dq[4] = {0.f, 0.f, 0.f, 0.f};
+    const __half2 off_c = __float2half2_rn(-1056.f), off_s = __float2half2_rn(-1152.f);
+    const uint32_t bx = slab + g * TOK_PITCH + t * 8;  // B fragments of token g
+#pragma unroll
+    for (int h = 0; h < 2; h++)
+#pragma unroll
+      for (int q = 0; q < 4; q++)
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+          const int hu = 2 * h + u, m = (h * 4 + q) * 2 + u;  // MMA m = sub-block m = scale byte m
+          uint32_t a[4];
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            const uint32_t lo4 = (q & 1) ? wc[r][hu] : wa[r][hu];
+            const uint32_t nib = (q >> 1) ? (lo4 >> 4) : lo4;
+            const uint32_t hi2 = q == 0 ? (wh[r][hu] << 4) : q == 1 ? (wh[r][hu] << 2) : q == 2 ? wh[r][hu] : (wh[r][hu] >> 2);
+            const uint32_t v = and_or(nib, m0f, hi2 & 0x30303030u);
+            // scale byte m of the row, as the f16 pair (sc, sc): 1024 + (sc + 128) by PRMT, then -1152
+            const uint32_t s16 = __byte_perm(scw[r][m >> 2], 0x64646464u, 0x4040 + 0x0101 * (m & 3));
+            const __half2 sc = __hadd2(u32_as_h2(s16), off_s);
+            a[r] = h2_as_u32(__hmul2(__hadd2(u32_as_h2(__byte_perm(v, 0x64646464u, 0x4240)), off_c), sc));
+            a[2 + r] = h2_as_u32(__hmul2(__hadd2(u32_as_h2(__byte_perm(v, 0x64646464u, 0x4341)), off_c), sc));
+          }
+          const uint2 b = lds64(bx + m * 32);
+          mma16816(dq, a[0], a[1], a[2], a[3], b.x, b.y);
+        }
+    accr[0] = fmaf(dd[0], dq[0], accr[0]), accr[1] = fmaf(dd[0], dq[1], accr[1]);
+    accr[2] = fmaf(dd[1], dq[2], accr[2]), accr[3] = fmaf(dd[1], dq[3], accr[3]);
+  };
+
+  int slot = 0;
+  for (int gt = t0; gt < t1; gt += GROUP) {
+    const int gs = min(GROUP, t1 - gt);
+    float acc[GROUP][4];
+#pragma unroll
+    for (int r = 0; r < GROUP; r++) acc[r][0] = acc[r][1] = acc[r][2] = acc[r][3] = 0.f;
+    for (int b = warp; b < nb; b += WARPS) {
+      // ---- this block's activations, all tokens, into the warp's slab: lane l takes float4 l and l + 32
+      __syncwarp();  // every lane is done reading the previous block's slab
+#pragma unroll 4
+      for (int tk = 0; tk < TOK; tk++) {
+        const float4 *xp = reinterpret_cast<const float4 *>(x + (size_t)tk * K + b * 256);
+        float4 v[2];
+        v[0] = v[1] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (tk < M) v[0] = __ldg(xp + lane), v[1] = __ldg(xp + lane + 32);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+          const __half2 lim = __float2half2_rn(65504.f);
+          const __half2 h02 = __hmax2(__hmin2(__floats2half2_rn(v[j].x, v[j].z), lim), __hneg2(lim));
+          const __half2 h13 = __hmax2(__hmin2(__floats2half2_rn(v[j].y, v[j].w), lim), __hneg2(lim));
+          sts64(slab + tk * TOK_PITCH + (uint32_t)(lane + 32 * j) * 8u, h2_as_u32(h02), h2_as_u32(h13));
+        }
+      }
+      __syncwarp();
+#pragma unroll
+      for (int rt = 0; rt < GROUP; rt++) {
+        if (rt < gs) {
+          cp_async_wait<S - 1>();  // this lane's granules of the tile have landed ...
+          __syncwarp();            // ... and so have the other lanes'
+          const uint32_t sb = ring + slot * Q6K_TILE_BYTES;
+          slot = slot + 1 == S ? 0 : slot + 1;
+          const int r0 = min((gt + rt) * ROWS, N - ROWS);
+          const uint32_t skew = ((uint32_t)r0 * row_bytes + (uint32_t)b * 210u + (uint32_t)g * row_bytes) & 15u;
+          if (b & 1)
+            unit(std::true_type{}, sb, skew, acc[rt]);
+          else
+            unit(std::false_type{}, sb, skew, acc[rt]);
+        }
+      }
+    }
+    // ---- add up the warps' parts: lane (g, t) of tile rt holds rows g, g+8 x tokens 2t, 2t+1
+    __syncthreads();  // the previous group's sums have been read
+#pragma unroll
+    for (int rt = 0; rt < GROUP; rt++)
+      asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};\n" ::"r"(red_lane + rt * 512), "f"(acc[rt][0]), "f"(acc[rt][1]),
+                   "f"(acc[rt][2]), "f"(acc[rt][3]));
+    __syncthreads();
+    for (int i = threadIdx.x; i < gs * ROWS * TOK; i += WARPS * 32) {
+      const int row = i & 15, tok = (i >> 4) & 7, rt = i >> 7;
+      const uint32_t a = red + (uint32_t)(rt * 32 + (row & 7) * 4 + (tok >> 1)) * 16u + (uint32_t)((row >> 3) * 2 + (tok & 1)) * 4u;
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) {
+        if (wq >= nb) break;
+        float p;
+        asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(p) : "r"(a + wq * (GROUP * 512)));
+        v += p;
+      }
+      if (tok < M) out[(size_t)tok * N + min((gt + rt) * ROWS, N - ROWS) + row] = v;
+    }
+  }
+  cp_async_wait<0>();
+}
+
 template <typename... Args>
 int launch_pdl(void (*kern)(Args...), unsigned grid, size_t dyn_smem, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -874,12 +1051,14 @@ int gguf_gemv_fast_init(int device) {
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                WARPS * Q6K_STAGES * Q6K_TILE_BYTES);
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q4K_TOK_SMEM);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q6k_gemv_tok_kernel<Q6K_TOK_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q6K_TOK_SMEM);
   if (err != cudaSuccess) return fail((int)err, "light_b200: init (decode): %s", cudaGetErrorString(err));
   return 0;
 }
@@ -890,8 +1069,9 @@ static int q4k_launch(const float *x, const MultiArgs &a, const TpArgs &tp, int 
   const size_t dyn = (size_t)WARPS * g_q4k_stages * Q4K_TILE_BYTES + (size_t)(K >> 8) * Q4K_SLAB;
   if (dyn > MAX_DYN_SMEM) return 0;  // very long rows: the activations do not fit beside the rings
   const int lt = a.act ? tiles / 2 : tiles;
-  const unsigned grid = (unsigned)(lt < g_sms * g_waves ? lt : g_sms * g_waves);
-  int rc = g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 2>, grid, dyn, st, x, a, tp, tiles, K)
+  const int per_sm = g_q4k_stages == 2 ? 3 : g_waves;  // the 2-deep ring leaves room for three CTAs per SM
+  const unsigned grid = (unsigned)(lt < g_sms * per_sm ? lt : g_sms * per_sm);
+  int rc = g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 3>, grid, dyn, st, x, a, tp, tiles, K)
                              : launch_pdl(q4k_gemv_mma_kernel<4, 2>, grid, dyn, st, x, a, tp, tiles, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
@@ -921,13 +1101,16 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
   return rc ? rc : 1;
 }
 
-// 2 .. 8 activation rows against one Q4_K matrix, tokens as MMA columns.  Returns 1 if launched, 0 if
+// 2 .. 8 activation rows against one Q4_K or Q6_K matrix, tokens as MMA columns.  Returns 1 if launched, 0 if
 // the shape is not covered.
 int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
-  if (type != LB200_Q4_K || M < 2 || M > TOK || K % 256 || N < ROWS || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
+  if ((type != LB200_Q4_K && type != LB200_Q6_K) || M < 2 || M > TOK || K % 256 || N < ROWS || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
+  if (type == LB200_Q6_K && (((K >> 8) & 1) || (unsigned long long)N * (K >> 8) * 210ull >= (1ull << 32))) return 0;
   const int tiles = (N + ROWS - 1) / ROWS;
   const unsigned grid = (unsigned)(tiles < g_sms * 2 ? tiles : g_sms * 2);
-  int rc = launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, (const uint8_t *)w, out, M, N, K);
+  int rc = type == LB200_Q4_K
+               ? launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, (const uint8_t *)w, out, M, N, K)
+               : launch_pdl(q6k_gemv_tok_kernel<Q6K_TOK_STAGES>, grid, (size_t)Q6K_TOK_SMEM, st, x, (const uint8_t *)w, out, M, N, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode, 2-8 rows)");
   return rc ? rc : 1;
