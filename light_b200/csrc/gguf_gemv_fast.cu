@@ -1103,17 +1103,30 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
 
 // 2 .. 8 activation rows against one Q4_K or Q6_K matrix, tokens as MMA columns.  Returns 1 if launched, 0 if
 // the shape is not covered.
+int g_tok_max_m = 8;  // LIGHT_B200_TOK_MAX_M (tuning knob): most activation rows served by passes of eight (beyond 8 the other kernels win)
 int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
-  if ((type != LB200_Q4_K && type != LB200_Q6_K) || M < 2 || M > TOK || K % 256 || N < ROWS || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
+  static bool knob = false;
+  if (!knob) {
+    if (const char *e = getenv("LIGHT_B200_TOK_MAX_M")) g_tok_max_m = atoi(e);
+    knob = true;
+  }
+  if ((type != LB200_Q4_K && type != LB200_Q6_K) || M < 2 || M > g_tok_max_m || K % 256 || N < ROWS || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
   if (type == LB200_Q6_K && (((K >> 8) & 1) || (unsigned long long)N * (K >> 8) * 210ull >= (1ull << 32))) return 0;
   const int tiles = (N + ROWS - 1) / ROWS;
   const unsigned grid = (unsigned)(tiles < g_sms * 2 ? tiles : g_sms * 2);
-  int rc = type == LB200_Q4_K
-               ? launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, (const uint8_t *)w, out, M, N, K)
-               : launch_pdl(q6k_gemv_tok_kernel<Q6K_TOK_STAGES>, grid, (size_t)Q6K_TOK_SMEM, st, x, (const uint8_t *)w, out, M, N, K);
-  if (rc) return rc;
-  rc = launched("matmul_q (decode, 2-8 rows)");
-  return rc ? rc : 1;
+  // eight tokens per pass; a second pass finds a decode-sized matrix in the 126 MB L2
+  for (int m0 = 0; m0 < M; m0 += TOK) {
+    const int mm = M - m0 < TOK ? M - m0 : TOK;
+    const float *xm = x + (size_t)m0 * K;
+    float *om = out + (size_t)m0 * N;
+    int rc = type == LB200_Q4_K
+                 ? launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, xm, (const uint8_t *)w, om, mm, N, K)
+                 : launch_pdl(q6k_gemv_tok_kernel<Q6K_TOK_STAGES>, grid, (size_t)Q6K_TOK_SMEM, st, xm, (const uint8_t *)w, om, mm, N, K);
+    if (rc) return rc;
+    rc = launched("matmul_q (decode, 2-8 rows)");
+    if (rc) return rc;
+  }
+  return 1;
 }
 
 // Several matrices of one type against one activation row in one launch (act == 0), or the gated
