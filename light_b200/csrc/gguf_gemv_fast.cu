@@ -218,7 +218,7 @@ constexpr int Q4K_SLAB = Slab<32>::BYTES + 16;  // a block's activations + its p
 //
 // All activations are converted once per CTA (warp w converts the blocks it will use), so the
 // tile loop holds no activation traffic at all.
-template <int S, int MINB>
+template <int S, int MINB, bool TP>
 __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const float *__restrict__ x,
                                                                        const __grid_constant__ MultiArgs a,
                                                                        const __grid_constant__ TpArgs tp, int tiles, int K) {
@@ -284,13 +284,15 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
   for (int p = 0; p < S; p++) issue();
   pdl_wait();  // x is the previous launch's output; the weights requested above are not
   unsigned int tag = 0;
-  if (tp.step) tag = *reinterpret_cast<const volatile unsigned int *>(tp.step);
   unsigned long long tp_t0 = 0;
   bool tp_gave_up = false;
-  if (tp.x_slots) asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(tp_t0));
+  if constexpr (TP) {
+    tag = *reinterpret_cast<const volatile unsigned int *>(tp.step);
+    if (tp.x_slots) asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(tp_t0));
+  }
   for (int b = warp; b < nb; b += WARPS) {
     float4 xv[2];
-    if (tp.x_slots) {  // the peers' parts of x arrive as tagged slots
+    if (TP && tp.x_slots) {  // the peers' parts of x arrive as tagged slots
       const uint2 *xs = tp.x_slots + (size_t)(tag & 1u) * K + b * 256 + lane * 4;
       xv[0] = ld_slots4(xs, tag, tp_t0, tp_gave_up);
       xv[1] = ld_slots4(xs + 128, tag, tp_t0, tp_gave_up);
@@ -379,7 +381,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
         resolve_tile(a, gt + 2 * pr, j, r0);
         const float v = gate_act(row_sum(2 * pr, row), a.act) * row_sum(2 * pr + 1, row);
         a.out[0][r0 + row] = v;
-        if (tp.peer[0][0]) st_slots(tp.peer[0], tp.world, (size_t)(tag & 1u) * a.n[0] * tp.world + (size_t)tp.rank * a.n[0] + r0 + row, v, tag);
+        if (TP && tp.peer[0][0]) st_slots(tp.peer[0], tp.world, (size_t)(tag & 1u) * a.n[0] * tp.world + (size_t)tp.rank * a.n[0] + r0 + row, v, tag);
       }
     } else {
       for (int i = threadIdx.x; i < gs * ROWS; i += WARPS * 32) {
@@ -388,7 +390,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
         resolve_tile(a, gt + rt, j, r0);
         const float v = row_sum(rt, row);
         a.out[j][r0 + row] = v;
-        if (tp.peer[j][0]) st_slots(tp.peer[j], tp.world, (size_t)(tag & 1u) * a.n[j] * tp.world + (size_t)tp.rank * a.n[j] + r0 + row, v, tag);
+        if (TP && tp.peer[j][0]) st_slots(tp.peer[j], tp.world, (size_t)(tag & 1u) * a.n[j] * tp.world + (size_t)tp.rank * a.n[j] + r0 + row, v, tag);
       }
     }
   }
@@ -634,7 +636,7 @@ __device__ __forceinline__ uint32_t lds32_skew(uint32_t addr) {
   return __funnelshift_r(lds32(addr - 2), lds32(addr + 2), 16);
 }
 
-template <int S>
+template <int S, bool TP>
 __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float *__restrict__ x,
                                                                     const uint8_t *__restrict__ w,
                                                                     float *__restrict__ out, const __grid_constant__ TpArgs tp,
@@ -714,12 +716,14 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
   __syncthreads();
   float4 xn[2];  // the activations of the block this warp stages next, requested one block ahead
   unsigned int tag = 0;
-  if (tp.step) tag = *reinterpret_cast<const volatile unsigned int *>(tp.step);
   unsigned long long tp_t0 = 0;
   bool tp_gave_up = false;
-  if (tp.x_slots) asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(tp_t0));
+  if constexpr (TP) {
+    tag = *reinterpret_cast<const volatile unsigned int *>(tp.step);
+    if (tp.x_slots) asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(tp_t0));
+  }
   auto load_x = [&](int b) {
-    if (tp.x_slots) {  // the peers' parts of x arrive as tagged slots
+    if (TP && tp.x_slots) {  // the peers' parts of x arrive as tagged slots
       const uint2 *xs = tp.x_slots + (size_t)(tag & 1u) * K + b * 256 + lane * 4;
       xn[0] = ld_slots4(xs, tag, tp_t0, tp_gave_up);
       xn[1] = ld_slots4(xs + 128, tag, tp_t0, tp_gave_up);
@@ -837,7 +841,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
       }
       const int orow = min((gt + rt) * ROWS, N - ROWS) + row;
       out[orow] = v;
-      if (tp.peer[0][0]) st_slots(tp.peer[0], tp.world, (size_t)(tag & 1u) * N * tp.world + (size_t)tp.rank * N + orow, v, tag);
+      if (TP && tp.peer[0][0]) st_slots(tp.peer[0], tp.world, (size_t)(tag & 1u) * N * tp.world + (size_t)tp.rank * N + orow, v, tag);
     }
   }
   cp_async_wait<0>();
@@ -1049,11 +1053,16 @@ int gguf_gemv_fast_init(int device) {
   if (const char *e = getenv("LIGHT_B200_Q4K_STAGES")) g_q4k_stages = atoi(e) == 2 ? 2 : 4;
   cudaError_t err = cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, device);
   if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<2, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               WARPS * Q6K_STAGES * Q6K_TILE_BYTES);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+  if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                WARPS * Q6K_STAGES * Q6K_TILE_BYTES);
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, Q4K_TOK_SMEM);
@@ -1066,13 +1075,14 @@ int gguf_gemv_fast_init(int device) {
 // One launch over up to four Q4_K matrices that share x (M = 1).  Returns 1 if launched, 0 if this
 // path does not apply, < 0 or a CUDA code on error.
 static int q4k_launch(const float *x, const MultiArgs &a, const TpArgs &tp, int tiles, int K, cudaStream_t st) {
-  const size_t dyn = (size_t)WARPS * g_q4k_stages * Q4K_TILE_BYTES + (size_t)(K >> 8) * Q4K_SLAB;
+  const size_t dyn = (size_t)WARPS * (tp.step ? 4 : g_q4k_stages) * Q4K_TILE_BYTES + (size_t)(K >> 8) * Q4K_SLAB;
   if (dyn > MAX_DYN_SMEM) return 0;  // very long rows: the activations do not fit beside the rings
   const int lt = a.act ? tiles / 2 : tiles;
-  const int per_sm = g_q4k_stages == 2 ? 3 : g_waves;  // the 2-deep ring leaves room for three CTAs per SM
+  const int per_sm = (g_q4k_stages == 2 && !tp.step) ? 3 : g_waves;  // the 2-deep ring leaves room for three CTAs per SM
   const unsigned grid = (unsigned)(lt < g_sms * per_sm ? lt : g_sms * per_sm);
-  int rc = g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 3>, grid, dyn, st, x, a, tp, tiles, K)
-                             : launch_pdl(q4k_gemv_mma_kernel<4, 2>, grid, dyn, st, x, a, tp, tiles, K);
+  int rc = tp.step            ? launch_pdl(q4k_gemv_mma_kernel<4, 2, true>, grid, dyn, st, x, a, tp, tiles, K)
+           : g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 3, false>, grid, dyn, st, x, a, tp, tiles, K)
+                               : launch_pdl(q4k_gemv_mma_kernel<4, 2, false>, grid, dyn, st, x, a, tp, tiles, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
   return rc ? rc : 1;
@@ -1095,7 +1105,7 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
     return q4k_launch(x, a, NO_TP, tiles, K, st);
   }
   const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
-  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x, wb, out, NO_TP, N, K);
+  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES, false>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x, wb, out, NO_TP, N, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
   return rc ? rc : 1;
@@ -1177,7 +1187,7 @@ int gguf_gemv_tp(int type, const float *x, const void *x_slots, const void *cons
   if (((K >> 8) & 1) || (unsigned long long)n[0] * (K >> 8) * 210ull >= (1ull << 32)) return 0;
   const int tiles = (n[0] + ROWS - 1) / ROWS;
   const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
-  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x,
+  int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES, true>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x,
                       (const uint8_t *)w[0], out[0], tp, n[0], K);
   if (rc) return rc;
   rc = launched("matmul_q (decode, row-split)");
