@@ -164,6 +164,8 @@ int light_b200_matmul_q(int t, const float *x, const void *w, float *out, int M,
   if (took != 0) return took == 1 ? 0 : took;
   took = gguf_prefill(t, x, w, out, M, N, K, device, st);
   if (took != 0) return took == 1 ? 0 : took;
+  took = gguf_decode_tile(t, x, w, out, M, N, K, st);
+  if (took != 0) return took == 1 ? 0 : took;
   took = gguf_decode_umma(t, x, w, out, M, N, K, device, st);
   if (took != 0) return took == 1 ? 0 : took;
   took = gguf_gemv_batch(t, x, w, out, M, N, K, st);

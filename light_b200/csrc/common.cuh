@@ -49,6 +49,7 @@ int gguf_matmul_generic(int type, const float *x, const void *w, float *out, int
 // returns 1 when a fast decode kernel took the call, 0 when the shape is not covered, <0 on error
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
 int gguf_gemv_fast_init(int device);
+int gguf_decode_tile(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
 int gguf_gemv_tp(int type, const float *x, const void *x_slots, const void *const *w, float *const *out, const int *n,
                  int count, int K, void *const *out_slots, const unsigned int *step, int world, int rank, cudaStream_t st);
 int gemv_tp_status();

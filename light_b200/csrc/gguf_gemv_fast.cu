@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "mma_sync.cuh"
+#include "umma.cuh"
 
 namespace lb {
 
@@ -602,6 +603,220 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float
   cp_async_wait<0>();
 }
 
+// ------------------------------------------------------------------------------------ Q4_K, 9 .. 64 rows of x
+//
+// More tokens than one MMA has columns: the token-column arithmetic of q4k_gemv_tok_kernel with NG groups
+// of eight tokens per code word, and a decomposition that lets all warps of a CTA share ONE copy of the
+// converted activations.  A CTA owns eight consecutive row tiles (one per warp, no sum across warps) and
+// walks a run of K blocks; every thread requests its share of block b + 1 of x (all tokens) before the
+// warp works on block b and converts it into the other half of a double buffer afterwards, one CTA
+// barrier per block.  K is split over a
+// thread-block cluster of KS CTAs, whose partial sums meet in distributed shared memory at the end, as in
+// decode_umma_kernel.  The expanded weights never leave registers: per 4096 weights this kernel issues
+// about a third of the instructions of the shared-memory-operand kernel.
+constexpr int DT_CW = 8, DT_THREADS = DT_CW * 32;
+constexpr int DT_STAGES = 3;
+constexpr int DT_RING = DT_CW * DT_STAGES * Q4K_TILE_BYTES;
+template <int NG>
+struct DtCfg {
+  static constexpr int NT = 8 * NG;                        // token columns
+  static constexpr int SX = NT * TOK_PITCH;                // then per token 8 hi | 8 lo sub-block sums
+  static constexpr int XBUF = SX + NT * 32;
+  static constexpr int SMEM = DT_RING + 2 * XBUF;
+  static_assert(NT * 128 * 4 <= DT_RING, "the partial sums reuse the ring");
+};
+
+template <int NG>
+__global__ void __launch_bounds__(DT_THREADS, 2) q4k_decode_tile_kernel(const float *__restrict__ x,
+                                                                                     const uint8_t *__restrict__ w,
+                                                                                     float *__restrict__ out, int M, int N, int K) {
+  using Cfg = DtCfg<NG>;
+  constexpr int S = DT_STAGES;
+  extern __shared__ __align__(16) unsigned char dyn[];  // [ring: 8 warps x S tiles][x buffer 0][x buffer 1]
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int nb = K >> 8, tiles = (N + ROWS - 1) / ROWS;
+  const int KS = gridDim.y, rank = blockIdx.y;
+  const int b0 = nb * rank / KS, b1 = nb * (rank + 1) / KS, nloc = b1 - b0;
+  // CTAs of one K run start at different blocks of it: otherwise all of them ask L2 for the same lines of x
+  // at the same moment
+  const int rot = (int)(blockIdx.x * 5u) % nloc;
+  auto blk = [&](int i) { const int j = i + rot; return b0 + (j >= nloc ? j - nloc : j); };
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dyn);
+  const uint32_t xs0 = sbase + DT_RING;
+
+  // this thread's share of a block of x: float4 F = tid & 63 of tokens (tid >> 6) + 4 j
+  constexpr int XJ = Cfg::NT / 4;
+  const int xF = threadIdx.x & 63, xT = threadIdx.x >> 6;
+  auto x_load = [&](int b, float4 (&v)[XJ]) {
+#pragma unroll
+    for (int j = 0; j < XJ; j++) {
+      const int tk = xT + 4 * j;
+      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (tk < M) v[j] = __ldg(reinterpret_cast<const float4 *>(x + (size_t)tk * K + b * 256) + xF);
+    }
+  };
+  auto x_store = [&](uint32_t xb, const float4 (&v)[XJ]) {
+#pragma unroll
+    for (int j = 0; j < XJ; j++) {
+      const int tk = xT + 4 * j;
+      const __half2 lim = __float2half2_rn(65504.f);
+      const __half2 h02 = __hmax2(__hmin2(__floats2half2_rn(v[j].x, v[j].z), lim), __hneg2(lim));
+      const __half2 h13 = __hmax2(__hmin2(__floats2half2_rn(v[j].y, v[j].w), lim), __hneg2(lim));
+      sts64(xb + tk * TOK_PITCH + (uint32_t)((((xF >> 3) & 1) * 8 + (xF & 7)) * 4 + (xF >> 4)) * 8u, h2_as_u32(h02), h2_as_u32(h13));
+      const float2 a = __half22float2(h02), c = __half22float2(h13);
+      float s = (a.x + a.y) + (c.x + c.y);  // of the ROUNDED values, the ones the tensor core multiplies
+      s += __shfl_xor_sync(0xffffffffu, s, 1), s += __shfl_xor_sync(0xffffffffu, s, 2), s += __shfl_xor_sync(0xffffffffu, s, 4);
+      const float s1 = __shfl_down_sync(0xffffffffu, s, 8);
+      if ((lane & 15) == 0) {  // sub-blocks (F / 8, F / 8 + 1) = pair F / 16
+        const __half2 hi = __floats2half2_rn(s, s1);
+        const float2 hf = __half22float2(hi);
+        const __half2 lo = __floats2half2_rn(s - hf.x, s1 - hf.y);
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(xb + Cfg::SX + tk * 32 + 4 * (xF >> 4)), "r"(h2_as_u32(hi)));
+        asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(xb + Cfg::SX + tk * 32 + 16 + 4 * (xF >> 4)), "r"(h2_as_u32(lo)));
+      }
+    }
+  };
+  {
+    // ---- consumers: warp w owns row tile 8 blockIdx.x + w over blocks b0 .. b1
+    const int tile = blockIdx.x * DT_CW + warp;
+    const bool live = tile < tiles;
+    const int r0 = min(tile * ROWS, N - ROWS);
+    const uint32_t row_bytes = (uint32_t)nb * 144u;
+    const uint32_t ring = sbase + warp * (S * Q4K_TILE_BYTES);
+    const bool hdr_hi = t >= 2;
+    const int hdr_sh = (t & 1) * 16;
+    const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
+    uint32_t soff[5];
+#pragma unroll
+    for (int i = 0; i < 5; i++) {
+      const uint32_t c = lane + 32 * i, row = c / 9u;
+      soff[i] = row * row_bytes + (c - 9u * row) * 16u;
+    }
+    const uint32_t ld_off = g * 144u + 32u * t;
+    int i_b = 0, i_slot = 0;
+    auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+      if (live && i_b < nloc) {
+        const uint8_t *base = w + ((size_t)r0 * row_bytes + (uint32_t)blk(i_b) * 144u);
+        const uint32_t dst = ring + i_slot * Q4K_TILE_BYTES + lane * 16;
+#pragma unroll
+        for (int i = 0; i < 4; i++) cp_async16(dst + i * 512, base + soff[i]);
+        if (lane < 16) cp_async16(dst + 2048, base + soff[4]);
+        i_slot = i_slot + 1 == S ? 0 : i_slot + 1;
+        i_b++;
+      }
+      cp_async_commit();
+    };
+#pragma unroll 1
+    for (int p = 0; p < S; p++) issue();
+    pdl_wait();  // x is the previous launch's output; the weights requested above are not
+    {
+      float4 v0[XJ];
+      x_load(blk(0), v0);
+      x_store(xs0, v0);
+    }
+    __syncthreads();
+
+    float acc[NG][4];
+#pragma unroll
+    for (int q = 0; q < NG; q++) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
+    int slot = 0;
+    for (int bi = 0; bi < nloc; bi++) {
+      const int half = bi & 1;
+      const uint32_t xb = xs0 + half * Cfg::XBUF;
+      float4 xn[XJ];
+      if (bi + 1 < nloc) x_load(blk(bi + 1), xn);
+      if (live) {
+        cp_async_wait<S - 1>();
+        __syncwarp();
+        const uint32_t sb = ring + slot * Q4K_TILE_BYTES + ld_off;
+        slot = slot + 1 == S ? 0 : slot + 1;
+        const uint4 h0 = lds128(sb - 32u * t), h1 = lds128(sb - 32u * t + 8 * 144);
+        const uint4 qa0 = lds128(sb + 16), qa1 = lds128(sb + 32);
+        const uint4 qb0 = lds128(sb + 8 * 144 + 16), qb1 = lds128(sb + 8 * 144 + 32);
+        __syncwarp();  // the slot is free again
+        issue();
+        __half2 s2[2][2], c2[2][2];
+        uint32_t dmh[2], dml[2];
+        float dd[2];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          const uint4 &h = r ? h1 : h0;
+          const float2 df = __half22float2(u32_as_h2(h.x));  // (d, dmin)
+          const uint32_t scw = hdr_hi ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
+          const uint32_t mnw = hdr_hi ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
+          const uint32_t sc = scw >> hdr_sh, mn = mnw >> hdr_sh;
+          s2[r][0] = __half2half2(__uint2half_rn(sc & 0xFFu)), s2[r][1] = __half2half2(__uint2half_rn((sc >> 8) & 0xFFu));
+          c2[r][0] = __hmul2(s2[r][0], __float2half2_rn(-64.f)), c2[r][1] = __hmul2(s2[r][1], __float2half2_rn(-64.f));
+          const float m0 = -df.y * (float)(mn & 0xFFu), m1 = -df.y * (float)((mn >> 8) & 0xFFu);
+          const __half2 mh = __floats2half2_rn(m0, m1);
+          const float2 mf = __half22float2(mh);
+          dmh[r] = h2_as_u32(mh), dml[r] = h2_as_u32(__floats2half2_rn(m0 - mf.x, m1 - mf.y));
+          dd[r] = df.x;
+        }
+        float dq[NG][4];
+#pragma unroll
+        for (int q = 0; q < NG; q++) dq[q][0] = dq[q][1] = dq[q][2] = dq[q][3] = 0.f;
+        const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+        const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+        auto scl = [](uint32_t raw, __half2 s, __half2 c) { return h2_as_u32(__hfma2(u32_as_h2(raw), s, c)); };
+        const uint32_t bx = xb + g * TOK_PITCH + t * 8;  // B fragments of token g of group 0
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const uint32_t vg = qg[i], vh = qh[i];
+          const uint32_t e0 = scl(and_or(vg << 4, mask, magic), s2[0][0], c2[0][0]), e1 = scl(and_or(vh << 4, mask, magic), s2[1][0], c2[1][0]);
+          const uint32_t e2 = scl(and_or(vg >> 4, mask, magic), s2[0][0], c2[0][0]), e3 = scl(and_or(vh >> 4, mask, magic), s2[1][0], c2[1][0]);
+          const uint32_t o0 = scl(and_or(vg, mask, magic), s2[0][1], c2[0][1]), o1 = scl(and_or(vh, mask, magic), s2[1][1], c2[1][1]);
+          const uint32_t o2 = scl(and_or(vg >> 8, mask, magic), s2[0][1], c2[0][1]), o3 = scl(and_or(vh >> 8, mask, magic), s2[1][1], c2[1][1]);
+#pragma unroll
+          for (int q = 0; q < NG; q++) {
+            const uint2 be = lds64(bx + q * (8 * TOK_PITCH) + i * 32), bo = lds64(bx + q * (8 * TOK_PITCH) + (8 + i) * 32);
+            mma16816(dq[q], e0, e1, e2, e3, be.x, be.y);
+            mma16816(dq[q], o0, o1, o2, o3, bo.x, bo.y);
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < NG; q++) {
+          acc[q][0] = fmaf(dd[0], dq[q][0], acc[q][0]), acc[q][1] = fmaf(dd[0], dq[q][1], acc[q][1]);
+          acc[q][2] = fmaf(dd[1], dq[q][2], acc[q][2]), acc[q][3] = fmaf(dd[1], dq[q][3], acc[q][3]);
+          const uint32_t sx_hi = lds32(xb + Cfg::SX + (q * 8 + g) * 32 + 4 * t), sx_lo = lds32(xb + Cfg::SX + (q * 8 + g) * 32 + 16 + 4 * t);
+          mma16816(acc[q], dmh[0], dmh[1], dml[0], dml[1], sx_hi, sx_hi);
+          mma16816(acc[q], dmh[0], dmh[1], 0u, 0u, sx_lo, 0u);
+        }
+      }
+      if (bi + 1 < nloc) x_store(xs0 + (half ^ 1) * Cfg::XBUF, xn);
+      __syncthreads();  // block b + 1 of x is in place, block b's half is free
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with its ring slots
+    // ---- partial[token][128 rows of this CTA] over the (drained) ring
+#pragma unroll
+    for (int q = 0; q < NG; q++)
+#pragma unroll
+      for (int c = 0; c < 4; c++) {
+        const int tok = q * 8 + 2 * t + (c & 1), row = warp * ROWS + g + 8 * (c >> 1);
+        asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(sbase + (uint32_t)(tok * 128 + row) * 4u), "f"(acc[q][c]));
+      }
+  }
+  // ---- add up the cluster's partials: CTA `rank` stores tokens rank NT / KS ..
+  if (KS > 1) umma::cluster_sync(); else __syncthreads();
+  {
+    const int per = Cfg::NT / KS;
+    for (int idx = threadIdx.x; idx < per * 128; idx += DT_THREADS) {
+      const int tok = rank * per + (idx >> 7), rr = idx & 127, tile = blockIdx.x * DT_CW + (rr >> 4);
+      const uint32_t a = sbase + (uint32_t)(tok * 128 + rr) * 4u;
+      float v = 0.f;
+      if (KS > 1) {
+        for (int p = 0; p < KS; p++) v += umma::ld_cluster_f32(umma::map_to_rank(a, (uint32_t)p));
+      } else {
+        asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(a));
+      }
+      if (tok < M && tile < tiles) out[(size_t)tok * N + min(tile * ROWS, N - ROWS) + (rr & 15)] = v;
+    }
+  }
+  if (KS > 1) umma::cluster_sync();  // nobody leaves while a peer still reads its partials
+}
+
 // ------------------------------------------------------------------------------------ Q6_K
 //
 // Block (210 B): [ql[128] | qh[64] | int8 sc[16] | f16 d]; element e = 128h + 32q + l
@@ -1134,6 +1349,59 @@ int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, in
                  : launch_pdl(q6k_gemv_tok_kernel<Q6K_TOK_STAGES>, grid, (size_t)Q6K_TOK_SMEM, st, xm, (const uint8_t *)w, om, mm, N, K);
     if (rc) return rc;
     rc = launched("matmul_q (decode, 2-8 rows)");
+    if (rc) return rc;
+  }
+  return 1;
+}
+
+// 9 .. 32 activation rows per pass (more rows: passes of 32) against one Q4_K matrix: eight row tiles per CTA,
+// K split over a cluster.  Returns 1 if launched, 0 if the shape is not covered.
+template <int NG>
+static int launch_tile(const float *x, const uint8_t *w, float *out, int M, int N, int K, cudaStream_t st) {
+  auto kern = q4k_decode_tile_kernel<NG>;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DtCfg<NG>::SMEM);
+    if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, tiles): %s", cudaGetErrorString(e));
+    attr_done = true;
+  }
+  const int tiles = (N + ROWS - 1) / ROWS, nx = (tiles + DT_CW - 1) / DT_CW, nb = K >> 8;
+  // measured on 4096 x 4096, 1024 x 4096 and 14336 x 4096: short K runs win (a CTA's start-up and its first
+  // block of x are not overlapped with anything) until two CTAs per SM are resident and more wait behind them
+  int ks = nx * 2 >= g_sms ? 2 : 8;
+  while (ks > nb) ks >>= 1;
+  if (const char *e = getenv("LIGHT_B200_TILE_KS")) { const int v = atoi(e); if (v >= 1 && v <= 8 && v <= nb) ks = v; }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)nx, (unsigned)ks, 1);
+  cfg.blockDim = dim3(DT_THREADS);
+  cfg.dynamicSmemBytes = DtCfg<NG>::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = 1, attr[1].val.clusterDim.y = (unsigned)ks, attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, x, w, out, M, N, K);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, tiles): %s", cudaGetErrorString(e));
+  return launched("matmul_q (decode, tiles)");
+}
+
+int g_tile_min_m = 9, g_tile_max_m = 32;  // LIGHT_B200_TILE_MIN_M / _MAX_M (tuning knobs)
+int gguf_decode_tile(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
+  static bool knob = false;
+  if (!knob) {
+    if (const char *e = getenv("LIGHT_B200_TILE_MIN_M")) g_tile_min_m = atoi(e);
+    if (const char *e = getenv("LIGHT_B200_TILE_MAX_M")) g_tile_max_m = atoi(e);
+    knob = true;
+  }
+  if (type != LB200_Q4_K || M < g_tile_min_m || M > g_tile_max_m || K % 256 || N < ROWS || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
+  for (int m0 = 0; m0 < M; m0 += 32) {
+    const int mm = M - m0 < 32 ? M - m0 : 32;
+    const float *xm = x + (size_t)m0 * K;
+    float *om = out + (size_t)m0 * N;
+    const int rc = mm <= 16 ? launch_tile<2>(xm, (const uint8_t *)w, om, mm, N, K, st) : launch_tile<4>(xm, (const uint8_t *)w, om, mm, N, K, st);
     if (rc) return rc;
   }
   return 1;

@@ -36,6 +36,25 @@ def test_gguf_batched_decode(cuda, oracle, name, dt, N, K):
     assert ops.prefill_status(cuda.index or 0) == 0
 
 
+@pytest.mark.parametrize("N,K", [(300, 4096), (129, 256), (1024, 768), (2064, 1280), (16, 2048)])
+def test_q4k_decode_9_to_32_rows(cuda, oracle, N, K):
+    """The register-fed kernel for 9 to 32 activation rows (eight row tiles per CTA, K split over a
+    cluster): ragged heights (a last row tile that overlaps the one before, CTAs with fewer than eight
+    live tiles, a single tile), one to 16 blocks per row (K runs of uneven length, clusters of 1, 2, 4
+    and 8), token counts that fill two and four groups of eight partly and fully; twice the same bits."""
+    raw = synth.gaussian_weight(331, ops.Q4_K, N, K).numpy()
+    deq = oracle.dequant(ops.Q4_K, raw.reshape(-1), N * K).reshape(N, K).astype(np.float64)
+    w = ops.QTensor(torch.from_numpy(raw.reshape(-1)).to(cuda), ops.Q4_K, (N, K))
+    g = torch.Generator().manual_seed(332)
+    for M in (9, 15, 16, 17, 25, 32):
+        x = torch.randn(M, K, generator=g)
+        got = ops.MatMulQ(x.to(cuda), w)
+        assert torch.equal(got, ops.MatMulQ(x.to(cuda), w)), "the cluster reduction must be deterministic"
+        want = x.numpy().astype(np.float64) @ deq.T
+        assert rel_l2(got.cpu().numpy(), want) <= 1e-3, (N, K, M, rel_l2(got.cpu().numpy(), want))
+    assert ops.prefill_status(cuda.index or 0) == 0
+
+
 @pytest.mark.parametrize("M", [1, 5, 16, 17, 33, 64])
 def test_int4_bf16_decode(cuda, oracle, M):
     """BASELINE config 4 shape class (K = 3584, group 128, bf16 activations): the operands are the
