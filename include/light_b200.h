@@ -261,6 +261,43 @@ LB200_API int light_b200_moe_gemm_static_scratch(const lb200_moe_args *args, int
  * x f32, GGUF block-quantized experts, out f32. */
 LB200_API int light_b200_moe_gemm_q(const lb200_moe_args *args, int device, void *stream);
 
+/* ---- decode-step attention against a fixed-capacity KV cache (the step beside the quantized matmuls)
+ *
+ * Registry keys {kv_append, CUDA, F32|BF16}, {decode_attn, CUDA, F32|BF16}, {inc_i64, CUDA, I64}
+ * (reference kernels/cuda/decode_attn.go:15-133; ops.KVAppend / ops.DecodeAttention / ops.IncrementI64,
+ * ops/decode_attn.go:13-205).  `pos` is a one-element device I64: the position of the new token, so the
+ * number of valid keys is pos + 1 and every launch is the same whatever the position (CUDA-graph
+ * capturable, models/decode_graph.go:27-230).  A position outside [0, Cap) is clamped, nothing is written
+ * outside the buffers, and light_b200_decode_attn_status reports it. */
+
+/* k, v (B, KH, 1, D) contiguous -> kbuf, vbuf (B, KH, Cap, D) at position pos[0]. */
+LB200_API int light_b200_kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_t *pos, int dtype,
+                                   int B, int KH, int D, int Cap, int device, void *stream);
+
+typedef struct lb200_decode_attn_args {
+  const void *q;       /* (B, NH, 1, D) contiguous                                              */
+  void *kbuf, *vbuf;   /* (B, KH, Cap, D) contiguous                                            */
+  const void *k_new;   /* NULL, or k (B, KH, 1, D): appended at pos by this launch, which then   */
+  const void *v_new;   /* replaces light_b200_kv_append (KVCache.decodeAttend does both)         */
+  const int64_t *pos;  /* device, one element                                                    */
+  void *out;           /* (B, NH, 1, D)                                                          */
+  int32_t dtype;       /* LB200_F32 or LB200_BF16: q, k, v, out alike                            */
+  int32_t B, NH, KH, Cap, D;
+  int32_t window;      /* 0, or the sliding window: keys [n - window, n)                         */
+  float scale;         /* scores = scale * q.k                                                   */
+} lb200_decode_attn_args;
+
+/* out = softmax(scale * q K^T) V over the valid keys, one launch, no scratch.  Limits as the reference's
+ * kernel (D a multiple of 32 up to 512, at most 16 query heads per KV head; else LB200_E_SHAPE and the
+ * caller composes the op as it does today, ops/decode_attn.go:116-170). */
+LB200_API int light_b200_decode_attn(const lb200_decode_attn_args *args, int device, void *stream);
+
+/* p[i] += 1 for i < n (the device-side position after a step). */
+LB200_API int light_b200_inc_i64(int64_t *p, int n, int device, void *stream);
+
+/* 0, or 1 if a launch ever saw a position outside [0, Cap).  Synchronises with the device. */
+LB200_API int light_b200_decode_attn_status(int device);
+
 #ifdef __cplusplus
 }
 #endif

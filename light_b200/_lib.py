@@ -41,6 +41,14 @@ class MoeArgs(C.Structure):
     ]
 
 
+class DecodeAttnArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("kbuf", C.c_void_p), ("vbuf", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
+        ("pos", C.c_void_p), ("out", C.c_void_p), ("dtype", C.c_int32), ("B", C.c_int32), ("NH", C.c_int32),
+        ("KH", C.c_int32), ("Cap", C.c_int32), ("D", C.c_int32), ("window", C.c_int32), ("scale", C.c_float),
+    ]
+
+
 # name -> (restype, argtypes): every symbol include/light_b200.h declares
 SYMBOLS = {
     "light_b200_init": (C.c_int, [C.c_int]),
@@ -75,6 +83,11 @@ SYMBOLS = {
     "light_b200_moe_gemm_q": (C.c_int, [C.POINTER(MoeArgs), C.c_int, C.c_void_p]),
     "light_b200_moe_gemm_f8block": (C.c_int, [C.POINTER(MoeArgs), C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_moe_gemm_static_scratch": (C.c_int, [C.POINTER(MoeArgs), C.c_int, C.c_void_p]),
+    "light_b200_kv_append": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
+                                       C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_decode_attn": (C.c_int, [C.POINTER(DecodeAttnArgs), C.c_int, C.c_void_p]),
+    "light_b200_inc_i64": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_decode_attn_status": (C.c_int, [C.c_int]),
 }
 
 _lib = None

@@ -336,6 +336,29 @@ int light_b200_moe_gemm_static_scratch(const lb200_moe_args *a, int device, void
   return moe_gemm_static_scratch(a, device, (cudaStream_t)stream);
 }
 
+int light_b200_kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_t *pos, int dtype, int B, int KH,
+                         int D, int Cap, int device, void *stream) {
+  if (int rc = bind(device)) return rc;
+  return kv_append(k, v, kbuf, vbuf, pos, dtype, B, KH, D, Cap, (cudaStream_t)stream);
+}
+
+int light_b200_decode_attn(const lb200_decode_attn_args *a, int device, void *stream) {
+  if (int rc = bind(device)) return rc;
+  return decode_attn(a, (cudaStream_t)stream);
+}
+
+int light_b200_inc_i64(int64_t *p, int n, int device, void *stream) {
+  if (int rc = bind(device)) return rc;
+  return inc_i64(p, n, (cudaStream_t)stream);
+}
+
+int light_b200_decode_attn_status(int device) {
+  if (int rc = bind(device)) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail((int)e, "light_b200: decode_attn_status: %s", cudaGetErrorString(e));
+  return decode_attn_status();
+}
+
 int light_b200_moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int block_r, int block_c, int device,
                                  void *stream) {
   if (!a) return fail(LB200_E_NULL, "light_b200: moe_gemm_f8block: null argument block");

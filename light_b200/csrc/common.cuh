@@ -90,5 +90,10 @@ int moe_gemm_q(const lb200_moe_args *a, int device, cudaStream_t st);
 int moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int bR, int bC, int device, cudaStream_t st);
 int moe_umma(const lb200_moe_args *a, int kind, const float *w_scale, int bR, int bC, int device, cudaStream_t st);
 int moe_gemm_static_scratch(const lb200_moe_args *a, int device, cudaStream_t st);
+int decode_attn(const lb200_decode_attn_args *a, cudaStream_t st);
+int kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_t *pos, int dtype, int B, int KH, int D, int Cap,
+              cudaStream_t st);
+int inc_i64(int64_t *p, int n, cudaStream_t st);
+int decode_attn_status();
 
 }  // namespace lb

@@ -404,3 +404,79 @@ def MoECombine(pair_out: torch.Tensor, topk: int) -> torch.Tensor:
     for s in range(1, topk):
         acc = acc + v[:, s, :]
     return acc.contiguous()
+
+
+# --------------------------------------------------------------------------- decode-step attention
+
+def _check_pos(pos: torch.Tensor, like: torch.Tensor, op: str) -> None:
+    if pos.dtype != torch.int64 or pos.numel() != 1:
+        raise ValueError(f"ops.{op}: position must be a one-element I64 tensor, got {pos.dtype} {tuple(pos.shape)}")
+    if pos.device != like.device:
+        raise ValueError(f"ops.{op}: position on {pos.device}, tensors on {like.device}")
+
+
+def _check_cache(kbuf: torch.Tensor, vbuf: torch.Tensor, op: str) -> None:
+    if kbuf.dim() != 4 or kbuf.shape != vbuf.shape:
+        raise ValueError(f"ops.{op}: want buffers (B, KH, cap, HD), got {tuple(kbuf.shape)} / {tuple(vbuf.shape)}")
+    if not kbuf.is_contiguous() or not vbuf.is_contiguous():
+        raise ValueError(f"ops.{op}: buffers must be contiguous")
+
+
+def KVAppend(kbuf: torch.Tensor, vbuf: torch.Tensor, k: torch.Tensor, v: torch.Tensor, pos: torch.Tensor) -> None:
+    """ops.KVAppend (ops/decode_attn.go:13-62): k, v (B, KH, 1, HD) into the buffers (B, KH, cap, HD) at the
+    position held on the device."""
+    _check_cache(kbuf, vbuf, "KVAppend")
+    if k.dim() != 4 or k.shape[2] != 1 or k.shape != v.shape:
+        raise ValueError(f"ops.KVAppend: want k / v (B, KH, 1, HD), got {tuple(k.shape)} / {tuple(v.shape)}")
+    if (kbuf.shape[0], kbuf.shape[1], kbuf.shape[3]) != (k.shape[0], k.shape[1], k.shape[3]):
+        raise ValueError(f"ops.KVAppend: k {tuple(k.shape)} does not fit buffer {tuple(kbuf.shape)}")
+    if k.dtype != kbuf.dtype or v.dtype != vbuf.dtype or k.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.KVAppend: dtype mismatch ({k.dtype} into {kbuf.dtype})")
+    _check_pos(pos, kbuf, "KVAppend")
+    dev = _dev(kbuf, "KVAppend")
+    B, KH, cap, D = kbuf.shape
+    _lib.check(_lib.lib().light_b200_kv_append(_ptr(k.contiguous()), _ptr(v.contiguous()), _ptr(kbuf), _ptr(vbuf), _ptr(pos),
+                                               _ACT[k.dtype], B, KH, D, cap, dev, _stream(dev)))
+
+
+def DecodeAttention(q: torch.Tensor, kbuf: torch.Tensor, vbuf: torch.Tensor, pos: torch.Tensor, scale: float, window: int = 0,
+                    k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """ops.DecodeAttention (ops/decode_attn.go:64-170): q (B, NH, 1, HD) against the first pos + 1 keys of the
+    buffers -> (B, NH, 1, HD).  With k_new / v_new (B, KH, 1, HD) the same launch appends them at pos first
+    (KVCache.decodeAttend, models/llama.go:1156-1160, does the two ops back to back)."""
+    _check_cache(kbuf, vbuf, "DecodeAttention")
+    if q.dim() != 4 or q.shape[2] != 1:
+        raise ValueError(f"ops.DecodeAttention: want q (B, NH, 1, HD), got {tuple(q.shape)}")
+    B, NH, _, D = q.shape
+    KH, cap = kbuf.shape[1], kbuf.shape[2]
+    if kbuf.shape[0] != B or kbuf.shape[3] != D or KH == 0 or NH % KH:
+        raise ValueError(f"ops.DecodeAttention: q {tuple(q.shape)} against buffers {tuple(kbuf.shape)}")
+    if q.dtype != kbuf.dtype or q.dtype != vbuf.dtype or q.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.DecodeAttention: dtype mismatch q {q.dtype} k {kbuf.dtype} v {vbuf.dtype}")
+    if (k_new is None) != (v_new is None):
+        raise ValueError("ops.DecodeAttention: k_new and v_new come together")
+    if k_new is not None and (tuple(k_new.shape) != (B, KH, 1, D) or k_new.shape != v_new.shape or k_new.dtype != q.dtype or v_new.dtype != q.dtype):
+        raise ValueError(f"ops.DecodeAttention: k_new {tuple(k_new.shape)} {k_new.dtype} against buffers {tuple(kbuf.shape)}")
+    _check_pos(pos, q, "DecodeAttention")
+    dev = _dev(q, "DecodeAttention")
+    out = torch.empty((B, NH, 1, D), dtype=q.dtype, device=q.device)
+    qc = q.contiguous()
+    kn = k_new.contiguous() if k_new is not None else None
+    vn = v_new.contiguous() if v_new is not None else None
+    a = _lib.DecodeAttnArgs(_ptr(qc), _ptr(kbuf), _ptr(vbuf), _ptr(kn), _ptr(vn), _ptr(pos), _ptr(out), _ACT[q.dtype], B, NH, KH, cap, D,
+                            int(window), float(scale))
+    _lib.check(_lib.lib().light_b200_decode_attn(C.byref(a), dev, _stream(dev)))
+    return out
+
+
+def IncrementI64(t: torch.Tensor) -> None:
+    """ops.IncrementI64 (ops/decode_attn.go:184-205): adds one to every element in place."""
+    if t.dtype != torch.int64 or not t.is_contiguous():
+        raise ValueError(f"ops.IncrementI64: want a contiguous I64 tensor, got {t.dtype} {tuple(t.shape)}")
+    dev = _dev(t, "IncrementI64")
+    _lib.check(_lib.lib().light_b200_inc_i64(_ptr(t), t.numel(), dev, _stream(dev)))
+
+
+def decode_attn_status(device_index: int = 0) -> int:
+    """1 if a decode-attention or append launch ever saw a position outside the cache (synchronises)."""
+    return _lib.lib().light_b200_decode_attn_status(device_index)

@@ -229,5 +229,26 @@ def deepseek_route_sigmoid(logits, bias, topk: int, norm_topk: bool = True):
     return ids, ws
 
 
+def kv_append(kbuf: np.ndarray, vbuf: np.ndarray, k: np.ndarray, v: np.ndarray, pos: int) -> None:
+    """In place; arrays of any one element size, kbuf / vbuf (B, KH, Cap, D), k / v (B, KH, 1, D)."""
+    B, KH, Cap, D = kbuf.shape
+    assert kbuf.flags.c_contiguous and vbuf.flags.c_contiguous and k.dtype == kbuf.dtype
+    k, v = np.ascontiguousarray(k), np.ascontiguousarray(v)
+    _chk(lib().lo_kv_append(_p(k), _p(v), _p(kbuf), _p(vbuf), C.c_int64(pos), B, KH, D, Cap, kbuf.dtype.itemsize), "kv_append")
+
+
+def decode_attn(q, kbuf, vbuf, pos: int, scale: float, window: int = 0) -> np.ndarray:
+    """q (B, NH, 1, D), buffers (B, KH, Cap, D), all f32 -> (B, NH, 1, D) f32."""
+    q = np.ascontiguousarray(q, dtype=np.float32)
+    kbuf = np.ascontiguousarray(kbuf, dtype=np.float32)
+    vbuf = np.ascontiguousarray(vbuf, dtype=np.float32)
+    B, NH, _, D = q.shape
+    KH, Cap = kbuf.shape[1], kbuf.shape[2]
+    out = np.empty_like(q)
+    _chk(lib().lo_decode_attn(_p(q), _p(kbuf), _p(vbuf), C.c_int64(pos), _p(out), B, NH, KH, Cap, D, C.c_float(scale), window),
+         "decode_attn")
+    return out
+
+
 def has_avx2() -> bool:
     return bool(lib().lo_has_avx2())

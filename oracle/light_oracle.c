@@ -725,4 +725,59 @@ LO_API int lo_deepseek_route_sigmoid(const float *logits, const float *bias, int
   return 0;
 }
 
+/* ------------------------------------------------------------------ decode-step attention */
+
+/* ops/decode_attn.go:13-62 (KVAppend, CPU branch): k, v (B, KH, 1, D) -> row `pos` of the buffers
+ * (B, KH, Cap, D).  `elt` is the element size in bytes (the copy is type-blind). */
+LO_API int lo_kv_append(const void *k, const void *v, void *kbuf, void *vbuf, int64_t pos, int B, int KH, int D, int Cap,
+                        int elt) {
+  if (pos < 0 || pos >= Cap) return -1; /* "position %d outside capacity %d" */
+  size_t row = (size_t)D * (size_t)elt;
+  for (int bh = 0; bh < B * KH; bh++) {
+    memcpy((char *)kbuf + ((size_t)bh * Cap + (size_t)pos) * row, (const char *)k + (size_t)bh * row, row);
+    memcpy((char *)vbuf + ((size_t)bh * Cap + (size_t)pos) * row, (const char *)v + (size_t)bh * row, row);
+  }
+  return 0;
+}
+
+/* ops/decode_attn.go:64-170 (DecodeAttention, composed branch): per (batch, KV head), the g = NH / KH
+ * query rows against keys [start, n), n = pos + 1, start = n - window when a window is set and
+ * shorter than n: scores = (q k^T) * scale, softmax over the keys, times v.  f32 throughout, as the
+ * reference's CPU MatMul / Affine / Softmax are; inputs and output are f32 arrays (a bf16 case is
+ * decoded before and rounded after by the caller). */
+LO_API int lo_decode_attn(const float *q, const float *kbuf, const float *vbuf, int64_t pos, float *out, int B, int NH,
+                          int KH, int Cap, int D, float scale, int window) {
+  int n = (int)pos + 1;
+  if (KH <= 0 || NH % KH || n < 1 || n > Cap) return -1; /* "%d valid positions of %d" */
+  int g = NH / KH, start = (window > 0 && n > window) ? n - window : 0, cnt = n - start;
+  float *sc = (float *)malloc(sizeof(float) * (size_t)cnt);
+  for (int b = 0; b < B; b++)
+    for (int h = 0; h < NH; h++) {
+      int kh = h / g;
+      const float *qr = q + ((size_t)b * NH + h) * D;
+      const float *K = kbuf + (((size_t)b * KH + kh) * Cap + start) * D;
+      const float *V = vbuf + (((size_t)b * KH + kh) * Cap + start) * D;
+      float mx = -INFINITY;
+      for (int j = 0; j < cnt; j++) {
+        float a = 0.f;
+        for (int d = 0; d < D; d++) a += qr[d] * K[(size_t)j * D + d];
+        sc[j] = a * scale;
+        if (sc[j] > mx) mx = sc[j];
+      }
+      float sum = 0.f;
+      for (int j = 0; j < cnt; j++) {
+        sc[j] = expf(sc[j] - mx);
+        sum += sc[j];
+      }
+      float *o = out + ((size_t)b * NH + h) * D;
+      for (int d = 0; d < D; d++) {
+        float a = 0.f;
+        for (int j = 0; j < cnt; j++) a += (sc[j] / sum) * V[(size_t)j * D + d];
+        o[d] = a;
+      }
+    }
+  free(sc);
+  return 0;
+}
+
 LO_API int lo_has_avx2(void) { return have_avx2(); }
