@@ -18,6 +18,7 @@ from __future__ import annotations
 import argparse
 import ctypes as C
 import json
+import math
 import os
 import statistics
 import sys
@@ -139,6 +140,7 @@ class Chain:
         self.local = [torch.empty(M, e[1], device=device) for e in self.lin] if world > 1 else self.out
         self.dev_index = device.index or 0
         self.peer, self.fx, self.gather_kind = None, None, "none"
+        self.attn = None
         if world > 1:
             from light_b200 import tp
 
@@ -184,6 +186,27 @@ class Chain:
                 if o is not None:
                     prev = o
         self.fx = fx
+
+    def enable_attention(self, kv_len=1024):
+        """Adds the decode-step attention of configs[1] (32 query / 8 KV heads of dim 128, KV length
+        kv_len, f32 cache, one sequence per activation row) after every layer's q,k,v launch: one
+        light_b200_decode_attn launch that appends the new k, v at the last position and attends."""
+        assert self.world == 1
+        NHQ, NHK, HD = 32, NKV // 128, 128
+        by = {e[0]: i for i, e in enumerate(self.lin)}
+        self.pos = torch.tensor([kv_len - 1], dtype=torch.int64, device=self.device)
+        self.attn, self.attn_bytes = {}, 0
+        g = torch.Generator(device=self.device)
+        g.manual_seed(11)
+        for l in range(sum(1 for e in self.lin if e[0].endswith(".q"))):
+            kb = torch.randn(self.M, NHK, kv_len, HD, generator=g, device=self.device)
+            vb = torch.randn(self.M, NHK, kv_len, HD, generator=g, device=self.device)
+            out = torch.empty(self.M, NHQ, 1, HD, device=self.device)
+            q, k, v = (self.out[by[f"l{l}.{n}"]] for n in ("q", "k", "v"))
+            a = _lib.DecodeAttnArgs(q.data_ptr(), kb.data_ptr(), vb.data_ptr(), k.data_ptr(), v.data_ptr(), self.pos.data_ptr(),
+                                    out.data_ptr(), ops.F32, self.M, NHQ, NHK, kv_len, HD, 0, 1.0 / math.sqrt(HD))
+            self.attn[by[f"l{l}.v"]] = (a, kb, vb, out)  # issued after the launch that produces v
+            self.attn_bytes += 2 * kb.numel() * 4
 
     def _make(self, name, N, K, dt, seed):
         assert N % self.world == 0
@@ -250,6 +273,9 @@ class Chain:
             else:
                 self.launch(idx[0], st)
             n += 1
+            if self.attn and only is None and idx[-1] in self.attn:
+                _lib.check(_lib.lib().light_b200_decode_attn(C.byref(self.attn[idx[-1]][0]), self.dev_index, C.c_void_p(st)))
+                n += 1
             for i in idx:
                 if self.world > 1 and only is None and self.lin[i][0].split(".")[-1] in self.GATHERED:
                     if self.peer is not None and i in self.pidx:
@@ -346,6 +372,19 @@ def extras(chain, device, args):
         out["decode_tokens_per_s"][str(M)] = {"ms_per_step": ms, "tok_s": M / (ms * 1e-3),
                                               "weights_gbs": c.bytes_per_step() / (ms * 1e-3) / 1e9}
         del g, c
+    # the same steps with the attention of configs[1] between the q,k,v and o launches (KV length 1024, f32 cache):
+    # what the linear chain leaves out of a decode step besides norms, rope and the residual adds
+    out["decode_with_attention_kv1024"] = {}
+    for M in (1, 8, 32, 64):
+        c = Chain(device, M, share=chain, fused=chain.fused)
+        c.enable_attention(1024)
+        g = capture(c.step, device)
+        ms = timed(g.replay, steps, 3, device, lambda: None) / steps
+        base = out["decode_tokens_per_s"][str(M)]["ms_per_step"] if M > 1 else None
+        out["decode_with_attention_kv1024"][str(M)] = {"ms_per_step": ms, "tok_s": M / (ms * 1e-3), "kv_bytes_per_step": c.attn_bytes,
+                                                       "attention_us_per_layer": None if base is None else (ms - base) * 1e3 / len(c.attn)}
+        del g, c
+    assert ops.decode_attn_status(device.index or 0) == 0
     # the Q4_K decode kernel on one matrix large enough that the cost of a launch does not matter (the vocabulary
     # projection's shape, 295 MB as Q4_K): its streaming rate, next to the launch-bound average of a step
     big = synth.gaussian_weight(4242, ops.Q4_K, VOCAB, HID, device=device)

@@ -69,20 +69,22 @@ __device__ __forceinline__ void load_row(const __nv_bfloat16 *p, float (&f)[PER]
   }
 }
 
-template <int PER>
+template <int PER, int GH_>
 struct AttnCfg {
   static constexpr int D = PER * 32;
-  static constexpr int GH = 32 / PER < DA_MAX_G ? 32 / PER : DA_MAX_G;  // query heads per pass over the keys
-  static constexpr int U = PER >= 16 ? 1 : PER == 8 ? 2 : 4;           // keys in flight per warp
+  static constexpr int GH = GH_;                                        // query heads per pass over the keys
+  static constexpr int U = PER >= 16 ? 1 : PER == 8 ? 2 : 4;           // keys per batch of a warp (two batches in flight)
   static constexpr int ROW = D + 2;                                     // max, sum, D dims
   static constexpr int WPART = DA_WARPS * GH * ROW;                     // floats: per-warp partials of a pass
   static size_t smem(int g) { return (size_t)(WPART + g * ROW) * sizeof(float); }
 };
 
-template <typename T, int PER>
+template <typename T, int PER, int GH_>
 __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) {
-  using Cfg = AttnCfg<PER>;
+  using Cfg = AttnCfg<PER, GH_>;
   constexpr int D = Cfg::D, GH = Cfg::GH, U = Cfg::U, ROW = Cfg::ROW;
+  constexpr int NV = GH * U;  // dot products per batch of keys
+  constexpr int SH = NV >= 32 ? 0 : NV == 16 ? 1 : NV == 8 ? 2 : NV == 4 ? 3 : NV == 2 ? 4 : 5;
   extern __shared__ __align__(16) float sm[];  // [warp][head of the pass][ROW] then [head][ROW] of this CTA
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -111,6 +113,7 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
   for (int h0 = 0; h0 < g; h0 += GH) {
     const int gh = min(GH, g - h0);
     float qf[GH][PER], acc[GH][PER], m[GH], l[GH];
+    float m_own = -INFINITY;  // m[head of the value this lane owns in the reduce-scatter]
 #pragma unroll
     for (int h = 0; h < GH; h++) {
       m[h] = -INFINITY, l[h] = 0.f;
@@ -118,31 +121,65 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
       for (int p = 0; p < PER; p++) acc[h][p] = 0.f, qf[h][p] = 0.f;
       if (h < gh) load_row<PER>(static_cast<const T *>(a.q) + ((size_t)b * a.NH + (size_t)kh * g + h0 + h) * D + lane * PER, qf[h]);
     }
-    for (int j = j0 + warp * U; j < j1; j += DA_WARPS * U) {
-      float kf[U][PER], vf[U][PER];
+    float kf[U][PER], vf[U][PER];
+    auto fetch = [&](int j, float (&kk)[U][PER], float (&vv)[U][PER]) {
 #pragma unroll
       for (int u = 0; u < U; u++) {
         if (j + u < j1) {
           const bool fresh = kn && j + u == (int)pos;
-          load_row<PER>(fresh ? kn : Kb + (size_t)(j + u) * D, kf[u]);
-          load_row<PER>(fresh ? vn : Vb + (size_t)(j + u) * D, vf[u]);
+          load_row<PER>(fresh ? kn : Kb + (size_t)(j + u) * D, kk[u]);
+          load_row<PER>(fresh ? vn : Vb + (size_t)(j + u) * D, vv[u]);
         } else {
 #pragma unroll
-          for (int p = 0; p < PER; p++) kf[u][p] = 0.f, vf[u][p] = 0.f;
+          for (int p = 0; p < PER; p++) kk[u][p] = 0.f, vv[u][p] = 0.f;
         }
       }
+    };
+    if (j0 + warp * U < j1) fetch(j0 + warp * U, kf, vf);
+    for (int j = j0 + warp * U; j < j1; j += DA_WARPS * U) {
+      float kx[U][PER], vx[U][PER];  // the next batch is requested before this one is used
+      if (j + DA_WARPS * U < j1) fetch(j + DA_WARPS * U, kx, vx);
+      if constexpr (NV <= 32) {
+        // The GH x U dot products of this batch are summed over the lanes by a reduce-scatter: at every
+        // step a lane hands half of its partial sums to its partner and keeps the other half, so that
+        // value i (head i / U, key i % U) ends up, complete, in lanes [i << SH, (i + 1) << SH) -- NV + 1
+        // shuffles instead of 5 NV -- and the exponentials are computed once, by the owners.
+        float v[NV];
 #pragma unroll
-      for (int h = 0; h < GH; h++) {
-        if (h < gh) {
-          float s[U], mx = m[h];
+        for (int h = 0; h < GH; h++)
 #pragma unroll
           for (int u = 0; u < U; u++) {
             float d = 0.f;
 #pragma unroll
             for (int p = 0; p < PER; p++) d = fmaf(qf[h][p], kf[u][p], d);
-            s[u] = j + u < j1 ? warp_sum(d) * a.scale : -INFINITY;
-            mx = fmaxf(mx, s[u]);
+            v[h * U + u] = d;
           }
+        int cnt = NV;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+          if (cnt > 1) {
+            const int half = cnt / 2;
+            const bool up = lane & off;
+#pragma unroll
+            for (int i = 0; i < half; i++) {
+              const float send = up ? v[i] : v[i + half], keep = up ? v[i + half] : v[i];
+              v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+            }
+            cnt = half;
+          } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+          }
+        }
+        const int own = lane >> SH;  // this lane's value: head own / U, key own % U
+        const float s_own = j + (own % U) < j1 ? v[0] * a.scale : -INFINITY;
+        float bm = s_own;            // maximum over the batch's keys of the own head
+#pragma unroll
+        for (int off = 1 << SH; off < (U << SH); off <<= 1) bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, off));
+        m_own = fmaxf(m_own, bm);
+        const float e_own = __expf(s_own - m_own);  // -inf for a missing key: 0
+#pragma unroll
+        for (int h = 0; h < GH; h++) {
+          const float mx = fmaxf(m[h], __shfl_sync(0xffffffffu, bm, (h * U) << SH));
           const float corr = __expf(m[h] - mx);  // m = -inf on the first batch: 0
           m[h] = mx;
           l[h] *= corr;
@@ -150,12 +187,45 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
           for (int p = 0; p < PER; p++) acc[h][p] *= corr;
 #pragma unroll
           for (int u = 0; u < U; u++) {
-            const float e = __expf(s[u] - mx);  // -inf for a missing key: 0
+            const float e = __shfl_sync(0xffffffffu, e_own, (h * U + u) << SH);
             l[h] += e;
 #pragma unroll
             for (int p = 0; p < PER; p++) acc[h][p] = fmaf(e, vf[u][p], acc[h][p]);
           }
         }
+      } else {
+#pragma unroll
+        for (int h = 0; h < GH; h++) {
+          if (h < gh) {
+            float s[U], mx = m[h];
+  #pragma unroll
+            for (int u = 0; u < U; u++) {
+              float d = 0.f;
+  #pragma unroll
+              for (int p = 0; p < PER; p++) d = fmaf(qf[h][p], kf[u][p], d);
+              s[u] = j + u < j1 ? warp_sum(d) * a.scale : -INFINITY;
+              mx = fmaxf(mx, s[u]);
+            }
+            const float corr = __expf(m[h] - mx);  // m = -inf on the first batch: 0
+            m[h] = mx;
+            l[h] *= corr;
+  #pragma unroll
+            for (int p = 0; p < PER; p++) acc[h][p] *= corr;
+  #pragma unroll
+            for (int u = 0; u < U; u++) {
+              const float e = __expf(s[u] - mx);  // -inf for a missing key: 0
+              l[h] += e;
+  #pragma unroll
+              for (int p = 0; p < PER; p++) acc[h][p] = fmaf(e, vf[u][p], acc[h][p]);
+            }
+          }
+        }
+      }
+      if (j + DA_WARPS * U < j1) {
+#pragma unroll
+        for (int u = 0; u < U; u++)
+#pragma unroll
+          for (int p = 0; p < PER; p++) kf[u][p] = kx[u][p], vf[u][p] = vx[u][p];
       }
     }
     // ---- the warps of this CTA
@@ -261,10 +331,10 @@ cudaError_t launch_chain(K kern, dim3 grid, dim3 block, size_t smem, unsigned cl
   return cudaLaunchKernelEx(&cfg, kern, args...);
 }
 
-template <typename T, int PER>
+template <typename T, int PER, int GH>
 int launch_attn(const AttnArgs &a, int ks, cudaStream_t st) {
-  auto kern = decode_attn_kernel<T, PER>;
-  const size_t smem = AttnCfg<PER>::smem(a.NH / a.KH);
+  auto kern = decode_attn_kernel<T, PER, GH>;
+  const size_t smem = AttnCfg<PER, GH>::smem(a.NH / a.KH);
   static size_t smem_set = 0;
   if (smem > smem_set) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -276,14 +346,31 @@ int launch_attn(const AttnArgs &a, int ks, cudaStream_t st) {
   return launched("decode_attn");
 }
 
+// heads per pass: the smallest of 1, 2, 4, ... that covers the group, while heads x dims-per-lane stays
+// within 32 accumulators per lane (larger groups walk the keys again; they hit in L2)
+template <typename T, int PER>
+int launch_attn_g(const AttnArgs &a, int ks, cudaStream_t st) {
+  constexpr int GMAX = 32 / PER < DA_MAX_G ? 32 / PER : DA_MAX_G;
+  const int g = a.NH / a.KH;
+  if constexpr (GMAX >= 2) {
+    if (g <= GMAX / 2) {
+      if constexpr (GMAX >= 4) {
+        if (g <= GMAX / 4) return launch_attn<T, PER, GMAX / 4>(a, ks, st);
+      }
+      return launch_attn<T, PER, GMAX / 2>(a, ks, st);
+    }
+  }
+  return launch_attn<T, PER, GMAX>(a, ks, st);
+}
+
 template <typename T>
 int launch_attn_d(const AttnArgs &a, int D, int ks, cudaStream_t st) {
   switch (D / 32) {
-    case 1: return launch_attn<T, 1>(a, ks, st);
-    case 2: return launch_attn<T, 2>(a, ks, st);
-    case 4: return launch_attn<T, 4>(a, ks, st);
-    case 8: return launch_attn<T, 8>(a, ks, st);
-    case 16: return launch_attn<T, 16>(a, ks, st);
+    case 1: return launch_attn_g<T, 1>(a, ks, st);
+    case 2: return launch_attn_g<T, 2>(a, ks, st);
+    case 4: return launch_attn_g<T, 4>(a, ks, st);
+    case 8: return launch_attn_g<T, 8>(a, ks, st);
+    case 16: return launch_attn_g<T, 16>(a, ks, st);
   }
   return fail(LB200_E_SHAPE, "light_b200: decode_attn: head dim %d (want 32, 64, 128, 256 or 512)", D);
 }
