@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(D_THREADS, 2) decode_umma_kernel(const typenam
     constexpr int UPB = 4 / Row::STEPS;  // load units per 256-element block
     const int b0 = kb0 / 4, b1 = kb1 / 4;
     // The packed blocks come in through a ring of shared memory, copied 16 bytes per lane with the
-    // 14 .. 16 lanes of a half-warp on one row (coalesced), Cfg::RS blocks ahead of their use; a
+    // 9 .. 16 lanes of a half-warp on one row (coalesced), Cfg::RS blocks ahead of their use; a
     // thread then reads its own row's slot.  (One thread per row reading global memory directly
     // touches 32 lines per load instruction and is bound by the load unit, not by HBM.)
     const int c_row = warp * 16 + (lane >> 4) * 8, c_piece = lane & 15;  // rows c_row + i, i = 0..7
@@ -186,6 +186,10 @@ __global__ void __launch_bounds__(D_THREADS, 2) decode_umma_kernel(const typenam
             cp_async16(dst, src);
           else if (src < lim)
             cp_async16_part(dst, src, (uint32_t)(lim - src));
+          if constexpr (Row::RAW_G > 16) {  // a 17th granule (Q8_0: 272 bytes): the first lanes copy it too
+            static_assert(Row::RAW_G <= 32, "two granules per lane at most");
+            if (c_piece < Row::RAW_G - 16) cp_async16(dst + 256, src + 256);
+          }
         }
       }
       i_b++;
@@ -353,11 +357,12 @@ int sm_count(int device) {
 constexpr int DECODE_MAX_M = 64;
 // Token counts from which this kernel is the fastest one measured (below it the register-fed
 // kernels win); LIGHT_B200_DECODE_MIN_M overrides both (tuning knob).
-int g_min_m_gguf = 17, g_min_m_other = 1;
+int g_min_m_gguf = 17, g_min_m_other = 1, g_min_m_q80 = 2;  // LIGHT_B200_DECODE_MIN_M / _MIN_M_Q80 (tuning knobs)
 bool g_knobs_read = false;
 void read_knobs() {
   if (g_knobs_read) return;
   if (const char *e = getenv("LIGHT_B200_DECODE_MIN_M")) g_min_m_gguf = g_min_m_other = atoi(e);
+  if (const char *e = getenv("LIGHT_B200_DECODE_MIN_M_Q80")) g_min_m_q80 = atoi(e) < 1 ? 1 : atoi(e);
   g_knobs_read = true;
 }
 
@@ -373,10 +378,14 @@ int decode_umma_status() {
 // its other kernels), other values are errors.
 int gguf_decode_umma(int type, const float *x, const void *w, float *out, int M, int N, int K, int device, cudaStream_t st) {
   read_knobs();
-  if (M < 2 || M < g_min_m_gguf || M > DECODE_MAX_M || K % 256 || ((uintptr_t)x & 15)) return 0;
+  if (M > DECODE_MAX_M || K % 256 || ((uintptr_t)x & 15)) return 0;
+  if (M < (type == LB200_Q8_0 ? g_min_m_q80 : (g_min_m_gguf < 2 ? 2 : g_min_m_gguf))) return 0;
   GgufCtx ctx{(const uint8_t *)w};
   int rc;
-  if (type == LB200_Q4_K) {
+  if (type == LB200_Q8_0) {  // no register-fed decode kernel exists for this format: every token count down to g_min_m_q80
+    if ((uintptr_t)w & 15) return 0;
+    rc = launch_by_act<Q80Row>(ctx, x, out, LB200_F32, M, N, K, sm_count(device), st);
+  } else if (type == LB200_Q4_K) {
     if ((uintptr_t)w & 15) return 0;
     rc = launch_by_act<Q4KRow>(ctx, x, out, LB200_F32, M, N, K, sm_count(device), st);
   } else if (type == LB200_Q6_K) {

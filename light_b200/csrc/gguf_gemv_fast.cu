@@ -422,11 +422,6 @@ constexpr int TOK_SLAB = TOK_SX + TOK * 32;
 constexpr int Q4K_TOK_STAGES = 3;
 constexpr int Q4K_TOK_SMEM = WARPS * Q4K_TOK_STAGES * Q4K_TILE_BYTES + WARPS * TOK_SLAB + WARPS * GROUP * 32 * 16;
 
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(v) : "r"(addr));
-  return v;
-}
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t *>(&v); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 

@@ -451,14 +451,17 @@ int gguf_prefill(int type, const float *x, const void *w, float *out, int M, int
     if ((uintptr_t)w & 15) return 0;
   } else if (type == LB200_Q6_K) {
     if (((uintptr_t)w & 3) || ((size_t)(K >> 8) * 210) % 4) return 0;  // rows must start 4-byte aligned
+  } else if (type == LB200_Q8_0) {
+    if ((uintptr_t)w & 15) return 0;  // K % 256 == 0 makes every row a whole number of 16-byte granules
   } else {
     return 0;
   }
   void *ws;
   if (!get_ws(device, LB200_F32, M, K, &ws)) return 0;
   GgufCtx ctx{(const uint8_t *)w};
-  int rc = type == LB200_Q4_K ? launch_by_act<Q4KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st)
-                              : launch_by_act<Q6KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st);
+  int rc = type == LB200_Q4_K   ? launch_by_act<Q4KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st)
+           : type == LB200_Q6_K ? launch_by_act<Q6KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st)
+                                : launch_by_act<Q80Row>(x, LB200_F32, ctx, out, M, N, K, ws, st);
   return rc ? rc : 1;
 }
 
@@ -557,6 +560,8 @@ int moe_umma(const lb200_moe_args *a, int kind, const float *w_scale, int bR, in
       rc = moe_launch<Q4KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
     else if (a->dtype == LB200_Q6_K && ((size_t)(a->K >> 8) * 210) % 4 == 0)
       rc = moe_launch<Q6KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
+    else if (a->dtype == LB200_Q8_0 && !((uintptr_t)a->weights & 15))
+      rc = moe_launch<Q80Row, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
     else
       return 0;
   } else {

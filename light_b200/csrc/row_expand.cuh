@@ -216,6 +216,64 @@ struct Q6KRow {
   }
 };
 
+// Q8_0 (34 B per 32 elements): [f16 d | int8 q[32]], blocks only 2-byte aligned.  One load() fetches 128
+// elements = 4 blocks = 136 bytes as 34 aligned words (rows start 4-byte aligned, checked on the host, and
+// 136 is a multiple of 8); block i of the unit starts 34 i bytes in, so its codes sit on word boundaries
+// for odd i and 16 bits into a word for even i: a funnel shift known at compile time.  Packed f16
+// arithmetic: XOR 0x80 makes the codes unsigned, PRMT builds (1024 + 128 + q) pairs in natural order, one
+// HADD2 takes 1152 off (q, exact), one HMUL2 applies d: the weight fl16(d q), one rounding.
+struct Q80Row {
+  using Ctx = GgufCtx;
+  static constexpr bool KPERM = false;
+  static constexpr int STEPS = 2;
+  const uint8_t *row;
+  uint32_t w[34];
+  __device__ __forceinline__ void init(const Ctx &c, int e, int n, int N, int K) {
+    row = c.w + ((size_t)e * N + n) * (size_t)(K / 32) * 34;
+  }
+  __device__ __forceinline__ void load(int unit) {
+    const uint32_t *p = reinterpret_cast<const uint32_t *>(row + (size_t)unit * 136);
+#pragma unroll
+    for (int i = 0; i < 34; i++) w[i] = __ldg(p + i);
+  }
+  __device__ __forceinline__ void prefetch(int unit) const {
+    if (!(unit & 1)) prefetch_l2(row + (size_t)(unit >> 1) * 272, 272);
+  }
+  // staged path: a 256-element run is 272 bytes = 17 granules (rows are 16-byte aligned when K % 256 == 0)
+  static constexpr int RAW_G = 17, RAW_PITCH = 304;
+  __device__ __forceinline__ const uint8_t *raw_end() const { return nullptr; }
+  __device__ __forceinline__ const uint8_t *raw_src(int b) const { return row + (size_t)b * 272; }
+  __device__ __forceinline__ const uint8_t *raw_src_unaligned(int b) const { return raw_src(b); }
+  __device__ __forceinline__ static size_t row_stride(const Ctx &, int K) { return (size_t)(K / 32) * 34; }
+  __device__ __forceinline__ void load_smem(uint32_t slot, int unit) {
+    const uint32_t a = slot + (uint32_t)(unit & 1) * 136u;
+#pragma unroll
+    for (int i = 0; i < 34; i++) w[i] = lds32(a + 4 * i);
+  }
+  template <bool BF16, int PART = 2>
+  __device__ __forceinline__ void step(int j, uint32_t tile, int r) const {
+    const __half2 off = __float2half2_rn(-1152.f);
+#pragma unroll
+    for (int c = (PART == 1 ? 4 : 0); c < (PART == 0 ? 4 : 8); c++) {  // chunk c: k = 8c .. 8c+7 of block 2j + c/4
+      const int bi = 2 * j + (c >> 2), byte0 = 34 * bi, qw = (byte0 + 2) / 4 + 2 * (c & 3);
+      const uint32_t dw = w[byte0 / 4];
+      const __half dh = (byte0 & 2) ? __ushort_as_half((unsigned short)(dw >> 16)) : __ushort_as_half((unsigned short)(dw & 0xFFFFu));
+      const __half2 d2 = __half2half2(dh);
+      uint32_t o[4];
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+        const uint32_t raw = (bi & 1) ? w[qw + e] : __funnelshift_r(w[qw + e], w[qw + e + 1], 16);
+        const uint32_t u = raw ^ 0x80808080u;
+        const uint32_t p01 = __byte_perm(u, 0x64646464u, 0x5140), p23 = __byte_perm(u, 0x64646464u, 0x7362);
+        const __half2 w01 = __hmul2(__hadd2(*reinterpret_cast<const __half2 *>(&p01), off), d2);
+        const __half2 w23 = __hmul2(__hadd2(*reinterpret_cast<const __half2 *>(&p23), off), d2);
+        o[2 * e] = *reinterpret_cast<const uint32_t *>(&w01), o[2 * e + 1] = *reinterpret_cast<const uint32_t *>(&w23);
+      }
+      st_chunk(tile + swz(r, c), make_uint4(o[0], o[1], o[2], o[3]));
+    }
+  }
+};
+
 // Group-quantized int4 in the reference's canonical layout (quant/int4.go:12-31): codes u32 (N, K/8),
 // nibble i of word c = element 8c + i; scales / zeros f32 (N, K/G).  W = fl(s * fl(code - z)): the two
 // f32 roundings of the reference's dequantize kernel (kernels/cuda/src/int4.cu:16-41), then one

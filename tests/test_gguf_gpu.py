@@ -60,8 +60,8 @@ def test_matmul_q_reference_shapes(cuda, oracle, name, K):
         want = x.numpy().astype(np.float64) @ deq.T
         scale = np.abs(want).max()
         # M = 1 and the shape-generic kernel compute in f32 (the reference's 2e-4); the batched
-        # tensor-core kernels (Q4_K / Q6_K, 2 <= M <= 64) round weights and activations to f16
-        f16_path = M > 1 and name in ("q4_k", "q6_k")
+        # tensor-core kernels (Q4_K / Q6_K / Q8_0, 2 <= M <= 64) round weights and activations to f16
+        f16_path = M > 1 and name in ("q4_k", "q6_k", "q8_0")
         assert np.max(np.abs(got - want)) / scale <= (2e-3 if f16_path else 2e-4), (name, K, M)
         assert rel_l2(got, want) <= TOL_REL_L2
 
@@ -94,7 +94,8 @@ def test_matmul_q_decode_kernels(cuda, oracle, name, N, K):
             assert rel_l2(host[32:32 + M * N].reshape(M, N), want) <= (1e-4 if M == 1 else TOL_REL_L2), (name, N, K, M, seed)
 
 
-@pytest.mark.parametrize("name,N,K", [("q4_k", 37, 1024), ("q4_k", 4096, 4096), ("q6_k", 50, 2048), ("q6_k", 1000, 4096)])
+@pytest.mark.parametrize("name,N,K", [("q4_k", 37, 1024), ("q4_k", 4096, 4096), ("q6_k", 50, 2048), ("q6_k", 1000, 4096),
+                                      ("q8_0", 37, 1024), ("q8_0", 300, 4096), ("q8_0", 129, 256)])
 def test_matmul_q_batched_decode(cuda, oracle, name, N, K):
     """Batched decode (BASELINE config 2: M = 8, 32, 64, plus ragged token counts): one pass over the
     weights per 16 tokens on the tensor cores; f16 operands, 1e-3 relative L2 against the f64 oracle."""

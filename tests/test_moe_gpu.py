@@ -147,9 +147,9 @@ def test_moe_grouped_tensor_core_dense_bf16(cuda, oracle):
     assert ops.prefill_status(0) == 0
 
 
-@pytest.mark.parametrize("name", ["q4_k", "q6_k"])
+@pytest.mark.parametrize("name", ["q4_k", "q6_k", "q8_0"])
 def test_moe_grouped_tensor_core_gguf(cuda, oracle, name):
-    dt = {"q4_k": ops.Q4_K, "q6_k": ops.Q6_K}[name]
+    dt = {"q4_k": ops.Q4_K, "q6_k": ops.Q6_K, "q8_0": ops.Q8_0}[name]
     T, E, topk, N, K = 400, 6, 2, 264, 512
     r = _skewed_routing(141, T, E, topk, cuda)
     raw = synth.random_blocks(142, dt, E * N, K)

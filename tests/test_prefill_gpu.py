@@ -62,6 +62,15 @@ def test_q6k_prefill_matches_f64_oracle(cuda, oracle, M, N, K):
     assert ops.prefill_status(0) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(65, 256, 256), (200, 300, 1024), (513, 1000, 2048), (1024, 1024, 14336), (70, 40, 800)])
+def test_q80_prefill_matches_f64_oracle(cuda, oracle, M, N, K):
+    """Q8_0 through the same kernel (K = 800 is no multiple of 256 and takes the shape-generic kernel)."""
+    for seed, bf16_x in ((341, True), (342, False)):
+        err = _case(ops.Q8_0, M, N, K, seed, cuda, oracle, bf16_x)
+        assert err <= (5e-4 if bf16_x else 1e-3), (M, N, K, seed, err)
+    assert ops.prefill_status(0) == 0
+
+
 def _bf16_round(a: np.ndarray) -> np.ndarray:
     return torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64)
 
