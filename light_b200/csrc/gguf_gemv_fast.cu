@@ -1057,6 +1057,183 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q6k_gemv_mma_kernel(const float
   cp_async_wait<0>();
 }
 
+// ------------------------------------------------------------------------------------ Q8_0
+//
+// The Q6_K kernel's structure (per-warp ring of 16-row tiles, activations staged per run of 256 k with the
+// next run requested ahead, one MMA per 16-element sub-block with the hi and lo halves of x in
+// neighbouring columns) on 34-byte blocks: a run of 256 k is eight blocks = 272 bytes = 17 granules per
+// row, rows are whole granules (K % 256 == 0), and a 272-byte pitch puts rows g and lanes t on 32
+// different banks.  reference: matmul_q8_0_f32_mv, kernels/cuda/src/matmul_q.cu:58-431.
+constexpr int Q80_PITCH = 272;
+constexpr int Q80_TILE_BYTES = ROWS * Q80_PITCH;
+constexpr int Q80_STAGES = 2;
+
+template <int S>
+__global__ void __launch_bounds__(WARPS * 32, 2) q80_gemv_mma_kernel(const float *__restrict__ x, const uint8_t *__restrict__ w,
+                                                                    float *__restrict__ out, int N, int K) {
+  using SL = Slab<16>;
+  extern __shared__ __align__(16) unsigned char dyn[];  // ring: WARPS x S tiles
+  __shared__ __align__(16) unsigned char slabs[WARPS][SL::BYTES];
+  __shared__ __align__(16) unsigned char zero[SL::ZERO_BYTES];
+  __shared__ __align__(16) float2 red[2][WARPS * GROUP * 32];  // by group parity
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int nb = K >> 8;
+  const uint32_t row_bytes = (uint32_t)nb * 272u;  // eight 34-byte blocks per 256 elements: rows are whole granules
+  for (int i = threadIdx.x; i < SL::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
+
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + warp * (S * Q80_TILE_BYTES);
+  const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
+  const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
+  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(&red[0][warp * GROUP * 32 + lane]);
+  constexpr uint32_t RED_PARITY = WARPS * GROUP * 32 * 8;
+  // B address of the MMA of (group q, u), which works on sub-block 8h + 2q + u: column 2q + u
+  // carries the hi half of x, the neighbouring column 2q + 1 - u (unused in this accumulator) the
+  // lo half; a lane of those columns reads elements 4t..4t+3 (h adds an immediate).  All other
+  // columns read zeros.
+  uint32_t pb[4][2];
+#pragma unroll
+  for (int q = 0; q < 4; q++)
+#pragma unroll
+    for (int u = 0; u < 2; u++)
+      pb[q][u] = (g >> 1) == q ? slab + (2 * q + u) * SL::SUB_BYTES + 8 * t + ((g & 1) == u ? 0 : SL::LO_OFF) : szero;
+
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const int t0 = (int)((uint32_t)tiles * blockIdx.x / gridDim.x), t1 = (int)((uint32_t)tiles * (blockIdx.x + 1) / gridDim.x);
+
+  // requests: lanes 0..15 / 16..31 copy granules 0..15 of rows 2i / 2i+1, i = 0..7; lanes 0 / 16 also the 17th
+  const uint32_t c_rsub = lane >> 4, c_piece = lane & 15;
+  int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_gt < t1 && warp < nb) {
+      const int r0 = min((i_gt + i_rt) * ROWS, N - ROWS);
+      const uint8_t *src = w + ((size_t)(r0 + c_rsub) * row_bytes + (uint32_t)i_b * 272u + c_piece * 16);
+      uint32_t dst = ring + i_slot * Q80_TILE_BYTES + c_rsub * Q80_PITCH + c_piece * 16;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        cp_async16(dst, src);
+        if (c_piece == 0) cp_async16(dst + 256, src + 256);
+        src += 2 * row_bytes, dst += 2 * Q80_PITCH;
+      }
+      i_slot = (i_slot + 1) & (S - 1);
+      if (++i_rt == i_gs) {
+        i_rt = 0, i_b += WARPS;
+        if (i_b >= nb) i_b = warp, i_gt += i_gs, i_gs = min(GROUP, t1 - i_gt);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int p = 0; p < S; p++) issue();
+
+  pdl_wait();  // x is the previous launch's output; the weights requested above are not
+  __syncthreads();
+  float4 xn[2];  // the activations of the block this warp stages next, requested one block ahead
+  auto load_x = [&](int b) {
+    xn[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+    xn[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+  };
+  if (warp < nb) load_x(warp);
+
+  // One unit: rows g, g+8 of one tile x one run of 256 k (eight 34-byte blocks), out of ring slot `sb`.
+  // Sub-block s = 8h + 2q + u (16 codes) is half s & 1 of block s >> 1; lane t takes its word t.  Even
+  // blocks start 2 bytes into a word (34 j + 2), odd ones on a word boundary.  XOR 0x80 makes the codes
+  // unsigned and PRMT gives f16 (1024 + 128 + q): the MMA sums (1152 + q) x, and 1152 sum(x) comes off.
+  auto unit = [&](uint32_t sb, const float2 (&sx)[2], float up, float (&vr)[2]) {
+    uint32_t wq[2][16];
+    float dd[2][2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const uint32_t blk = sb + (g + 8 * r) * Q80_PITCH;
+#pragma unroll
+      for (int s = 0; s < 16; s++) {
+        const uint32_t a = blk + 34 * (s >> 1) + 2 + 16 * (s & 1) + 4 * t;
+        wq[r][s] = (((s >> 1) & 1) ? lds32(a) : __funnelshift_r(lds32(a - 2), lds32(a + 2), 16)) ^ 0x80808080u;
+      }
+      dd[r][0] = f16_bits_to_f32((uint16_t)lds16(blk + 34 * t)), dd[r][1] = f16_bits_to_f32((uint16_t)lds16(blk + 34 * (4 + t)));
+    }
+    __syncwarp();  // the slot is free again
+    issue();
+    vr[0] = vr[1] = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // u = 0 / u = 1 chains
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int s = 8 * h + 2 * q + u;
+          uint32_t a[4];
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            a[r] = __byte_perm(wq[r][s], 0x64646464u, 0x4240);      // f16x2 (1024 + b0, 1024 + b2)
+            a[2 + r] = __byte_perm(wq[r][s], 0x64646464u, 0x4341);  // f16x2 (1024 + b1, 1024 + b3)
+          }
+          const uint2 bh = lds64(pb[q][u] + h * (8 * SL::SUB_BYTES));
+          if (u == 0)
+            mma16816(d0, a[0], a[1], a[2], a[3], bh.x, bh.y);
+          else
+            mma16816(d1, a[0], a[1], a[2], a[3], bh.x, bh.y);
+        }
+      }
+      // lane (g, t): d0[0] + d0[1] = row g, sub-block 8h+2t; d1[0] + d1[1] = row g, sub-block 8h+2t+1: the
+      // two halves of block 4h + t; [2], [3] the same for row g+8
+#pragma unroll
+      for (int r = 0; r < 2; r++)
+        vr[r] += dd[r][h] * ((d0[2 * r] + d0[2 * r + 1]) + (d1[2 * r] + d1[2 * r + 1]) - 1152.f * (sx[h].x + sx[h].y));
+    }
+    vr[0] *= up, vr[1] *= up;
+  };
+
+  int slot = 0, parity = 0;
+  for (int gt = t0; gt < t1; gt += GROUP, parity ^= 1) {
+    const int gs = min(GROUP, t1 - gt);
+    const uint32_t red_g = red_lane + parity * RED_PARITY;
+    for (int b = warp; b < nb; b += WARPS) {
+      // this block's activations into the warp's slab; the next block's are requested meanwhile
+      const float4 xv[2] = {xn[0], xn[1]};
+      {
+        const int bn = b + WARPS < nb ? b + WARPS : warp;
+        if (b + WARPS < nb || gt + GROUP < t1) load_x(bn);
+      }
+      __syncwarp();  // every lane is done reading the previous block's slab
+      const float up = stage_block<16>(xv, slab, lane);
+      __syncwarp();
+      float2 sx[2];
+      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[0].x), "=f"(sx[0].y) : "r"(slab + SL::SX_OFF + 8 * t));
+      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[1].x), "=f"(sx[1].y) : "r"(slab + SL::SX_OFF + 32 + 8 * t));
+      for (int rt = 0; rt < gs; rt++) {
+        cp_async_wait<S - 1>();  // this lane's granules of the tile have landed ...
+        __syncwarp();            // ... and so have the other lanes'
+        const uint32_t sb = ring + slot * Q80_TILE_BYTES;
+        slot = (slot + 1) & (S - 1);
+        float vr[2];
+        unit(sb, sx, up, vr);
+        // the warp's first block of a group overwrites what an earlier group left behind
+        const uint32_t ra = red_g + rt * (32 * 8);
+        float2 o = make_float2(0.f, 0.f);
+        if (b != warp) asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(o.x), "=f"(o.y) : "r"(ra));
+        asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(ra), "f"(o.x + vr[0]), "f"(o.y + vr[1]));
+      }
+    }
+    __syncthreads();  // also orders this group's reads of red[parity] before its reuse two groups on
+    for (int i = threadIdx.x; i < gs * ROWS; i += WARPS * 32) {
+      const int rt = i >> 4, row = i & 15, gg = row & 7, hi = row >> 3;
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) {
+        if (wq >= nb) break;  // a warp without a K block never wrote its part
+        const float2 *p = &red[parity][(wq * GROUP + rt) * 32 + gg * 4];
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;
+      }
+      const int orow = min((gt + rt) * ROWS, N - ROWS) + row;
+      out[orow] = v;
+    }
+  }
+  cp_async_wait<0>();
+}
+
 // ------------------------------------------------------------------------------------ Q6_K, 2 .. 8 rows of x
 //
 // Tokens as MMA columns, as in q4k_gemv_tok_kernel.  The 16 k slots of an MMA are one 16-element
@@ -1270,6 +1447,8 @@ int gguf_gemv_fast_init(int device) {
     err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                WARPS * Q6K_STAGES * Q6K_TILE_BYTES);
   if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q80_gemv_mma_kernel<Q80_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * Q80_STAGES * Q80_TILE_BYTES);
+  if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -1302,7 +1481,7 @@ static const TpArgs NO_TP = {};
 
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
   if (M != 1 || K % 256 || N < ROWS) return 0;
-  if (type != LB200_Q4_K && type != LB200_Q6_K) return 0;
+  if (type != LB200_Q4_K && type != LB200_Q6_K && type != LB200_Q8_0) return 0;
   if ((uintptr_t)w & 15) return 0;
   // Q6_K: an even number of blocks per row keeps every row's skew equal for rows 8 apart and
   // word-aligned for even blocks; byte offsets are 32-bit
@@ -1315,6 +1494,12 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
     return q4k_launch(x, a, NO_TP, tiles, K, st);
   }
   const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
+  if (type == LB200_Q8_0) {
+    int rc = launch_pdl(q80_gemv_mma_kernel<Q80_STAGES>, grid, (size_t)WARPS * Q80_STAGES * Q80_TILE_BYTES, st, x, wb, out, N, K);
+    if (rc) return rc;
+    rc = launched("matmul_q (decode)");
+    return rc ? rc : 1;
+  }
   int rc = launch_pdl(q6k_gemv_mma_kernel<Q6K_STAGES, false>, grid, (size_t)WARPS * Q6K_STAGES * Q6K_TILE_BYTES, st, x, wb, out, NO_TP, N, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");

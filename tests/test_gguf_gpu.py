@@ -68,7 +68,7 @@ def test_matmul_q_reference_shapes(cuda, oracle, name, K):
 
 @pytest.mark.parametrize("name,N,K", [("q4_k", 16, 256), ("q4_k", 37, 2048), ("q4_k", 1, 4096), ("q4_k", 100, 14336),
                                       ("q6_k", 16, 512), ("q6_k", 37, 2048), ("q6_k", 5, 14336), ("q6_k", 9, 768),
-                                      ("q8_0", 33, 4096)])
+                                      ("q8_0", 33, 4096), ("q8_0", 16, 256), ("q8_0", 37, 2048), ("q8_0", 100, 14336)])
 def test_matmul_q_decode_kernels(cuda, oracle, name, N, K):
     """The decode kernels (M <= 4) on ragged N, one-block and long rows, both weight kinds; the
     output buffer sits between canaries that must survive."""
