@@ -1480,6 +1480,13 @@ static int q4k_launch(const float *x, const MultiArgs &a, const TpArgs &tp, int 
 static const TpArgs NO_TP = {};
 
 int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st) {
+  if (type == LB200_Q8_0 && M >= 2 && M <= 3) {  // no token-column kernel for this format: a pass per row beats the tensor-core kernel up to three rows
+    for (int m = 0; m < M; m++) {
+      const int rc = gguf_gemv_fast(type, x + (size_t)m * K, w, out + (size_t)m * N, 1, N, K, st);
+      if (rc != 1) return m == 0 ? rc : fail(rc < 0 ? rc : LB200_E_SHAPE, "light_b200: matmul_q (decode): row %d refused after row 0 was launched", m);
+    }
+    return 1;
+  }
   if (M != 1 || K % 256 || N < ROWS) return 0;
   if (type != LB200_Q4_K && type != LB200_Q6_K && type != LB200_Q8_0) return 0;
   if ((uintptr_t)w & 15) return 0;
