@@ -285,12 +285,30 @@ typedef struct lb200_decode_attn_args {
   int32_t B, NH, KH, Cap, D;
   int32_t window;      /* 0, or the sliding window: keys [n - window, n)                         */
   float scale;         /* scores = scale * q.k                                                   */
+  float rope_base;     /* 0, or the rotary base (ops.RoPE, ops/rope.go:30-77): q and k_new are      */
+                       /* rotated at position pos inside the launch (rotate-half pairing), the    */
+                       /* key is cached rotated; without k_new only q is rotated                  */
 } lb200_decode_attn_args;
 
 /* out = softmax(scale * q K^T) V over the valid keys, one launch, no scratch.  Limits as the reference's
  * kernel (D a multiple of 32 up to 512, at most 16 query heads per KV head; else LB200_E_SHAPE and the
  * caller composes the op as it does today, ops/decode_attn.go:116-170). */
 LB200_API int light_b200_decode_attn(const lb200_decode_attn_args *args, int device, void *stream);
+
+/* Registry key {rmsnorm, CUDA, F32|BF16} (reference ops.RMSNorm, ops/norm.go:69-111; kernels
+ * rmsnorm_f32 / rmsnorm_bf16, kernels/cuda/src/elementwise.cu:275-312): out = s * rsqrt(mean(s^2) + eps) *
+ * weight along the last axis, x (rows, cols), weight (cols).  With residual == NULL, s = x.  With a
+ * residual, s = x + residual is also written to sum_out (the ops.Add that precedes the norm in every
+ * decoder layer, models/llama.go, folded into the same launch); sum_out may alias x or residual. */
+LB200_API int light_b200_rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype,
+                                 int64_t rows, int cols, float eps, int device, void *stream);
+
+/* Registry key {rope, CUDA, F32|BF16} (reference ops.RoPE, ops/rope.go:30-77; rope_f32,
+ * kernels/cuda/src/elementwise.cu:748-774): x (rows, head_dim) with rows = batch * seq_len, positions
+ * (seq_len) I64 on the device; dim i pairs with dim i + head_dim / 2 at angle pos * base^(-2 i / head_dim),
+ * computed in f64 like the reference's CPU kernel (kernels/cpu/misc_registry.go:27-62). */
+LB200_API int light_b200_rope(const void *x, const int64_t *positions, void *out, int dtype, int64_t rows, int seq_len,
+                              int head_dim, double base, int device, void *stream);
 
 /* p[i] += 1 for i < n (the device-side position after a step). */
 LB200_API int light_b200_inc_i64(int64_t *p, int n, int device, void *stream);

@@ -46,6 +46,7 @@ class DecodeAttnArgs(C.Structure):
         ("q", C.c_void_p), ("kbuf", C.c_void_p), ("vbuf", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
         ("pos", C.c_void_p), ("out", C.c_void_p), ("dtype", C.c_int32), ("B", C.c_int32), ("NH", C.c_int32),
         ("KH", C.c_int32), ("Cap", C.c_int32), ("D", C.c_int32), ("window", C.c_int32), ("scale", C.c_float),
+        ("rope_base", C.c_float),
     ]
 
 
@@ -87,6 +88,9 @@ SYMBOLS = {
                                        C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_decode_attn": (C.c_int, [C.POINTER(DecodeAttnArgs), C.c_int, C.c_void_p]),
     "light_b200_inc_i64": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_rmsnorm": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_float,
+                                     C.c_int, C.c_void_p]),
+    "light_b200_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_double, C.c_int, C.c_void_p]),
     "light_b200_decode_attn_status": (C.c_int, [C.c_int]),
 }
 

@@ -347,6 +347,18 @@ int light_b200_decode_attn(const lb200_decode_attn_args *a, int device, void *st
   return decode_attn(a, (cudaStream_t)stream);
 }
 
+int light_b200_rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype, int64_t rows,
+                       int cols, float eps, int device, void *stream) {
+  if (int rc = bind(device)) return rc;
+  return rmsnorm(x, residual, weight, sum_out, out, dtype, rows, cols, eps, (cudaStream_t)stream);
+}
+
+int light_b200_rope(const void *x, const int64_t *positions, void *out, int dtype, int64_t rows, int seq_len, int head_dim,
+                    double base, int device, void *stream) {
+  if (int rc = bind(device)) return rc;
+  return rope(x, positions, out, dtype, rows, seq_len, head_dim, base, (cudaStream_t)stream);
+}
+
 int light_b200_inc_i64(int64_t *p, int n, int device, void *stream) {
   if (int rc = bind(device)) return rc;
   return inc_i64(p, n, (cudaStream_t)stream);

@@ -95,5 +95,9 @@ int kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_
               cudaStream_t st);
 int inc_i64(int64_t *p, int n, cudaStream_t st);
 int decode_attn_status();
+int rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype, long long rows, int cols,
+            float eps, cudaStream_t st);
+int rope(const void *x, const int64_t *positions, void *out, int dtype, long long rows, int seq_len, int head_dim, double base,
+         cudaStream_t st);
 
 }  // namespace lb

@@ -29,7 +29,19 @@ struct AttnArgs {
   const long long *pos;
   int B, NH, KH, Cap, window;
   float scale;
+  double rope_k;  // 0: no rotation; else -2 log2(base) / D, so that base^(-2 i / D) = 2^(i rope_k)
 };
+
+// cos and sin of pos * base^(-2 i / D): the angle in f64 (an f32 angle of a few hundred radians is already
+// off by 1e-5), reduced to [-pi, pi] there, then the f32 functions.  Out of line: its registers are not the
+// attention loop's.
+__device__ __noinline__ float2 rope_cos_sin(long long pos, int i, double rope_k) {
+  const double theta = (double)pos * exp2((double)i * rope_k);
+  const double r = theta - 6.283185307179586476925 * rint(theta * 0.15915494309189533577);
+  float sn, c;
+  sincosf((float)r, &sn, &c);
+  return make_float2(c, sn);
+}
 
 // PER consecutive elements of a row, as floats; 2 to 64 bytes per lane, naturally aligned
 template <int PER>
@@ -105,9 +117,36 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
   const T *Vb = static_cast<const T *>(a.vbuf) + (size_t)bkh * a.Cap * D + lane * PER;
   const T *kn = a.k_new ? static_cast<const T *>(a.k_new) + (size_t)bkh * D + lane * PER : nullptr;
   const T *vn = a.k_new ? static_cast<const T *>(a.v_new) + (size_t)bkh * D + lane * PER : nullptr;
+  // rotary embedding of q and of the new key at position pos (rotate-half pairing: dim i with i + D / 2,
+  // which is lane ^ 16 here); cached keys were rotated when they were appended
+  const bool roped = a.rope_k != 0.0;
+  float rc[PER], rs[PER];
+  if (roped) {
+#pragma unroll
+    for (int p = 0; p < PER; p++) {
+      const float2 cs = rope_cos_sin(pos, (lane * PER + p) & (D / 2 - 1), a.rope_k);
+      rc[p] = cs.x, rs[p] = cs.y;
+    }
+  }
+  auto rotate = [&](float (&v)[PER]) {
+#pragma unroll
+    for (int p = 0; p < PER; p++) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[p], 16);
+      v[p] = lane < 16 ? v[p] * rc[p] - o * rs[p] : o * rs[p] + v[p] * rc[p];
+    }
+  };
   if (kn && rank == 0 && threadIdx.x < D) {  // the append: readers of position pos take the row from k_new
-    static_cast<T *>(a.kbuf)[((size_t)bkh * a.Cap + (size_t)pos) * D + threadIdx.x] = static_cast<const T *>(a.k_new)[(size_t)bkh * D + threadIdx.x];
-    static_cast<T *>(a.vbuf)[((size_t)bkh * a.Cap + (size_t)pos) * D + threadIdx.x] = static_cast<const T *>(a.v_new)[(size_t)bkh * D + threadIdx.x];
+    const T *ks = static_cast<const T *>(a.k_new) + (size_t)bkh * D;
+    const size_t dst = ((size_t)bkh * a.Cap + (size_t)pos) * D + threadIdx.x;
+    if (roped) {
+      const int i = threadIdx.x & (D / 2 - 1);
+      const float2 cs = rope_cos_sin(pos, i, a.rope_k);
+      const float x0 = ld_act(ks, i), x1 = ld_act(ks, i + D / 2);
+      st_act(static_cast<T *>(a.kbuf), (long long)dst, (int)threadIdx.x < D / 2 ? x0 * cs.x - x1 * cs.y : x0 * cs.y + x1 * cs.x);
+    } else {
+      static_cast<T *>(a.kbuf)[dst] = ks[threadIdx.x];
+    }
+    static_cast<T *>(a.vbuf)[dst] = static_cast<const T *>(a.v_new)[(size_t)bkh * D + threadIdx.x];
   }
 
   for (int h0 = 0; h0 < g; h0 += GH) {
@@ -120,6 +159,7 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
 #pragma unroll
       for (int p = 0; p < PER; p++) acc[h][p] = 0.f, qf[h][p] = 0.f;
       if (h < gh) load_row<PER>(static_cast<const T *>(a.q) + ((size_t)b * a.NH + (size_t)kh * g + h0 + h) * D + lane * PER, qf[h]);
+      if (roped) rotate(qf[h]);
     }
     float kf[U][PER], vf[U][PER];
     auto fetch = [&](int j, float (&kk)[U][PER], float (&vv)[U][PER]) {
@@ -129,6 +169,7 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
           const bool fresh = kn && j + u == (int)pos;
           load_row<PER>(fresh ? kn : Kb + (size_t)(j + u) * D, kk[u]);
           load_row<PER>(fresh ? vn : Vb + (size_t)(j + u) * D, vv[u]);
+          if (fresh && roped) rotate(kk[u]);
         } else {
 #pragma unroll
           for (int p = 0; p < PER; p++) kk[u][p] = 0.f, vv[u][p] = 0.f;
@@ -390,7 +431,9 @@ int decode_attn(const lb200_decode_attn_args *p, cudaStream_t st) {
   if ((long long)p->B * p->KH > 65535ll * 1024) return fail(LB200_E_TOO_LARGE, "light_b200: decode_attn: B x KH too large");
   const uintptr_t al = (uintptr_t)p->q | (uintptr_t)p->kbuf | (uintptr_t)p->vbuf | (uintptr_t)p->k_new | (uintptr_t)p->v_new;
   if (al & 15) return fail(LB200_E_ALIGN, "light_b200: decode_attn: q / k / v must be 16-byte aligned");
-  AttnArgs a{p->q, p->k_new, p->v_new, p->kbuf, p->vbuf, p->out, (const long long *)p->pos, p->B, p->NH, p->KH, p->Cap, p->window, p->scale};
+  if (p->rope_base < 0.f) return fail(LB200_E_SHAPE, "light_b200: decode_attn: rope_base %g", (double)p->rope_base);
+  const double rope_k = p->rope_base > 0.f ? -2.0 * log2((double)p->rope_base) / (double)p->D : 0.0;
+  AttnArgs a{p->q, p->k_new, p->v_new, p->kbuf, p->vbuf, p->out, (const long long *)p->pos, p->B, p->NH, p->KH, p->Cap, p->window, p->scale, rope_k};
   // enough CTAs to fill the GPU, at least 32 keys of the capacity each, a portable cluster
   int ks = 1;
   while (ks < 8 && p->B * p->KH * ks < 148 && p->Cap >= 64 * ks) ks *= 2;

@@ -440,10 +440,11 @@ def KVAppend(kbuf: torch.Tensor, vbuf: torch.Tensor, k: torch.Tensor, v: torch.T
 
 
 def DecodeAttention(q: torch.Tensor, kbuf: torch.Tensor, vbuf: torch.Tensor, pos: torch.Tensor, scale: float, window: int = 0,
-                    k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None, rope_base: float = 0.0) -> torch.Tensor:
     """ops.DecodeAttention (ops/decode_attn.go:64-170): q (B, NH, 1, HD) against the first pos + 1 keys of the
     buffers -> (B, NH, 1, HD).  With k_new / v_new (B, KH, 1, HD) the same launch appends them at pos first
-    (KVCache.decodeAttend, models/llama.go:1156-1160, does the two ops back to back)."""
+    (KVCache.decodeAttend, models/llama.go:1156-1160, does the two ops back to back); with rope_base the launch
+    also rotates q and k_new at that position (the two ops.RoPE calls before it, models/llama.go:1136-1146)."""
     _check_cache(kbuf, vbuf, "DecodeAttention")
     if q.dim() != 4 or q.shape[2] != 1:
         raise ValueError(f"ops.DecodeAttention: want q (B, NH, 1, HD), got {tuple(q.shape)}")
@@ -464,7 +465,7 @@ def DecodeAttention(q: torch.Tensor, kbuf: torch.Tensor, vbuf: torch.Tensor, pos
     kn = k_new.contiguous() if k_new is not None else None
     vn = v_new.contiguous() if v_new is not None else None
     a = _lib.DecodeAttnArgs(_ptr(qc), _ptr(kbuf), _ptr(vbuf), _ptr(kn), _ptr(vn), _ptr(pos), _ptr(out), _ACT[q.dtype], B, NH, KH, cap, D,
-                            int(window), float(scale))
+                            int(window), float(scale), float(rope_base))
     _lib.check(_lib.lib().light_b200_decode_attn(C.byref(a), dev, _stream(dev)))
     return out
 
@@ -475,6 +476,51 @@ def IncrementI64(t: torch.Tensor) -> None:
         raise ValueError(f"ops.IncrementI64: want a contiguous I64 tensor, got {t.dtype} {tuple(t.shape)}")
     dev = _dev(t, "IncrementI64")
     _lib.check(_lib.lib().light_b200_inc_i64(_ptr(t), t.numel(), dev, _stream(dev)))
+
+
+def RMSNorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None):
+    """ops.RMSNorm (ops/norm.go:69-111): y = x * rsqrt(mean(x^2, -1) + eps) * weight.  With `residual`, the sum
+    x + residual is normalised and returned as well: (y, sum), the ops.Add before the norm in the same launch."""
+    if x.device != weight.device:
+        raise ValueError("ops.RMSNorm: device mismatch")
+    if x.dtype != weight.dtype:
+        raise ValueError(f"ops.RMSNorm: dtype mismatch (x={x.dtype}, weight={weight.dtype}) -- cast at load time")
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.RMSNorm: dtype {x.dtype} unsupported (F32/BF16)")
+    if weight.dim() != 1 or weight.shape[0] != x.shape[-1]:
+        raise ValueError(f"ops.RMSNorm: weight shape {tuple(weight.shape)} incompatible with x last dim {x.shape[-1]}")
+    if residual is not None and (residual.shape != x.shape or residual.dtype != x.dtype):
+        raise ValueError(f"ops.RMSNorm: residual {tuple(residual.shape)} {residual.dtype} against x {tuple(x.shape)} {x.dtype}")
+    dev = _dev(x, "RMSNorm")
+    xc, wc = x.contiguous(), weight.contiguous()
+    rc = residual.contiguous() if residual is not None else None
+    out = torch.empty_like(xc)
+    total = torch.empty_like(xc) if residual is not None else None
+    cols = x.shape[-1]
+    _lib.check(_lib.lib().light_b200_rmsnorm(_ptr(xc), _ptr(rc), _ptr(wc), _ptr(total), _ptr(out), _ACT[x.dtype], xc.numel() // cols, cols,
+                                             float(eps), dev, _stream(dev)))
+    return out if residual is None else (out, total)
+
+
+def RoPE(x: torch.Tensor, positions: torch.Tensor, base: float) -> torch.Tensor:
+    """ops.RoPE (ops/rope.go:30-77): x (..., seqLen, headDim), positions (seqLen,) I64, rotate-half pairing."""
+    if x.dim() < 2:
+        raise ValueError(f"ops.RoPE: x rank must be >= 2 (got {x.dim()})")
+    if x.dtype not in (torch.float32, torch.bfloat16):
+        raise ValueError(f"ops.RoPE: dtype {x.dtype} unsupported (F32/BF16)")
+    if positions.dtype != torch.int64 or positions.dim() != 1:
+        raise ValueError("ops.RoPE: positions must be 1-D I64")
+    head_dim, seq_len = x.shape[-1], x.shape[-2]
+    if head_dim % 2:
+        raise ValueError(f"ops.RoPE: headDim must be even (got {head_dim})")
+    if positions.shape[0] != seq_len:
+        raise ValueError(f"ops.RoPE: positions length {positions.shape[0]} != seqLen {seq_len}")
+    dev = _dev(x, "RoPE")
+    xc = x.contiguous()
+    out = torch.empty_like(xc)
+    _lib.check(_lib.lib().light_b200_rope(_ptr(xc), _ptr(positions.contiguous()), _ptr(out), _ACT[x.dtype], xc.numel() // head_dim, seq_len,
+                                          head_dim, float(base), dev, _stream(dev)))
+    return out
 
 
 def decode_attn_status(device_index: int = 0) -> int:

@@ -250,5 +250,23 @@ def decode_attn(q, kbuf, vbuf, pos: int, scale: float, window: int = 0) -> np.nd
     return out
 
 
+def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    out = np.empty_like(x)
+    _chk(lib().lo_rmsnorm_f32(_p(x), _p(w), _p(out), C.c_int64(x.size // x.shape[-1]), x.shape[-1], C.c_double(eps)), "rmsnorm")
+    return out
+
+
+def rope(x: np.ndarray, positions: np.ndarray, base: float) -> np.ndarray:
+    """x (..., seq_len, head_dim) f32, positions (seq_len,) i64."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    positions = np.ascontiguousarray(positions, dtype=np.int64)
+    out = np.empty_like(x)
+    seq_len, hd = x.shape[-2], x.shape[-1]
+    _chk(lib().lo_rope_f32(_p(x), _p(positions), _p(out), C.c_int64(x.size // (seq_len * hd)), seq_len, hd, C.c_double(base)), "rope")
+    return out
+
+
 def has_avx2() -> bool:
     return bool(lib().lo_has_avx2())

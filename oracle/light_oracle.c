@@ -780,4 +780,38 @@ LO_API int lo_decode_attn(const float *q, const float *kbuf, const float *vbuf, 
   return 0;
 }
 
+/* kernels/cpu/norm.go:27-51 (rmsnormF32): one f32 sum of squares per row, in order; the reciprocal root
+ * in f64; y = x * inv * w. */
+LO_API int lo_rmsnorm_f32(const float *x, const float *w, float *out, int64_t rows, int cols, double eps) {
+  for (int64_t r = 0; r < rows; r++) {
+    const float *rx = x + (size_t)r * cols;
+    float ss = 0.f;
+    for (int i = 0; i < cols; i++) ss += rx[i] * rx[i];
+    float inv = (float)(1.0 / sqrt((double)(ss / (float)cols) + eps));
+    for (int i = 0; i < cols; i++) out[(size_t)r * cols + i] = rx[i] * inv * w[i];
+  }
+  return 0;
+}
+
+/* kernels/cpu/misc_registry.go:27-62 (ropeF32CPU): rotate-half pairing, dim i with dim i + head_dim / 2
+ * at angle pos * base^(-2 i / head_dim); angle, cosine and sine in f64, the rotation in f32. */
+LO_API int lo_rope_f32(const float *x, const int64_t *positions, float *out, int64_t batch, int seq_len, int head_dim,
+                       double base) {
+  if (head_dim % 2) return -1;
+  int half = head_dim / 2;
+  for (int64_t b = 0; b < batch; b++)
+    for (int s = 0; s < seq_len; s++) {
+      double pos = (double)positions[s];
+      size_t rb = ((size_t)b * seq_len + s) * head_dim;
+      for (int i = 0; i < half; i++) {
+        double theta = pos * pow(base, -(double)(2 * i) / (double)head_dim);
+        float c = (float)cos(theta), sn = (float)sin(theta);
+        float x0 = x[rb + i], x1 = x[rb + i + half];
+        out[rb + i] = x0 * c - x1 * sn;
+        out[rb + i + half] = x0 * sn + x1 * c;
+      }
+    }
+  return 0;
+}
+
 LO_API int lo_has_avx2(void) { return have_avx2(); }
