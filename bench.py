@@ -291,6 +291,60 @@ class Chain:
         return len(self.plan(only))
 
 
+
+class FullStep:
+    """One whole decode step of configs[1] at M = 1 on the chain's weights: per layer
+    add + RMSNorm -> q,k,v (one launch) -> RoPE + KV append + attention (one launch) -> o -> add + RMSNorm ->
+    SiLU(gate) * up (one launch) -> down; then the final norm and lm_head.  Every operator reads what the
+    one before it wrote (227 launches), KV length kv_len, f32 cache.  A side measurement: the headline stays
+    the quantized linears alone."""
+
+    def __init__(self, chain, kv_len=1024):
+        dev = chain.device
+        self.c, self.dev_index = chain, chain.dev_index
+        self.by = {e[0]: e for e in chain.lin}
+        self.layers = sum(1 for e in chain.lin if e[0].endswith(".q"))
+        g = torch.Generator(device=dev)
+        g.manual_seed(21)
+        z = lambda *s: torch.zeros(*s, device=dev)
+        self.h, self.xn, self.attn, self.o, self.act, self.down = torch.randn(1, HID, generator=g, device=dev), z(1, HID), z(1, 32, 1, 128), z(1, HID), z(1, FFN), z(1, HID)
+        self.q, self.k, self.v = z(1, HID), z(1, NKV), z(1, NKV)
+        self.logits = z(1, VOCAB)
+        self.norm_w = torch.ones(HID, device=dev)
+        self.pos = torch.tensor([kv_len - 1], dtype=torch.int64, device=dev)
+        self.kb = [torch.randn(1, NKV // 128, kv_len, 128, generator=g, device=dev) for _ in range(self.layers)]
+        self.vb = [torch.randn(1, NKV // 128, kv_len, 128, generator=g, device=dev) for _ in range(self.layers)]
+        self.attn_args = [_lib.DecodeAttnArgs(self.q.data_ptr(), self.kb[l].data_ptr(), self.vb[l].data_ptr(), self.k.data_ptr(), self.v.data_ptr(),
+                                              self.pos.data_ptr(), self.attn.data_ptr(), ops.F32, 1, 32, NKV // 128, kv_len, 128, 0,
+                                              1.0 / math.sqrt(128), 500000.0) for l in range(self.layers)]
+        self.qkv = []
+        for l in range(self.layers):
+            ws = [self.by[f"l{l}.{n}"][5] for n in ("q", "k", "v")]
+            self.qkv.append(((C.c_void_p * 3)(*[w.data_ptr() for w in ws]), (C.c_void_p * 3)(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()),
+                             (C.c_int32 * 3)(HID, NKV, NKV)))
+
+    def step(self):
+        L, st, d = _lib.lib(), C.c_void_p(torch.cuda.current_stream(self.c.device).cuda_stream), self.dev_index
+        P = lambda t: C.c_void_p(t.data_ptr())
+        n = 0
+        for l in range(self.layers):
+            # the first layer normalises the embedding row; later ones add the MLP output to the stream first
+            _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.down) if l else None, P(self.norm_w), P(self.h) if l else None, P(self.xn), ops.F32, 1, HID,
+                                            1e-5, d, st))
+            wp, op, nn = self.qkv[l]
+            _lib.check(L.light_b200_matmul_q_multi(ops.Q4_K, P(self.xn), wp, op, nn, 3, HID, d, st))
+            _lib.check(L.light_b200_decode_attn(C.byref(self.attn_args[l]), d, st))
+            _lib.check(L.light_b200_matmul_q(ops.Q4_K, P(self.attn), P(self.by[f"l{l}.o"][5]), P(self.o), 1, HID, HID, d, st))
+            _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.o), P(self.norm_w), P(self.h), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
+            _lib.check(L.light_b200_matmul_q_gated(ops.Q4_K, P(self.xn), P(self.by[f"l{l}.gate"][5]), P(self.by[f"l{l}.up"][5]), P(self.act), FFN, HID,
+                                                   1, d, st))
+            _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.act), P(self.by[f"l{l}.down"][5]), P(self.down), 1, HID, FFN, d, st))
+            n += 7
+        _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.down), P(self.norm_w), P(self.h), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
+        _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.xn), P(self.by[HEAD[0]][5]), P(self.logits), 1, VOCAB, HID, d, st))
+        return n + 2
+
+
 def capture(fn, device):
     """Warm up on a side stream, then capture fn() into a CUDA graph (as the reference's decode loop
     replays its step, models/decode_graph.go:58-205)."""
@@ -384,6 +438,14 @@ def extras(chain, device, args):
         out["decode_with_attention_kv1024"][str(M)] = {"ms_per_step": ms, "tok_s": M / (ms * 1e-3), "kv_bytes_per_step": c.attn_bytes,
                                                        "attention_us_per_layer": None if base is None else (ms - base) * 1e3 / len(c.attn)}
         del g, c
+    if chain.world == 1 and chain.M == 1:
+        fs = FullStep(chain)
+        g = capture(fs.step, device)
+        h0 = fs.h.clone()
+        ms = timed(lambda: (fs.h.copy_(h0), g.replay()), steps, 3, device, lambda: None) / steps
+        out["decode_m1_full_step_kv1024"] = {"launches": 7 * fs.layers + 2, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3),
+                                             "logits_finite": bool(torch.isfinite(fs.logits).all().item())}
+        del g, fs
     assert ops.decode_attn_status(device.index or 0) == 0
     # the Q4_K decode kernel on one matrix large enough that the cost of a launch does not matter (the vocabulary
     # projection's shape, 295 MB as Q4_K): its streaming rate, next to the launch-bound average of a step
