@@ -299,8 +299,9 @@ class FullStep:
     one before it wrote (227 launches), KV length kv_len, f32 cache.  A side measurement: the headline stays
     the quantized linears alone."""
 
-    def __init__(self, chain, kv_len=1024):
+    def __init__(self, chain, kv_len=1024, fold_norms=True):
         dev = chain.device
+        self.fold_norms = fold_norms
         self.c, self.dev_index = chain, chain.dev_index
         self.by = {e[0]: e for e in chain.lin}
         self.layers = sum(1 for e in chain.lin if e[0].endswith(".q"))
@@ -322,8 +323,42 @@ class FullStep:
             ws = [self.by[f"l{l}.{n}"][5] for n in ("q", "k", "v")]
             self.qkv.append(((C.c_void_p * 3)(*[w.data_ptr() for w in ws]), (C.c_void_p * 3)(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()),
                              (C.c_int32 * 3)(HID, NKV, NKV)))
+        # norms folded into the q,k,v and gate,up launches: the residual stream alternates between two buffers,
+        # because the launch that writes the new sum is still reading the old one
+        self.h2 = z(1, HID)
+        self.gu = [((C.c_void_p * 2)(self.by[f"l{l}.gate"][5].data_ptr(), self.by[f"l{l}.up"][5].data_ptr()),
+                    (C.c_void_p * 2)(self.act.data_ptr(), self.act.data_ptr()), (C.c_int32 * 2)(FFN, FFN)) for l in range(self.layers)]
+        self.folded, cur, other = [], self.h, self.h2
+        for l in range(self.layers):
+            if l == 0:
+                first = (cur, _lib.NormArgs(self.norm_w.data_ptr(), None, None, 1e-5))
+            else:
+                first = (cur, _lib.NormArgs(self.norm_w.data_ptr(), self.down.data_ptr(), other.data_ptr(), 1e-5))
+                cur, other = other, cur
+            second = (cur, _lib.NormArgs(self.norm_w.data_ptr(), self.o.data_ptr(), other.data_ptr(), 1e-5))
+            cur, other = other, cur
+            self.folded.append((first, second))
+        self.last_h = cur
+
+    def step_folded(self):
+        L, st, d = _lib.lib(), C.c_void_p(torch.cuda.current_stream(self.c.device).cuda_stream), self.dev_index
+        P = lambda t: C.c_void_p(t.data_ptr())
+        for l in range(self.layers):
+            (x1, n1), (x2, n2) = self.folded[l]
+            wp, op, nn = self.qkv[l]
+            _lib.check(L.light_b200_matmul_q_fused(ops.Q4_K, P(x1), C.byref(n1), wp, op, nn, 3, 0, HID, d, st))
+            _lib.check(L.light_b200_decode_attn(C.byref(self.attn_args[l]), d, st))
+            _lib.check(L.light_b200_matmul_q(ops.Q4_K, P(self.attn), P(self.by[f"l{l}.o"][5]), P(self.o), 1, HID, HID, d, st))
+            wp, op, nn = self.gu[l]
+            _lib.check(L.light_b200_matmul_q_fused(ops.Q4_K, P(x2), C.byref(n2), wp, op, nn, 2, 1, HID, d, st))
+            _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.act), P(self.by[f"l{l}.down"][5]), P(self.down), 1, HID, FFN, d, st))
+        _lib.check(L.light_b200_rmsnorm(P(self.last_h), P(self.down), P(self.norm_w), P(self.xn), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
+        _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.xn), P(self.by[HEAD[0]][5]), P(self.logits), 1, VOCAB, HID, d, st))
+        return 5 * self.layers + 2
 
     def step(self):
+        if self.fold_norms:
+            return self.step_folded()
         L, st, d = _lib.lib(), C.c_void_p(torch.cuda.current_stream(self.c.device).cuda_stream), self.dev_index
         P = lambda t: C.c_void_p(t.data_ptr())
         n = 0
@@ -439,13 +474,18 @@ def extras(chain, device, args):
                                                        "attention_us_per_layer": None if base is None else (ms - base) * 1e3 / len(c.attn)}
         del g, c
     if chain.world == 1 and chain.M == 1:
-        fs = FullStep(chain)
-        g = capture(fs.step, device)
-        h0 = fs.h.clone()
-        ms = timed(lambda: (fs.h.copy_(h0), g.replay()), steps, 3, device, lambda: None) / steps
-        out["decode_m1_full_step_kv1024"] = {"launches": 7 * fs.layers + 2, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3),
-                                             "logits_finite": bool(torch.isfinite(fs.logits).all().item())}
-        del g, fs
+        logits = []
+        for key, fold in (("decode_m1_full_step_kv1024", True), ("decode_m1_full_step_kv1024_norms_as_launches", False)):
+            fs = FullStep(chain, fold_norms=fold)
+            h0 = fs.h.clone()  # before the warm-up steps: they advance the residual stream in place
+            g = capture(fs.step, device)
+            ms = timed(lambda: (fs.h.copy_(h0), g.replay()), steps, 3, device, lambda: None) / steps
+            out[key] = {"launches": (5 if fold else 7) * fs.layers + 2, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3),
+                        "logits_finite": bool(torch.isfinite(fs.logits).all().item())}
+            logits.append(fs.logits.clone())
+            del g, fs
+        d = (logits[0] - logits[1]).norm() / logits[1].norm()
+        out["decode_m1_full_step_kv1024"]["rel_l2_of_logits_against_norms_as_launches"] = float(d)
     assert ops.decode_attn_status(device.index or 0) == 0
     # the Q4_K decode kernel on one matrix large enough that the cost of a launch does not matter (the vocabulary
     # projection's shape, 295 MB as Q4_K): its streaming rate, next to the launch-bound average of a step

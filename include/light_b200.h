@@ -295,6 +295,26 @@ typedef struct lb200_decode_attn_args {
  * caller composes the op as it does today, ops/decode_attn.go:116-170). */
 LB200_API int light_b200_decode_attn(const lb200_decode_attn_args *args, int device, void *stream);
 
+/* RMSNorm (and the residual add before it) folded into the Q4_K decode launch that consumes it:
+ * light_b200_rmsnorm + light_b200_matmul_q_multi (act 0: count matrices, out[i] = w[i] . y) or
+ * + light_b200_matmul_q_gated (act 1 SiLU / 2 GELU: count 2, out[0] = act(w[0] . y) * (w[1] . y)) as ONE
+ * launch, y = s * rsqrt(mean(s^2) + eps) * weight, s = x + residual (residual NULL: s = x).  A decoder
+ * layer does exactly this twice (models/llama.go:1085-1110,1290-1326: Add, RMSNorm, then the q,k,v or
+ * gate,up projections); a dependent launch costs about 5 us whatever its size, so the two small
+ * operators are worth more as a prologue than as launches.  One f32 activation row, Q4_K weights,
+ * K a multiple of 256 that fits the kernel's activation staging; else LB200_E_SHAPE / LB200_E_DTYPE and
+ * the caller keeps its unfused sequence.  sum_out (required with a residual) receives s; it must not
+ * alias x or residual, because other thread blocks of the launch still read them. */
+typedef struct lb200_norm {
+  const float *weight;   /* (K)                                   */
+  const float *residual; /* (K) or NULL                           */
+  float *sum_out;        /* (K); NULL when residual is NULL       */
+  float eps;
+} lb200_norm;
+LB200_API int light_b200_matmul_q_fused(int ggml_type, const float *x, const lb200_norm *norm, const void *const *w,
+                                        float *const *out, const int32_t *n, int count, int act, int K, int device,
+                                        void *stream);
+
 /* Registry key {rmsnorm, CUDA, F32|BF16} (reference ops.RMSNorm, ops/norm.go:69-111; kernels
  * rmsnorm_f32 / rmsnorm_bf16, kernels/cuda/src/elementwise.cu:275-312): out = s * rsqrt(mean(s^2) + eps) *
  * weight along the last axis, x (rows, cols), weight (cols).  With residual == NULL, s = x.  With a

@@ -41,6 +41,11 @@ class MoeArgs(C.Structure):
     ]
 
 
+class NormArgs(C.Structure):
+    """lb200_norm"""
+    _fields_ = [("weight", C.c_void_p), ("residual", C.c_void_p), ("sum_out", C.c_void_p), ("eps", C.c_float)]
+
+
 class DecodeAttnArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("kbuf", C.c_void_p), ("vbuf", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
@@ -71,6 +76,8 @@ SYMBOLS = {
                                             C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_matmul_q_gated": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                             C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_matmul_q_fused": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(NormArgs), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                            C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_dequant": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_void_p]),
     "light_b200_int4_dequant": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                           C.c_int, C.c_int64, C.c_int, C.c_void_p]),

@@ -221,6 +221,37 @@ int light_b200_matmul_q_gated(int t, const float *x, const void *wg, const void 
   return took;
 }
 
+int light_b200_matmul_q_fused(int t, const float *x, const lb200_norm *norm, const void *const *w, float *const *out,
+                              const int32_t *n, int count, int act, int K, int device, void *stream) {
+  if (t != LB200_Q4_K) return fail(LB200_E_DTYPE, "light_b200: matmul_q_fused: ggml type %d has no fused kernel", t);
+  if (act < 0 || act > 2 || count < 1 || count > 4 || (act && count != 2))
+    return fail(LB200_E_SHAPE, "light_b200: matmul_q_fused: act %d with %d matrices (act 0: 1..4, act 1 / 2: 2)", act, count);
+  if (K <= 0 || K % 256) return fail(LB200_E_SHAPE, "light_b200: matmul_q_fused: K=%d, want a multiple of 256", K);
+  REQUIRE_PTR(x, "matmul_q_fused");
+  REQUIRE_PTR(norm, "matmul_q_fused");
+  REQUIRE_PTR(w, "matmul_q_fused");
+  REQUIRE_PTR(out, "matmul_q_fused");
+  REQUIRE_PTR(n, "matmul_q_fused");
+  if (!norm->weight || (norm->residual && !norm->sum_out))
+    return fail(LB200_E_NULL, "light_b200: matmul_q_fused: norm weight missing, or a residual without sum_out");
+  if (norm->sum_out && (norm->sum_out == x || norm->sum_out == norm->residual))
+    return fail(LB200_E_SHAPE, "light_b200: matmul_q_fused: sum_out must not alias x or residual");
+  if (!aligned(x, 16) || !aligned(norm->weight, 16) || !aligned(norm->residual, 16) || !aligned(norm->sum_out, 16))
+    return fail(LB200_E_ALIGN, "light_b200: matmul_q_fused: x, norm weight, residual and sum_out must be 16-byte aligned");
+  for (int i = 0; i < count; i++) {
+    if (n[i] < 16 || (act && n[i] != n[0])) return fail(LB200_E_SHAPE, "light_b200: matmul_q_fused: matrix %d has %d rows", i, n[i]);
+    if (!w[i] || !out[act ? 0 : i]) return fail(LB200_E_NULL, "light_b200: matmul_q_fused: null pointer for matrix %d", i);
+    if (!aligned(w[i], 16) || !aligned(out[act ? 0 : i], 4))
+      return fail(LB200_E_ALIGN, "light_b200: matmul_q_fused: w must be 16-byte, out 4-byte aligned (matrix %d)", i);
+  }
+  if (int rc = bind(device)) return rc;
+  float *o2[2] = {out[0], out[0]};
+  const int took = gguf_gemv_multi(t, x, w, act ? o2 : out, n, count, act, K, (cudaStream_t)stream, norm);
+  if (took == 1) return 0;
+  if (took == 0) return fail(LB200_E_SHAPE, "light_b200: matmul_q_fused: K=%d is too long for the fused kernel", K);
+  return took;
+}
+
 int light_b200_dequant(int t, const void *src, float *dst, int64_t n, int device, void *stream) {
   const int be = block_elems(t);
   if (!be) return fail(LB200_E_DTYPE, "light_b200: dequant: ggml type %d has no kernel", t);

@@ -219,10 +219,22 @@ constexpr int Q4K_SLAB = Slab<32>::BYTES + 16;  // a block's activations + its p
 //
 // All activations are converted once per CTA (warp w converts the blocks it will use), so the
 // tile loop holds no activation traffic at all.
-template <int S, int MINB, bool TP>
+// RMSNorm (and the residual add before it) folded into the launch: the activations are s = x + residual
+// (residual may be null), every CTA stages s * weight and accumulates sum(s^2) on the way, and the outputs
+// are multiplied by rsqrt(mean(s^2) + eps) at the end -- W (s w) r = r W (s w).  CTA 0 writes s to sum_out
+// (the new residual stream), which therefore must not alias x or residual: the other CTAs still read them.
+struct NormArgs {
+  const float *weight, *residual;
+  float *sum_out;
+  float eps;
+};
+
+template <int S, int MINB, bool TP, bool NORM = false>
 __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const float *__restrict__ x,
                                                                        const __grid_constant__ MultiArgs a,
-                                                                       const __grid_constant__ TpArgs tp, int tiles, int K) {
+                                                                       const __grid_constant__ TpArgs tp,
+                                                                       const __grid_constant__ NormArgs nrm, int tiles, int K) {
+  __shared__ float nrm_part[WARPS];
   using SL = Slab<32>;
   extern __shared__ __align__(16) unsigned char dyn[];  // [ring: WARPS x S tiles][slabs: K/256]
   __shared__ __align__(16) unsigned char zero[SL::ZERO_BYTES];
@@ -291,6 +303,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
     tag = *reinterpret_cast<const volatile unsigned int *>(tp.step);
     if (tp.x_slots) asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(tp_t0));
   }
+  float nrm_ss = 0.f;
   for (int b = warp; b < nb; b += WARPS) {
     float4 xv[2];
     if (TP && tp.x_slots) {  // the peers' parts of x arrive as tagged slots
@@ -301,11 +314,36 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
       xv[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
       xv[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
     }
+    if constexpr (NORM) {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const int e4 = b * 64 + i * 32 + lane;  // float4 index into the row
+        if (nrm.residual) {
+          const float4 r = __ldg(reinterpret_cast<const float4 *>(nrm.residual) + e4);
+          xv[i].x += r.x, xv[i].y += r.y, xv[i].z += r.z, xv[i].w += r.w;
+          if (blockIdx.x == 0) reinterpret_cast<float4 *>(nrm.sum_out)[e4] = xv[i];
+        }
+        nrm_ss = fmaf(xv[i].x, xv[i].x, fmaf(xv[i].y, xv[i].y, fmaf(xv[i].z, xv[i].z, fmaf(xv[i].w, xv[i].w, nrm_ss))));
+        const float4 wn = __ldg(reinterpret_cast<const float4 *>(nrm.weight) + e4);
+        xv[i].x *= wn.x, xv[i].y *= wn.y, xv[i].z *= wn.z, xv[i].w *= wn.w;
+      }
+    }
     const uint32_t slab = slabs + b * Q4K_SLAB;
     const float up = stage_block<32>(xv, slab, lane);
     if (lane == 0) asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(slab + SL::BYTES), "f"(up));
   }
+  if constexpr (NORM) {
+    nrm_ss = warp_sum(nrm_ss);
+    if (lane == 0) nrm_part[warp] = nrm_ss;
+  }
   __syncthreads();
+  float nrm_inv = 1.f;
+  if constexpr (NORM) {
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < WARPS; i++) tot += nrm_part[i];
+    nrm_inv = (float)(1.0 / sqrt((double)(tot / (float)K) + (double)nrm.eps));
+  }
   int slot = 0, parity = 0;
   for (int gt = t0; gt < t1; gt += GROUP, parity ^= 1) {
     const int gs = min(GROUP, t1 - gt);
@@ -380,7 +418,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
         const int pr = i >> 4, row = i & 15;
         int j, r0;
         resolve_tile(a, gt + 2 * pr, j, r0);
-        const float v = gate_act(row_sum(2 * pr, row), a.act) * row_sum(2 * pr + 1, row);
+        const float v = gate_act(row_sum(2 * pr, row) * nrm_inv, a.act) * (row_sum(2 * pr + 1, row) * nrm_inv);
         a.out[0][r0 + row] = v;
         if (TP && tp.peer[0][0]) st_slots(tp.peer[0], tp.world, (size_t)(tag & 1u) * a.n[0] * tp.world + (size_t)tp.rank * a.n[0] + r0 + row, v, tag);
       }
@@ -389,7 +427,7 @@ __global__ void __launch_bounds__(WARPS * 32, MINB) q4k_gemv_mma_kernel(const fl
         const int rt = i >> 4, row = i & 15;
         int j, r0;
         resolve_tile(a, gt + rt, j, r0);
-        const float v = row_sum(rt, row);
+        const float v = row_sum(rt, row) * nrm_inv;
         a.out[j][r0 + row] = v;
         if (TP && tp.peer[j][0]) st_slots(tp.peer[j], tp.world, (size_t)(tag & 1u) * a.n[j] * tp.world + (size_t)tp.rank * a.n[j] + r0 + row, v, tag);
       }
@@ -1451,6 +1489,8 @@ int gguf_gemv_fast_init(int device) {
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
+    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+  if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q6k_gemv_mma_kernel<Q6K_STAGES, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                WARPS * Q6K_STAGES * Q6K_TILE_BYTES);
   if (err == cudaSuccess)
@@ -1463,15 +1503,17 @@ int gguf_gemv_fast_init(int device) {
 
 // One launch over up to four Q4_K matrices that share x (M = 1).  Returns 1 if launched, 0 if this
 // path does not apply, < 0 or a CUDA code on error.
-static int q4k_launch(const float *x, const MultiArgs &a, const TpArgs &tp, int tiles, int K, cudaStream_t st) {
-  const size_t dyn = (size_t)WARPS * (tp.step ? 4 : g_q4k_stages) * Q4K_TILE_BYTES + (size_t)(K >> 8) * Q4K_SLAB;
+static const NormArgs NO_NORM = {};
+static int q4k_launch(const float *x, const MultiArgs &a, const TpArgs &tp, int tiles, int K, cudaStream_t st, const NormArgs &nrm = NO_NORM) {
+  const size_t dyn = (size_t)WARPS * (tp.step || nrm.weight ? 4 : g_q4k_stages) * Q4K_TILE_BYTES + (size_t)(K >> 8) * Q4K_SLAB;
   if (dyn > MAX_DYN_SMEM) return 0;  // very long rows: the activations do not fit beside the rings
   const int lt = a.act ? tiles / 2 : tiles;
-  const int per_sm = (g_q4k_stages == 2 && !tp.step) ? 3 : g_waves;  // the 2-deep ring leaves room for three CTAs per SM
+  const int per_sm = (g_q4k_stages == 2 && !tp.step && !nrm.weight) ? 3 : g_waves;  // the 2-deep ring leaves room for three CTAs per SM
   const unsigned grid = (unsigned)(lt < g_sms * per_sm ? lt : g_sms * per_sm);
-  int rc = tp.step            ? launch_pdl(q4k_gemv_mma_kernel<4, 2, true>, grid, dyn, st, x, a, tp, tiles, K)
-           : g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 3, false>, grid, dyn, st, x, a, tp, tiles, K)
-                               : launch_pdl(q4k_gemv_mma_kernel<4, 2, false>, grid, dyn, st, x, a, tp, tiles, K);
+  int rc = nrm.weight         ? launch_pdl(q4k_gemv_mma_kernel<4, 2, false, true>, grid, dyn, st, x, a, tp, nrm, tiles, K)
+           : tp.step           ? launch_pdl(q4k_gemv_mma_kernel<4, 2, true>, grid, dyn, st, x, a, tp, nrm, tiles, K)
+           : g_q4k_stages == 2 ? launch_pdl(q4k_gemv_mma_kernel<2, 3, false>, grid, dyn, st, x, a, tp, nrm, tiles, K)
+                               : launch_pdl(q4k_gemv_mma_kernel<4, 2, false>, grid, dyn, st, x, a, tp, nrm, tiles, K);
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
   return rc ? rc : 1;
@@ -1598,8 +1640,13 @@ int gguf_decode_tile(int type, const float *x, const void *w, float *out, int M,
 // pair act(w[0] x) * (w[1] x) -> out[0] (act 1 = SiLU, 2 = GELU).  Returns 1 if launched, 0 if no
 // single-launch kernel applies (the caller then issues one matmul per matrix), else an error.
 int gguf_gemv_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int act,
-                    int K, cudaStream_t st) {
+                    int K, cudaStream_t st, const lb200_norm *norm) {
   if (type != LB200_Q4_K || K % 256 || count < 1 || count > 4) return 0;
+  NormArgs nrm = {};
+  if (norm) {
+    if (((uintptr_t)norm->weight | (uintptr_t)norm->residual | (uintptr_t)norm->sum_out) & 15) return 0;
+    nrm.weight = norm->weight, nrm.residual = norm->residual, nrm.sum_out = norm->sum_out, nrm.eps = norm->eps;
+  }
   if (act && (count != 2 || n[0] != n[1])) return 0;
   MultiArgs a = {};
   int tiles = 0;
@@ -1609,7 +1656,7 @@ int gguf_gemv_multi(int type, const float *x, const void *const *w, float *const
     a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
   }
   a.count = count, a.act = act;
-  return q4k_launch(x, a, NO_TP, tiles, K, st);
+  return q4k_launch(x, a, NO_TP, tiles, K, st, nrm);
 }
 
 // Row-split matmul with the exchange inside the launch (see TpArgs): `count` matrices of one type that

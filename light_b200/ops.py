@@ -197,6 +197,36 @@ def MatMulQGated(x: torch.Tensor, wg: QTensor, wu: QTensor, gelu: bool = False, 
     return out
 
 
+def NormMatMulQ(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, ws: Sequence[QTensor], residual: Optional[torch.Tensor] = None,
+                gate: Optional[str] = None):
+    """RMSNorm(x [+ residual]) followed by LinearMulti (gate None) or GatedLinear (gate "silu" / "gelu") over Q4_K
+    weights, as one launch (light_b200_matmul_q_fused).  One activation row.  Returns the list of outputs (one
+    tensor for a gated pair), and with a residual also the sum x + residual."""
+    K = _one_row(x, "NormMatMulQ")
+    act = {None: 0, "silu": 1, "gelu": 2}[gate]
+    if act and len(ws) != 2:
+        raise ValueError("ops.NormMatMulQ: a gated launch takes exactly the gate and the up matrix")
+    if norm_weight.shape != (K,) or norm_weight.dtype != torch.float32 or (residual is not None and residual.numel() != K):
+        raise ValueError(f"ops.NormMatMulQ: norm weight {tuple(norm_weight.shape)} / residual against K = {K}")
+    for w in ws:
+        if len(w.shape) != 2 or w.shape[1] != K or w.ggml_type != ws[0].ggml_type:
+            raise ValueError(f"ops.NormMatMulQ: weight {w.shape} against K = {K}")
+    dev = _dev(x, "NormMatMulQ")
+    xc = x.contiguous()
+    total = torch.empty_like(xc) if residual is not None else None
+    rc = residual.contiguous() if residual is not None else None
+    nw = norm_weight.contiguous()
+    outs = [torch.empty(tuple(x.shape[:-1]) + (w.shape[0],), dtype=torch.float32, device=x.device) for w in (ws[:1] if act else ws)]
+    n = len(ws)
+    na = _lib.NormArgs(_ptr(nw), _ptr(rc), _ptr(total), float(eps))
+    wp = (C.c_void_p * n)(*[w.data.data_ptr() for w in ws])
+    op = (C.c_void_p * n)(*[outs[0 if act else i].data_ptr() for i in range(n)])
+    nn = (C.c_int32 * n)(*[w.shape[0] for w in ws])
+    _lib.check(_lib.lib().light_b200_matmul_q_fused(ws[0].ggml_type, _ptr(xc), C.byref(na), wp, op, nn, n, act, K, dev, _stream(dev)))
+    res = outs[0] if act else outs
+    return res if residual is None else (res, total)
+
+
 def Dequantize(w: QTensor) -> torch.Tensor:
     """quant.Dequantize on a CUDA tensor (quant/cuda_hook.go:28-46): blocks -> f32, same shape."""
     dev = _dev(w.data, "Dequantize")

@@ -90,3 +90,32 @@ def test_multi_and_gated_errors(cuda):
     rc = L.light_b200_matmul_q_gated(ops.Q4_K, C.c_void_p(x.data_ptr()), C.c_void_p(w.data.data_ptr()),
                                      C.c_void_p(w.data.data_ptr()), C.c_void_p(out.data_ptr()), 32, K, 3, 0, None)
     assert rc != 0
+
+
+@pytest.mark.parametrize("K", [4096, 2048, 256])
+def test_norm_folded_into_the_launch(cuda, oracle, K):
+    """RMSNorm(x [+ residual]) then LinearMulti / GatedLinear as one launch (light_b200_matmul_q_fused) against
+    the oracle's RMSNorm followed by the f64 products; the residual sum comes back bit for bit."""
+    g = torch.Generator().manual_seed(500 + K)
+    ns = (256, 64, 80)
+    raws = [synth.gaussian_weight(510 + i, ops.Q4_K, n, K).numpy() for i, n in enumerate(ns)]
+    deqs = [oracle.dequant(ops.Q4_K, r.reshape(-1), n * K).reshape(n, K).astype(np.float64) for r, n in zip(raws, ns)]
+    ws = [ops.QTensor(torch.from_numpy(r.reshape(-1)).to(cuda), ops.Q4_K, (n, K)) for r, n in zip(raws, ns)]
+    x, r, nw = torch.randn(1, K, generator=g) * 3, torch.randn(1, K, generator=g), torch.randn(K, generator=g)
+    for res in (None, r):
+        s = x if res is None else x + res
+        y = oracle.rmsnorm(s.numpy(), nw.numpy(), 1e-5).astype(np.float64)
+        got = ops.NormMatMulQ(x.to(cuda), nw.to(cuda), 1e-5, ws, residual=None if res is None else res.to(cuda))
+        if res is not None:
+            got, total = got
+            assert torch.equal(total.cpu(), s)
+        for o, d in zip(got, deqs):
+            assert rel_l2(o.cpu().numpy(), y @ d.T) <= 1e-4
+    # gated pair: two matrices of equal height
+    pair = [ws[1], ops.QTensor(torch.from_numpy(synth.gaussian_weight(520, ops.Q4_K, 64, K).numpy().reshape(-1)).to(cuda), ops.Q4_K, (64, K))]
+    du = oracle.dequant(ops.Q4_K, synth.gaussian_weight(520, ops.Q4_K, 64, K).numpy().reshape(-1), 64 * K).reshape(64, K).astype(np.float64)
+    y = oracle.rmsnorm((x + r).numpy(), nw.numpy(), 1e-5).astype(np.float64)
+    got, total = ops.NormMatMulQ(x.to(cuda), nw.to(cuda), 1e-5, pair, residual=r.to(cuda), gate="silu")
+    gl, up = y @ deqs[1].T, y @ du.T
+    assert rel_l2(got.cpu().numpy(), gl / (1 + np.exp(-gl)) * up) <= 1e-4
+    assert torch.equal(total.cpu(), x + r)
