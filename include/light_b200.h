@@ -295,6 +295,22 @@ typedef struct lb200_decode_attn_args {
  * caller composes the op as it does today, ops/decode_attn.go:116-170). */
 LB200_API int light_b200_decode_attn(const lb200_decode_attn_args *args, int device, void *stream);
 
+/* Quantized embedding lookup (reference nn.Embedding over a quantized table: ops.IndexSelect of the byte
+ * rows + quant.Dequantize of the gathered rows, nn/embedding.go; nn/embedding_test.go:127): out row i =
+ * dequantized row ids[i] of the (V, K) table, bit-identical to light_b200_dequant of that row.  ids are
+ * device I64; an id outside [0, V) yields a row of zeros. */
+LB200_API int light_b200_embedding_q(int ggml_type, const void *table, const int64_t *ids, float *out, int64_t n_ids, int64_t V,
+                                     int K, int device, void *stream);
+
+/* Checkpoint tensors -> the canonical 4-bit layout, on the device (reference quant.FromGPTQ / quant.FromAWQ,
+ * quant/int4.go:103-261, host loops at load time).  layout 0: AutoGPTQ "gptq" -- qweight i32 (K/8, N) packed
+ * along K, qzeros i32 (K/G, N/8) packed along N holding zero - 1; 1: "gptq_v2" (qzeros hold the zero);
+ * 2: AutoAWQ GEMM -- qweight (K, N/8) and qzeros packed along N in the order (0,2,4,6,1,3,5,7).  scales f32
+ * (K/G, N) (cast by the caller).  Out: codes u32 (N, K/8), scales / zeros f32 (N, K/G).  Ordered groups only:
+ * an act-order GPTQ checkpoint (g_idx) keeps the host path, which also builds the column permutation. */
+LB200_API int light_b200_int4_repack(const void *qweight, const void *qzeros, const float *scales, void *codes, float *scales_out,
+                                     float *zeros_out, int N, int K, int group, int layout, int device, void *stream);
+
 /* RMSNorm (and the residual add before it) folded into the Q4_K decode launch that consumes it:
  * light_b200_rmsnorm + light_b200_matmul_q_multi (act 0: count matrices, out[i] = w[i] . y) or
  * + light_b200_matmul_q_gated (act 1 SiLU / 2 GELU: count 2, out[0] = act(w[0] . y) * (w[1] . y)) as ONE

@@ -378,6 +378,34 @@ int light_b200_decode_attn(const lb200_decode_attn_args *a, int device, void *st
   return decode_attn(a, (cudaStream_t)stream);
 }
 
+int light_b200_embedding_q(int t, const void *table, const int64_t *ids, float *out, int64_t n_ids, int64_t V, int K, int device,
+                           void *stream) {
+  const int be = block_elems(t);
+  if (!be) return fail(LB200_E_DTYPE, "light_b200: embedding_q: ggml type %d has no kernel", t);
+  if (n_ids < 0 || n_ids > 0x7fffffffLL || V <= 0 || K <= 0 || K % be || K % 8)
+    return fail(LB200_E_SHAPE, "light_b200: embedding_q: %lld ids, table (%lld, %d)", (long long)n_ids, (long long)V, K);
+  if (n_ids == 0) return 0;
+  REQUIRE_PTR(table, "embedding_q");
+  REQUIRE_PTR(ids, "embedding_q");
+  REQUIRE_PTR(out, "embedding_q");
+  if (!aligned(out, 16) || !aligned(table, 2)) return fail(LB200_E_ALIGN, "light_b200: embedding_q: out must be 16-byte, table 2-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return gguf_embedding(t, table, ids, out, n_ids, V, K, (cudaStream_t)stream);
+}
+
+int light_b200_int4_repack(const void *qweight, const void *qzeros, const float *scales, void *codes, float *scales_out, float *zeros_out,
+                           int N, int K, int group, int layout, int device, void *stream) {
+  REQUIRE_PTR(qweight, "int4_repack");
+  REQUIRE_PTR(qzeros, "int4_repack");
+  REQUIRE_PTR(scales, "int4_repack");
+  REQUIRE_PTR(codes, "int4_repack");
+  REQUIRE_PTR(scales_out, "int4_repack");
+  REQUIRE_PTR(zeros_out, "int4_repack");
+  if (int rc = bind(device)) return rc;
+  return int4_repack((const uint32_t *)qweight, (const uint32_t *)qzeros, scales, (uint32_t *)codes, scales_out, zeros_out, N, K,
+                     group <= 0 ? K : group, layout, (cudaStream_t)stream);
+}
+
 int light_b200_rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype, int64_t rows,
                        int cols, float eps, int device, void *stream) {
   if (int rc = bind(device)) return rc;

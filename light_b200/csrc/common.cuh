@@ -95,6 +95,9 @@ int kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_
               cudaStream_t st);
 int inc_i64(int64_t *p, int n, cudaStream_t st);
 int decode_attn_status();
+int gguf_embedding(int type, const void *table, const int64_t *ids, float *out, long long n_ids, long long V, int K, cudaStream_t st);
+int int4_repack(const uint32_t *qweight, const uint32_t *qzeros, const float *scales, uint32_t *codes, float *s_out, float *z_out,
+                int N, int K, int G, int kind, cudaStream_t st);
 int rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype, long long rows, int cols,
             float eps, cudaStream_t st);
 int rope(const void *x, const int64_t *positions, void *out, int dtype, long long rows, int seq_len, int head_dim, double base,

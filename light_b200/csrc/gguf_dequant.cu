@@ -42,4 +42,42 @@ int gguf_dequant(int type, const void *src, float *dst, long long n, cudaStream_
   return fail(LB200_E_DTYPE, "dequant: ggml type %d has no kernel", type);
 }
 
+// Quantized embedding lookup: row ids[i] of a block-quantized table (V, K) -> f32 row i of out, the reference's
+// nn.Embedding over a quantized table (IndexSelect of the byte rows, then Dequantize of the gathered rows only,
+// nn/embedding.go; tested by nn/embedding_test.go:127).  An id outside [0, V) yields a row of zeros.
+template <int T>
+__global__ void __launch_bounds__(256) gguf_embedding_kernel(const uint8_t *__restrict__ table, const long long *__restrict__ ids,
+                                                             float *__restrict__ out, long long V, int K) {
+  constexpr int BE = block_elems(T), BB = block_bytes(T);
+  const long long id = ids[blockIdx.x];
+  const uint8_t *row = table + (size_t)id * (size_t)(K / BE) * BB;
+  float *dst = out + (size_t)blockIdx.x * K;
+  for (int e = threadIdx.x * 8; e < K; e += 256 * 8) {
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (id >= 0 && id < V) decode8<T>(row + (size_t)(e / BE) * BB, e % BE, v);
+    float4 *o = reinterpret_cast<float4 *>(dst + e);
+    o[0] = make_float4(v[0], v[1], v[2], v[3]);
+    o[1] = make_float4(v[4], v[5], v[6], v[7]);
+  }
+}
+
+template <int T>
+static int run_embedding(const void *table, const int64_t *ids, float *out, long long n_ids, long long V, int K, cudaStream_t st) {
+  gguf_embedding_kernel<T><<<(unsigned)n_ids, 256, 0, st>>>((const uint8_t *)table, (const long long *)ids, out, V, K);
+  return launched("embedding_q");
+}
+
+int gguf_embedding(int type, const void *table, const int64_t *ids, float *out, long long n_ids, long long V, int K, cudaStream_t st) {
+  if (n_ids == 0) return 0;
+  switch (type) {
+    case LB200_Q4_0: return run_embedding<LB200_Q4_0>(table, ids, out, n_ids, V, K, st);
+    case LB200_Q5_0: return run_embedding<LB200_Q5_0>(table, ids, out, n_ids, V, K, st);
+    case LB200_Q8_0: return run_embedding<LB200_Q8_0>(table, ids, out, n_ids, V, K, st);
+    case LB200_Q4_K: return run_embedding<LB200_Q4_K>(table, ids, out, n_ids, V, K, st);
+    case LB200_Q5_K: return run_embedding<LB200_Q5_K>(table, ids, out, n_ids, V, K, st);
+    case LB200_Q6_K: return run_embedding<LB200_Q6_K>(table, ids, out, n_ids, V, K, st);
+  }
+  return fail(LB200_E_DTYPE, "embedding_q: ggml type %d has no kernel", type);
+}
+
 }  // namespace lb

@@ -112,4 +112,64 @@ int int4_gemv(const void *x, const uint32_t *codes, const float *s, const float 
   return launched("int4_gemv");
 }
 
+// ---- checkpoint layouts -> the canonical layout, on the device (the reference converts on the host with
+// O(N K) Go loops at load time, quant/int4.go:103-261).  kind 0: AutoGPTQ "gptq" (qzeros hold zero - 1),
+// 1: "gptq_v2", 2: AutoAWQ GEMM.  Ordered groups only (g_idx[k] = k / G); an act-order checkpoint keeps the
+// host path, which also builds the column permutation.
+__device__ __forceinline__ uint32_t nib_at(uint32_t w, int j) { return (w >> (4 * j)) & 0xFu; }
+__device__ __forceinline__ int awq_slot(int col) { return (col >> 1) + 4 * (col & 1); }  // inverse of (0,2,4,6,1,3,5,7)
+
+// codes: one thread per canonical word (n, c).  GPTQ: the word is qweight[c][n] itself (a transpose).  AWQ:
+// nibble j is column n of row 8c + j.  A 32 x 32 tile goes through shared memory so that reads and writes
+// are both coalesced.
+__global__ void __launch_bounds__(256) int4_repack_codes_kernel(const uint32_t *__restrict__ qweight, uint32_t *__restrict__ codes,
+                                                                int N, int K, int kind) {
+  __shared__ uint32_t tile[32][33];
+  const int KW = K / 8;
+  const int c0 = blockIdx.x * 32, n0 = blockIdx.y * 32, tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {  // tile[c - c0][n - n0], read along n
+    const int c = c0 + r, n = n0 + tx;
+    uint32_t w = 0;
+    if (c < KW && n < N) {
+      if (kind == 2) {
+        const int slot = awq_slot(n & 7);
+#pragma unroll
+        for (int j = 0; j < 8; j++) w |= nib_at(qweight[(size_t)(8 * c + j) * (N / 8) + (n >> 3)], slot) << (4 * j);
+      } else {
+        w = qweight[(size_t)c * N + n];
+      }
+    }
+    tile[r][tx] = w;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {  // written along c
+    const int n = n0 + r, c = c0 + tx;
+    if (n < N && c < KW) codes[(size_t)n * KW + c] = tile[tx][r];
+  }
+}
+
+// scales / zeros: (K/G, N) and packed (K/G, N/8) -> f32 (N, K/G)
+__global__ void int4_repack_sz_kernel(const uint32_t *__restrict__ qzeros, const float *__restrict__ scales, float *__restrict__ s_out,
+                                      float *__restrict__ z_out, int N, int G, int kind) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)N * G) return;
+  const int g = (int)(i / N), n = (int)(i - (long long)g * N);  // read along n
+  const uint32_t w = qzeros[(size_t)g * (N / 8) + (n >> 3)];
+  const float z = (float)nib_at(w, kind == 2 ? awq_slot(n & 7) : (n & 7));
+  s_out[(size_t)n * G + g] = scales[(size_t)g * N + n];
+  z_out[(size_t)n * G + g] = kind == 0 ? z + 1.f : z;
+}
+
+int int4_repack(const uint32_t *qweight, const uint32_t *qzeros, const float *scales, uint32_t *codes, float *s_out, float *z_out,
+                int N, int K, int G, int kind, cudaStream_t st) {
+  if (kind < 0 || kind > 2) return fail(LB200_E_DTYPE, "light_b200: int4_repack: layout %d (0 gptq, 1 gptq_v2, 2 awq)", kind);
+  if (N <= 0 || K <= 0 || G <= 0 || N % 8 || K % 8 || K % G) return fail(LB200_E_SHAPE, "light_b200: int4_repack: N %d K %d group %d", N, K, G);
+  dim3 grid((K / 8 + 31) / 32, (N + 31) / 32);
+  if (grid.y > 65535) return fail(LB200_E_TOO_LARGE, "light_b200: int4_repack: N=%d exceeds the kernel's grid", N);
+  int4_repack_codes_kernel<<<grid, 256, 0, st>>>(qweight, codes, N, K, kind);
+  const long long n = (long long)N * (K / G);
+  int4_repack_sz_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(qzeros, scales, s_out, z_out, N, K / G, kind);
+  return launched("int4_repack");
+}
+
 }  // namespace lb

@@ -238,7 +238,43 @@ def Dequantize(w: QTensor) -> torch.Tensor:
     return out
 
 
+def EmbeddingQ(table: QTensor, ids: torch.Tensor) -> torch.Tensor:
+    """nn.Embedding over a quantized table (nn/embedding.go; nn/embedding_test.go:127): only the gathered rows are
+    dequantized.  table (V, K) blocks, ids I64 of any shape -> f32 ids.shape + (K,)."""
+    if len(table.shape) != 2:
+        raise ValueError(f"ops.EmbeddingQ: table shape {table.shape}, want (V, K)")
+    if ids.dtype != torch.int64:
+        raise ValueError(f"ops.EmbeddingQ: ids must be I64, got {ids.dtype}")
+    dev = _dev(table.data, "EmbeddingQ")
+    V, K = table.shape
+    flat = ids.contiguous().reshape(-1)
+    out = torch.empty((flat.numel(), K), dtype=torch.float32, device=table.device)
+    _lib.check(_lib.lib().light_b200_embedding_q(table.ggml_type, _ptr(table.data), _ptr(flat), _ptr(out), flat.numel(), V, K, dev, _stream(dev)))
+    return out.reshape(tuple(ids.shape) + (K,))
+
+
 # --------------------------------------------------------------------------- int4
+
+def Int4FromCheckpoint(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, group: int, layout: str) -> "Int4":
+    """quant.FromGPTQ (ordered groups) / quant.FromAWQ (quant/int4.go:103-261) on the device: layout "gptq",
+    "gptq_v2" or "awq"; qweight / qzeros I32, scales F32 (K/G, N)."""
+    kind = {"gptq": 0, "gptq_v2": 1, "awq": 2}[layout]
+    if qweight.dim() != 2 or qzeros.dim() != 2 or scales.dim() != 2:
+        raise ValueError("quant.From%s: rank-2 qweight / qzeros / scales expected" % ("AWQ" if kind == 2 else "GPTQ"))
+    K, N = (qweight.shape[0], qweight.shape[1] * 8) if kind == 2 else (qweight.shape[0] * 8, qweight.shape[1])
+    if group <= 0:
+        group = K
+    if K % group or tuple(scales.shape) != (K // group, N) or tuple(qzeros.shape) != (K // group, N // 8) or scales.dtype != torch.float32:
+        raise ValueError(f"quant.From{'AWQ' if kind == 2 else 'GPTQ'}: qweight {tuple(qweight.shape)}, qzeros {tuple(qzeros.shape)}, "
+                         f"scales {tuple(scales.shape)}, group {group} inconsistent")
+    dev = _dev(qweight, "Int4FromCheckpoint")
+    codes = torch.empty((N, K // 8), dtype=torch.int32, device=qweight.device)
+    s = torch.empty((N, K // group), dtype=torch.float32, device=qweight.device)
+    z = torch.empty_like(s)
+    _lib.check(_lib.lib().light_b200_int4_repack(_ptr(qweight.contiguous()), _ptr(qzeros.contiguous()), _ptr(scales.contiguous()), _ptr(codes),
+                                                 _ptr(s), _ptr(z), N, K, group, kind, dev, _stream(dev)))
+    return Int4(codes, s, z, group)
+
 
 def DequantizeInt4(w: Int4, out_dtype: torch.dtype, out: Optional[torch.Tensor] = None, offset: int = 0) -> torch.Tensor:
     """ops.DequantizeInt4 / dequantizeInt4At (ops/int4.go:13-57): (N, K) at F32 or BF16; with

@@ -158,3 +158,18 @@ def test_fp8_vs_reference_cuda(cuda):
     mine = ops.DequantizeF8Block(wd, sd, b, b, torch.float32)
     torch.cuda.synchronize()
     assert torch.equal(mine, theirs)
+
+
+@pytest.mark.parametrize("layout,N,K,G", [("gptq", 600, 3584, 128), ("gptq_v2", 40, 256, 64), ("awq", 600, 3584, 128), ("awq", 8, 64, 32)])
+def test_int4_checkpoint_repack_matches_oracle(cuda, oracle, layout, N, K, G):
+    """The device converters against the oracle's quant.FromGPTQ / quant.FromAWQ at a BASELINE config 4 shape and at
+    ragged tile edges (N, K/8 not multiples of 32)."""
+    codes, s, z = synth.random_int4(701, N, K, G)
+    if layout == "gptq":
+        z[z == 0] = 1.0  # the v1 format stores zero - 1 in four bits
+    qw, qz, sc = synth.to_awq(codes, s, z) if layout == "awq" else synth.to_gptq(codes, s, z, v2=layout == "gptq_v2")
+    t = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.int32) if a.dtype == np.uint32 else np.ascontiguousarray(a)).to(cuda)
+    w = ops.Int4FromCheckpoint(t(qw), t(qz), t(sc), G, layout)
+    c2, s2, z2 = oracle.int4_from_awq(qw, qz, sc, G) if layout == "awq" else oracle.int4_from_gptq(qw, qz, sc, G, v2=layout == "gptq_v2")
+    assert np.array_equal(w.codes.cpu().numpy().view(np.uint32), c2) and np.array_equal(c2, codes)
+    assert np.array_equal(w.scales.cpu().numpy(), s2) and np.array_equal(w.zeros.cpu().numpy(), z2)
