@@ -311,6 +311,16 @@ LB200_API int light_b200_embedding_q(int ggml_type, const void *table, const int
 LB200_API int light_b200_int4_repack(const void *qweight, const void *qzeros, const float *scales, void *codes, float *scales_out,
                                      float *zeros_out, int N, int K, int group, int layout, int device, void *stream);
 
+/* INT8 weights x INT8 activations.  Registry key {matmul_w8a8, CUDA, F32} (reference ops.MatMulW8A8,
+ * ops/matmul_w8a8.go:13-120): x f32 (M, K), wq int8 (N, K), ws f32 (N) -> out f32 (M, N).  The activation
+ * rows are quantised on the device exactly as QuantizeRowsInt8 does (scale = amax / 127, round half to even,
+ * clamp to +-127), the contraction accumulates in int32 on the integer tensor cores, and the epilogue is
+ * f32(acc) * xs[m] * ws[n]: bit-identical to the reference's Go path.  xq_scratch (M * K bytes, 16-byte
+ * aligned) and xs_scratch (M floats) are the caller's, like every other scratch of this ABI.  K % 16 == 0. */
+LB200_API int light_b200_quantize_rows_int8(const float *x, int8_t *q, float *scales, int64_t M, int K, int device, void *stream);
+LB200_API int light_b200_matmul_w8a8(const float *x, const int8_t *wq, const float *ws, float *out, int8_t *xq_scratch,
+                                     float *xs_scratch, int M, int N, int K, int device, void *stream);
+
 /* RMSNorm (and the residual add before it) folded into the Q4_K decode launch that consumes it:
  * light_b200_rmsnorm + light_b200_matmul_q_multi (act 0: count matrices, out[i] = w[i] . y) or
  * + light_b200_matmul_q_gated (act 1 SiLU / 2 GELU: count 2, out[0] = act(w[0] . y) * (w[1] . y)) as ONE

@@ -406,6 +406,33 @@ int light_b200_int4_repack(const void *qweight, const void *qzeros, const float 
                      group <= 0 ? K : group, layout, (cudaStream_t)stream);
 }
 
+int light_b200_quantize_rows_int8(const float *x, int8_t *q, float *scales, int64_t M, int K, int device, void *stream) {
+  if (M < 0 || M > 0x7fffffffLL || K <= 0) return fail(LB200_E_SHAPE, "light_b200: quantize_rows_int8: M=%lld K=%d", (long long)M, K);
+  if (M == 0) return 0;
+  REQUIRE_PTR(x, "quantize_rows_int8");
+  REQUIRE_PTR(q, "quantize_rows_int8");
+  REQUIRE_PTR(scales, "quantize_rows_int8");
+  if (int rc = bind(device)) return rc;
+  return quantize_rows_int8(x, q, scales, M, K, (cudaStream_t)stream);
+}
+
+int light_b200_matmul_w8a8(const float *x, const int8_t *wq, const float *ws, float *out, int8_t *xq_scratch, float *xs_scratch, int M,
+                           int N, int K, int device, void *stream) {
+  if (M < 0 || N < 0 || K <= 0) return fail(LB200_E_SHAPE, "light_b200: matmul_w8a8: bad shape M=%d N=%d K=%d", M, N, K);
+  if (K % 16) return fail(LB200_E_SHAPE, "light_b200: matmul_w8a8: K=%d, want a multiple of 16", K);
+  if (M == 0 || N == 0) return 0;
+  REQUIRE_PTR(x, "matmul_w8a8");
+  REQUIRE_PTR(wq, "matmul_w8a8");
+  REQUIRE_PTR(ws, "matmul_w8a8");
+  REQUIRE_PTR(out, "matmul_w8a8");
+  REQUIRE_PTR(xq_scratch, "matmul_w8a8");
+  REQUIRE_PTR(xs_scratch, "matmul_w8a8");
+  if (!aligned(wq, 16) || !aligned(xq_scratch, 16) || !aligned(out, 4) || !aligned(x, 4))
+    return fail(LB200_E_ALIGN, "light_b200: matmul_w8a8: wq and xq_scratch must be 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return matmul_w8a8(x, wq, ws, out, xq_scratch, xs_scratch, M, N, K, (cudaStream_t)stream);
+}
+
 int light_b200_rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype, int64_t rows,
                        int cols, float eps, int device, void *stream) {
   if (int rc = bind(device)) return rc;

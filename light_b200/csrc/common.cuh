@@ -95,6 +95,9 @@ int kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_
               cudaStream_t st);
 int inc_i64(int64_t *p, int n, cudaStream_t st);
 int decode_attn_status();
+int quantize_rows_int8(const float *x, int8_t *q, float *scales, long long M, int K, cudaStream_t st);
+int matmul_w8a8(const float *x, const int8_t *wq, const float *ws, float *out, int8_t *xq, float *xs, int M, int N, int K,
+                cudaStream_t st);
 int gguf_embedding(int type, const void *table, const int64_t *ids, float *out, long long n_ids, long long V, int K, cudaStream_t st);
 int int4_repack(const uint32_t *qweight, const uint32_t *qzeros, const float *scales, uint32_t *codes, float *s_out, float *z_out,
                 int N, int K, int G, int kind, cudaStream_t st);

@@ -238,6 +238,26 @@ def Dequantize(w: QTensor) -> torch.Tensor:
     return out
 
 
+def MatMulW8A8(x: torch.Tensor, wq: torch.Tensor, ws: torch.Tensor) -> torch.Tensor:
+    """ops.MatMulW8A8 (ops/matmul_w8a8.go:13-63): x F32 (M, K), wq I8 (N, K), ws F32 (N,) -> F32 (M, N); the rows of x
+    are quantised to int8 on the device, the products accumulate in int32."""
+    if x.dim() != 2 or wq.dim() != 2 or ws.dim() != 1:
+        raise ValueError(f"ops.MatMulW8A8: want x (M,K), wq (N,K), ws (N,); got {tuple(x.shape)}, {tuple(wq.shape)}, {tuple(ws.shape)}")
+    if x.dtype != torch.float32 or wq.dtype != torch.int8 or ws.dtype != torch.float32:
+        raise ValueError(f"ops.MatMulW8A8: dtypes must be x=F32, wq=I8, ws=F32 (got {x.dtype}, {wq.dtype}, {ws.dtype})")
+    M, K = x.shape
+    N = wq.shape[0]
+    if wq.shape[1] != K or ws.shape[0] != N:
+        raise ValueError(f"ops.MatMulW8A8: x {tuple(x.shape)}, wq {tuple(wq.shape)}, ws {tuple(ws.shape)} do not agree")
+    dev = _dev(x, "MatMulW8A8")
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    xq = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    xs = torch.empty((M,), dtype=torch.float32, device=x.device)
+    _lib.check(_lib.lib().light_b200_matmul_w8a8(_ptr(x.contiguous()), _ptr(wq.contiguous()), _ptr(ws.contiguous()), _ptr(out), _ptr(xq), _ptr(xs),
+                                                 M, N, K, dev, _stream(dev)))
+    return out
+
+
 def EmbeddingQ(table: QTensor, ids: torch.Tensor) -> torch.Tensor:
     """nn.Embedding over a quantized table (nn/embedding.go; nn/embedding_test.go:127): only the gathered rows are
     dequantized.  table (V, K) blocks, ids I64 of any shape -> f32 ids.shape + (K,)."""

@@ -268,5 +268,25 @@ def rope(x: np.ndarray, positions: np.ndarray, base: float) -> np.ndarray:
     return out
 
 
+def quantize_rows_int8(x: np.ndarray):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    M, K = x.shape
+    q, s = np.empty((M, K), np.int8), np.empty(M, np.float32)
+    _chk(lib().lo_quantize_rows_int8(_p(x), _p(q), _p(s), C.c_int64(M), K), "quantize_rows_int8")
+    return q, s
+
+
+def matmul_w8a8(x: np.ndarray, wq: np.ndarray, ws: np.ndarray):
+    """-> (out f32 (M, N), the int32 accumulators)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    wq = np.ascontiguousarray(wq, dtype=np.int8)
+    ws = np.ascontiguousarray(ws, dtype=np.float32)
+    M, K = x.shape
+    N = wq.shape[0]
+    out, acc = np.empty((M, N), np.float32), np.empty((M, N), np.int32)
+    _chk(lib().lo_matmul_w8a8(_p(x), _p(wq), _p(ws), _p(out), _p(acc), M, N, K), "matmul_w8a8")
+    return out, acc
+
+
 def has_avx2() -> bool:
     return bool(lib().lo_has_avx2())

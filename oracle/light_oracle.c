@@ -814,4 +814,44 @@ LO_API int lo_rope_f32(const float *x, const int64_t *positions, float *out, int
   return 0;
 }
 
+/* ops/matmul_w8a8.go:65-93 (QuantizeRowsInt8): per row scale = amax / 127, q = clamp(round_to_even(x * (1 / scale))). */
+LO_API int lo_quantize_rows_int8(const float *x, int8_t *q, float *scales, int64_t M, int K) {
+  for (int64_t m = 0; m < M; m++) {
+    const float *row = x + (size_t)m * K;
+    float amax = 0.f;
+    for (int k = 0; k < K; k++) {
+      float a = (float)fabs((double)row[k]);
+      if (a > amax) amax = a;
+    }
+    float scale = amax / 127, inv = 0.f;
+    if (scale > 0) inv = 1 / scale;
+    scales[m] = scale;
+    for (int k = 0; k < K; k++) {
+      float r = (float)nearbyint((double)(row[k] * inv)); /* round half to even in the default rounding mode */
+      if (r > 127) r = 127;
+      else if (r < -127) r = -127;
+      q[(size_t)m * K + k] = (int8_t)r;
+    }
+  }
+  return 0;
+}
+
+/* ops/matmul_w8a8.go:95-120 (matMulW8A8Reference): int32 accumulation, out = f32(acc) * xs[m] * ws[n]. */
+LO_API int lo_matmul_w8a8(const float *x, const int8_t *wq, const float *ws, float *out, int32_t *acc_out, int M, int N, int K) {
+  int8_t *xq = (int8_t *)malloc((size_t)M * K);
+  float *xs = (float *)malloc(sizeof(float) * (size_t)M);
+  lo_quantize_rows_int8(x, xq, xs, M, K);
+  for (int m = 0; m < M; m++)
+    for (int n = 0; n < N; n++) {
+      int32_t acc = 0;
+      const int8_t *xr = xq + (size_t)m * K, *wr = wq + (size_t)n * K;
+      for (int k = 0; k < K; k++) acc += (int32_t)xr[k] * (int32_t)wr[k];
+      if (acc_out) acc_out[(size_t)m * N + n] = acc;
+      out[(size_t)m * N + n] = (float)acc * xs[m] * ws[n];
+    }
+  free(xq);
+  free(xs);
+  return 0;
+}
+
 LO_API int lo_has_avx2(void) { return have_avx2(); }
