@@ -1272,6 +1272,214 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q80_gemv_mma_kernel(const float
   cp_async_wait<0>();
 }
 
+// ------------------------------------------------------------------------------------ int4 (GPTQ / AWQ), one row of x
+//
+// The canonical 4-bit layout (codes u32 (N, K/8), nibble j of word c = element 8c + j; scales / zeros f32
+// (N, K/G)) through the Q4_K arithmetic: LOP3 turns nibble pairs into f16 (64 + code), the MMA columns are
+// sets of 32 elements that share a scale (here the even- and the odd-numbered elements of a lane's 64), and
+// acc += s (D - (64 + z) Sx).  Structure as the Q8_0 kernel (per-warp ring, activations staged per run of
+// 256 k, so any K fits); a tile row sits 16 bytes into a 144-byte slot, which keeps the Q4_K kernel's
+// conflict-free 16-byte loads.  Needs G % 64 == 0 and K % 256 == 0.  reference: int4_gemv_f32 / _bf16,
+// kernels/cuda/src/int4.cu:43-106.
+constexpr int I4_PITCH = 144;
+constexpr int I4_TILE_BYTES = ROWS * I4_PITCH;
+constexpr int I4_STAGES = 4;
+
+// stage_block<32> for the int4 element order: lanes l, l^1 hold the eight elements of one code word; the even
+// lane assembles (x0, x4, x2, x6) for the even set, the odd lane (x1, x5, x3, x7) for the odd set.
+__device__ __forceinline__ float stage_block_int4(const float4 (&xv)[2], uint32_t slab, int lane) {
+  using S = Slab<32>;
+  uint32_t m = 0;
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    m = max(m, __float_as_uint(xv[i].x) & 0x7fffffffu);
+    m = max(m, __float_as_uint(xv[i].y) & 0x7fffffffu);
+    m = max(m, __float_as_uint(xv[i].z) & 0x7fffffffu);
+    m = max(m, __float_as_uint(xv[i].w) & 0x7fffffffu);
+  }
+  m = __reduce_max_sync(0xffffffffu, m);
+  int sh = (int)(m >> 23) - 127 - 14;
+  sh = sh < 0 ? 0 : (sh > 100 ? 100 : sh);
+  const float down = __uint_as_float((uint32_t)(127 - sh) << 23), up = __uint_as_float((uint32_t)(127 + sh) << 23);
+  const bool odd = lane & 1;
+#pragma unroll
+  for (int i = 0; i < 2; i++) {
+    float4 v = xv[i];
+    if (sh) v.x *= down, v.y *= down, v.z *= down, v.w *= down;
+    // the even lane needs the partner's x and z, the odd lane the partner's y and w
+    const float ra = __shfl_xor_sync(0xffffffffu, odd ? v.x : v.y, 1), rb = __shfl_xor_sync(0xffffffffu, odd ? v.z : v.w, 1);
+    const float s0 = odd ? ra : v.x, s1 = odd ? v.y : ra, s2 = odd ? rb : v.z, s3 = odd ? v.w : rb;  // slots 0..3 of this word
+    __half2 h01 = __floats2half2_rn(s0, s1), h23 = __floats2half2_rn(s2, s3);
+    float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+    __half2 l01 = __floats2half2_rn(s0 - f01.x, s1 - f01.y), l23 = __floats2half2_rn(s2 - f23.x, s3 - f23.y);
+    const int t = 2 * i + (lane >> 4), w = (lane >> 1) & 7, vs = 2 * t + (lane & 1);  // lane quarter, word, set
+    const uint32_t a = slab + vs * S::SUB_BYTES + w * 8;
+    sts64(a, *reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+    sts64(a + S::LO_OFF, *reinterpret_cast<uint32_t *>(&l01), *reinterpret_cast<uint32_t *>(&l23));
+    float s = (s0 + s1) + (s2 + s3);
+    s += __shfl_xor_sync(0xffffffffu, s, 2), s += __shfl_xor_sync(0xffffffffu, s, 4), s += __shfl_xor_sync(0xffffffffu, s, 8);
+    if (w == 0) asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(slab + S::SX_OFF + vs * 4), "f"(s));
+  }
+  return up;
+}
+
+template <int S, typename XT>
+__global__ void __launch_bounds__(WARPS * 32, 2) int4_gemv_mma_kernel(const XT *__restrict__ x, const uint8_t *__restrict__ w,
+                                                                     const float *__restrict__ scales, const float *__restrict__ zeros,
+                                                                     XT *__restrict__ out, int N, int K, int G) {
+  using SL = Slab<32>;
+  extern __shared__ __align__(16) unsigned char dyn[];  // ring: WARPS x S tiles
+  __shared__ __align__(16) unsigned char slabs[WARPS][SL::BYTES];
+  __shared__ __align__(16) unsigned char zero[SL::ZERO_BYTES];
+  __shared__ __align__(16) float2 red[2][WARPS * GROUP * 32];  // by group parity
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int nb = K >> 8;
+  const uint32_t row_bytes = (uint32_t)K >> 1;  // 128 bytes of codes per 256 elements
+  const int ngrp = K / G;
+  for (int i = threadIdx.x; i < SL::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
+
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + warp * (S * I4_TILE_BYTES);
+  const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
+  const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
+  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(&red[0][warp * GROUP * 32 + lane]);
+  constexpr uint32_t RED_PARITY = WARPS * GROUP * 32 * 8;
+  // B addresses inside the slab, as in the Q4_K kernel: the even MMA's column 2t carries the hi half of the
+  // even-numbered elements of lane t's 64, column 2t+1 their lo half; the odd MMA the other way round
+  const bool mine = (g >> 1) == t;
+  const uint32_t pe = mine ? slab + (2 * t) * SL::SUB_BYTES + ((g & 1) ? SL::LO_OFF : 0) : szero;
+  const uint32_t po = mine ? slab + (2 * t + 1) * SL::SUB_BYTES + ((g & 1) ? 0 : SL::LO_OFF) : szero;
+  const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
+
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const int t0 = (int)((uint32_t)tiles * blockIdx.x / gridDim.x), t1 = (int)((uint32_t)tiles * (blockIdx.x + 1) / gridDim.x);
+
+  // requests: a tile is 16 rows x 8 granules; lane l copies granule l & 7 of rows (l >> 3) + 4 i, i = 0..3
+  const uint32_t c_row = lane >> 3, c_piece = lane & 7;
+  int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_gt < t1 && warp < nb) {
+      const int r0 = min((i_gt + i_rt) * ROWS, N - ROWS);
+      const uint8_t *src = w + ((size_t)(r0 + c_row) * row_bytes + (uint32_t)i_b * 128u + c_piece * 16);
+      uint32_t dst = ring + i_slot * I4_TILE_BYTES + c_row * I4_PITCH + 16 + c_piece * 16;
+#pragma unroll
+      for (int i = 0; i < 4; i++) {
+        cp_async16(dst, src);
+        src += 4 * row_bytes, dst += 4 * I4_PITCH;
+      }
+      i_slot = (i_slot + 1) & (S - 1);
+      if (++i_rt == i_gs) {
+        i_rt = 0, i_b += WARPS;
+        if (i_b >= nb) i_b = warp, i_gt += i_gs, i_gs = min(GROUP, t1 - i_gt);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int p = 0; p < S; p++) issue();
+
+  pdl_wait();  // x is the previous launch's output; the weights requested above are not
+  __syncthreads();
+  float4 xn[2];  // the activations of the block this warp stages next, requested one block ahead
+  auto load_x = [&](int b) {
+    if constexpr (std::is_same<XT, float>::value) {
+      xn[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+      xn[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(x + b * 256 + 128 * i) + lane);
+        xn[i] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+      }
+    }
+  };
+  if (warp < nb) load_x(warp);
+
+  // One unit: rows g, g+8 of one tile x one run of 256 k, out of ring slot `sb`.  Lane t owns words 8t .. 8t+7
+  // of both rows (elements 64t .. 64t+63, one quantization group).  Word i gives the even MMA the f16 pairs
+  // (64 + n0, 64 + n4), (64 + n2, 64 + n6) and the odd MMA (n1, n5), (n3, n7); the slab holds x in that order.
+  // acc += s ((D_even + D_odd) - (64 + z) (Sx_even + Sx_odd)).
+  auto unit = [&](uint32_t sb, int r0, int b, const float2 sx, float up, float (&vr)[2]) {
+    const int grp = (b * 256 + 64 * t) / G;
+    float sc[2], zp[2];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const size_t o = (size_t)(r0 + g + 8 * r) * ngrp + grp;
+      sc[r] = __ldg(scales + o), zp[r] = __ldg(zeros + o);
+    }
+    const uint32_t la = sb + g * I4_PITCH + 32u * t;
+    const uint4 qa0 = lds128(la + 16), qa1 = lds128(la + 32);
+    const uint4 qb0 = lds128(la + 8 * I4_PITCH + 16), qb1 = lds128(la + 8 * I4_PITCH + 32);
+    __syncwarp();  // the slot is free again
+    issue();
+    float de[4] = {0.f, 0.f, 0.f, 0.f}, dq[4] = {0.f, 0.f, 0.f, 0.f};  // even / odd element chains
+    const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+    const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const uint32_t vg = qg[i], vh = qh[i];
+      const uint32_t e0 = and_or(vg << 4, mask, magic), e1 = and_or(vh << 4, mask, magic);
+      const uint32_t e2 = and_or(vg >> 4, mask, magic), e3 = and_or(vh >> 4, mask, magic);
+      const uint32_t o0 = and_or(vg, mask, magic), o1 = and_or(vh, mask, magic);
+      const uint32_t o2 = and_or(vg >> 8, mask, magic), o3 = and_or(vh >> 8, mask, magic);
+      const uint2 be = lds64(pe + i * 8), bo = lds64(po + i * 8);
+      mma16816(de, e0, e1, e2, e3, be.x, be.y);
+      mma16816(dq, o0, o1, o2, o3, bo.x, bo.y);
+    }
+    const float ssum = sx.x + sx.y;
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+      vr[r] = sc[r] * (((de[2 * r] + de[2 * r + 1]) + (dq[2 * r] + dq[2 * r + 1])) - (64.f + zp[r]) * ssum) * up;
+  };
+
+  int slot = 0, parity = 0;
+  for (int gt = t0; gt < t1; gt += GROUP, parity ^= 1) {
+    const int gs = min(GROUP, t1 - gt);
+    const uint32_t red_g = red_lane + parity * RED_PARITY;
+    for (int b = warp; b < nb; b += WARPS) {
+      // this block's activations into the warp's slab; the next block's are requested meanwhile
+      const float4 xv[2] = {xn[0], xn[1]};
+      {
+        const int bn = b + WARPS < nb ? b + WARPS : warp;
+        if (b + WARPS < nb || gt + GROUP < t1) load_x(bn);
+      }
+      __syncwarp();  // every lane is done reading the previous block's slab
+      const float up = stage_block_int4(xv, slab, lane);
+      __syncwarp();
+      float2 sx;
+      asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + SL::SX_OFF + 8 * t));
+      for (int rt = 0; rt < gs; rt++) {
+        cp_async_wait<S - 1>();  // this lane's granules of the tile have landed ...
+        __syncwarp();            // ... and so have the other lanes'
+        const uint32_t sb = ring + slot * I4_TILE_BYTES;
+        slot = (slot + 1) & (S - 1);
+        float vr[2];
+        unit(sb, min((gt + rt) * ROWS, N - ROWS), b, sx, up, vr);
+        // the warp's first block of a group overwrites what an earlier group left behind
+        const uint32_t ra = red_g + rt * (32 * 8);
+        float2 o = make_float2(0.f, 0.f);
+        if (b != warp) asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(o.x), "=f"(o.y) : "r"(ra));
+        asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(ra), "f"(o.x + vr[0]), "f"(o.y + vr[1]));
+      }
+    }
+    __syncthreads();  // also orders this group's reads of red[parity] before its reuse two groups on
+    for (int i = threadIdx.x; i < gs * ROWS; i += WARPS * 32) {
+      const int rt = i >> 4, row = i & 15, gg = row & 7, hi = row >> 3;
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) {
+        if (wq >= nb) break;  // a warp without a K block never wrote its part
+        const float2 *p = &red[parity][(wq * GROUP + rt) * 32 + gg * 4];
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;
+      }
+      const int orow = min((gt + rt) * ROWS, N - ROWS) + row;
+      st_act(out, orow, v);
+    }
+  }
+  cp_async_wait<0>();
+}
+
 // ------------------------------------------------------------------------------------ Q6_K, 2 .. 8 rows of x
 //
 // Tokens as MMA columns, as in q4k_gemv_tok_kernel.  The 16 k slots of an MMA are one 16-element
@@ -1553,6 +1761,47 @@ int gguf_gemv_fast(int type, const float *x, const void *w, float *out, int M, i
   if (rc) return rc;
   rc = launched("matmul_q (decode)");
   return rc ? rc : 1;
+}
+
+// One to a few activation rows against group-quantized 4-bit weights in the canonical layout: a pass of the
+// one-row kernel per row: bf16 activations up to three rows (then the tensor-core decode kernel wins), f32
+// activations up to 64 (their only other kernel below the prefill range is the CUDA-core one, which a pass per
+// row beats at every count: 10.5 us against 236 us per row at 18944 x 3584).  Returns 1 if launched, 0 if
+// the shape is not covered.
+int g_int4_fast_max_f32 = 64, g_int4_fast_max_bf16 = 3;  // LIGHT_B200_INT4_FAST_MAX_M (tuning knob, both)
+int int4_gemv_fast(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N, int K,
+                   int G, cudaStream_t st) {
+  static bool knob = false;
+  if (!knob) {
+    if (const char *e = getenv("LIGHT_B200_INT4_FAST_MAX_M")) g_int4_fast_max_f32 = g_int4_fast_max_bf16 = atoi(e);
+    knob = true;
+  }
+  if (M < 1 || M > (act_dtype == LB200_F32 ? g_int4_fast_max_f32 : g_int4_fast_max_bf16)) return 0;
+  if (K % 256 || G % 64 || N < ROWS || ((uintptr_t)codes & 15) || ((uintptr_t)x & 15) || (act_dtype == LB200_BF16 && (K % 8))) return 0;
+  if (act_dtype != LB200_F32 && act_dtype != LB200_BF16) return 0;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(int4_gemv_mma_kernel<I4_STAGES, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * I4_STAGES * I4_TILE_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(int4_gemv_mma_kernel<I4_STAGES, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * I4_STAGES * I4_TILE_BYTES);
+    if (e != cudaSuccess) return fail((int)e, "light_b200: int4_gemv (decode): %s", cudaGetErrorString(e));
+    attr_done = true;
+  }
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
+  const size_t dyn = (size_t)WARPS * I4_STAGES * I4_TILE_BYTES;
+  for (int m = 0; m < M; m++) {
+    int rc;
+    if (act_dtype == LB200_F32)
+      rc = launch_pdl(int4_gemv_mma_kernel<I4_STAGES, float>, grid, dyn, st, (const float *)x + (size_t)m * K, (const uint8_t *)codes, s, z,
+                      (float *)y + (size_t)m * N, N, K, G);
+    else
+      rc = launch_pdl(int4_gemv_mma_kernel<I4_STAGES, __nv_bfloat16>, grid, dyn, st, (const __nv_bfloat16 *)x + (size_t)m * K, (const uint8_t *)codes,
+                      s, z, (__nv_bfloat16 *)y + (size_t)m * N, N, K, G);
+    if (rc) return rc;
+    if (int l = launched("int4_gemv (decode)")) return l;
+  }
+  return 1;
 }
 
 // 2 .. 8 activation rows against one Q4_K or Q6_K matrix, tokens as MMA columns.  Returns 1 if launched, 0 if

@@ -173,3 +173,25 @@ def test_int4_checkpoint_repack_matches_oracle(cuda, oracle, layout, N, K, G):
     c2, s2, z2 = oracle.int4_from_awq(qw, qz, sc, G) if layout == "awq" else oracle.int4_from_gptq(qw, qz, sc, G, v2=layout == "gptq_v2")
     assert np.array_equal(w.codes.cpu().numpy().view(np.uint32), c2) and np.array_equal(c2, codes)
     assert np.array_equal(w.scales.cpu().numpy(), s2) and np.array_equal(w.zeros.cpu().numpy(), z2)
+
+
+@pytest.mark.parametrize("N,K,G", [(600, 3584, 128), (16, 256, 64), (37, 2048, 256), (200, 18944, 128)])
+def test_int4_one_row_tensor_core_kernel(cuda, oracle, N, K, G):
+    """The one-row decode kernel (tensor-core arithmetic on the canonical layout): ragged heights, one to 74
+    runs of 256 k, groups of 64 to 256; f32 rows 1..8 (ops/int4_test.go's 1e-4 bound) and bf16 rows 1..3."""
+    codes, s, z, w = _int4(801, N, K, G, cuda)
+    deq = oracle.int4_dequant(codes, s, z, G).astype(np.float64)
+    g = torch.Generator().manual_seed(802)
+    for M in (1, 2, 8):
+        x = torch.randn(M, K, generator=g)
+        got = ops.MatMulInt4(x.to(cuda), w)
+        assert torch.equal(got, ops.MatMulInt4(x.to(cuda), w))
+        want = x.numpy().astype(np.float64) @ deq.T
+        assert max_rel(got.cpu().numpy(), want) <= 1e-4 and rel_l2(got.cpu().numpy(), want) <= 1e-5, (M, rel_l2(got.cpu().numpy(), want))
+    for M in (1, 3):
+        xb = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        got = ops.MatMulInt4(xb.to(cuda), w)
+        assert got.dtype == torch.bfloat16
+        assert max_rel(got.float().cpu().numpy(), xb.float().numpy().astype(np.float64) @ deq.T) <= 3e-2
+    big = torch.randn(1, K, generator=g) * 1e6  # beyond f16 range: the exact power-of-two prescale
+    assert rel_l2(ops.MatMulInt4(big.to(cuda), w).cpu().numpy(), big.numpy().astype(np.float64) @ deq.T) <= 1e-5
