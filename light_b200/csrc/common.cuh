@@ -95,6 +95,8 @@ int kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_
               cudaStream_t st);
 int inc_i64(int64_t *p, int n, cudaStream_t st);
 int decode_attn_status();
+int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR, int bC,
+                  cudaStream_t st);
 // one-row tensor-core decode kernel for canonical int4 weights: 1 = took the call, 0 = not covered, other = error
 int int4_gemv_fast(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N, int K,
                    int G, cudaStream_t st);

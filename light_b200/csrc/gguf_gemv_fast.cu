@@ -1272,6 +1272,187 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q80_gemv_mma_kernel(const float
   cp_async_wait<0>();
 }
 
+// ------------------------------------------------------------------------------------ block-scaled FP8 (e4m3), one row of x
+//
+// The Q8_0 kernel's structure on one-byte codes: a run of 256 k is 256 bytes = 16 granules per row, a
+// 272-byte pitch keeps the 32 lanes on 32 banks.  The codes need no offset and no table: two shifts and a
+// LOP3 turn a pair of e4m3 bytes into their exact f16 values / 256.  One f32 scale per 128 x 128 block, applied
+// once per run and lane.  Needs K % 256 == 0, bC % 32 == 0, bR % 16 == 0.  reference: fp8_block_gemv_f32 /
+// _bf16, kernels/cuda/src/fp8_block.cu:60-130.
+constexpr int F8_PITCH = 272;
+constexpr int F8_TILE_BYTES = ROWS * F8_PITCH;
+constexpr int F8_STAGES = 2;
+
+template <int S, typename XT>
+__global__ void __launch_bounds__(WARPS * 32, 2) fp8_gemv_mma_kernel(const XT *__restrict__ x, const uint8_t *__restrict__ w,
+                                                                    const float *__restrict__ scale, XT *__restrict__ out, int N, int K,
+                                                                    int bR, int bC) {
+  using SL = Slab<16>;
+  extern __shared__ __align__(16) unsigned char dyn[];  // ring: WARPS x S tiles
+  __shared__ __align__(16) unsigned char slabs[WARPS][SL::BYTES];
+  __shared__ __align__(16) unsigned char zero[SL::ZERO_BYTES];
+  __shared__ __align__(16) float2 red[2][WARPS * GROUP * 32];  // by group parity
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int nb = K >> 8;
+  const uint32_t row_bytes = (uint32_t)K;  // one byte per weight
+  const int scols = K / bC;
+  for (int i = threadIdx.x; i < SL::ZERO_BYTES / 4; i += WARPS * 32) reinterpret_cast<uint32_t *>(zero)[i] = 0u;
+
+  const uint32_t ring = (uint32_t)__cvta_generic_to_shared(dyn) + warp * (S * F8_TILE_BYTES);
+  const uint32_t slab = (uint32_t)__cvta_generic_to_shared(slabs[warp]);
+  const uint32_t szero = (uint32_t)__cvta_generic_to_shared(zero);
+  const uint32_t red_lane = (uint32_t)__cvta_generic_to_shared(&red[0][warp * GROUP * 32 + lane]);
+  constexpr uint32_t RED_PARITY = WARPS * GROUP * 32 * 8;
+  // B address of the MMA of (group q, u), which works on sub-block 8h + 2q + u: column 2q + u
+  // carries the hi half of x, the neighbouring column 2q + 1 - u (unused in this accumulator) the
+  // lo half; a lane of those columns reads elements 4t..4t+3 (h adds an immediate).  All other
+  // columns read zeros.
+  uint32_t pb[4][2];
+#pragma unroll
+  for (int q = 0; q < 4; q++)
+#pragma unroll
+    for (int u = 0; u < 2; u++)
+      pb[q][u] = (g >> 1) == q ? slab + (2 * q + u) * SL::SUB_BYTES + 8 * t + ((g & 1) == u ? 0 : SL::LO_OFF) : szero;
+
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const int t0 = (int)((uint32_t)tiles * blockIdx.x / gridDim.x), t1 = (int)((uint32_t)tiles * (blockIdx.x + 1) / gridDim.x);
+
+  // requests: lanes 0..15 / 16..31 copy the 16 granules of rows 2i / 2i+1, i = 0..7
+  const uint32_t c_rsub = lane >> 4, c_piece = lane & 15;
+  int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_gt < t1 && warp < nb) {
+      const int r0 = min((i_gt + i_rt) * ROWS, N - ROWS);
+      const uint8_t *src = w + ((size_t)(r0 + c_rsub) * row_bytes + (uint32_t)i_b * 256u + c_piece * 16);
+      uint32_t dst = ring + i_slot * F8_TILE_BYTES + c_rsub * F8_PITCH + c_piece * 16;
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        cp_async16(dst, src);
+        src += 2 * row_bytes, dst += 2 * F8_PITCH;
+      }
+      i_slot = (i_slot + 1) & (S - 1);
+      if (++i_rt == i_gs) {
+        i_rt = 0, i_b += WARPS;
+        if (i_b >= nb) i_b = warp, i_gt += i_gs, i_gs = min(GROUP, t1 - i_gt);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int p = 0; p < S; p++) issue();
+
+  pdl_wait();  // x is the previous launch's output; the weights requested above are not
+  __syncthreads();
+  float4 xn[2];  // the activations of the block this warp stages next, requested one block ahead
+  auto load_x = [&](int b) {
+    if constexpr (std::is_same<XT, float>::value) {
+      xn[0] = __ldg(reinterpret_cast<const float4 *>(x + b * 256) + lane);
+      xn[1] = __ldg(reinterpret_cast<const float4 *>(x + b * 256 + 128) + lane);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 2; i++) {
+        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(x + b * 256 + 128 * i) + lane);
+        xn[i] = make_float4(__uint_as_float(v.x << 16), __uint_as_float(v.x & 0xFFFF0000u), __uint_as_float(v.y << 16), __uint_as_float(v.y & 0xFFFF0000u));
+      }
+    }
+  };
+  if (warp < nb) load_x(warp);
+
+  // One unit: rows g, g+8 of one tile x one run of 256 k, out of ring slot `sb`.  Sub-block s = 8h + 2q + u is
+  // bytes 16 s .. 16 s + 15 of the row's 256; lane t takes its word t.  An e4m3 code c becomes the f16 with the
+  // bits sign(c) << 15 | (c & 0x7F) << 7, which is the code's value / 256 for normal and subnormal codes alike
+  // (exact); the 256 goes into the block scale.
+  auto unit = [&](uint32_t sb, int r0, int b, float up, float (&vr)[2]) {
+    uint32_t wq[2][16];
+#pragma unroll
+    for (int r = 0; r < 2; r++) {
+      const uint32_t blk = sb + (g + 8 * r) * F8_PITCH + 4 * t;
+#pragma unroll
+      for (int s = 0; s < 16; s++) wq[r][s] = lds32(blk + 16 * s);
+    }
+    __syncwarp();  // the slot is free again
+    issue();
+    // both rows of the tile lie in one row block (the launcher checks bR % 16 == 0)
+    const float *srow = scale + (size_t)(r0 / bR) * scols;
+    vr[0] = vr[1] = 0.f;
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};  // u = 0 / u = 1 chains
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int s = 8 * h + 2 * q + u;
+          uint32_t a[4];
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            const uint32_t p02 = __byte_perm(wq[r][s], 0u, 0x2404), p13 = __byte_perm(wq[r][s], 0u, 0x3414);  // codes in the high bytes
+            a[r] = and_or(p02, 0x80008000u, (p02 >> 1) & 0x3F803F80u);
+            a[2 + r] = and_or(p13, 0x80008000u, (p13 >> 1) & 0x3F803F80u);
+          }
+          const uint2 bh = lds64(pb[q][u] + h * (8 * SL::SUB_BYTES));
+          if (u == 0)
+            mma16816(d0, a[0], a[1], a[2], a[3], bh.x, bh.y);
+          else
+            mma16816(d1, a[0], a[1], a[2], a[3], bh.x, bh.y);
+        }
+      }
+      // lane (g, t): d0[0] + d0[1] = row g, sub-block 8h+2t; d1[0] + d1[1] = row g, sub-block 8h+2t+1; [2], [3]
+      // the same for row g+8.  Both sub-blocks lie in elements 256 b + 128 h + 32 t .. + 31: one column block
+      const float sc = __ldg(srow + (b * 256 + 128 * h + 32 * t) / bC) * 256.f;
+#pragma unroll
+      for (int r = 0; r < 2; r++) vr[r] += sc * ((d0[2 * r] + d0[2 * r + 1]) + (d1[2 * r] + d1[2 * r + 1]));
+    }
+    vr[0] *= up, vr[1] *= up;
+  };
+
+  int slot = 0, parity = 0;
+  for (int gt = t0; gt < t1; gt += GROUP, parity ^= 1) {
+    const int gs = min(GROUP, t1 - gt);
+    const uint32_t red_g = red_lane + parity * RED_PARITY;
+    for (int b = warp; b < nb; b += WARPS) {
+      // this block's activations into the warp's slab; the next block's are requested meanwhile
+      const float4 xv[2] = {xn[0], xn[1]};
+      {
+        const int bn = b + WARPS < nb ? b + WARPS : warp;
+        if (b + WARPS < nb || gt + GROUP < t1) load_x(bn);
+      }
+      __syncwarp();  // every lane is done reading the previous block's slab
+      const float up = stage_block<16>(xv, slab, lane);
+      __syncwarp();
+      for (int rt = 0; rt < gs; rt++) {
+        cp_async_wait<S - 1>();  // this lane's granules of the tile have landed ...
+        __syncwarp();            // ... and so have the other lanes'
+        const uint32_t sb = ring + slot * F8_TILE_BYTES;
+        slot = (slot + 1) & (S - 1);
+        float vr[2];
+        unit(sb, min((gt + rt) * ROWS, N - ROWS), b, up, vr);
+        // the warp's first block of a group overwrites what an earlier group left behind
+        const uint32_t ra = red_g + rt * (32 * 8);
+        float2 o = make_float2(0.f, 0.f);
+        if (b != warp) asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(o.x), "=f"(o.y) : "r"(ra));
+        asm volatile("st.shared.v2.f32 [%0], {%1,%2};\n" ::"r"(ra), "f"(o.x + vr[0]), "f"(o.y + vr[1]));
+      }
+    }
+    __syncthreads();  // also orders this group's reads of red[parity] before its reuse two groups on
+    for (int i = threadIdx.x; i < gs * ROWS; i += WARPS * 32) {
+      const int rt = i >> 4, row = i & 15, gg = row & 7, hi = row >> 3;
+      float v = 0.f;
+#pragma unroll
+      for (int wq = 0; wq < WARPS; wq++) {
+        if (wq >= nb) break;  // a warp without a K block never wrote its part
+        const float2 *p = &red[parity][(wq * GROUP + rt) * 32 + gg * 4];
+#pragma unroll
+        for (int tt = 0; tt < 4; tt++) v += hi ? p[tt].y : p[tt].x;
+      }
+      const int orow = min((gt + rt) * ROWS, N - ROWS) + row;
+      st_act(out, orow, v);
+    }
+  }
+  cp_async_wait<0>();
+}
+
 // ------------------------------------------------------------------------------------ int4 (GPTQ / AWQ), one row of x
 //
 // The canonical 4-bit layout (codes u32 (N, K/8), nibble j of word c = element 8c + j; scales / zeros f32
@@ -1800,6 +1981,44 @@ int int4_gemv_fast(const void *x, const uint32_t *codes, const float *s, const f
                       s, z, (__nv_bfloat16 *)y + (size_t)m * N, N, K, G);
     if (rc) return rc;
     if (int l = launched("int4_gemv (decode)")) return l;
+  }
+  return 1;
+}
+
+// One to a few activation rows against block-scaled e4m3 weights: a pass of the one-row kernel per row (bf16
+// up to two rows, f32 up to 64: as for int4).  Returns 1 if launched, 0 if the shape is not covered.
+int g_fp8_fast_max_f32 = 64, g_fp8_fast_max_bf16 = 2;  // LIGHT_B200_FP8_FAST_MAX_M (tuning knob, both)
+int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR, int bC,
+                  cudaStream_t st) {
+  static bool knob = false;
+  if (!knob) {
+    if (const char *e = getenv("LIGHT_B200_FP8_FAST_MAX_M")) g_fp8_fast_max_f32 = g_fp8_fast_max_bf16 = atoi(e);
+    knob = true;
+  }
+  if (act_dtype != LB200_F32 && act_dtype != LB200_BF16) return 0;
+  if (M < 1 || M > (act_dtype == LB200_F32 ? g_fp8_fast_max_f32 : g_fp8_fast_max_bf16)) return 0;
+  if (K % 256 || bC % 32 || bR % 16 || N < ROWS || N % bR || K % bC || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
+  static bool attr_done = false;
+  if (!attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(fp8_gemv_mma_kernel<F8_STAGES, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * F8_STAGES * F8_TILE_BYTES);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(fp8_gemv_mma_kernel<F8_STAGES, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * F8_STAGES * F8_TILE_BYTES);
+    if (e != cudaSuccess) return fail((int)e, "light_b200: fp8_block_gemv (decode): %s", cudaGetErrorString(e));
+    attr_done = true;
+  }
+  const int tiles = (N + ROWS - 1) / ROWS;
+  const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
+  const size_t dyn = (size_t)WARPS * F8_STAGES * F8_TILE_BYTES;
+  for (int m = 0; m < M; m++) {
+    int rc;
+    if (act_dtype == LB200_F32)
+      rc = launch_pdl(fp8_gemv_mma_kernel<F8_STAGES, float>, grid, dyn, st, (const float *)x + (size_t)m * K, w, scale, (float *)y + (size_t)m * N, N, K,
+                      bR, bC);
+    else
+      rc = launch_pdl(fp8_gemv_mma_kernel<F8_STAGES, __nv_bfloat16>, grid, dyn, st, (const __nv_bfloat16 *)x + (size_t)m * K, w, scale,
+                      (__nv_bfloat16 *)y + (size_t)m * N, N, K, bR, bC);
+    if (rc) return rc;
+    if (int l = launched("fp8_block_gemv (decode)")) return l;
   }
   return 1;
 }

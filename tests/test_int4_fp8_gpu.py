@@ -195,3 +195,27 @@ def test_int4_one_row_tensor_core_kernel(cuda, oracle, N, K, G):
         assert max_rel(got.float().cpu().numpy(), xb.float().numpy().astype(np.float64) @ deq.T) <= 3e-2
     big = torch.randn(1, K, generator=g) * 1e6  # beyond f16 range: the exact power-of-two prescale
     assert rel_l2(ops.MatMulInt4(big.to(cuda), w).cpu().numpy(), big.numpy().astype(np.float64) @ deq.T) <= 1e-5
+
+
+@pytest.mark.parametrize("N,K,bR,bC", [(384, 7168, 128, 128), (128, 256, 128, 128), (64, 2048, 16, 32), (4096, 512, 128, 256)])
+def test_fp8_one_row_tensor_core_kernel(cuda, oracle, N, K, bR, bC):
+    """The one-row decode kernel for block-scaled e4m3: every code value (subnormals, both zeros) through the
+    bit-shift decode, one to 28 runs of 256 k, block shapes down to 16 x 32; f32 rows against the 1e-4 bound of
+    ops/fp8_block_test.go, bf16 rows against 3e-2."""
+    rng = np.random.Generator(np.random.Philox(811))
+    legal = np.array([c for c in range(256) if (c & 0x7F) != 0x7F], np.uint8)
+    codes = torch.from_numpy(legal[rng.integers(0, legal.size, size=(N, K))])
+    scale = torch.from_numpy(rng.uniform(1e-4, 2.1e-3, size=(N // bR, K // bC)).astype(np.float32))
+    deq = oracle.fp8_block_dequant(codes.numpy(), scale.numpy(), bR, bC).astype(np.float64)
+    g = torch.Generator().manual_seed(812)
+    for M in (1, 2, 9):
+        x = torch.randn(M, K, generator=g)
+        got = ops.MatMulF8Block(x.to(cuda), codes.to(cuda), scale.to(cuda), bR, bC)
+        assert torch.equal(got, ops.MatMulF8Block(x.to(cuda), codes.to(cuda), scale.to(cuda), bR, bC))
+        want = x.numpy().astype(np.float64) @ deq.T
+        assert max_rel(got.cpu().numpy(), want) <= 1e-4 and rel_l2(got.cpu().numpy(), want) <= 1e-5, (M, rel_l2(got.cpu().numpy(), want))
+    for M in (1, 2):
+        xb = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        got = ops.MatMulF8Block(xb.to(cuda), codes.to(cuda), scale.to(cuda), bR, bC)
+        assert got.dtype == torch.bfloat16
+        assert max_rel(got.float().cpu().numpy(), xb.float().numpy().astype(np.float64) @ deq.T) <= 3e-2
