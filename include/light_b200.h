@@ -311,6 +311,25 @@ LB200_API int light_b200_embedding_q(int ggml_type, const void *table, const int
 LB200_API int light_b200_int4_repack(const void *qweight, const void *qzeros, const float *scales, void *codes, float *scales_out,
                                      float *zeros_out, int N, int K, int group, int layout, int device, void *stream);
 
+/* Device-side routing.  The reference routes DeepSeek-style models on the host (models/deepseek_route.go:27-133)
+ * and sorts pairs with TopK + Sort + count + scan launches (ops/moe.go:24-99, kernels/cuda/src/moe.cu:28-42).
+ *
+ * moe_route_sigmoid: router logits (T, E) and an optional per-expert bias (E) -> ids (T, topk) I64 and weights
+ * (T, topk) F32: scores = sigmoid(logit) in f64, choice = score + bias, stable descending top-k of the
+ * choices (ties: the lower expert id), weights = the unbiased scores, divided by (their sum + 1e-20) when
+ * norm_topk.  E <= 1024, topk <= 32.
+ *
+ * moe_sort_pairs: ids (M) I64 -> counts i32 (E), offsets i32 (E + 1), sorted_pairs / sorted_expts I64 (M): pair
+ * ids in expert order, pairs of one expert ascending (ops.MoERouteFromIDs, ops/moe.go:73-99, plus the
+ * counts / offsets that light_b200_moe_gemm* otherwise compute).  scratch: M + ceil(M / 1024) * E int32.  An id
+ * outside [0, E) is treated as expert 0 and reported by light_b200_moe_route_status (synchronises).  The first
+ * call on a device must not be inside stream capture. */
+LB200_API int light_b200_moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E,
+                                           int topk, int norm_topk, int device, void *stream);
+LB200_API int light_b200_moe_sort_pairs(const int64_t *ids, int32_t *counts, int32_t *offsets, int64_t *sorted_pairs,
+                                        int64_t *sorted_expts, int32_t *scratch, int64_t M, int E, int device, void *stream);
+LB200_API int light_b200_moe_route_status(int device);
+
 /* INT8 weights x INT8 activations.  Registry key {matmul_w8a8, CUDA, F32} (reference ops.MatMulW8A8,
  * ops/matmul_w8a8.go:13-120): x f32 (M, K), wq int8 (N, K), ws f32 (N) -> out f32 (M, N).  The activation
  * rows are quantised on the device exactly as QuantizeRowsInt8 does (scale = amax / 127, round half to even,

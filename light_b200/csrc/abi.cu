@@ -435,6 +435,40 @@ int light_b200_matmul_w8a8(const float *x, const int8_t *wq, const float *ws, fl
   return matmul_w8a8(x, wq, ws, out, xq_scratch, xs_scratch, M, N, K, (cudaStream_t)stream);
 }
 
+int light_b200_moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E, int topk,
+                                 int norm_topk, int device, void *stream) {
+  if (T < 0 || E < 1 || E > 1024 || topk < 1 || topk > E || topk > 32)
+    return fail(LB200_E_SHAPE, "light_b200: moe_route_sigmoid: T=%d E=%d (at most 1024) topk=%d (at most 32)", T, E, topk);
+  if (T == 0) return 0;
+  REQUIRE_PTR(logits, "moe_route_sigmoid");
+  REQUIRE_PTR(ids, "moe_route_sigmoid");
+  REQUIRE_PTR(weights, "moe_route_sigmoid");
+  if (int rc = bind(device)) return rc;
+  return moe_route_sigmoid(logits, bias, ids, weights, T, E, topk, norm_topk, (cudaStream_t)stream);
+}
+
+int light_b200_moe_sort_pairs(const int64_t *ids, int32_t *counts, int32_t *offsets, int64_t *sorted_pairs, int64_t *sorted_expts,
+                              int32_t *scratch, int64_t M, int E, int device, void *stream) {
+  if (M < 0 || M > 0x7fffffffLL || E < 1 || E > 1024) return fail(LB200_E_SHAPE, "light_b200: moe_sort_pairs: M=%lld E=%d (at most 1024)", (long long)M, E);
+  REQUIRE_PTR(counts, "moe_sort_pairs");
+  REQUIRE_PTR(offsets, "moe_sort_pairs");
+  if (M > 0) {
+    REQUIRE_PTR(ids, "moe_sort_pairs");
+    REQUIRE_PTR(sorted_pairs, "moe_sort_pairs");
+    REQUIRE_PTR(sorted_expts, "moe_sort_pairs");
+    REQUIRE_PTR(scratch, "moe_sort_pairs");
+  }
+  if (int rc = bind(device)) return rc;
+  return moe_sort_pairs(ids, counts, offsets, sorted_pairs, sorted_expts, scratch, M, E, (cudaStream_t)stream);
+}
+
+int light_b200_moe_route_status(int device) {
+  if (int rc = bind(device)) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail((int)e, "light_b200: moe_route_status: %s", cudaGetErrorString(e));
+  return moe_route_status();
+}
+
 int light_b200_rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype, int64_t rows,
                        int cols, float eps, int device, void *stream) {
   if (int rc = bind(device)) return rc;

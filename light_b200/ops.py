@@ -395,6 +395,43 @@ def MoERoute(probs: torch.Tensor, topk: int, normalize: bool) -> MoERouting:
     return MoERouteFromIDs(ids, vals.contiguous(), T, topk)
 
 
+def MoERouteSigmoid(logits: torch.Tensor, bias: Optional[torch.Tensor], topk: int, norm_topk: bool = True, E_sort: Optional[int] = None) -> MoERouting:
+    """The DeepSeek-V3 router (models/deepseek_route.go:30-133, sigmoid branch, one group) and the expert sort of
+    ops.MoERouteFromIDs (ops/moe.go:73-99), both on the device: logits (T, E) F32, bias (E) F32 or None."""
+    if logits.dim() != 2 or logits.dtype != torch.float32:
+        raise ValueError(f"moe_route: logits must be (T, E) F32, got {tuple(logits.shape)} {logits.dtype}")
+    T, E = logits.shape
+    if topk < 1 or topk > E:
+        raise ValueError(f"moe_route: topk {topk} out of range [1, {E}]")
+    dev = _dev(logits, "MoERouteSigmoid")
+    ids = torch.empty((T, topk), dtype=torch.int64, device=logits.device)
+    w = torch.empty((T, topk), dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.lib().light_b200_moe_route_sigmoid(_ptr(logits.contiguous()), _ptr(None if bias is None else bias.contiguous()), _ptr(ids),
+                                                       _ptr(w), T, E, topk, int(norm_topk), dev, _stream(dev)))
+    sp, se, _, _ = MoESortPairs(ids.reshape(-1), E)
+    return MoERouting(ids, w.reshape(-1), sp, se)
+
+
+def MoESortPairs(ids: torch.Tensor, E: int):
+    """Expert-sorted pairs with their counts and offsets: (sorted_pairs, sorted_expts, counts, offsets)."""
+    if ids.dtype != torch.int64 or ids.dim() != 1:
+        raise ValueError(f"moe_sort_pairs: ids must be 1-D I64, got {ids.dtype} {tuple(ids.shape)}")
+    dev = _dev(ids, "MoESortPairs")
+    M = ids.numel()
+    sp, se = torch.empty_like(ids), torch.empty_like(ids)
+    counts = torch.empty(E, dtype=torch.int32, device=ids.device)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=ids.device)
+    scratch = torch.empty(M + (M + 1023) // 1024 * E + 1, dtype=torch.int32, device=ids.device)
+    _lib.check(_lib.lib().light_b200_moe_sort_pairs(_ptr(ids.contiguous()), _ptr(counts), _ptr(offsets), _ptr(sp), _ptr(se), _ptr(scratch), M, E, dev,
+                                                    _stream(dev)))
+    return sp, se, counts, offsets
+
+
+def moe_route_status(device_index: int = 0) -> int:
+    """1 if an expert id outside [0, E) ever reached MoESortPairs on this device (synchronises)."""
+    return _lib.lib().light_b200_moe_route_status(device_index)
+
+
 def _moe_dispatch(op: str, key_dtype: int, quant: bool, inp: torch.Tensor, weights, wshape, routing: MoERouting,
                   topk_weights: Optional[torch.Tensor], topk: int, out_dtype: torch.dtype, f8=None) -> torch.Tensor:
     """moeGemmDispatch (ops/moe.go:124-204)."""
