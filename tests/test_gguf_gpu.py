@@ -205,3 +205,21 @@ def test_config1_full_size_properties(cuda, oracle):
     part = ops.QTensor(raw[1000:1512].reshape(-1).to(cuda), ops.Q4_K, (512, K))
     assert rel_l2(ops.MatMulQ(x1.to(cuda), part).cpu().numpy(), y1[:, 1000:1512]) <= 1e-6
     assert rb == 2304
+
+
+def test_weights_from_a_gguf_file(cuda, oracle):
+    """gguf.File -> QTensor -> MatMulQ: the container's bytes reach the kernel untouched (gguf/reader.go:237-251,
+    models/llama_gguf.go:32-151)."""
+    import io
+
+    from light_b200 import gguf
+
+    N, K = 48, 1024
+    raw = synth.gaussian_weight(960, ops.Q4_K, N, K).numpy()
+    buf = io.BytesIO()
+    gguf.write(buf, {"general.architecture": "llama"}, [("blk.0.attn_q.weight", ops.Q4_K, (K, N), raw.tobytes())])
+    w = gguf.File(buf).qtensor("blk.0.attn_q.weight", cuda)
+    assert w.shape == (N, K) and w.ggml_type == ops.Q4_K
+    x = torch.randn(1, K, generator=torch.Generator().manual_seed(961))
+    deq = oracle.dequant(ops.Q4_K, raw.reshape(-1), N * K).reshape(N, K).astype(np.float64)
+    assert rel_l2(ops.MatMulQ(x.to(cuda), w).cpu().numpy(), x.numpy().astype(np.float64) @ deq.T) <= 1e-4
