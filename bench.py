@@ -499,6 +499,31 @@ def extras(chain, device, args):
     out["q4k_gemv_one_large_matrix"] = {"shape": [VOCAB, HID], "bytes": nbytes, "us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9,
                                         "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peak}
     del big, qt
+    # the other weight formats of the path at one activation row, on shapes of configs[3] / [4] (weights rotated so
+    # that L2 does not hold them): bytes of weights (+ scales) per launch over the time of a launch
+    out["other_formats_m1"] = {}
+    peak, _ = load_peaks()
+
+    def rotate(make, call, nbytes, key):
+        R = max(2, min(24, int(1.0e9 // nbytes) + 1))
+        ws = [make(i) for i in range(R)]
+        g = capture(lambda: [call(w) for w in ws], device)
+        ms = timed(g.replay, 5, 2, device, lambda: None) / 5 / R
+        del g
+        out["other_formats_m1"][key] = {"us": ms * 1e3, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / peak}
+
+    x4, x35, x71 = torch.randn(1, HID, device=device), torch.randn(1, 3584, device=device), torch.randn(1, 7168, device=device)
+    x35b = x35.to(torch.bfloat16)
+    rotate(lambda i: ops.QTensor(synth.gaussian_weight(7000 + i, ops.Q8_0, FFN, HID, device=device).reshape(-1), ops.Q8_0, (FFN, HID)),
+           lambda w: ops.MatMulQ(x4, w), FFN * HID // 32 * 34, "q8_0_14336x4096")
+    i4 = synth.random_int4(7100, 18944, 3584, 128)
+    i4d = [torch.from_numpy(a.view(np.int32) if a.dtype == np.uint32 else a).to(device) for a in i4]
+    rotate(lambda i: ops.Int4(i4d[0].clone(), i4d[1], i4d[2], 128), lambda w: ops.MatMulInt4(x35, w), 18944 * 3584 // 2 + 2 * 18944 * 28 * 4,
+           "int4_g128_18944x3584_f32")
+    rotate(lambda i: ops.Int4(i4d[0].clone(), i4d[1], i4d[2], 128), lambda w: ops.MatMulInt4(x35b, w),
+           18944 * 3584 // 2 + 2 * 18944 * 28 * 4, "int4_g128_18944x3584_bf16")
+    rotate(lambda i: synth.random_fp8_block(7200 + i, 4096, 7168, device=device), lambda w: ops.MatMulF8Block(x71, w[0], w[1], 128, 128),
+           4096 * 7168 + 32 * 56 * 4, "fp8_block128_4096x7168_f32")
     M = 2048
     by = {e[0]: e for e in chain.lin}
     qkv = torch.cat([by["l0.q"][5], by["l0.k"][5], by["l0.v"][5]])          # fused rows: a byte concatenation

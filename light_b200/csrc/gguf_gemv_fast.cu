@@ -1580,14 +1580,7 @@ __global__ void __launch_bounds__(WARPS * 32, 2) int4_gemv_mma_kernel(const XT *
   // of both rows (elements 64t .. 64t+63, one quantization group).  Word i gives the even MMA the f16 pairs
   // (64 + n0, 64 + n4), (64 + n2, 64 + n6) and the odd MMA (n1, n5), (n3, n7); the slab holds x in that order.
   // acc += s ((D_even + D_odd) - (64 + z) (Sx_even + Sx_odd)).
-  auto unit = [&](uint32_t sb, int r0, int b, const float2 sx, float up, float (&vr)[2]) {
-    const int grp = (b * 256 + 64 * t) / G;
-    float sc[2], zp[2];
-#pragma unroll
-    for (int r = 0; r < 2; r++) {
-      const size_t o = (size_t)(r0 + g + 8 * r) * ngrp + grp;
-      sc[r] = __ldg(scales + o), zp[r] = __ldg(zeros + o);
-    }
+  auto unit = [&](uint32_t sb, const float (&sc)[2], const float (&zp)[2], const float2 sx, float up, float (&vr)[2]) {
     const uint32_t la = sb + g * I4_PITCH + 32u * t;
     const uint4 qa0 = lds128(la + 16), qa1 = lds128(la + 32);
     const uint4 qb0 = lds128(la + 8 * I4_PITCH + 16), qb1 = lds128(la + 8 * I4_PITCH + 32);
@@ -1624,18 +1617,32 @@ __global__ void __launch_bounds__(WARPS * 32, 2) int4_gemv_mma_kernel(const XT *
         const int bn = b + WARPS < nb ? b + WARPS : warp;
         if (b + WARPS < nb || gt + GROUP < t1) load_x(bn);
       }
+      // scales and zeros of this block's row tiles: requested here, used after the staging and the first MMAs
+      float scg[GROUP][2], zpg[GROUP][2];
+      {
+        const int grp = (b * 256 + 64 * t) / G;
+#pragma unroll
+        for (int rt = 0; rt < GROUP; rt++)
+#pragma unroll
+          for (int r = 0; r < 2; r++) {
+            const size_t o = (size_t)(min((gt + min(rt, gs - 1)) * ROWS, N - ROWS) + g + 8 * r) * ngrp + grp;
+            scg[rt][r] = __ldg(scales + o), zpg[rt][r] = __ldg(zeros + o);
+          }
+      }
       __syncwarp();  // every lane is done reading the previous block's slab
       const float up = stage_block_int4(xv, slab, lane);
       __syncwarp();
       float2 sx;
       asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + SL::SX_OFF + 8 * t));
-      for (int rt = 0; rt < gs; rt++) {
+#pragma unroll
+      for (int rt = 0; rt < GROUP; rt++) {
+        if (rt >= gs) break;
         cp_async_wait<S - 1>();  // this lane's granules of the tile have landed ...
         __syncwarp();            // ... and so have the other lanes'
         const uint32_t sb = ring + slot * I4_TILE_BYTES;
         slot = (slot + 1) & (S - 1);
         float vr[2];
-        unit(sb, min((gt + rt) * ROWS, N - ROWS), b, sx, up, vr);
+        unit(sb, scg[rt], zpg[rt], sx, up, vr);
         // the warp's first block of a group overwrites what an earlier group left behind
         const uint32_t ra = red_g + rt * (32 * 8);
         float2 o = make_float2(0.f, 0.f);
