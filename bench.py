@@ -295,8 +295,10 @@ class Chain:
 class FullStep:
     """One whole decode step of configs[1] at M = 1 on the chain's weights: per layer
     add + RMSNorm -> q,k,v (one launch) -> RoPE + KV append + attention (one launch) -> o -> add + RMSNorm ->
-    SiLU(gate) * up (one launch) -> down; then the final norm and lm_head.  Every operator reads what the
-    one before it wrote (227 launches), KV length kv_len, f32 cache.  A side measurement: the headline stays
+    SiLU(gate) * up (one launch) -> down; then the final norm, lm_head and greedy sampling; the step starts with
+    the quantized embedding row of the token the previous step sampled, so replaying the graph is a generation
+    loop without a host round trip.  Every operator reads what the one before it wrote, KV length kv_len, f32
+    cache.  A side measurement: the headline stays
     the quantized linears alone."""
 
     def __init__(self, chain, kv_len=1024, fold_norms=True):
@@ -312,6 +314,7 @@ class FullStep:
         self.q, self.k, self.v = z(1, HID), z(1, NKV), z(1, NKV)
         self.logits = z(1, VOCAB)
         self.norm_w = torch.ones(HID, device=dev)
+        self.token = torch.ones(1, dtype=torch.int64, device=dev)  # the current token id: written by the step's own argmax
         self.pos = torch.tensor([kv_len - 1], dtype=torch.int64, device=dev)
         self.kb = [torch.randn(1, NKV // 128, kv_len, 128, generator=g, device=dev) for _ in range(self.layers)]
         self.vb = [torch.randn(1, NKV // 128, kv_len, 128, generator=g, device=dev) for _ in range(self.layers)]
@@ -343,6 +346,7 @@ class FullStep:
     def step_folded(self):
         L, st, d = _lib.lib(), C.c_void_p(torch.cuda.current_stream(self.c.device).cuda_stream), self.dev_index
         P = lambda t: C.c_void_p(t.data_ptr())
+        self.embed(L, d, st)
         for l in range(self.layers):
             (x1, n1), (x2, n2) = self.folded[l]
             wp, op, nn = self.qkv[l]
@@ -354,14 +358,25 @@ class FullStep:
             _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.act), P(self.by[f"l{l}.down"][5]), P(self.down), 1, HID, FFN, d, st))
         _lib.check(L.light_b200_rmsnorm(P(self.last_h), P(self.down), P(self.norm_w), P(self.xn), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
         _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.xn), P(self.by[HEAD[0]][5]), P(self.logits), 1, VOCAB, HID, d, st))
-        return 5 * self.layers + 2
+        self.sample(L, d, st)
+        return 5 * self.layers + 4
+
+    def embed(self, L, d, st):
+        """The token's row of the (tied, Q6_K) embedding table -> the residual stream."""
+        _lib.check(L.light_b200_embedding_q(ops.Q6_K, C.c_void_p(self.by[HEAD[0]][5].data_ptr()), C.c_void_p(self.token.data_ptr()),
+                                            C.c_void_p(self.h.data_ptr()), 1, VOCAB, HID, d, st))
+
+    def sample(self, L, d, st):
+        """Greedy sampling on the device: the next replay reads the token this one chose."""
+        _lib.check(L.light_b200_argmax(C.c_void_p(self.logits.data_ptr()), C.c_void_p(self.token.data_ptr()), 1, VOCAB, d, st))
 
     def step(self):
         if self.fold_norms:
             return self.step_folded()
         L, st, d = _lib.lib(), C.c_void_p(torch.cuda.current_stream(self.c.device).cuda_stream), self.dev_index
         P = lambda t: C.c_void_p(t.data_ptr())
-        n = 0
+        n = 2
+        self.embed(L, d, st)
         for l in range(self.layers):
             # the first layer normalises the embedding row; later ones add the MLP output to the stream first
             _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.down) if l else None, P(self.norm_w), P(self.h) if l else None, P(self.xn), ops.F32, 1, HID,
@@ -377,6 +392,7 @@ class FullStep:
             n += 7
         _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.down), P(self.norm_w), P(self.h), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
         _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.xn), P(self.by[HEAD[0]][5]), P(self.logits), 1, VOCAB, HID, d, st))
+        self.sample(L, d, st)
         return n + 2
 
 
@@ -477,11 +493,13 @@ def extras(chain, device, args):
         logits = []
         for key, fold in (("decode_m1_full_step_kv1024", True), ("decode_m1_full_step_kv1024_norms_as_launches", False)):
             fs = FullStep(chain, fold_norms=fold)
-            h0 = fs.h.clone()  # before the warm-up steps: they advance the residual stream in place
             g = capture(fs.step, device)
-            ms = timed(lambda: (fs.h.copy_(h0), g.replay()), steps, 3, device, lambda: None) / steps
-            out[key] = {"launches": (5 if fold else 7) * fs.layers + 2, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3),
-                        "logits_finite": bool(torch.isfinite(fs.logits).all().item())}
+            ms = timed(g.replay, steps, 3, device, lambda: None) / steps  # a closed loop: every replay decodes the token the last one sampled
+            fs.token.fill_(1)
+            g.replay()  # one step from a known token, for the comparison of the two variants
+            torch.cuda.synchronize(device)
+            out[key] = {"launches": (5 if fold else 7) * fs.layers + 4, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3),
+                        "logits_finite": bool(torch.isfinite(fs.logits).all().item()), "sampled_token": int(fs.token.item())}
             logits.append(fs.logits.clone())
             del g, fs
         d = (logits[0] - logits[1]).norm() / logits[1].norm()

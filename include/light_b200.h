@@ -375,6 +375,12 @@ LB200_API int light_b200_rmsnorm(const void *x, const void *residual, const void
 LB200_API int light_b200_rope(const void *x, const int64_t *positions, void *out, int dtype, int64_t rows, int seq_len,
                               int head_dim, double base, int device, void *stream);
 
+/* Registry key {argmax, CUDA, F32}, last axis (reference ops.Argmax, ops/argmax.go:14-60; kernels/cuda/topk.go:56-90):
+ * out[r] = index of the largest element of row r of x (rows, cols), the lowest index among equals.  With the
+ * logits as x this is greedy sampling on the device: the token id never visits the host inside a decode graph
+ * (engine/engine.go:419-565 samples on the device for the same reason). */
+LB200_API int light_b200_argmax(const float *x, int64_t *out, int64_t rows, int cols, int device, void *stream);
+
 /* p[i] += 1 for i < n (the device-side position after a step). */
 LB200_API int light_b200_inc_i64(int64_t *p, int n, int device, void *stream);
 

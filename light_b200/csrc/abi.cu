@@ -469,6 +469,11 @@ int light_b200_moe_route_status(int device) {
   return moe_route_status();
 }
 
+int light_b200_argmax(const float *x, int64_t *out, int64_t rows, int cols, int device, void *stream) {
+  if (int rc = bind(device)) return rc;
+  return argmax_rows(x, out, rows, cols, (cudaStream_t)stream);
+}
+
 int light_b200_rmsnorm(const void *x, const void *residual, const void *weight, void *sum_out, void *out, int dtype, int64_t rows,
                        int cols, float eps, int device, void *stream) {
   if (int rc = bind(device)) return rc;

@@ -95,6 +95,7 @@ int kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_
               cudaStream_t st);
 int inc_i64(int64_t *p, int n, cudaStream_t st);
 int decode_attn_status();
+int argmax_rows(const float *x, int64_t *out, long long rows, int cols, cudaStream_t st);
 int moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E, int topk, int norm_topk,
                       cudaStream_t st);
 int moe_sort_pairs(const int64_t *ids, int *counts, int *offsets, int64_t *sorted_pairs, int64_t *sorted_expts, int *scratch, long long M,

@@ -66,6 +66,41 @@ __global__ void rope_kernel(const T *__restrict__ x, const long long *__restrict
   st_act(out, o + half, x0 * sf + x1 * cf);
 }
 
+// Greedy sampling: the index of the largest element of every row (ties: the lowest index), as I64.  One CTA per
+// row; reference ops.Argmax on the last axis (ops/argmax.go:14-60, kernels/cuda/topk.go:56-90).
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *__restrict__ x, long long *__restrict__ out, int cols) {
+  __shared__ float bv[32];
+  __shared__ int bi[32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const float *row = x + (size_t)blockIdx.x * cols;
+  float v = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int j = threadIdx.x; j < cols; j += 1024) {
+    const float c = row[j];
+    if (c > v || (c == v && j < idx) || idx == 0x7fffffff) v = c, idx = j;  // NaN never wins over a number; the first element seeds
+  }
+  auto better = [](float a, int ai, float b, int bi_) { return a > b || (a == b && ai < bi_); };
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (oi != 0x7fffffff && (idx == 0x7fffffff || better(ov, oi, v, idx))) v = ov, idx = oi;
+  }
+  if ((threadIdx.x & 31) == 0) bv[threadIdx.x >> 5] = v, bi[threadIdx.x >> 5] = idx;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    v = bv[threadIdx.x], idx = bi[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+      if (oi != 0x7fffffff && (idx == 0x7fffffff || better(ov, oi, v, idx))) v = ov, idx = oi;
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = idx;
+  }
+}
+
 template <typename K, typename... Args>
 cudaError_t launch_chain(K kern, unsigned grid, unsigned block, cudaStream_t st, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -96,6 +131,15 @@ int rmsnorm(const void *x, const void *residual, const void *weight, void *sum_o
     return fail(LB200_E_DTYPE, "light_b200: rmsnorm: element type %d, want F32 or BF16", dtype);
   if (e != cudaSuccess) return fail((int)e, "light_b200: rmsnorm: %s", cudaGetErrorString(e));
   return launched("rmsnorm");
+}
+
+int argmax_rows(const float *x, int64_t *out, long long rows, int cols, cudaStream_t st) {
+  if (!x || !out) return fail(LB200_E_NULL, "light_b200: argmax: null pointer");
+  if (rows < 0 || rows > 0x7fffffffLL || cols <= 0) return fail(LB200_E_SHAPE, "light_b200: argmax: rows %lld cols %d", rows, cols);
+  if (rows == 0) return 0;
+  cudaError_t e = launch_chain(argmax_rows_kernel, (unsigned)rows, 1024u, st, x, (long long *)out, cols);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: argmax: %s", cudaGetErrorString(e));
+  return launched("argmax");
 }
 
 int rope(const void *x, const int64_t *positions, void *out, int dtype, long long rows, int seq_len, int head_dim, double base,

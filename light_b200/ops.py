@@ -646,6 +646,18 @@ def RoPE(x: torch.Tensor, positions: torch.Tensor, base: float) -> torch.Tensor:
     return out
 
 
+def Argmax(x: torch.Tensor) -> torch.Tensor:
+    """ops.Argmax over the last axis (ops/argmax.go:14-60): F32 (..., cols) -> I64 (...), lowest index among equals."""
+    if x.dtype != torch.float32 or x.dim() < 1:
+        raise ValueError(f"ops.Argmax: want an F32 tensor, got {x.dtype} {tuple(x.shape)}")
+    dev = _dev(x, "Argmax")
+    xc = x.contiguous()
+    cols = x.shape[-1]
+    out = torch.empty(x.shape[:-1], dtype=torch.int64, device=x.device)
+    _lib.check(_lib.lib().light_b200_argmax(_ptr(xc), _ptr(out), xc.numel() // cols, cols, dev, _stream(dev)))
+    return out
+
+
 def decode_attn_status(device_index: int = 0) -> int:
     """1 if a decode-attention or append launch ever saw a position outside the cache (synchronises)."""
     return _lib.lib().light_b200_decode_attn_status(device_index)

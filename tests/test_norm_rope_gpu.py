@@ -86,3 +86,15 @@ def test_rotation_inside_the_attention_launch(cuda, oracle, dt, tol, B, NH, KH, 
     assert _err(kd[:, :, n - 1], kr[:, :, 0]) <= (1e-6 if dt == torch.float32 else 1e-2)  # the key is cached rotated
     assert torch.equal(vd[:, :, n - 1].cpu(), v[:, :, 0])
     assert ops.decode_attn_status(0) == 0
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 128256), (5, 1000), (64, 33), (2, 1)])
+def test_argmax(cuda, rows, cols):
+    """ops.Argmax over the last axis: the lowest index among equal maxima."""
+    g = torch.Generator().manual_seed(130)
+    x = torch.randn(rows, cols, generator=g)
+    if cols > 40:
+        x[0, 37] = x[0, 5] = 9.0  # a tie: index 5
+    got = ops.Argmax(x.to(cuda)).cpu()
+    want = torch.tensor([int(np.flatnonzero(r == r.max())[0]) for r in x.numpy()])
+    assert torch.equal(got, want)
