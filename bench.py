@@ -123,7 +123,7 @@ class Chain:
 
     def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0, share=None, fused=True):
         self.device, self.M, self.rank, self.world = device, M, rank, world
-        self.fused = fused and M == 1
+        self.fused = fused and M <= 8  # q,k,v and gate,up as one launch each: one row, or the 2..8-row Q4_K kernel
         self._multi = {}
         self.lin = []  # (name, N_local, N, K, dt, weight bytes tensor)
         if share is not None:  # same weights, another token count
@@ -149,7 +149,7 @@ class Chain:
             mode = os.environ.get("LIGHT_B200_TP_GATHER", "fused")
             if mode in ("fused", "peer"):
                 try:
-                    fused = mode == "fused" and self.fused  # the in-launch exchange serves one activation row
+                    fused = mode == "fused" and self.fused and M == 1  # the in-launch exchange serves one activation row
                     pidx = [i for i in self.gidx if not fused or self.lin[i][0] == HEAD[0]]  # gathered by the gather kernel
                     self.peer = tp.PeerGather(device)
                     outs = self.peer.plan([(M, self.lin[i][2]) for i in pidx])
@@ -231,8 +231,8 @@ class Chain:
                                 (C.c_int32 * n)(*[self.lin[i][1] for i in idx]))
         wp, op, nn = self._multi[key]
         _, _, _, K, dt, _ = self.lin[key]
-        _lib.check(_lib.lib().light_b200_matmul_q_multi(dt, C.c_void_p(self.x[K].data_ptr()), wp, op, nn, len(idx), K,
-                                                        self.dev_index, C.c_void_p(stream)))
+        _lib.check(_lib.lib().light_b200_matmul_q_multi_rows(dt, C.c_void_p(self.x[K].data_ptr()), wp, op, nn, len(idx), self.M, K,
+                                                             self.dev_index, C.c_void_p(stream)))
 
     def plan(self, only=None):
         """The launches of one step: lists of indices into self.lin, one list per launch."""

@@ -101,6 +101,13 @@ LB200_API int light_b200_block_bytes(int ggml_type);
 LB200_API int light_b200_matmul_q(int ggml_type, const float *x, const void *w, float *out, int M, int N, int K, int device,
                         void *stream);
 
+/* light_b200_matmul_q_multi for a small batch: x f32 (M, K) against up to four quantized matrices of one type
+ * that share it, out[i] (M, n[i]) dense.  2 <= M <= 8 and Q4_K run as ONE launch (the token-column decode
+ * kernel over the joint tile list of the matrices); other row counts and types run one launch per matrix, so
+ * the call is always valid where light_b200_matmul_q is. */
+LB200_API int light_b200_matmul_q_multi_rows(int ggml_type, const float *x, const void *const *w, float *const *out,
+                                             const int32_t *n, int count, int M, int K, int device, void *stream);
+
 /* Decode-time fused launches over quantized weights, the quantized twins of the reference's
  * ops.LinearMulti / registry key gemv_multi (ops/gemv.go:21-78, kernels/cuda/gemv.go:15-94) and
  * ops.GatedLinear / gemv_gated (ops/gemv.go:80-140), which the reference applies to the q/k/v trio

@@ -74,6 +74,8 @@ SYMBOLS = {
                                       C.c_void_p]),
     "light_b200_matmul_q_multi": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                                             C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_matmul_q_multi_rows": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                                 C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_matmul_q_gated": (C.c_int, [C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                             C.c_int, C.c_int, C.c_void_p]),
     "light_b200_matmul_q_fused": (C.c_int, [C.c_int, C.c_void_p, C.POINTER(NormArgs), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),

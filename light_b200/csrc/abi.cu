@@ -199,6 +199,31 @@ int light_b200_matmul_q_multi(int t, const float *x, const void *const *w, float
   return 0;
 }
 
+int light_b200_matmul_q_multi_rows(int t, const float *x, const void *const *w, float *const *out, const int32_t *n, int count,
+                                   int M, int K, int device, void *stream) {
+  if (M == 1) return light_b200_matmul_q_multi(t, x, w, out, n, count, K, device, stream);
+  const int be = block_elems(t);
+  if (!be) return fail(LB200_E_DTYPE, "light_b200: matmul_q_multi_rows: ggml type %d has no fused kernel", t);
+  if (count < 1 || count > 4) return fail(LB200_E_SHAPE, "light_b200: matmul_q_multi_rows: %d matrices, want 1..4", count);
+  if (M < 0 || K <= 0 || K % be) return fail(LB200_E_SHAPE, "light_b200: matmul_q_multi_rows: M=%d K=%d (K a multiple of %d)", M, K, be);
+  if (M == 0) return 0;
+  REQUIRE_PTR(x, "matmul_q_multi_rows");
+  REQUIRE_PTR(w, "matmul_q_multi_rows");
+  REQUIRE_PTR(out, "matmul_q_multi_rows");
+  REQUIRE_PTR(n, "matmul_q_multi_rows");
+  for (int i = 0; i < count; i++) {
+    if (n[i] <= 0) return fail(LB200_E_SHAPE, "light_b200: matmul_q_multi_rows: matrix %d has %d rows", i, n[i]);
+    if (!w[i] || !out[i]) return fail(LB200_E_NULL, "light_b200: matmul_q_multi_rows: null pointer for matrix %d", i);
+  }
+  if (!aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: matmul_q_multi_rows: x must be 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  const int took = gguf_gemv_tok_multi(t, x, w, out, n, count, M, K, (cudaStream_t)stream);
+  if (took != 0) return took == 1 ? 0 : took;
+  for (int i = 0; i < count; i++)  // other types and row counts: one launch per matrix, each (M, n[i]) dense
+    if (int rc = light_b200_matmul_q(t, x, w[i], out[i], M, n[i], K, device, stream)) return rc;
+  return 0;
+}
+
 int light_b200_matmul_q_gated(int t, const float *x, const void *wg, const void *wu, float *out, int N, int K, int act,
                               int device, void *stream) {
   if (t != LB200_Q4_K) return fail(LB200_E_DTYPE, "light_b200: matmul_q_gated: ggml type %d has no gated kernel", t);

@@ -54,6 +54,8 @@ int gguf_gemv_tp(int type, const float *x, const void *x_slots, const void *cons
                  int count, int K, void *const *out_slots, const unsigned int *step, int world, int rank, cudaStream_t st);
 int gemv_tp_status();
 int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, int N, int K, cudaStream_t st);
+int gguf_gemv_tok_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K,
+                        cudaStream_t st);
 int gguf_gemv_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int act,
                     int K, cudaStream_t st, const lb200_norm *norm = nullptr);
 // batched decode (2..64 rows): 1 = took the call, 0 = not covered, other = error

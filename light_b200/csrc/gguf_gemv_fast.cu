@@ -464,8 +464,8 @@ __device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_c
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2 *>(&v); }
 
 template <int S>
-__global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float *__restrict__ x, const uint8_t *__restrict__ w,
-                                                                    float *__restrict__ out, int M, int N, int K) {
+__global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float *__restrict__ x, const __grid_constant__ MultiArgs ma,
+                                                                    int tiles, int M, int K) {
   extern __shared__ __align__(16) unsigned char dyn[];  // [ring: WARPS x S tiles][slabs: WARPS][red: WARPS x GROUP x 32 float4]
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -480,7 +480,6 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float
   const int hdr_sh = (t & 1) * 16;
   const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
 
-  const int tiles = (N + ROWS - 1) / ROWS;
   const int t0 = (int)((uint32_t)tiles * blockIdx.x / gridDim.x), t1 = (int)((uint32_t)tiles * (blockIdx.x + 1) / gridDim.x);
   uint32_t soff[5];
 #pragma unroll
@@ -493,8 +492,9 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float
   int i_gt = t0, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0, i_slot = 0;
   auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
     if (i_gt < t1 && warp < nb) {
-      const int r0 = min((i_gt + i_rt) * ROWS, N - ROWS);
-      const uint8_t *base = w + ((size_t)r0 * row_bytes + (uint32_t)i_b * 144u);
+      int j, r0;
+      resolve_tile(ma, i_gt + i_rt, j, r0);  // up to four matrices that share x form one tile list
+      const uint8_t *base = ma.w[j] + ((size_t)r0 * row_bytes + (uint32_t)i_b * 144u);
       const uint32_t dst = ring + i_slot * Q4K_TILE_BYTES + lane * 16;
 #pragma unroll
       for (int i = 0; i < 4; i++) cp_async16(dst + i * 512, base + soff[i]);
@@ -630,7 +630,11 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float
         asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(p) : "r"(a + wq * (GROUP * 512)));
         v += p;
       }
-      if (tok < M) out[(size_t)tok * N + min((gt + rt) * ROWS, N - ROWS) + row] = v;
+      if (tok < M) {
+        int j, r0;
+        resolve_tile(ma, gt + rt, j, r0);
+        ma.out[j][(size_t)tok * ma.n[j] + r0 + row] = v;
+      }
     }
   }
   cp_async_wait<0>();
@@ -2048,14 +2052,36 @@ int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, in
     const int mm = M - m0 < TOK ? M - m0 : TOK;
     const float *xm = x + (size_t)m0 * K;
     float *om = out + (size_t)m0 * N;
+    MultiArgs a = {};
+    a.w[0] = (const uint8_t *)w, a.out[0] = om, a.n[0] = N, a.tend[0] = tiles, a.count = 1;
     int rc = type == LB200_Q4_K
-                 ? launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, xm, (const uint8_t *)w, om, mm, N, K)
+                 ? launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, xm, a, tiles, mm, K)
                  : launch_pdl(q6k_gemv_tok_kernel<Q6K_TOK_STAGES>, grid, (size_t)Q6K_TOK_SMEM, st, xm, (const uint8_t *)w, om, mm, N, K);
     if (rc) return rc;
     rc = launched("matmul_q (decode, 2-8 rows)");
     if (rc) return rc;
   }
   return 1;
+}
+
+// 2 .. 8 activation rows against up to four Q4_K matrices that share them (q, k, v; gate, up), one launch:
+// ops.LinearMulti for a small batch.  Returns 1 if launched, 0 if the shape is not covered.
+int gguf_gemv_tok_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K,
+                        cudaStream_t st) {
+  if (type != LB200_Q4_K || M < 2 || M > TOK || count < 1 || count > 4 || K % 256 || ((uintptr_t)x & 15)) return 0;
+  MultiArgs a = {};
+  int tiles = 0;
+  for (int i = 0; i < count; i++) {
+    if (n[i] < ROWS || ((uintptr_t)w[i] & 15)) return 0;
+    tiles += (n[i] + ROWS - 1) / ROWS;
+    a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
+  }
+  a.count = count;
+  const unsigned grid = (unsigned)(tiles < g_sms * 2 ? tiles : g_sms * 2);
+  int rc = launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, a, tiles, M, K);
+  if (rc) return rc;
+  rc = launched("matmul_q_multi (2-8 rows)");
+  return rc ? rc : 1;
 }
 
 // 9 .. 32 activation rows per pass (more rows: passes of 32) against one Q4_K matrix: eight row tiles per CTA,

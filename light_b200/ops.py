@@ -156,12 +156,16 @@ def _one_row(x: torch.Tensor, op: str) -> int:
 
 
 def MatMulQMulti(x: torch.Tensor, ws: Sequence[QTensor], outs: Optional[Sequence[torch.Tensor]] = None) -> list:
-    """The quantized twin of ops.LinearMulti (ops/gemv.go:21-78): one f32 activation row against up to
-    four quantized weights of one type that share K (the q/k/v trio, gate and up), in one launch.
-    Returns one (..., N_i) f32 tensor per weight (written into `outs` when given)."""
+    """The quantized twin of ops.LinearMulti (ops/gemv.go:21-78): f32 activations (one row, or a small batch
+    (M, K)) against up to four quantized weights of one type that share K (the q/k/v trio, gate and up), in one
+    launch for one row and for 2..8 rows of Q4_K.  Returns one (..., N_i) f32 tensor per weight (written into
+    `outs` when given)."""
     if not 1 <= len(ws) <= 4:
         raise ValueError(f"MatMulQMulti: {len(ws)} weights, want 1..4")
-    K = _one_row(x, "MatMulQMulti")
+    if x.dtype != torch.float32:
+        raise ValueError(f"MatMulQMulti: x must be F32, got {x.dtype}")
+    K = x.shape[-1]
+    M = x.numel() // K
     for i, w in enumerate(ws):
         if len(w.shape) != 2 or w.shape[1] != K or w.ggml_type != ws[0].ggml_type or w.device != x.device:
             raise ValueError(f"MatMulQMulti: weight {i} must be (N, {K}) of type {ws[0].ggml_type} on {x.device}")
@@ -174,7 +178,9 @@ def MatMulQMulti(x: torch.Tensor, ws: Sequence[QTensor], outs: Optional[Sequence
     wp = (C.c_void_p * n)(*[w.data.data_ptr() for w in ws])
     op = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
     nn = (C.c_int32 * n)(*[w.shape[0] for w in ws])
-    _lib.check(_lib.lib().light_b200_matmul_q_multi(ws[0].ggml_type, _ptr(xc), wp, op, nn, n, K, dev, _stream(dev)))
+    if M > 8:
+        ensure_workspace(dev, M * K * 2)
+    _lib.check(_lib.lib().light_b200_matmul_q_multi_rows(ws[0].ggml_type, _ptr(xc), wp, op, nn, n, M, K, dev, _stream(dev)))
     return list(outs)
 
 

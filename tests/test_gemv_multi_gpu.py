@@ -82,7 +82,9 @@ def test_multi_and_gated_errors(cuda):
     with pytest.raises(ValueError):
         ops.MatMulQMulti(x, [w] * 5)
     with pytest.raises(ValueError):
-        ops.MatMulQMulti(torch.randn(2, K, device=cuda), [w])
+        ops.MatMulQMulti(x.to(torch.bfloat16), [w])
+    with pytest.raises(ValueError):
+        ops.MatMulQMulti(torch.randn(2, K + 256, device=cuda), [w])
     w6 = _qt(synth.random_blocks(71, ops.Q6_K, 32, K), ops.Q6_K, (32, K), cuda)
     with pytest.raises(ops.Light200Error):
         ops.MatMulQGated(x, w6, w6)
@@ -119,3 +121,20 @@ def test_norm_folded_into_the_launch(cuda, oracle, K):
     gl, up = y @ deqs[1].T, y @ du.T
     assert rel_l2(got.cpu().numpy(), gl / (1 + np.exp(-gl)) * up) <= 1e-4
     assert torch.equal(total.cpu(), x + r)
+
+
+@pytest.mark.parametrize("M", [2, 5, 8, 9])
+def test_multi_for_a_small_batch(cuda, oracle, M):
+    """LinearMulti for 2..8 rows of x as one launch of the token-column kernel (q, k, v heights of configs[1] scaled
+    down, a ragged one among them); 9 rows fall back to one launch per matrix: same results either way."""
+    K = 2048
+    ns = (256, 64, 72)
+    raws = [synth.gaussian_weight(530 + i, ops.Q4_K, n, K).numpy() for i, n in enumerate(ns)]
+    ws = [ops.QTensor(torch.from_numpy(r.reshape(-1)).to(cuda), ops.Q4_K, (n, K)) for r, n in zip(raws, ns)]
+    x = torch.randn(M, K, generator=torch.Generator().manual_seed(540 + M))
+    outs = ops.MatMulQMulti(x.to(cuda), ws)
+    for o, w, r, n in zip(outs, ws, raws, ns):
+        assert o.shape == (M, n)
+        assert torch.equal(o, ops.MatMulQ(x.to(cuda), w))  # the same kernel arithmetic, tile by tile
+        deq = oracle.dequant(ops.Q4_K, r.reshape(-1), n * K).reshape(n, K).astype(np.float64)
+        assert rel_l2(o.cpu().numpy(), x.numpy().astype(np.float64) @ deq.T) <= 1e-3
