@@ -665,14 +665,14 @@ struct DtCfg {
 
 template <int NG>
 __global__ void __launch_bounds__(DT_THREADS, 2) q4k_decode_tile_kernel(const float *__restrict__ x,
-                                                                                     const uint8_t *__restrict__ w,
-                                                                                     float *__restrict__ out, int M, int N, int K) {
+                                                                                     const __grid_constant__ MultiArgs ma, int tiles,
+                                                                                     int M, int K) {
   using Cfg = DtCfg<NG>;
   constexpr int S = DT_STAGES;
   extern __shared__ __align__(16) unsigned char dyn[];  // [ring: 8 warps x S tiles][x buffer 0][x buffer 1]
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int nb = K >> 8, tiles = (N + ROWS - 1) / ROWS;
+  const int nb = K >> 8;
   const int KS = gridDim.y, rank = blockIdx.y;
   const int b0 = nb * rank / KS, b1 = nb * (rank + 1) / KS, nloc = b1 - b0;
   // CTAs of one K run start at different blocks of it: otherwise all of them ask L2 for the same lines of x
@@ -718,7 +718,9 @@ __global__ void __launch_bounds__(DT_THREADS, 2) q4k_decode_tile_kernel(const fl
     // ---- consumers: warp w owns row tile 8 blockIdx.x + w over blocks b0 .. b1
     const int tile = blockIdx.x * DT_CW + warp;
     const bool live = tile < tiles;
-    const int r0 = min(tile * ROWS, N - ROWS);
+    int wj = 0, r0 = 0;
+    if (live) resolve_tile(ma, tile, wj, r0);  // up to four matrices that share x form one tile list
+    const uint8_t *w = ma.w[wj];
     const uint32_t row_bytes = (uint32_t)nb * 144u;
     const uint32_t ring = sbase + warp * (S * Q4K_TILE_BYTES);
     const bool hdr_hi = t >= 2;
@@ -848,7 +850,11 @@ __global__ void __launch_bounds__(DT_THREADS, 2) q4k_decode_tile_kernel(const fl
       } else {
         asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(a));
       }
-      if (tok < M && tile < tiles) out[(size_t)tok * N + min(tile * ROWS, N - ROWS) + (rr & 15)] = v;
+      if (tok < M && tile < tiles) {
+        int oj, orow;
+        resolve_tile(ma, tile, oj, orow);
+        ma.out[oj][(size_t)tok * ma.n[oj] + orow + (rr & 15)] = v;
+      }
     }
   }
   if (KS > 1) umma::cluster_sync();  // nobody leaves while a peer still reads its partials
@@ -2064,30 +2070,10 @@ int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, in
   return 1;
 }
 
-// 2 .. 8 activation rows against up to four Q4_K matrices that share them (q, k, v; gate, up), one launch:
-// ops.LinearMulti for a small batch.  Returns 1 if launched, 0 if the shape is not covered.
-int gguf_gemv_tok_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K,
-                        cudaStream_t st) {
-  if (type != LB200_Q4_K || M < 2 || M > TOK || count < 1 || count > 4 || K % 256 || ((uintptr_t)x & 15)) return 0;
-  MultiArgs a = {};
-  int tiles = 0;
-  for (int i = 0; i < count; i++) {
-    if (n[i] < ROWS || ((uintptr_t)w[i] & 15)) return 0;
-    tiles += (n[i] + ROWS - 1) / ROWS;
-    a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
-  }
-  a.count = count;
-  const unsigned grid = (unsigned)(tiles < g_sms * 2 ? tiles : g_sms * 2);
-  int rc = launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, a, tiles, M, K);
-  if (rc) return rc;
-  rc = launched("matmul_q_multi (2-8 rows)");
-  return rc ? rc : 1;
-}
-
 // 9 .. 32 activation rows per pass (more rows: passes of 32) against one Q4_K matrix: eight row tiles per CTA,
 // K split over a cluster.  Returns 1 if launched, 0 if the shape is not covered.
 template <int NG>
-static int launch_tile(const float *x, const uint8_t *w, float *out, int M, int N, int K, cudaStream_t st) {
+static int launch_tile(const float *x, const MultiArgs &ma, int tiles, int M, int K, cudaStream_t st) {
   auto kern = q4k_decode_tile_kernel<NG>;
   static bool attr_done = false;
   if (!attr_done) {
@@ -2095,7 +2081,7 @@ static int launch_tile(const float *x, const uint8_t *w, float *out, int M, int 
     if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, tiles): %s", cudaGetErrorString(e));
     attr_done = true;
   }
-  const int tiles = (N + ROWS - 1) / ROWS, nx = (tiles + DT_CW - 1) / DT_CW, nb = K >> 8;
+  const int nx = (tiles + DT_CW - 1) / DT_CW, nb = K >> 8;
   // measured on 4096 x 4096, 1024 x 4096 and 14336 x 4096: short K runs win (a CTA's start-up and its first
   // block of x are not overlapped with anything) until two CTAs per SM are resident and more wait behind them
   int ks = nx * 2 >= g_sms ? 2 : 8;
@@ -2113,7 +2099,7 @@ static int launch_tile(const float *x, const uint8_t *w, float *out, int M, int 
   attr[1].val.clusterDim.x = 1, attr[1].val.clusterDim.y = (unsigned)ks, attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, x, w, out, M, N, K);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, x, ma, tiles, M, K);
   if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, tiles): %s", cudaGetErrorString(e));
   return launched("matmul_q (decode, tiles)");
 }
@@ -2131,10 +2117,35 @@ int gguf_decode_tile(int type, const float *x, const void *w, float *out, int M,
     const int mm = M - m0 < 32 ? M - m0 : 32;
     const float *xm = x + (size_t)m0 * K;
     float *om = out + (size_t)m0 * N;
-    const int rc = mm <= 16 ? launch_tile<2>(xm, (const uint8_t *)w, om, mm, N, K, st) : launch_tile<4>(xm, (const uint8_t *)w, om, mm, N, K, st);
+    MultiArgs ma = {};
+    const int tiles = (N + ROWS - 1) / ROWS;
+    ma.w[0] = (const uint8_t *)w, ma.out[0] = om, ma.n[0] = N, ma.tend[0] = tiles, ma.count = 1;
+    const int rc = mm <= 16 ? launch_tile<2>(xm, ma, tiles, mm, K, st) : launch_tile<4>(xm, ma, tiles, mm, K, st);
     if (rc) return rc;
   }
   return 1;
+}
+
+// 2 .. 8 activation rows against up to four Q4_K matrices that share them (q, k, v; gate, up), one launch:
+// ops.LinearMulti for a small batch.  Returns 1 if launched, 0 if the shape is not covered.
+int gguf_gemv_tok_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K,
+                        cudaStream_t st) {
+  // (the eight-tiles-per-CTA kernel takes the same tile list, but measured slower on the joint lists of
+  // configs[1] at 32 rows than one launch per matrix -- 9.3 against 6.05 ms per step -- so 9..32 rows are not merged)
+  if (type != LB200_Q4_K || M < 2 || M > TOK || count < 1 || count > 4 || K % 256 || ((uintptr_t)x & 15)) return 0;
+  MultiArgs a = {};
+  int tiles = 0;
+  for (int i = 0; i < count; i++) {
+    if (n[i] < ROWS || ((uintptr_t)w[i] & 15)) return 0;
+    tiles += (n[i] + ROWS - 1) / ROWS;
+    a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
+  }
+  a.count = count;
+  const unsigned grid = (unsigned)(tiles < g_sms * 2 ? tiles : g_sms * 2);
+  int rc = launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, a, tiles, M, K);
+  if (rc) return rc;
+  rc = launched("matmul_q_multi (2-8 rows)");
+  return rc ? rc : 1;
 }
 
 // Several matrices of one type against one activation row in one launch (act == 0), or the gated
