@@ -123,7 +123,7 @@ class Chain:
 
     def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0, share=None, fused=True):
         self.device, self.M, self.rank, self.world = device, M, rank, world
-        self.fused = fused and M <= 8  # q,k,v and gate,up as one launch each: one row, or the 2..8-row Q4_K kernel
+        self.fused = fused and M <= 32  # q,k,v and gate,up as one launch each: one row, or the 2..32-row Q4_K kernels
         self._multi = {}
         self.lin = []  # (name, N_local, N, K, dt, weight bytes tensor)
         if share is not None:  # same weights, another token count

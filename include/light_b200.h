@@ -102,8 +102,8 @@ LB200_API int light_b200_matmul_q(int ggml_type, const float *x, const void *w, 
                         void *stream);
 
 /* light_b200_matmul_q_multi for a small batch: x f32 (M, K) against up to four quantized matrices of one type
- * that share it, out[i] (M, n[i]) dense.  2 <= M <= 8 and Q4_K run as ONE launch (the token-column decode
- * kernel over the joint tile list of the matrices); other row counts and types run one launch per matrix, so
+ * that share it, out[i] (M, n[i]) dense.  2 <= M <= 32 and Q4_K run as ONE launch (the token-column decode
+ * kernels over the joint tile list of the matrices); other row counts and types run one launch per matrix, so
  * the call is always valid where light_b200_matmul_q is. */
 LB200_API int light_b200_matmul_q_multi_rows(int ggml_type, const float *x, const void *const *w, float *const *out,
                                              const int32_t *n, int count, int M, int K, int device, void *stream);

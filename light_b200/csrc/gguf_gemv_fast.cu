@@ -2126,13 +2126,14 @@ int gguf_decode_tile(int type, const float *x, const void *w, float *out, int M,
   return 1;
 }
 
-// 2 .. 8 activation rows against up to four Q4_K matrices that share them (q, k, v; gate, up), one launch:
-// ops.LinearMulti for a small batch.  Returns 1 if launched, 0 if the shape is not covered.
+// 2 .. 32 activation rows against up to four Q4_K matrices that share them (q, k, v; gate, up), one launch:
+// ops.LinearMulti for a small batch (the token-column kernel up to 8 rows, the eight-tiles-per-CTA kernel above:
+// q,k,v of configs[1] at 32 rows 23.4 us merged against 32.9 us as three launches; gate,up the same either way).  Returns 1 if launched, 0 if the shape is not covered.
 int gguf_gemv_tok_multi(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K,
                         cudaStream_t st) {
-  // (the eight-tiles-per-CTA kernel takes the same tile list, but measured slower on the joint lists of
-  // configs[1] at 32 rows than one launch per matrix -- 9.3 against 6.05 ms per step -- so 9..32 rows are not merged)
-  if (type != LB200_Q4_K || M < 2 || M > TOK || count < 1 || count > 4 || K % 256 || ((uintptr_t)x & 15)) return 0;
+  static int tile_multi = -1;  // LIGHT_B200_TILE_MULTI=0 (tuning knob): merge only up to 8 rows
+  if (tile_multi < 0) tile_multi = getenv("LIGHT_B200_TILE_MULTI") ? atoi(getenv("LIGHT_B200_TILE_MULTI")) : 1;
+  if (type != LB200_Q4_K || M < 2 || M > (tile_multi ? g_tile_max_m : TOK) || count < 1 || count > 4 || K % 256 || ((uintptr_t)x & 15)) return 0;
   MultiArgs a = {};
   int tiles = 0;
   for (int i = 0; i < count; i++) {
@@ -2141,6 +2142,10 @@ int gguf_gemv_tok_multi(int type, const float *x, const void *const *w, float *c
     a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
   }
   a.count = count;
+  if (M > TOK) {  // 9 .. 32 rows: the kernel with eight row tiles per CTA
+    const int rc = M <= 16 ? launch_tile<2>(x, a, tiles, M, K, st) : launch_tile<4>(x, a, tiles, M, K, st);
+    return rc ? rc : 1;
+  }
   const unsigned grid = (unsigned)(tiles < g_sms * 2 ? tiles : g_sms * 2);
   int rc = launch_pdl(q4k_gemv_tok_kernel<Q4K_TOK_STAGES>, grid, (size_t)Q4K_TOK_SMEM, st, x, a, tiles, M, K);
   if (rc) return rc;

@@ -126,7 +126,8 @@ def test_norm_folded_into_the_launch(cuda, oracle, K):
 @pytest.mark.parametrize("M", [2, 5, 8, 9, 16, 27, 32, 40])
 def test_multi_for_a_small_batch(cuda, oracle, M):
     """LinearMulti for 2..8 rows of x as one launch of the token-column kernel (q, k, v heights of configs[1] scaled
-    down, a ragged one among them); more rows fall back to one launch per matrix: same results either way."""
+    down, a ragged one among them), of the eight-tiles-per-CTA kernel for 9..32 rows; 40 rows fall back to one
+    launch per matrix: same results either way."""
     K = 2048
     ns = (256, 64, 72)
     raws = [synth.gaussian_weight(530 + i, ops.Q4_K, n, K).numpy() for i, n in enumerate(ns)]
