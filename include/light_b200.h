@@ -164,7 +164,9 @@ LB200_API int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const f
  * w(p) = topk_weights[p], or 1 when topk_weights is null.  counts (E) and offsets (E+1) are
  * int32 SCRATCH the caller provides; the call fills them (offsets = exclusive prefix sum of the
  * per-expert pair counts) and they are valid outputs afterwards.  Rows of `out` whose pair id
- * does not appear (or is outside [0, size_m)) are left untouched. */
+ * does not appear (or is outside [0, size_m)) are left untouched.  An expert id outside [0, E) never
+ * indexes anything: a negative id owns no range and its pair is skipped, an id >= E is skipped by the
+ * matmul and counted under the last expert's boundary; either is reported by light_b200_moe_route_status. */
 typedef struct lb200_moe_args {
   const void *input;          /* (rows, K) at dtype (moe_gemm) or f32 (moe_gemm_q)          */
   const void *weights;        /* (E, N, K) at dtype, or GGUF blocks of ggml_type            */
@@ -274,8 +276,9 @@ LB200_API int light_b200_moe_gemm_q(const lb200_moe_args *args, int device, void
  * (reference kernels/cuda/decode_attn.go:15-133; ops.KVAppend / ops.DecodeAttention / ops.IncrementI64,
  * ops/decode_attn.go:13-205).  `pos` is a one-element device I64: the position of the new token, so the
  * number of valid keys is pos + 1 and every launch is the same whatever the position (CUDA-graph
- * capturable, models/decode_graph.go:27-230).  A position outside [0, Cap) is clamped, nothing is written
- * outside the buffers, and light_b200_decode_attn_status reports it. */
+ * capturable, models/decode_graph.go:27-230).  With a position outside [0, Cap) nothing is appended (neither
+ * by light_b200_kv_append nor by the append inside light_b200_decode_attn), the attention runs over the cached
+ * rows of the clamped range, and light_b200_decode_attn_status reports it. */
 
 /* k, v (B, KH, 1, D) contiguous -> kbuf, vbuf (B, KH, Cap, D) at position pos[0]. */
 LB200_API int light_b200_kv_append(const void *k, const void *v, void *kbuf, void *vbuf, const int64_t *pos, int dtype,
@@ -329,8 +332,9 @@ LB200_API int light_b200_int4_repack(const void *qweight, const void *qzeros, co
  * moe_sort_pairs: ids (M) I64 -> counts i32 (E), offsets i32 (E + 1), sorted_pairs / sorted_expts I64 (M): pair
  * ids in expert order, pairs of one expert ascending (ops.MoERouteFromIDs, ops/moe.go:73-99, plus the
  * counts / offsets that light_b200_moe_gemm* otherwise compute).  scratch: M + ceil(M / 1024) * E int32.  An id
- * outside [0, E) is treated as expert 0 and reported by light_b200_moe_route_status (synchronises).  The first
- * call on a device must not be inside stream capture. */
+ * outside [0, E) is treated as expert 0 and reported by light_b200_moe_route_status (synchronises; the same
+ * word reports ids outside [0, E) seen by the grouped matmuls' offsets kernel).  The first call on a device
+ * must not be inside stream capture. */
 LB200_API int light_b200_moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E,
                                            int topk, int norm_topk, int device, void *stream);
 LB200_API int light_b200_moe_sort_pairs(const int64_t *ids, int32_t *counts, int32_t *offsets, int64_t *sorted_pairs,

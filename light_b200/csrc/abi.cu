@@ -33,6 +33,17 @@ int launched(const char *what) {
 static std::mutex g_mu;
 static bool g_ready[64];
 
+int sm_count() {
+  static std::atomic<int> sms[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int v = sms[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) return 148;
+  sms[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
+
 static int bind(int device) {
   if (device < 0 || device >= 64) return fail(LB200_E_DEVICE, "light_b200: device ordinal %d out of range", device);
   cudaError_t e = cudaSetDevice(device);
@@ -491,7 +502,10 @@ int light_b200_moe_route_status(int device) {
   if (int rc = bind(device)) return rc;
   cudaError_t e = cudaDeviceSynchronize();
   if (e != cudaSuccess) return fail((int)e, "light_b200: moe_route_status: %s", cudaGetErrorString(e));
-  return moe_route_status();
+  const int a = moe_route_status(), b = moe_bad_ids_status();
+  if (a > 1 || a < 0) return a;
+  if (b > 1 || b < 0) return b;
+  return a | b;
 }
 
 int light_b200_argmax(const float *x, int64_t *out, int64_t rows, int cols, int device, void *stream) {

@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 #include "../../include/light_b200.h"
 
 namespace lb {
@@ -13,6 +15,29 @@ namespace lb {
 int fail(int code, const char *fmt, ...);
 // Maps the launch status of the kernel just enqueued (no synchronisation).
 int launched(const char *what);
+
+// Set-up that belongs to ONE device -- the opt-in to more than 48 KB of dynamic shared memory of a kernel
+// (cudaFuncSetAttribute), the address of a __device__ symbol -- guarded per device: one process may drive
+// several GPUs through this library, from several threads.  ensure(f, want) runs f() with the calling thread's
+// current device when that device has not reached level `want` yet (levels only grow: a shared-memory size).
+struct DeviceOnce {
+  std::mutex mu;
+  size_t level[64] = {};
+  template <typename F>
+  cudaError_t ensure(F &&f, size_t want = 1) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lk(mu);
+    if (level[dev] >= want) return cudaSuccess;
+    e = f();
+    if (e == cudaSuccess) level[dev] = want;
+    return e;
+  }
+};
+// SMs of the calling thread's current device (looked up once per device).
+int sm_count();
 
 // Block geometry of the GGUF formats with a fused kernel (reference dtype/dtype.go:53-60).
 __host__ __device__ constexpr int block_elems(int t) {
@@ -103,6 +128,7 @@ int moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, floa
 int moe_sort_pairs(const int64_t *ids, int *counts, int *offsets, int64_t *sorted_pairs, int64_t *sorted_expts, int *scratch, long long M,
                    int E, cudaStream_t st);
 int moe_route_status();
+int moe_bad_ids_status();  // 0 / 1, or a CUDA error code (> 1)
 int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR, int bC,
                   cudaStream_t st);
 // one-row tensor-core decode kernel for canonical int4 weights: 1 = took the call, 0 = not covered, other = error

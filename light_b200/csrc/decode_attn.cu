@@ -105,7 +105,10 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
   float *wpart = sm, *cpart = sm + Cfg::WPART;
   pdl_wait();  // q, k_new, v_new are the previous launch's output; pos is older
   long long pos = a.pos[0];
-  if (pos < 0 || pos >= a.Cap) {
+  // A position outside the cache: reported, nothing is appended (as kv_append_kernel), and the launch attends
+  // over the cached rows of the clamped range, so that append-inside stays equal to append-then-attend.
+  const bool in_range = pos >= 0 && pos < a.Cap;
+  if (!in_range) {
     if (threadIdx.x == 0) atomicOr(&g_attn_status, 1u);
     pos = pos < 0 ? 0 : a.Cap - 1;
   }
@@ -115,8 +118,8 @@ __global__ void __launch_bounds__(DA_THREADS, 1) decode_attn_kernel(AttnArgs a) 
   const int j0 = start + rank * chunk, j1 = min(n, j0 + chunk);
   const T *Kb = static_cast<const T *>(a.kbuf) + (size_t)bkh * a.Cap * D + lane * PER;
   const T *Vb = static_cast<const T *>(a.vbuf) + (size_t)bkh * a.Cap * D + lane * PER;
-  const T *kn = a.k_new ? static_cast<const T *>(a.k_new) + (size_t)bkh * D + lane * PER : nullptr;
-  const T *vn = a.k_new ? static_cast<const T *>(a.v_new) + (size_t)bkh * D + lane * PER : nullptr;
+  const T *kn = a.k_new && in_range ? static_cast<const T *>(a.k_new) + (size_t)bkh * D + lane * PER : nullptr;
+  const T *vn = a.k_new && in_range ? static_cast<const T *>(a.v_new) + (size_t)bkh * D + lane * PER : nullptr;
   // rotary embedding of q and of the new key at position pos (rotate-half pairing: dim i with i + D / 2,
   // which is lane ^ 16 here); cached keys were rotated when they were appended
   const bool roped = a.rope_k != 0.0;
@@ -376,11 +379,10 @@ template <typename T, int PER, int GH>
 int launch_attn(const AttnArgs &a, int ks, cudaStream_t st) {
   auto kern = decode_attn_kernel<T, PER, GH>;
   const size_t smem = AttnCfg<PER, GH>::smem(a.NH / a.KH);
-  static size_t smem_set = 0;
-  if (smem > smem_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static DeviceOnce smem_set;  // per instantiation and device: the largest size opted in so far
+  {
+    cudaError_t e = smem_set.ensure([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); }, smem);
     if (e != cudaSuccess) return fail((int)e, "light_b200: decode_attn: %s", cudaGetErrorString(e));
-    smem_set = smem;
   }
   cudaError_t e = launch_chain(kern, dim3((unsigned)(a.B * a.KH), (unsigned)ks), dim3(DA_THREADS), smem, (unsigned)ks, st, a);
   if (e != cudaSuccess) return fail((int)e, "light_b200: decode_attn: %s", cudaGetErrorString(e));

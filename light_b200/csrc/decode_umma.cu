@@ -303,11 +303,10 @@ __global__ void __launch_bounds__(D_THREADS, 2) decode_umma_kernel(const typenam
 template <typename Row, int NTOK, typename XT, typename OutT>
 int launch_decode(const typename Row::Ctx &ctx, const XT *x, OutT *out, int M, int N, int K, int sms, cudaStream_t st) {
   auto kern = decode_umma_kernel<Row, NTOK, XT, OutT>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DCfg<Row, NTOK>::SMEM);
+  static DeviceOnce attr_done;
+  {
+    cudaError_t e = attr_done.ensure([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DCfg<Row, NTOK>::SMEM); });
     if (e != cudaSuccess) return fail((int)e, "light_b200: decode (tcgen05): %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   // K split: the smallest cluster that gives every SM two CTAs, at most 8 and at most one per block
   const int nx = (N + DM - 1) / DM, nblk = K >> 8;

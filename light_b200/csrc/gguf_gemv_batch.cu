@@ -266,12 +266,13 @@ int gguf_gemv_batch(int type, const float *x, const void *w, float *out, int M, 
   if (type != LB200_Q4_K && type != LB200_Q6_K) return 0;
   if (type == LB200_Q4_K && ((uintptr_t)w & 15)) return 0;
   if (type == LB200_Q6_K && (((uintptr_t)w & 3) || ((size_t)(K >> 8) * 210) % 4)) return 0;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(q4k_gemv_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-    if (e == cudaSuccess) e = cudaFuncSetAttribute(q6k_gemv_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  static DeviceOnce attr_done;
+  {
+    cudaError_t e = attr_done.ensure([&] {
+      cudaError_t r = cudaFuncSetAttribute(q4k_gemv_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+      return r != cudaSuccess ? r : cudaFuncSetAttribute(q6k_gemv_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    });
     if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (batched decode): %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   const int tiles = (N + ROWS - 1) / ROWS;
   const int rt = tiles >= 148 * 6 ? 2 : 1;

@@ -1872,7 +1872,7 @@ int launch_pdl(void (*kern)(Args...), unsigned grid, size_t dyn_smem, cudaStream
   return 0;
 }
 
-int g_sms = 148;       // SMs of the bound device
+#define g_sms (sm_count())  // SMs of the calling thread's current device (every entry point binds it first)
 int g_waves = 2;       // LIGHT_B200_GEMV_WAVES: CTAs per SM of the persistent kernels' grids (1 or 2)
 int g_q4k_stages = 4;  // LIGHT_B200_Q4K_STAGES: ring depth (2 or 4)
 constexpr size_t MAX_DYN_SMEM = 96 * 1024;  // keeps two launches resident per SM
@@ -1882,9 +1882,7 @@ constexpr size_t MAX_DYN_SMEM = 96 * 1024;  // keeps two launches resident per S
 int gguf_gemv_fast_init(int device) {
   if (const char *e = getenv("LIGHT_B200_GEMV_WAVES")) g_waves = atoi(e) == 1 ? 1 : 2;
   if (const char *e = getenv("LIGHT_B200_Q4K_STAGES")) g_q4k_stages = atoi(e) == 2 ? 2 : 4;
-  cudaError_t err = cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, device);
-  if (err == cudaSuccess)
-    err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
+  cudaError_t err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<4, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
     err = cudaFuncSetAttribute(q4k_gemv_mma_kernel<2, 3, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)MAX_DYN_SMEM);
   if (err == cudaSuccess)
@@ -1977,13 +1975,13 @@ int int4_gemv_fast(const void *x, const uint32_t *codes, const float *s, const f
   if (M < 1 || M > (act_dtype == LB200_F32 ? g_int4_fast_max_f32 : g_int4_fast_max_bf16)) return 0;
   if (K % 256 || G % 64 || N < ROWS || ((uintptr_t)codes & 15) || ((uintptr_t)x & 15) || (act_dtype == LB200_BF16 && (K % 8))) return 0;
   if (act_dtype != LB200_F32 && act_dtype != LB200_BF16) return 0;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(int4_gemv_mma_kernel<I4_STAGES, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * I4_STAGES * I4_TILE_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(int4_gemv_mma_kernel<I4_STAGES, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * I4_STAGES * I4_TILE_BYTES);
+  static DeviceOnce attr_done;
+  {
+    cudaError_t e = attr_done.ensure([&] {
+      cudaError_t r = cudaFuncSetAttribute(int4_gemv_mma_kernel<I4_STAGES, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * I4_STAGES * I4_TILE_BYTES);
+      return r != cudaSuccess ? r : cudaFuncSetAttribute(int4_gemv_mma_kernel<I4_STAGES, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * I4_STAGES * I4_TILE_BYTES);
+    });
     if (e != cudaSuccess) return fail((int)e, "light_b200: int4_gemv (decode): %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   const int tiles = (N + ROWS - 1) / ROWS;
   const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
@@ -2015,13 +2013,13 @@ int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale, void *y, 
   if (act_dtype != LB200_F32 && act_dtype != LB200_BF16) return 0;
   if (M < 1 || M > (act_dtype == LB200_F32 ? g_fp8_fast_max_f32 : g_fp8_fast_max_bf16)) return 0;
   if (K % 256 || bC % 32 || bR % 16 || N < ROWS || N % bR || K % bC || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(fp8_gemv_mma_kernel<F8_STAGES, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * F8_STAGES * F8_TILE_BYTES);
-    if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(fp8_gemv_mma_kernel<F8_STAGES, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * F8_STAGES * F8_TILE_BYTES);
+  static DeviceOnce attr_done;
+  {
+    cudaError_t e = attr_done.ensure([&] {
+      cudaError_t r = cudaFuncSetAttribute(fp8_gemv_mma_kernel<F8_STAGES, float>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * F8_STAGES * F8_TILE_BYTES);
+      return r != cudaSuccess ? r : cudaFuncSetAttribute(fp8_gemv_mma_kernel<F8_STAGES, __nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, WARPS * F8_STAGES * F8_TILE_BYTES);
+    });
     if (e != cudaSuccess) return fail((int)e, "light_b200: fp8_block_gemv (decode): %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   const int tiles = (N + ROWS - 1) / ROWS;
   const unsigned grid = (unsigned)(tiles < g_sms * g_waves ? tiles : g_sms * g_waves);
@@ -2075,11 +2073,10 @@ int gguf_gemv_tok(int type, const float *x, const void *w, float *out, int M, in
 template <int NG>
 static int launch_tile(const float *x, const MultiArgs &ma, int tiles, int M, int K, cudaStream_t st) {
   auto kern = q4k_decode_tile_kernel<NG>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DtCfg<NG>::SMEM);
+  static DeviceOnce attr_done;
+  {
+    cudaError_t e = attr_done.ensure([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, DtCfg<NG>::SMEM); });
     if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, tiles): %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   const int nx = (tiles + DT_CW - 1) / DT_CW, nb = K >> 8;
   // measured on 4096 x 4096, 1024 x 4096 and 14336 x 4096: short K runs win (a CTA's start-up and its first

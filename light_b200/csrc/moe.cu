@@ -12,7 +12,14 @@
 
 namespace lb {
 
-// offsets[e] = first sorted index whose expert id is >= e; offsets[E] = M.
+// Non-zero once an expert id outside [0, E) was seen by the offsets kernel (sticky; light_b200_moe_route_status
+// reports it together with the routing kernels' own word).
+__device__ unsigned int g_moe_bad_ids;
+
+// offsets[e] = first sorted index whose expert id is >= e; offsets[E] = M.  Nobody validates the ids before
+// this kernel, so it does: both ends of a boundary are clamped into [-1, E - 1] and made non-decreasing
+// before they index anything.  A negative id therefore owns no range (the matmul kernel skips such pairs
+// too), an id >= E is counted under the last expert's boundary, and either sets the status word.
 __global__ void moe_offsets_kernel(const int64_t *__restrict__ ids, int32_t *__restrict__ offsets, long long M, int E) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (M == 0) {
@@ -21,7 +28,10 @@ __global__ void moe_offsets_kernel(const int64_t *__restrict__ ids, int32_t *__r
   }
   if (i >= M) return;
   long long cur = ids[i], prev = i == 0 ? -1 : ids[i - 1];
-  if (cur >= E) cur = E - 1;  // ids are validated by the caller; clamp so no store leaves the array
+  if (cur < 0 || cur >= E) g_moe_bad_ids = 1u;
+  cur = cur < -1 ? -1 : (cur >= E ? E - 1 : cur);
+  prev = prev < -1 ? -1 : (prev >= E ? E - 1 : prev);
+  if (cur < prev) cur = prev;  // unsorted input: no boundary here, and no store below
   for (long long e = prev + 1; e <= cur; e++) offsets[e] = (int32_t)i;
   if (i == M - 1)
     for (long long e = cur + 1; e <= E; e++) offsets[e] = (int32_t)M;
@@ -155,6 +165,13 @@ static int run(const lb200_moe_args *a, cudaStream_t st) {
       (const TI *)a->input, a->weights, a->sorted_pairs, a->expert_ids, a->offsets, a->topk_weights, (TO *)a->out, a->M,
       a->size_m, a->E, a->N, a->K, a->topk, a->row_per_pair);
   return launched("moe_gemm");
+}
+
+int moe_bad_ids_status() {
+  unsigned int v = 0;
+  cudaError_t e = cudaMemcpyFromSymbol(&v, g_moe_bad_ids, sizeof(v));
+  if (e != cudaSuccess) return fail((int)e, "light_b200: moe status: %s", cudaGetErrorString(e));
+  return (int)v;
 }
 
 int moe_gemm(const lb200_moe_args *a, int device, cudaStream_t st) {

@@ -176,14 +176,19 @@ int moe_sort_pairs(const int64_t *ids, int *counts, int *offsets, int64_t *sorte
                    int E, cudaStream_t st) {
   const int nblocks = (int)((M + SORT_BLOCK - 1) / SORT_BLOCK);
   int *local_rank = scratch, *block_hist = scratch + M;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(moe_sort_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * 4);
-    if (e != cudaSuccess) return fail((int)e, "light_b200: moe_sort_pairs: %s", cudaGetErrorString(e));
-    attr_done = true;
-  }
-  static unsigned int *status = nullptr;  // looked up on the first call (make it outside stream capture)
-  cudaError_t e = status ? cudaSuccess : cudaGetSymbolAddress((void **)&status, g_route_status);
+  // per device: the sort kernel's shared-memory opt-in, and the address of this device's copy of the status word
+  static DeviceOnce attr_done;
+  static unsigned int *status_of[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess && (dev < 0 || dev >= 64)) e = cudaErrorInvalidDevice;
+  if (e == cudaSuccess)
+    e = attr_done.ensure([&] {  // the first call on a device: make it outside stream capture
+      cudaError_t r = cudaFuncSetAttribute(moe_sort_local_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * 4);
+      return r != cudaSuccess ? r : cudaGetSymbolAddress((void **)&status_of[dev], g_route_status);
+    });
+  if (e != cudaSuccess) return fail((int)e, "light_b200: moe_sort_pairs: %s", cudaGetErrorString(e));
+  unsigned int *status = status_of[dev];
   if (e == cudaSuccess && nblocks > 0)
     e = launch_chain(moe_sort_local_kernel, (unsigned)nblocks, SORT_BLOCK, (size_t)32 * E * 4, st, (const long long *)ids, local_rank, block_hist, M, E,
                      status);

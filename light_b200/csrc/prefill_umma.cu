@@ -40,8 +40,7 @@ constexpr int NUM_DEQ_WARPS = 8, TMA_WARP = 8, MMA_WARP = 9, THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int SMEM_BYTES = SA * A_STAGE + SB * B_STAGE + 1024 /*alignment*/ + 256 /*barriers*/;
 
-__device__ int g_prefill_status;
-int g_sm_count_pf = 148;  // SMs of the device (set on first use)  // non-zero: a bounded wait gave up (sticky, read by the host on demand)
+__device__ int g_prefill_status;  // non-zero: a bounded wait gave up (sticky, read by the host on demand)
 
 // Grouped (mixture-of-experts) mode: the token rows of the A operand have been gathered into expert
 // order, expert e owns rows offsets[e] .. offsets[e+1] of it; output row i goes to pair sorted_pairs[i],
@@ -353,11 +352,10 @@ template <typename Row, bool BF16, typename OutT>
 int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp, OutT *out, int M, int N, int K,
            cudaStream_t st) {
   auto kern = prefill_umma_kernel<Row, BF16, OutT>;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+  static DeviceOnce attr_done;
+  {
+    cudaError_t e = attr_done.ensure([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
     if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   // Token-tile height: 256 amortises the weight expansion best, but when the grid of 256-row tiles leaves
   // the last wave of the 148 SMs mostly empty, 128-row tiles (twice as many CTAs) finish sooner.
@@ -375,7 +373,7 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
   if (!grp.offsets && M <= 128 && K % 256 == 0) {
     bm = 128;
     const int nblk = K >> 8;
-    while (ks < 8 && ks * 2 <= nblk && nt * ks < g_sm_count_pf) ks *= 2;
+    while (ks < 8 && ks * 2 <= nblk && nt * ks < sm_count()) ks *= 2;
   }
   // grouped: at most ceil(M / bm) + E tiles (every expert can end with one partial tile)
   dim3 grid((unsigned)nt, (M + bm - 1) / bm + (grp.offsets ? grp.E : 0), (unsigned)ks);
@@ -437,8 +435,6 @@ bool g_pf_knobs = false;
 void pf_knobs() {
   if (g_pf_knobs) return;
   if (const char *e = getenv("LIGHT_B200_PREFILL_MIN_M")) g_prefill_min_m = atoi(e) < 1 ? 1 : atoi(e);
-  int dev = 0, v = 148;
-  if (cudaGetDevice(&dev) == cudaSuccess && cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess) g_sm_count_pf = v;
   g_pf_knobs = true;
 }
 #define PREFILL_MIN_M (pf_knobs(), g_prefill_min_m)

@@ -153,11 +153,10 @@ int quantize_rows_int8(const float *x, int8_t *q, float *scales, long long M, in
 int matmul_w8a8(const float *x, const int8_t *wq, const float *ws, float *out, int8_t *xq, float *xs, int M, int N, int K,
                 cudaStream_t st) {
   if (M == 0 || N == 0) return 0;
-  static bool attr_done = false;
-  if (!attr_done) {
-    cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W8_SMEM);
+  static DeviceOnce attr_done;
+  {
+    cudaError_t e = attr_done.ensure([&] { return cudaFuncSetAttribute(w8a8_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, W8_SMEM); });
     if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_w8a8: %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   if (int rc = quantize_rows_int8(x, xq, xs, M, K, st)) return rc;
   dim3 grid((N + W8_BN - 1) / W8_BN, (M + W8_BM - 1) / W8_BM);

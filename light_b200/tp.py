@@ -224,13 +224,27 @@ class FusedExchange:
         _lib.check(_lib.lib().light_b200_matmul_q_tp(ggml_type, C.c_void_p(x.data_ptr() if x is not None else 0), wp, op, nn, n, K,
                                                      C.byref(args), dev, C.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)))
 
-    def read(self, index: int, N: int) -> torch.Tensor:
-        """The exchanged output `index` of the step just run, as (N,) f32 (test helper: synchronises)."""
+    def read(self, index: int, N: int, timeout_s: float = 2.0) -> torch.Tensor:
+        """The exchanged output `index` of the step last begun, as (N,) f32 (test helper: synchronises).
+
+        A local synchronise only proves that THIS rank's launches are done: a slower peer may still be storing
+        its part of an output that no local launch has consumed yet.  So the slots' tags are compared with the
+        step word, and re-read until they all match; after timeout_s a RuntimeError names the stale slots."""
+        import time
+
         torch.cuda.synchronize(self.device)
-        par = int(self.step.item()) & 1
+        step = int(self.step.item()) & 0xFFFFFFFF
+        par = step & 1
         off = self.slots[index][self.rank] - int(self.handle.buffer_ptrs[self.rank])
-        sl = self.arena[off + par * N * 8: off + (par + 1) * N * 8].view(torch.float32).view(N, 2)
-        return sl[:, 0].clone()
+        t0 = time.time()
+        while True:
+            sl = self.arena[off + par * N * 8: off + (par + 1) * N * 8].view(torch.int32).view(N, 2).clone()
+            stale = int((sl[:, 1].to(torch.int64) & 0xFFFFFFFF != step).sum().item())
+            if stale == 0:
+                return sl[:, 0].contiguous().view(torch.float32).clone()
+            if time.time() - t0 > timeout_s:
+                raise RuntimeError(f"FusedExchange.read: {stale} of {N} slots of output {index} do not carry step {step}")
+            time.sleep(0.001)
 
     def status(self) -> int:
         from . import _lib

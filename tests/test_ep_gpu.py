@@ -72,7 +72,7 @@ def test_expert_parallel_matches_single_gpu():
     world = torch.cuda.device_count()
     if world < 2:
         pytest.skip("needs at least two GPUs")
-    world = min(world, 4)
+    world = min(world, 8)
     import torch.multiprocessing as mp
 
     ctx = mp.get_context("spawn")
