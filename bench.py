@@ -427,36 +427,52 @@ def timed(replay, steps, warmup, device, barrier):
     return e0.elapsed_time(e1)  # ms
 
 
-def cpu_reference(M, threads, steps, warmup):
-    """The reference's CPU implementation of the path (kernels/cpu/quant_matmul.go matmulQCPU), as
-    restated in oracle/light_oracle.c, on a bounded sample: one decoder layer (7 linears) + nothing
-    else per timed step; the whole-step time is 32 x that + one lm_head pass timed once."""
+def cpu_reference(M, threads, steps, warmup, budget_s=150.0):
+    """The reference's CPU implementation of the path (kernels/cpu/quant_matmul.go matmulQCPU: AVX2 row
+    decoders, 48-row tiles, 4x3 FMA tiles, static chunks over all host threads), as restated in
+    oracle/light_oracle.c.  One step = the 225 linears of a decode step when `steps` of them fit the time
+    budget; otherwise the first L of the 32 layers plus lm_head's share, and the step time is scaled by 32 / L.
+    Four distinct layers' weights are rotated (551 MB: beyond the host's last-level cache).
+    Returns (tok/s, seconds per whole step, seconds per timed step, layers per timed step, description)."""
     from oracle import binding as ob
 
     rng = np.random.Generator(np.random.Philox(5))
     xs = {HID: rng.standard_normal((M, HID)).astype(np.float32), FFN: rng.standard_normal((M, FFN)).astype(np.float32)}
     # decode time does not depend on the code values: random blocks stand in for quantized Gaussians here
-    ws = [(N, K, dt, synth.random_blocks(900 + i, dt, N, K)) for i, (_, N, K, dt) in enumerate(LAYER)]
+    rot = [[(N, K, dt, synth.random_blocks(900 + 16 * r + i, dt, N, K)) for i, (_, N, K, dt) in enumerate(LAYER)] for r in range(4)]
+    _, NH, KH, dth = HEAD
+    head = synth.random_blocks(999, dth, NH, KH)
 
-    def layer():
-        for N, K, dt, w in ws:
-            ob.matmul_q(dt, xs[K], w, N, threads=threads)
+    def layers(n, first=0):
+        for l in range(first, first + n):
+            for N, K, dt, w in rot[l % 4]:
+                ob.matmul_q(dt, xs[K], w, N, threads=threads)
 
-    for _ in range(max(1, min(warmup, 2))):
-        layer()
+    def head_rows(frac):
+        n = max(48, int(NH * frac) // 48 * 48)
+        ob.matmul_q(dth, xs[KH], head[:n], n, threads=threads)
+
+    layers(1)
+    t0 = time.perf_counter()
+    layers(2, 1)
+    t_layer = (time.perf_counter() - t0) / 2
+    est_full = LAYERS * t_layer * (1 + weight_bytes(NH, KH, dth) / (LAYERS * sum(weight_bytes(N, K, dt) for _, N, K, dt in LAYER)))
+    L = LAYERS if (steps + warmup) * est_full <= budget_s else max(1, min(LAYERS, int(budget_s / ((steps + warmup) * est_full) * LAYERS)))
+
+    def step():
+        layers(L)
+        head_rows(L / LAYERS)
+
+    for _ in range(warmup):
+        step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        layer()
-    t_layer = (time.perf_counter() - t0) / steps
-    _, N, K, dt = HEAD
-    head = synth.random_blocks(999, dt, N, K)
-    ob.matmul_q(dt, xs[K], head, N, threads=threads)
-    t0 = time.perf_counter()
-    ob.matmul_q(dt, xs[K], head, N, threads=threads)
-    t_head = time.perf_counter() - t0
-    t_step = LAYERS * t_layer + t_head
-    return M / t_step, t_step, f"{steps} x one decoder layer (7 linears, 137.8 MB) + 1 x lm_head (430.9 MB), " \
-                               f"scaled to 32 layers + lm_head; M={M}"
+        step()
+    t_timed = (time.perf_counter() - t0) / steps
+    t_step = t_timed * LAYERS / L
+    what = "the whole step: 32 layers x 7 linears + lm_head (4.84 GB of weights)" if L == LAYERS else \
+        f"{L} of 32 layers + {L}/32 of lm_head's rows per timed step, scaled by 32/{L}"
+    return M / t_step, t_step, t_timed, L, f"{steps} timed steps of {what}; M={M}; AVX2 row decoders: {bool(ob.lib().lo_uses_avx2())}"
 
 
 def extras(chain, device, args):
@@ -590,14 +606,14 @@ def main():
         if rank != 0:
             return 0
         threads = os.cpu_count() or 1
-        steps = max(1, min(args.steps, 5))
-        v, t_step, sample = cpu_reference(M, threads, steps, args.warmup)
+        v, t_step, t_timed, L, sample = cpu_reference(M, threads, args.steps, min(args.warmup, 3))
         print(json.dumps({
             "impl": "reference", "metric": metric, "value": v, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong",
+            "warmup": args.warmup, "ms_per_step": t_timed * 1e3, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload, "timed_steps_of_sample": steps},
-            "cpu_baseline": {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample},
+            "config": {"workload": workload},
+            "cpu_baseline": {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample,
+                             "layers_per_timed_step": L, "ms_per_whole_step": t_step * 1e3},
             "e2e": {"value": v, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
         return 0
@@ -688,7 +704,7 @@ def main():
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
-            v, t_step, sample = cpu_reference(M, threads, 3, 1)
+            v, t_step, _, _, sample = cpu_reference(M, threads, 3, 1)
             line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
     if world > 1 and chain.peer is not None and chain.peer.status() != 0:  # (one status word covers both exchanges)

@@ -25,7 +25,11 @@ def build(force: bool = False) -> None:
     kernels into oracle/_ref/)."""
     if force and os.path.exists(LIB_PATH):
         os.remove(LIB_PATH)
-    subprocess.run(["make", "-s", "-C", HERE], check=True)
+    ref = os.environ.get("LIGHT_REFERENCE_DIR", "")
+    if not ref:  # the checkout sits beside this repository where the build is developed; absent elsewhere
+        cand = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+        ref = cand if os.path.isdir(os.path.join(cand, "kernels", "cuda", "src")) else ""
+    subprocess.run(["make", "-s", "-C", HERE] + ([f"REF={ref}"] if ref else []), check=True)
 
 
 _lib = None
@@ -290,3 +294,21 @@ def matmul_w8a8(x: np.ndarray, wq: np.ndarray, ws: np.ndarray):
 
 def has_avx2() -> bool:
     return bool(lib().lo_has_avx2())
+
+
+def decode_row_avx2(dt: int, raw: np.ndarray, K: int) -> np.ndarray:
+    """One weight row through the AVX2 row decoder of its format (kernels/cpu/quant_matmul.go:208-250)."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    out = np.empty(K, np.float32)
+    _chk(lib().lo_decode_row_avx2(dt, _p(raw), _p(out), K), "decode_row_avx2")
+    return out
+
+
+def int4_row_avx2(codes: np.ndarray, s: np.ndarray, z: np.ndarray, G: int) -> np.ndarray:
+    """One canonical int4 row (K / 8 words, K / G scales and zeros) through int4RowAVX2's restatement."""
+    codes = np.ascontiguousarray(codes, np.uint32)
+    K = codes.size * 8
+    out = np.empty(K, np.float32)
+    _chk(lib().lo_int4_row_avx2(_p(codes), _p(np.ascontiguousarray(s, np.float32)), _p(np.ascontiguousarray(z, np.float32)), _p(out), K, G),
+         "int4_row_avx2")
+    return out

@@ -16,10 +16,13 @@
  * reference CPU path is Go + Plan 9 AVX2 assembly (no Go toolchain is available), so
  * this is a C restatement, not a build of the reference.  The reference's AVX2 row
  * decoders are bit-identical to its scalar Go decoders (kernels/cpu/qdecode_test.go:38-89),
- * so the scalar decoders below ARE the decode oracle; compile with -ffp-contract=off so
- * that `a*b - c` stays a separate multiply and subtract exactly as Go on amd64 does.
+ * so the scalar decoders below ARE the decode oracle, and the AVX2 row decoders restated
+ * further down (with intrinsics) are what the timed matmul uses, as the reference's does;
+ * compile with -ffp-contract=off so that `a*b - c` stays a separate multiply and subtract
+ * exactly as Go on amd64 does.
  */
 #define _GNU_SOURCE
+#include <malloc.h>
 #include <math.h>
 #include <pthread.h>
 #include <stdint.h>
@@ -441,6 +444,153 @@ static void parallel_for(int n, int grain, int threads, range_fn fn, void *ctx) 
   free(jobs);
 }
 
+/* ------------------------------------------------ AVX2 row decoders
+ *
+ * kernels/cpu/qdecode_amd64.s:33-285 with its driver decodeRowAVX2 (kernels/cpu/quant_matmul.go:208-250):
+ * the reference's CPU matmul decodes Q8_0 / Q4_0 / Q5_0 / Q4_K / Q6_K rows (and int4 rows) eight lanes at
+ * a time -- the integer code is formed per lane, converted to f32 and scaled with the same operations in
+ * the same order as the scalar decoders, so the floats are identical (the reference asserts this in
+ * kernels/cpu/qdecode_test.go:38-89; tests/test_oracle_avx2.py asserts it for this restatement).  These
+ * are what lo_matmul_q times when the host has AVX2 + FMA + F16C, as the reference's matmulQCPU does. */
+
+#define LO_AVX2 __attribute__((target("avx2,fma,f16c")))
+
+LO_AVX2 static inline __m256i ld8_u8(const uint8_t *p) { return _mm256_cvtepu8_epi32(_mm_loadl_epi64((const __m128i *)p)); }
+LO_AVX2 static inline __m256i ld8_s8(const uint8_t *p) { return _mm256_cvtepi8_epi32(_mm_loadl_epi64((const __m128i *)p)); }
+
+/* qdecode_amd64.s:33-68 (q8_0RowAVX2): d * float(int8). */
+LO_AVX2 static void row_q8_0_avx2(const uint8_t *raw, float *dst, int K) {
+  for (int b = 0; b < K / 32; b++, raw += 34, dst += 32) {
+    const __m256 d = _mm256_set1_ps(f16le(raw));
+    for (int i = 0; i < 4; i++) _mm256_storeu_ps(dst + 8 * i, _mm256_mul_ps(_mm256_cvtepi32_ps(ld8_s8(raw + 2 + 8 * i)), d));
+  }
+}
+/* qdecode_amd64.s:70-114 (q4_0RowAVX2): d * float(nibble - 8); low nibbles are elements 0..15, high 16..31. */
+LO_AVX2 static void row_q4_0_avx2(const uint8_t *raw, float *dst, int K) {
+  const __m256i m15 = _mm256_set1_epi32(15), off = _mm256_set1_epi32(8);
+  for (int b = 0; b < K / 32; b++, raw += 18, dst += 32) {
+    const __m256 d = _mm256_set1_ps(f16le(raw));
+    for (int h = 0; h < 2; h++) {
+      const __m256i v = ld8_u8(raw + 2 + 8 * h);
+      const __m256i lo = _mm256_sub_epi32(_mm256_and_si256(v, m15), off), hi = _mm256_sub_epi32(_mm256_srli_epi32(v, 4), off);
+      _mm256_storeu_ps(dst + 8 * h, _mm256_mul_ps(_mm256_cvtepi32_ps(lo), d));
+      _mm256_storeu_ps(dst + 16 + 8 * h, _mm256_mul_ps(_mm256_cvtepi32_ps(hi), d));
+    }
+  }
+}
+/* qdecode_amd64.s:116-161 (q5_0RowAVX2): the fifth bit of element e is bit e of the 32-bit qh; offset 16. */
+LO_AVX2 static void row_q5_0_avx2(const uint8_t *raw, float *dst, int K) {
+  const __m256i m15 = _mm256_set1_epi32(15), one = _mm256_set1_epi32(1), off = _mm256_set1_epi32(16);
+  const __m256i lanes = _mm256_setr_epi32(0, 1, 2, 3, 4, 5, 6, 7);
+  for (int b = 0; b < K / 32; b++, raw += 22, dst += 32) {
+    const __m256 d = _mm256_set1_ps(f16le(raw));
+    uint32_t qhw;
+    memcpy(&qhw, raw + 2, 4);
+    const __m256i qh = _mm256_set1_epi32((int)qhw);
+    for (int h = 0; h < 2; h++) {
+      const __m256i v = ld8_u8(raw + 6 + 8 * h);
+      const __m256i sl = _mm256_add_epi32(lanes, _mm256_set1_epi32(8 * h)), sh = _mm256_add_epi32(sl, _mm256_set1_epi32(16));
+      const __m256i bl = _mm256_slli_epi32(_mm256_and_si256(_mm256_srlv_epi32(qh, sl), one), 4);
+      const __m256i bh = _mm256_slli_epi32(_mm256_and_si256(_mm256_srlv_epi32(qh, sh), one), 4);
+      const __m256i lo = _mm256_sub_epi32(_mm256_or_si256(_mm256_and_si256(v, m15), bl), off);
+      const __m256i hi = _mm256_sub_epi32(_mm256_or_si256(_mm256_srli_epi32(v, 4), bh), off);
+      _mm256_storeu_ps(dst + 8 * h, _mm256_mul_ps(_mm256_cvtepi32_ps(lo), d));
+      _mm256_storeu_ps(dst + 16 + 8 * h, _mm256_mul_ps(_mm256_cvtepi32_ps(hi), d));
+    }
+  }
+}
+/* qdecode_amd64.s:163-205 (q4KBlockAVX2) + quant_matmul.go:225-236: sc[j] = d * scale_j and mn[j] = dmin * min_j
+ * are formed first (scalar), then q * sc - mn as a separate multiply and subtract (VMULPS, VSUBPS). */
+LO_AVX2 static void row_q4_k_avx2(const uint8_t *raw, float *dst, int K) {
+  const __m256i m15 = _mm256_set1_epi32(15);
+  for (int b = 0; b < K / 256; b++, raw += 144, dst += 256) {
+    const float d = f16le(raw), dmin = f16le(raw + 2);
+    float sc[8], mn[8];
+    for (int j = 0; j < 8; j++) {
+      uint8_t s, m;
+      scale_min_k4(j, raw + 4, &s, &m);
+      sc[j] = d * (float)s, mn[j] = dmin * (float)m;
+    }
+    const uint8_t *qs = raw + 16;
+    for (int p = 0; p < 4; p++) {
+      const __m256 s0 = _mm256_set1_ps(sc[2 * p]), m0 = _mm256_set1_ps(mn[2 * p]);
+      const __m256 s1 = _mm256_set1_ps(sc[2 * p + 1]), m1 = _mm256_set1_ps(mn[2 * p + 1]);
+      for (int c = 0; c < 4; c++) {
+        const __m256i v = ld8_u8(qs + 32 * p + 8 * c);
+        const __m256 lo = _mm256_cvtepi32_ps(_mm256_and_si256(v, m15)), hi = _mm256_cvtepi32_ps(_mm256_srli_epi32(v, 4));
+        _mm256_storeu_ps(dst + 64 * p + 8 * c, _mm256_sub_ps(_mm256_mul_ps(lo, s0), m0));
+        _mm256_storeu_ps(dst + 64 * p + 32 + 8 * c, _mm256_sub_ps(_mm256_mul_ps(hi, s1), m1));
+      }
+    }
+  }
+}
+/* qdecode_amd64.s:207-245 (q6KBlockAVX2) + quant_matmul.go:237-247: sc[j] = d * int8 scale first, then
+ * float(q - 32) * sc for the four quarters of each half. */
+LO_AVX2 static void row_q6_k_avx2(const uint8_t *raw, float *dst, int K) {
+  const __m256i m15 = _mm256_set1_epi32(15), m3 = _mm256_set1_epi32(3), off = _mm256_set1_epi32(32);
+  for (int b = 0; b < K / 256; b++, raw += 210, dst += 256) {
+    const float d = f16le(raw + 208);
+    float sc[16];
+    for (int j = 0; j < 16; j++) sc[j] = d * (float)(int8_t)raw[192 + j];
+    for (int half = 0; half < 2; half++) {
+      const uint8_t *ql = raw + 64 * half, *qh = raw + 128 + 32 * half;
+      const float *s = sc + 8 * half;
+      float *y = dst + 128 * half;
+      for (int c = 0; c < 4; c++) {  /* l = 8c .. 8c+7; is = l / 16 */
+        const int is = c >> 1;
+        const __m256i a = ld8_u8(ql + 8 * c), bq = ld8_u8(ql + 32 + 8 * c), h = ld8_u8(qh + 8 * c);
+        const __m256i nib[4] = {_mm256_and_si256(a, m15), _mm256_and_si256(bq, m15), _mm256_srli_epi32(a, 4), _mm256_srli_epi32(bq, 4)};
+        for (int q = 0; q < 4; q++) {
+          const __m256i hi = _mm256_slli_epi32(_mm256_and_si256(_mm256_srli_epi32(h, 2 * q), m3), 4);
+          const __m256i code = _mm256_sub_epi32(_mm256_or_si256(nib[q], hi), off);
+          _mm256_storeu_ps(y + 32 * q + 8 * c, _mm256_mul_ps(_mm256_cvtepi32_ps(code), _mm256_set1_ps(s[2 * q + is])));
+        }
+      }
+    }
+  }
+}
+/* qdecode_amd64.s:248-285 (int4RowAVX2): word w holds elements 8w .. 8w+7; s * (float(q) - z), the subtract in f32. */
+LO_AVX2 static void row_int4_avx2(const uint32_t *words, const float *s, const float *z, float *dst, int groups, int wpg) {
+  const __m256i m15 = _mm256_set1_epi32(15), sh = _mm256_setr_epi32(0, 4, 8, 12, 16, 20, 24, 28);
+  for (int g = 0; g < groups; g++) {
+    const __m256 sv = _mm256_set1_ps(s[g]), zv = _mm256_set1_ps(z[g]);
+    for (int w = 0; w < wpg; w++, words++, dst += 8) {
+      const __m256i q = _mm256_and_si256(_mm256_srlv_epi32(_mm256_set1_epi32((int)*words), sh), m15);
+      _mm256_storeu_ps(dst, _mm256_mul_ps(_mm256_sub_ps(_mm256_cvtepi32_ps(q), zv), sv));
+    }
+  }
+}
+
+typedef void (*row_avx2)(const uint8_t *, float *, int);
+/* ggufAVX2 (kernels/cpu/quant_matmul.go:172-176): the formats decodeRowAVX2 handles. */
+static row_avx2 avx2_row_for(int dt) {
+  switch (dt) {
+    case LO_Q8_0: return row_q8_0_avx2;
+    case LO_Q4_0: return row_q4_0_avx2;
+    case LO_Q5_0: return row_q5_0_avx2;
+    case LO_Q4_K: return row_q4_k_avx2;
+    case LO_Q6_K: return row_q6_k_avx2;
+  }
+  return 0;
+}
+static int have_avx2(void);
+
+/* One row of K elements through the AVX2 decoder of its format.  Returns -1 when the format has none or the
+ * host lacks AVX2 (the caller then uses the scalar decoders, as the reference does). */
+LO_API int lo_decode_row_avx2(int dt, const uint8_t *raw, float *dst, int K) {
+  row_avx2 f = avx2_row_for(dt);
+  if (!f || !have_avx2() || K <= 0 || K % lo_block_elems(dt)) return -1;
+  f(raw, dst, K);
+  return 0;
+}
+LO_API int lo_int4_row_avx2(const uint32_t *codes, const float *s, const float *z, float *dst, int K, int G) {
+  if (!have_avx2() || G <= 0 || G % 8 || K % G) return -1;
+  row_int4_avx2(codes, s, z, dst, K / G, G / 8);
+  return 0;
+}
+/* 1 when lo_matmul_q / lo_matmul_int4 decode rows with the AVX2 decoders on this host. */
+LO_API int lo_uses_avx2(void) { return have_avx2(); }
+
 /* ------------------------------------------------ x (M,K) . W^T, W quantized */
 
 #define TILE_ROWS 48 /* kernels/cpu/matmul_f32.go:9 */
@@ -467,6 +617,12 @@ static void rtx_range(int lo, int hi, void *p) {
   free(rows);
 }
 static void rows_times_x(const float *x, float *out, int M, int K, int N, int threads, row_dec dec, void *dctx) {
+  static int tuned;
+  if (!tuned) { /* keep the per-worker row tiles (up to a few MB) on the heap instead of a fresh mmap per call */
+    mallopt(M_MMAP_THRESHOLD, 1 << 30);
+    mallopt(M_TRIM_THRESHOLD, 1 << 30);
+    tuned = 1;
+  }
   rtx r = {x, out, M, K, N, dec, dctx};
   int grain = 16384 / (K + 1);
   parallel_for(N, grain < 1 ? 1 : grain, threads, rtx_range, &r);
@@ -476,10 +632,15 @@ typedef struct {
   const uint8_t *w;
   block_dec dec;
   int be, bb, K;
+  row_avx2 fast; /* non-null: kernels/cpu/quant_matmul.go:153-166, the AVX2 row decoder (K / 32 <= 2048) */
 } gguf_ctx;
 static void gguf_row(int n, float *dst, void *p) {
   gguf_ctx *g = (gguf_ctx *)p;
   const uint8_t *row = g->w + (size_t)n * (size_t)(g->K / g->be) * (size_t)g->bb;
+  if (g->fast) {
+    g->fast(row, dst, g->K);
+    return;
+  }
   for (int b = 0; b < g->K / g->be; b++) g->dec(row + (size_t)b * g->bb, dst + (size_t)b * g->be);
 }
 
@@ -488,7 +649,8 @@ static void gguf_row(int n, float *dst, void *p) {
 LO_API int lo_matmul_q(int dt, const float *x, const uint8_t *w, float *out, int M, int N, int K, int threads) {
   block_dec dec = decoder_for(dt);
   if (!dec || M < 0 || N < 0 || K <= 0 || K % lo_block_elems(dt)) return -1;
-  gguf_ctx g = {w, dec, lo_block_elems(dt), lo_block_bytes(dt), K};
+  gguf_ctx g = {w, dec, lo_block_elems(dt), lo_block_bytes(dt), K, 0};
+  if (have_avx2() && __builtin_cpu_supports("f16c") && K / 32 <= 2048) g.fast = avx2_row_for(dt);
   rows_times_x(x, out, M, K, N, threads, gguf_row, &g);
   return 0;
 }
@@ -522,6 +684,10 @@ static void int4_row(int n, float *dst, void *p) {
   int4_ctx *c = (int4_ctx *)p;
   int ng = c->K / c->G;
   const uint32_t *words = c->codes + (size_t)n * (c->K / 8);
+  if (have_avx2() && c->G % 8 == 0) {  /* kernels/cpu/quant_matmul.go:188-191 */
+    row_int4_avx2(words, c->s + (size_t)n * ng, c->z + (size_t)n * ng, dst, ng, c->G / 8);
+    return;
+  }
   for (int g = 0; g < ng; g++) {
     float s = c->s[(size_t)n * ng + g], z = c->z[(size_t)n * ng + g];
     for (int k = g * c->G; k < (g + 1) * c->G; k += 8) {
