@@ -398,6 +398,63 @@ LB200_API int light_b200_inc_i64(int64_t *p, int n, int device, void *stream);
 /* 0, or 1 if a launch ever saw a position outside [0, Cap).  Synchronises with the device. */
 LB200_API int light_b200_decode_attn_status(int device);
 
+/* ---- a decode step's dependent matrix-vector products as ONE launch
+ *
+ * The reference replays a decode step as a CUDA graph with one kernel per operator (models/decode_graph.go:58-205,
+ * built from models/llama.go:1070-1330: per layer RMSNorm, q/k/v, attention, o, RMSNorm, gate/up, down; then the
+ * final norm and lm_head).  For one activation row every one of those launches waits for the one before it and
+ * streams only a few MB, so the step is bound by launch boundaries.  A chain is a PROGRAM of such operators
+ * executed by one persistent launch (one thread block per SM): an operator's outputs reach the operators that
+ * consume them through "chain vectors" -- buffers of 8-byte {f32, tag} slots in an arena the caller provides --
+ * with no barrier and no launch in between, while the weights of the following operators are already being
+ * fetched.  One f32 activation row; Q4_K and Q6_K weights.
+ *
+ * lb200_chain_op: out[i] (n[i]) = dequant(w[i] (n[i], K)) . y for i < count (Q4_K: up to four matrices of one
+ *   launch, Q6_K: one), or with act 1 (SiLU) / 2 (GELU-erf) and count == 2: out[0] = act(w[0] . y) * (w[1] . y).
+ *   y = the activations: plain f32 `x` (K values written before the call) or chain vector x_vec (written by an
+ *   earlier operator of the program).  With norm_weight: y = s * rsqrt(mean(s^2) + norm_eps) * norm_weight,
+ *   s = activations + chain vector res_vec (res_vec < 0: s = activations), and s is written to chain vector
+ *   sum_vec when sum_vec >= 0 (the new residual stream) -- light_b200_matmul_q_fused's arithmetic; K <= 4096.
+ *   Output i goes to plain memory out[i] when that is not NULL and to chain vector out_vec[i] when that is
+ *   >= 0.  A vector may be rewritten by a later operator (the layers of a model reuse their vectors), as long
+ *   as at least one other operator of the chain lies between its last reader and the writer.
+ *   Row-split over `world` GPUs: n[i] are the rows this rank holds, rank r's values fill positions
+ *   [r n[i], (r + 1) n[i]) of the vector on EVERY rank (stores into the peers' arenas), and a consumer's K is
+ *   world * n[i].  K must be a multiple of 256 (Q6_K: of 2048), n[i] >= 16, weights 16-byte aligned.
+ *
+ * light_b200_chain_build validates the program and writes its device form into `program`
+ *   (light_b200_chain_program_bytes(n_ops) bytes of device memory, 256-byte aligned) and zeroes this rank's
+ *   arena (light_b200_chain_arena_bytes bytes, 256-byte aligned; arena[p] = rank p's arena, peer-addressable
+ *   when world > 1, the same layout on every rank).  Do it once, outside stream capture.
+ * light_b200_chain_run enqueues one pass over the program: `step` (a device word, zeroed once) is bumped and
+ *   tags everything the pass writes.  Graph-capturable; allocates nothing; two launches.  Every wait inside
+ *   the kernel is bounded (about 200 ms without progress), after which light_b200_chain_status reports 1 and
+ *   the pass's outputs are not valid.  Passes over programs that share an arena must not overlap on the GPU,
+ *   and the GPU must be able to hold one thread block of the kernel on every SM at once (nothing else may
+ *   occupy it for longer than a launch). */
+typedef struct lb200_chain_op {
+  int32_t wtype;            /* LB200_Q4_K or LB200_Q6_K                                   */
+  int32_t K;
+  int32_t count;            /* matrices that share the activations: 1..4 (Q6_K: 1)        */
+  int32_t act;              /* 0, or 1 SiLU / 2 GELU gate (count == 2, result in out[0])  */
+  const void *w[4];         /* (n[i], K) blocks                                           */
+  int32_t n[4];
+  float *out[4];            /* plain f32 (n[i]) or NULL                                   */
+  int32_t out_vec[4];       /* chain vector or -1                                         */
+  const float *x;           /* plain activations (K), or NULL: x_vec                      */
+  int32_t x_vec;
+  int32_t res_vec;          /* -1, or the vector added to the activations before the norm */
+  int32_t sum_vec;          /* -1, or the vector that receives activations + residual     */
+  const float *norm_weight; /* (K) or NULL: no norm                                       */
+  float norm_eps;
+} lb200_chain_op;
+LB200_API size_t light_b200_chain_program_bytes(int n_ops);
+LB200_API int64_t light_b200_chain_arena_bytes(const lb200_chain_op *ops, int n_ops, int n_vecs, int world);
+LB200_API int light_b200_chain_build(const lb200_chain_op *ops, int n_ops, int n_vecs, void *program, size_t program_bytes,
+                                     void *const *arena, size_t arena_bytes, int world, int rank, int device, void *stream);
+LB200_API int light_b200_chain_run(const void *program, uint32_t *step, int device, void *stream);
+LB200_API int light_b200_chain_status(int device);
+
 #ifdef __cplusplus
 }
 #endif

@@ -46,6 +46,13 @@ class NormArgs(C.Structure):
     _fields_ = [("weight", C.c_void_p), ("residual", C.c_void_p), ("sum_out", C.c_void_p), ("eps", C.c_float)]
 
 
+class ChainOp(C.Structure):
+    """lb200_chain_op"""
+    _fields_ = [("wtype", C.c_int32), ("K", C.c_int32), ("count", C.c_int32), ("act", C.c_int32), ("w", C.c_void_p * 4),
+                ("n", C.c_int32 * 4), ("out", C.c_void_p * 4), ("out_vec", C.c_int32 * 4), ("x", C.c_void_p), ("x_vec", C.c_int32),
+                ("res_vec", C.c_int32), ("sum_vec", C.c_int32), ("norm_weight", C.c_void_p), ("norm_eps", C.c_float)]
+
+
 class DecodeAttnArgs(C.Structure):
     _fields_ = [
         ("q", C.c_void_p), ("kbuf", C.c_void_p), ("vbuf", C.c_void_p), ("k_new", C.c_void_p), ("v_new", C.c_void_p),
@@ -112,6 +119,12 @@ SYMBOLS = {
                                      C.c_int, C.c_void_p]),
     "light_b200_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_double, C.c_int, C.c_void_p]),
     "light_b200_decode_attn_status": (C.c_int, [C.c_int]),
+    "light_b200_chain_program_bytes": (C.c_size_t, [C.c_int]),
+    "light_b200_chain_arena_bytes": (C.c_int64, [C.POINTER(ChainOp), C.c_int, C.c_int, C.c_int]),
+    "light_b200_chain_build": (C.c_int, [C.POINTER(ChainOp), C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_size_t,
+                                         C.c_int, C.c_int, C.c_int, C.c_void_p]),
+    "light_b200_chain_run": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]),
+    "light_b200_chain_status": (C.c_int, [C.c_int]),
 }
 
 _lib = None

@@ -508,6 +508,42 @@ int light_b200_moe_route_status(int device) {
   return a | b;
 }
 
+size_t light_b200_chain_program_bytes(int n_ops) { return n_ops < 0 ? 0 : chain_program_bytes(n_ops); }
+
+int64_t light_b200_chain_arena_bytes(const lb200_chain_op *ops, int n_ops, int n_vecs, int world) {
+  if (!ops || n_ops < 1 || n_vecs < 0 || world < 1 || world > LB200_MAX_PEERS) return -1;
+  return chain_arena_bytes(ops, n_ops, n_vecs, world);
+}
+
+int light_b200_chain_build(const lb200_chain_op *ops, int n_ops, int n_vecs, void *program, size_t program_bytes, void *const *arena,
+                           size_t arena_bytes, int world, int rank, int device, void *stream) {
+  REQUIRE_PTR(ops, "chain_build");
+  REQUIRE_PTR(program, "chain_build");
+  REQUIRE_PTR(arena, "chain_build");
+  if (world < 1 || world > LB200_MAX_PEERS || rank < 0 || rank >= world)
+    return fail(LB200_E_SHAPE, "light_b200: chain_build: rank %d of %d", rank, world);
+  if (n_vecs < 0 || n_vecs > 4096) return fail(LB200_E_SHAPE, "light_b200: chain_build: %d chain vectors", n_vecs);
+  for (int p = 0; p < world; p++)
+    if (!arena[p] || !aligned(arena[p], 256)) return fail(LB200_E_ALIGN, "light_b200: chain_build: arena of rank %d is null or not 256-byte aligned", p);
+  if (!aligned(program, 256)) return fail(LB200_E_ALIGN, "light_b200: chain_build: program buffer not 256-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return chain_build(ops, n_ops, n_vecs, program, program_bytes, arena, arena_bytes, world, rank, (cudaStream_t)stream);
+}
+
+int light_b200_chain_run(const void *program, uint32_t *step, int device, void *stream) {
+  REQUIRE_PTR(program, "chain_run");
+  REQUIRE_PTR(step, "chain_run");
+  if (int rc = bind(device)) return rc;
+  return chain_run(program, step, (cudaStream_t)stream);
+}
+
+int light_b200_chain_status(int device) {
+  if (int rc = bind(device)) return rc;
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail((int)e, "light_b200: chain_status: %s", cudaGetErrorString(e));
+  return chain_status();
+}
+
 int light_b200_argmax(const float *x, int64_t *out, int64_t rows, int cols, int device, void *stream) {
   if (int rc = bind(device)) return rc;
   return argmax_rows(x, out, rows, cols, (cudaStream_t)stream);

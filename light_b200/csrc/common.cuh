@@ -128,6 +128,12 @@ int moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, floa
 int moe_sort_pairs(const int64_t *ids, int *counts, int *offsets, int64_t *sorted_pairs, int64_t *sorted_expts, int *scratch, long long M,
                    int E, cudaStream_t st);
 int moe_route_status();
+size_t chain_program_bytes(int n_ops);
+long long chain_arena_bytes(const lb200_chain_op *ops, int n_ops, int n_vecs, int world);
+int chain_build(const lb200_chain_op *ops, int n_ops, int n_vecs, void *program, size_t program_bytes, void *const *arena, size_t arena_bytes,
+                int world, int rank, cudaStream_t st);
+int chain_run(const void *program, unsigned int *step, cudaStream_t st);
+int chain_status();
 int moe_bad_ids_status();  // 0 / 1, or a CUDA error code (> 1)
 int fp8_gemv_fast(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR, int bC,
                   cudaStream_t st);
