@@ -165,8 +165,8 @@ LB200_API int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const f
  * int32 SCRATCH the caller provides; the call fills them (offsets = exclusive prefix sum of the
  * per-expert pair counts) and they are valid outputs afterwards.  Rows of `out` whose pair id
  * does not appear (or is outside [0, size_m)) are left untouched.  An expert id outside [0, E) never
- * indexes anything: a negative id owns no range and its pair is skipped, an id >= E is skipped by the
- * matmul and counted under the last expert's boundary; either is reported by light_b200_moe_route_status. */
+ * indexes anything: a negative id owns no range, an id >= E lies at or beyond offsets[E] (which then is the
+ * index of the first such pair instead of M); their pairs are skipped, and light_b200_moe_route_status reports it. */
 typedef struct lb200_moe_args {
   const void *input;          /* (rows, K) at dtype (moe_gemm) or f32 (moe_gemm_q)          */
   const void *weights;        /* (E, N, K) at dtype, or GGUF blocks of ggml_type            */

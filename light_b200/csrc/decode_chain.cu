@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
 
 __global__ void chain_step_kernel(unsigned int *step) { *step += 1; }
 
-bool g_chain_bulk = true;  // LIGHT_B200_CHAIN_BULK=0: 16-byte cp.async copies instead of bulk copies (A/B knob)
+bool g_chain_bulk = false;  // LIGHT_B200_CHAIN_BULK=1: bulk copies (one row piece per lane) instead of 16-byte cp.async copies: measured slower (2.2 against 2.9 TB/s on one large Q4_K matrix)
 
 }  // namespace
 
@@ -730,6 +730,14 @@ int chain_build(const lb200_chain_op *ops, int n_ops, int n_vecs, void *program,
     } else if (o.res_vec >= 0 || o.sum_vec >= 0) {
       return fail(LB200_E_SHAPE, "light_b200: chain_build: operator %d: residual / sum vectors need a norm weight", i);
     }
+    // an operator never writes a vector it reads: other CTAs may still be polling the old tag
+    for (int j = 0; j < 4; j++) {
+      const int ov = j < (o.act ? 1 : o.count) ? o.out_vec[j] : -1;
+      if (ov >= 0 && ((!o.x && ov == o.x_vec) || ov == o.res_vec || ov == o.sum_vec))
+        return fail(LB200_E_SHAPE, "light_b200: chain_build: operator %d: output %d goes to a vector the operator itself reads or writes", i, j);
+    }
+    if (o.sum_vec >= 0 && ((!o.x && o.sum_vec == o.x_vec) || o.sum_vec == o.res_vec))
+      return fail(LB200_E_SHAPE, "light_b200: chain_build: operator %d: sum_vec is the vector its activations or residual come from", i);
     // what this operator writes carries its tag from here on
     if (o.sum_vec >= 0) tag_of[o.sum_vec] = i + 1;
     for (int j = 0; j < (o.act ? 1 : o.count); j++)

@@ -16,10 +16,11 @@ namespace lb {
 // reports it together with the routing kernels' own word).
 __device__ unsigned int g_moe_bad_ids;
 
-// offsets[e] = first sorted index whose expert id is >= e; offsets[E] = M.  Nobody validates the ids before
-// this kernel, so it does: both ends of a boundary are clamped into [-1, E - 1] and made non-decreasing
-// before they index anything.  A negative id therefore owns no range (the matmul kernel skips such pairs
-// too), an id >= E is counted under the last expert's boundary, and either sets the status word.
+// offsets[e] = first sorted index whose expert id is >= e, for e <= E (so offsets[E] = M when every id is an
+// expert).  Nobody validates the ids before this kernel, so it does: both ends of a boundary are clamped
+// into [-1, E] and made non-decreasing before they index anything.  A negative id therefore owns no range,
+// an id >= E lies at or beyond offsets[E], outside every expert's range (the matmul kernels skip both), and
+// either sets the status word.
 __global__ void moe_offsets_kernel(const int64_t *__restrict__ ids, int32_t *__restrict__ offsets, long long M, int E) {
   long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (M == 0) {
@@ -29,8 +30,8 @@ __global__ void moe_offsets_kernel(const int64_t *__restrict__ ids, int32_t *__r
   if (i >= M) return;
   long long cur = ids[i], prev = i == 0 ? -1 : ids[i - 1];
   if (cur < 0 || cur >= E) g_moe_bad_ids = 1u;
-  cur = cur < -1 ? -1 : (cur >= E ? E - 1 : cur);
-  prev = prev < -1 ? -1 : (prev >= E ? E - 1 : prev);
+  cur = cur < -1 ? -1 : (cur > E ? E : cur);
+  prev = prev < -1 ? -1 : (prev > E ? E : prev);
   if (cur < prev) cur = prev;  // unsorted input: no boundary here, and no store below
   for (long long e = prev + 1; e <= cur; e++) offsets[e] = (int32_t)i;
   if (i == M - 1)

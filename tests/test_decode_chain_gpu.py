@@ -107,16 +107,17 @@ def _layers(cuda, oracle, H, KV, F, V, L):
     vq, vo, va, vd, vh = c.vec(), c.vec(), c.vec(), c.vec(), [c.vec(), c.vec()]
     cur = None  # the vector holding the residual stream (None: plain h0)
     for l in range(L):
-        kw = dict(x=h0) if cur is None else dict(x_vec=cur, res_vec=vd, sum_vec=vh[l % 2])
+        other = None if cur is None else (vh[0] if cur == vh[1] else vh[1])   # the new sum never overwrites the vector it is read from
+        kw = dict(x=h0) if cur is None else dict(x_vec=cur, res_vec=vd, sum_vec=other)
         c.matmul([W[l]["q"][0], W[l]["k"][0], W[l]["v"][0]], outs=[None, k_out[l], v_out[l]], out_vecs=[vq, None, None],
                  norm_weight=nw[2 * l], eps=1e-5, **kw)
-        stream1 = None if cur is None else vh[l % 2]
+        stream1 = other
         c.matmul([W[l]["o"][0]], x_vec=vq, out_vecs=[vo])
         if stream1 is None:   # layer 0: the stream is still the plain h0
             c.matmul([W[l]["g"][0], W[l]["u"][0]], x=h0, res_vec=vo, sum_vec=vh[1], act=1, out_vecs=[va], norm_weight=nw[2 * l + 1], eps=1e-5)
             cur = vh[1]
         else:
-            nxt = vh[(l + 1) % 2]
+            nxt = vh[0] if stream1 == vh[1] else vh[1]
             c.matmul([W[l]["g"][0], W[l]["u"][0]], x_vec=stream1, res_vec=vo, sum_vec=nxt, act=1, out_vecs=[va], norm_weight=nw[2 * l + 1], eps=1e-5)
             cur = nxt
         c.matmul([W[l]["d"][0]], x_vec=va, out_vecs=[vd])
@@ -146,7 +147,7 @@ def _layers(cuda, oracle, H, KV, F, V, L):
     return c, (h0, k_out, v_out, logits), reference
 
 
-@pytest.mark.parametrize("H,KV,F,V,L", [(1024, 256, 2048, 3000, 3), (4096, 1024, 14336, 5008, 2)])
+@pytest.mark.parametrize("H,KV,F,V,L", [(2048, 256, 4096, 3000, 3), (4096, 1024, 14336, 5008, 2)])
 def test_decoder_layers_as_one_launch(cuda, oracle, H, KV, F, V, L):
     c, (h0, k_out, v_out, logits), reference = _layers(cuda, oracle, H, KV, F, V, L)
     want, ks = reference()
@@ -190,6 +191,15 @@ def test_build_rejects_bad_programs(cuda, oracle):
     c = chain.DecodeChain(cuda)
     v = c.vec()
     c.matmul([w], x_vec=v, outs=[torch.empty(64, device=cuda)])    # reads a vector nobody wrote
+    with pytest.raises(_lib.Light200Error):
+        c.build()
+    c = chain.DecodeChain(cuda)
+    v, v2 = c.vec(), c.vec()
+    nwt = torch.ones(512, device=cuda)
+    w5, _ = _w(3, ops.Q4_K, 512, 512, cuda, oracle)
+    c.matmul([w5], x=x, out_vecs=[v])
+    c.matmul([w5], x_vec=v, out_vecs=[v2])
+    c.matmul([w5], x_vec=v2, res_vec=v, sum_vec=v2, norm_weight=nwt, eps=1e-5, outs=[torch.empty(512, device=cuda)])   # sum over its own input
     with pytest.raises(_lib.Light200Error):
         c.build()
     c = chain.DecodeChain(cuda)

@@ -56,7 +56,8 @@ def test_moe_bad_expert_ids_are_contained(cuda):
         g = guard.cpu()
         assert (g[:G] == -7).all() and (g[G + E:G + E + G] == -7).all() and (g[-G:] == -7).all(), ("guard bands", ids_l, g.tolist())
         off = offsets.cpu().tolist()
-        assert all(0 <= o <= M for o in off) and off == sorted(off) and off[-1] == M, off
+        assert all(0 <= o <= M for o in off) and off == sorted(off), off
+        assert off[-1] == sum(1 for e in ids_l if e < E), off      # offsets[E]: the first pair whose id is not an expert
         for i, e in enumerate(ids_l):
             row = out[i].cpu()
             if 0 <= e < E:
