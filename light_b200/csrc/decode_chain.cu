@@ -64,7 +64,10 @@ constexpr int RED_FLOATS = 2 * CW * GROUP * ROWS;  // two parities
 constexpr int SMEM_RED = RING + CW * SLAB;
 constexpr int SMEM_NRM = SMEM_RED + RED_FLOATS * 4;  // [2][CW] floats
 constexpr int SMEM_BAR = SMEM_NRM + 2 * CW * 4;
-constexpr int SMEM_BYTES = SMEM_BAR + CW * STAGES * 8;
+constexpr int SMEM_ZERO = SMEM_BAR + CW * STAGES * 8;  // what the B-fragment loads of lanes outside an MMA's live columns read
+constexpr int ZERO_BYTES = 160;
+constexpr int SMEM_ABORT = SMEM_ZERO + ZERO_BYTES;  // one int: a bounded wait of this CTA gave up
+constexpr int SMEM_BYTES = SMEM_ABORT + 16;
 
 constexpr uint32_t NONE = 0xFFFFFFFFu;
 
@@ -99,17 +102,6 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// shared-memory loads that inactive lanes do not perform (they get zeros)
-__device__ __forceinline__ uint2 lds64_if(uint32_t addr, uint32_t on) {
-  uint2 v = make_uint2(0u, 0u);
-  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %3, 0;\n\t@q ld.shared.v2.u32 {%0,%1}, [%2];\n\t}\n" : "+r"(v.x), "+r"(v.y) : "r"(addr), "r"(on));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds32_if(uint32_t addr, uint32_t on) {
-  uint32_t v = 0u;
-  asm volatile("{\n\t.reg .pred q;\n\tsetp.ne.u32 q, %2, 0;\n\t@q ld.shared.u32 %0, [%1];\n\t}\n" : "+r"(v) : "r"(addr), "r"(on));
-  return v;
-}
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(addr), "r"(v)); }
 __device__ __forceinline__ uint32_t lds16u(uint32_t addr) {
   uint16_t v;
@@ -130,37 +122,32 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
-struct Wait {  // the launch's one clock for bounded waits
-  unsigned long long t0 = 0;
-  bool gave_up = false;
-  __device__ __forceinline__ bool expired() {  // called every few hundred polls
-    const unsigned long long t = umma::global_ns();
-    if (t0 == 0) t0 = t;
-    if (t - t0 > 200000000ull) {  // 200 ms without progress: a producer is gone
-      g_chain_status = 1u;
-      gave_up = true;
-    }
-    return gave_up;
+// Bounded waits: every poll loop calls this now and then.  It gives up 200 ms after the loop's own start, or as
+// soon as any thread of the CTA has given up (the flag in shared memory), sets the sticky status word, and from
+// then on every wait of the CTA falls through: the launch ends quickly, with outputs that are not valid.
+__device__ __forceinline__ bool wait_expired(volatile int *abort_flag, unsigned long long &t0) {
+  if (*abort_flag) return true;
+  const unsigned long long t = umma::global_ns();
+  if (t0 == 0) t0 = t;
+  if (t - t0 > 200000000ull) {
+    g_chain_status = 1u;
+    *abort_flag = 1;
+    return true;
   }
-  __device__ __forceinline__ void progress() { t0 = 0; }
-};
-
-// four consecutive slots -> four values, once all four carry `tag`
-__device__ __forceinline__ float4 ld_slots4(const uint2 *s, unsigned int tag, Wait &wt) {
-  uint4 a, b;
-  for (unsigned int it = 0;; it++) {
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(a.x), "=r"(a.y), "=r"(a.z), "=r"(a.w) : "l"(s) : "memory");
-    asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(b.x), "=r"(b.y), "=r"(b.z), "=r"(b.w) : "l"(s + 2) : "memory");
-    if ((a.y == tag && a.w == tag && b.y == tag && b.w == tag) || wt.gave_up) break;
-    if ((it & 255u) == 255u && wt.expired()) break;
-    __nanosleep(200);  // the polls of 148 x 16 warps share L2 with the weight stream
-  }
-  return make_float4(__uint_as_float(a.x), __uint_as_float(a.z), __uint_as_float(b.x), __uint_as_float(b.z));
+  return false;
 }
-__device__ __forceinline__ void st_slot(uint8_t *const (&arena)[LB200_MAX_PEERS], int world, uint32_t off, size_t e, float v, unsigned int tag) {
-  for (int p = 0; p < world; p++)
-    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(reinterpret_cast<uint2 *>(arena[p] + off) + e), "r"(__float_as_uint(v)), "r"(tag)
+
+// one value, tagged, into the same slot of every rank's arena (one rank: this GPU's own)
+__device__ __forceinline__ void st_slot(const Header *hd, uint8_t *arena_me, int world, uint32_t off, size_t e, float v, unsigned int tag) {
+  if (world == 1) {
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(reinterpret_cast<uint2 *>(arena_me + off) + e), "r"(__float_as_uint(v)), "r"(tag)
                  : "memory");
+    return;
+  }
+  for (int p = 0; p < world; p++) {
+    uint8_t *a = (uint8_t *)__ldg(reinterpret_cast<const unsigned long long *>(&hd->arena[p]));
+    asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(reinterpret_cast<uint2 *>(a + off) + e), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+  }
 }
 
 __device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
@@ -246,6 +233,83 @@ __device__ __forceinline__ void cta_share(int tiles, int act, int &t0, int &t1) 
   t1 = (int)((uint32_t)lt * (blockIdx.x + 1) / gridDim.x) * unit;
 }
 
+// A block of x into the warp's slab (once per operator when K <= 4096: the warp's block never changes).  All the
+// slots a lane needs -- eight of the activations, eight of the residual -- are requested together and checked
+// together: one trip to L2 when they are there.  With a norm: the activations are s = x + residual, the writer
+// CTA stores s into the sum vector, the slab receives s * weight and the function returns this lane's share of
+// sum(s^2) (0 without a norm).
+__device__ __forceinline__ float stage_block(const OpDev *op, const Header *hd, uint8_t *arena_me, int b, uint32_t slab, int lane, int world,
+                                          unsigned int tag0, unsigned int tag_me, bool writer, int kind, volatile int *abort_flag) {
+  const int e0 = b * 256 + lane * 4;
+  const float *x_plain = (const float *)__ldg(reinterpret_cast<const unsigned long long *>(&op->x_plain));
+  const float *norm_w = (const float *)__ldg(reinterpret_cast<const unsigned long long *>(&op->norm_w));
+  const uint32_t x_off = __ldg(&op->x_off), res_off = __ldg(&op->res_off), sum_off = __ldg(&op->sum_off);
+  const unsigned int tag_x = tag0 + __ldg(&op->x_tag), tag_r = tag0 + __ldg(&op->res_tag);
+  float nrm_ss = 0.f;
+  float4 wn[2];
+  if (norm_w) wn[0] = __ldg(reinterpret_cast<const float4 *>(norm_w + e0)), wn[1] = __ldg(reinterpret_cast<const float4 *>(norm_w + e0 + 128));
+  float4 xv[2];
+  const bool has_res = norm_w && res_off != NONE;
+  if (x_plain) {
+    xv[0] = __ldcg(reinterpret_cast<const float4 *>(x_plain + e0));
+    xv[1] = __ldcg(reinterpret_cast<const float4 *>(x_plain + e0 + 128));
+  }
+  if (!x_plain || has_res) {
+    const uint2 *xs = x_plain ? nullptr : reinterpret_cast<const uint2 *>(arena_me + x_off) + e0;
+    const uint2 *rs = has_res ? reinterpret_cast<const uint2 *>(arena_me + res_off) + e0 : nullptr;
+    uint4 a[4], r[4];
+    auto ld16 = [](const uint2 *p) {
+      uint4 v;
+      asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+      return v;
+    };
+    unsigned long long ts = 0;
+    for (unsigned int it = 1;; it++) {
+      bool ok = true;
+      if (xs) {
+        a[0] = ld16(xs), a[1] = ld16(xs + 2), a[2] = ld16(xs + 128), a[3] = ld16(xs + 130);
+#pragma unroll
+        for (int i = 0; i < 4; i++) ok = ok && a[i].y == tag_x && a[i].w == tag_x;
+      }
+      if (rs) {
+        r[0] = ld16(rs), r[1] = ld16(rs + 2), r[2] = ld16(rs + 128), r[3] = ld16(rs + 130);
+#pragma unroll
+        for (int i = 0; i < 4; i++) ok = ok && r[i].y == tag_r && r[i].w == tag_r;
+      }
+      if (ok) break;
+      if ((it & 31u) == 0u && wait_expired(abort_flag, ts)) break;
+      __nanosleep(100);  // the polls of 148 x 16 warps share L2 with the weight stream
+    }
+    if (xs) {
+      xv[0] = make_float4(__uint_as_float(a[0].x), __uint_as_float(a[0].z), __uint_as_float(a[1].x), __uint_as_float(a[1].z));
+      xv[1] = make_float4(__uint_as_float(a[2].x), __uint_as_float(a[2].z), __uint_as_float(a[3].x), __uint_as_float(a[3].z));
+    }
+    if (rs) {
+      xv[0].x += __uint_as_float(r[0].x), xv[0].y += __uint_as_float(r[0].z), xv[0].z += __uint_as_float(r[1].x), xv[0].w += __uint_as_float(r[1].z);
+      xv[1].x += __uint_as_float(r[2].x), xv[1].y += __uint_as_float(r[2].z), xv[1].z += __uint_as_float(r[3].x), xv[1].w += __uint_as_float(r[3].z);
+    }
+  }
+  if (norm_w) {
+#pragma unroll
+    for (int i = 0; i < 2; i++) {
+      const int e = e0 + i * 128;
+      if (sum_off != NONE && writer) {
+        st_slot(hd, arena_me, world, sum_off, e, xv[i].x, tag_me), st_slot(hd, arena_me, world, sum_off, e + 1, xv[i].y, tag_me);
+        st_slot(hd, arena_me, world, sum_off, e + 2, xv[i].z, tag_me), st_slot(hd, arena_me, world, sum_off, e + 3, xv[i].w, tag_me);
+      }
+      nrm_ss = fmaf(xv[i].x, xv[i].x, fmaf(xv[i].y, xv[i].y, fmaf(xv[i].z, xv[i].z, fmaf(xv[i].w, xv[i].w, nrm_ss))));
+      xv[i].x *= wn[i].x, xv[i].y *= wn[i].y, xv[i].z *= wn[i].z, xv[i].w *= wn[i].w;
+    }
+  }
+  __syncwarp();  // every lane is done reading the slab of the block before
+  if (kind)
+    stage3<true>(xv, slab, lane);
+  else
+    stage3<false>(xv, slab, lane);
+  __syncwarp();
+  return nrm_ss;
+}
+
 template <bool BULK>
 __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict__ program, const unsigned int *__restrict__ step) {
   extern __shared__ __align__(128) unsigned char dyn[];
@@ -262,19 +326,34 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
     for (int s = 0; s < STAGES; s++) umma::mbar_init(bar0 + 8 * s, BULK ? 1u : 32u);
     umma::fence_barrier_init();
   }
-  __syncwarp();
+  if (threadIdx.x < (ZERO_BYTES + 16) / 4) reinterpret_cast<uint32_t *>(dyn + SMEM_ZERO)[threadIdx.x] = 0u;
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(dyn + SMEM_ABORT);
+  const uint32_t zpage = sbase + SMEM_ZERO;
+  __syncthreads();
 
   const Header *hd = reinterpret_cast<const Header *>(program);
   const OpDev *ops = reinterpret_cast<const OpDev *>(program + HEADER_BYTES);
   const int n_ops = __ldg(&hd->n_ops), world = __ldg(&hd->world), rank = __ldg(&hd->rank);
-  uint8_t *arena[LB200_MAX_PEERS];
-#pragma unroll
-  for (int p = 0; p < LB200_MAX_PEERS; p++) arena[p] = p < world ? (uint8_t *)__ldg(reinterpret_cast<const unsigned long long *>(&hd->arena[p])) : nullptr;
+  uint8_t *const arena_me = (uint8_t *)__ldg(reinterpret_cast<const unsigned long long *>(&hd->arena[rank]));
 
   // ---- the weight requests: a cursor over (operator, group of row tiles, K block of this warp, tile), which
   // is exactly the order in which the arithmetic below consumes them, STAGES tiles ahead of it
-  int i_op = -1, i_gt = 0, i_t1 = 0, i_gs = 0, i_b = 0, i_rt = 0, i_nb = 0, i_kind = 0, i_slot = 0, in_flight = 0;
-  uint32_t i_rb = 0;
+  int i_op = -1, i_gt = 0, i_t1 = 0, i_gs = 0, i_b = 0, i_rt = 0, i_nb = 0, i_kind = 0, i_slot = 0;
+  uint32_t i_rb = 0, i_blk = 144u;
+  // this lane's first copy inside a tile, fixed per operator.  Q4_K: lanes 0..26 copy granule lane % 9 of rows
+  // 3i + lane / 9, i = 0..4 (consecutive lanes, consecutive bytes), lanes 0..8 also row 15; Q6_K: lanes 0..13 /
+  // 16..29 copy one of the 14 granules of rows 2i / 2i+1, i = 0..7
+  uint32_t i_so = 0u;
+  unsigned long long i_tb = 0;  // lane rt < i_gs: first byte of row tile i_gt + rt of the current group
+  auto load_group = [&]() {
+    i_tb = 0;
+    if (lane < i_gs) {
+      const OpDev *op = ops + i_op;
+      int j, r0;
+      resolve_tile(op, i_gt + lane, j, r0);
+      i_tb = __ldg(reinterpret_cast<const unsigned long long *>(&op->w[j])) + (unsigned long long)r0 * i_rb;
+    }
+  };
   auto next_op = [&]() {  // first operator after i_op in which this warp has tiles
     for (i_op++; i_op < n_ops; i_op++) {
       const OpDev *op = ops + i_op;
@@ -283,20 +362,19 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
       i_nb = __ldg(&op->K) >> 8;
       if (t0 < t1 && warp < i_nb) {
         i_kind = __ldg(&op->kind);
-        i_rb = (uint32_t)i_nb * (i_kind ? 210u : 144u);
+        i_blk = i_kind ? 210u : 144u;
+        i_rb = (uint32_t)i_nb * i_blk;
+        i_so = i_kind ? (uint32_t)(lane >> 4) * i_rb + (uint32_t)(lane & 15) * 16u : (uint32_t)(lane / 9) * i_rb + (uint32_t)(lane % 9) * 16u;
         i_gt = t0, i_t1 = t1, i_gs = min(GROUP, t1 - t0), i_b = warp, i_rt = 0;
-        if (i_op + 1 < n_ops) asm volatile("prefetch.global.L2 [%0];\n" ::"l"(ops + i_op + 1));
+        load_group();
         return;
       }
     }
   };
   auto issue = [&]() {
-    if (i_op >= n_ops) return;
-    const OpDev *op = ops + i_op;
-    int j, r0;
-    resolve_tile(op, i_gt + i_rt, j, r0);
-    const uint8_t *w = (const uint8_t *)__ldg(reinterpret_cast<const unsigned long long *>(&op->w[j]));
-    const uint8_t *base = w + ((size_t)r0 * i_rb + (uint32_t)i_b * (i_kind ? 210u : 144u));
+    if (i_op < n_ops) {
+    const uint32_t tlo = __shfl_sync(0xffffffffu, (uint32_t)i_tb, i_rt), thi = __shfl_sync(0xffffffffu, (uint32_t)(i_tb >> 32), i_rt);
+    const uint8_t *base = reinterpret_cast<const uint8_t *>(((unsigned long long)thi << 32) | tlo) + (uint32_t)i_b * i_blk;
     const uint32_t dst = ring + i_slot * SLOT, bar = bar0 + 8 * i_slot;
     if constexpr (BULK) {
       if (lane == 0) umma::mbar_arrive_expect_tx(bar, (uint32_t)ROWS * (i_kind ? (uint32_t)Q6_COPY : (uint32_t)Q4_PITCH));
@@ -309,33 +387,39 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
           bulk_g2s(dst + lane * Q4_PITCH, src, Q4_PITCH, bar);
       }
     } else {
-      if (i_kind) {  // lanes 0..13 / 16..29 copy the 14 granules of rows 2i / 2i+1
-        const uint32_t rsub = lane >> 4, piece = lane & 15;
-        if (piece < 14) {
+      if (i_kind) {
+        if ((lane & 15) < 14) {
+          const uint8_t *src = reinterpret_cast<const uint8_t *>((uintptr_t)base & ~(uintptr_t)15) + i_so;
+          uint32_t d = dst + (lane >> 4) * Q6_PITCH + (lane & 15) * 16;
 #pragma unroll
           for (int i = 0; i < 8; i++) {
-            const uint8_t *src = base + (size_t)(2 * i + rsub) * i_rb;
-            cp_async16(dst + (2 * i + rsub) * Q6_PITCH + piece * 16, (const uint8_t *)((uintptr_t)src & ~(uintptr_t)15) + piece * 16);
+            cp_async16(d, src);
+            src += 2u * i_rb, d += 2 * Q6_PITCH;
           }
         }
-      } else {  // 144 granules of 16 bytes: lane l takes granules l, l + 32, ...
+      } else {
+        if (lane < 27) {
+          const uint8_t *src = base + i_so;
+          const uint32_t d = dst + lane * 16;  // row r' of a triple starts 9 granules after row r' - 1: the tile is dense
 #pragma unroll
-        for (int i = 0; i < 5; i++) {
-          const uint32_t c = lane + 32 * i, row = c / 9u;
-          if (c < 144u) cp_async16(dst + c * 16, base + (size_t)row * i_rb + (c - 9u * row) * 16u);
+          for (int i = 0; i < 5; i++) cp_async16(d + i * (3 * Q4_PITCH), src + (size_t)i * (3u * i_rb));
+          if (lane < 9) cp_async16(d + 15 * Q4_PITCH, src + (size_t)15u * i_rb);
         }
       }
       cp_async_arrive_noinc(bar);
     }
-    in_flight++;
-    i_slot = i_slot + 1 == STAGES ? 0 : i_slot + 1;
     if (++i_rt == i_gs) {
       i_rt = 0, i_b += CW;
       if (i_b >= i_nb) {
         i_b = warp, i_gt += i_gs, i_gs = min(GROUP, i_t1 - i_gt);
-        if (i_gt >= i_t1) next_op();
+        if (i_gt >= i_t1)
+          next_op();
+        else
+          load_group();
       }
     }
+      }
+    i_slot = i_slot + 1 == STAGES ? 0 : i_slot + 1;  // also past the end of the program: the arithmetic's slot index follows this one
   };
   next_op();
 #pragma unroll 1
@@ -343,180 +427,171 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
 
   pdl_wait();  // activations and the step word are earlier launches' outputs; the weights requested above are not
   const unsigned int tag0 = (*reinterpret_cast<const volatile unsigned int *>(step)) << 10;
-  Wait wt;
-  int c_slot = 0;
-  uint32_t c_phase = 0;
+  uint32_t c_phase = 0;  // (the slot consumed next is the slot requested next: i_slot)
   int parity = 0;
   auto slot_wait = [&]() -> uint32_t {  // the next tile of this warp has landed; returns its shared address
-    const uint32_t bar = bar0 + 8 * c_slot;
-    if (!wt.gave_up) {
-      for (unsigned int it = 0; !umma::mbar_test_wait(bar, c_phase); it++)
-        if ((it & 1023u) == 1023u && wt.expired()) break;
+    const uint32_t bar = bar0 + 8 * i_slot;
+    if (!umma::mbar_test_wait(bar, c_phase)) {
+      unsigned long long ts = 0;
+      for (unsigned int it = 1; !umma::mbar_test_wait(bar, c_phase); it++)
+        if ((it & 255u) == 0u && wait_expired(abort_flag, ts)) break;
     }
-    const uint32_t sb = ring + c_slot * SLOT;
-    if (++c_slot == STAGES) c_slot = 0, c_phase ^= 1u;
-    in_flight--;
+    const uint32_t sb = ring + i_slot * SLOT;
+    if (i_slot + 1 == STAGES) c_phase ^= 1u;
     return sb;
   };
 
   const bool hdr_hi = t >= 2;
   const int hdr_sh = (t & 1) * 16;
   // B-fragment addresses inside the slab (see the unit bodies)
-  const uint32_t own4 = (g >> 1) == t;  // Q4_K: this lane's column belongs to the sub-block pair of A-lane t
-  const uint32_t pe1 = slab + ((g & 1) ? X4_PLANE : 0) + (2 * t) * X4_SUB;           // even MMA, (hi | mid) of sub-block 2t
-  const uint32_t pe2 = slab + 2 * X4_PLANE + (2 * t) * X4_SUB;                       // even MMA, lo (column 2t only)
-  const uint32_t po1 = slab + ((g & 1) ? 0 : X4_PLANE) + (2 * t + 1) * X4_SUB;       // odd MMA, (mid | hi) of sub-block 2t+1
-  const uint32_t po2 = slab + 2 * X4_PLANE + (2 * t + 1) * X4_SUB;                   // odd MMA, lo (column 2t+1 only)
-  const uint32_t lo_e = own4 && !(g & 1), lo_o = own4 && (g & 1);
+  // (lanes whose column is not live in an MMA read the zero page instead)
+  const bool own4 = (g >> 1) == t;  // Q4_K: this lane's column belongs to the sub-block pair of A-lane t
+  const uint32_t pe1 = own4 ? slab + ((g & 1) ? X4_PLANE : 0) + (2 * t) * X4_SUB : zpage;            // even MMA, (hi | mid) of sub-block 2t
+  const uint32_t pe2 = own4 && !(g & 1) ? slab + 2 * X4_PLANE + (2 * t) * X4_SUB : zpage;            // even MMA, lo (column 2t only)
+  const uint32_t po1 = own4 ? slab + ((g & 1) ? 0 : X4_PLANE) + (2 * t + 1) * X4_SUB : zpage;        // odd MMA, (mid | hi) of sub-block 2t+1
+  const uint32_t po2 = own4 && (g & 1) ? slab + 2 * X4_PLANE + (2 * t + 1) * X4_SUB : zpage;         // odd MMA, lo (column 2t+1 only)
   const uint32_t q6sel = g >> 1;  // Q6_K: the group (0..3) whose sub-blocks this column serves
-  const uint32_t p6a = slab + ((g & 1) ? X6_PLANE : 0) + 32 * q6sel + 4 * t;         // (hi | mid), + 128 h + 16 u
-  const uint32_t p6b = slab + 2 * X6_PLANE + 32 * q6sel + 4 * t;                     // lo (even columns only)
-  const uint32_t lo6 = !(g & 1);
+  const uint32_t p6a = slab + ((g & 1) ? X6_PLANE : 0) + 32 * q6sel + 4 * t;                         // (hi | mid), + 128 h + 16 u
+  const uint32_t p6b = (g & 1) ? zpage : slab + 2 * X6_PLANE + 32 * q6sel + 4 * t;                   // lo (even columns only)
 
   for (int oi = 0; oi < n_ops; oi++) {
     const OpDev *op = ops + oi;
+    if (oi + 1 < n_ops && lane == 0) {  // the next operator's record into L1 while this one computes
+      asm volatile("prefetch.global.L1 [%0];\n" ::"l"(reinterpret_cast<const uint8_t *>(op + 1)));
+      asm volatile("prefetch.global.L1 [%0];\n" ::"l"(reinterpret_cast<const uint8_t *>(op + 1) + 128));
+    }
     const int kind = __ldg(&op->kind), K = __ldg(&op->K), act = __ldg(&op->act), nb = K >> 8;
     int t0, t1;
     cta_share(__ldg(&op->tiles), act, t0, t1);
-    const float *x_plain = (const float *)__ldg(reinterpret_cast<const unsigned long long *>(&op->x_plain));
-    const float *norm_w = (const float *)__ldg(reinterpret_cast<const unsigned long long *>(&op->norm_w));
-    const uint32_t x_off = __ldg(&op->x_off), res_off = __ldg(&op->res_off), sum_off = __ldg(&op->sum_off);
-    const unsigned int tag_x = tag0 + __ldg(&op->x_tag), tag_r = tag0 + __ldg(&op->res_tag), tag_me = tag0 + (unsigned)oi + 1u;
+    const bool has_norm = __ldg(reinterpret_cast<const unsigned long long *>(&op->norm_w)) != 0ull;
+    const unsigned int tag_me = tag0 + (unsigned)oi + 1u;
     const uint32_t row_bytes = (uint32_t)nb * (kind ? 210u : 144u);
     const bool writer = blockIdx.x == gridDim.x - 1;  // the CTA that always has tiles writes x + residual
     float nrm_ss = 0.f, nrm_inv = 1.f;
     int staged = -1;
 
-    // a block of x into the slab (once per operator when K <= 4096: the warp's block never changes)
     auto stage = [&](int b) {
-      float4 xv[2];
-      if (x_plain) {
-        xv[0] = __ldcg(reinterpret_cast<const float4 *>(x_plain + b * 256) + lane);
-        xv[1] = __ldcg(reinterpret_cast<const float4 *>(x_plain + b * 256 + 128) + lane);
-      } else {
-        const uint2 *xs = reinterpret_cast<const uint2 *>(arena[rank] + x_off) + b * 256 + lane * 4;
-        xv[0] = ld_slots4(xs, tag_x, wt);
-        xv[1] = ld_slots4(xs + 128, tag_x, wt);
-      }
-      if (norm_w) {
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-          const int e = b * 256 + i * 128 + lane * 4;
-          if (res_off != NONE) {
-            const float4 r = ld_slots4(reinterpret_cast<const uint2 *>(arena[rank] + res_off) + e, tag_r, wt);
-            xv[i].x += r.x, xv[i].y += r.y, xv[i].z += r.z, xv[i].w += r.w;
-          }
-          if (sum_off != NONE && writer) {
-            st_slot(arena, world, sum_off, e, xv[i].x, tag_me), st_slot(arena, world, sum_off, e + 1, xv[i].y, tag_me);
-            st_slot(arena, world, sum_off, e + 2, xv[i].z, tag_me), st_slot(arena, world, sum_off, e + 3, xv[i].w, tag_me);
-          }
-          nrm_ss = fmaf(xv[i].x, xv[i].x, fmaf(xv[i].y, xv[i].y, fmaf(xv[i].z, xv[i].z, fmaf(xv[i].w, xv[i].w, nrm_ss))));
-          const float4 wn = __ldg(reinterpret_cast<const float4 *>(norm_w + e));
-          xv[i].x *= wn.x, xv[i].y *= wn.y, xv[i].z *= wn.z, xv[i].w *= wn.w;
-        }
-      }
-      __syncwarp();  // every lane is done reading the slab of the block before
-      if (kind)
-        stage3<true>(xv, slab, lane);
-      else
-        stage3<false>(xv, slab, lane);
-      __syncwarp();
+      nrm_ss += stage_block(op, hd, arena_me, b, slab, lane, world, tag0, tag_me, writer, kind, abort_flag);
       staged = b;
     };
     for (int gt = t0; gt < t1; gt += GROUP, parity ^= 1) {
       const int gs = min(GROUP, t1 - gt);
-      float acc[GROUP][2];
-#pragma unroll
-      for (int r = 0; r < GROUP; r++) acc[r][0] = acc[r][1] = 0.f;
+      // partial sums of this warp: red[parity][warp][tile of the group][row], written by the lanes t == 0 after
+      // the four t-lanes of a row have been added up
+      float *const my_red = red + ((parity * CW + warp) * GROUP) * ROWS;
       for (int b = warp; b < nb; b += CW) {
         if (b != staged) stage(b);
-        float4 sc;  // s0, s1, s2, up
-        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(sc.x), "=f"(sc.y), "=f"(sc.z), "=f"(sc.w) : "r"(slab + SLAB_SC));
+        const bool first = b == warp;  // the warp's first block of a group overwrites what an earlier group left behind
+        auto park = [&](int rt, float v0, float v1) {
+          v0 += __shfl_xor_sync(0xffffffffu, v0, 1), v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+          v0 += __shfl_xor_sync(0xffffffffu, v0, 2), v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+          if (t == 0) {
+            float *p = my_red + rt * ROWS;
+            if (!first) v0 += p[g], v1 += p[g + 8];
+            p[g] = v0, p[g + 8] = v1;
+          }
+        };
         if (kind == 0) {
-          float2 sx;
-          asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + SLAB_SX + 8 * t));
+#pragma unroll 1
+          for (int rt = 0; rt < gs; rt++) {
+            const uint32_t sb = slot_wait() + g * Q4_PITCH;
+            const uint4 h0 = lds128(sb), h1 = lds128(sb + 8 * Q4_PITCH);
+            const uint4 qa0 = lds128(sb + 16 + 32 * t), qa1 = lds128(sb + 32 + 32 * t);
+            const uint4 qb0 = lds128(sb + 8 * Q4_PITCH + 16 + 32 * t), qb1 = lds128(sb + 8 * Q4_PITCH + 32 + 32 * t);
+            __syncwarp();  // the slot is free again
+            issue();
+            const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+            const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+            float4 sc;  // s0, s1, s2, up
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(sc.x), "=f"(sc.y), "=f"(sc.z), "=f"(sc.w) : "r"(slab + SLAB_SC));
+            float de[2], dq[2];
+            {  // even sub-block 2t: the low nibbles; elements 8 i .. 8 i + 7 per MMA
+              int E[4] = {0, 0, 0, 0}, E2[4] = {0, 0, 0, 0};
 #pragma unroll
-          for (int rt = 0; rt < GROUP; rt++) {
-            if (rt < gs) {
-              const uint32_t sb = slot_wait() + g * Q4_PITCH;
-              const uint4 h0 = lds128(sb), h1 = lds128(sb + 8 * Q4_PITCH);
-              const uint4 qa0 = lds128(sb + 16 + 32 * t), qa1 = lds128(sb + 32 + 32 * t);
-              const uint4 qb0 = lds128(sb + 8 * Q4_PITCH + 16 + 32 * t), qb1 = lds128(sb + 8 * Q4_PITCH + 32 + 32 * t);
-              __syncwarp();  // the slot is free again
-              issue();
-              float dsc[2][2], dmn[2][2];
-              q4k_scales(h0, hdr_hi, hdr_sh, dsc[0], dmn[0]);
-              q4k_scales(h1, hdr_hi, hdr_sh, dsc[1], dmn[1]);
-              int E[4] = {0, 0, 0, 0}, E2[4] = {0, 0, 0, 0}, O[4] = {0, 0, 0, 0}, O2[4] = {0, 0, 0, 0};
-              const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
-              const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-#pragma unroll
-              for (int i = 0; i < 4; i++) {  // elements 8 i .. 8 i + 7 of both sub-blocks of pair t
-                const uint32_t lo = 0x0F0F0F0Fu, hi = 0xF0F0F0F0u;
-                const uint2 be1 = lds64_if(pe1 + 8 * i, own4), be2 = lds64_if(pe2 + 8 * i, lo_e);
-                const uint2 bo1 = lds64_if(po1 + 8 * i, own4), bo2 = lds64_if(po2 + 8 * i, lo_o);
+              for (int i = 0; i < 4; i++) {
+                const uint32_t lo = 0x0F0F0F0Fu;
+                const uint2 be1 = lds64(pe1 + 8 * i), be2 = lds64(pe2 + 8 * i);
                 const uint32_t a0 = qg[2 * i] & lo, a1 = qh[2 * i] & lo, a2 = qg[2 * i + 1] & lo, a3 = qh[2 * i + 1] & lo;
-                const uint32_t o0 = qg[2 * i] & hi, o1 = qh[2 * i] & hi, o2 = qg[2 * i + 1] & hi, o3 = qh[2 * i + 1] & hi;
                 imma_u8s8(E, a0, a1, a2, a3, be1.x, be1.y);
                 imma_u8s8(E2, a0, a1, a2, a3, be2.x, be2.y);
+              }
+              // lane (g, t): E[0], E[1] = row g against (hi, mid); E2[0] against lo; [2], [3] the same for row g+8
+              de[0] = fmaf(sc.x, (float)E[0], fmaf(sc.y, (float)E[1], sc.z * (float)E2[0]));
+              de[1] = fmaf(sc.x, (float)E[2], fmaf(sc.y, (float)E[3], sc.z * (float)E2[2]));
+            }
+            {  // odd sub-block 2t+1: the high nibbles, taken as 16 * code
+              int O[4] = {0, 0, 0, 0}, O2[4] = {0, 0, 0, 0};
+#pragma unroll
+              for (int i = 0; i < 4; i++) {
+                const uint32_t hi = 0xF0F0F0F0u;
+                const uint2 bo1 = lds64(po1 + 8 * i), bo2 = lds64(po2 + 8 * i);
+                const uint32_t o0 = qg[2 * i] & hi, o1 = qh[2 * i] & hi, o2 = qg[2 * i + 1] & hi, o3 = qh[2 * i + 1] & hi;
                 imma_u8s8(O, o0, o1, o2, o3, bo1.x, bo1.y);
                 imma_u8s8(O2, o0, o1, o2, o3, bo2.x, bo2.y);
               }
-              // lane (g, t): E[0], E[1] = row g, sub-block 2t against (hi, mid); E2[0] against lo; O[1], O[0] = row g,
-              // sub-block 2t+1 (codes times 16) against (hi, mid); O2[1] against lo; [2], [3] the same for row g+8.
-#pragma unroll
-              for (int r = 0; r < 2; r++) {
-                const float de = fmaf(sc.x, (float)E[2 * r], fmaf(sc.y, (float)E[2 * r + 1], sc.z * (float)E2[2 * r]));
-                const float dq = fmaf(sc.x, (float)O[2 * r + 1], fmaf(sc.y, (float)O[2 * r], sc.z * (float)O2[2 * r + 1])) * 0.0625f;
-                const float v = fmaf(dsc[r][0], de, -dmn[r][0] * sx.x) + fmaf(dsc[r][1], dq, -dmn[r][1] * sx.y);
-                acc[rt][r] = fmaf(v, sc.w, acc[rt][r]);
-              }
+              // O[1], O[0] = row g against (hi, mid); O2[1] against lo
+              dq[0] = fmaf(sc.x, (float)O[1], fmaf(sc.y, (float)O[0], sc.z * (float)O2[1])) * 0.0625f;
+              dq[1] = fmaf(sc.x, (float)O[3], fmaf(sc.y, (float)O[2], sc.z * (float)O2[3])) * 0.0625f;
             }
+            float dsc[2][2], dmn[2][2];
+            q4k_scales(h0, t >= 2, (t & 1) * 16, dsc[0], dmn[0]);
+            q4k_scales(h1, t >= 2, (t & 1) * 16, dsc[1], dmn[1]);
+            float2 sx;
+            asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + SLAB_SX + 8 * t));
+            const float v0 = fmaf(dsc[0][0], de[0], -dmn[0][0] * sx.x) + fmaf(dsc[0][1], dq[0], -dmn[0][1] * sx.y);
+            const float v1 = fmaf(dsc[1][0], de[1], -dmn[1][0] * sx.x) + fmaf(dsc[1][1], dq[1], -dmn[1][1] * sx.y);
+            park(rt, v0 * sc.w, v1 * sc.w);
           }
         } else {
-          float2 sx[2];
-          asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[0].x), "=f"(sx[0].y) : "r"(slab + SLAB_SX + 8 * t));
-          asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx[1].x), "=f"(sx[1].y) : "r"(slab + SLAB_SX + 32 + 8 * t));
-          // one unit: rows g, g+8 of one tile x one K block; `ODD`: the block starts 2 bytes off a word
+          const int n0 = __ldg(&op->n[0]);
+          const uintptr_t w0 = (uintptr_t)__ldg(reinterpret_cast<const unsigned long long *>(&op->w[0]));
+          // one unit: rows g, g+8 of one tile x one K block; `ODD`: the block starts 2 bytes off a word.  The two
+          // 128-element halves of the block are loaded and multiplied one after the other; the slot is released
+          // (and requested again) once the second half's words are in registers.
           auto unit6 = [&](auto odd_tag, uint32_t sb, uint32_t skew, float (&vr)[2]) {
             constexpr bool ODD = decltype(odd_tag)::value;
-            uint32_t wa[2][4], wc[2][4], wh[2][4], scw[2];
-            float dd[2];
-#pragma unroll
-            for (int r = 0; r < 2; r++) {
-              const uint32_t blk = sb + (g + 8 * r) * Q6_PITCH + skew;  // the block's first byte
-#pragma unroll
-              for (int hu = 0; hu < 4; hu++) {
-                const int h = hu >> 1, u = hu & 1;
-                wa[r][hu] = lds32_at2<ODD>(blk + 4 * (16 * h + 4 * u + t));
-                wc[r][hu] = lds32_at2<ODD>(blk + 4 * (16 * h + 8 + 4 * u + t));
-                wh[r][hu] = lds32_at2<ODD>(blk + 4 * (32 + 8 * h + 4 * u + t));
-              }
-              scw[r] = lds16u(blk + 192 + 2 * t) | (lds16u(blk + 200 + 2 * t) << 16);  // scales 2t, 2t+1 | 8+2t, 8+2t+1
-              dd[r] = f16_bits_to_f32((uint16_t)lds16u(blk + 208));
-            }
-            __syncwarp();  // the slot is free again
-            issue();
-            vr[0] = vr[1] = 0.f;
             const uint32_t m0f = 0x0F0F0F0Fu, m30 = 0x30303030u;
+            float4 sc;  // s0, s1, s2, up
+            asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(sc.x), "=f"(sc.y), "=f"(sc.z), "=f"(sc.w) : "r"(slab + SLAB_SC));
+            uint32_t scw[2];
+            float dd[2], half0_u1[2];
+            vr[0] = vr[1] = 0.f;
 #pragma unroll
             for (int h = 0; h < 2; h++) {
+              uint32_t wa[2][2], wc[2][2], wh[2][2];  // [row][u]
+#pragma unroll
+              for (int r = 0; r < 2; r++) {
+                const uint32_t blk = sb + (g + 8 * r) * Q6_PITCH + skew;  // the block's first byte
+#pragma unroll
+                for (int u = 0; u < 2; u++) {
+                  wa[r][u] = lds32_at2<ODD>(blk + 4 * (16 * h + 4 * u + t));
+                  wc[r][u] = lds32_at2<ODD>(blk + 4 * (16 * h + 8 + 4 * u + t));
+                  wh[r][u] = lds32_at2<ODD>(blk + 4 * (32 + 8 * h + 4 * u + t));
+                }
+                if (h == 1) {
+                  scw[r] = lds16u(blk + 192 + 2 * t) | (lds16u(blk + 200 + 2 * t) << 16);  // scales 2t, 2t+1 | 8+2t, 8+2t+1
+                  dd[r] = f16_bits_to_f32((uint16_t)lds16u(blk + 208));
+                }
+              }
+              if (h == 1) {
+                __syncwarp();  // the slot is free again
+                issue();
+              }
               int A1[2][4], A2[2][4];
 #pragma unroll
               for (int u = 0; u < 2; u++) {
-                const int hu = 2 * h + u;
 #pragma unroll
                 for (int i = 0; i < 4; i++) A1[u][i] = 0, A2[u][i] = 0;
                 uint32_t v[4][2];  // [group q][row]: four 6-bit codes as bytes
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
-                  v[0][r] = and_or(wa[r][hu], m0f, (wh[r][hu] << 4) & m30);
-                  v[1][r] = and_or(wc[r][hu], m0f, (wh[r][hu] << 2) & m30);
-                  v[2][r] = and_or(wa[r][hu] >> 4, m0f, wh[r][hu] & m30);
-                  v[3][r] = and_or(wc[r][hu] >> 4, m0f, (wh[r][hu] >> 2) & m30);
+                  v[0][r] = and_or(wa[r][u], m0f, (wh[r][u] << 4) & m30);
+                  v[1][r] = and_or(wc[r][u], m0f, (wh[r][u] << 2) & m30);
+                  v[2][r] = and_or(wa[r][u] >> 4, m0f, wh[r][u] & m30);
+                  v[3][r] = and_or(wc[r][u] >> 4, m0f, (wh[r][u] >> 2) & m30);
                 }
                 // the columns of group q = q6sel: (hi | mid) in both sets' first MMA, lo in the second
-                const uint32_t x1 = lds32(p6a + 128 * h + 16 * u), x2 = lds32_if(p6b + 128 * h + 16 * u, lo6);
+                const uint32_t x1 = lds32(p6a + 128 * h + 16 * u), x2 = lds32(p6b + 128 * h + 16 * u);
                 const uint32_t b0_01 = q6sel == 0 ? x1 : 0u, b1_01 = q6sel == 1 ? x1 : 0u, b0_23 = q6sel == 2 ? x1 : 0u, b1_23 = q6sel == 3 ? x1 : 0u;
                 const uint32_t c0_01 = q6sel == 0 ? x2 : 0u, c1_01 = q6sel == 1 ? x2 : 0u, c0_23 = q6sel == 2 ? x2 : 0u, c1_23 = q6sel == 3 ? x2 : 0u;
                 imma_u8s8(A1[u], v[0][0], v[0][1], v[1][0], v[1][1], b0_01, b1_01);
@@ -525,53 +600,47 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
                 imma_u8s8(A2[u], v[2][0], v[2][1], v[3][0], v[3][1], c0_23, c1_23);
               }
               // lane (g, t): A1[u][0], A1[u][1] = row g, sub-block 8h + 2t + u against (hi, mid); A2[u][0] against lo;
-              // [2], [3] the same for row g+8
+              // [2], [3] the same for row g+8.  Half 0's sums wait for the scales, which arrive with half 1.
+              float2 sx;
+              asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];\n" : "=f"(sx.x), "=f"(sx.y) : "r"(slab + SLAB_SX + 32 * h + 8 * t));
+              float d_[2][2];  // [row][u]
 #pragma unroll
               for (int r = 0; r < 2; r++) {
-                const float s_0 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h)) & 0xff);
-                const float s_1 = dd[r] * (float)(int8_t)((scw[r] >> (16 * h + 8)) & 0xff);
-                const float d_0 = fmaf(sc.x, (float)A1[0][2 * r], fmaf(sc.y, (float)A1[0][2 * r + 1], sc.z * (float)A2[0][2 * r]));
-                const float d_1 = fmaf(sc.x, (float)A1[1][2 * r], fmaf(sc.y, (float)A1[1][2 * r + 1], sc.z * (float)A2[1][2 * r]));
-                vr[r] += s_0 * fmaf(-32.f, sx[h].x, d_0) + s_1 * fmaf(-32.f, sx[h].y, d_1);
+                d_[r][0] = fmaf(-32.f, sx.x, fmaf(sc.x, (float)A1[0][2 * r], fmaf(sc.y, (float)A1[0][2 * r + 1], sc.z * (float)A2[0][2 * r])));
+                d_[r][1] = fmaf(-32.f, sx.y, fmaf(sc.x, (float)A1[1][2 * r], fmaf(sc.y, (float)A1[1][2 * r + 1], sc.z * (float)A2[1][2 * r])));
+              }
+              if (h == 0) {  // kept unscaled until the scales are read
+                vr[0] = d_[0][0], vr[1] = d_[1][0], half0_u1[0] = d_[0][1], half0_u1[1] = d_[1][1];
+              } else {
+#pragma unroll
+                for (int r = 0; r < 2; r++) {
+                  const float s00 = dd[r] * (float)(int8_t)(scw[r] & 0xff), s01 = dd[r] * (float)(int8_t)((scw[r] >> 8) & 0xff);
+                  const float s10 = dd[r] * (float)(int8_t)((scw[r] >> 16) & 0xff), s11 = dd[r] * (float)(int8_t)((scw[r] >> 24) & 0xff);
+                  vr[r] = (s00 * vr[r] + s01 * half0_u1[r] + s10 * d_[r][0] + s11 * d_[r][1]) * sc.w;
+                }
               }
             }
           };
-#pragma unroll
-          for (int rt = 0; rt < GROUP; rt++) {
-            if (rt < gs) {
-              const uint32_t sb = slot_wait();
-              const int n0 = __ldg(&op->n[0]);
-              const int r0 = min((gt + rt) * ROWS, n0 - ROWS);
-              const uint8_t *w = (const uint8_t *)__ldg(reinterpret_cast<const unsigned long long *>(&op->w[0]));
-              const uint32_t skew = (uint32_t)(((uintptr_t)w + (size_t)(r0 + g) * row_bytes + (uint32_t)b * 210u) & 15u);
-              float vr[2];
-              if (skew & 2u)
-                unit6(std::true_type{}, sb, skew, vr);
-              else
-                unit6(std::false_type{}, sb, skew, vr);
-              acc[rt][0] = fmaf(vr[0], sc.w, acc[rt][0]);
-              acc[rt][1] = fmaf(vr[1], sc.w, acc[rt][1]);
-            }
+#pragma unroll 1
+          for (int rt = 0; rt < gs; rt++) {
+            const uint32_t sb = slot_wait();
+            const int r0 = min((gt + rt) * ROWS, n0 - ROWS);
+            const uint32_t skew = (uint32_t)((w0 + (size_t)(r0 + g) * row_bytes + (uint32_t)b * 210u) & 15u);
+            float vr[2];
+            if (skew & 2u)
+              unit6(std::true_type{}, sb, skew, vr);
+            else
+              unit6(std::false_type{}, sb, skew, vr);
+            park(rt, vr[0], vr[1]);
           }
         }
       }
-      // sum the four t-lanes of a row; lane t == 0 parks rows g, g+8 of every tile for the other warps
-#pragma unroll
-      for (int rt = 0; rt < GROUP; rt++) {
-        float a = acc[rt][0], c = acc[rt][1];
-        a += __shfl_xor_sync(0xffffffffu, a, 1), c += __shfl_xor_sync(0xffffffffu, c, 1);
-        a += __shfl_xor_sync(0xffffffffu, a, 2), c += __shfl_xor_sync(0xffffffffu, c, 2);
-        if (t == 0 && rt < gs) {
-          float *p = red + ((parity * CW + warp) * GROUP + rt) * ROWS;
-          p[g] = a, p[g + 8] = c;
-        }
-      }
-      if (norm_w && gt == t0) {
+      if (has_norm && gt == t0) {
         nrm_ss = warp_sum(nrm_ss);
         if (lane == 0) nrm[(oi & 1) * CW + warp] = warp < nb ? nrm_ss : 0.f;
       }
       __syncthreads();  // also orders this group's reads of red[parity] before its reuse two groups on
-      if (norm_w && gt == t0) {
+      if (has_norm && gt == t0) {
         float tot = 0.f;
 #pragma unroll
         for (int i = 0; i < CW; i++) tot += nrm[(oi & 1) * CW + i];
@@ -592,7 +661,7 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
           float *o = (float *)__ldg(reinterpret_cast<const unsigned long long *>(&op->out[0]));
           if (o) o[r0 + row] = v;
           const uint32_t off = __ldg(&op->out_off[0]);
-          if (off != NONE) st_slot(arena, world, off, (size_t)rank * __ldg(&op->n[0]) + r0 + row, v, tag_me);
+          if (off != NONE) st_slot(hd, arena_me, world, off, (size_t)rank * __ldg(&op->n[0]) + r0 + row, v, tag_me);
         }
       } else {
         for (int i = threadIdx.x; i < gs * ROWS; i += CT) {
@@ -603,20 +672,16 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
           float *o = (float *)__ldg(reinterpret_cast<const unsigned long long *>(&op->out[j]));
           if (o) o[r0 + row] = v;
           const uint32_t off = __ldg(&op->out_off[j]);
-          if (off != NONE) st_slot(arena, world, off, (size_t)rank * __ldg(&op->n[j]) + r0 + row, v, tag_me);
+          if (off != NONE) st_slot(hd, arena_me, world, off, (size_t)rank * __ldg(&op->n[j]) + r0 + row, v, tag_me);
         }
       }
     }
   }
-  // Nothing should be in flight here (the requests end with the program); after a wait that gave up there may
-  // be: let those copies land before the CTA's shared memory goes away.
-  while (in_flight > 0) {
-    const uint32_t bar = bar0 + 8 * c_slot;
+  // Nothing is in flight here (the requests end with the program and every requested tile was waited for) unless
+  // a wait gave up: then let the outstanding copies land before the CTA's shared memory goes away.
+  if (*abort_flag) {
     const unsigned long long ts = umma::global_ns();
-    while (!umma::mbar_test_wait(bar, c_phase) && umma::global_ns() - ts < 2000000ull) {
-    }
-    if (++c_slot == STAGES) c_slot = 0, c_phase ^= 1u;
-    in_flight--;
+    while (umma::global_ns() - ts < 2000000ull) __nanosleep(1000);
   }
 }
 
