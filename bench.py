@@ -139,7 +139,7 @@ class Chain:
         self.out = [torch.empty(M, e[2], device=device) for e in self.lin]  # full-width outputs (gathered when world > 1)
         self.local = [torch.empty(M, e[1], device=device) for e in self.lin] if world > 1 else self.out
         self.dev_index = device.index or 0
-        self.peer, self.fx, self.gather_kind = None, None, "none"
+        self.peer, self.fx, self.dc, self.gather_kind = None, None, None, "none"
         self.attn = None
         if world > 1:
             from light_b200 import tp
@@ -147,9 +147,10 @@ class Chain:
             self.gidx = [i for i, e in enumerate(self.lin) if e[0].split(".")[-1] in self.GATHERED]
             self.gather_kind = "nccl"
             mode = os.environ.get("LIGHT_B200_TP_GATHER", "fused")
-            if mode in ("fused", "peer"):
+            if mode in ("chain", "fused", "peer"):
                 try:
-                    fused = mode == "fused" and self.fused and M == 1  # the in-launch exchange serves one activation row
+                    in_chain = mode == "chain" and self.fused and M == 1  # the whole step as one persistent launch per rank
+                    fused = (mode == "fused" or in_chain) and self.fused and M == 1  # the in-launch exchange serves one activation row
                     pidx = [i for i in self.gidx if not fused or self.lin[i][0] == HEAD[0]]  # gathered by the gather kernel
                     self.peer = tp.PeerGather(device)
                     outs = self.peer.plan([(M, self.lin[i][2]) for i in pidx])
@@ -157,7 +158,10 @@ class Chain:
                         self.out[i] = outs[j]
                     self.pidx = pidx
                     self.gather_kind = "peer"
-                    if fused:
+                    if in_chain:
+                        self._plan_chain(tp)
+                        self.gather_kind = "inside one persistent launch per rank (tagged slots stored into every rank's arena; logits: peer-store gather kernel)"
+                    elif fused:
                         self._plan_fused(tp)
                         self.gather_kind = "fused into the matmul launches (logits: peer-store gather kernel)"
                 except Exception as e:  # noqa: BLE001  (no peer mapping on this box: NCCL does the gathers)
@@ -186,6 +190,29 @@ class Chain:
                 if o is not None:
                     prev = o
         self.fx = fx
+
+    def _plan_chain(self, tp):
+        """The same dependent chain (q -> o -> gate -> down -> next layer's q ... -> lm_head) as ONE persistent launch
+        per rank (light_b200_chain_*): every exchanged output is a chain vector in symmetric memory that all ranks
+        store their rows into; the logits stay row-local and are gathered by the gather kernel."""
+        from light_b200 import chain as lbchain
+
+        dc = lbchain.DecodeChain(self.device, world=self.world, rank=self.rank)
+        vecs = {n: dc.vec() for n in ("q", "o", "gate", "down")}
+        prev = None
+        for idx in self.plan():
+            names = [self.lin[i][0].split(".")[-1] for i in idx]
+            K, dt = self.lin[idx[0]][3], self.lin[idx[0]][4]
+            ws = [ops.QTensor(self.lin[i][5].reshape(-1), dt, (self.lin[i][1], K)) for i in idx]
+            outs = [self.local[i].reshape(-1) for i in idx]
+            out_vecs = [vecs.get(n) for n in names]
+            kw = dict(x=self.x[K].reshape(-1)) if prev is None or prev[1] != K else dict(x_vec=prev[0])
+            dc.matmul(ws, outs=outs, out_vecs=out_vecs, **kw)
+            for n, i in zip(names, idx):
+                if n in vecs:
+                    prev = (vecs[n], self.lin[i][2])
+        tp.build_chain_symmetric(dc)
+        self.dc = dc
 
     def enable_attention(self, kv_len=1024):
         """Adds the decode-step attention of configs[1] (32 query / 8 KV heads of dim 128, KV length
@@ -262,6 +289,12 @@ class Chain:
             self.peer.step_begin()
         if self.fx is not None and only is None:
             self.fx.step_begin()
+        if self.dc is not None and only is None:
+            self.dc.run()
+            n = 2
+            li_head = len(self.lin) - 1
+            self.peer.gather(self.pidx.index(li_head), self.local[li_head])
+            return n + 1
         for li, idx in enumerate(self.plan(only)):
             if self.fx is not None and only is None:
                 args, plain_x, wp, op, nn = self.launch_args[li]
@@ -288,7 +321,29 @@ class Chain:
         return sum(algorithmic_bytes(e[1], e[3], e[4], self.M) for e in self.lin if only is None or e[4] == only)
 
     def launches(self, only=None):
+        if self.dc is not None and only is None:
+            return 4  # step words of the chain and of the gather, the persistent chain kernel, the logits gather
         return len(self.plan(only))
+
+    def reference_logits(self):
+        """The same dependent chain, one launch per linear and an NCCL all-gather after every exchanged output: what
+        the exchange inside the launches must reproduce."""
+        from light_b200 import tp
+
+        prev, logits = None, None
+        for idx in self.plan():
+            K, dt = self.lin[idx[0]][3], self.lin[idx[0]][4]
+            x = self.x[K] if prev is None or prev.shape[1] != K else prev
+            for i in idx:
+                name = self.lin[i][0].split(".")[-1]
+                y = ops.MatMulQ(x, ops.QTensor(self.lin[i][5].reshape(-1), dt, (self.lin[i][1], K)))
+                if name in self.GATHERED:
+                    full = tp.all_gather_columns(y)
+                    if name == HEAD[0]:
+                        logits = full
+                    else:
+                        prev = full
+        return logits
 
 
 
@@ -701,6 +756,19 @@ def main():
     }
     if world == 1 and not args.no_extras:
         line["extras"] = extras(chain, device, args)
+    if world > 1 and chain.peer is not None:
+        # correctness of the exchange that was just timed: rank 0's logits against the NCCL-gathered chain
+        graph.replay()
+        torch.cuda.synchronize(device)
+        got = chain.out[-1].clone()
+        want = chain.reference_logits()
+        torch.cuda.synchronize(device)
+        rel = float(((got.double() - want.double()).norm() / want.double().norm()).item())  # (the chain's values grow far beyond f32's square root)
+        st = chain.peer.status() | (chain.dc.status() if chain.dc is not None else 0)
+        check = torch.tensor([rel, float(st)], device=device)
+        dist.all_reduce(check, op=dist.ReduceOp.MAX)
+        line["tp_check"] = {"rel_l2_vs_nccl_chain_max_over_ranks": float(check[0].item()), "comm_status": int(check[1].item()),
+                            "finite": bool(torch.isfinite(got).all().item())}
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1

@@ -102,6 +102,12 @@ __device__ __forceinline__ void imma_u8s8(int (&d)[4], uint32_t a0, uint32_t a1,
                : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// the first MMA of a chain: the accumulator starts from zero (no registers to clear)
+__device__ __forceinline__ void imma_u8s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(addr), "r"(v)); }
 __device__ __forceinline__ uint32_t lds16u(uint32_t addr) {
   uint16_t v;
@@ -506,28 +512,38 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
             asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];\n" : "=f"(sc.x), "=f"(sc.y), "=f"(sc.z), "=f"(sc.w) : "r"(slab + SLAB_SC));
             float de[2], dq[2];
             {  // even sub-block 2t: the low nibbles; elements 8 i .. 8 i + 7 per MMA
-              int E[4] = {0, 0, 0, 0}, E2[4] = {0, 0, 0, 0};
+              int E[4], E2[4];
 #pragma unroll
               for (int i = 0; i < 4; i++) {
                 const uint32_t lo = 0x0F0F0F0Fu;
                 const uint2 be1 = lds64(pe1 + 8 * i), be2 = lds64(pe2 + 8 * i);
                 const uint32_t a0 = qg[2 * i] & lo, a1 = qh[2 * i] & lo, a2 = qg[2 * i + 1] & lo, a3 = qh[2 * i + 1] & lo;
-                imma_u8s8(E, a0, a1, a2, a3, be1.x, be1.y);
-                imma_u8s8(E2, a0, a1, a2, a3, be2.x, be2.y);
+                if (i == 0) {
+                  imma_u8s8_first(E, a0, a1, a2, a3, be1.x, be1.y);
+                  imma_u8s8_first(E2, a0, a1, a2, a3, be2.x, be2.y);
+                } else {
+                  imma_u8s8(E, a0, a1, a2, a3, be1.x, be1.y);
+                  imma_u8s8(E2, a0, a1, a2, a3, be2.x, be2.y);
+                }
               }
               // lane (g, t): E[0], E[1] = row g against (hi, mid); E2[0] against lo; [2], [3] the same for row g+8
               de[0] = fmaf(sc.x, (float)E[0], fmaf(sc.y, (float)E[1], sc.z * (float)E2[0]));
               de[1] = fmaf(sc.x, (float)E[2], fmaf(sc.y, (float)E[3], sc.z * (float)E2[2]));
             }
             {  // odd sub-block 2t+1: the high nibbles, taken as 16 * code
-              int O[4] = {0, 0, 0, 0}, O2[4] = {0, 0, 0, 0};
+              int O[4], O2[4];
 #pragma unroll
               for (int i = 0; i < 4; i++) {
                 const uint32_t hi = 0xF0F0F0F0u;
                 const uint2 bo1 = lds64(po1 + 8 * i), bo2 = lds64(po2 + 8 * i);
                 const uint32_t o0 = qg[2 * i] & hi, o1 = qh[2 * i] & hi, o2 = qg[2 * i + 1] & hi, o3 = qh[2 * i + 1] & hi;
-                imma_u8s8(O, o0, o1, o2, o3, bo1.x, bo1.y);
-                imma_u8s8(O2, o0, o1, o2, o3, bo2.x, bo2.y);
+                if (i == 0) {
+                  imma_u8s8_first(O, o0, o1, o2, o3, bo1.x, bo1.y);
+                  imma_u8s8_first(O2, o0, o1, o2, o3, bo2.x, bo2.y);
+                } else {
+                  imma_u8s8(O, o0, o1, o2, o3, bo1.x, bo1.y);
+                  imma_u8s8(O2, o0, o1, o2, o3, bo2.x, bo2.y);
+                }
               }
               // O[1], O[0] = row g against (hi, mid); O2[1] against lo
               dq[0] = fmaf(sc.x, (float)O[1], fmaf(sc.y, (float)O[0], sc.z * (float)O2[1])) * 0.0625f;
@@ -580,8 +596,6 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
               int A1[2][4], A2[2][4];
 #pragma unroll
               for (int u = 0; u < 2; u++) {
-#pragma unroll
-                for (int i = 0; i < 4; i++) A1[u][i] = 0, A2[u][i] = 0;
                 uint32_t v[4][2];  // [group q][row]: four 6-bit codes as bytes
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
@@ -594,9 +608,9 @@ __global__ void __launch_bounds__(CT, 1) chain_kernel(const uint8_t *__restrict_
                 const uint32_t x1 = lds32(p6a + 128 * h + 16 * u), x2 = lds32(p6b + 128 * h + 16 * u);
                 const uint32_t b0_01 = q6sel == 0 ? x1 : 0u, b1_01 = q6sel == 1 ? x1 : 0u, b0_23 = q6sel == 2 ? x1 : 0u, b1_23 = q6sel == 3 ? x1 : 0u;
                 const uint32_t c0_01 = q6sel == 0 ? x2 : 0u, c1_01 = q6sel == 1 ? x2 : 0u, c0_23 = q6sel == 2 ? x2 : 0u, c1_23 = q6sel == 3 ? x2 : 0u;
-                imma_u8s8(A1[u], v[0][0], v[0][1], v[1][0], v[1][1], b0_01, b1_01);
+                imma_u8s8_first(A1[u], v[0][0], v[0][1], v[1][0], v[1][1], b0_01, b1_01);
                 imma_u8s8(A1[u], v[2][0], v[2][1], v[3][0], v[3][1], b0_23, b1_23);
-                imma_u8s8(A2[u], v[0][0], v[0][1], v[1][0], v[1][1], c0_01, c1_01);
+                imma_u8s8_first(A2[u], v[0][0], v[0][1], v[1][0], v[1][1], c0_01, c1_01);
                 imma_u8s8(A2[u], v[2][0], v[2][1], v[3][0], v[3][1], c0_23, c1_23);
               }
               // lane (g, t): A1[u][0], A1[u][1] = row g, sub-block 8h + 2t + u against (hi, mid); A2[u][0] against lo;

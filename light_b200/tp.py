@@ -252,6 +252,30 @@ class FusedExchange:
         return _lib.lib().light_b200_comm_status(self.device.index or 0)
 
 
+def build_chain_symmetric(chain, group=None) -> None:
+    """Builds a row-split chain.DecodeChain whose chain vectors live in symmetric memory: every rank allocates an
+    arena of the same size, the ranks exchange the addresses (torch.distributed._symmetric_memory: plumbing only),
+    and each rank's program stores its output slots into all of them.  Call on every rank with the same program."""
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+
+    group = group if group is not None else dist.group.WORLD
+    nbytes = chain.arena_bytes()
+    arena = symm_mem.empty(nbytes + 256, dtype=torch.uint8, device=chain.device)
+    arena.zero_()
+    try:
+        hdl = symm_mem.rendezvous(arena, group)
+    except TypeError:
+        hdl = symm_mem.rendezvous(arena, group.group_name)
+    torch.cuda.synchronize(chain.device)
+    dist.barrier(group)
+    ptrs = [int(p) for p in hdl.buffer_ptrs]
+    chain._symm = (arena, hdl)
+    chain.build(arenas=[p + (-p) % 256 for p in ptrs], arena=arena)
+    torch.cuda.synchronize(chain.device)
+    dist.barrier(group)   # nobody stores into an arena that its owner is still zeroing
+
+
 class ExpertParallel:
     """Mixture-of-experts layer with the experts sharded over the ranks (E / P contiguous experts each)
     and a token all-to-all on either side of the local grouped matmuls -- the multi-GPU form of the
