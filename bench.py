@@ -347,108 +347,28 @@ class Chain:
 
 
 
-class FullStep:
-    """One whole decode step of configs[1] at M = 1 on the chain's weights: per layer
-    add + RMSNorm -> q,k,v (one launch) -> RoPE + KV append + attention (one launch) -> o -> add + RMSNorm ->
-    SiLU(gate) * up (one launch) -> down; then the final norm, lm_head and greedy sampling; the step starts with
-    the quantized embedding row of the token the previous step sampled, so replaying the graph is a generation
-    loop without a host round trip.  Every operator reads what the one before it wrote, KV length kv_len, f32
-    cache.  A side measurement: the headline stays
-    the quantized linears alone."""
+def full_step_graph(chain, kv_len=1024, fold_norms=True):
+    """configs[1]'s whole decode step at M = 1 on the chain's weights as a light_b200.decode.DecodeGraph (the
+    counterpart of models/decode_graph.go): embedding row of the last sampled token -> 32 layers of [norm, q/k/v,
+    RoPE + KV append + attention, o, norm, SiLU(gate) * up, down] -> final norm -> lm_head -> argmax.  The KV cache
+    holds kv_len - 1 earlier positions (f32) and grows by one per replay."""
+    from light_b200 import decode
 
-    def __init__(self, chain, kv_len=1024, fold_norms=True):
-        dev = chain.device
-        self.fold_norms = fold_norms
-        self.c, self.dev_index = chain, chain.dev_index
-        self.by = {e[0]: e for e in chain.lin}
-        self.layers = sum(1 for e in chain.lin if e[0].endswith(".q"))
-        g = torch.Generator(device=dev)
-        g.manual_seed(21)
-        z = lambda *s: torch.zeros(*s, device=dev)
-        self.h, self.xn, self.attn, self.o, self.act, self.down = torch.randn(1, HID, generator=g, device=dev), z(1, HID), z(1, 32, 1, 128), z(1, HID), z(1, FFN), z(1, HID)
-        self.q, self.k, self.v = z(1, HID), z(1, NKV), z(1, NKV)
-        self.logits = z(1, VOCAB)
-        self.norm_w = torch.ones(HID, device=dev)
-        self.token = torch.ones(1, dtype=torch.int64, device=dev)  # the current token id: written by the step's own argmax
-        self.pos = torch.tensor([kv_len - 1], dtype=torch.int64, device=dev)
-        self.kb = [torch.randn(1, NKV // 128, kv_len, 128, generator=g, device=dev) for _ in range(self.layers)]
-        self.vb = [torch.randn(1, NKV // 128, kv_len, 128, generator=g, device=dev) for _ in range(self.layers)]
-        self.attn_args = [_lib.DecodeAttnArgs(self.q.data_ptr(), self.kb[l].data_ptr(), self.vb[l].data_ptr(), self.k.data_ptr(), self.v.data_ptr(),
-                                              self.pos.data_ptr(), self.attn.data_ptr(), ops.F32, 1, 32, NKV // 128, kv_len, 128, 0,
-                                              1.0 / math.sqrt(128), 500000.0) for l in range(self.layers)]
-        self.qkv = []
-        for l in range(self.layers):
-            ws = [self.by[f"l{l}.{n}"][5] for n in ("q", "k", "v")]
-            self.qkv.append(((C.c_void_p * 3)(*[w.data_ptr() for w in ws]), (C.c_void_p * 3)(self.q.data_ptr(), self.k.data_ptr(), self.v.data_ptr()),
-                             (C.c_int32 * 3)(HID, NKV, NKV)))
-        # norms folded into the q,k,v and gate,up launches: the residual stream alternates between two buffers,
-        # because the launch that writes the new sum is still reading the old one
-        self.h2 = z(1, HID)
-        self.gu = [((C.c_void_p * 2)(self.by[f"l{l}.gate"][5].data_ptr(), self.by[f"l{l}.up"][5].data_ptr()),
-                    (C.c_void_p * 2)(self.act.data_ptr(), self.act.data_ptr()), (C.c_int32 * 2)(FFN, FFN)) for l in range(self.layers)]
-        self.folded, cur, other = [], self.h, self.h2
-        for l in range(self.layers):
-            if l == 0:
-                first = (cur, _lib.NormArgs(self.norm_w.data_ptr(), None, None, 1e-5))
-            else:
-                first = (cur, _lib.NormArgs(self.norm_w.data_ptr(), self.down.data_ptr(), other.data_ptr(), 1e-5))
-                cur, other = other, cur
-            second = (cur, _lib.NormArgs(self.norm_w.data_ptr(), self.o.data_ptr(), other.data_ptr(), 1e-5))
-            cur, other = other, cur
-            self.folded.append((first, second))
-        self.last_h = cur
-
-    def step_folded(self):
-        L, st, d = _lib.lib(), C.c_void_p(torch.cuda.current_stream(self.c.device).cuda_stream), self.dev_index
-        P = lambda t: C.c_void_p(t.data_ptr())
-        self.embed(L, d, st)
-        for l in range(self.layers):
-            (x1, n1), (x2, n2) = self.folded[l]
-            wp, op, nn = self.qkv[l]
-            _lib.check(L.light_b200_matmul_q_fused(ops.Q4_K, P(x1), C.byref(n1), wp, op, nn, 3, 0, HID, d, st))
-            _lib.check(L.light_b200_decode_attn(C.byref(self.attn_args[l]), d, st))
-            _lib.check(L.light_b200_matmul_q(ops.Q4_K, P(self.attn), P(self.by[f"l{l}.o"][5]), P(self.o), 1, HID, HID, d, st))
-            wp, op, nn = self.gu[l]
-            _lib.check(L.light_b200_matmul_q_fused(ops.Q4_K, P(x2), C.byref(n2), wp, op, nn, 2, 1, HID, d, st))
-            _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.act), P(self.by[f"l{l}.down"][5]), P(self.down), 1, HID, FFN, d, st))
-        _lib.check(L.light_b200_rmsnorm(P(self.last_h), P(self.down), P(self.norm_w), P(self.xn), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
-        _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.xn), P(self.by[HEAD[0]][5]), P(self.logits), 1, VOCAB, HID, d, st))
-        self.sample(L, d, st)
-        return 5 * self.layers + 4
-
-    def embed(self, L, d, st):
-        """The token's row of the (tied, Q6_K) embedding table -> the residual stream."""
-        _lib.check(L.light_b200_embedding_q(ops.Q6_K, C.c_void_p(self.by[HEAD[0]][5].data_ptr()), C.c_void_p(self.token.data_ptr()),
-                                            C.c_void_p(self.h.data_ptr()), 1, VOCAB, HID, d, st))
-
-    def sample(self, L, d, st):
-        """Greedy sampling on the device: the next replay reads the token this one chose."""
-        _lib.check(L.light_b200_argmax(C.c_void_p(self.logits.data_ptr()), C.c_void_p(self.token.data_ptr()), 1, VOCAB, d, st))
-
-    def step(self):
-        if self.fold_norms:
-            return self.step_folded()
-        L, st, d = _lib.lib(), C.c_void_p(torch.cuda.current_stream(self.c.device).cuda_stream), self.dev_index
-        P = lambda t: C.c_void_p(t.data_ptr())
-        n = 2
-        self.embed(L, d, st)
-        for l in range(self.layers):
-            # the first layer normalises the embedding row; later ones add the MLP output to the stream first
-            _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.down) if l else None, P(self.norm_w), P(self.h) if l else None, P(self.xn), ops.F32, 1, HID,
-                                            1e-5, d, st))
-            wp, op, nn = self.qkv[l]
-            _lib.check(L.light_b200_matmul_q_multi(ops.Q4_K, P(self.xn), wp, op, nn, 3, HID, d, st))
-            _lib.check(L.light_b200_decode_attn(C.byref(self.attn_args[l]), d, st))
-            _lib.check(L.light_b200_matmul_q(ops.Q4_K, P(self.attn), P(self.by[f"l{l}.o"][5]), P(self.o), 1, HID, HID, d, st))
-            _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.o), P(self.norm_w), P(self.h), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
-            _lib.check(L.light_b200_matmul_q_gated(ops.Q4_K, P(self.xn), P(self.by[f"l{l}.gate"][5]), P(self.by[f"l{l}.up"][5]), P(self.act), FFN, HID,
-                                                   1, d, st))
-            _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.act), P(self.by[f"l{l}.down"][5]), P(self.down), 1, HID, FFN, d, st))
-            n += 7
-        _lib.check(L.light_b200_rmsnorm(P(self.h), P(self.down), P(self.norm_w), P(self.h), P(self.xn), ops.F32, 1, HID, 1e-5, d, st))
-        _lib.check(L.light_b200_matmul_q(ops.Q6_K, P(self.xn), P(self.by[HEAD[0]][5]), P(self.logits), 1, VOCAB, HID, d, st))
-        self.sample(L, d, st)
-        return n + 2
+    by = {e[0]: e for e in chain.lin}
+    qt = lambda e: ops.QTensor(e[5].reshape(-1), e[4], (e[1], e[3]))  # noqa: E731
+    n_layers = sum(1 for e in chain.lin if e[0].endswith(".q"))
+    ones = torch.ones(HID, device=chain.device)
+    layers = [decode.LlamaLayer(*[qt(by[f"l{l}.{n}"]) for n in ("q", "k", "v", "o", "gate", "up", "down")], ones, ones) for l in range(n_layers)]
+    cfg = decode.LlamaConfig(hidden=HID, n_heads=32, n_kv_heads=NKV // 128, head_dim=128)
+    g = decode.DecodeGraph(cfg, layers, ones, qt(by[HEAD[0]]), qt(by[HEAD[0]]), kv_len + 256, chain.device, fold_norms=fold_norms)
+    gen = torch.Generator(device=chain.device)
+    gen.manual_seed(21)
+    for kb, vb in zip(g.kbuf, g.vbuf):   # a cache with content, as after kv_len - 1 decoded tokens
+        kb[:, :, :kv_len - 1].copy_(torch.randn(1, NKV // 128, kv_len - 1, 128, generator=gen, device=chain.device))
+        vb[:, :, :kv_len - 1].copy_(torch.randn(1, NKV // 128, kv_len - 1, 128, generator=gen, device=chain.device))
+    g.reset(1, kv_len - 1)
+    g.capture()
+    return g
 
 
 def capture(fn, device):
@@ -563,18 +483,22 @@ def extras(chain, device, args):
     if chain.world == 1 and chain.M == 1:
         logits = []
         for key, fold in (("decode_m1_full_step_kv1024", True), ("decode_m1_full_step_kv1024_norms_as_launches", False)):
-            fs = FullStep(chain, fold_norms=fold)
-            g = capture(fs.step, device)
-            ms = timed(g.replay, steps, 3, device, lambda: None) / steps  # a closed loop: every replay decodes the token the last one sampled
-            fs.token.fill_(1)
-            g.replay()  # one step from a known token, for the comparison of the two variants
+            fs = full_step_graph(chain, 1024, fold)
+            for _ in range(3):
+                fs.step()
             torch.cuda.synchronize(device)
-            out[key] = {"launches": (5 if fold else 7) * fs.layers + 4, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3),
+            fs.reset(1, 1023)
+            ms = timed(fs.step, steps, 0, device, lambda: None) / steps  # a closed loop: every replay decodes the token the last one sampled
+            fs.reset(1, 1023)
+            fs.step()  # one step from a known token and position, for the comparison of the two variants
+            torch.cuda.synchronize(device)
+            out[key] = {"launches": fs.launches_per_step, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3),
                         "logits_finite": bool(torch.isfinite(fs.logits).all().item()), "sampled_token": int(fs.token.item())}
             logits.append(fs.logits.clone())
-            del g, fs
+            del fs
         d = (logits[0] - logits[1]).norm() / logits[1].norm()
         out["decode_m1_full_step_kv1024"]["rel_l2_of_logits_against_norms_as_launches"] = float(d)
+        out["decode_m1_full_step_kv1024"]["parity"] = "tests/test_decode_graph_gpu.py: this class against the CPU oracle, operator by operator"
     assert ops.decode_attn_status(device.index or 0) == 0
     # the Q4_K decode kernel on one matrix large enough that the cost of a launch does not matter (the vocabulary
     # projection's shape, 295 MB as Q4_K): its streaming rate, next to the launch-bound average of a step

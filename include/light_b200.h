@@ -125,6 +125,19 @@ LB200_API int light_b200_matmul_q_multi(int ggml_type, const float *x, const voi
 LB200_API int light_b200_matmul_q_gated(int ggml_type, const float *x, const void *wg, const void *wu, float *out, int N,
                                         int K, int act, int device, void *stream);
 
+/* Registry keys {gemv_multi, CUDA, BF16} and {gemv_gated, CUDA, BF16} (reference kernels/cuda/gemv.go:15-94;
+ * ops.LinearMulti / ops.GatedLinear, ops/gemv.go:21-140): the same two fused launches for UNQUANTIZED bf16 weights.
+ * x is one bf16 activation row (K), every w[i] (n[i], K) bf16 row-major.
+ *   gemv_multi: out[i] (n[i]) = x . w[i]^T for i < count <= 4, f32 sums rounded once to bf16, or stored as f32
+ *     when out_f32 != 0.
+ *   gemv_gated: out (N) bf16 = act(x . wg^T) * (x . wu^T), act SiLU (gelu = 0) or GELU-erf, with both products and
+ *     the activation rounded to bf16 first, as the unfused sequence leaves them.
+ * K % 8 == 0 and K <= 16384 (the reference: 12288); pointers 16-byte aligned. */
+LB200_API int light_b200_gemv_multi(const void *x, const void *const *w, void *const *out, const int32_t *n, int count, int K,
+                                    int out_f32, int device, void *stream);
+LB200_API int light_b200_gemv_gated(const void *x, const void *wg, const void *wu, void *out, int N, int K, int gelu, int device,
+                                    void *stream);
+
 /* The CUDA dequantize hook, quant.RegisterCUDADequant (reference quant/cuda_hook.go:13-46,
  * kernels/cuda/dequant.go:15-75):  dst f32 [n_elems] = dequant(src blocks).  n_elems must be a
  * whole number of blocks.  Bit-identical to the reference's CPU decoders. */

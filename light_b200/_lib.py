@@ -119,6 +119,9 @@ SYMBOLS = {
                                      C.c_int, C.c_void_p]),
     "light_b200_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_double, C.c_int, C.c_void_p]),
     "light_b200_decode_attn_status": (C.c_int, [C.c_int]),
+    "light_b200_gemv_multi": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int,
+                                        C.c_int, C.c_void_p]),
+    "light_b200_gemv_gated": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_chain_program_bytes": (C.c_size_t, [C.c_int]),
     "light_b200_chain_arena_bytes": (C.c_int64, [C.POINTER(ChainOp), C.c_int, C.c_int, C.c_int]),
     "light_b200_chain_build": (C.c_int, [C.POINTER(ChainOp), C.c_int, C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p), C.c_size_t,

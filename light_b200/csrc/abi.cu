@@ -508,6 +508,35 @@ int light_b200_moe_route_status(int device) {
   return a | b;
 }
 
+int light_b200_gemv_multi(const void *x, const void *const *w, void *const *out, const int32_t *n, int count, int K, int out_f32, int device,
+                          void *stream) {
+  if (count < 1 || count > 4) return fail(LB200_E_SHAPE, "light_b200: gemv_multi: %d weights, want 1..4", count);
+  if (K <= 0 || K % 8) return fail(LB200_E_SHAPE, "light_b200: gemv_multi: K=%d not a positive multiple of 8", K);
+  REQUIRE_PTR(x, "gemv_multi");
+  REQUIRE_PTR(w, "gemv_multi");
+  REQUIRE_PTR(out, "gemv_multi");
+  REQUIRE_PTR(n, "gemv_multi");
+  if (!aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: gemv_multi: x not 16-byte aligned");
+  for (int i = 0; i < count; i++) {
+    if (n[i] <= 0 || !w[i] || !out[i]) return fail(LB200_E_NULL, "light_b200: gemv_multi: matrix %d: null pointer or no rows", i);
+    if (!aligned(w[i], 16)) return fail(LB200_E_ALIGN, "light_b200: gemv_multi: matrix %d not 16-byte aligned", i);
+  }
+  if (int rc = bind(device)) return rc;
+  return gemv_bf16_multi(x, w, out, n, count, K, out_f32, (cudaStream_t)stream);
+}
+
+int light_b200_gemv_gated(const void *x, const void *wg, const void *wu, void *out, int N, int K, int gelu, int device, void *stream) {
+  if (N < 0 || K <= 0 || K % 8) return fail(LB200_E_SHAPE, "light_b200: gemv_gated: bad shape N=%d K=%d", N, K);
+  if (N == 0) return 0;
+  REQUIRE_PTR(x, "gemv_gated");
+  REQUIRE_PTR(wg, "gemv_gated");
+  REQUIRE_PTR(wu, "gemv_gated");
+  REQUIRE_PTR(out, "gemv_gated");
+  if (!aligned(x, 16) || !aligned(wg, 16) || !aligned(wu, 16)) return fail(LB200_E_ALIGN, "light_b200: gemv_gated: x / weights not 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return gemv_bf16_gated(x, wg, wu, out, N, K, gelu, (cudaStream_t)stream);
+}
+
 size_t light_b200_chain_program_bytes(int n_ops) { return n_ops < 0 ? 0 : chain_program_bytes(n_ops); }
 
 int64_t light_b200_chain_arena_bytes(const lb200_chain_op *ops, int n_ops, int n_vecs, int world) {

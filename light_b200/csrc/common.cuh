@@ -128,6 +128,8 @@ int moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, floa
 int moe_sort_pairs(const int64_t *ids, int *counts, int *offsets, int64_t *sorted_pairs, int64_t *sorted_expts, int *scratch, long long M,
                    int E, cudaStream_t st);
 int moe_route_status();
+int gemv_bf16_multi(const void *x, const void *const *w, void *const *out, const int *n, int count, int K, int out_f32, cudaStream_t st);
+int gemv_bf16_gated(const void *x, const void *wg, const void *wu, void *y, int N, int K, int gelu, cudaStream_t st);
 size_t chain_program_bytes(int n_ops);
 long long chain_arena_bytes(const lb200_chain_op *ops, int n_ops, int n_vecs, int world);
 int chain_build(const lb200_chain_op *ops, int n_ops, int n_vecs, void *program, size_t program_bytes, void *const *arena, size_t arena_bytes,

@@ -203,6 +203,50 @@ def MatMulQGated(x: torch.Tensor, wg: QTensor, wu: QTensor, gelu: bool = False, 
     return out
 
 
+def LinearMulti(x: torch.Tensor, ws: Sequence[torch.Tensor], out_dtype: torch.dtype = torch.bfloat16) -> list:
+    """ops.LinearMulti (ops/gemv.go:21-78): one BF16 activation row against up to four (N_i, K) BF16 weights in one
+    launch; outputs at BF16 or F32."""
+    if len(ws) == 0:
+        raise ValueError("LinearMulti: no weights")
+    K = x.shape[-1]
+    if x.dtype != torch.bfloat16 or x.numel() != K:
+        raise ValueError(f"LinearMulti: x must be one BF16 row, got {x.dtype} {tuple(x.shape)}")
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError(f"LinearMulti: outDT {out_dtype}")
+    for i, w in enumerate(ws):
+        if w.dim() != 2 or w.shape[1] != K or w.dtype != torch.bfloat16 or w.device != x.device:
+            raise ValueError(f"LinearMulti: weight {i} must be (N, {K}) BF16 on {x.device}, got {tuple(w.shape)} {w.dtype} on {w.device}")
+    if len(ws) > 4 or K % 8:
+        raise ValueError(f"LinearMulti: K {K} / {len(ws)} weights unsupported by the fused kernel")
+    dev = _dev(x, "LinearMulti")
+    xc = x.contiguous()
+    wc = [w.contiguous() for w in ws]
+    lead = tuple(x.shape[:-1])
+    outs = [torch.empty(lead + (w.shape[0],), dtype=out_dtype, device=x.device) for w in ws]
+    n = len(ws)
+    wp = (C.c_void_p * n)(*[w.data_ptr() for w in wc])
+    op = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
+    nn = (C.c_int32 * n)(*[w.shape[0] for w in ws])
+    _lib.check(_lib.lib().light_b200_gemv_multi(_ptr(xc), wp, op, nn, n, K, int(out_dtype == torch.float32), dev, _stream(dev)))
+    return outs
+
+
+def GatedLinear(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, gelu: bool = False) -> torch.Tensor:
+    """ops.GatedLinear (ops/gemv.go:80-140): act(x . wg^T) * (x . wu^T) for one BF16 row, BF16 weights, act SiLU or
+    GELU-erf, with the BF16 roundings of the unfused sequence."""
+    K = x.shape[-1]
+    if x.dtype != torch.bfloat16 or x.numel() != K:
+        raise ValueError(f"GatedLinear: x must be one BF16 row, got {x.dtype} {tuple(x.shape)}")
+    for w in (wg, wu):
+        if w.dim() != 2 or w.shape[1] != K or w.shape[0] != wg.shape[0] or w.dtype != torch.bfloat16 or w.device != x.device:
+            raise ValueError(f"GatedLinear: weights must be (N, {K}) BF16 on {x.device}, got {tuple(wg.shape)} / {tuple(wu.shape)}")
+    dev = _dev(x, "GatedLinear")
+    out = torch.empty(tuple(x.shape[:-1]) + (wg.shape[0],), dtype=torch.bfloat16, device=x.device)
+    _lib.check(_lib.lib().light_b200_gemv_gated(_ptr(x.contiguous()), _ptr(wg.contiguous()), _ptr(wu.contiguous()), _ptr(out), wg.shape[0], K,
+                                                int(gelu), dev, _stream(dev)))
+    return out
+
+
 def NormMatMulQ(x: torch.Tensor, norm_weight: torch.Tensor, eps: float, ws: Sequence[QTensor], residual: Optional[torch.Tensor] = None,
                 gate: Optional[str] = None):
     """RMSNorm(x [+ residual]) followed by LinearMulti (gate None) or GatedLinear (gate "silu" / "gelu") over Q4_K
