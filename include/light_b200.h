@@ -156,6 +156,12 @@ LB200_API int light_b200_int4_dequant(const uint32_t *codes, const float *scales
 LB200_API int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *scales, const float *zeros, void *y,
                          int act_dtype, int M, int N, int K, int group, int device, void *stream);
 
+/* out (M, K) = x[:, idx]: the activation-column gather in front of an act-order GPTQ weight (reference ops/int4.go:129-147
+ * gatherColumns, three tensor ops there).  idx (K) device I64, a permutation of 0..K-1 (an index outside yields 0);
+ * dtype LB200_F32 / BF16 / F16. */
+LB200_API int light_b200_gather_columns(const void *x, const int64_t *idx, void *out, int dtype, int64_t M, int K, int device,
+                                        void *stream);
+
 /* Registry key {fp8_block_dequant, CUDA, F32|BF16} (reference kernels/cuda/fp8_block.go:44-69):
  * w e4m3fn codes (R,C), scale f32 (R/bR, C/bC) -> out (R,C) = f32(w) * scale, rounded once.
  * C % 4 == 0, bC % 4 == 0, R % bR == 0, C % bC == 0. */
@@ -204,8 +210,10 @@ LB200_API int light_b200_moe_gemm(const lb200_moe_args *args, int device, void *
  * (E, N / block_r, K / block_c); args->dtype = activation and output type (LB200_F32 or LB200_BF16);
  * everything else as light_b200_moe_gemm.  The reference has no grouped kernel for FP8 experts: its
  * models loop over experts on the host, one ops.MatMulF8Block per expert plus gather / scatter
- * (models/moe_routed.go:34-79); this entry point is that loop as one launch.  Needs a workspace of
- * M * K * 2 bytes (light_b200_set_workspace), M >= 256, K % 128 == 0, block_c % 64 == 0. */
+ * (models/moe_routed.go:34-79); this entry point is that loop as one launch.  With M >= 256 pairs, K % 128 == 0,
+ * block_c % 64 == 0 and a workspace of M * K * 2 bytes (light_b200_set_workspace) the tensor-core path runs;
+ * otherwise (a decode step's few pairs) one warp per output column and tile of sorted pairs, which needs only
+ * block_c % 8 == 0 and blocks that tile the weight. */
 LB200_API int light_b200_moe_gemm_f8block(const lb200_moe_args *args, const float *w_scale, int block_r, int block_c,
                                           int device, void *stream);
 
@@ -353,6 +361,33 @@ LB200_API int light_b200_moe_route_sigmoid(const float *logits, const float *bia
 LB200_API int light_b200_moe_sort_pairs(const int64_t *ids, int32_t *counts, int32_t *offsets, int64_t *sorted_pairs,
                                         int64_t *sorted_expts, int32_t *scratch, int64_t M, int E, int device, void *stream);
 LB200_API int light_b200_moe_route_status(int device);
+
+/* moe_route_deepseek: every branch of the reference's host router (models/deepseek_route.go:30-133): sigmoid != 0: scores =
+ * sigmoid(logit), choice = score + bias (bias may be NULL); else scores = choice = softmax(logits) (bias ignored).  With
+ * n_group > 1 and topk_group < n_group only the topk_group best groups of E / n_group experts stay eligible (group score:
+ * the sum of its two best choices for the sigmoid router, its best for the softmax router).  Weights are the scores of the
+ * chosen experts, divided by (their sum + 1e-20) when sigmoid and norm_topk.  E <= 1024, topk <= 32, n_group <= 32,
+ * E % n_group == 0.
+ *
+ * moe_route_topk: the selection of ops.MoERoute (ops/moe.go:29-50): probs (T, E) F32 (after the softmax) -> the topk
+ * largest per token (ties: the lower expert id), their values as weights, divided by their sum when normalize.
+ * light_b200_moe_sort_pairs then gives the expert-sorted pairs. */
+LB200_API int light_b200_moe_route_deepseek(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E,
+                                            int topk, int n_group, int topk_group, int sigmoid, int norm_topk, int device,
+                                            void *stream);
+LB200_API int light_b200_moe_route_topk(const float *probs, int64_t *ids, float *weights, int T, int E, int topk, int normalize,
+                                        int device, void *stream);
+
+/* The element-wise steps of a sparse MoE block around the two grouped matmuls, each as one launch with the roundings of
+ * the reference's unfused sequence (nn/moe.go:206-236: Narrow gate / up -> SiLU -> Mul; ops.MoECombine, ops/moe.go:206-240).
+ *   moe_gate_mul: h (M, 2 I), gate = h[:, :I], up = h[:, I:] -> out (M, I) = act(gate) * up, act SiLU (gelu = 0) or GELU-erf,
+ *     the activation rounded to the element type before the product.  I % 8 == 0.
+ *   moe_combine: pair_out (tokens * topk, N) -> out (tokens, N): the topk slot rows of a token added one after the other,
+ *     slot 0 first, every sum rounded to the element type (routing weights were applied by the grouped matmul).  N % 8 == 0.
+ * dtype LB200_F32 / BF16 / F16; pointers 16-byte aligned. */
+LB200_API int light_b200_moe_gate_mul(const void *h, void *out, int dtype, int64_t M, int I, int gelu, int device, void *stream);
+LB200_API int light_b200_moe_combine(const void *pair_out, void *out, int dtype, int64_t tokens, int N, int topk, int device,
+                                     void *stream);
 
 /* INT8 weights x INT8 activations.  Registry key {matmul_w8a8, CUDA, F32} (reference ops.MatMulW8A8,
  * ops/matmul_w8a8.go:13-120): x f32 (M, K), wq int8 (N, K), ws f32 (N) -> out f32 (M, N).  The activation

@@ -498,6 +498,51 @@ int light_b200_moe_sort_pairs(const int64_t *ids, int32_t *counts, int32_t *offs
   return moe_sort_pairs(ids, counts, offsets, sorted_pairs, sorted_expts, scratch, M, E, (cudaStream_t)stream);
 }
 
+int light_b200_moe_route_deepseek(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E, int topk, int n_group,
+                                  int topk_group, int sigmoid, int norm_topk, int device, void *stream) {
+  if (n_group < 1) n_group = 1;
+  if (T < 0 || E < 1 || E > 1024 || topk < 1 || topk > 32 || topk > E || n_group > 32 || E % n_group || topk_group < 1)
+    return fail(LB200_E_SHAPE, "light_b200: moe_route_deepseek: T=%d E=%d topk=%d n_group=%d topk_group=%d (E <= 1024, topk <= 32, n_group <= 32 divides E)",
+                T, E, topk, n_group, topk_group);
+  if (T == 0) return 0;
+  REQUIRE_PTR(logits, "moe_route_deepseek");
+  REQUIRE_PTR(ids, "moe_route_deepseek");
+  REQUIRE_PTR(weights, "moe_route_deepseek");
+  if (int rc = bind(device)) return rc;
+  return moe_route_deepseek(logits, sigmoid ? bias : nullptr, ids, weights, T, E, topk, n_group, topk_group, sigmoid, norm_topk, (cudaStream_t)stream);
+}
+
+int light_b200_moe_route_topk(const float *probs, int64_t *ids, float *weights, int T, int E, int topk, int normalize, int device, void *stream) {
+  if (T < 0 || E < 1 || E > 1024 || topk < 1 || topk > 32 || topk > E)
+    return fail(LB200_E_SHAPE, "light_b200: moe_route_topk: T=%d E=%d topk=%d (E <= 1024, topk <= min(32, E))", T, E, topk);
+  if (T == 0) return 0;
+  REQUIRE_PTR(probs, "moe_route_topk");
+  REQUIRE_PTR(ids, "moe_route_topk");
+  REQUIRE_PTR(weights, "moe_route_topk");
+  if (int rc = bind(device)) return rc;
+  return moe_route_topk(probs, ids, weights, T, E, topk, normalize, (cudaStream_t)stream);
+}
+
+int light_b200_moe_gate_mul(const void *h, void *out, int dtype, int64_t M, int I, int gelu, int device, void *stream) {
+  if (M < 0 || I <= 0 || I % 8) return fail(LB200_E_SHAPE, "light_b200: moe_gate_mul: M=%lld I=%d (I a positive multiple of 8)", (long long)M, I);
+  if (M == 0) return 0;
+  REQUIRE_PTR(h, "moe_gate_mul");
+  REQUIRE_PTR(out, "moe_gate_mul");
+  if (!aligned(h, 16) || !aligned(out, 16)) return fail(LB200_E_ALIGN, "light_b200: moe_gate_mul: pointers not 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return moe_gate_mul(h, out, dtype, M, I, gelu, (cudaStream_t)stream);
+}
+
+int light_b200_moe_combine(const void *pair_out, void *out, int dtype, int64_t tokens, int N, int topk, int device, void *stream) {
+  if (tokens < 0 || N <= 0 || N % 8 || topk < 1) return fail(LB200_E_SHAPE, "light_b200: moe_combine: tokens=%lld N=%d topk=%d", (long long)tokens, N, topk);
+  if (tokens == 0) return 0;
+  REQUIRE_PTR(pair_out, "moe_combine");
+  REQUIRE_PTR(out, "moe_combine");
+  if (!aligned(pair_out, 16) || !aligned(out, 16)) return fail(LB200_E_ALIGN, "light_b200: moe_combine: pointers not 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return moe_combine(pair_out, out, dtype, tokens, N, topk, (cudaStream_t)stream);
+}
+
 int light_b200_moe_route_status(int device) {
   if (int rc = bind(device)) return rc;
   cudaError_t e = cudaDeviceSynchronize();
@@ -506,6 +551,17 @@ int light_b200_moe_route_status(int device) {
   if (a > 1 || a < 0) return a;
   if (b > 1 || b < 0) return b;
   return a | b;
+}
+
+int light_b200_gather_columns(const void *x, const int64_t *idx, void *out, int dtype, int64_t M, int K, int device, void *stream) {
+  if (M < 0 || K < 0) return fail(LB200_E_SHAPE, "light_b200: gather_columns: M=%lld K=%d", (long long)M, K);
+  if (dtype != LB200_F32 && dtype != LB200_BF16 && dtype != LB200_F16) return fail(LB200_E_DTYPE, "light_b200: gather_columns: element type %d", dtype);
+  if (M == 0 || K == 0) return 0;
+  REQUIRE_PTR(x, "gather_columns");
+  REQUIRE_PTR(idx, "gather_columns");
+  REQUIRE_PTR(out, "gather_columns");
+  if (int rc = bind(device)) return rc;
+  return gather_columns(x, idx, out, dtype == LB200_F32 ? 4 : 2, M, K, (cudaStream_t)stream);
 }
 
 int light_b200_gemv_multi(const void *x, const void *const *w, void *const *out, const int32_t *n, int count, int K, int out_f32, int device,

@@ -128,6 +128,12 @@ int moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, floa
 int moe_sort_pairs(const int64_t *ids, int *counts, int *offsets, int64_t *sorted_pairs, int64_t *sorted_expts, int *scratch, long long M,
                    int E, cudaStream_t st);
 int moe_route_status();
+int moe_route_deepseek(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E, int topk, int n_group, int topk_group,
+                       int sigmoid, int norm_topk, cudaStream_t st);
+int moe_route_topk(const float *probs, int64_t *ids, float *weights, int T, int E, int topk, int normalize, cudaStream_t st);
+int gather_columns(const void *x, const int64_t *idx, void *out, int elt, long long M, int K, cudaStream_t st);
+int moe_gate_mul(const void *h, void *out, int dtype, long long M, int I, int gelu, cudaStream_t st);
+int moe_combine(const void *pair_out, void *out, int dtype, long long tokens, int N, int topk, cudaStream_t st);
 int gemv_bf16_multi(const void *x, const void *const *w, void *const *out, const int *n, int count, int K, int out_f32, cudaStream_t st);
 int gemv_bf16_gated(const void *x, const void *wg, const void *wu, void *y, int N, int K, int gelu, cudaStream_t st);
 size_t chain_program_bytes(int n_ops);

@@ -172,4 +172,32 @@ int int4_repack(const uint32_t *qweight, const uint32_t *qzeros, const float *sc
   return launched("int4_repack");
 }
 
+
+// out[m, k] = x[m, idx[k]]: the activation-column gather in front of an act-order GPTQ weight (reference
+// ops/int4.go:129-147 gatherColumns: transpose, IndexSelect, transpose).  Element size 2 or 4 bytes.
+template <typename T>
+__global__ void __launch_bounds__(256) gather_columns_kernel(const T *__restrict__ x, const long long *__restrict__ idx, T *__restrict__ out, long long M,
+                                                             int K) {
+  const long long total = M * K;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / K;
+    const int k = (int)(i - m * K);
+    const long long src = idx[k];
+    out[i] = (src >= 0 && src < K) ? x[m * K + src] : T(0);
+  }
+}
+
+int gather_columns(const void *x, const int64_t *idx, void *out, int elt, long long M, int K, cudaStream_t st) {
+  if (M == 0 || K == 0) return 0;
+  long long blocks = (M * K + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (elt == 4)
+    gather_columns_kernel<uint32_t><<<(unsigned)blocks, 256, 0, st>>>((const uint32_t *)x, (const long long *)idx, (uint32_t *)out, M, K);
+  else if (elt == 2)
+    gather_columns_kernel<uint16_t><<<(unsigned)blocks, 256, 0, st>>>((const uint16_t *)x, (const long long *)idx, (uint16_t *)out, M, K);
+  else
+    return fail(LB200_E_DTYPE, "light_b200: gather_columns: element size %d", elt);
+  return launched("gather_columns");
+}
+
 }  // namespace lb

@@ -6,6 +6,8 @@
 // Pairs arrive sorted by expert, so expert e owns the index range offsets[e] .. offsets[e+1].
 // The ranges come from boundary detection on the sorted expert ids (no atomics, deterministic);
 // every output row is written by exactly one warp lane set, so the result is deterministic too.
+#include <cuda_fp8.h>
+
 #include <mutex>
 
 #include "gguf_decode.cuh"
@@ -72,21 +74,57 @@ __device__ __forceinline__ void st_out(__half *p, long long i, float v) { p[i] =
 constexpr int MOE_MT = 8;     // sorted pairs per tile
 constexpr int MOE_WARPS = 8;  // output columns per CTA
 
+// What a row fetcher needs beyond the weight pointer (block-scaled FP8 only).
+struct RowAux {
+  const float *scale;
+  int bR, bC;
+};
+
 // Weight row fetchers: eight consecutive K elements of row n of expert e as f32.
 template <typename T>
 struct DenseRow {
   const T *row;
-  __device__ DenseRow(const void *w, long long e, int n, int N, int K) : row((const T *)w + ((size_t)e * N + n) * K) {}
+  __device__ DenseRow(const void *w, long long e, int n, int N, int K, const RowAux &) : row((const T *)w + ((size_t)e * N + n) * K) {}
   __device__ __forceinline__ void get(int k, float v[8]) const { load8(row + k, v); }
 };
 template <int QT>
 struct QuantRow {
   const uint8_t *row;
-  __device__ QuantRow(const void *w, long long e, int n, int N, int K)
+  __device__ QuantRow(const void *w, long long e, int n, int N, int K, const RowAux &)
       : row((const uint8_t *)w + ((size_t)e * N + n) * (size_t)(K / block_elems(QT)) * block_bytes(QT)) {}
   __device__ __forceinline__ void get(int k, float v[8]) const {
     int b = k / block_elems(QT);
     decode8<QT>(row + (size_t)b * block_bytes(QT), k - b * block_elems(QT), v);
+  }
+};
+
+// Block-scaled e4m3 codes (E, N, K) with f32 scales (E, N / bR, K / bC), bC % 8 == 0: the weight is code * scale
+// rounded to the activation type TA, i.e. the value a dequantize-then-matmul at that type multiplies with
+// (reference ops/fp8_block.go:13-60 followed by ops.MoEGemm).
+template <typename TA>
+struct F8BlockRow {
+  const uint8_t *row;
+  const float *srow;
+  int bC;
+  __device__ F8BlockRow(const void *w, long long e, int n, int N, int K, const RowAux &aux)
+      : row((const uint8_t *)w + ((size_t)e * N + n) * K),
+        srow(aux.scale + ((size_t)e * (N / aux.bR) + n / aux.bR) * (size_t)(K / aux.bC)),
+        bC(aux.bC) {}
+  __device__ __forceinline__ void get(int k, float v[8]) const {
+    const uint2 q = __ldg(reinterpret_cast<const uint2 *>(row + k));
+    const float sc = __ldg(srow + k / bC);
+    const uint32_t u[2] = {q.x, q.y};
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+      __half2_raw lo = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(u[h] & 0xFFFFu), __NV_E4M3);
+      __half2_raw hi = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(u[h] >> 16), __NV_E4M3);
+      const float2 a = __half22float2(__half2(lo)), b = __half22float2(__half2(hi));
+      v[4 * h + 0] = round_to(a.x * sc), v[4 * h + 1] = round_to(a.y * sc), v[4 * h + 2] = round_to(b.x * sc), v[4 * h + 3] = round_to(b.y * sc);
+    }
+  }
+  static __device__ __forceinline__ float round_to(float f) {
+    if constexpr (sizeof(TA) == 2) return __bfloat162float(__float2bfloat16_rn(f));
+    return f;
   }
 };
 
@@ -96,7 +134,7 @@ template <typename TI, typename TO, typename Row>
 __global__ void __launch_bounds__(MOE_WARPS * 32) moe_gemm_kernel(
     const TI *__restrict__ in, const void *__restrict__ w, const int64_t *__restrict__ pairs,
     const int64_t *__restrict__ ids, const int32_t *__restrict__ offsets, const float *__restrict__ topkw,
-    TO *__restrict__ out, long long M, long long sizeM, int E, int N, int K, int topk, int rowPerPair) {
+    TO *__restrict__ out, long long M, long long sizeM, int E, int N, int K, int topk, int rowPerPair, RowAux aux) {
   const int lane = threadIdx.x & 31;
   const int n = blockIdx.x * MOE_WARPS + (threadIdx.x >> 5);
   if (n >= N) return;
@@ -124,7 +162,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_gemm_kernel(
     float acc[MOE_MT];
 #pragma unroll
     for (int m = 0; m < MOE_MT; m++) acc[m] = 0.f;
-    Row wr(w, e, n, N, K);
+    Row wr(w, e, n, N, K, aux);
     for (int k = lane * 8; k < K; k += 256) {
       float wv[8];
       wr.get(k, wv);
@@ -157,14 +195,14 @@ static int prep(const lb200_moe_args *a, cudaStream_t st) {
 }
 
 template <typename TI, typename TO, typename Row>
-static int run(const lb200_moe_args *a, cudaStream_t st) {
+static int run(const lb200_moe_args *a, cudaStream_t st, RowAux aux = RowAux{nullptr, 0, 0}) {
   if (a->M == 0 || a->N == 0) return 0;
   dim3 grid((a->N + MOE_WARPS - 1) / MOE_WARPS, (unsigned)((a->M + MOE_MT - 1) / MOE_MT));
   if ((a->M + MOE_MT - 1) / MOE_MT > 65535)
     return fail(LB200_E_TOO_LARGE, "moe_gemm: %lld pairs exceed the kernel's grid", (long long)a->M);
   moe_gemm_kernel<TI, TO, Row><<<grid, MOE_WARPS * 32, 0, st>>>(
       (const TI *)a->input, a->weights, a->sorted_pairs, a->expert_ids, a->offsets, a->topk_weights, (TO *)a->out, a->M,
-      a->size_m, a->E, a->N, a->K, a->topk, a->row_per_pair);
+      a->size_m, a->E, a->N, a->K, a->topk, a->row_per_pair, aux);
   return launched("moe_gemm");
 }
 
@@ -226,9 +264,14 @@ int moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int bR, int 
   int took = moe_umma(a, 2, w_scale, bR, bC, device, st);
   if (took == 1) return 0;
   if (took) return took;
-  return fail(LB200_E_SHAPE,
-              "light_b200: moe_gemm_f8block: needs M >= 256 pairs, K %% 128 == 0, block_c %% 64 == 0, 16-byte aligned "
-              "tensors and a workspace of M * K * 2 bytes (light_b200_set_workspace)");
+  // Few pairs (a decode step), or a shape the tensor-core path does not take: one warp per output column and
+  // tile of sorted pairs, the weight row read once per tile.
+  if (bR <= 0 || bC <= 0 || bC % 8 || a->K % bC || a->N % bR || a->K % 8)
+    return fail(LB200_E_SHAPE, "light_b200: moe_gemm_f8block: N=%d K=%d with blocks (%d, %d): block_c must be a multiple of 8 and the blocks must tile the weight",
+                a->N, a->K, bR, bC);
+  const RowAux aux{w_scale, bR, bC};
+  if (a->dtype == LB200_F32) return run<float, float, F8BlockRow<float>>(a, st, aux);
+  return run<__nv_bfloat16, __nv_bfloat16, F8BlockRow<__nv_bfloat16>>(a, st, aux);
 }
 
 int moe_gemm_q(const lb200_moe_args *a, int device, cudaStream_t st) {

@@ -68,6 +68,169 @@ __global__ void __launch_bounds__(256) moe_route_sigmoid_kernel(const float *__r
   }
 }
 
+// The general DeepSeek router (models/deepseek_route.go:30-133, every branch), one warp per token, f64 like the
+// host code it replaces: sigmoid scores with a selection bias (V3) or a softmax over the experts (V2); with
+// n_group > 1 and topk_group < n_group only the topk_group best groups stay eligible (group score: the sum of its
+// two best choices for the sigmoid router, its best for the softmax router); then the stable descending top-k.
+// Expert e sits in slot e / 32 of lane e % 32; group g's score sits in lane g (n_group <= 32).
+__global__ void __launch_bounds__(256) moe_route_deepseek_kernel(const float *__restrict__ logits, const float *__restrict__ bias,
+                                                                 long long *__restrict__ ids, float *__restrict__ weights, int T, int E, int topk,
+                                                                 int n_group, int topk_group, int sigmoid, int norm_topk) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (tok >= T) return;
+  const int per = (E + 31) / 32, gsize = E / n_group;
+  double score[RT_MAX_PER_LANE], choice[RT_MAX_PER_LANE];
+  if (sigmoid) {
+#pragma unroll 1
+    for (int i = 0; i < per; i++) {
+      const int e = i * 32 + lane;
+      if (e < E) {
+        score[i] = 1.0 / (1.0 + exp(-(double)logits[(size_t)tok * E + e]));
+        choice[i] = score[i] + (bias ? (double)bias[e] : 0.0);
+      } else {
+        score[i] = 0.0, choice[i] = -INFINITY;
+      }
+    }
+  } else {
+    double mx = -INFINITY;
+#pragma unroll 1
+    for (int i = 0; i < per; i++) {
+      const int e = i * 32 + lane;
+      score[i] = e < E ? (double)logits[(size_t)tok * E + e] : -INFINITY;
+      mx = fmax(mx, score[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmax(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    double sum = 0.0;  // added in expert order, as the host loop does
+#pragma unroll 1
+    for (int i = 0; i < per; i++) {
+      const int e = i * 32 + lane;
+      score[i] = e < E ? exp(score[i] - mx) : 0.0;
+      for (int l = 0; l < 32; l++) {
+        const double v = __shfl_sync(0xffffffffu, score[i], l);
+        if (i * 32 + l < E) sum += v;
+      }
+    }
+#pragma unroll 1
+    for (int i = 0; i < per; i++) {
+      const int e = i * 32 + lane;
+      score[i] = e < E ? score[i] / sum : 0.0;
+      choice[i] = e < E ? score[i] : -INFINITY;
+    }
+  }
+  if (n_group > 1 && topk_group < n_group) {
+    double gsv = -INFINITY;  // lane g: score of group g
+    for (int g = 0; g < n_group; g++) {
+      double b1 = -INFINITY, b2 = -INFINITY;  // this lane's two best choices inside group g
+#pragma unroll 1
+      for (int i = 0; i < per; i++) {
+        const int e = i * 32 + lane;
+        if (e < E && e / gsize == g) {
+          if (choice[i] > b1)
+            b2 = b1, b1 = choice[i];
+          else if (choice[i] > b2)
+            b2 = choice[i];
+        }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {  // merge two sorted pairs
+        const double o1 = __shfl_xor_sync(0xffffffffu, b1, o), o2 = __shfl_xor_sync(0xffffffffu, b2, o);
+        const double n1 = fmax(b1, o1), n2 = fmax(fmin(b1, o1), fmax(b2, o2));
+        b1 = n1, b2 = n2;
+      }
+      const double sc = sigmoid ? b1 + (gsize > 1 ? b2 : 0.0) : b1;
+      if (lane == g) gsv = sc;
+    }
+    // stable descending rank of each group: groups ahead of it are the larger ones and the equal ones before it
+    int rank = 0;
+    for (int h = 0; h < n_group; h++) {
+      const double ov = __shfl_sync(0xffffffffu, gsv, h);
+      if (ov > gsv || (ov == gsv && h < lane)) rank++;
+    }
+    const int keep = lane < n_group && rank < topk_group;
+#pragma unroll 1
+    for (int i = 0; i < per; i++) {
+      const int e = i * 32 + lane;
+      const int kept = __shfl_sync(0xffffffffu, keep, e < E ? e / gsize : 0);
+      if (e < E && !kept) {
+        if (sigmoid)
+          choice[i] = -INFINITY;
+        else
+          choice[i] = 0.0, score[i] = 0.0;
+      }
+    }
+  }
+  unsigned taken = 0;
+  double den = 0.0, mine_w = 0.0;
+  long long mine_id = 0;
+  for (int k = 0; k < topk; k++) {
+    double bv = -INFINITY;
+    int be = 0x7fffffff;
+    bool have = false;
+#pragma unroll 1
+    for (int i = 0; i < per; i++)
+      if (!(taken >> i & 1u) && i * 32 + lane < E && (!have || choice[i] > bv)) bv = choice[i], be = i * 32 + lane, have = true;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const double ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (oe != 0x7fffffff && (be == 0x7fffffff || ov > bv || (ov == bv && oe < be))) bv = ov, be = oe;
+    }
+    double sc = 0.0;
+    if ((be & 31) == lane && be < E) {
+      taken |= 1u << (be >> 5);
+      sc = score[be >> 5];
+    }
+    sc = __shfl_sync(0xffffffffu, sc, be & 31);
+    den += sc;
+    if (lane == k % 32) mine_w = sc, mine_id = be;
+  }
+  if (lane < topk) {
+    const double w = (sigmoid && norm_topk) ? mine_w / (den + 1e-20) : mine_w;
+    ids[(size_t)tok * topk + lane] = mine_id;
+    weights[(size_t)tok * topk + lane] = (float)w;
+  }
+}
+
+// ops.MoERoute's selection (ops/moe.go:29-50): the k largest router probabilities of a token (ties keep the lower
+// expert id), their values as weights, divided by their f32 sum (added in selection order) when normalize.
+__global__ void __launch_bounds__(256) moe_route_topk_kernel(const float *__restrict__ probs, long long *__restrict__ ids, float *__restrict__ weights,
+                                                             int T, int E, int topk, int normalize) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tok = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (tok >= T) return;
+  const int per = (E + 31) / 32;
+  float v[RT_MAX_PER_LANE];
+#pragma unroll 1
+  for (int i = 0; i < per; i++) v[i] = i * 32 + lane < E ? probs[(size_t)tok * E + i * 32 + lane] : 0.f;
+  unsigned taken = 0;
+  float sum = 0.f, mine_w = 0.f;
+  long long mine_id = 0;
+  for (int k = 0; k < topk; k++) {
+    float bv = 0.f;
+    int be = 0x7fffffff;
+#pragma unroll 1
+    for (int i = 0; i < per; i++)
+      if (!(taken >> i & 1u) && i * 32 + lane < E && (be == 0x7fffffff || v[i] > bv)) bv = v[i], be = i * 32 + lane;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+      if (oe != 0x7fffffff && (be == 0x7fffffff || ov > bv || (ov == bv && oe < be))) bv = ov, be = oe;
+    }
+    if ((be & 31) == lane && be < E) taken |= 1u << (be >> 5);
+    sum += bv;
+    if (lane == k % 32) mine_w = bv, mine_id = be;
+  }
+  if (lane < topk) {
+    ids[(size_t)tok * topk + lane] = mine_id;
+    weights[(size_t)tok * topk + lane] = normalize ? mine_w / sum : mine_w;
+  }
+}
+
 // ---- stable counting sort of M pair ids by expert, in blocks of 1024 pairs
 constexpr int SORT_BLOCK = 1024;
 
@@ -169,6 +332,22 @@ int moe_route_sigmoid(const float *logits, const float *bias, int64_t *ids, floa
                                norm_topk);
   if (e != cudaSuccess) return fail((int)e, "light_b200: moe_route_sigmoid: %s", cudaGetErrorString(e));
   return launched("moe_route_sigmoid");
+}
+
+int moe_route_deepseek(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E, int topk, int n_group, int topk_group,
+                       int sigmoid, int norm_topk, cudaStream_t st) {
+  if (T == 0) return 0;
+  cudaError_t e = launch_chain(moe_route_deepseek_kernel, (unsigned)((T + 7) / 8), 256, 0, st, logits, bias, (long long *)ids, weights, T, E, topk,
+                               n_group, topk_group, sigmoid, norm_topk);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: moe_route_deepseek: %s", cudaGetErrorString(e));
+  return launched("moe_route_deepseek");
+}
+
+int moe_route_topk(const float *probs, int64_t *ids, float *weights, int T, int E, int topk, int normalize, cudaStream_t st) {
+  if (T == 0) return 0;
+  cudaError_t e = launch_chain(moe_route_topk_kernel, (unsigned)((T + 7) / 8), 256, 0, st, probs, (long long *)ids, weights, T, E, topk, normalize);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: moe_route_topk: %s", cudaGetErrorString(e));
+  return launched("moe_route_topk");
 }
 
 // scratch: M + nblocks * E ints (local ranks, then the per-block histograms)

@@ -164,6 +164,74 @@ class File:
         return ops.QTensor(raw.to(device), t.ggml_type, t.shape_row_major)
 
 
+    def _row_bytes(self, t: TensorInfo) -> int:
+        _, be, bb = GGML_TYPES[t.ggml_type]
+        if t.dims[0] % be:
+            raise GGUFError(f"gguf: tensor {t.name!r}: inner dim {t.dims[0]} is not a whole number of {be}-element blocks")
+        return t.dims[0] // be * bb
+
+    def qtensor_unpermuted(self, name: str, heads: int, device):
+        """loadGGUFLinearWeightUnpermuted (models/llama_gguf.go:343-382): a llama attn_q / attn_k weight with the
+        converter's row interleave undone.  File row h*hd + 2i + s holds the row h*hd + s*hd/2 + i of the original
+        checkpoint; a row is a whole run of blocks, so the rows move as bytes and stay quantized."""
+        import numpy as np
+        import torch
+
+        from . import ops
+
+        t = self.tensors.get(name)
+        if t is None:
+            raise GGUFError(f"gguf: tensor {name!r} not found")
+        if len(t.dims) != 2 or heads <= 0 or t.dims[1] % (2 * heads):
+            raise GGUFError(f"gguf: tensor {name!r} dims {t.dims} cannot be un-permuted over {heads} heads")
+        rb = self._row_bytes(t)
+        N = t.dims[1]
+        if rb * N != t.nbytes:
+            raise GGUFError(f"{name}: {t.nbytes} bytes, want {N} rows x {rb}")
+        rows = np.frombuffer(self.tensor_bytes(name), dtype=np.uint8).reshape(N, rb)
+        out = unpermute_rows(rows, heads)
+        return ops.QTensor(torch.from_numpy(out.reshape(-1)).to(device), t.ggml_type, (N, t.dims[0]))
+
+    def moe_gate_up(self, gate_name: str, up_name: str, device):
+        """The fused (E, 2 I, H) expert tensor of loadGGUFMoE (models/llama_gguf.go:153-216): expert e's gate rows
+        followed by its up rows, concatenated as bytes (a row is a whole number of blocks)."""
+        import numpy as np
+        import torch
+
+        from . import ops
+
+        gi, ui = self.tensors.get(gate_name), self.tensors.get(up_name)
+        if gi is None:
+            raise GGUFError(f"{gate_name} missing")
+        if ui is None or ui.ggml_type != gi.ggml_type or len(gi.dims) != 3 or ui.dims != gi.dims:
+            raise GGUFError(f"{up_name} missing or mismatched")
+        H, I, E = gi.dims
+        slab = self._row_bytes(gi) * I
+        gb = np.frombuffer(self.tensor_bytes(gate_name), dtype=np.uint8).reshape(E, slab)
+        ub = np.frombuffer(self.tensor_bytes(up_name), dtype=np.uint8).reshape(E, slab)
+        fused = concat_expert_slabs(gb, ub)
+        return ops.QTensor(torch.from_numpy(fused.reshape(-1)).to(device), gi.ggml_type, (E, 2 * I, H))
+
+
+def unpermute_rows(rows, heads: int):
+    """rows (N, row_bytes) uint8 -> the same rows with dst h*hd + s*hd/2 + i taken from src h*hd + 2i + s."""
+    import numpy as np
+
+    N = rows.shape[0]
+    hd = N // heads
+    half = hd // 2
+    # src index as a (heads, half, 2) array read in (heads, 2, half) order
+    src = np.arange(N).reshape(heads, half, 2).transpose(0, 2, 1).reshape(-1)
+    return np.ascontiguousarray(rows[src])
+
+
+def concat_expert_slabs(gate, up):
+    """gate, up (E, slab_bytes) uint8 -> (E, 2 * slab_bytes): every expert's gate slab, then its up slab."""
+    import numpy as np
+
+    return np.ascontiguousarray(np.concatenate([gate, up], axis=1))
+
+
 def open_file(path: str) -> File:
     return File(open(path, "rb"))
 

@@ -362,6 +362,50 @@ def DequantizeInt4(w: Int4, out_dtype: torch.dtype, out: Optional[torch.Tensor] 
     return out
 
 
+def GatherColumns(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """gatherColumns (ops/int4.go:129-147): x (M, K) -> x[:, idx], one launch."""
+    if x.dim() != 2 or idx.dtype != torch.int64 or idx.numel() != x.shape[1] or x.dtype not in _ACT:
+        raise ValueError(f"gather_columns: x {tuple(x.shape)} {x.dtype}, idx {tuple(idx.shape)} {idx.dtype}")
+    dev = _dev(x, "GatherColumns")
+    out = torch.empty_like(x, memory_format=torch.contiguous_format)
+    _lib.check(_lib.lib().light_b200_gather_columns(_ptr(x.contiguous()), _ptr(idx.contiguous()), _ptr(out), _ACT[x.dtype], x.shape[0], x.shape[1], dev,
+                                                    _stream(dev)))
+    return out
+
+
+def ConcatInt4(a: Int4, b: Int4) -> Int4:
+    """concatInt4 (models/int4_load.go:226-244): two weights stacked along N (gate over up); same K, same group, no act-order."""
+    if a.group != b.group or a.K() != b.K() or a.perm is not None or b.perm is not None:
+        raise ValueError(f"concatInt4: incompatible gate / up (group {a.group} / {b.group}, act-order {a.perm is not None} / {b.perm is not None})")
+    return Int4(torch.cat([a.codes, b.codes], 0), torch.cat([a.scales, b.scales], 0), torch.cat([a.zeros, b.zeros], 0), a.group)
+
+
+def MoEInt4(x: torch.Tensor, gate_up: Sequence[Int4], down: Sequence[Int4], route: MoERouting, topk: int, gelu: bool = False) -> torch.Tensor:
+    """ops.MoEInt4 (ops/int4.go:157-268): a sparse block over 4-bit experts.  Only the experts the routing uses are
+    expanded (light_b200_int4_dequant into one stacked buffer at x's dtype), the routing is renumbered onto them, and
+    the two grouped matmuls, the gate and the combine run as for dense experts."""
+    if x.dim() != 2 or len(gate_up) == 0 or len(gate_up) != len(down):
+        raise ValueError(f"ops.MoEInt4: x {tuple(x.shape)}, {len(gate_up)} gate-up / {len(down)} down experts")
+    T, H = x.shape
+    I2, I = gate_up[0].N(), down[0].K()
+    if gate_up[0].K() != H or down[0].N() != H or I2 != 2 * I:
+        raise ValueError(f"ops.MoEInt4: expert shapes gate-up ({I2}, {gate_up[0].K()}), down ({down[0].N()}, {I}) for hidden {H}")
+    ids = route.topk_ids.reshape(-1)
+    if int(ids.min()) < 0 or int(ids.max()) >= len(gate_up):
+        raise ValueError("ops.MoEInt4: expert out of range")
+    used, compact = torch.unique(ids, return_inverse=True)   # the experts in use, and every pair's slot among them
+    U = used.numel()
+    gu = torch.empty((U, I2, H), dtype=x.dtype, device=x.device)
+    dn = torch.empty((U, H, I), dtype=x.dtype, device=x.device)
+    for s, e in enumerate(used.tolist()):
+        DequantizeInt4(gate_up[e], x.dtype, out=gu, offset=s * I2 * H)
+        DequantizeInt4(down[e], x.dtype, out=dn, offset=s * H * I)
+    r = MoERouteFromIDs(compact.reshape(-1), route.weights, T, topk)
+    h = MoEGemm(x.contiguous(), gu, r, None, topk)
+    pair = MoEGemm(MoEGateMul(h, gelu), dn, r, r.weights, topk)
+    return MoECombine(pair, topk)
+
+
 def MatMulInt4(x: torch.Tensor, w: Int4) -> torch.Tensor:
     """ops.MatMulInt4 (ops/int4.go:66-127): x (M, K) F32 or BF16 -> (M, N) at x's dtype."""
     if x.dim() != 2 or x.shape[1] != w.K():
@@ -370,8 +414,8 @@ def MatMulInt4(x: torch.Tensor, w: Int4) -> torch.Tensor:
         raise ValueError(f"ops.MatMulInt4: activations {x.dtype}, want F32 or BF16")
     dev = _dev(x, "MatMulInt4")
     xc = x.contiguous()
-    if w.perm is not None:  # act-order GPTQ: gather x's columns into the weight's K order
-        xc = xc.index_select(1, w.perm).contiguous()
+    if w.perm is not None:  # act-order GPTQ: gather x's columns into the weight's K order (ops/int4.go:129-147)
+        xc = GatherColumns(xc, w.perm)
     M, N = x.shape[0], w.N()
     if M > 64 and x.dtype == torch.float32:  # tensor-core path: f16 copy of x in the workspace
         ensure_workspace(dev, M * w.K() * 2)
@@ -433,16 +477,41 @@ def MoERouteFromIDs(ids: torch.Tensor, weights: torch.Tensor, T: int, topk: int)
 
 
 def MoERoute(probs: torch.Tensor, topk: int, normalize: bool) -> MoERouting:
-    """ops.MoERoute (ops/moe.go:24-71): top-k of router probabilities (T, E), optional renorm."""
+    """ops.MoERoute (ops/moe.go:29-71): router probabilities (T, E) F32 -> the k largest experts per token, their
+    probabilities (renormalised when `normalize`), and the pairs sorted by expert.  Selection and sort run on the
+    device (light_b200_moe_route_topk + light_b200_moe_sort_pairs); ties keep the lower expert id."""
     if probs.dim() != 2 or probs.dtype != torch.float32:
         raise ValueError(f"moe_route: probs must be (T, E) F32, got {tuple(probs.shape)} {probs.dtype}")
     T, E = probs.shape
     if topk < 1 or topk > E:
         raise ValueError(f"moe_route: topk {topk} out of range [1, {E}]")
-    vals, ids = torch.topk(probs, topk, dim=1)
-    if normalize:
-        vals = vals / vals.sum(dim=1, keepdim=True)
-    return MoERouteFromIDs(ids, vals.contiguous(), T, topk)
+    dev = _dev(probs, "MoERoute")
+    ids = torch.empty((T, topk), dtype=torch.int64, device=probs.device)
+    w = torch.empty((T, topk), dtype=torch.float32, device=probs.device)
+    _lib.check(_lib.lib().light_b200_moe_route_topk(_ptr(probs.contiguous()), _ptr(ids), _ptr(w), T, E, topk, int(normalize), dev, _stream(dev)))
+    sp, se, _, _ = MoESortPairs(ids.reshape(-1), E)
+    return MoERouting(ids, w.reshape(-1), sp, se)
+
+
+def MoERouteDeepseek(logits: torch.Tensor, bias: Optional[torch.Tensor], topk: int, n_group: int = 1, topk_group: int = 1, sigmoid: bool = True,
+                     norm_topk: bool = True) -> MoERouting:
+    """The DeepSeek router on the device, every branch of models/deepseek_route.go:30-133 (sigmoid + bias or softmax
+    scores, group-limited selection, stable top-k), followed by the expert sort of ops.MoERouteFromIDs."""
+    if logits.dim() != 2 or logits.dtype != torch.float32:
+        raise ValueError(f"deepseek router: logits must be (T, E) F32, got {tuple(logits.shape)} {logits.dtype}")
+    T, E = logits.shape
+    n_group = max(1, n_group)
+    if E % n_group:
+        raise ValueError(f"deepseek router: {E} experts not divisible into {n_group} groups")
+    if topk < 1 or topk > E:
+        raise ValueError(f"moe_route: topk {topk} out of range [1, {E}]")
+    dev = _dev(logits, "MoERouteDeepseek")
+    ids = torch.empty((T, topk), dtype=torch.int64, device=logits.device)
+    w = torch.empty((T, topk), dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.lib().light_b200_moe_route_deepseek(_ptr(logits.contiguous()), _ptr(None if bias is None else bias.contiguous()), _ptr(ids), _ptr(w),
+                                                        T, E, topk, n_group, topk_group, int(sigmoid), int(norm_topk), dev, _stream(dev)))
+    sp, se, _, _ = MoESortPairs(ids.reshape(-1), E)
+    return MoERouting(ids, w.reshape(-1), sp, se)
 
 
 def MoERouteSigmoid(logits: torch.Tensor, bias: Optional[torch.Tensor], topk: int, norm_topk: bool = True, E_sort: Optional[int] = None) -> MoERouting:
@@ -568,15 +637,29 @@ def MoEGemmF8Block(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, block_
 
 
 def MoECombine(pair_out: torch.Tensor, topk: int) -> torch.Tensor:
-    """ops.MoECombine (ops/moe.go:206-240): sum of the topk slot rows, (M, N) -> (T, N), slot 0 first."""
+    """ops.MoECombine (ops/moe.go:206-240): sum of the topk slot rows, (M, N) -> (T, N), slot 0 first, every sum
+    rounded to the tensor's dtype (the reference adds the slots one after the other with its Add kernel): one launch."""
     M, N = pair_out.shape
     if M % topk:
         raise ValueError(f"moe_combine: {M} rows not divisible by topk {topk}")
-    v = pair_out.contiguous().reshape(M // topk, topk, N)
-    acc = v[:, 0, :]
-    for s in range(1, topk):
-        acc = acc + v[:, s, :]
-    return acc.contiguous()
+    if pair_out.dtype not in _ACT or N % 8:
+        raise ValueError(f"moe_combine: dtype {pair_out.dtype} / N {N} (a multiple of 8) unsupported")
+    dev = _dev(pair_out, "MoECombine")
+    out = torch.empty((M // topk, N), dtype=pair_out.dtype, device=pair_out.device)
+    _lib.check(_lib.lib().light_b200_moe_combine(_ptr(pair_out.contiguous()), _ptr(out), _ACT[pair_out.dtype], M // topk, N, topk, dev, _stream(dev)))
+    return out
+
+
+def MoEGateMul(h: torch.Tensor, gelu: bool = False) -> torch.Tensor:
+    """The step between the two grouped matmuls of a sparse block (nn/moe.go:206-224): h (M, 2 I) -> act(h[:, :I]) * h[:, I:],
+    act SiLU or GELU-erf, the activation rounded to the tensor's dtype before the product: one launch."""
+    if h.dim() != 2 or h.shape[1] % 16 or h.dtype not in _ACT:
+        raise ValueError(f"moe_gate_mul: want (M, 2 I) with I a multiple of 8 at F32 / BF16 / F16, got {tuple(h.shape)} {h.dtype}")
+    M, I2 = h.shape
+    dev = _dev(h, "MoEGateMul")
+    out = torch.empty((M, I2 // 2), dtype=h.dtype, device=h.device)
+    _lib.check(_lib.lib().light_b200_moe_gate_mul(_ptr(h.contiguous()), _ptr(out), _ACT[h.dtype], M, I2 // 2, int(gelu), dev, _stream(dev)))
+    return out
 
 
 # --------------------------------------------------------------------------- decode-step attention

@@ -233,6 +233,28 @@ def deepseek_route_sigmoid(logits, bias, topk: int, norm_topk: bool = True):
     return ids, ws
 
 
+def deepseek_route(logits, bias, topk: int, n_group: int = 1, topk_group: int = 1, sigmoid: bool = True, norm_topk: bool = True):
+    """models/deepseek_route.go:30-133, every branch -> (ids (T, topk) i64, weights (T, topk) f32)."""
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    if bias is not None:
+        bias = np.ascontiguousarray(bias, dtype=np.float32)
+    T, E = logits.shape
+    ids = np.empty((T, topk), np.int64)
+    ws = np.empty((T, topk), np.float32)
+    _chk(lib().lo_deepseek_route(_p(logits), _p(bias), T, E, topk, n_group, topk_group, int(sigmoid), int(norm_topk), _p(ids), _p(ws)), "deepseek_route")
+    return ids, ws
+
+
+def moe_route_topk(probs, topk: int, normalize: bool):
+    """ops.MoERoute's selection (ops/moe.go:29-50) -> (ids (T, topk) i64, weights (T, topk) f32)."""
+    probs = np.ascontiguousarray(probs, dtype=np.float32)
+    T, E = probs.shape
+    ids = np.empty((T, topk), np.int64)
+    ws = np.empty((T, topk), np.float32)
+    _chk(lib().lo_moe_route_topk(_p(probs), T, E, topk, int(normalize), _p(ids), _p(ws)), "moe_route_topk")
+    return ids, ws
+
+
 def kv_append(kbuf: np.ndarray, vbuf: np.ndarray, k: np.ndarray, v: np.ndarray, pos: int) -> None:
     """In place; arrays of any one element size, kbuf / vbuf (B, KH, Cap, D), k / v (B, KH, 1, D)."""
     B, KH, Cap, D = kbuf.shape

@@ -852,22 +852,70 @@ LO_API int lo_moe_gemm_f32(const float *in, const float *w, const int64_t *pairs
   return 0;
 }
 
-/* models/deepseek_route.go:30-133 (deepseekRouter, V3 "sigmoid" branch with nGroup = 1):
- * scores = sigmoid(logit) in f64, choice = score + bias, stable descending top-k of the
- * choices, weights = unbiased scores, renormalised by (sum + 1e-20) when norm_topk. */
-LO_API int lo_deepseek_route_sigmoid(const float *logits, const float *bias, int T, int E, int topk, int norm_topk,
-                                     int64_t *ids, float *weights) {
-  if (topk < 1 || topk > E) return -1;
-  double *scores = (double *)malloc(sizeof(double) * (size_t)E * 2);
-  double *choice = scores + E;
-  int *order = (int *)malloc(sizeof(int) * (size_t)E);
+/* models/deepseek_route.go:30-133 (deepseekRouter), every branch: scores in f64 -- sigmoid(logit) (V3; choice =
+ * score + bias) or softmax over the experts (V2) --, then, with n_group > 1 and topk_group < n_group, only the
+ * topk_group best groups stay eligible (group score: sum of its two best choices for the sigmoid router, its
+ * best for the softmax router; the others' choices become -inf, resp. choice and score become 0), a stable
+ * descending top-k of the choices (ties keep the lower expert id), weights = the scores, divided by
+ * (their sum + 1e-20) for the sigmoid router when norm_topk. */
+static int cmp_desc(const void *a, const void *b) {
+  double x = *(const double *)a, y = *(const double *)b;
+  return x < y ? 1 : x > y ? -1 : 0;
+}
+LO_API int lo_deepseek_route(const float *logits, const float *bias, int T, int E, int topk, int n_group, int topk_group,
+                             int sigmoid, int norm_topk, int64_t *ids, float *weights) {
+  if (n_group < 1) n_group = 1;
+  if (topk < 1 || topk > E || E % n_group) return -1;
+  const int per = E / n_group;
+  double *scores = (double *)malloc(sizeof(double) * (size_t)E * 3);
+  double *choice = scores + E, *grp = choice + E;
+  int *order = (int *)malloc(sizeof(int) * (size_t)(E + n_group));
+  int *gorder = order + E;
+  double *gs = (double *)malloc(sizeof(double) * (size_t)n_group);
+  char *keep = (char *)malloc((size_t)n_group);
   for (int t = 0; t < T; t++) {
     const float *row = logits + (size_t)t * E;
-    for (int e = 0; e < E; e++) {
-      scores[e] = 1.0 / (1.0 + exp(-(double)row[e]));
-      choice[e] = scores[e] + (bias ? (double)bias[e] : 0.0);
-      order[e] = e;
+    if (sigmoid) {
+      for (int e = 0; e < E; e++) {
+        scores[e] = 1.0 / (1.0 + exp(-(double)row[e]));
+        choice[e] = scores[e] + (bias ? (double)bias[e] : 0.0);
+      }
+    } else {
+      double mx = -INFINITY, sum = 0;
+      for (int e = 0; e < E; e++) mx = fmax(mx, (double)row[e]);
+      for (int e = 0; e < E; e++) {
+        scores[e] = exp((double)row[e] - mx);
+        sum += scores[e];
+      }
+      for (int e = 0; e < E; e++) {
+        scores[e] /= sum;
+        choice[e] = scores[e];
+      }
     }
+    if (n_group > 1 && topk_group < n_group) {
+      for (int g = 0; g < n_group; g++) {
+        memcpy(grp, choice + (size_t)g * per, sizeof(double) * (size_t)per);
+        qsort(grp, (size_t)per, sizeof(double), cmp_desc);
+        gs[g] = sigmoid ? grp[0] + (per > 1 ? grp[1] : 0.0) : grp[0];
+        gorder[g] = g;
+      }
+      /* stable descending order of the groups (insertion sort) */
+      for (int i = 1; i < n_group; i++) {
+        int g = gorder[i], j = i;
+        while (j > 0 && gs[gorder[j - 1]] < gs[g]) gorder[j] = gorder[j - 1], j--;
+        gorder[j] = g;
+      }
+      memset(keep, 0, (size_t)n_group);
+      for (int i = 0; i < topk_group; i++) keep[gorder[i]] = 1;
+      for (int e = 0; e < E; e++)
+        if (!keep[e / per]) {
+          if (sigmoid)
+            choice[e] = -INFINITY;
+          else
+            choice[e] = 0, scores[e] = 0;
+        }
+    }
+    for (int e = 0; e < E; e++) order[e] = e;
     /* stable selection of the topk largest choices (ties keep the lower expert id) */
     for (int k = 0; k < topk; k++) {
       int best = k;
@@ -881,13 +929,44 @@ LO_API int lo_deepseek_route_sigmoid(const float *logits, const float *bias, int
     for (int k = 0; k < topk; k++) den += scores[order[k]];
     for (int k = 0; k < topk; k++) {
       double w = scores[order[k]];
-      if (norm_topk) w /= den + 1e-20;
+      if (sigmoid && norm_topk) w /= den + 1e-20;
       ids[(size_t)t * topk + k] = order[k];
       weights[(size_t)t * topk + k] = (float)w;
     }
   }
   free(scores);
   free(order);
+  free(gs);
+  free(keep);
+  return 0;
+}
+LO_API int lo_deepseek_route_sigmoid(const float *logits, const float *bias, int T, int E, int topk, int norm_topk,
+                                     int64_t *ids, float *weights) {
+  return lo_deepseek_route(logits, bias, T, E, topk, 1, 1, 1, norm_topk, ids, weights);
+}
+
+/* ops/moe.go:29-71 (MoERoute) up to the sort: the k largest probabilities per token (ties keep the lower expert id),
+ * their values as weights, divided by their f32 sum (added in selection order) when normalize. */
+LO_API int lo_moe_route_topk(const float *probs, int T, int E, int topk, int normalize, int64_t *ids, float *weights) {
+  if (topk < 1 || topk > E) return -1;
+  char *taken = (char *)malloc((size_t)E);
+  for (int t = 0; t < T; t++) {
+    const float *row = probs + (size_t)t * E;
+    memset(taken, 0, (size_t)E);
+    float sum = 0;
+    for (int k = 0; k < topk; k++) {
+      int best = -1;
+      for (int e = 0; e < E; e++)
+        if (!taken[e] && (best < 0 || row[e] > row[best])) best = e;
+      taken[best] = 1;
+      ids[(size_t)t * topk + k] = best;
+      weights[(size_t)t * topk + k] = row[best];
+      sum += row[best];
+    }
+    if (normalize)
+      for (int k = 0; k < topk; k++) weights[(size_t)t * topk + k] /= sum;
+  }
+  free(taken);
   return 0;
 }
 

@@ -83,7 +83,14 @@ def test_host_ops_reject_cpu_tensors_and_bad_shapes():
         ops.MoEGemm(torch.zeros(3, 8), torch.zeros(2, 4, 8), r, None, 2)
     with pytest.raises(ValueError, match="topk 5 out of range"):
         ops.MoERoute(torch.zeros(2, 4), 5, False)
-    assert torch.equal(ops.MoECombine(torch.arange(8.0).reshape(4, 2), 2), torch.tensor([[2.0, 4.0], [10.0, 12.0]]))
+    with pytest.raises(ValueError, match="multiple of 8"):
+        ops.MoECombine(torch.arange(8.0).reshape(4, 2), 2)
+    with pytest.raises(ValueError, match="CUDA kernels only"):
+        ops.MoECombine(torch.zeros(4, 8), 2)
+    with pytest.raises(ValueError, match="CUDA kernels only"):
+        ops.GatherColumns(torch.zeros(4, 8), torch.arange(8))
+    with pytest.raises(ValueError, match="concatInt4"):
+        ops.ConcatInt4(i4, ops.Int4(i4.codes, i4.scales, i4.zeros, i4.group * 2))
 
 
 def test_missing_library_fails_loudly(monkeypatch):

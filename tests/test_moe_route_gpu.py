@@ -46,3 +46,60 @@ def test_sort_pairs(cuda, oracle, M, E):
     c = np.bincount(ids, minlength=E)
     assert np.array_equal(counts.cpu().numpy(), c) and np.array_equal(offsets.cpu().numpy(), np.concatenate([[0], np.cumsum(c)]))
     assert ops.moe_route_status(0) == 0
+
+
+@pytest.mark.parametrize("E,topk,n_group,topk_group,sigmoid", [(256, 8, 8, 4, True), (64, 6, 8, 3, False), (160, 6, 1, 1, False), (256, 8, 1, 1, True),
+                                                                 (96, 4, 4, 2, True), (33, 5, 1, 1, False)])
+def test_deepseek_router_every_branch(cuda, oracle, E, topk, n_group, topk_group, sigmoid):
+    """models/deepseek_route.go:30-133: group-limited selection (V3: two best per group; V2: the best), sigmoid + bias
+    and softmax scores, ids exact, weights to 1e-6."""
+    g = torch.Generator().manual_seed(E + topk)
+    T = 300
+    logits = torch.randn(T, E, generator=g)
+    logits[5] = logits[4]              # equal rows
+    logits[7, :8] = 0.25               # ties inside a row: the lower expert id wins
+    bias = torch.randn(E, generator=g) * 0.5 if sigmoid else None
+    r = ops.MoERouteDeepseek(logits.to(cuda), None if bias is None else bias.to(cuda), topk, n_group, topk_group, sigmoid, True)
+    ids, w = oracle.deepseek_route(logits.numpy(), None if bias is None else bias.numpy(), topk, n_group, topk_group, sigmoid, True)
+    assert np.array_equal(r.topk_ids.cpu().numpy(), ids)
+    assert np.max(np.abs(r.weights.reshape(T, topk).cpu().numpy() - w)) <= 1e-6
+    se, sp = torch.sort(r.topk_ids.reshape(-1), stable=True)
+    assert torch.equal(r.sorted_expts, se) and torch.equal(r.sorted_pairs, sp)
+    assert ops.moe_route_status(0) == 0
+
+
+@pytest.mark.parametrize("normalize", [True, False])
+def test_softmax_route_on_the_device(cuda, oracle, normalize):
+    """ops.MoERoute (ops/moe.go:29-71) without torch.topk / torch.sort."""
+    T, E, topk = 257, 60, 4
+    probs = torch.softmax(torch.randn(T, E, generator=torch.Generator().manual_seed(3)), dim=1)
+    probs[9, 3] = probs[9, 11]         # a tie
+    r = ops.MoERoute(probs.to(cuda), topk, normalize)
+    ids, w = oracle.moe_route_topk(probs.numpy(), topk, normalize)
+    assert np.array_equal(r.topk_ids.cpu().numpy(), ids)
+    assert np.max(np.abs(r.weights.reshape(T, topk).cpu().numpy() - w)) <= 1e-6
+    se, sp = torch.sort(r.topk_ids.reshape(-1), stable=True)
+    assert torch.equal(r.sorted_expts, se) and torch.equal(r.sorted_pairs, sp)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_gate_mul_and_combine(cuda, dtype):
+    """The unfused sequence's arithmetic (nn/moe.go:206-236, ops/moe.go:206-240): activation rounded, then the product;
+    slot rows added one after the other with a rounding per sum."""
+    g = torch.Generator().manual_seed(8)
+    M, I, topk, N = 96, 72, 4, 40
+    h = torch.randn(M, 2 * I, generator=g).to(dtype)
+    for gelu in (False, True):
+        got = ops.MoEGateMul(h.to(cuda), gelu)
+        gv = h[:, :I].float()
+        a = (0.5 * gv * (1 + torch.erf(gv / 2 ** 0.5))) if gelu else gv / (1 + torch.exp(-gv))
+        want = (a.to(dtype).float() * h[:, I:].float()).to(dtype)
+        tol = 1e-6 if dtype == torch.float32 else 2e-2
+        assert torch.allclose(got.float().cpu(), want.float(), rtol=tol, atol=tol)
+    y = torch.randn(M, N, generator=g).to(dtype)
+    got = ops.MoECombine(y.to(cuda), topk)
+    v = y.reshape(M // topk, topk, N)
+    acc = v[:, 0]
+    for s in range(1, topk):
+        acc = (acc.float() + v[:, s].float()).to(dtype)
+    assert torch.equal(got.cpu(), acc)
