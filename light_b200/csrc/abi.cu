@@ -148,8 +148,8 @@ int light_b200_matmul_q_tp(int t, const float *x, const void *const *w, float *c
 
 int light_b200_prefill_status(int device) {
   if (int rc = bind(device)) return rc;
-  const int a = prefill_status(device), b = decode_umma_status();
-  return a ? a : b;
+  const int a = prefill_status(device), b = decode_umma_status(), c = decode_nt_status();
+  return a ? a : b ? b : c;
 }
 unsigned long long light_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 int light_b200_block_elems(int t) { return block_elems(t); }
@@ -171,6 +171,15 @@ int light_b200_matmul_q(int t, const float *x, const void *w, float *out, int M,
   int took = gguf_gemv_fast(t, x, w, out, M, N, K, st);
   if (took < 0) return took;
   if (took) return 0;
+  if (M >= 2 && M <= 64) {  // tokens as MMA columns over activations staged once (needs the workspace)
+    size_t wsb = 0;
+    void *ws = workspace_ptr(device, &wsb);
+    const void *wv[1] = {w};
+    float *ov[1] = {out};
+    const int nv[1] = {N};
+    took = gguf_decode_nt(t, x, wv, ov, nv, 1, M, K, ws, wsb, st);
+    if (took != 0) return took == 1 ? 0 : took;
+  }
   took = gguf_gemv_tok(t, x, w, out, M, N, K, st);
   if (took != 0) return took == 1 ? 0 : took;
   took = gguf_prefill(t, x, w, out, M, N, K, device, st);
@@ -228,7 +237,14 @@ int light_b200_matmul_q_multi_rows(int t, const float *x, const void *const *w, 
   }
   if (!aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: matmul_q_multi_rows: x must be 16-byte aligned");
   if (int rc = bind(device)) return rc;
-  const int took = gguf_gemv_tok_multi(t, x, w, out, n, count, M, K, (cudaStream_t)stream);
+  int took = 0;
+  if (M <= 64) {
+    size_t wsb = 0;
+    void *ws = workspace_ptr(device, &wsb);
+    took = gguf_decode_nt(t, x, w, out, n, count, M, K, ws, wsb, (cudaStream_t)stream);
+    if (took != 0) return took == 1 ? 0 : took;
+  }
+  took = gguf_gemv_tok_multi(t, x, w, out, n, count, M, K, (cudaStream_t)stream);
   if (took != 0) return took == 1 ? 0 : took;
   for (int i = 0; i < count; i++)  // other types and row counts: one launch per matrix, each (M, n[i]) dense
     if (int rc = light_b200_matmul_q(t, x, w[i], out[i], M, n[i], K, device, stream)) return rc;

@@ -131,6 +131,11 @@ int moe_route_status();
 int moe_route_deepseek(const float *logits, const float *bias, int64_t *ids, float *weights, int T, int E, int topk, int n_group, int topk_group,
                        int sigmoid, int norm_topk, cudaStream_t st);
 int moe_route_topk(const float *probs, int64_t *ids, float *weights, int T, int E, int topk, int normalize, cudaStream_t st);
+void *workspace_ptr(int device, size_t *bytes);
+size_t decode_nt_ws_bytes(int M, int K);
+int gguf_decode_nt(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K, void *ws,
+                   size_t ws_bytes, cudaStream_t st);
+int decode_nt_status();
 int gather_columns(const void *x, const int64_t *idx, void *out, int elt, long long M, int K, cudaStream_t st);
 int moe_gate_mul(const void *h, void *out, int dtype, long long M, int I, int gelu, cudaStream_t st);
 int moe_combine(const void *pair_out, void *out, int dtype, long long tokens, int N, int topk, cudaStream_t st);

@@ -422,6 +422,12 @@ bool get_ws(int device, int act_dtype, int M, int K, void **ws) {
 
 }  // namespace
 
+void *workspace_ptr(int device, size_t *bytes) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  *bytes = g_ws[device].bytes;
+  return g_ws[device].ptr;
+}
+
 int set_workspace(int device, void *ptr, size_t bytes) {
   if (device < 0 || device >= 64) return fail(LB200_E_DEVICE, "light_b200: device ordinal %d out of range", device);
   if (((uintptr_t)ptr & 1023) != 0) return fail(LB200_E_ALIGN, "light_b200: workspace must be 1024-byte aligned");
