@@ -123,7 +123,7 @@ class Chain:
 
     def __init__(self, device, M, rank=0, world=1, layers=LAYERS, seed=0, share=None, fused=True):
         self.device, self.M, self.rank, self.world = device, M, rank, world
-        self.fused = fused and M <= 32  # q,k,v and gate,up as one launch each: one row, or the 2..32-row Q4_K kernels
+        self.fused = fused and M <= 64  # q,k,v and gate,up as one launch each: one row, or the batched-decode kernels (2 .. 64 rows)
         self._multi = {}
         self.lin = []  # (name, N_local, N, K, dt, weight bytes tensor)
         if share is not None:  # same weights, another token count
@@ -139,6 +139,8 @@ class Chain:
         self.out = [torch.empty(M, e[2], device=device) for e in self.lin]  # full-width outputs (gathered when world > 1)
         self.local = [torch.empty(M, e[1], device=device) for e in self.lin] if world > 1 else self.out
         self.dev_index = device.index or 0
+        if M > 1:  # the batched-decode kernels stage x and keep their split-K partial sums in the library's workspace
+            ops.ensure_workspace(self.dev_index, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, FFN)))
         self.peer, self.fx, self.dc, self.gather_kind = None, None, None, "none"
         self.attn = None
         if world > 1:

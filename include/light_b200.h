@@ -81,9 +81,14 @@ LB200_API unsigned long long light_b200_launch_count(void);
  * The reference keeps the same kind of buffer, one reusable weight scratch per device
  * (ops/fp8_block.go:105-154 weightScratch).  Here it holds the f16 copy of the activations that the
  * tensor-core prefill path streams by TMA: matmul_q with M > 64 needs M * K * 2 bytes; without a
- * large enough workspace such calls run the slower shape-generic kernel.  Calls that use the
- * workspace must not overlap on the GPU. */
+ * large enough workspace such calls run the slower shape-generic kernel.  Batched decode (matmul_q and
+ * matmul_q_multi_rows with 2 <= M <= 64 on Q4_K / Q6_K) keeps there the activations staged as f16 fragment
+ * records and the split-K partial sums of its persistent grid.  Calls that use the workspace must not overlap
+ * on the GPU. */
 LB200_API int light_b200_set_workspace(int device, void *ptr, size_t bytes);
+
+/* The workspace size with which light_b200_matmul_q / _multi_rows take their fastest path for M rows of K. */
+LB200_API unsigned long long light_b200_matmul_q_workspace_bytes(int M, int K);
 
 /* 0 if no bounded device-side wait of the tensor-core kernels ever gave up on this device, 1 if one
  * did (the affected call's output is then incomplete).  Synchronises with the device. */

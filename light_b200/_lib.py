@@ -124,6 +124,7 @@ SYMBOLS = {
                                      C.c_int, C.c_void_p]),
     "light_b200_rope": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_double, C.c_int, C.c_void_p]),
     "light_b200_decode_attn_status": (C.c_int, [C.c_int]),
+    "light_b200_matmul_q_workspace_bytes": (C.c_ulonglong, [C.c_int, C.c_int]),
     "light_b200_gather_columns": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int, C.c_int, C.c_void_p]),
     "light_b200_gemv_multi": (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int,
                                         C.c_int, C.c_void_p]),

@@ -151,6 +151,12 @@ int light_b200_prefill_status(int device) {
   const int a = prefill_status(device), b = decode_umma_status(), c = decode_nt_status();
   return a ? a : b ? b : c;
 }
+unsigned long long light_b200_matmul_q_workspace_bytes(int M, int K) {
+  if (M <= 1 || K <= 0) return 0;
+  const unsigned long long f16_copy = (unsigned long long)M * K * 2;  // the tensor-core paths' f16 copy of x
+  const unsigned long long staged = M <= 64 ? decode_nt_ws_bytes(M, K) : 0;
+  return f16_copy > staged ? f16_copy : staged;
+}
 unsigned long long light_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 int light_b200_block_elems(int t) { return block_elems(t); }
 int light_b200_block_bytes(int t) { return block_bytes(t); }

@@ -4,18 +4,23 @@
 //   pre-pass   x (M, K) f32 -> f16 in the order the B fragments are read, one 544-byte record per (K block,
 //              token): 512 bytes of values and, for Q4_K, the eight sub-block sums as f16 hi | lo.  Tokens are
 //              padded to a multiple of eight with zeros.  One warp per record.
-//   main       a CTA of eight warps owns eight consecutive row tiles of 16 (one per warp, no sum across warps)
-//              and walks a run of K blocks.  Per block ONE bulk copy (cp.async.bulk, completion on an mbarrier)
-//              brings all tokens' records into a double buffer shared by the eight warps; the weights arrive
-//              through a per-warp ring of 16-byte asynchronous copies and are expanded in registers straight
-//              into A fragments (Q4_K: LOP3 to f16 (64 + q), one HFMA2 with the 6-bit scale; Q6_K: PRMT to f16
-//              (1024 + code), offset and scale by HADD2 / HMUL2), so an expanded weight never touches shared
-//              memory and serves NG groups of eight tokens.  Once per block and row, acc += d * D.  K is split
-//              over a thread-block cluster of up to 8 CTAs whose partial sums meet in distributed shared memory.
+//   main       the work is the list of (group of eight row tiles, K block) pairs, group-major; a persistent grid
+//              (one or two CTAs per SM) cuts the list into equal consecutive runs, so every SM gets the same
+//              number of blocks whatever the matrix's height.  A CTA of eight warps walks its run: warp w owns
+//              row tile w of the current group.  Per block ONE bulk copy (cp.async.bulk, completion on an
+//              mbarrier) brings all tokens' records into a ring shared by the eight warps, who hand a buffer back
+//              through a second mbarrier (no CTA-wide barrier in the loop); the weights arrive through a per-warp
+//              ring of 16-byte asynchronous copies and are expanded in registers straight into A fragments
+//              (Q4_K: LOP3 to f16 (64 + q), one HFMA2 with the 6-bit scale; Q6_K: PRMT to f16 (1024 + code),
+//              offset and scale by HADD2 / HMUL2), so an expanded weight never touches shared memory and serves
+//              NG groups of eight tokens.  Once per block and row, acc += d * D.
+//   split K    a run that starts or ends inside a group leaves a partial sum.  Partial sums go to the workspace
+//              with a per-warp flag carrying the call's epoch; the CTA that holds the END of a group adds the
+//              parts of the CTAs before it, in CTA order, after it has finished its own run (by then they are
+//              there; the wait is bounded) and stores the rows.
 //
-// Every sum has a fixed order (k inside an MMA, blocks in a rotated but fixed sequence per CTA, cluster ranks
-// ascending), so results are deterministic.  x is rounded to f16 once (2^-11 relative per element, about 2e-4
-// relative L2 on the output).  Replaces, for 9 .. 64 rows, kernels that converted x inside every CTA.
+// Every sum has a fixed order (k inside an MMA, blocks ascending inside a run, runs in CTA order), so results are
+// deterministic.  x is rounded to f16 once (2^-11 relative per element, about 2e-4 relative L2 on the output).
 #include <type_traits>
 
 #include "common.cuh"
@@ -37,7 +42,13 @@ struct NtArgs {  // up to four matrices that share x: their row tiles form one l
   int count;
 };
 
-__device__ int g_nt_status;  // non-zero: a bounded wait for a block of activations gave up (sticky)
+__device__ int g_nt_status;  // non-zero: a bounded wait (a block of activations, a partial sum) gave up (sticky)
+
+// Split-K bookkeeping of the persistent grid, in the library's own device memory (zero at load, never handed out):
+// the epoch of the current call (bumped by the staging launch) and one flag per (CTA, first | last run, warp).
+constexpr int MAX_GRID = 320;
+__device__ unsigned int g_nt_epoch;
+__device__ unsigned int g_nt_flags[MAX_GRID * 2 * 8];
 
 __device__ __forceinline__ void resolve(const NtArgs &a, int T, int &j, int &r0) {
   j = 0;
@@ -61,6 +72,7 @@ __global__ void __launch_bounds__(THREADS) x_stage_kernel(const float *__restric
   const int rec = blockIdx.x * CW + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int nb = K >> 8;
   pdl_wait();  // x is the previous launch's output, and the launch before may still read the staging buffer
+  if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_nt_epoch, 1u);  // a new call: flags of earlier calls no longer match
   if (rec >= nb * NT) return;
   const int b = rec / NT, tk = rec - b * NT;
   uint8_t *dst = xs + (size_t)rec * TOK_PITCH;
@@ -104,70 +116,144 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
   asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
+__device__ __forceinline__ unsigned int ld_acquire(const unsigned int *p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(unsigned int *p, unsigned int v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
 
+// The ring of staged activations: XS buffers, each with a `full` mbarrier (one arrival + the copy's bytes) and an
+// `empty` mbarrier (one arrival per warp).  Thread 0 is the producer; it refills a buffer as soon as all warps have
+// handed it back, looking at the barrier without blocking except when its own warp needs the block.
 template <int NG>
-struct XFeed {  // a ring of XS buffers of staged activations, one mbarrier each
+struct XFeed {
   static constexpr int NT = 8 * NG, XBUF = NT * TOK_PITCH;
-  static constexpr int XS = NG <= 2 ? 4 : NG == 4 ? 3 : 2;  // blocks of x in flight: the copy's latency spans several short blocks
-  static constexpr int BYTES = XS * XBUF + 64;
-  uint32_t buf0, bar0;
+  static constexpr int XS = NG <= 2 ? 4 : NG == 4 ? 3 : 2;
+  static constexpr int BYTES = XS * XBUF + 128;
+  uint32_t buf0, full0, empty0;
   const uint8_t *xs;
   volatile int *abort_flag;
-  __device__ __forceinline__ void init(uint32_t base, unsigned char *gen, const uint8_t *xs_) {
-    buf0 = base, bar0 = base + XS * XBUF, xs = xs_;
-    abort_flag = reinterpret_cast<volatile int *>(gen + XS * XBUF + 8 * XS);
+  int nf, n, nb, it0;  // next block to fetch (local index), blocks in this CTA's run
+  __device__ __forceinline__ void init(uint32_t base, unsigned char *gen, const uint8_t *xs_, int it0_, int n_, int nb_) {
+    buf0 = base, full0 = base + XS * XBUF, empty0 = full0 + 8 * XS, xs = xs_, nf = 0, n = n_, nb = nb_, it0 = it0_;
+    abort_flag = reinterpret_cast<volatile int *>(gen + XS * XBUF + 16 * XS);
     if (threadIdx.x == 0) {
 #pragma unroll
-      for (int i = 0; i < XS; i++) umma::mbar_init(bar0 + 8 * i, 1);
+      for (int i = 0; i < XS; i++) umma::mbar_init(full0 + 8 * i, 1), umma::mbar_init(empty0 + 8 * i, CW);
       *abort_flag = 0;
       umma::fence_barrier_init();
     }
   }
-  __device__ __forceinline__ uint32_t buf(int i) const { return buf0 + (uint32_t)(i % XS) * XBUF; }
-  __device__ __forceinline__ void fetch(int i, int block) const {  // one thread
-    const uint32_t h = (uint32_t)(i % XS);
-    umma::mbar_arrive_expect_tx(bar0 + 8 * h, XBUF);
-    bulk_g2s(buf0 + h * XBUF, xs + (size_t)block * XBUF, XBUF, bar0 + 8 * h);
+  __device__ __forceinline__ uint32_t buf(int k) const { return buf0 + (uint32_t)(k % XS) * XBUF; }
+  __device__ __forceinline__ void fetch() {  // thread 0: block nf of the run
+    const uint32_t h = (uint32_t)(nf % XS);
+    umma::mbar_arrive_expect_tx(full0 + 8 * h, XBUF);
+    bulk_g2s(buf0 + h * XBUF, xs + (size_t)((it0 + nf) % nb) * XBUF, XBUF, full0 + 8 * h);
+    nf++;
   }
-  __device__ __forceinline__ bool wait(int i) const {
-    const bool ok = umma::mbar_wait(bar0 + 8 * (i % XS), (uint32_t)((i / XS) & 1), abort_flag, 200000000ull);
+  __device__ __forceinline__ void start() {  // thread 0, after the barriers are visible and x is staged
+    while (nf < n && nf < XS) fetch();
+  }
+  // thread 0, before its warp waits for block k: refill what is free; block for the buffer only if block k itself
+  // has not been requested yet
+  __device__ __forceinline__ void pump(int k) {
+    while (nf < n) {
+      const uint32_t bar = empty0 + 8 * (uint32_t)(nf % XS), par = (uint32_t)((nf / XS - 1) & 1);
+      if (umma::mbar_test_wait(bar, par)) { fetch(); continue; }
+      if (nf > k) break;
+      if (!umma::mbar_wait(bar, par, abort_flag, 200000000ull)) { g_nt_status = 1; break; }
+    }
+  }
+  __device__ __forceinline__ bool wait_full(int k) const {
+    const bool ok = umma::mbar_wait(full0 + 8 * (uint32_t)(k % XS), (uint32_t)((k / XS) & 1), abort_flag, 200000000ull);
     if (!ok) g_nt_status = 1;
     return ok;
   }
+  __device__ __forceinline__ void release(int k, int lane) const {  // the warp is done reading block k
+    __syncwarp();
+    if (lane == 0) umma::mbar_arrive(empty0 + 8 * (uint32_t)(k % XS));
+  }
 };
 
-// The CTA's partial sums partial[token][128 rows] (over its drained weight ring) -> out, summed over the cluster.
-template <int NT>
-__device__ __forceinline__ void reduce_out(const NtArgs &ma, uint32_t sbase, int KS, int rank, int tiles, int M) {
-  if (KS > 1) umma::cluster_sync(); else __syncthreads();
-  const int per = NT / KS;  // KS divides 8
-  for (int idx = threadIdx.x; idx < per * 128; idx += THREADS) {
-    const int tok = rank * per + (idx >> 7), rr = idx & 127, tile = blockIdx.x * CW + (rr >> 4);
-    const uint32_t a = sbase + (uint32_t)(tok * 128 + rr) * 4u;
-    float v = 0.f;
-    if (KS > 1) {
-      for (int p = 0; p < KS; p++) v += umma::ld_cluster_f32(umma::map_to_rank(a, (uint32_t)p));
-    } else {
-      asm volatile("ld.shared.f32 %0, [%1];\n" : "=f"(v) : "r"(a));
-    }
-    if (tok < M && tile < tiles) {
-      int oj, orow;
-      resolve(ma, tile, oj, orow);
-      ma.out[oj][(size_t)tok * ma.n[oj] + orow + (rr & 15)] = v;
-    }
-  }
-  if (KS > 1) umma::cluster_sync();  // nobody leaves while a peer still reads its partials
-}
+struct Run {  // the (group, block) list cut into G consecutive runs, one per CTA: q entries each (q > 0), or as even as possible
+  int T, G, q, c, nb;
+  __device__ __forceinline__ int begin(int cta) const { return q > 0 ? min(cta * q, T) : (int)((long long)T * cta / G); }
+};
 
+// acc -> out rows of one tile: lane (g, t) holds rows g, g+8 x tokens 2t, 2t+1 of every group of eight
 template <int NG>
-__device__ __forceinline__ void park_acc(const float (&acc)[NG][4], uint32_t sbase, int warp, int g, int t) {
+__device__ __forceinline__ void store_tile(const float (&acc)[NG][4], float *out, int n, int r0, int M, int g, int t) {
 #pragma unroll
   for (int q = 0; q < NG; q++)
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-      const int tok = q * 8 + 2 * t + (c & 1), row = warp * ROWS + g + 8 * (c >> 1);
-      asm volatile("st.shared.f32 [%0], %1;\n" ::"r"(sbase + (uint32_t)(tok * 128 + row) * 4u), "f"(acc[q][c]));
+      const int tok = q * 8 + 2 * t + (c & 1), row = r0 + g + 8 * (c >> 1);
+      if (tok < M) out[(size_t)tok * n + row] = acc[q][c];
     }
+}
+
+template <int NG>
+__device__ __forceinline__ float *part_of(float *parts, int cta, int slot, int warp) {
+  return parts + ((size_t)(cta * 2 + slot) * CW + warp) * (NG * 4 * 32);
+}
+
+template <int NG>
+__device__ __forceinline__ void write_part(const float (&acc)[NG][4], float *parts, int cta, int slot, int warp, int lane, unsigned int epoch) {
+  float *p = part_of<NG>(parts, cta, slot, warp) + lane;
+#pragma unroll
+  for (int q = 0; q < NG; q++)
+#pragma unroll
+    for (int c = 0; c < 4; c++) __stcg(p + (q * 4 + c) * 32, acc[q][c]);
+  __threadfence();
+  __syncwarp();
+  if (lane == 0) st_release(&g_nt_flags[(cta * 2 + slot) * CW + warp], epoch);
+}
+
+// The group whose end this CTA holds: parts of the CTAs before it (in CTA order), then its own, -> acc.  The flags
+// are polled by one lane each, all at once; the parts are fetched several CTAs at a time and added in order.
+template <int NG>
+__device__ __forceinline__ void fix_up(const Run &run, int grp, float *parts, int warp, int lane, unsigned int epoch, float (&acc)[NG][4]) {
+  const int first = grp * run.nb;  // the group's first list index
+  int lo = run.q > 0 ? first / run.q : (int)((long long)first * run.G / run.T);
+  while (lo > 0 && run.begin(lo) > first) lo--;
+  while (run.begin(lo + 1) <= first) lo++;
+  auto slot_of = [&](int cta) { return (cta == run.c || run.begin(cta) >= first) ? 0 : 1; };  // its first run, or (it began in an earlier group) its last
+  for (int base = lo; base < run.c; base += 32) {
+    const int cta = base + lane;
+    bool ok = true;
+    if (cta < run.c) {
+      const unsigned int *f = &g_nt_flags[(cta * 2 + slot_of(cta)) * CW + warp];
+      const unsigned long long t0 = umma::global_ns();
+      for (uint32_t i = 0; ld_acquire(f) != epoch; i++)
+        if ((i & 63u) == 63u) {
+          if (umma::global_ns() - t0 > 200000000ull) { ok = false; break; }
+          __nanosleep(100);
+        }
+    }
+    if (!__all_sync(0xffffffffu, ok)) { g_nt_status = 2; return; }
+  }
+  __threadfence();
+#pragma unroll
+  for (int q = 0; q < NG; q++) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
+  constexpr int AT = NG <= 2 ? 4 : NG == 4 ? 2 : 1;  // CTAs whose parts are in flight together
+  for (int base = lo; base <= run.c; base += AT) {
+    float v[AT][NG * 4];
+#pragma unroll
+    for (int a = 0; a < AT; a++) {
+      const int cta = min(base + a, run.c);
+      const float *p = part_of<NG>(parts, cta, slot_of(cta), warp) + lane;
+#pragma unroll
+      for (int i = 0; i < NG * 4; i++) v[a][i] = __ldcg(p + i * 32);
+    }
+#pragma unroll
+    for (int a = 0; a < AT; a++)
+      if (base + a <= run.c)
+#pragma unroll
+        for (int i = 0; i < NG * 4; i++) acc[i >> 2][i & 3] += v[a][i];
+  }
 }
 
 // ------------------------------------------------------------------------------------ Q4_K
@@ -175,140 +261,86 @@ __device__ __forceinline__ void park_acc(const float (&acc)[NG][4], uint32_t sba
 // sub-block 2t (low nibbles) and one for 2t+1 (high nibbles).  The minimum term -dmin * m_s * sum_{k in s} x_k
 // is a second small contraction over the eight sub-blocks: A' = -dmin * m as f16 hi + lo, B' = the sub-block
 // sums of x as f16 hi (both k halves), then A' = hi against the lo half of the sums.
-constexpr int Q4_STAGES = 3, Q4_TILE = ROWS * 144, Q4_RING = CW * Q4_STAGES * Q4_TILE;
-
-template <int NG>
-constexpr int q4_smem() { return Q4_RING + XFeed<NG>::BYTES; }
-
-template <int NG>
-__global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) q4k_nt_kernel(const uint8_t *__restrict__ xs, const __grid_constant__ NtArgs ma,
-                                                                        int tiles, int M, int K) {
-  constexpr int S = Q4_STAGES;
-  static_assert(8 * NG * 128 * 4 <= Q4_RING, "the partial sums reuse the ring");
-  extern __shared__ __align__(128) unsigned char dyn[];  // [ring: 8 warps x S tiles][x buffer 0][x buffer 1][2 mbarriers][flag]
-  pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int nb = K >> 8;
-  const int KS = gridDim.y, rank = blockIdx.y;
-  const int b0 = nb * rank / KS, b1 = nb * (rank + 1) / KS, nloc = b1 - b0;
-  // CTAs of one K run start at different blocks of it: otherwise all of them ask L2 for the same lines at once
-  const int rot = (int)(blockIdx.x * 5u) % nloc;
-  auto blk = [&](int i) { const int j = i + rot; return b0 + (j >= nloc ? j - nloc : j); };
-  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dyn);
-  XFeed<NG> xf;
-  xf.init(sbase + Q4_RING, dyn + Q4_RING, xs);
-
-  const int tile = blockIdx.x * CW + warp;
-  const bool live = tile < tiles;
-  int wj = 0, r0 = 0;
-  if (live) resolve(ma, tile, wj, r0);
-  const uint8_t *w = ma.w[wj];
-  const uint32_t row_bytes = (uint32_t)nb * 144u;
-  const uint32_t ring = sbase + warp * (S * Q4_TILE);
-  const bool hdr_hi = t >= 2;
-  const int hdr_sh = (t & 1) * 16;
-  const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
-  uint32_t soff[5];
+struct Q4Fmt {
+  static constexpr int S = 3, TILE = ROWS * 144, BLOCK = 144;
+  uint32_t soff[5], ld_off, hdr_sh;
+  bool hdr_hi;
+  __device__ __forceinline__ void setup(int lane, uint32_t row_bytes) {
 #pragma unroll
-  for (int i = 0; i < 5; i++) {
-    const uint32_t c = lane + 32 * i, row = c / 9u;
-    soff[i] = row * row_bytes + (c - 9u * row) * 16u;
-  }
-  const uint32_t ld_off = g * 144u + 32u * t;
-  int i_b = 0, i_slot = 0;
-  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
-    if (live && i_b < nloc) {
-      const uint8_t *base = w + ((size_t)r0 * row_bytes + (uint32_t)blk(i_b) * 144u);
-      const uint32_t dst = ring + i_slot * Q4_TILE + lane * 16;
-#pragma unroll
-      for (int i = 0; i < 4; i++) cp_async16(dst + i * 512, base + soff[i]);
-      if (lane < 16) cp_async16(dst + 2048, base + soff[4]);
-      i_slot = i_slot + 1 == S ? 0 : i_slot + 1;
-      i_b++;
+    for (int i = 0; i < 5; i++) {
+      const uint32_t c = lane + 32 * i, row = c / 9u;
+      soff[i] = row * row_bytes + (c - 9u * row) * 16u;
     }
-    cp_async_commit();
-  };
-#pragma unroll 1
-  for (int p = 0; p < S; p++) issue();
-  __syncthreads();  // the mbarriers are initialised
-  pdl_wait();       // the staged activations are the pre-pass's output; the weights requested above are not
-  if (threadIdx.x == 0)
-    for (int i = 0; i < XFeed<NG>::XS && i < nloc; i++) xf.fetch(i, blk(i));
-
-  float acc[NG][4];
+    const int g = lane >> 2, t = lane & 3;
+    ld_off = g * 144u + 32u * t, hdr_hi = t >= 2, hdr_sh = (t & 1) * 16;
+  }
+  __device__ __forceinline__ void issue(uint32_t dst, const uint8_t *tile0, uint32_t blk, int lane, const uint8_t *) const {
+    const uint8_t *base = tile0 + blk * 144u;
+    dst += lane * 16;
 #pragma unroll
-  for (int q = 0; q < NG; q++) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
-  int slot = 0;
-  for (int bi = 0; bi < nloc; bi++) {
-    const uint32_t xb = xf.buf(bi);
-    if (!xf.wait(bi)) break;
-    if (live) {
-      cp_async_wait<S - 1>();
-      __syncwarp();
-      const uint32_t sb = ring + slot * Q4_TILE + ld_off;
-      slot = slot + 1 == S ? 0 : slot + 1;
-      const uint4 h0 = lds128(sb - 32u * t), h1 = lds128(sb - 32u * t + 8 * 144);
-      const uint4 qa0 = lds128(sb + 16), qa1 = lds128(sb + 32);
-      const uint4 qb0 = lds128(sb + 8 * 144 + 16), qb1 = lds128(sb + 8 * 144 + 32);
-      __syncwarp();  // the slot is free again
-      issue();
-      __half2 s2[2][2], c2[2][2];
-      uint32_t dmh[2], dml[2];
-      float dd[2];
+    for (int i = 0; i < 4; i++) cp_async16(dst + i * 512, base + soff[i]);
+    if (lane < 16) cp_async16(dst + 2048, base + soff[4]);
+  }
+  template <int NG, typename F>
+  __device__ __forceinline__ void unit(uint32_t slot_addr, uint32_t xb, float (&acc)[NG][4], uint32_t, uint32_t, int lane, F &&slot_free) const {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
+    const uint32_t sb = slot_addr + ld_off;
+    const uint4 h0 = lds128(sb - 32u * t), h1 = lds128(sb - 32u * t + 8 * 144);
+    const uint4 qa0 = lds128(sb + 16), qa1 = lds128(sb + 32);
+    const uint4 qb0 = lds128(sb + 8 * 144 + 16), qb1 = lds128(sb + 8 * 144 + 32);
+    __syncwarp();  // the slot is free again
+    slot_free();
+    __half2 s2[2][2], c2[2][2];
+    uint32_t dmh[2], dml[2];
+    float dd[2];
 #pragma unroll
-      for (int r = 0; r < 2; r++) {
-        const uint4 &h = r ? h1 : h0;
-        const float2 df = __half22float2(u2h(h.x));  // (d, dmin)
-        const uint32_t scw = hdr_hi ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
-        const uint32_t mnw = hdr_hi ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
-        const uint32_t sc = scw >> hdr_sh, mn = mnw >> hdr_sh;
-        s2[r][0] = __half2half2(__uint2half_rn(sc & 0xFFu)), s2[r][1] = __half2half2(__uint2half_rn((sc >> 8) & 0xFFu));
-        c2[r][0] = __hmul2(s2[r][0], __float2half2_rn(-64.f)), c2[r][1] = __hmul2(s2[r][1], __float2half2_rn(-64.f));
-        const float m0 = -df.y * (float)(mn & 0xFFu), m1 = -df.y * (float)((mn >> 8) & 0xFFu);
-        const __half2 mh = __floats2half2_rn(m0, m1);
-        const float2 mf = __half22float2(mh);
-        dmh[r] = h2u(mh), dml[r] = h2u(__floats2half2_rn(m0 - mf.x, m1 - mf.y));
-        dd[r] = df.x;
-      }
-      float dq[NG][4];
+    for (int r = 0; r < 2; r++) {
+      const uint4 &h = r ? h1 : h0;
+      const float2 df = __half22float2(u2h(h.x));  // (d, dmin)
+      const uint32_t scw = hdr_hi ? ((h.w & 0x0F0F0F0Fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3F3F3F3Fu);
+      const uint32_t mnw = hdr_hi ? (((h.w >> 4) & 0x0F0F0F0Fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3F3F3F3Fu);
+      const uint32_t sc = scw >> hdr_sh, mn = mnw >> hdr_sh;
+      s2[r][0] = __half2half2(__uint2half_rn(sc & 0xFFu)), s2[r][1] = __half2half2(__uint2half_rn((sc >> 8) & 0xFFu));
+      c2[r][0] = __hmul2(s2[r][0], __float2half2_rn(-64.f)), c2[r][1] = __hmul2(s2[r][1], __float2half2_rn(-64.f));
+      const float m0 = -df.y * (float)(mn & 0xFFu), m1 = -df.y * (float)((mn >> 8) & 0xFFu);
+      const __half2 mh = __floats2half2_rn(m0, m1);
+      const float2 mf = __half22float2(mh);
+      dmh[r] = h2u(mh), dml[r] = h2u(__floats2half2_rn(m0 - mf.x, m1 - mf.y));
+      dd[r] = df.x;
+    }
+    float dq[NG][4];
 #pragma unroll
-      for (int q = 0; q < NG; q++) dq[q][0] = dq[q][1] = dq[q][2] = dq[q][3] = 0.f;
-      const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
-      const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
-      auto scl = [](uint32_t raw, __half2 s, __half2 c) { return h2u(__hfma2(u2h(raw), s, c)); };  // (64 + q) sc - 64 sc, exact
-      const uint32_t bx = xb + g * TOK_PITCH + t * 8;  // B fragments of token g of group 0
+    for (int q = 0; q < NG; q++) dq[q][0] = dq[q][1] = dq[q][2] = dq[q][3] = 0.f;
+    const uint32_t qg[8] = {qa0.x, qa0.y, qa0.z, qa0.w, qa1.x, qa1.y, qa1.z, qa1.w};
+    const uint32_t qh[8] = {qb0.x, qb0.y, qb0.z, qb0.w, qb1.x, qb1.y, qb1.z, qb1.w};
+    auto scl = [](uint32_t raw, __half2 s, __half2 c) { return h2u(__hfma2(u2h(raw), s, c)); };  // (64 + q) sc - 64 sc, exact
+    const uint32_t bx = xb + g * TOK_PITCH + t * 8;  // B fragments of token g of group 0
 #pragma unroll
-      for (int i = 0; i < 8; i++) {
-        const uint32_t vg = qg[i], vh = qh[i];
-        const uint32_t e0 = scl(and_or(vg << 4, mask, magic), s2[0][0], c2[0][0]), e1 = scl(and_or(vh << 4, mask, magic), s2[1][0], c2[1][0]);
-        const uint32_t e2 = scl(and_or(vg >> 4, mask, magic), s2[0][0], c2[0][0]), e3 = scl(and_or(vh >> 4, mask, magic), s2[1][0], c2[1][0]);
-        const uint32_t o0 = scl(and_or(vg, mask, magic), s2[0][1], c2[0][1]), o1 = scl(and_or(vh, mask, magic), s2[1][1], c2[1][1]);
-        const uint32_t o2 = scl(and_or(vg >> 8, mask, magic), s2[0][1], c2[0][1]), o3 = scl(and_or(vh >> 8, mask, magic), s2[1][1], c2[1][1]);
-#pragma unroll
-        for (int q = 0; q < NG; q++) {
-          const uint2 be = lds64(bx + q * (8 * TOK_PITCH) + i * 32), bo = lds64(bx + q * (8 * TOK_PITCH) + (8 + i) * 32);
-          mma16816(dq[q], e0, e1, e2, e3, be.x, be.y);
-          mma16816(dq[q], o0, o1, o2, o3, bo.x, bo.y);
-        }
-      }
+    for (int i = 0; i < 8; i++) {
+      const uint32_t vg = qg[i], vh = qh[i];
+      const uint32_t e0 = scl(and_or(vg << 4, mask, magic), s2[0][0], c2[0][0]), e1 = scl(and_or(vh << 4, mask, magic), s2[1][0], c2[1][0]);
+      const uint32_t e2 = scl(and_or(vg >> 4, mask, magic), s2[0][0], c2[0][0]), e3 = scl(and_or(vh >> 4, mask, magic), s2[1][0], c2[1][0]);
+      const uint32_t o0 = scl(and_or(vg, mask, magic), s2[0][1], c2[0][1]), o1 = scl(and_or(vh, mask, magic), s2[1][1], c2[1][1]);
+      const uint32_t o2 = scl(and_or(vg >> 8, mask, magic), s2[0][1], c2[0][1]), o3 = scl(and_or(vh >> 8, mask, magic), s2[1][1], c2[1][1]);
 #pragma unroll
       for (int q = 0; q < NG; q++) {
-        acc[q][0] = fmaf(dd[0], dq[q][0], acc[q][0]), acc[q][1] = fmaf(dd[0], dq[q][1], acc[q][1]);
-        acc[q][2] = fmaf(dd[1], dq[q][2], acc[q][2]), acc[q][3] = fmaf(dd[1], dq[q][3], acc[q][3]);
-        const uint32_t sx = xb + (q * 8 + g) * TOK_PITCH + 512 + 4 * t;
-        const uint32_t sx_hi = lds32(sx), sx_lo = lds32(sx + 16);
-        mma16816(acc[q], dmh[0], dmh[1], dml[0], dml[1], sx_hi, sx_hi);
-        mma16816(acc[q], dmh[0], dmh[1], 0u, 0u, sx_lo, 0u);
+        const uint2 be = lds64(bx + q * (8 * TOK_PITCH) + i * 32), bo = lds64(bx + q * (8 * TOK_PITCH) + (8 + i) * 32);
+        mma16816(dq[q], e0, e1, e2, e3, be.x, be.y);
+        mma16816(dq[q], o0, o1, o2, o3, bo.x, bo.y);
       }
     }
-    __syncthreads();  // every warp is done with this block's half of the x buffer
-    if (threadIdx.x == 0 && bi + XFeed<NG>::XS < nloc) xf.fetch(bi + XFeed<NG>::XS, blk(bi + XFeed<NG>::XS));
+#pragma unroll
+    for (int q = 0; q < NG; q++) {
+      acc[q][0] = fmaf(dd[0], dq[q][0], acc[q][0]), acc[q][1] = fmaf(dd[0], dq[q][1], acc[q][1]);
+      acc[q][2] = fmaf(dd[1], dq[q][2], acc[q][2]), acc[q][3] = fmaf(dd[1], dq[q][3], acc[q][3]);
+      const uint32_t sx = xb + (q * 8 + g) * TOK_PITCH + 512 + 4 * t;
+      const uint32_t sx_hi = lds32(sx), sx_lo = lds32(sx + 16);
+      mma16816(acc[q], dmh[0], dmh[1], dml[0], dml[1], sx_hi, sx_hi);
+      mma16816(acc[q], dmh[0], dmh[1], 0u, 0u, sx_lo, 0u);
+    }
   }
-  cp_async_wait<0>();
-  __syncthreads();  // every warp is done with its ring slots
-  if (live) park_acc<NG>(acc, sbase, warp, g, t);
-  reduce_out<8 * NG>(ma, sbase, KS, rank, tiles, M);
-}
+};
 
 // ------------------------------------------------------------------------------------ Q6_K
 // Block (210 B): [ql[128] | qh[64] | int8 sc[16] | f16 d]; element e = 128h + 32q + l has its low nibble in
@@ -318,11 +350,6 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) q4k_nt_kernel(const 
 // sub-block m = 8h + 2q + u.  A row's block is copied as the 14 granules that cover it, to a 240-byte pitch; it
 // begins `skew` = (its byte offset & 15) bytes into the row's slot: a multiple of 4 for even blocks and 2 mod 4
 // for odd ones (rows hold an even number of blocks), where a word is two aligned words funnel-shifted.
-constexpr int Q6_PITCH = 240, Q6_TILE = ROWS * Q6_PITCH, Q6_STAGES = 2, Q6_RING = CW * Q6_STAGES * Q6_TILE;
-
-template <int NG>
-constexpr int q6_smem() { return Q6_RING + XFeed<NG>::BYTES; }
-
 __device__ __forceinline__ uint32_t lds16u(uint32_t addr) {
   uint16_t v;
   asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
@@ -334,74 +361,35 @@ __device__ __forceinline__ uint32_t lds32s(uint32_t addr) {  // word at a 2-byte
   return __funnelshift_r(lds32(addr - 2), lds32(addr + 2), 16);
 }
 
-template <int NG>
-__global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) q6k_nt_kernel(const uint8_t *__restrict__ xs, const __grid_constant__ NtArgs ma,
-                                                                        int tiles, int M, int K) {
-  constexpr int S = Q6_STAGES;
-  static_assert(8 * NG * 128 * 4 <= Q6_RING, "the partial sums reuse the ring");
-  extern __shared__ __align__(128) unsigned char dyn[];
-  pdl_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const int nb = K >> 8;
-  const int KS = gridDim.y, rank = blockIdx.y;
-  const int b0 = nb * rank / KS, b1 = nb * (rank + 1) / KS, nloc = b1 - b0;
-  const int rot = (int)(blockIdx.x * 5u) % nloc;
-  auto blk = [&](int i) { const int j = i + rot; return b0 + (j >= nloc ? j - nloc : j); };
-  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dyn);
-  XFeed<NG> xf;
-  xf.init(sbase + Q6_RING, dyn + Q6_RING, xs);
-
-  const int tile = blockIdx.x * CW + warp;
-  const bool live = tile < tiles;
-  int wj = 0, r0 = 0;
-  if (live) resolve(ma, tile, wj, r0);
-  const uint8_t *w = ma.w[wj];
-  const uint32_t row_bytes = (uint32_t)nb * 210u;  // a multiple of 4: nb is even (checked by the launcher)
-  const uint8_t *w_end = w + (size_t)ma.n[wj] * row_bytes;
-  const uint32_t ring = sbase + warp * (S * Q6_TILE);
-  const uint32_t m0f = 0x0F0F0F0Fu;
-  const uint32_t c_rsub = lane >> 4, c_piece = lane & 15;
-  int i_b = 0, i_slot = 0;
-  auto issue = [&]() {
-    if (live && i_b < nloc) {
-      uint32_t ro = (uint32_t)r0 * row_bytes + (uint32_t)blk(i_b) * 210u + c_rsub * row_bytes;
-      uint32_t dst = ring + i_slot * Q6_TILE + c_rsub * Q6_PITCH + c_piece * 16;
-      if (c_piece < 14) {
+struct Q6Fmt {
+  static constexpr int S = 2, PITCH = 240, TILE = ROWS * PITCH, BLOCK = 210;
+  uint32_t row_bytes, c_rsub, c_piece;
+  __device__ __forceinline__ void setup(int lane, uint32_t row_bytes_) { row_bytes = row_bytes_, c_rsub = lane >> 4, c_piece = lane & 15; }
+  // tile0 = first byte of the tile's first row; the copy never reads past w_end (the last rows of a matrix)
+  __device__ __forceinline__ void issue(uint32_t dst, const uint8_t *tile0, uint32_t blk, int, const uint8_t *w_end) const {
+    if (c_piece >= 14) return;
+    const uint8_t *row = tile0 + (size_t)c_rsub * row_bytes + blk * 210u;
+    dst += c_rsub * PITCH + c_piece * 16;
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-          const uint8_t *src = w + ((ro & ~15u) + c_piece * 16);
-          const long long left = w_end - src;  // the last rows of the matrix: never read past its end
-          if (left >= 16)
-            cp_async16(dst, src);
-          else if (left > 0)
-            cp_async16_part(dst, src, (uint32_t)left);
-          ro += 2 * row_bytes, dst += 2 * Q6_PITCH;
-        }
-      }
-      i_slot = i_slot + 1 == S ? 0 : i_slot + 1;
-      i_b++;
+    for (int i = 0; i < 8; i++) {
+      const uint8_t *src = reinterpret_cast<const uint8_t *>(reinterpret_cast<uintptr_t>(row) & ~(uintptr_t)15) + c_piece * 16;
+      const long long left = w_end - src;
+      if (left >= 16)
+        cp_async16(dst, src);
+      else if (left > 0)
+        cp_async16_part(dst, src, (uint32_t)left);
+      row += 2 * (size_t)row_bytes, dst += 2 * PITCH;
     }
-    cp_async_commit();
-  };
-#pragma unroll 1
-  for (int p = 0; p < S; p++) issue();
-  __syncthreads();
-  pdl_wait();
-  if (threadIdx.x == 0)
-    for (int i = 0; i < XFeed<NG>::XS && i < nloc; i++) xf.fetch(i, blk(i));
-
-  float acc[NG][4];
-#pragma unroll
-  for (int q = 0; q < NG; q++) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
-
-  // one unit: rows g, g+8 of this warp's tile x one K block out of ring slot `sb`, all token groups of buffer `xb`
-  auto unit = [&](auto odd_tag, uint32_t sb, uint32_t skew, uint32_t xb) {
-    constexpr bool ODD = decltype(odd_tag)::value;
+  }
+  template <int NG, bool ODD, typename F>
+  __device__ __forceinline__ void unit_p(uint32_t sb, uint32_t xb, float (&acc)[NG][4], uint32_t skew, int lane, F &&slot_free) const {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t m0f = 0x0F0F0F0Fu;
     uint32_t wa[2][4], wc[2][4], wh[2][4], scw[2][4];
     float dd[2];
 #pragma unroll
     for (int r = 0; r < 2; r++) {
-      const uint32_t bk = sb + (g + 8 * r) * Q6_PITCH + skew;  // the block's first byte
+      const uint32_t bk = sb + (g + 8 * r) * PITCH + skew;  // the block's first byte
 #pragma unroll
       for (int hu = 0; hu < 4; hu++) {
         const int h = hu >> 1, u = hu & 1;
@@ -414,7 +402,7 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) q6k_nt_kernel(const 
       dd[r] = f16_bits_to_f32((uint16_t)lds16u(bk + 208));
     }
     __syncwarp();  // the slot is free again
-    issue();
+    slot_free();
     float dq[NG][4];
 #pragma unroll
     for (int q = 0; q < NG; q++) dq[q][0] = dq[q][1] = dq[q][2] = dq[q][3] = 0.f;
@@ -451,81 +439,169 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) q6k_nt_kernel(const 
       acc[qg][0] = fmaf(dd[0], dq[qg][0], acc[qg][0]), acc[qg][1] = fmaf(dd[0], dq[qg][1], acc[qg][1]);
       acc[qg][2] = fmaf(dd[1], dq[qg][2], acc[qg][2]), acc[qg][3] = fmaf(dd[1], dq[qg][3], acc[qg][3]);
     }
+  }
+  // tile_off = byte offset of the tile's first row from the matrix start (its low four bits matter)
+  template <int NG, typename F>
+  __device__ __forceinline__ void unit(uint32_t sb, uint32_t xb, float (&acc)[NG][4], uint32_t tile_off, uint32_t blk, int lane, F &&slot_free) const {
+    const uint32_t skew = (tile_off + blk * 210u + (uint32_t)(lane >> 2) * row_bytes) & 15u;
+    if (blk & 1)
+      unit_p<NG, true>(sb, xb, acc, skew, lane, slot_free);
+    else
+      unit_p<NG, false>(sb, xb, acc, skew, lane, slot_free);
+  }
+};
+
+template <typename Fmt, int NG>
+constexpr int nt_smem() { return CW * Fmt::S * Fmt::TILE + XFeed<NG>::BYTES; }
+
+template <typename Fmt, int NG>
+__global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint8_t *__restrict__ xs, float *__restrict__ parts,
+                                                                    const __grid_constant__ NtArgs ma, int tiles, int M, int K, int run_len) {
+  constexpr int S = Fmt::S;
+  extern __shared__ __align__(128) unsigned char dyn[];  // [weight rings: 8 warps x S tiles][x ring][mbarriers][flag]
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int nb = K >> 8;
+  const int groups = (tiles + CW - 1) / CW;
+  const Run run{groups * nb, (int)gridDim.x, run_len, (int)blockIdx.x, nb};
+  const int it0 = run.begin(run.c), it1 = run.begin(run.c + 1), n = it1 - it0;
+  const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dyn);
+  const uint32_t ring = sbase + warp * (S * Fmt::TILE);
+  XFeed<NG> xf;
+  xf.init(sbase + CW * S * Fmt::TILE, dyn + CW * S * Fmt::TILE, xs, it0, n, nb);
+  const uint32_t row_bytes = (uint32_t)nb * Fmt::BLOCK;
+  Fmt fmt;
+  fmt.setup(lane, row_bytes);
+
+  // where a list index lies: which tile this warp has there
+  struct At {
+    bool live;
+    int wj, r0;
+    const uint8_t *tile0, *w_end;
+  };
+  auto at_group = [&](int grp) {
+    At a;
+    const int tile = grp * CW + warp;
+    a.live = tile < tiles, a.wj = 0, a.r0 = 0;
+    if (a.live) resolve(ma, tile, a.wj, a.r0);
+    a.tile0 = ma.w[a.wj] + (size_t)a.r0 * row_bytes;
+    a.w_end = ma.w[a.wj] + (size_t)ma.n[a.wj] * row_bytes;
+    return a;
   };
 
-  int slot = 0;
-  for (int bi = 0; bi < nloc; bi++) {
-    const uint32_t xb = xf.buf(bi);
-    if (!xf.wait(bi)) break;
-    if (live) {
+  // ---- the weight ring runs ahead of the arithmetic, across group boundaries
+  int i_k = 0, i_blk = it0 % nb, i_grp = it0 / nb, i_slot = 0;
+  At i_at = at_group(i_grp);
+  auto issue = [&]() {  // always closes a commit group, so that group counts stay uniform
+    if (i_k < n) {
+      if (i_at.live) {
+        fmt.issue(ring + i_slot * Fmt::TILE, i_at.tile0, (uint32_t)i_blk, lane, i_at.w_end);
+        i_slot = i_slot + 1 == S ? 0 : i_slot + 1;
+      }
+      i_k++;
+      if (++i_blk == nb) {
+        i_blk = 0, i_grp++;
+        if (i_k < n) i_at = at_group(i_grp);
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll 1
+  for (int p = 0; p < S; p++) issue();
+  __syncthreads();  // the mbarriers are initialised
+  pdl_wait();       // the staged activations are the pre-pass's output; the weights requested above are not
+  const unsigned int epoch = *reinterpret_cast<volatile unsigned int *>(&g_nt_epoch);
+  if (threadIdx.x == 0) xf.start();
+
+  float acc[NG][4];
+  int slot = 0, blk = it0 % nb, grp = it0 / nb, seg_b0 = blk;
+  At at = at_group(grp);
+  int fix_grp = -1;  // the group whose end this CTA holds after starting inside it
+  At fix_at = at;
+#pragma unroll
+  for (int q = 0; q < NG; q++) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
+  bool dead = false;
+  for (int k = 0; k < n; k++) {
+    if (threadIdx.x == 0) xf.pump(k);
+    __syncwarp();
+    if (!xf.wait_full(k)) { dead = true; break; }
+    if (at.live) {
       cp_async_wait<S - 1>();
       __syncwarp();
-      const uint32_t sb = ring + slot * Q6_TILE;
+      const uint32_t sb = ring + slot * Fmt::TILE;
       slot = slot + 1 == S ? 0 : slot + 1;
-      const int b = blk(bi);
-      const uint32_t skew = ((uint32_t)r0 * row_bytes + (uint32_t)b * 210u + (uint32_t)g * row_bytes) & 15u;
-      if (b & 1)
-        unit(std::true_type{}, sb, skew, xb);
-      else
-        unit(std::false_type{}, sb, skew, xb);
+      fmt.template unit<NG>(sb, xf.buf(k), acc, (uint32_t)((size_t)at.r0 * row_bytes), (uint32_t)blk, lane, issue);
+    } else {
+      issue();  // keeps the commit-group count in step with the live warps' (and requests the next group's tiles)
     }
-    __syncthreads();
-    if (threadIdx.x == 0 && bi + XFeed<NG>::XS < nloc) xf.fetch(bi + XFeed<NG>::XS, blk(bi + XFeed<NG>::XS));
+    xf.release(k, lane);
+    if (blk == nb - 1 || k == n - 1) {  // the run leaves this group
+      if (at.live) {
+        if (seg_b0 == 0 && blk == nb - 1) {
+          store_tile<NG>(acc, ma.out[at.wj], ma.n[at.wj], at.r0, M, g, t);
+        } else {
+          const bool first = k - (blk - seg_b0) == 0;  // this CTA's first run (slot 0) or its last (slot 1)
+          write_part<NG>(acc, parts, run.c, first ? 0 : 1, warp, lane, epoch);
+          if (blk == nb - 1) fix_grp = grp, fix_at = at;
+        }
+      }
+      if (k + 1 < n) {
+        grp++, blk = 0, seg_b0 = 0;
+        at = at_group(grp);
+#pragma unroll
+        for (int q = 0; q < NG; q++) acc[q][0] = acc[q][1] = acc[q][2] = acc[q][3] = 0.f;
+      }
+    } else {
+      blk++;
+    }
   }
   cp_async_wait<0>();
-  __syncthreads();
-  if (live) park_acc<NG>(acc, sbase, warp, g, t);
-  reduce_out<8 * NG>(ma, sbase, KS, rank, tiles, M);
+  if (!dead && fix_grp >= 0 && fix_at.live) {
+    fix_up<NG>(run, fix_grp, parts, warp, lane, epoch, acc);
+    store_tile<NG>(acc, ma.out[fix_at.wj], ma.n[fix_at.wj], fix_at.r0, M, g, t);
+  }
 }
 
 // ------------------------------------------------------------------------------------ launch
-template <int NG, bool Q6>
-int launch_nt(const uint8_t *xs, const NtArgs &ma, int tiles, int M, int K, cudaStream_t st) {
-  auto kern = Q6 ? q6k_nt_kernel<NG> : q4k_nt_kernel<NG>;
-  const int smem = Q6 ? q6_smem<NG>() : q4_smem<NG>();
+template <typename Fmt, int NG>
+int launch_nt(const uint8_t *xs, float *parts, const NtArgs &ma, int tiles, int M, int K, int grid, int run_len, cudaStream_t st) {
+  auto kern = nt_kernel<Fmt, NG>;
+  const int smem = nt_smem<Fmt, NG>();
   static DeviceOnce attr_done;
   {
     cudaError_t e = attr_done.ensure([&] { return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); });
     if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, token tiles): %s", cudaGetErrorString(e));
   }
-  const int nx = (tiles + CW - 1) / CW, nb = K >> 8, sms = sm_count();
-  const int per_sm = NG <= 4 ? 2 : 1;
-  // short K runs win (a CTA's start-up and its first block of x are not overlapped with anything) until the SMs'
-  // CTA slots are taken and more CTAs wait behind them
-  // first until every SM has a CTA, then, while a K run keeps at least four blocks, until the CTA slots are taken
-  int ks = 1;
-  while (ks < 8 && ks * 2 <= nb && (nx * ks * 2 <= sms || (nx * ks * 2 <= sms * per_sm && nb / (ks * 2) >= 4))) ks *= 2;
-  static int env_ks = -1;
-  if (env_ks < 0) env_ks = getenv("LIGHT_B200_NT_KS") ? atoi(getenv("LIGHT_B200_NT_KS")) : 0;
-  if (env_ks >= 1 && env_ks <= 8 && (env_ks & (env_ks - 1)) == 0 && env_ks <= nb) ks = env_ks;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3((unsigned)nx, (unsigned)ks, 1);
+  cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[2];
+  cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  attr[1].id = cudaLaunchAttributeClusterDimension;
-  attr[1].val.clusterDim.x = 1, attr[1].val.clusterDim.y = (unsigned)ks, attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 2;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, xs, ma, tiles, M, K);
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kern, xs, parts, ma, tiles, M, K, run_len);
   if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, token tiles): %s", cudaGetErrorString(e));
   return launched("matmul_q (decode, token tiles)");
 }
 
-template <bool Q6>
-int launch_by_ng(int ng, const uint8_t *xs, const NtArgs &ma, int tiles, int M, int K, cudaStream_t st) {
+template <typename Fmt>
+int launch_by_ng(int ng, const uint8_t *xs, float *parts, const NtArgs &ma, int tiles, int M, int K, int grid, int run_len, cudaStream_t st) {
   switch (ng) {
-    case 1: return launch_nt<1, Q6>(xs, ma, tiles, M, K, st);
-    case 2: return launch_nt<2, Q6>(xs, ma, tiles, M, K, st);
-    case 4: return launch_nt<4, Q6>(xs, ma, tiles, M, K, st);
-    default: return launch_nt<8, Q6>(xs, ma, tiles, M, K, st);
+    case 1: return launch_nt<Fmt, 1>(xs, parts, ma, tiles, M, K, grid, run_len, st);
+    case 2: return launch_nt<Fmt, 2>(xs, parts, ma, tiles, M, K, grid, run_len, st);
+    case 4: return launch_nt<Fmt, 4>(xs, parts, ma, tiles, M, K, grid, run_len, st);
+    default: return launch_nt<Fmt, 8>(xs, parts, ma, tiles, M, K, grid, run_len, st);
   }
 }
 
 int g_nt_min_m = 9, g_nt_max_m = 64;  // LIGHT_B200_NT_MIN_M / _MAX_M (tuning knobs)
+
+int ng_of(int M) { return M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8; }
+size_t stage_bytes(int M, int K) { return ((size_t)(K >> 8) * 8 * ng_of(M) * TOK_PITCH + 1023) & ~(size_t)1023; }
+size_t parts_bytes(int M) { return (size_t)MAX_GRID * 2 * CW * ng_of(M) * 4 * 32 * sizeof(float); }
 
 }  // namespace
 
@@ -536,24 +612,24 @@ int decode_nt_status() {
   return v;
 }
 
-// `count` (1..4) matrices of one type (Q4_K or Q6_K) that share x (M rows, 9 .. 64 by default).  `ws` is staging
-// memory of at least decode_nt_ws_bytes(M, K) bytes that stays untouched until the launches have run.
-// Returns 1 if launched, 0 if the shape is not covered, else an error.
-size_t decode_nt_ws_bytes(int M, int K) {
-  const int ng = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8;
-  return (size_t)(K >> 8) * 8 * ng * TOK_PITCH;
-}
+// Workspace the path needs for M rows of K: the staged activations and the split-K partial sums.
+size_t decode_nt_ws_bytes(int M, int K) { return stage_bytes(M, K) + parts_bytes(M); }
 
+// `count` (1..4) matrices of one type (Q4_K or Q6_K) that share x (M rows, 9 .. 64 by default).  `ws` is memory of
+// at least decode_nt_ws_bytes(M, K) bytes that stays untouched until the launches have run.
+// Returns 1 if launched, 0 if the shape is not covered, else an error.
 int gguf_decode_nt(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K, void *ws,
                    size_t ws_bytes, cudaStream_t st) {
   static bool knob = false;
+  static int env_grid = 0;
   if (!knob) {
     if (const char *e = getenv("LIGHT_B200_NT_MIN_M")) g_nt_min_m = atoi(e);
     if (const char *e = getenv("LIGHT_B200_NT_MAX_M")) g_nt_max_m = atoi(e);
+    if (const char *e = getenv("LIGHT_B200_NT_GRID")) env_grid = atoi(e);
     knob = true;
   }
   if ((type != LB200_Q4_K && type != LB200_Q6_K) || M < g_nt_min_m || M > g_nt_max_m || M > 64 || M < 1 || K % 256 || count < 1 || count > 4 ||
-      ((uintptr_t)x & 15) || !ws || ((uintptr_t)ws & 15) || ws_bytes < decode_nt_ws_bytes(M, K))
+      ((uintptr_t)x & 15) || !ws || ((uintptr_t)ws & 127) || ws_bytes < decode_nt_ws_bytes(M, K))
     return 0;
   const bool q6 = type == LB200_Q6_K;
   if (q6 && ((K >> 8) & 1)) return 0;
@@ -561,14 +637,33 @@ int gguf_decode_nt(int type, const float *x, const void *const *w, float *const 
   int tiles = 0;
   for (int i = 0; i < count; i++) {
     if (n[i] < ROWS) return 0;
-    if (q6 ? (((uintptr_t)w[i] & 3) || (unsigned long long)n[i] * (K >> 8) * 210ull >= (1ull << 32)) : ((uintptr_t)w[i] & 15)) return 0;
+    if ((uintptr_t)w[i] & 15) return 0;
     tiles += (n[i] + ROWS - 1) / ROWS;
     a.w[i] = (const uint8_t *)w[i], a.out[i] = out[i], a.n[i] = n[i], a.tend[i] = tiles;
   }
   a.count = count;
-  const int ng = M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8, NT = 8 * ng;
+  const int ng = ng_of(M), NT = 8 * ng, nb = K >> 8;
+  // the persistent grid: every CTA slot of the GPU, but at least about four blocks per CTA unless SMs would idle
+  const int sms = sm_count(), slots = sms * (ng <= 4 ? 2 : 1);
+  const long long T = (long long)((tiles + CW - 1) / CW) * nb;
+  if (T >= (1ll << 30)) return 0;
+  // a short list (a 4096 x 4096 matrix is 512 entries) leaves each CTA a few blocks and most of the time goes into
+  // starting and the split-K fix-up: up to 32 rows the cluster kernel for Q4_K is quicker there
+  if (!q6 && M <= 32 && T < 4ll * sms && !env_grid) return 0;
+  long long limit = T / 4 > sms ? T / 4 : (T < sms ? T : sms);
+  if (limit > slots) limit = slots;
+  if (env_grid > 0) limit = env_grid < T ? env_grid : T;
+  if (limit > MAX_GRID) limit = MAX_GRID;
+  // Runs as even as possible over `limit` CTAs; but where one CTA per SM is all there is, runs of one fixed length that
+  // divides a row's blocks take the same time and never straddle a group (fewer partial sums).
+  int run_len = 0;
+  long long grid = limit;
   {
-    const int recs = (K >> 8) * NT;
+    const int q = (int)((T + limit - 1) / limit);
+    if (limit <= sms && q <= nb && nb % q == 0) run_len = q, grid = (T + q - 1) / q;
+  }
+  {
+    const int recs = nb * NT;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)((recs + CW - 1) / CW));
     cfg.blockDim = dim3(THREADS);
@@ -583,7 +678,9 @@ int gguf_decode_nt(int type, const float *x, const void *const *w, float *const 
     if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, staging): %s", cudaGetErrorString(e));
     if (int rc = launched("matmul_q (decode, staging)")) return rc;
   }
-  const int rc = q6 ? launch_by_ng<true>(ng, (const uint8_t *)ws, a, tiles, M, K, st) : launch_by_ng<false>(ng, (const uint8_t *)ws, a, tiles, M, K, st);
+  float *parts = reinterpret_cast<float *>((uint8_t *)ws + stage_bytes(M, K));
+  const int rc = q6 ? launch_by_ng<Q6Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, (int)grid, run_len, st)
+                    : launch_by_ng<Q4Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, (int)grid, run_len, st);
   return rc ? rc : 1;
 }
 

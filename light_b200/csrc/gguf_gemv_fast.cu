@@ -534,9 +534,10 @@ __global__ void __launch_bounds__(WARPS * 32, 2) q4k_gemv_tok_kernel(const float
 #pragma unroll
           for (int j = 0; j < 2; j++) {
             const float a0 = s[j], a1 = j ? n1 : n0;
-            const __half2 hi = __floats2half2_rn(a0, a1);
+            const __half2 slim = __float2half2_rn(65504.f);  // sums of clamped values can leave the f16 range too
+            const __half2 hi = __hmax2(__hmin2(__floats2half2_rn(a0, a1), slim), __hneg2(slim));
             const float2 hf = __half22float2(hi);
-            const __half2 lo = __floats2half2_rn(a0 - hf.x, a1 - hf.y);
+            const __half2 lo = __hmax2(__hmin2(__floats2half2_rn(a0 - hf.x, a1 - hf.y), slim), __hneg2(slim));
             const uint32_t at = slab + TOK_SX + tk * 32 + 4 * ((lane >> 4) + 2 * j);
             asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at), "r"(h2_as_u32(hi)));
             asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(at + 16), "r"(h2_as_u32(lo)));
@@ -693,9 +694,9 @@ __global__ void __launch_bounds__(DT_THREADS, 2) q4k_decode_tile_kernel(const fl
       s += __shfl_xor_sync(0xffffffffu, s, 1), s += __shfl_xor_sync(0xffffffffu, s, 2), s += __shfl_xor_sync(0xffffffffu, s, 4);
       const float s1 = __shfl_down_sync(0xffffffffu, s, 8);
       if ((lane & 15) == 0) {  // sub-blocks (F / 8, F / 8 + 1) = pair F / 16
-        const __half2 hi = __floats2half2_rn(s, s1);
+        const __half2 hi = __hmax2(__hmin2(__floats2half2_rn(s, s1), lim), __hneg2(lim));  // sums of clamped values can leave the f16 range too
         const float2 hf = __half22float2(hi);
-        const __half2 lo = __floats2half2_rn(s - hf.x, s1 - hf.y);
+        const __half2 lo = __hmax2(__hmin2(__floats2half2_rn(s - hf.x, s1 - hf.y), lim), __hneg2(lim));
         asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(xb + Cfg::SX + tk * 32 + 4 * (xF >> 4)), "r"(h2_as_u32(hi)));
         asm volatile("st.shared.u32 [%0], %1;\n" ::"r"(xb + Cfg::SX + tk * 32 + 16 + 4 * (xF >> 4)), "r"(h2_as_u32(lo)));
       }

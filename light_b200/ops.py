@@ -138,8 +138,8 @@ def MatMulQ(x: torch.Tensor, w: QTensor) -> torch.Tensor:
         raise ValueError(f"MatMulQ: inner dim mismatch (x K={K}, w K={w.shape[1]})")
     dev = _dev(x, "MatMulQ")
     xc = x.contiguous()
-    if M > 1:  # the batched paths stream an f16 copy of x (tokens padded to eight, 544 bytes per 256 values) from the workspace
-        ensure_workspace(dev, (M + 7) // 8 * 8 * K * 3)
+    if M > 1:  # the batched paths keep an f16 copy of x (and split-K partial sums) in the workspace
+        ensure_workspace(dev, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, K)))
     out = torch.empty((M, N), dtype=torch.float32, device=x.device)
     _lib.check(_lib.lib().light_b200_matmul_q(w.ggml_type, _ptr(xc), _ptr(w.data), _ptr(out), M, N, K, dev,
                                               _stream(dev)))
@@ -179,7 +179,7 @@ def MatMulQMulti(x: torch.Tensor, ws: Sequence[QTensor], outs: Optional[Sequence
     op = (C.c_void_p * n)(*[o.data_ptr() for o in outs])
     nn = (C.c_int32 * n)(*[w.shape[0] for w in ws])
     if M > 1:
-        ensure_workspace(dev, (M + 7) // 8 * 8 * K * 3)
+        ensure_workspace(dev, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, K)))
     _lib.check(_lib.lib().light_b200_matmul_q_multi_rows(ws[0].ggml_type, _ptr(xc), wp, op, nn, n, M, K, dev, _stream(dev)))
     return list(outs)
 
