@@ -10,7 +10,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblight_b200.so")
 SOURCES = ["abi.cu", "gguf_dequant.cu", "gguf_matmul_generic.cu", "gguf_gemv_fast.cu", "gguf_gemv_batch.cu", "prefill_umma.cu", "decode_umma.cu", "int4.cu", "fp8_block.cu",
-           "moe.cu", "peer_gather.cu", "decode_attn.cu", "norm_rope.cu", "w8a8.cu", "moe_route.cu", "decode_chain.cu", "gemv_bf16.cu", "moe_elementwise.cu", "gguf_decode_nt.cu"]
+           "moe.cu", "peer_gather.cu", "decode_attn.cu", "norm_rope.cu", "w8a8.cu", "moe_route.cu", "decode_chain.cu", "gemv_bf16.cu", "moe_elementwise.cu", "gguf_decode_nt.cu", "gguf_decode_ts.cu"]
 NVCC_FLAGS = os.environ.get("LIGHT_B200_NVCC_EXTRA", "").split() + ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC",
               "-Xcompiler", "-fvisibility=hidden", "-Xptxas", "-v"]
 

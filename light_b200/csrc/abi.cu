@@ -148,13 +148,14 @@ int light_b200_matmul_q_tp(int t, const float *x, const void *const *w, float *c
 
 int light_b200_prefill_status(int device) {
   if (int rc = bind(device)) return rc;
-  const int a = prefill_status(device), b = decode_umma_status(), c = decode_nt_status();
-  return a ? a : b ? b : c;
+  const int a = prefill_status(device), b = decode_umma_status(), c = decode_nt_status(), d = decode_ts_status();
+  return a ? a : b ? b : c ? c : d;
 }
 unsigned long long light_b200_matmul_q_workspace_bytes(int M, int K) {
   if (M <= 1 || K <= 0) return 0;
   const unsigned long long f16_copy = (unsigned long long)M * K * 2;  // the tensor-core paths' f16 copy of x
-  const unsigned long long staged = M <= 64 ? decode_nt_ws_bytes(M, K) : 0;
+  unsigned long long staged = M <= 64 ? decode_nt_ws_bytes(M, K) : 0;
+  if (M <= 64 && decode_ts_ws_bytes(M, K) > staged) staged = decode_ts_ws_bytes(M, K);
   return f16_copy > staged ? f16_copy : staged;
 }
 unsigned long long light_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
@@ -174,7 +175,17 @@ int light_b200_matmul_q(int t, const float *x, const void *w, float *out, int M,
     return fail(LB200_E_ALIGN, "light_b200: matmul_q: x must be 16-byte, out 4-byte, w 2-byte aligned");
   if (int rc = bind(device)) return rc;
   cudaStream_t st = (cudaStream_t)stream;
-  int took = gguf_gemv_fast(t, x, w, out, M, N, K, st);
+  int took = 0;
+  if (M <= 64) {  // weights expanded into tensor memory (needs the workspace)
+    size_t wsb = 0;
+    void *ws = workspace_ptr(device, &wsb);
+    const void *wv[1] = {w};
+    float *ov[1] = {out};
+    const int nv[1] = {N};
+    took = gguf_decode_ts(t, x, wv, ov, nv, 1, M, K, ws, wsb, st);
+    if (took != 0) return took == 1 ? 0 : took;
+  }
+  took = gguf_gemv_fast(t, x, w, out, M, N, K, st);
   if (took < 0) return took;
   if (took) return 0;
   if (M >= 2 && M <= 64) {  // tokens as MMA columns over activations staged once (needs the workspace)
@@ -247,6 +258,8 @@ int light_b200_matmul_q_multi_rows(int t, const float *x, const void *const *w, 
   if (M <= 64) {
     size_t wsb = 0;
     void *ws = workspace_ptr(device, &wsb);
+    took = gguf_decode_ts(t, x, w, out, n, count, M, K, ws, wsb, (cudaStream_t)stream);
+    if (took != 0) return took == 1 ? 0 : took;
     took = gguf_decode_nt(t, x, w, out, n, count, M, K, ws, wsb, (cudaStream_t)stream);
     if (took != 0) return took == 1 ? 0 : took;
   }

@@ -136,6 +136,10 @@ size_t decode_nt_ws_bytes(int M, int K);
 int gguf_decode_nt(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K, void *ws,
                    size_t ws_bytes, cudaStream_t st);
 int decode_nt_status();
+size_t decode_ts_ws_bytes(int M, int K);
+int gguf_decode_ts(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K, void *ws,
+                   size_t ws_bytes, cudaStream_t st);
+int decode_ts_status();
 int gather_columns(const void *x, const int64_t *idx, void *out, int elt, long long M, int K, cudaStream_t st);
 int moe_gate_mul(const void *h, void *out, int dtype, long long M, int I, int gelu, cudaStream_t st);
 int moe_combine(const void *pair_out, void *out, int dtype, long long tokens, int N, int topk, cudaStream_t st);

@@ -98,9 +98,12 @@ print("CASE OK")
 """ % (ROOT, "%s")
 
 
-@pytest.mark.parametrize("env,ms", [({"LIGHT_B200_NT_MIN_M": "2"}, "(2, 3, 8)"), ({"LIGHT_B200_NT_MAX_M": "0"}, "(9, 32, 64)")])
+@pytest.mark.parametrize("env,ms", [({"LIGHT_B200_NT_MIN_M": "2"}, "(2, 3, 8)"), ({"LIGHT_B200_NT_MAX_M": "0"}, "(9, 32, 64)"),
+                                    ({"LIGHT_B200_TS": "1"}, "(1, 5, 16, 17, 32, 33, 64)"), ({"LIGHT_B200_TS": "1", "LIGHT_B200_TS_GRID": "7"}, "(1, 32, 64)")])
 def test_token_tiles_row_count_knobs(cuda, env, ms):
     """The same kernels serve 2 to 8 rows when asked to (one group of eight); with the path switched off the
-    earlier kernels still serve 9 to 64 rows."""
+    earlier kernels still serve 9 to 64 rows; and the kernel that hands the expanded weights to tcgen05.mma through
+    tensor memory (opt-in) serves 1 to 64 rows of Q4_K, also when a grid of 7 CTAs cuts every group's K range into
+    partial sums."""
     r = subprocess.run([sys.executable, "-c", textwrap.dedent(CHILD % ms)], capture_output=True, text=True, timeout=600, env={**os.environ, **env})
     assert r.returncode == 0 and "CASE OK" in r.stdout, r.stdout + r.stderr[-3000:]
