@@ -38,8 +38,9 @@ HID, FFN, NKV, VOCAB, LAYERS = 4096, 14336, 1024, 128256, 32
 LAYER = [("q", HID, HID, ops.Q4_K), ("k", NKV, HID, ops.Q4_K), ("v", NKV, HID, ops.Q4_K), ("o", HID, HID, ops.Q4_K),
          ("gate", FFN, HID, ops.Q4_K), ("up", FFN, HID, ops.Q4_K), ("down", HID, FFN, ops.Q6_K)]
 HEAD = ("lm_head", VOCAB, HID, ops.Q6_K)
-# DRAM traffic of the Q4_K decode kernel per algorithmic byte, from the ncu capture summarised in
-# profiles/q4k_gemv_mma_kernel__llama8b_decode_small_case.md (every weight byte is fetched once)
+# DRAM traffic of the Q4_K decode kernel per algorithmic byte: dram__bytes_read + dram__bytes_write over the
+# algorithmic bytes of the three launches of one ncu capture of this kernel on one layer's shapes (every weight
+# byte is fetched once).  A constant of the kernel as it stands: it has to be captured again when the kernel changes.
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 89.78 / 89.86
 
 
@@ -557,8 +558,142 @@ def extras(chain, device, args):
         tot_t = sum(v["ms"] for v in out["prefill_m2048"].values()) * 1e-3
         out["prefill_m2048"]["all_four"] = {"tflops": tot_f / tot_t / 1e12,
                                             "frac_of_measured_sustained_bf16": tot_f / tot_t / 1e12 / peaks["bf16_tflops_sustained"]}
+    out["int4_w4a16_qwen7b_shapes"] = int4_extras(device, peak, peaks)
+    out["moe_fp8_deepseek_v3_layer"] = moe_extras(device, peaks)
+    if chain.world == 1 and chain.M == 1:
+        out["decode_m1_dependent_chain_one_launch"] = chain_kernel_extras(chain, device, steps)
     out["tensor_core_status"] = ops.prefill_status(device.index or 0)
     return out
+
+
+def int4_extras(device, hbm_peak, peaks):
+    """configs[3]: GPTQ / AWQ-style 4-bit weights, group 128, at Qwen2.5-7B shapes, 16-bit activations, M = 1, 16, 256 and
+    4096: microseconds per call with the weights rotated through more than L2 holds, and the roofline that bounds
+    each (HBM for the decode sizes, the tensor pipe for 256 and 4096 rows)."""
+    res = {}
+    tf_peak = peaks.get("bf16_tflops")
+    for name, N, K in (("qkv_4608x3584", 4608, 3584), ("gate_up_37888x3584", 37888, 3584), ("down_3584x18944", 3584, 18944)):
+        codes, s, z = synth.random_int4(7300 + N % 97, N, K, 128)
+        base = [torch.from_numpy(a.view(np.int32) if a.dtype == np.uint32 else a).to(device) for a in (codes, s, z)]
+        nbytes = N * K // 2 + 2 * N * (K // 128) * 4
+        R = max(2, min(16, int(0.6e9 // nbytes) + 1))
+        ws = [ops.Int4(base[0].clone(), base[1], base[2], 128) for _ in range(R)]
+        res[name] = {}
+        for M in (1, 16, 256, 4096):
+            x = torch.randn(M, K, device=device).to(torch.bfloat16)
+            ops.MatMulInt4(x, ws[0])
+            g = capture(lambda: [ops.MatMulInt4(x, w) for w in ws], device)
+            ms = timed(g.replay, 5, 2, device, lambda: None) / 5 / R
+            del g
+            e = {"us": ms * 1e3}
+            if M <= 16:
+                e["gbs"] = nbytes / (ms * 1e-3) / 1e9
+                e["frac_of_measured_hbm"] = e["gbs"] / hbm_peak
+            else:
+                e["tflops"] = 2.0 * M * N * K / (ms * 1e-3) / 1e12
+                if tf_peak:
+                    e["frac_of_measured_bf16_burst"] = e["tflops"] / tf_peak
+            res[name][str(M)] = e
+        del ws, base
+        torch.cuda.empty_cache()
+    return res
+
+
+def moe_extras(device, peaks):
+    """configs[4] on one GPU: a DeepSeek-V3-shaped sparse block, 256 routed experts with block-scaled FP8 weights
+    (128 x 128 blocks), hidden 7168, expert width 2048, 4096 bf16 tokens routed top-8 by the sigmoid + bias router
+    (bias ~ N(0, 0.5): a skewed load).  Router, counting sort, grouped gate-up matmul, SiLU gate, grouped down matmul
+    with the routing weights, combine: every step a launch of this library.  Needs about 12 GB; skipped with less."""
+    E, H, I, T, topk, b = 256, 7168, 2048, 4096, 8, 128
+    free, _ = torch.cuda.mem_get_info(device)
+    if free < 16 * (1 << 30):
+        return {"skipped": "needs about 12 GB of free device memory"}
+    w1, s1 = synth.random_fp8_block(7401, E * 2 * I, H, b, b, device=device)
+    w2, s2 = synth.random_fp8_block(7402, E * H, I, b, b, device=device)
+    w1, s1 = w1.reshape(E, 2 * I, H), s1.reshape(E, 2 * I // b, H // b)
+    w2, s2 = w2.reshape(E, H, I), s2.reshape(E, H // b, I // b)
+    g = torch.Generator(device=device)
+    g.manual_seed(7403)
+    x = (torch.randn(T, H, generator=g, device=device) * 0.05).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=device)
+    bias = torch.randn(E, generator=g, device=device) * 0.5
+    state = {}
+
+    def layer():
+        r = ops.MoERouteSigmoid(logits, bias, topk, True)
+        h = ops.MoEGemmF8Block(x, w1, s1, b, b, r, None, topk)
+        y = ops.MoEGemmF8Block(ops.MoEGateMul(h), w2, s2, b, b, r, r.weights, topk)
+        state["out"], state["r"] = ops.MoECombine(y, topk), r
+
+    layer()
+    torch.cuda.synchronize(device)
+    r = state["r"]
+    cnt = torch.bincount(r.sorted_expts, minlength=E)
+    ms = timed(layer, 5, 2, device, lambda: None) / 5
+    M = T * topk
+    hh = ops.MoEGateMul(ops.MoEGemmF8Block(x, w1, s1, b, b, r, None, topk))
+    ms1 = timed(lambda: ops.MoEGemmF8Block(x, w1, s1, b, b, r, None, topk), 5, 2, device, lambda: None) / 5
+    ms2 = timed(lambda: ops.MoEGemmF8Block(hh, w2, s2, b, b, r, r.weights, topk), 5, 2, device, lambda: None) / 5
+    f1, f2 = 2.0 * M * 2 * I * H, 2.0 * M * H * I
+    res = {"tokens": T, "pairs_per_expert_min_mean_max": [int(cnt.min()), float(cnt.float().mean()), int(cnt.max())],
+           "layer_ms": ms, "tokens_per_s": T / (ms * 1e-3), "layer_tflops": (f1 + f2) / (ms * 1e-3) / 1e12,
+           "gate_up_matmul": {"ms": ms1, "tflops": f1 / (ms1 * 1e-3) / 1e12}, "down_matmul": {"ms": ms2, "tflops": f2 / (ms2 * 1e-3) / 1e12},
+           "finite": bool(torch.isfinite(state["out"].float()).all().item()), "route_status": ops.moe_route_status(device.index or 0)}
+    if "bf16_tflops" in peaks:  # the experts are expanded to bf16 for the tensor core: the bf16 peak bounds the matmuls
+        res["layer_frac_of_measured_bf16_burst"] = res["layer_tflops"] / peaks["bf16_tflops"]
+    # the same block for one decode step's tokens (few pairs per expert: the warp-per-column kernel)
+    xd = x[:8].contiguous()
+    rd = ops.MoERouteSigmoid(logits[:8].contiguous(), bias, topk, True)
+
+    def small():
+        h = ops.MoEGemmF8Block(xd, w1, s1, b, b, rd, None, topk)
+        return ops.MoECombine(ops.MoEGemmF8Block(ops.MoEGateMul(h), w2, s2, b, b, rd, rd.weights, topk), topk)
+
+    small()
+    msd = timed(small, 5, 2, device, lambda: None) / 5
+    touched = 8 * topk * (2 * I * H + H * I)  # bytes of expert weights 64 pairs read (distinct experts assumed)
+    res["decode_8_tokens"] = {"ms": msd, "expert_bytes": touched, "gbs": touched / (msd * 1e-3) / 1e9}
+    del w1, w2, s1, s2
+    torch.cuda.empty_cache()
+    return res
+
+
+def chain_kernel_extras(chain, device, steps):
+    """The M = 1 step as ONE persistent launch: the 129 operators as a device-side program, every operator reading the
+    vector the one before wrote (a dependent chain, unlike the headline's launches, which all read fixed inputs)."""
+    from light_b200 import chain as dchain
+
+    dc = dchain.DecodeChain(device)
+    vq, vo, va, vd = dc.vec(), dc.vec(), dc.vec(), dc.vec()
+    qt = lambda e: ops.QTensor(e[5].reshape(-1), e[4], (e[2], e[3]))  # noqa: E731
+    by_layer = {}
+    for i, e in enumerate(chain.lin):
+        by_layer.setdefault(e[0].split(".")[0], []).append(i)
+    outs = {}
+    first = True
+    for name, idx in by_layer.items():
+        if name == "lm_head":
+            e = chain.lin[idx[0]]
+            outs["logits"] = torch.empty(e[2], device=device)
+            dc.matmul([qt(e)], x_vec=vd, outs=[outs["logits"]])
+            continue
+        q, k, v, o_, gate, up, down = [chain.lin[i] for i in idx]
+        kw = dict(x=chain.x[HID][0].contiguous()) if first else dict(x_vec=vd)
+        first = False
+        dc.matmul([qt(q), qt(k), qt(v)], out_vecs=[vq, None, None], **kw)   # q stands in for the attention output
+        dc.matmul([qt(o_)], x_vec=vq, out_vecs=[vo])
+        dc.matmul([qt(gate), qt(up)], x_vec=vo, act=1, out_vecs=[va])
+        dc.matmul([qt(down)], x_vec=va, out_vecs=[vd])
+    try:
+        dc.build()
+    except Exception as e:  # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {e}"}
+    for _ in range(3):
+        dc.run()
+    torch.cuda.synchronize(device)
+    ms = timed(dc.run, steps, 0, device, lambda: None) / steps
+    return {"operators": 129, "launches": 2, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3), "status": dc.status(),
+            "logits_finite": bool(torch.isfinite(outs["logits"]).all().item())}
 
 
 def main():

@@ -370,7 +370,7 @@ int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *s, c
   if (int took = int4_gemv_fast(x, codes, s, z, y, act_dtype, M, N, K, G, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = int4_prefill(x, codes, s, z, y, act_dtype, M, N, K, G, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = int4_decode_umma(x, codes, s, z, y, act_dtype, M, N, K, G, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
-  return int4_gemv(x, codes, s, z, y, act_dtype, M, N, K, G, (cudaStream_t)stream);
+  return int4_rows_dot(x, codes, s, z, y, act_dtype, M, N, K, G, (cudaStream_t)stream);  // the tile kernel with the 4-bit row fetcher
 }
 
 int light_b200_fp8_block_dequant(const uint8_t *w, const float *s, void *out, int out_dtype, int R, int C, int bR,
@@ -402,7 +402,7 @@ int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *s, v
   if (int took = fp8_gemv_fast(x, w, s, y, act_dtype, M, N, K, bR, bC, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = fp8_prefill(x, w, s, y, act_dtype, M, N, K, bR, bC, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = fp8_decode_umma(x, w, s, y, act_dtype, M, N, K, bR, bC, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
-  return fp8_block_gemv(x, w, s, y, act_dtype, M, N, K, bR, bC, (cudaStream_t)stream);
+  return fp8_block_rows_dot(x, w, s, y, act_dtype, M, N, K, bR, bC, (cudaStream_t)stream);  // the tile kernel with the block-FP8 row fetcher
 }
 
 static int moe_check(const lb200_moe_args *a, const char *op, bool quant, bool need_scratch = true) {

@@ -106,12 +106,12 @@ int fp8_decode_umma(const void *x, const uint8_t *w, const float *scale, void *y
 
 int int4_dequant(const uint32_t *codes, const float *s, const float *z, void *out, int out_dtype, int N, int K, int G,
                  long long offset, cudaStream_t st);
-int int4_gemv(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N,
-              int K, int G, cudaStream_t st);
+int int4_rows_dot(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N, int K, int G,
+                  cudaStream_t st);
 int fp8_block_dequant(const uint8_t *w, const float *s, void *out, int out_dtype, int R, int C, int bR, int bC,
                       cudaStream_t st);
-int fp8_block_gemv(const void *x, const uint8_t *w, const float *s, void *y, int act_dtype, int M, int N, int K, int bR,
-                   int bC, cudaStream_t st);
+int fp8_block_rows_dot(const void *x, const uint8_t *w, const float *s, void *y, int act_dtype, int M, int N, int K, int bR, int bC,
+                       cudaStream_t st);
 int moe_gemm(const lb200_moe_args *a, int device, cudaStream_t st);
 int moe_gemm_q(const lb200_moe_args *a, int device, cudaStream_t st);
 int moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int bR, int bC, int device, cudaStream_t st);

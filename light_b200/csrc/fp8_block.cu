@@ -54,63 +54,4 @@ int fp8_block_dequant(const uint8_t *w, const float *s, void *out, int out_dtype
   return launched("fp8_block_dequant");
 }
 
-// ---- decode GEMV: one warp per weight row and MT activation rows; a lane takes 16 codes (one
-// 16-byte load) per step, all under one scale because bC % 16 == 0.  The scale multiplies the
-// 16-term partial sum, not each weight.
-template <typename T, int MT>
-__global__ void __launch_bounds__(256) fp8_block_gemv_kernel(const T *__restrict__ x, const uint4 *__restrict__ w,
-                                                             const float *__restrict__ s, T *__restrict__ y, int M,
-                                                             int N, int K, int bR, int bC) {
-  const int lane = threadIdx.x & 31;
-  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (n >= N) return;
-  const int m0 = blockIdx.y * MT;
-  const int chunks = K / 16, gc = K / bC;
-  const uint4 *wr = w + (size_t)n * chunks;
-  const float *sr = s + (size_t)(n / bR) * gc;
-  float acc[MT];
-#pragma unroll
-  for (int m = 0; m < MT; m++) acc[m] = 0.f;
-  for (int c = lane; c < chunks; c += 32) {
-    uint4 q = __ldg(wr + c);
-    const int k0 = c * 16;
-    const float sc = __ldg(sr + k0 / bC);
-    float wv[16];
-    e4m3x4_to_f32(q.x, wv);
-    e4m3x4_to_f32(q.y, wv + 4);
-    e4m3x4_to_f32(q.z, wv + 8);
-    e4m3x4_to_f32(q.w, wv + 12);
-#pragma unroll
-    for (int m = 0; m < MT; m++) {
-      if (m0 + m < M) {
-        const T *xr = x + (size_t)(m0 + m) * K + k0;
-        float a = 0.f;
-#pragma unroll
-        for (int j = 0; j < 16; j++) a = fmaf(wv[j], ld_act(xr, j), a);
-        acc[m] = fmaf(a, sc, acc[m]);
-      }
-    }
-  }
-#pragma unroll
-  for (int m = 0; m < MT; m++) {
-    float v = warp_sum(acc[m]);
-    if (lane == 0 && m0 + m < M) st_act(y, (long long)(m0 + m) * N + n, v);
-  }
-}
-
-int fp8_block_gemv(const void *x, const uint8_t *w, const float *s, void *y, int act_dtype, int M, int N, int K, int bR,
-                   int bC, cudaStream_t st) {
-  if (M == 0 || N == 0) return 0;
-  constexpr int MT = 4, WARPS = 8;
-  dim3 grid((N + WARPS - 1) / WARPS, (M + MT - 1) / MT);
-  if (grid.y > 65535) return fail(LB200_E_TOO_LARGE, "fp8_block_gemv: M=%d exceeds the kernel's grid", M);
-  if (act_dtype == LB200_F32)
-    fp8_block_gemv_kernel<float, MT>
-        <<<grid, WARPS * 32, 0, st>>>((const float *)x, (const uint4 *)w, s, (float *)y, M, N, K, bR, bC);
-  else
-    fp8_block_gemv_kernel<__nv_bfloat16, MT><<<grid, WARPS * 32, 0, st>>>((const __nv_bfloat16 *)x, (const uint4 *)w, s,
-                                                                           (__nv_bfloat16 *)y, M, N, K, bR, bC);
-  return launched("fp8_block_gemv");
-}
-
 }  // namespace lb

@@ -50,68 +50,6 @@ int int4_dequant(const uint32_t *codes, const float *s, const float *z, void *ou
   return launched("int4_dequant");
 }
 
-// ---- decode GEMV: one warp per weight row and MT activation rows.  A lane takes 32 codes
-// (one 16-byte load) per step; the group affine is folded, sum s*(q-z)*x = s*(sum q*x - z*sum x),
-// so the inner loop is one FMA per weight plus the running sum of x.
-template <typename T, int MT>
-__global__ void __launch_bounds__(256) int4_gemv_kernel(const T *__restrict__ x, const uint4 *__restrict__ codes,
-                                                        const float *__restrict__ s, const float *__restrict__ z,
-                                                        T *__restrict__ y, int M, int N, int K, int G) {
-  const int lane = threadIdx.x & 31;
-  const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (n >= N) return;
-  const int m0 = blockIdx.y * MT;
-  const int steps = K / 32, ng = K / G;
-  const uint4 *row = codes + (size_t)n * steps;
-  const float *sr = s + (size_t)n * ng, *zr = z + (size_t)n * ng;
-  float acc[MT];
-#pragma unroll
-  for (int m = 0; m < MT; m++) acc[m] = 0.f;
-  for (int c = lane; c < steps; c += 32) {
-    uint4 q = __ldg(row + c);
-    const int k0 = c * 32;
-    const float sc = __ldg(sr + k0 / G), zp = __ldg(zr + k0 / G);
-    const uint32_t wd[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int m = 0; m < MT; m++) {
-      if (m0 + m < M) {
-        const T *xr = x + (size_t)(m0 + m) * K + k0;
-        float dot = 0.f, sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; i++) {
-#pragma unroll
-          for (int j = 0; j < 8; j++) {
-            float xv = ld_act(xr, 8 * i + j);
-            dot = fmaf((float)((wd[i] >> (4 * j)) & 0xFu), xv, dot);
-            sum += xv;
-          }
-        }
-        acc[m] = fmaf(sc, dot - zp * sum, acc[m]);
-      }
-    }
-  }
-#pragma unroll
-  for (int m = 0; m < MT; m++) {
-    float v = warp_sum(acc[m]);
-    if (lane == 0 && m0 + m < M) st_act(y, (long long)(m0 + m) * N + n, v);
-  }
-}
-
-int int4_gemv(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N,
-              int K, int G, cudaStream_t st) {
-  if (M == 0 || N == 0) return 0;
-  constexpr int MT = 4, WARPS = 8;
-  dim3 grid((N + WARPS - 1) / WARPS, (M + MT - 1) / MT);
-  if (grid.y > 65535) return fail(LB200_E_TOO_LARGE, "int4_gemv: M=%d exceeds the kernel's grid", M);
-  if (act_dtype == LB200_F32)
-    int4_gemv_kernel<float, MT>
-        <<<grid, WARPS * 32, 0, st>>>((const float *)x, (const uint4 *)codes, s, z, (float *)y, M, N, K, G);
-  else
-    int4_gemv_kernel<__nv_bfloat16, MT><<<grid, WARPS * 32, 0, st>>>((const __nv_bfloat16 *)x, (const uint4 *)codes, s,
-                                                                      z, (__nv_bfloat16 *)y, M, N, K, G);
-  return launched("int4_gemv");
-}
-
 // ---- checkpoint layouts -> the canonical layout, on the device (the reference converts on the host with
 // O(N K) Go loops at load time, quant/int4.go:103-261).  kind 0: AutoGPTQ "gptq" (qzeros hold zero - 1),
 // 1: "gptq_v2", 2: AutoAWQ GEMM.  Ordered groups only (g_idx[k] = k / G); an act-order checkpoint keeps the

@@ -74,10 +74,12 @@ __device__ __forceinline__ void st_out(__half *p, long long i, float v) { p[i] =
 constexpr int MOE_MT = 8;     // sorted pairs per tile
 constexpr int MOE_WARPS = 8;  // output columns per CTA
 
-// What a row fetcher needs beyond the weight pointer (block-scaled FP8 only).
+// What a row fetcher needs beyond the weight pointer: block-scaled FP8 (scale, bR, bC) and group-quantized 4-bit
+// (scale, zeros, bC = group).
 struct RowAux {
   const float *scale;
   int bR, bC;
+  const float *zeros;
 };
 
 // Weight row fetchers: eight consecutive K elements of row n of expert e as f32.
@@ -128,6 +130,26 @@ struct F8BlockRow {
   }
 };
 
+// Group-quantized 4-bit rows in the canonical layout (codes u32 (N, K/8), nibble j of word c = W[n, 8c + j]; scales and
+// zeros f32 (N, K/G), G % 8 == 0): eight weights are one code word, w = s * (q - z) with the two operations rounded
+// separately, as the dequantize kernel forms them.
+struct Int4Row {
+  const uint32_t *row;
+  const float *srow, *zrow;
+  int G;
+  __device__ Int4Row(const void *w, long long e, int n, int N, int K, const RowAux &aux)
+      : row((const uint32_t *)w + ((size_t)e * N + n) * (size_t)(K / 8)),
+        srow(aux.scale + ((size_t)e * N + n) * (size_t)(K / aux.bC)),
+        zrow(aux.zeros + ((size_t)e * N + n) * (size_t)(K / aux.bC)),
+        G(aux.bC) {}
+  __device__ __forceinline__ void get(int k, float v[8]) const {
+    const uint32_t q = __ldg(row + (k >> 3));
+    const float sc = __ldg(srow + k / G), zp = __ldg(zrow + k / G);
+#pragma unroll
+    for (int j = 0; j < 8; j++) v[j] = __fmul_rn(sc, __fsub_rn((float)((q >> (4 * j)) & 0xFu), zp));
+  }
+};
+
 // One warp: one output column n, the pairs of one tile.  A tile may straddle experts; each run
 // of equal expert id inside it is handled with that expert's weight row.
 template <typename TI, typename TO, typename Row>
@@ -141,12 +163,12 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_gemm_kernel(
   const long long t0 = (long long)blockIdx.y * MOE_MT, t1 = t0 + MOE_MT < M ? t0 + MOE_MT : M;
   long long i = t0;
   while (i < t1) {
-    const long long e = ids[i];
+    const long long e = ids ? ids[i] : 0;  // no routing: one weight matrix, row m of the input gives row m of the output
     if (e < 0 || e >= E) {  // not an expert: the pair is skipped, as an out-of-range pair id is
       i++;
       continue;
     }
-    long long r1 = offsets[e + 1];
+    long long r1 = ids ? offsets[e + 1] : t1;
     if (r1 > t1) r1 = t1;
     if (r1 <= i) r1 = i + 1;  // unsorted input: still make progress
     const int cnt = (int)(r1 - i);
@@ -154,7 +176,7 @@ __global__ void __launch_bounds__(MOE_WARPS * 32) moe_gemm_kernel(
     long long pr[MOE_MT];
 #pragma unroll
     for (int m = 0; m < MOE_MT; m++) {
-      long long p = m < cnt ? pairs[i + m] : -1;
+      long long p = m < cnt ? (pairs ? pairs[i + m] : i + m) : -1;
       if (p < 0 || p >= sizeM) p = -1;
       pr[m] = p;
       xrow[m] = p < 0 ? nullptr : in + (size_t)(rowPerPair ? p : p / topk) * K;
@@ -195,7 +217,7 @@ static int prep(const lb200_moe_args *a, cudaStream_t st) {
 }
 
 template <typename TI, typename TO, typename Row>
-static int run(const lb200_moe_args *a, cudaStream_t st, RowAux aux = RowAux{nullptr, 0, 0}) {
+static int run(const lb200_moe_args *a, cudaStream_t st, RowAux aux = RowAux{nullptr, 0, 0, nullptr}) {
   if (a->M == 0 || a->N == 0) return 0;
   dim3 grid((a->N + MOE_WARPS - 1) / MOE_WARPS, (unsigned)((a->M + MOE_MT - 1) / MOE_MT));
   if ((a->M + MOE_MT - 1) / MOE_MT > 65535)
@@ -204,6 +226,31 @@ static int run(const lb200_moe_args *a, cudaStream_t st, RowAux aux = RowAux{nul
       (const TI *)a->input, a->weights, a->sorted_pairs, a->expert_ids, a->offsets, a->topk_weights, (TO *)a->out, a->M,
       a->size_m, a->E, a->N, a->K, a->topk, a->row_per_pair, aux);
   return launched("moe_gemm");
+}
+
+// x (M, K) . W^T for one matrix through the same tile kernel (no routing): the shapes the tensor-core and one-row kernels
+// of these formats do not take (K % 256 != 0, groups or blocks that are not multiples of 64).
+template <typename T, typename Row>
+static int run_plain(const void *x, const void *w, void *y, int M, int N, int K, const RowAux &aux, cudaStream_t st) {
+  if (M == 0 || N == 0) return 0;
+  dim3 grid((N + MOE_WARPS - 1) / MOE_WARPS, (unsigned)((M + MOE_MT - 1) / MOE_MT));
+  if ((M + MOE_MT - 1) / MOE_MT > 65535) return fail(LB200_E_TOO_LARGE, "light_b200: matmul: %d rows exceed the kernel's grid", M);
+  moe_gemm_kernel<T, T, Row><<<grid, MOE_WARPS * 32, 0, st>>>((const T *)x, w, nullptr, nullptr, nullptr, nullptr, (T *)y, M, M, 1, N, K, 1, 1, aux);
+  return launched("matmul (row fetcher)");
+}
+
+int int4_rows_dot(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N, int K, int G,
+                  cudaStream_t st) {
+  const RowAux aux{s, 0, G, z};
+  if (act_dtype == LB200_F32) return run_plain<float, Int4Row>(x, codes, y, M, N, K, aux, st);
+  return run_plain<__nv_bfloat16, Int4Row>(x, codes, y, M, N, K, aux, st);
+}
+
+int fp8_block_rows_dot(const void *x, const uint8_t *w, const float *s, void *y, int act_dtype, int M, int N, int K, int bR, int bC,
+                       cudaStream_t st) {
+  const RowAux aux{s, bR, bC, nullptr};
+  if (act_dtype == LB200_F32) return run_plain<float, F8BlockRow<float>>(x, w, y, M, N, K, aux, st);
+  return run_plain<__nv_bfloat16, F8BlockRow<__nv_bfloat16>>(x, w, y, M, N, K, aux, st);
 }
 
 int moe_bad_ids_status() {
@@ -269,7 +316,7 @@ int moe_gemm_f8block(const lb200_moe_args *a, const float *w_scale, int bR, int 
   if (bR <= 0 || bC <= 0 || bC % 8 || a->K % bC || a->N % bR || a->K % 8)
     return fail(LB200_E_SHAPE, "light_b200: moe_gemm_f8block: N=%d K=%d with blocks (%d, %d): block_c must be a multiple of 8 and the blocks must tile the weight",
                 a->N, a->K, bR, bC);
-  const RowAux aux{w_scale, bR, bC};
+  const RowAux aux{w_scale, bR, bC, nullptr};
   if (a->dtype == LB200_F32) return run<float, float, F8BlockRow<float>>(a, st, aux);
   return run<__nv_bfloat16, __nv_bfloat16, F8BlockRow<__nv_bfloat16>>(a, st, aux);
 }

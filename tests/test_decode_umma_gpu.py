@@ -57,7 +57,7 @@ def test_q4k_decode_9_to_32_rows(cuda, oracle, N, K):
 
 @pytest.mark.parametrize("M", [1, 5, 16, 17, 33, 64])
 def test_int4_bf16_decode(cuda, oracle, M):
-    """BASELINE config 4 shape class (K = 3584, group 128, bf16 activations): the operands are the
+    """The Qwen2.5-7B W4A16 shape class (K = 3584, group 128, bf16 activations): the operands are the
     reference's bf16 weights bit for bit, so the f64 product of bf16-rounded weights and bf16 x is the
     oracle, up to the one bf16 rounding of the output."""
     N, K, G = 600, 3584, 128
@@ -74,7 +74,7 @@ def test_int4_bf16_decode(cuda, oracle, M):
 
 @pytest.mark.parametrize("M", [1, 8, 24, 64])
 def test_fp8_block_bf16_decode(cuda, oracle, M):
-    """BASELINE config 5 expert shape class (K = 7168, 128 x 128 blocks, bf16 activations)."""
+    """The DeepSeek-V3 expert shape class (K = 7168, 128 x 128 blocks, bf16 activations)."""
     N, K, b = 384, 7168, 128
     codes, scale = synth.random_fp8_block(321, N, K, b, b)
     wq = _bf16(oracle.fp8_block_dequant(codes.numpy(), scale.numpy(), b, b))

@@ -97,7 +97,7 @@ def test_matmul_q_decode_kernels(cuda, oracle, name, N, K):
 @pytest.mark.parametrize("name,N,K", [("q4_k", 37, 1024), ("q4_k", 4096, 4096), ("q6_k", 50, 2048), ("q6_k", 1000, 4096),
                                       ("q8_0", 37, 1024), ("q8_0", 300, 4096), ("q8_0", 129, 256)])
 def test_matmul_q_batched_decode(cuda, oracle, name, N, K):
-    """Batched decode (BASELINE config 2: M = 8, 32, 64, plus ragged token counts): one pass over the
+    """Batched decode (the Llama-3-8B decoder workload: M = 8, 32, 64, plus ragged token counts): one pass over the
     weights per 16 tokens on the tensor cores; f16 operands, 1e-3 relative L2 against the f64 oracle."""
     dt = FORMATS[name]
     raw = synth.gaussian_weight(45, dt, N, K).numpy()
@@ -187,7 +187,7 @@ def test_dequant_vs_reference_cuda(cuda, name):
 
 
 def test_config1_full_size_properties(cuda, oracle):
-    """BASELINE config 1 at full size (N = K = 4096, Q4_K from N(0, 0.02) weights, x ~ N(0, 1)):
+    """The single Q4_K linear at full size (N = K = 4096, Q4_K from N(0, 0.02) weights, x ~ N(0, 1)):
     parity with the threaded CPU oracle, linearity, and row-slice consistency (a row split is a
     byte slice, which is what the multi-GPU column split relies on)."""
     N = K = 4096

@@ -162,7 +162,7 @@ def test_fp8_vs_reference_cuda(cuda):
 
 @pytest.mark.parametrize("layout,N,K,G", [("gptq", 600, 3584, 128), ("gptq_v2", 40, 256, 64), ("awq", 600, 3584, 128), ("awq", 8, 64, 32)])
 def test_int4_checkpoint_repack_matches_oracle(cuda, oracle, layout, N, K, G):
-    """The device converters against the oracle's quant.FromGPTQ / quant.FromAWQ at a BASELINE config 4 shape and at
+    """The device converters against the oracle's quant.FromGPTQ / quant.FromAWQ at a Qwen2.5-7B W4A16 shape and at
     ragged tile edges (N, K/8 not multiples of 32)."""
     codes, s, z = synth.random_int4(701, N, K, G)
     if layout == "gptq":

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 @pytest.mark.parametrize("T,E,topk,norm", [(4096, 256, 8, True), (33, 8, 2, True), (5, 64, 6, False), (1, 1000, 32, True)])
 def test_route_sigmoid(cuda, oracle, T, E, topk, norm):
-    """BASELINE config 5 routing: logits ~ N(0, 1), per-expert bias ~ N(0, 0.5)."""
+    """The DeepSeek-V3 MoE workload's routing: logits ~ N(0, 1), per-expert bias ~ N(0, 0.5)."""
     g = torch.Generator().manual_seed(900 + T)
     logits, bias = torch.randn(T, E, generator=g), torch.randn(E, generator=g) * 0.5
     want_ids, want_w = oracle.deepseek_route_sigmoid(logits.numpy(), bias.numpy(), topk, norm)
