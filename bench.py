@@ -659,30 +659,38 @@ def moe_extras(device, peaks):
 
 
 def chain_kernel_extras(chain, device, steps):
-    """The M = 1 step as ONE persistent launch: the 129 operators as a device-side program, every operator reading the
-    vector the one before wrote (a dependent chain, unlike the headline's launches, which all read fixed inputs)."""
+    """The M = 1 step as ONE persistent launch: the 129 operators as a device-side program with the RMS norms and the
+    residual adds folded in, every operator reading the vector the one before wrote (a dependent chain, unlike the
+    headline's launches, which all read fixed inputs)."""
     from light_b200 import chain as dchain
 
     dc = dchain.DecodeChain(device)
-    vq, vo, va, vd = dc.vec(), dc.vec(), dc.vec(), dc.vec()
+    vq, vo, va, vd, vh = dc.vec(), dc.vec(), dc.vec(), dc.vec(), [dc.vec(), dc.vec()]
     qt = lambda e: ops.QTensor(e[5].reshape(-1), e[4], (e[2], e[3]))  # noqa: E731
     by_layer = {}
     for i, e in enumerate(chain.lin):
         by_layer.setdefault(e[0].split(".")[0], []).append(i)
-    outs = {}
-    first = True
+    outs = {"logits": torch.empty(VOCAB, device=device)}
+    nw = torch.ones(HID, device=device)
+    h0 = chain.x[HID][0].contiguous()
+    cur = None  # the chain vector that holds the residual stream
     for name, idx in by_layer.items():
         if name == "lm_head":
-            e = chain.lin[idx[0]]
-            outs["logits"] = torch.empty(e[2], device=device)
-            dc.matmul([qt(e)], x_vec=vd, outs=[outs["logits"]])
+            last = vh[0] if cur == vh[1] else vh[1]
+            dc.matmul([qt(chain.lin[idx[0]])], x_vec=cur, res_vec=vd, sum_vec=last, outs=[outs["logits"]], norm_weight=nw, eps=1e-5)
             continue
         q, k, v, o_, gate, up, down = [chain.lin[i] for i in idx]
-        kw = dict(x=chain.x[HID][0].contiguous()) if first else dict(x_vec=vd)
-        first = False
-        dc.matmul([qt(q), qt(k), qt(v)], out_vecs=[vq, None, None], **kw)   # q stands in for the attention output
-        dc.matmul([qt(o_)], x_vec=vq, out_vecs=[vo])
-        dc.matmul([qt(gate), qt(up)], x_vec=vo, act=1, out_vecs=[va])
+        # decoder layer: norm(h + down) -> q,k,v (q stands in for the attention output) -> o -> norm(h' + o) -> act(gate) * up -> down
+        if cur is None:
+            dc.matmul([qt(q), qt(k), qt(v)], x=h0, out_vecs=[vq, None, None], norm_weight=nw, eps=1e-5)
+            dc.matmul([qt(o_)], x_vec=vq, out_vecs=[vo])
+            dc.matmul([qt(gate), qt(up)], x=h0, res_vec=vo, sum_vec=vh[1], act=1, out_vecs=[va], norm_weight=nw, eps=1e-5)
+            cur = vh[1]
+        else:
+            other = vh[0] if cur == vh[1] else vh[1]
+            dc.matmul([qt(q), qt(k), qt(v)], x_vec=cur, res_vec=vd, sum_vec=other, out_vecs=[vq, None, None], norm_weight=nw, eps=1e-5)
+            dc.matmul([qt(o_)], x_vec=vq, out_vecs=[vo])
+            dc.matmul([qt(gate), qt(up)], x_vec=other, res_vec=vo, sum_vec=cur, act=1, out_vecs=[va], norm_weight=nw, eps=1e-5)
         dc.matmul([qt(down)], x_vec=va, out_vecs=[vd])
     try:
         dc.build()
@@ -692,7 +700,7 @@ def chain_kernel_extras(chain, device, steps):
         dc.run()
     torch.cuda.synchronize(device)
     ms = timed(dc.run, steps, 0, device, lambda: None) / steps
-    return {"operators": 129, "launches": 2, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3), "status": dc.status(),
+    return {"operators": len(dc.ops), "launches": 2, "ms_per_step": ms, "tok_s": 1 / (ms * 1e-3), "status": dc.status(),
             "logits_finite": bool(torch.isfinite(outs["logits"]).all().item())}
 
 
