@@ -367,6 +367,11 @@ int light_b200_int4_gemv(const void *x, const uint32_t *codes, const float *s, c
   REQUIRE_PTR(y, "int4_gemv");
   if (!aligned(codes, 16) || !aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: int4_gemv: x and codes must be 16-byte aligned");
   if (int rc = bind(device)) return rc;
+  if (M >= 4 && M <= 64) {  // token tiles over activations staged once (needs the workspace)
+    size_t wsb = 0;
+    void *ws = workspace_ptr(device, &wsb);
+    if (int took = int4_decode_nt(x, codes, s, z, y, act_dtype, M, N, K, G, ws, wsb, (cudaStream_t)stream)) return took == 1 ? 0 : took;
+  }
   if (int took = int4_gemv_fast(x, codes, s, z, y, act_dtype, M, N, K, G, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = int4_prefill(x, codes, s, z, y, act_dtype, M, N, K, G, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = int4_decode_umma(x, codes, s, z, y, act_dtype, M, N, K, G, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;

@@ -36,10 +36,19 @@ constexpr int TOK_PITCH = 544;  // bytes per (block, token) record: 512 of f16 +
 
 struct NtArgs {  // up to four matrices that share x: their row tiles form one list
   const uint8_t *w[4];
-  float *out[4];
+  float *out[4];   // bf16 rows when out_bf16 is set
   int n[4];
   int tend[4];
   int count;
+  int out_bf16;
+  const float *scales[4], *zeros[4];  // group-quantized 4-bit only: (n, K / 128) each
+};
+
+struct TileAt {  // where a list index lies for one warp: its row tile
+  bool live;
+  int wj, r0;
+  const uint8_t *tile0, *w_end;
+  const float *sc, *zp;  // 4-bit only: the scale / zero rows of the tile's first row
 };
 
 __device__ int g_nt_status;  // non-zero: a bounded wait (a block of activations, a partial sum) gave up (sticky)
@@ -66,8 +75,18 @@ __device__ __forceinline__ __half2 u2h(uint32_t v) { return *reinterpret_cast<__
 // PAIR (Q4_K): the 8-byte group F (elements 4F .. 4F+3 as (x0, x2), (x1, x3)) lands at slot
 // ((F / 8 & 1) * 8 + (F & 7)) * 4 + F / 16, so that lane (token g, t) finds pair t's low-nibble sub-block at
 // i * 32 + t * 8 and its high-nibble sub-block 256 bytes further.  Otherwise (Q6_K) natural order.
-template <bool PAIR>
-__global__ void __launch_bounds__(THREADS) x_stage_kernel(const float *__restrict__ x, uint8_t *__restrict__ xs, int M, int NT, int K) {
+// LAYOUT 2 (4-bit, canonical layout): a code word holds eight consecutive k, and a lane's two values of an MMA k slot
+// pair are nibbles t and t + 4 of one word, so the 16 values of k step s lie as [t][j]: value 16 s + 4 j + t.
+__device__ __forceinline__ float4 ld_x4(const float *p) { return __ldg(reinterpret_cast<const float4 *>(p)); }
+__device__ __forceinline__ float4 ld_x4(const __nv_bfloat16 *p) {
+  const uint2 u = __ldg(reinterpret_cast<const uint2 *>(p));
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.x)), b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <int LAYOUT, typename XT>
+__global__ void __launch_bounds__(THREADS) x_stage_kernel(const XT *__restrict__ x, uint8_t *__restrict__ xs, int M, int NT, int K) {
+  constexpr bool PAIR = LAYOUT == 1;
   pdl_launch_dependents();
   const int rec = blockIdx.x * CW + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   const int nb = K >> 8;
@@ -79,8 +98,8 @@ __global__ void __launch_bounds__(THREADS) x_stage_kernel(const float *__restric
   float4 v[2];
   v[0] = v[1] = make_float4(0.f, 0.f, 0.f, 0.f);
   if (tk < M) {
-    const float4 *xp = reinterpret_cast<const float4 *>(x + (size_t)tk * K + b * 256);
-    v[0] = __ldg(xp + lane), v[1] = __ldg(xp + lane + 32);
+    const XT *xp = x + (size_t)tk * K + b * 256;
+    v[0] = ld_x4(xp + 4 * lane), v[1] = ld_x4(xp + 4 * (lane + 32));
   }
   float s[2];
 #pragma unroll
@@ -89,8 +108,14 @@ __global__ void __launch_bounds__(THREADS) x_stage_kernel(const float *__restric
     const __half2 lim = __float2half2_rn(65504.f);
     const __half2 h02 = __hmax2(__hmin2(__floats2half2_rn(v[j].x, v[j].z), lim), __hneg2(lim));
     const __half2 h13 = __hmax2(__hmin2(__floats2half2_rn(v[j].y, v[j].w), lim), __hneg2(lim));
-    const int P = PAIR ? (((F >> 3) & 1) * 8 + (F & 7)) * 4 + (F >> 4) : F;
-    *reinterpret_cast<uint2 *>(dst + P * 8) = make_uint2(h2u(h02), h2u(h13));
+    if constexpr (LAYOUT == 2) {
+      // values 4 F .. 4 F + 3 = k step F / 4, j = F % 4, t = 0 .. 3: four 2-byte stores, 8 bytes apart
+      __half *o = reinterpret_cast<__half *>(dst) + (F >> 2) * 16 + (F & 3);
+      o[0] = __low2half(h02), o[4] = __low2half(h13), o[8] = __high2half(h02), o[12] = __high2half(h13);
+    } else {
+      const int P = PAIR ? (((F >> 3) & 1) * 8 + (F & 7)) * 4 + (F >> 4) : F;
+      *reinterpret_cast<uint2 *>(dst + P * 8) = make_uint2(h2u(h02), h2u(h13));
+    }
     const float2 a = __half22float2(h02), c = __half22float2(h13);
     float p = (a.x + a.y) + (c.x + c.y);  // of the ROUNDED values, the ones the tensor core multiplies
     p += __shfl_xor_sync(0xffffffffu, p, 1), p += __shfl_xor_sync(0xffffffffu, p, 2), p += __shfl_xor_sync(0xffffffffu, p, 4);
@@ -185,13 +210,18 @@ struct Run {  // the (group, block) list cut into G consecutive runs, one per CT
 
 // acc -> out rows of one tile: lane (g, t) holds rows g, g+8 x tokens 2t, 2t+1 of every group of eight
 template <int NG>
-__device__ __forceinline__ void store_tile(const float (&acc)[NG][4], float *out, int n, int r0, int M, int g, int t) {
+__device__ __forceinline__ void store_tile(const float (&acc)[NG][4], float *out, bool bf16, int n, int r0, int M, int g, int t) {
 #pragma unroll
   for (int q = 0; q < NG; q++)
 #pragma unroll
     for (int c = 0; c < 4; c++) {
       const int tok = q * 8 + 2 * t + (c & 1), row = r0 + g + 8 * (c >> 1);
-      if (tok < M) out[(size_t)tok * n + row] = acc[q][c];
+      if (tok < M) {
+        if (bf16)
+          reinterpret_cast<__nv_bfloat16 *>(out)[(size_t)tok * n + row] = __float2bfloat16_rn(acc[q][c]);
+        else
+          out[(size_t)tok * n + row] = acc[q][c];
+      }
     }
 }
 
@@ -282,7 +312,7 @@ struct Q4Fmt {
     if (lane < 16) cp_async16(dst + 2048, base + soff[4]);
   }
   template <int NG, typename F>
-  __device__ __forceinline__ void unit(uint32_t slot_addr, uint32_t xb, float (&acc)[NG][4], uint32_t, uint32_t, int lane, F &&slot_free) const {
+  __device__ __forceinline__ void unit(uint32_t slot_addr, uint32_t xb, float (&acc)[NG][4], const TileAt &, uint32_t, int lane, F &&slot_free) const {
     const int g = lane >> 2, t = lane & 3;
     const uint32_t mask = 0x00F000F0u, magic = 0x54005400u;  // f16 (64 + nibble)
     const uint32_t sb = slot_addr + ld_off;
@@ -440,14 +470,65 @@ struct Q6Fmt {
       acc[qg][2] = fmaf(dd[1], dq[qg][2], acc[qg][2]), acc[qg][3] = fmaf(dd[1], dq[qg][3], acc[qg][3]);
     }
   }
-  // tile_off = byte offset of the tile's first row from the matrix start (its low four bits matter)
+  // only the low four bits of the block's byte offset from the matrix start matter (the matrix is 16-byte aligned)
   template <int NG, typename F>
-  __device__ __forceinline__ void unit(uint32_t sb, uint32_t xb, float (&acc)[NG][4], uint32_t tile_off, uint32_t blk, int lane, F &&slot_free) const {
-    const uint32_t skew = (tile_off + blk * 210u + (uint32_t)(lane >> 2) * row_bytes) & 15u;
+  __device__ __forceinline__ void unit(uint32_t sb, uint32_t xb, float (&acc)[NG][4], const TileAt &at, uint32_t blk, int lane, F &&slot_free) const {
+    const uint32_t skew = ((uint32_t)at.r0 * row_bytes + blk * 210u + (uint32_t)(lane >> 2) * row_bytes) & 15u;
     if (blk & 1)
       unit_p<NG, true>(sb, xb, acc, skew, lane, slot_free);
     else
       unit_p<NG, false>(sb, xb, acc, skew, lane, slot_free);
+  }
+};
+
+// ------------------------------------------------------------------------------------ 4-bit, group 128
+// Canonical layout (codes u32 (N, K/8), nibble j of word c = W[n, 8c + j]; scales, zeros f32 (N, K/128)).  A row's 256-k
+// block is 128 bytes = 32 words; k step s uses words 2s and 2s + 1.  Lane (g, t) takes nibbles t and t + 4 of each (one
+// shift by 4t, one LOP3 to f16 1024 + q), subtracts the group's zero point exactly (HADD2 with -(1024 + z)) and multiplies
+// by the group's scale (HMUL2): w = f16((q - z) * s), one rounding.  The tile lies at a 144-byte pitch so that the eight
+// rows of a load fall into distinct banks.
+struct Int4Fmt {
+  static constexpr int S = 3, PITCH = 144, TILE = ROWS * PITCH, BLOCK = 128;
+  uint32_t row_bytes;
+  __device__ __forceinline__ void setup(int, uint32_t row_bytes_) { row_bytes = row_bytes_; }
+  __device__ __forceinline__ void issue(uint32_t dst, const uint8_t *tile0, uint32_t blk, int lane, const uint8_t *) const {
+#pragma unroll
+    for (int i = 0; i < 4; i++) {  // 128 chunks of 16 bytes: chunk c = lane + 32 i is piece c % 8 of row c / 8
+      const uint32_t c = lane + 32 * i, r = c >> 3, piece = c & 7;
+      cp_async16(dst + r * PITCH + piece * 16, tile0 + (size_t)r * row_bytes + blk * 128u + piece * 16u);
+    }
+  }
+  template <int NG, typename F>
+  __device__ __forceinline__ void unit(uint32_t sb, uint32_t xb, float (&acc)[NG][4], const TileAt &at, uint32_t blk, int lane, F &&slot_free) const {
+    const int g = lane >> 2, t = lane & 3;
+    __half2 sc[2][2], off[2][2];  // [row g | g + 8][group of this block]
+    const int ng = (int)(row_bytes >> 6);  // groups per row: K / 128
+#pragma unroll
+    for (int r = 0; r < 2; r++)
+#pragma unroll
+      for (int gi = 0; gi < 2; gi++) {
+        const size_t o = (size_t)(g + 8 * r) * ng + blk * 2 + gi;
+        sc[r][gi] = __float2half2_rn(__ldg(at.sc + o));
+        off[r][gi] = __float2half2_rn(-(1024.f + __ldg(at.zp + o)));
+      }
+    const uint32_t sh = 4u * t;
+    const uint32_t bx = xb + g * TOK_PITCH + t * 8;
+    auto cvt = [&](uint32_t w, __half2 o, __half2 s) { return h2u(__hmul2(__hadd2(u2h(and_or(w >> sh, 0x000F000Fu, 0x64006400u)), o), s)); };
+#pragma unroll
+    for (int i = 0; i < 8; i++) {  // two k steps per 16-byte load
+      const int gi = i >> 2;
+      const uint4 a = lds128(sb + g * PITCH + 16 * i), b = lds128(sb + (g + 8) * PITCH + 16 * i);
+      const uint32_t e0 = cvt(a.x, off[0][gi], sc[0][gi]), e1 = cvt(b.x, off[1][gi], sc[1][gi]), e2 = cvt(a.y, off[0][gi], sc[0][gi]), e3 = cvt(b.y, off[1][gi], sc[1][gi]);
+      const uint32_t f0 = cvt(a.z, off[0][gi], sc[0][gi]), f1 = cvt(b.z, off[1][gi], sc[1][gi]), f2 = cvt(a.w, off[0][gi], sc[0][gi]), f3 = cvt(b.w, off[1][gi], sc[1][gi]);
+#pragma unroll
+      for (int q = 0; q < NG; q++) {
+        const uint2 be = lds64(bx + q * (8 * TOK_PITCH) + (2 * i) * 32), bo = lds64(bx + q * (8 * TOK_PITCH) + (2 * i + 1) * 32);
+        mma16816(acc[q], e0, e1, e2, e3, be.x, be.y);
+        mma16816(acc[q], f0, f1, f2, f3, bo.x, bo.y);
+      }
+    }
+    __syncwarp();  // the slot is free again
+    slot_free();
   }
 };
 
@@ -473,12 +554,7 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint
   Fmt fmt;
   fmt.setup(lane, row_bytes);
 
-  // where a list index lies: which tile this warp has there
-  struct At {
-    bool live;
-    int wj, r0;
-    const uint8_t *tile0, *w_end;
-  };
+  using At = TileAt;
   auto at_group = [&](int grp) {
     At a;
     const int tile = grp * CW + warp;
@@ -486,6 +562,8 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint
     if (a.live) resolve(ma, tile, a.wj, a.r0);
     a.tile0 = ma.w[a.wj] + (size_t)a.r0 * row_bytes;
     a.w_end = ma.w[a.wj] + (size_t)ma.n[a.wj] * row_bytes;
+    a.sc = ma.scales[a.wj] ? ma.scales[a.wj] + (size_t)a.r0 * (K >> 7) : nullptr;
+    a.zp = ma.zeros[a.wj] ? ma.zeros[a.wj] + (size_t)a.r0 * (K >> 7) : nullptr;
     return a;
   };
 
@@ -530,7 +608,7 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint
       __syncwarp();
       const uint32_t sb = ring + slot * Fmt::TILE;
       slot = slot + 1 == S ? 0 : slot + 1;
-      fmt.template unit<NG>(sb, xf.buf(k), acc, (uint32_t)((size_t)at.r0 * row_bytes), (uint32_t)blk, lane, issue);
+      fmt.template unit<NG>(sb, xf.buf(k), acc, at, (uint32_t)blk, lane, issue);
     } else {
       issue();  // keeps the commit-group count in step with the live warps' (and requests the next group's tiles)
     }
@@ -538,7 +616,7 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint
     if (blk == nb - 1 || k == n - 1) {  // the run leaves this group
       if (at.live) {
         if (seg_b0 == 0 && blk == nb - 1) {
-          store_tile<NG>(acc, ma.out[at.wj], ma.n[at.wj], at.r0, M, g, t);
+          store_tile<NG>(acc, ma.out[at.wj], ma.out_bf16 != 0, ma.n[at.wj], at.r0, M, g, t);
         } else {
           const bool first = k - (blk - seg_b0) == 0;  // this CTA's first run (slot 0) or its last (slot 1)
           write_part<NG>(acc, parts, run.c, first ? 0 : 1, warp, lane, epoch);
@@ -558,7 +636,7 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint
   cp_async_wait<0>();
   if (!dead && fix_grp >= 0 && fix_at.live) {
     fix_up<NG>(run, fix_grp, parts, warp, lane, epoch, acc);
-    store_tile<NG>(acc, ma.out[fix_at.wj], ma.n[fix_at.wj], fix_at.r0, M, g, t);
+    store_tile<NG>(acc, ma.out[fix_at.wj], ma.out_bf16 != 0, ma.n[fix_at.wj], fix_at.r0, M, g, t);
   }
 }
 
@@ -598,6 +676,48 @@ int launch_by_ng(int ng, const uint8_t *xs, float *parts, const NtArgs &ma, int 
 }
 
 int g_nt_min_m = 9, g_nt_max_m = 64;  // LIGHT_B200_NT_MIN_M / _MAX_M (tuning knobs)
+
+// the pre-pass: layout 0 (natural, Q6_K), 1 (sub-block pairs, Q4_K) or 2 (4-bit code words); x f32 or bf16
+int stage_x(int layout, const void *x, int x_dtype, void *ws, int M, int NT, int K, cudaStream_t st) {
+  const int recs = (K >> 8) * NT;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((recs + CW - 1) / CW));
+  cfg.blockDim = dim3(THREADS);
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  const float *xf = (const float *)x;
+  const __nv_bfloat16 *xb = (const __nv_bfloat16 *)x;
+  uint8_t *dst = (uint8_t *)ws;
+  if (x_dtype == LB200_F32)
+    e = layout == 0   ? cudaLaunchKernelEx(&cfg, x_stage_kernel<0, float>, xf, dst, M, NT, K)
+        : layout == 1 ? cudaLaunchKernelEx(&cfg, x_stage_kernel<1, float>, xf, dst, M, NT, K)
+                      : cudaLaunchKernelEx(&cfg, x_stage_kernel<2, float>, xf, dst, M, NT, K);
+  else
+    e = layout == 0   ? cudaLaunchKernelEx(&cfg, x_stage_kernel<0, __nv_bfloat16>, xb, dst, M, NT, K)
+        : layout == 1 ? cudaLaunchKernelEx(&cfg, x_stage_kernel<1, __nv_bfloat16>, xb, dst, M, NT, K)
+                      : cudaLaunchKernelEx(&cfg, x_stage_kernel<2, __nv_bfloat16>, xb, dst, M, NT, K);
+  if (e != cudaSuccess) return fail((int)e, "light_b200: matmul (decode, staging): %s", cudaGetErrorString(e));
+  return launched("matmul (decode, staging)");
+}
+
+// the persistent grid: every CTA slot of the GPU, but at least about four blocks per CTA unless SMs would idle; runs as
+// even as possible, or, where one CTA per SM is all there is, of one fixed length that divides a row's blocks
+void plan_grid(long long T, int nb, int ng, int env_grid, int &grid, int &run_len) {
+  const int sms = sm_count(), slots = sms * (ng <= 4 ? 2 : 1);
+  long long limit = T / 4 > sms ? T / 4 : (T < sms ? T : sms);
+  if (limit > slots) limit = slots;
+  if (env_grid > 0) limit = env_grid < T ? env_grid : T;
+  if (limit > MAX_GRID) limit = MAX_GRID;
+  run_len = 0;
+  grid = (int)limit;
+  const int q = (int)((T + limit - 1) / limit);
+  if (limit <= sms && q <= nb && nb % q == 0) run_len = q, grid = (int)((T + q - 1) / q);
+}
 
 int ng_of(int M) { return M <= 8 ? 1 : M <= 16 ? 2 : M <= 32 ? 4 : 8; }
 size_t stage_bytes(int M, int K) { return ((size_t)(K >> 8) * 8 * ng_of(M) * TOK_PITCH + 1023) & ~(size_t)1023; }
@@ -643,44 +763,45 @@ int gguf_decode_nt(int type, const float *x, const void *const *w, float *const 
   }
   a.count = count;
   const int ng = ng_of(M), NT = 8 * ng, nb = K >> 8;
-  // the persistent grid: every CTA slot of the GPU, but at least about four blocks per CTA unless SMs would idle
-  const int sms = sm_count(), slots = sms * (ng <= 4 ? 2 : 1);
   const long long T = (long long)((tiles + CW - 1) / CW) * nb;
   if (T >= (1ll << 30)) return 0;
   // a short list (a 4096 x 4096 matrix is 512 entries) leaves each CTA a few blocks and most of the time goes into
   // starting and the split-K fix-up: up to 32 rows the cluster kernel for Q4_K is quicker there
-  if (!q6 && M <= 32 && T < 4ll * sms && !env_grid) return 0;
-  long long limit = T / 4 > sms ? T / 4 : (T < sms ? T : sms);
-  if (limit > slots) limit = slots;
-  if (env_grid > 0) limit = env_grid < T ? env_grid : T;
-  if (limit > MAX_GRID) limit = MAX_GRID;
-  // Runs as even as possible over `limit` CTAs; but where one CTA per SM is all there is, runs of one fixed length that
-  // divides a row's blocks take the same time and never straddle a group (fewer partial sums).
-  int run_len = 0;
-  long long grid = limit;
-  {
-    const int q = (int)((T + limit - 1) / limit);
-    if (limit <= sms && q <= nb && nb % q == 0) run_len = q, grid = (T + q - 1) / q;
-  }
-  {
-    const int recs = nb * NT;
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)((recs + CW - 1) / CW));
-    cfg.blockDim = dim3(THREADS);
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = q6 ? cudaLaunchKernelEx(&cfg, x_stage_kernel<false>, x, (uint8_t *)ws, M, NT, K)
-                       : cudaLaunchKernelEx(&cfg, x_stage_kernel<true>, x, (uint8_t *)ws, M, NT, K);
-    if (e != cudaSuccess) return fail((int)e, "light_b200: matmul_q (decode, staging): %s", cudaGetErrorString(e));
-    if (int rc = launched("matmul_q (decode, staging)")) return rc;
-  }
+  if (!q6 && M <= 32 && T < 4ll * sm_count() && !env_grid) return 0;
+  int grid, run_len;
+  plan_grid(T, nb, ng, env_grid, grid, run_len);
+  if (int rc = stage_x(q6 ? 0 : 1, x, LB200_F32, ws, M, NT, K, st)) return rc;
   float *parts = reinterpret_cast<float *>((uint8_t *)ws + stage_bytes(M, K));
-  const int rc = q6 ? launch_by_ng<Q6Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, (int)grid, run_len, st)
-                    : launch_by_ng<Q4Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, (int)grid, run_len, st);
+  const int rc = q6 ? launch_by_ng<Q6Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st)
+                    : launch_by_ng<Q4Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st);
+  return rc ? rc : 1;
+}
+
+// Group-quantized 4-bit weights (canonical layout, group 128), x (M, K) and y (M, N) BF16, 4 .. 64 rows.  F32 activations
+// stay on the kernels that keep x at f32 accuracy (the reference's bound for that type is 1e-4; f16 activations give 3e-4).
+// Returns 1 if launched, 0 if the shape is not covered, else an error.
+int int4_decode_nt(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N, int K, int G,
+                   void *ws, size_t ws_bytes, cudaStream_t st) {
+  static int on = -1, min_m = 4;
+  if (on < 0) {
+    on = getenv("LIGHT_B200_NT_INT4") ? atoi(getenv("LIGHT_B200_NT_INT4")) : 1;
+    if (const char *e = getenv("LIGHT_B200_NT_INT4_MIN_M")) min_m = atoi(e);
+  }
+  if (!on || act_dtype != LB200_BF16 || G != 128 || M < min_m || M > 64 || K % 256 || N < ROWS || ((uintptr_t)x & 15) || ((uintptr_t)codes & 15) || !ws || ((uintptr_t)ws & 127) ||
+      ws_bytes < decode_nt_ws_bytes(M, K))
+    return 0;
+  NtArgs a = {};
+  const int tiles = (N + ROWS - 1) / ROWS;
+  a.w[0] = (const uint8_t *)codes, a.out[0] = (float *)y, a.n[0] = N, a.tend[0] = tiles, a.count = 1;
+  a.out_bf16 = act_dtype == LB200_BF16, a.scales[0] = s, a.zeros[0] = z;
+  const int ng = ng_of(M), NT = 8 * ng, nb = K >> 8;
+  const long long T = (long long)((tiles + CW - 1) / CW) * nb;
+  if (T >= (1ll << 30)) return 0;
+  int grid, run_len;
+  plan_grid(T, nb, ng, 0, grid, run_len);
+  if (int rc = stage_x(2, x, act_dtype, ws, M, NT, K, st)) return rc;
+  float *parts = reinterpret_cast<float *>((uint8_t *)ws + stage_bytes(M, K));
+  const int rc = launch_by_ng<Int4Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st);
   return rc ? rc : 1;
 }
 

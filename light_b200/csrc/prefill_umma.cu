@@ -367,13 +367,14 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
   // (measured: a 128-row tile takes 0.75 of a 256-row tile)
   int bm = (!grp.offsets && waves_cost(128) < waves_cost(256)) ? 128 : 256;
   if (const char *e = getenv("LIGHT_B200_PREFILL_BM")) bm = (atoi(e) == 128 && !grp.offsets) ? 128 : atoi(e) == 256 ? 256 : bm;
-  // Few tokens (one 128-row tile) and few weight-row tiles: split K over a cluster of up to 8 CTAs so that
-  // every SM has one, the smallest power of two that does
+  // Few tokens and few weight-row tiles (fewer 128-row tiles than SMs): split K over a cluster of up to 8 CTAs so
+  // that every SM has one, the smallest power of two that does
   int ks = 1;
-  if (!grp.offsets && M <= 128 && K % 256 == 0) {
+  if (!grp.offsets && K % 256 == 0 && (M <= 128 || nt * ((M + 127) / 128) < sm_count())) {
     bm = 128;
     const int nblk = K >> 8;
-    while (ks < 8 && ks * 2 <= nblk && nt * ks < sm_count()) ks *= 2;
+    const long long ctas = nt * ((M + 127) / 128);
+    while (ks < 8 && ks * 2 <= nblk && ctas * ks < sm_count()) ks *= 2;
   }
   // grouped: at most ceil(M / bm) + E tiles (every expert can end with one partial tile)
   dim3 grid((unsigned)nt, (M + bm - 1) / bm + (grp.offsets ? grp.E : 0), (unsigned)ks);

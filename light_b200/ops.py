@@ -419,6 +419,8 @@ def MatMulInt4(x: torch.Tensor, w: Int4) -> torch.Tensor:
     M, N = x.shape[0], w.N()
     if M > 64 and x.dtype == torch.float32:  # tensor-core path: f16 copy of x in the workspace
         ensure_workspace(dev, M * w.K() * 2)
+    elif 4 <= M <= 64 and x.dtype == torch.bfloat16:  # token tiles over activations staged once
+        ensure_workspace(dev, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, w.K())))
     out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
     _lib.check(_lib.lib().light_b200_int4_gemv(_ptr(xc), _ptr(w.codes.contiguous()), _ptr(w.scales.contiguous()),
                                                _ptr(w.zeros.contiguous()), _ptr(out), _ACT[x.dtype], M, N, w.K(),
