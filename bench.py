@@ -540,6 +540,10 @@ def extras(chain, device, args):
            18944 * 3584 // 2 + 2 * 18944 * 28 * 4, "int4_g128_18944x3584_bf16")
     rotate(lambda i: synth.random_fp8_block(7200 + i, 4096, 7168, device=device), lambda w: ops.MatMulF8Block(x71, w[0], w[1], 128, 128),
            4096 * 7168 + 32 * 56 * 4, "fp8_block128_4096x7168_f32")
+    # the same formats with bf16 activations at 16 rows (token tiles over activations staged once)
+    x71b = torch.randn(16, 7168, device=device).to(torch.bfloat16)
+    rotate(lambda i: synth.random_fp8_block(7300 + i, 18432, 7168, device=device), lambda w: ops.MatMulF8Block(x71b, w[0], w[1], 128, 128),
+           18432 * 7168 + 144 * 56 * 4, "fp8_block128_18432x7168_bf16_16rows")
     M = 2048
     by = {e[0]: e for e in chain.lin}
     qkv = torch.cat([by["l0.q"][5], by["l0.k"][5], by["l0.v"][5]])          # fused rows: a byte concatenation

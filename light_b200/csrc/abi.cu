@@ -404,6 +404,11 @@ int light_b200_fp8_block_gemv(const void *x, const uint8_t *w, const float *s, v
   REQUIRE_PTR(y, "fp8_block_gemv");
   if (!aligned(w, 16) || !aligned(x, 16)) return fail(LB200_E_ALIGN, "light_b200: fp8_block_gemv: x and w must be 16-byte aligned");
   if (int rc = bind(device)) return rc;
+  if (M >= 4 && M <= 64) {  // token tiles over activations staged once (needs the workspace)
+    size_t wsb = 0;
+    void *ws = workspace_ptr(device, &wsb);
+    if (int took = fp8_decode_nt(x, w, s, y, act_dtype, M, N, K, bR, bC, ws, wsb, (cudaStream_t)stream)) return took == 1 ? 0 : took;
+  }
   if (int took = fp8_gemv_fast(x, w, s, y, act_dtype, M, N, K, bR, bC, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = fp8_prefill(x, w, s, y, act_dtype, M, N, K, bR, bC, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;
   if (int took = fp8_decode_umma(x, w, s, y, act_dtype, M, N, K, bR, bC, device, (cudaStream_t)stream)) return took == 1 ? 0 : took;

@@ -136,6 +136,8 @@ size_t decode_nt_ws_bytes(int M, int K);
 int gguf_decode_nt(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K, void *ws,
                    size_t ws_bytes, cudaStream_t st);
 int decode_nt_status();
+int fp8_decode_nt(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR, int bC, void *ws,
+                  size_t ws_bytes, cudaStream_t st);
 int int4_decode_nt(const void *x, const uint32_t *codes, const float *s, const float *z, void *y, int act_dtype, int M, int N, int K, int G,
                    void *ws, size_t ws_bytes, cudaStream_t st);
 size_t decode_ts_ws_bytes(int M, int K);

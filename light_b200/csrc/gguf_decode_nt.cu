@@ -21,6 +21,8 @@
 //
 // Every sum has a fixed order (k inside an MMA, blocks ascending inside a run, runs in CTA order), so results are
 // deterministic.  x is rounded to f16 once (2^-11 relative per element, about 2e-4 relative L2 on the output).
+#include <cuda_fp8.h>
+
 #include <type_traits>
 
 #include "common.cuh"
@@ -108,7 +110,13 @@ __global__ void __launch_bounds__(THREADS) x_stage_kernel(const XT *__restrict__
     const __half2 lim = __float2half2_rn(65504.f);
     const __half2 h02 = __hmax2(__hmin2(__floats2half2_rn(v[j].x, v[j].z), lim), __hneg2(lim));
     const __half2 h13 = __hmax2(__hmin2(__floats2half2_rn(v[j].y, v[j].w), lim), __hneg2(lim));
-    if constexpr (LAYOUT == 2) {
+    if constexpr (LAYOUT == 3) {
+      // values 4 F .. 4 F + 3 = 64-byte chunk c = F / 16, granule t = (F / 4) % 4, word j = F % 4 of a weight row:
+      // k step 4 c + j, lane t -> 8 bytes at (k step) * 32 + t * 8, in the order (0, 1, 2, 3)
+      const int c = F >> 4, tt = (F >> 2) & 3, jj = F & 3;
+      const __half2 h01 = __halves2half2(__low2half(h02), __low2half(h13)), h23 = __halves2half2(__high2half(h02), __high2half(h13));
+      *reinterpret_cast<uint2 *>(dst + (4 * c + jj) * 32 + tt * 8) = make_uint2(h2u(h01), h2u(h23));
+    } else if constexpr (LAYOUT == 2) {
       // values 4 F .. 4 F + 3 = k step F / 4, j = F % 4, t = 0 .. 3: four 2-byte stores, 8 bytes apart
       __half *o = reinterpret_cast<__half *>(dst) + (F >> 2) * 16 + (F & 3);
       o[0] = __low2half(h02), o[4] = __low2half(h13), o[8] = __high2half(h02), o[12] = __high2half(h13);
@@ -153,10 +161,11 @@ __device__ __forceinline__ void st_release(unsigned int *p, unsigned int v) {
 // The ring of staged activations: XS buffers, each with a `full` mbarrier (one arrival + the copy's bytes) and an
 // `empty` mbarrier (one arrival per warp).  Thread 0 is the producer; it refills a buffer as soon as all warps have
 // handed it back, looking at the barrier without blocking except when its own warp needs the block.
-template <int NG>
+template <int NG, int XS_CAP = 4>
 struct XFeed {
   static constexpr int NT = 8 * NG, XBUF = NT * TOK_PITCH;
-  static constexpr int XS = NG <= 2 ? 4 : NG == 4 ? 3 : 2;
+  static constexpr int XS_WANT = NG <= 2 ? 4 : NG == 4 ? 3 : 2;
+  static constexpr int XS = XS_WANT < XS_CAP ? XS_WANT : XS_CAP;  // a format with large weight tiles caps the ring: two CTAs must fit an SM
   static constexpr int BYTES = XS * XBUF + 128;
   uint32_t buf0, full0, empty0;
   const uint8_t *xs;
@@ -292,7 +301,7 @@ __device__ __forceinline__ void fix_up(const Run &run, int grp, float *parts, in
 // is a second small contraction over the eight sub-blocks: A' = -dmin * m as f16 hi + lo, B' = the sub-block
 // sums of x as f16 hi (both k halves), then A' = hi against the lo half of the sums.
 struct Q4Fmt {
-  static constexpr int S = 3, TILE = ROWS * 144, BLOCK = 144;
+  static constexpr int S = 3, TILE = ROWS * 144, BLOCK = 144, XS_CAP = 4;
   uint32_t soff[5], ld_off, hdr_sh;
   bool hdr_hi;
   __device__ __forceinline__ void setup(int lane, uint32_t row_bytes) {
@@ -392,7 +401,7 @@ __device__ __forceinline__ uint32_t lds32s(uint32_t addr) {  // word at a 2-byte
 }
 
 struct Q6Fmt {
-  static constexpr int S = 2, PITCH = 240, TILE = ROWS * PITCH, BLOCK = 210;
+  static constexpr int S = 2, PITCH = 240, TILE = ROWS * PITCH, BLOCK = 210, XS_CAP = 4;
   uint32_t row_bytes, c_rsub, c_piece;
   __device__ __forceinline__ void setup(int lane, uint32_t row_bytes_) { row_bytes = row_bytes_, c_rsub = lane >> 4, c_piece = lane & 15; }
   // tile0 = first byte of the tile's first row; the copy never reads past w_end (the last rows of a matrix)
@@ -488,7 +497,7 @@ struct Q6Fmt {
 // by the group's scale (HMUL2): w = f16((q - z) * s), one rounding.  The tile lies at a 144-byte pitch so that the eight
 // rows of a load fall into distinct banks.
 struct Int4Fmt {
-  static constexpr int S = 3, PITCH = 144, TILE = ROWS * PITCH, BLOCK = 128;
+  static constexpr int S = 3, PITCH = 144, TILE = ROWS * PITCH, BLOCK = 128, XS_CAP = 4;
   uint32_t row_bytes;
   __device__ __forceinline__ void setup(int, uint32_t row_bytes_) { row_bytes = row_bytes_; }
   __device__ __forceinline__ void issue(uint32_t dst, const uint8_t *tile0, uint32_t blk, int lane, const uint8_t *) const {
@@ -532,8 +541,63 @@ struct Int4Fmt {
   }
 };
 
+// ------------------------------------------------------------------------------------ block-scaled FP8 (e4m3), 128 x 128 blocks
+// A row's 256-k block is 256 bytes.  Lane (g, t) loads granule t of each 64-byte chunk (one 16-byte load per row and
+// chunk); word j of it is the lane's four values of k step 4 c + j.  e4m3 -> f16 is exact (one cvt per pair), so the
+// weights carry no rounding at all; the block scale (one per 128 k for the whole 16-row tile) multiplies the f32 partial
+// sum of its eight k steps.
+struct Fp8Fmt {
+  static constexpr int S = 2, PITCH = 272, TILE = ROWS * PITCH, BLOCK = 256, XS_CAP = 2;
+  uint32_t row_bytes;
+  __device__ __forceinline__ void setup(int, uint32_t row_bytes_) { row_bytes = row_bytes_; }
+  __device__ __forceinline__ void issue(uint32_t dst, const uint8_t *tile0, uint32_t blk, int lane, const uint8_t *) const {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {  // 256 chunks of 16 bytes: chunk c = lane + 32 i is piece c % 16 of row c / 16
+      const uint32_t c = lane + 32 * i, r = c >> 4, piece = c & 15;
+      cp_async16(dst + r * PITCH + piece * 16, tile0 + (size_t)r * row_bytes + blk * 256u + piece * 16u);
+    }
+  }
+  static __device__ __forceinline__ uint32_t cvt2(uint32_t two_codes) {
+    const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)two_codes, __NV_E4M3);
+    return (uint32_t)h.x | ((uint32_t)h.y << 16);
+  }
+  template <int NG, typename F>
+  __device__ __forceinline__ void unit(uint32_t sb, uint32_t xb, float (&acc)[NG][4], const TileAt &at, uint32_t blk, int lane, F &&slot_free) const {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t bx = xb + g * TOK_PITCH + t * 8;
+    const float sc[2] = {__ldg(at.sc + blk * 2), __ldg(at.sc + blk * 2 + 1)};  // at.sc: the tile's row of block scales
+#pragma unroll
+    for (int half = 0; half < 2; half++) {  // 128 k under one scale
+      float dq[NG][4];
+#pragma unroll
+      for (int q = 0; q < NG; q++) dq[q][0] = dq[q][1] = dq[q][2] = dq[q][3] = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < 2; cc++) {
+        const int c = 2 * half + cc;
+        const uint4 a = lds128(sb + g * PITCH + 64 * c + 16 * t), b = lds128(sb + (g + 8) * PITCH + 64 * c + 16 * t);
+        const uint32_t wa[4] = {a.x, a.y, a.z, a.w}, wb[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+          const uint32_t e0 = cvt2(wa[j] & 0xFFFFu), e1 = cvt2(wb[j] & 0xFFFFu), e2 = cvt2(wa[j] >> 16), e3 = cvt2(wb[j] >> 16);
+#pragma unroll
+          for (int q = 0; q < NG; q++) {
+            const uint2 bb = lds64(bx + q * (8 * TOK_PITCH) + (4 * c + j) * 32);
+            mma16816(dq[q], e0, e1, e2, e3, bb.x, bb.y);
+          }
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < NG; q++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[q][i] = fmaf(sc[half], dq[q][i], acc[q][i]);
+    }
+    __syncwarp();  // the slot is free again
+    slot_free();
+  }
+};
+
 template <typename Fmt, int NG>
-constexpr int nt_smem() { return CW * Fmt::S * Fmt::TILE + XFeed<NG>::BYTES; }
+constexpr int nt_smem() { return CW * Fmt::S * Fmt::TILE + XFeed<NG, Fmt::XS_CAP>::BYTES; }
 
 template <typename Fmt, int NG>
 __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint8_t *__restrict__ xs, float *__restrict__ parts,
@@ -548,7 +612,7 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint
   const int it0 = run.begin(run.c), it1 = run.begin(run.c + 1), n = it1 - it0;
   const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(dyn);
   const uint32_t ring = sbase + warp * (S * Fmt::TILE);
-  XFeed<NG> xf;
+  XFeed<NG, Fmt::XS_CAP> xf;
   xf.init(sbase + CW * S * Fmt::TILE, dyn + CW * S * Fmt::TILE, xs, it0, n, nb);
   const uint32_t row_bytes = (uint32_t)nb * Fmt::BLOCK;
   Fmt fmt;
@@ -562,7 +626,8 @@ __global__ void __launch_bounds__(THREADS, NG <= 4 ? 2 : 1) nt_kernel(const uint
     if (a.live) resolve(ma, tile, a.wj, a.r0);
     a.tile0 = ma.w[a.wj] + (size_t)a.r0 * row_bytes;
     a.w_end = ma.w[a.wj] + (size_t)ma.n[a.wj] * row_bytes;
-    a.sc = ma.scales[a.wj] ? ma.scales[a.wj] + (size_t)a.r0 * (K >> 7) : nullptr;
+    // 4-bit: one scale row per weight row; block-scaled FP8 (no zero points): one per 128 weight rows
+    a.sc = ma.scales[a.wj] ? ma.scales[a.wj] + (size_t)(ma.zeros[a.wj] ? a.r0 : a.r0 >> 7) * (K >> 7) : nullptr;
     a.zp = ma.zeros[a.wj] ? ma.zeros[a.wj] + (size_t)a.r0 * (K >> 7) : nullptr;
     return a;
   };
@@ -677,7 +742,7 @@ int launch_by_ng(int ng, const uint8_t *xs, float *parts, const NtArgs &ma, int 
 
 int g_nt_min_m = 9, g_nt_max_m = 64;  // LIGHT_B200_NT_MIN_M / _MAX_M (tuning knobs)
 
-// the pre-pass: layout 0 (natural, Q6_K), 1 (sub-block pairs, Q4_K) or 2 (4-bit code words); x f32 or bf16
+// the pre-pass: layout 0 (natural, Q6_K), 1 (sub-block pairs, Q4_K), 2 (4-bit code words) or 3 (FP8 granules); x f32 or bf16
 int stage_x(int layout, const void *x, int x_dtype, void *ws, int M, int NT, int K, cudaStream_t st) {
   const int recs = (K >> 8) * NT;
   cudaLaunchConfig_t cfg = {};
@@ -696,11 +761,13 @@ int stage_x(int layout, const void *x, int x_dtype, void *ws, int M, int NT, int
   if (x_dtype == LB200_F32)
     e = layout == 0   ? cudaLaunchKernelEx(&cfg, x_stage_kernel<0, float>, xf, dst, M, NT, K)
         : layout == 1 ? cudaLaunchKernelEx(&cfg, x_stage_kernel<1, float>, xf, dst, M, NT, K)
-                      : cudaLaunchKernelEx(&cfg, x_stage_kernel<2, float>, xf, dst, M, NT, K);
+        : layout == 2 ? cudaLaunchKernelEx(&cfg, x_stage_kernel<2, float>, xf, dst, M, NT, K)
+                      : cudaLaunchKernelEx(&cfg, x_stage_kernel<3, float>, xf, dst, M, NT, K);
   else
     e = layout == 0   ? cudaLaunchKernelEx(&cfg, x_stage_kernel<0, __nv_bfloat16>, xb, dst, M, NT, K)
         : layout == 1 ? cudaLaunchKernelEx(&cfg, x_stage_kernel<1, __nv_bfloat16>, xb, dst, M, NT, K)
-                      : cudaLaunchKernelEx(&cfg, x_stage_kernel<2, __nv_bfloat16>, xb, dst, M, NT, K);
+        : layout == 2 ? cudaLaunchKernelEx(&cfg, x_stage_kernel<2, __nv_bfloat16>, xb, dst, M, NT, K)
+                      : cudaLaunchKernelEx(&cfg, x_stage_kernel<3, __nv_bfloat16>, xb, dst, M, NT, K);
   if (e != cudaSuccess) return fail((int)e, "light_b200: matmul (decode, staging): %s", cudaGetErrorString(e));
   return launched("matmul (decode, staging)");
 }
@@ -802,6 +869,33 @@ int int4_decode_nt(const void *x, const uint32_t *codes, const float *s, const f
   if (int rc = stage_x(2, x, act_dtype, ws, M, NT, K, st)) return rc;
   float *parts = reinterpret_cast<float *>((uint8_t *)ws + stage_bytes(M, K));
   const int rc = launch_by_ng<Int4Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st);
+  return rc ? rc : 1;
+}
+
+// Block-scaled FP8 (e4m3) weights (N, K) with f32 scales per 128 x 128 block, x and y BF16, 4 .. 64 rows.
+// Returns 1 if launched, 0 if the shape is not covered, else an error.
+int fp8_decode_nt(const void *x, const uint8_t *w, const float *scale, void *y, int act_dtype, int M, int N, int K, int bR, int bC, void *ws,
+                  size_t ws_bytes, cudaStream_t st) {
+  static int on = -1, min_m = 4;
+  if (on < 0) {
+    on = getenv("LIGHT_B200_NT_FP8") ? atoi(getenv("LIGHT_B200_NT_FP8")) : 1;
+    if (const char *e = getenv("LIGHT_B200_NT_FP8_MIN_M")) min_m = atoi(e);
+  }
+  if (!on || act_dtype != LB200_BF16 || bR != 128 || bC != 128 || M < min_m || M > 64 || K % 256 || N % 128 || N < ROWS || ((uintptr_t)x & 15) ||
+      ((uintptr_t)w & 15) || !ws || ((uintptr_t)ws & 127) || ws_bytes < decode_nt_ws_bytes(M, K))
+    return 0;
+  NtArgs a = {};
+  const int tiles = N / ROWS;
+  a.w[0] = w, a.out[0] = (float *)y, a.n[0] = N, a.tend[0] = tiles, a.count = 1;
+  a.out_bf16 = 1, a.scales[0] = scale, a.zeros[0] = nullptr;
+  const int ng = ng_of(M), NT = 8 * ng, nb = K >> 8;
+  const long long T = (long long)((tiles + CW - 1) / CW) * nb;
+  if (T >= (1ll << 30)) return 0;
+  int grid, run_len;
+  plan_grid(T, nb, ng, 0, grid, run_len);
+  if (int rc = stage_x(3, x, act_dtype, ws, M, NT, K, st)) return rc;
+  float *parts = reinterpret_cast<float *>((uint8_t *)ws + stage_bytes(M, K));
+  const int rc = launch_by_ng<Fp8Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st);
   return rc ? rc : 1;
 }
 

@@ -460,6 +460,8 @@ def MatMulF8Block(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, block_r
     dev = _dev(x, "MatMulF8Block")
     if M > 64 and x.dtype == torch.float32:
         ensure_workspace(dev, M * K * 2)
+    elif 4 <= M <= 64 and x.dtype == torch.bfloat16:  # token tiles over activations staged once
+        ensure_workspace(dev, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, K)))
     out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
     _lib.check(_lib.lib().light_b200_fp8_block_gemv(_ptr(x.contiguous()), _ptr(w.contiguous()),
                                                     _ptr(scale.contiguous()), _ptr(out), _ACT[x.dtype], M, N, K,
