@@ -20,6 +20,8 @@
 #include <cstdlib>
 #include <mutex>
 
+#include <vector>
+
 #include "common.cuh"
 #include "mma_sync.cuh"
 #include "row_expand.cuh"
@@ -60,7 +62,7 @@ struct Group {
 template <typename Row, bool BF16, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_constant__ CUtensorMap tmap_x,
                                                                  const typename Row::Ctx ctx, const Group grp,
-                                                                 OutT *__restrict__ out, int M, int N, int K, int bm) {
+                                                                 OutT *__restrict__ out, int M, int N, int K, int bm, int n256) {
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t sA = base, sB = base + SA * A_STAGE, sBar = sB + SB * B_STAGE;
@@ -71,7 +73,10 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
   __shared__ uint32_t tmem_base_sh;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BN;
-  int m0 = blockIdx.y * bm, m_end = M, expert = 0;  // bm = 256, or 128 when that fills the SMs better
+  // bm = 256, or 128 when that fills the SMs better; with n256 >= 0 the first n256 token tiles are 256 rows high and
+  // the rest 128 (the tail of the last wave is cut finer)
+  if (n256 >= 0) bm = (int)blockIdx.y < n256 ? 256 : 128;
+  int m0 = n256 >= 0 && (int)blockIdx.y >= n256 ? n256 * 256 + ((int)blockIdx.y - n256) * 128 : blockIdx.y * bm, m_end = M, expert = 0;
   if (grp.offsets) {
     // which (expert, tile of its rows) is this CTA's?  Tiles are numbered expert by expert.
     __shared__ int tile_info[3];
@@ -367,19 +372,59 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
   // (measured: a 128-row tile takes 0.75 of a 256-row tile)
   int bm = (!grp.offsets && waves_cost(128) < waves_cost(256)) ? 128 : 256;
   if (const char *e = getenv("LIGHT_B200_PREFILL_BM")) bm = (atoi(e) == 128 && !grp.offsets) ? 128 : atoi(e) == 256 ? 256 : bm;
+  // Mixed heights: n256 tiles of 256 rows first, 128-row tiles for the rest.  The CTAs start in grid order on the first
+  // free SM; the split with the shortest finish under that rule (a 128-row tile costs 0.75) wins over either uniform grid.
+  int n256 = -1;
+  static int mixed = -1;
+  if (mixed < 0) mixed = getenv("LIGHT_B200_PREFILL_MIXED") ? atoi(getenv("LIGHT_B200_PREFILL_MIXED")) : 1;
+  if (mixed && !grp.offsets && M > 256 && nt * ((M + 255) / 256) <= 8192) {
+    static std::mutex plan_mu;
+    static std::vector<std::pair<std::pair<int, long long>, int>> plans;  // (M, nt) -> n256, found once per shape
+    std::lock_guard<std::mutex> lk(plan_mu);
+    bool known = false;
+    for (const auto &p : plans)
+      if (p.first.first == M && p.first.second == nt) n256 = p.second, known = true;
+    if (!known) {
+      const int sms = sm_count(), big_max = M / 256;
+      auto finish = [&](int nb256) {
+        const int small = (M - nb256 * 256 + 127) / 128;
+        std::vector<double> sm(sms, 0.0);
+        double end = 0;
+        auto place = [&](long long count, double cost) {
+          for (long long i = 0; i < count; i++) {
+            int best = 0;
+            for (int j = 1; j < sms; j++)
+              if (sm[j] < sm[best]) best = j;
+            sm[best] += cost;
+            if (sm[best] > end) end = sm[best];
+          }
+        };
+        place((long long)nb256 * nt, 1.0);
+        place((long long)small * nt, 0.75);
+        return end;
+      };
+      double best = bm == 256 ? waves_cost(256) : waves_cost(128);
+      for (int c = big_max; c >= 0 && c >= big_max - 4; c--) {
+        const double f = finish(c);
+        if (f < best - 1e-9) best = f, n256 = c;
+      }
+      if (plans.size() < 256) plans.push_back({{M, nt}, n256});
+    }
+  }
   // Few tokens and few weight-row tiles (fewer 128-row tiles than SMs): split K over a cluster of up to 8 CTAs so
   // that every SM has one, the smallest power of two that does
   int ks = 1;
   if (!grp.offsets && K % 256 == 0 && (M <= 128 || nt * ((M + 127) / 128) < sm_count())) {
-    bm = 128;
+    bm = 128, n256 = -1;
     const int nblk = K >> 8;
     const long long ctas = nt * ((M + 127) / 128);
     while (ks < 8 && ks * 2 <= nblk && ctas * ks < sm_count()) ks *= 2;
   }
   // grouped: at most ceil(M / bm) + E tiles (every expert can end with one partial tile)
   dim3 grid((unsigned)nt, (M + bm - 1) / bm + (grp.offsets ? grp.E : 0), (unsigned)ks);
+  if (n256 >= 0) grid.y = (unsigned)(n256 + (M - n256 * 256 + 127) / 128);
   if (ks == 1) {
-    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, bm);
+    kern<<<grid, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, bm, n256);
   } else {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -391,7 +436,7 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
     attr[0].val.clusterDim.x = 1, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = (unsigned)ks;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm, ctx, grp, out, M, N, K, bm);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm, ctx, grp, out, M, N, K, bm, n256);
     if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
   }
   return launched("prefill (tcgen05)");
