@@ -828,7 +828,13 @@ def main():
         "clocks": clk.summary(),
     }
     if world == 1 and not args.no_extras:
-        line["extras"] = extras(chain, device, args)
+        line["extras"] = ex = extras(chain, device, args)
+        # the side measurements a reader looks for first, lifted out of `extras` (same numbers)
+        line["also_measured"] = {
+            "batched_decode_tok_s": {k: round(v["tok_s"], 1) for k, v in ex["decode_tokens_per_s"].items()},
+            "whole_decode_step_kv1024_tok_s": round(ex["decode_m1_full_step_kv1024"]["tok_s"], 1) if "decode_m1_full_step_kv1024" in ex else None,
+            "prefill_m2048_frac_of_sustained_bf16": ex["prefill_m2048"].get("all_four", {}).get("frac_of_measured_sustained_bf16"),
+        }
     if world > 1 and chain.peer is not None:
         # correctness of the exchange that was just timed: rank 0's logits against the NCCL-gathered chain
         graph.replay()
