@@ -541,6 +541,61 @@ struct Int4Fmt {
   }
 };
 
+// ------------------------------------------------------------------------------------ Q8_0
+// Block (34 B): [f16 d | 32 int8].  A row's run of 256 k is eight blocks = 272 bytes = 17 granules (rows are whole
+// granules when K % 256 == 0).  Lane (g, t) takes the word at 4t of each half block: XOR 0x80 makes the bytes unsigned,
+// PRMT puts two of them into f16 1152 + q, HADD2 takes the 1152 off exactly and HMUL2 multiplies by the block's d (an
+// f16 itself): one rounding per weight.  Words of even blocks lie 2 bytes off a word boundary and are funnel-shifted.
+struct Q80Fmt {
+  static constexpr int S = 2, PITCH = 272, TILE = ROWS * PITCH, BLOCK = 272, XS_CAP = 2;
+  uint32_t row_bytes;
+  __device__ __forceinline__ void setup(int, uint32_t row_bytes_) { row_bytes = row_bytes_; }
+  __device__ __forceinline__ void issue(uint32_t dst, const uint8_t *tile0, uint32_t blk, int lane, const uint8_t *) const {
+#pragma unroll
+    for (int i = 0; i < 9; i++) {  // 272 chunks of 16 bytes: chunk c = lane + 32 i is piece c % 17 of row c / 17
+      const uint32_t c = lane + 32 * i, r = (c * 241u) >> 12, piece = c - 17u * r;
+      if (c < 272u) cp_async16(dst + r * PITCH + piece * 16, tile0 + (size_t)r * row_bytes + blk * 272u + piece * 16u);
+    }
+  }
+  template <int NG, typename F>
+  __device__ __forceinline__ void unit(uint32_t sb, uint32_t xb, float (&acc)[NG][4], const TileAt &, uint32_t, int lane, F &&slot_free) const {
+    const int g = lane >> 2, t = lane & 3;
+    const uint32_t bx = xb + g * TOK_PITCH + t * 8;
+    const __half2 off = __float2half2_rn(-1152.f);
+#pragma unroll
+    for (int j = 0; j < 8; j++) {  // block j: k steps 2j and 2j + 1
+      __half2 d2[2];
+      uint32_t w[2][2];  // [row g | g + 8][half of the block]
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        const uint32_t bk = sb + (g + 8 * r) * PITCH + 34 * j;
+        d2[r] = __half2half2(__ushort_as_half((unsigned short)lds16u(bk)));
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+          const uint32_t a = bk + 2 + 16 * hf + 4 * t;
+          w[r][hf] = ((j & 1) ? lds32(a) : __funnelshift_r(lds32(a - 2), lds32(a + 2), 16)) ^ 0x80808080u;
+        }
+      }
+#pragma unroll
+      for (int hf = 0; hf < 2; hf++) {
+        uint32_t a[4];
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+          a[r] = h2u(__hmul2(__hadd2(u2h(__byte_perm(w[r][hf], 0x64646464u, 0x4240)), off), d2[r]));
+          a[2 + r] = h2u(__hmul2(__hadd2(u2h(__byte_perm(w[r][hf], 0x64646464u, 0x4341)), off), d2[r]));
+        }
+#pragma unroll
+        for (int q = 0; q < NG; q++) {
+          const uint2 b = lds64(bx + q * (8 * TOK_PITCH) + (2 * j + hf) * 32);
+          mma16816(acc[q], a[0], a[1], a[2], a[3], b.x, b.y);
+        }
+      }
+    }
+    __syncwarp();  // the slot is free again
+    slot_free();
+  }
+};
+
 // ------------------------------------------------------------------------------------ block-scaled FP8 (e4m3), 128 x 128 blocks
 // A row's 256-k block is 256 bytes.  Lane (g, t) loads granule t of each 64-byte chunk (one 16-byte load per row and
 // chunk); word j of it is the lane's four values of k step 4 c + j.  e4m3 -> f16 is exact (one cvt per pair), so the
@@ -815,7 +870,8 @@ int gguf_decode_nt(int type, const float *x, const void *const *w, float *const 
     if (const char *e = getenv("LIGHT_B200_NT_GRID")) env_grid = atoi(e);
     knob = true;
   }
-  if ((type != LB200_Q4_K && type != LB200_Q6_K) || M < g_nt_min_m || M > g_nt_max_m || M > 64 || M < 1 || K % 256 || count < 1 || count > 4 ||
+  const bool q8 = type == LB200_Q8_0;
+  if ((type != LB200_Q4_K && type != LB200_Q6_K && !q8) || M < (q8 && g_nt_min_m > 4 ? 4 : g_nt_min_m) || M > g_nt_max_m || M > 64 || M < 1 || K % 256 || count < 1 || count > 4 ||
       ((uintptr_t)x & 15) || !ws || ((uintptr_t)ws & 127) || ws_bytes < decode_nt_ws_bytes(M, K))
     return 0;
   const bool q6 = type == LB200_Q6_K;
@@ -834,13 +890,14 @@ int gguf_decode_nt(int type, const float *x, const void *const *w, float *const 
   if (T >= (1ll << 30)) return 0;
   // a short list (a 4096 x 4096 matrix is 512 entries) leaves each CTA a few blocks and most of the time goes into
   // starting and the split-K fix-up: up to 32 rows the cluster kernel for Q4_K is quicker there
-  if (!q6 && M <= 32 && T < 4ll * sm_count() && !env_grid) return 0;
+  if (!q6 && !q8 && M <= 32 && T < 4ll * sm_count() && !env_grid) return 0;
   int grid, run_len;
   plan_grid(T, nb, ng, env_grid, grid, run_len);
-  if (int rc = stage_x(q6 ? 0 : 1, x, LB200_F32, ws, M, NT, K, st)) return rc;
+  if (int rc = stage_x(q6 || q8 ? 0 : 1, x, LB200_F32, ws, M, NT, K, st)) return rc;
   float *parts = reinterpret_cast<float *>((uint8_t *)ws + stage_bytes(M, K));
-  const int rc = q6 ? launch_by_ng<Q6Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st)
-                    : launch_by_ng<Q4Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st);
+  const int rc = q6   ? launch_by_ng<Q6Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st)
+                 : q8 ? launch_by_ng<Q80Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st)
+                      : launch_by_ng<Q4Fmt>(ng, (const uint8_t *)ws, parts, a, tiles, M, K, grid, run_len, st);
   return rc ? rc : 1;
 }
 
