@@ -109,9 +109,11 @@ def ensure_workspace(device_index: int, nbytes: int) -> None:
     """Keeps one reusable device buffer per GPU registered with the library (the counterpart of the
     reference's per-device weight scratch, ops/fp8_block.go:105-154); grows it when a call needs more."""
     cur = _workspaces.get(device_index)
-    if cur is not None and cur.numel() >= nbytes:
+    if cur is not None and cur.numel() - 1024 >= nbytes:
         return
-    buf = torch.empty(max(nbytes, 1 << 20) + 1024, dtype=torch.uint8, device=torch.device("cuda", device_index))
+    # 64 MB to begin with: what batched decode (22 MB) and a 2048-row prefill of the widest layer need, so that the
+    # buffer is not replaced under a captured graph that holds its address
+    buf = torch.empty(max(nbytes, 64 << 20) + 1024, dtype=torch.uint8, device=torch.device("cuda", device_index))
     off = (-buf.data_ptr()) % 1024
     _lib.check(_lib.lib().light_b200_set_workspace(device_index, C.c_void_p(buf.data_ptr() + off), buf.numel() - 1024))
     _workspaces[device_index] = buf
