@@ -458,6 +458,8 @@ def extras(chain, device, args):
     batched decode at the other token counts of configs[1], and the prefill matmuls of configs[2]."""
     out = {"decode_tokens_per_s": {}, "prefill_m2048": {}}
     steps = max(5, min(20, args.steps))
+    if args.only_extra == "chain":
+        return {"decode_m1_dependent_chain_one_launch": chain_kernel_extras(chain, device, steps)}
     if chain.fused:  # the same step with one launch per linear
         c = Chain(device, 1, share=chain, fused=False)
         g = capture(c.step, device)
@@ -720,6 +722,7 @@ def main():
                     help="fused: q/k/v and gate/up of a layer as one launch each at M=1; single: one launch per linear")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the batched-decode and prefill side measurements")
+    ap.add_argument("--only-extra", default="", help="run a single side measurement (for a small profiling case): chain")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -830,7 +833,7 @@ def main():
     if world == 1 and not args.no_extras:
         line["extras"] = ex = extras(chain, device, args)
         # the side measurements a reader looks for first, lifted out of `extras` (same numbers)
-        line["also_measured"] = {
+        line["also_measured"] = None if args.only_extra else {
             "batched_decode_tok_s": {k: round(v["tok_s"], 1) for k, v in ex["decode_tokens_per_s"].items()},
             "whole_decode_step_kv1024_tok_s": round(ex["decode_m1_full_step_kv1024"]["tok_s"], 1) if "decode_m1_full_step_kv1024" in ex else None,
             "prefill_m2048_frac_of_sustained_bf16": ex["prefill_m2048"].get("all_four", {}).get("frac_of_measured_sustained_bf16"),
