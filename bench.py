@@ -664,6 +664,72 @@ def moe_extras(device, peaks):
     return res
 
 
+def moe_ep_extras(device, world, rank, barrier):
+    """configs[4] with its 256 experts sharded over the ranks (256 / world each): 4096 tokens in total, 4096 / world
+    brought by every rank, routed top-8 by the sigmoid + bias router; tokens travel to their experts' ranks by
+    all-to-all (NCCL over NVLink), run through this library's grouped block-FP8 matmuls there, travel back and are
+    summed with the routing weights (light_b200.tp.ExpertParallel).  Times are CUDA events, max over ranks."""
+    import torch.distributed as dist
+    from light_b200 import tp
+
+    E, H, I, T, topk, b = 256, 7168, 2048, 4096 // world, 8, 128
+    if E % world:
+        return {"skipped": f"256 experts do not split over {world} ranks"}
+    El = E // world
+    free = torch.tensor([torch.cuda.mem_get_info(device)[0]], device=device, dtype=torch.float64)
+    dist.all_reduce(free, op=dist.ReduceOp.MIN)
+    if float(free.item()) < El * 3 * I * H * 1.3 + (4 << 30):
+        return {"skipped": "not enough free device memory for this rank's experts"}
+    w1, s1 = synth.random_fp8_block(7401 + 10 * rank, El * 2 * I, H, b, b, device=device)
+    w2, s2 = synth.random_fp8_block(7402 + 10 * rank, El * H, I, b, b, device=device)
+    w1, s1 = w1.reshape(El, 2 * I, H), s1.reshape(El, 2 * I // b, H // b)
+    w2, s2 = w2.reshape(El, H, I), s2.reshape(El, H // b, I // b)
+    g = torch.Generator(device=device)
+    g.manual_seed(7403 + rank)
+    x = (torch.randn(T, H, generator=g, device=device) * 0.05).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=g, device=device)
+    gb = torch.Generator(device=device)
+    gb.manual_seed(7404)  # the router bias is the layer's: the same on every rank
+    bias = torch.randn(E, generator=gb, device=device) * 0.5
+    ep = tp.ExpertParallel(E)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    seen = {}
+
+    def ffn(rows, order, le):
+        seen["rows"] = rows.shape[0]
+        ev[0].record()
+        r = ops.MoERouting(None, None, order.contiguous(), le.contiguous())
+        h = ops.MoEGemmF8Block(rows, w1, s1, b, b, r, None, 1)
+        y = ops.MoEGemmF8Block(ops.MoEGateMul(h), w2, s2, b, b, r, None, 1)
+        ev[1].record()
+        return y
+
+    def layer():
+        r = ops.MoERouteSigmoid(logits, bias, topk, True)
+        seen["out"] = ep.forward(x, r.topk_ids, r.weights.reshape(T, topk), ffn, routing=r)
+
+    layer()
+    n = 5
+    ms = timed(layer, n, 2, device, barrier) / n
+    ms_ffn = ev[0].elapsed_time(ev[1])  # the last step's local matmuls
+    t = torch.tensor([ms, ms_ffn, float(seen["rows"]), -float(seen["rows"])], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    fin = torch.tensor([float(torch.isfinite(seen["out"]).all().item()), -float(ops.moe_route_status(device.index or 0))], device=device)
+    dist.all_reduce(fin, op=dist.ReduceOp.MIN)
+    ms, ms_ffn = float(t[0]), float(t[1])
+    flops = 2.0 * 4096 * topk * 3 * I * H
+    res = {"experts_per_rank": El, "tokens_total": 4096, "tokens_per_rank": T,
+           "pairs_received_per_rank_min_max": [int(-float(t[3])), int(float(t[2]))],
+           "layer_ms": ms, "tokens_per_s": 4096 / (ms * 1e-3), "layer_tflops_all_ranks": flops / (ms * 1e-3) / 1e12,
+           "local_matmuls_ms_slowest_rank": ms_ffn, "exchange_and_host_ms": ms - ms_ffn,
+           "dispatch_bytes_per_rank": T * topk * H * 2, "combine_bytes_per_rank": T * topk * H * 2,
+           "exchange": "torch.distributed.all_to_all_single (NCCL) for the rows out, the expert ids out, the results back; the split sizes of all ranks in one all-gather read once on the host; weighted slot sum as one launch",
+           "finite": bool(fin[0].item() > 0), "route_status": int(-float(fin[1]))}
+    del w1, w2, s1, s2
+    torch.cuda.empty_cache()
+    return res
+
+
 def chain_kernel_extras(chain, device, steps):
     """The M = 1 step as ONE persistent launch: the 129 operators as a device-side program with the RMS norms and the
     residual adds folded in, every operator reading the vector the one before wrote (a dependent chain, unlike the
@@ -838,6 +904,8 @@ def main():
             "whole_decode_step_kv1024_tok_s": round(ex["decode_m1_full_step_kv1024"]["tok_s"], 1) if "decode_m1_full_step_kv1024" in ex else None,
             "prefill_m2048_frac_of_sustained_bf16": ex["prefill_m2048"].get("all_four", {}).get("frac_of_measured_sustained_bf16"),
         }
+    if world > 1 and not args.no_extras:
+        line["moe_fp8_deepseek_v3_layer_expert_parallel"] = moe_ep_extras(device, world, rank, barrier)
     if world > 1 and chain.peer is not None:
         # correctness of the exchange that was just timed: rank 0's logits against the NCCL-gathered chain
         graph.replay()

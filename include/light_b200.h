@@ -393,6 +393,14 @@ LB200_API int light_b200_moe_route_topk(const float *probs, int64_t *ids, float 
 LB200_API int light_b200_moe_gate_mul(const void *h, void *out, int dtype, int64_t M, int I, int gelu, int device, void *stream);
 LB200_API int light_b200_moe_combine(const void *pair_out, void *out, int dtype, int64_t tokens, int N, int topk, int device,
                                      void *stream);
+/* The combine of a block whose expert rows arrive in another order and unweighted (experts sharded over GPUs: the rows
+ * come back from the experts' ranks in expert order; the reference has one GPU and no such step, the arithmetic is
+ * MoEGemm's weighted epilogue followed by MoECombine, ops/moe.go:121-240, kept in f32):
+ *   out f32 (tokens, N)[t] = sum over slots s, slot 0 first, of weights[t * topk + s] * rows[index[t * topk + s]]
+ * rows (n_rows, N) at dtype; index int64 per pair (NULL: pair p is row p; a value outside [0, n_rows) drops the pair);
+ * weights f32 per pair (NULL: 1).  N % 8 == 0; rows and out 16-byte aligned. */
+LB200_API int light_b200_moe_combine_weighted(const void *rows, const int64_t *index, const float *weights, float *out, int dtype,
+                                              int64_t tokens, int N, int topk, int64_t n_rows, int device, void *stream);
 
 /* INT8 weights x INT8 activations.  Registry key {matmul_w8a8, CUDA, F32} (reference ops.MatMulW8A8,
  * ops/matmul_w8a8.go:13-120): x f32 (M, K), wq int8 (N, K), ws f32 (N) -> out f32 (M, N).  The activation

@@ -588,6 +588,19 @@ int light_b200_moe_combine(const void *pair_out, void *out, int dtype, int64_t t
   return moe_combine(pair_out, out, dtype, tokens, N, topk, (cudaStream_t)stream);
 }
 
+int light_b200_moe_combine_weighted(const void *rows, const int64_t *index, const float *weights, float *out, int dtype, int64_t tokens,
+                                    int N, int topk, int64_t n_rows, int device, void *stream) {
+  if (tokens < 0 || N <= 0 || N % 8 || topk < 1 || n_rows < 0)
+    return fail(LB200_E_SHAPE, "light_b200: moe_combine_weighted: tokens=%lld N=%d topk=%d rows=%lld", (long long)tokens, N, topk, (long long)n_rows);
+  if (tokens == 0) return 0;
+  REQUIRE_PTR(out, "moe_combine_weighted");
+  if (n_rows) REQUIRE_PTR(rows, "moe_combine_weighted");
+  if (!index && n_rows < tokens * topk) return fail(LB200_E_SHAPE, "light_b200: moe_combine_weighted: no index and fewer rows than pairs");
+  if (!aligned(rows, 16) || !aligned(out, 16)) return fail(LB200_E_ALIGN, "light_b200: moe_combine_weighted: pointers not 16-byte aligned");
+  if (int rc = bind(device)) return rc;
+  return moe_combine_weighted(rows, index, weights, out, dtype, tokens, N, topk, n_rows, (cudaStream_t)stream);
+}
+
 int light_b200_moe_route_status(int device) {
   if (int rc = bind(device)) return rc;
   cudaError_t e = cudaDeviceSynchronize();

@@ -147,6 +147,8 @@ int decode_ts_status();
 int gather_columns(const void *x, const int64_t *idx, void *out, int elt, long long M, int K, cudaStream_t st);
 int moe_gate_mul(const void *h, void *out, int dtype, long long M, int I, int gelu, cudaStream_t st);
 int moe_combine(const void *pair_out, void *out, int dtype, long long tokens, int N, int topk, cudaStream_t st);
+int moe_combine_weighted(const void *rows, const int64_t *index, const float *weights, float *out, int dtype, long long tokens, int N,
+                         int topk, long long n_rows, cudaStream_t st);
 int gemv_bf16_multi(const void *x, const void *const *w, void *const *out, const int *n, int count, int K, int out_f32, cudaStream_t st);
 int gemv_bf16_gated(const void *x, const void *wg, const void *wu, void *y, int N, int K, int gelu, cudaStream_t st);
 size_t chain_program_bytes(int n_ops);

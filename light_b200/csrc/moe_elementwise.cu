@@ -70,6 +70,34 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const T *__restrict__ 
   }
 }
 
+// rows (n_rows, N) in any order, index[p] = the row of pair p (outside [0, n_rows): the pair contributes nothing),
+// weights[p] its routing weight -> out f32 (tokens, N) = sum over a token's slots, slot 0 first, accumulated in f32:
+// the receiving end of an expert-parallel combine, where the rows come back in expert order
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_weighted_kernel(const T *__restrict__ rows, const int64_t *__restrict__ index,
+                                                                   const float *__restrict__ weights, float *__restrict__ out,
+                                                                   long long tokens, int N, int topk, long long n_rows) {
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  const long long per_row = N / 8, total = tokens * per_row;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / per_row;
+    const int c = (int)(i - t * per_row) * 8;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < topk; s++) {
+      const long long p = t * topk + s, r = index ? index[p] : p;
+      if (r < 0 || r >= n_rows) continue;
+      const float w = weights ? weights[p] : 1.f;
+      const Vec8<T> v = *reinterpret_cast<const Vec8<T> *>(rows + r * (long long)N + c);
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] = fmaf((float)v.v[j], w, acc[j]);
+    }
+    float4 *o = reinterpret_cast<float4 *>(out + t * N + c);
+    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
 template <typename K, typename... Args>
 int go(K kern, long long work, cudaStream_t st, const char *what, Args... args) {
   long long blocks = (work + 255) / 256;
@@ -107,6 +135,17 @@ int moe_combine(const void *pair_out, void *out, int dtype, long long tokens, in
     case LB200_F16: return go(moe_combine_kernel<__half>, work, st, "moe_combine", (const __half *)pair_out, (__half *)out, tokens, N, topk);
   }
   return fail(LB200_E_DTYPE, "light_b200: moe_combine: element type %d", dtype);
+}
+
+int moe_combine_weighted(const void *rows, const int64_t *index, const float *weights, float *out, int dtype, long long tokens, int N,
+                         int topk, long long n_rows, cudaStream_t st) {
+  const long long work = tokens * (N / 8);
+  switch (dtype) {
+    case LB200_F32: return go(moe_combine_weighted_kernel<float>, work, st, "moe_combine_weighted", (const float *)rows, index, weights, out, tokens, N, topk, n_rows);
+    case LB200_BF16: return go(moe_combine_weighted_kernel<__nv_bfloat16>, work, st, "moe_combine_weighted", (const __nv_bfloat16 *)rows, index, weights, out, tokens, N, topk, n_rows);
+    case LB200_F16: return go(moe_combine_weighted_kernel<__half>, work, st, "moe_combine_weighted", (const __half *)rows, index, weights, out, tokens, N, topk, n_rows);
+  }
+  return fail(LB200_E_DTYPE, "light_b200: moe_combine_weighted: element type %d", dtype);
 }
 
 }  // namespace lb

@@ -656,6 +656,28 @@ def MoECombine(pair_out: torch.Tensor, topk: int) -> torch.Tensor:
     return out
 
 
+def MoECombineWeighted(rows: torch.Tensor, index: Optional[torch.Tensor], weights: Optional[torch.Tensor], tokens: int, topk: int) -> torch.Tensor:
+    """out f32 (tokens, N)[t] = sum over the token's slots, slot 0 first, of weights[t * topk + s] * rows[index[t * topk + s]]:
+    the combine of a sparse block whose expert rows arrive unweighted and in another order (experts sharded over GPUs,
+    tp.ExpertParallel); the arithmetic of MoEGemm's weighted epilogue followed by MoECombine (ops/moe.go:121-240), in f32.
+    index int64 per pair (None: pair p is row p; outside [0, rows) drops the pair), weights f32 per pair (None: 1)."""
+    if rows.dim() != 2 or rows.dtype not in _ACT or rows.shape[1] % 8:
+        raise ValueError(f"moe_combine_weighted: rows {tuple(rows.shape)} {rows.dtype}: want (R, N), N a multiple of 8, F32 / BF16 / F16")
+    M = tokens * topk
+    for name, t, dt in (("index", index, torch.int64), ("weights", weights, torch.float32)):
+        if t is not None and (t.dtype != dt or t.numel() != M or t.device != rows.device):
+            raise ValueError(f"moe_combine_weighted: {name} must be {dt} with {M} elements on {rows.device}")
+    if index is None and rows.shape[0] < M:
+        raise ValueError(f"moe_combine_weighted: {rows.shape[0]} rows for {M} pairs and no index")
+    dev = _dev(rows, "MoECombineWeighted")
+    rows = rows.contiguous()
+    out = torch.empty((tokens, rows.shape[1]), dtype=torch.float32, device=rows.device)
+    _lib.check(_lib.lib().light_b200_moe_combine_weighted(_ptr(rows), _ptr(None if index is None else index.contiguous()),
+                                                          _ptr(None if weights is None else weights.contiguous()), _ptr(out), _ACT[rows.dtype],
+                                                          tokens, rows.shape[1], topk, rows.shape[0], dev, _stream(dev)))
+    return out
+
+
 def MoEGateMul(h: torch.Tensor, gelu: bool = False) -> torch.Tensor:
     """The step between the two grouped matmuls of a sparse block (nn/moe.go:206-224): h (M, 2 I) -> act(h[:, :I]) * h[:, I:],
     act SiLU or GELU-erf, the activation rounded to the tensor's dtype before the product: one launch."""

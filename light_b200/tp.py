@@ -303,29 +303,40 @@ class ExpertParallel:
         self.E = num_experts
         self.lo, self.hi = expert_range(num_experts, self.rank, self.world)
 
-    def plan(self, topk_ids: torch.Tensor):
-        """Routing of this rank's tokens: (sorted_pairs, sorted_expts, send_counts, recv_counts)."""
+    def plan(self, topk_ids: torch.Tensor, routing=None):
+        """Routing of this rank's tokens: (sorted_pairs, sorted_expts, send_counts, recv_counts).  `routing`
+        (ops.MoERouting of the same ids, from the router) brings the expert order the router already made; the
+        counts of all ranks and the range check of all ids take one exchange and one read on the host, and a bad
+        id on any rank raises on every rank (nobody is left waiting in the next exchange)."""
         import torch.distributed as dist
 
         T, topk = topk_ids.shape
-        flat = topk_ids.reshape(T * topk).to(torch.int64)
-        if flat.numel() and (int(flat.min()) < 0 or int(flat.max()) >= self.E):
-            raise ValueError(f"ExpertParallel: expert id outside [0, {self.E})")
-        sorted_expts, sorted_pairs = torch.sort(flat, stable=True)
+        if routing is not None and routing.sorted_pairs is not None and routing.sorted_expts is not None:
+            sorted_expts, sorted_pairs = routing.sorted_expts, routing.sorted_pairs
+            if sorted_pairs.numel() != T * topk:
+                raise ValueError(f"ExpertParallel: routing holds {sorted_pairs.numel()} pairs, the ids {T * topk}")
+        else:
+            sorted_expts, sorted_pairs = torch.sort(topk_ids.reshape(T * topk).to(torch.int64), stable=True)
         offs = split_pairs_by_rank(sorted_expts, self.E, self.world)
-        send = (offs[1:] - offs[:-1]).to(torch.int64)
-        recv = torch.empty_like(send)
-        dist.all_to_all_single(recv, send, group=self.group)
-        return sorted_pairs, sorted_expts, send.tolist(), recv.tolist()
+        ends = torch.stack([sorted_expts[0], sorted_expts[-1]]) if T * topk else torch.zeros(2, dtype=torch.int64, device=topk_ids.device)
+        mine = torch.cat([(offs[1:] - offs[:-1]).to(torch.int64), ends.to(torch.int64)])
+        table = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(table, mine, group=self.group)
+        table = torch.stack(table).tolist()
+        for r, row in enumerate(table):
+            if row[self.world] < 0 or row[self.world + 1] >= self.E:
+                raise ValueError(f"ExpertParallel: expert id outside [0, {self.E}) on rank {r}")
+        return sorted_pairs, sorted_expts, table[self.rank][:self.world], [table[r][self.rank] for r in range(self.world)]
 
-    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, ffn) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, topk_ids: torch.Tensor, topk_weights: torch.Tensor, ffn, routing=None) -> torch.Tensor:
         """x (T, H) this rank's tokens, topk_ids / topk_weights (T, topk); ffn(rows (R, H), order (R,) int64,
         local_expert_of_order (R,) int64 non-decreasing) -> (R, H_out) rows in the order it was given them.
+        `routing`: the router's ops.MoERouting for these ids, when there is one (its expert order is reused).
         Returns (T, H_out) f32."""
         import torch.distributed as dist
 
         T, topk = topk_ids.shape
-        sorted_pairs, sorted_expts, send, recv = self.plan(topk_ids)
+        sorted_pairs, sorted_expts, send, recv = self.plan(topk_ids, routing)
         rows = x.index_select(0, sorted_pairs // topk).contiguous()
         R = sum(recv)
         got_rows = torch.empty(R, x.shape[1], dtype=x.dtype, device=x.device)
@@ -337,7 +348,14 @@ class ExpertParallel:
         done = ffn(got_rows, order, local_sorted)
         back = torch.empty(rows.shape[0], done.shape[1], dtype=done.dtype, device=x.device)
         dist.all_to_all_single(back, done.contiguous(), output_split_sizes=send, input_split_sizes=recv, group=self.group)
-        w = topk_weights.reshape(T * topk).float().index_select(0, sorted_pairs)
+        w = topk_weights.reshape(T * topk).float()
+        if back.is_cuda and back.shape[1] % 8 == 0 and back.dtype in (torch.float32, torch.bfloat16, torch.float16):
+            from . import ops
+
+            # row of every pair in `back`, then one launch: weight, sum over the slots in slot order, f32
+            where = torch.empty(T * topk, dtype=torch.int64, device=x.device)
+            where[sorted_pairs] = torch.arange(T * topk, dtype=torch.int64, device=x.device)
+            return ops.MoECombineWeighted(back, where, w, T, topk)
         out = torch.zeros(T, done.shape[1], dtype=torch.float32, device=x.device)
-        out.index_add_(0, sorted_pairs // topk, back.float() * w[:, None])
+        out.index_add_(0, sorted_pairs // topk, back.float() * w.index_select(0, sorted_pairs)[:, None])
         return out

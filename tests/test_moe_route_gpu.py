@@ -103,3 +103,30 @@ def test_gate_mul_and_combine(cuda, dtype):
     for s in range(1, topk):
         acc = (acc.float() + v[:, s].float()).to(dtype)
     assert torch.equal(got.cpu(), acc)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_combine_weighted(cuda, dtype):
+    """Rows in another order, unweighted: out[t] = sum over slots (slot 0 first, f32) of weight * row(index); pairs whose
+    index lies outside the rows contribute nothing; no index = pair order, no weights = 1."""
+    g = torch.Generator().manual_seed(21)
+    T, topk, N = 37, 3, 48
+    M = T * topk
+    rows = torch.randn(M + 5, N, generator=g).to(dtype)
+    index = torch.randperm(M + 5, generator=g)[:M]
+    index[4], index[50] = -1, M + 5
+    w = torch.rand(M, generator=g)
+    got = ops.MoECombineWeighted(rows.to(cuda), index.to(cuda), w.to(cuda), T, topk).cpu()
+    want = torch.zeros(T, N)
+    for t in range(T):
+        for s in range(topk):
+            p = t * topk + s
+            if 0 <= int(index[p]) < M + 5:
+                want[t] = torch.addcmul(want[t], rows[index[p]].float(), w[p])
+    assert got.dtype == torch.float32 and torch.allclose(got, want, rtol=1e-6, atol=1e-6)
+    plain = ops.MoECombineWeighted(rows.to(cuda), None, None, T, topk).cpu()
+    assert torch.allclose(plain, rows[:M].float().reshape(T, topk, N).sum(1), rtol=1e-6, atol=1e-6)
+    with pytest.raises(ValueError, match="no index"):
+        ops.MoECombineWeighted(rows[:M - 1].to(cuda), None, None, T, topk)
+    with pytest.raises(ValueError, match="index must be"):
+        ops.MoECombineWeighted(rows.to(cuda), index[:5].to(cuda), None, T, topk)
