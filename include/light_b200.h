@@ -87,7 +87,10 @@ LB200_API unsigned long long light_b200_launch_count(void);
  * on the GPU. */
 LB200_API int light_b200_set_workspace(int device, void *ptr, size_t bytes);
 
-/* The workspace size with which light_b200_matmul_q / _multi_rows take their fastest path for M rows of K. */
+/* The workspace size with which light_b200_matmul_q / _multi_rows (and the int4, block-FP8 and grouped matmuls, M
+ * then the number of activation rows or routed pairs) take their fastest path for M rows of K: above 64 rows the f16
+ * copy of x plus about 42 MB of partial tiles for the persistent tensor-core kernel; with less, those calls run the
+ * kernel that needs the copy alone. */
 LB200_API unsigned long long light_b200_matmul_q_workspace_bytes(int M, int K);
 
 /* 0 if no bounded device-side wait of the tensor-core kernels ever gave up on this device, 1 if one

@@ -153,7 +153,8 @@ int light_b200_prefill_status(int device) {
 }
 unsigned long long light_b200_matmul_q_workspace_bytes(int M, int K) {
   if (M < 1 || K <= 0) return 0;
-  const unsigned long long f16_copy = M > 1 ? (unsigned long long)M * K * 2 : 0;  // the tensor-core paths' f16 copy of x
+  unsigned long long f16_copy = M > 1 ? (unsigned long long)M * K * 2 : 0;  // the tensor-core paths' f16 copy of x
+  if (M > 64) f16_copy += prefill_sk_ws_bytes();  // and, behind it, the partial tiles of the persistent prefill kernel
   unsigned long long staged = M <= 64 ? decode_nt_ws_bytes(M, K) : 0;
   if (M <= 64 && decode_ts_ws_bytes(M, K) > staged) staged = decode_ts_ws_bytes(M, K);
   return f16_copy > staged ? f16_copy : staged;

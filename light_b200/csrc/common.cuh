@@ -132,6 +132,7 @@ int moe_route_deepseek(const float *logits, const float *bias, int64_t *ids, flo
                        int sigmoid, int norm_topk, cudaStream_t st);
 int moe_route_topk(const float *probs, int64_t *ids, float *weights, int T, int E, int topk, int normalize, cudaStream_t st);
 void *workspace_ptr(int device, size_t *bytes);
+size_t prefill_sk_ws_bytes();
 size_t decode_nt_ws_bytes(int M, int K);
 int gguf_decode_nt(int type, const float *x, const void *const *w, float *const *out, const int *n, int count, int M, int K, void *ws,
                    size_t ws_bytes, cudaStream_t st);

@@ -292,6 +292,370 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
   if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ---- the same tile as a persistent kernel over an even split of ALL k-steps (stream-K).
+// A grid of equal tiles leaves the last wave of the SMs partly empty (192 tiles on 148 SMs run as two rounds), and a
+// grouped launch has tiles of unequal height.  Here the work is the list of (tile, 256-element K block) pairs in tile
+// order, cut into gridDim.x runs of equal length, one CTA per SM and per run.  A run is a tail of one tile, whole
+// tiles, and a head of one tile; each piece ("segment") runs through the same TMA / expander / MMA pipeline, the rings
+// carry on from one segment to the next, and the accumulator is handed over through one more barrier (d_empty).
+//   * a segment that covers its tile stores it;
+//   * a segment that does not start at k = 0 writes its 256 x 256 f32 partial tile to this CTA's slot of the
+//     workspace and raises the slot's flag: it is the FIRST thing its CTA does, and it waits for nobody;
+//   * the segment that starts a tile (the LAST of its CTA's run) owns it: it adds the partials of the CTAs after it, in
+//     run order (a fixed order of summation), and stores.  The wait is bounded (the status word is set when it runs
+//     out), and what it waits for was written at the start of the other runs, so it is there long before.
+constexpr int SK_PART_FLOATS = 2 * 4 * 32 * 256;  // one partial tile: (token half, 32-column chunk, column, thread)
+constexpr int SK_MAX_E = 1024;                    // experts whose tile counts fit the shared prefix table
+constexpr size_t SK_FLAG_BYTES = 4096;
+
+struct SkTile {
+  int n0, m0, m_end, expert;
+  bool two;
+};
+
+__device__ __forceinline__ bool sk_wait_flag(const unsigned *flag, unsigned want, volatile int *abort) {
+  const unsigned long long t0 = global_ns();
+  for (uint32_t i = 1;; i++) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];\n" : "=r"(v) : "l"(flag) : "memory");
+    if (v == want) return true;
+    if ((i & 15u) == 0) {
+      if (*abort) return false;
+      if (global_ns() - t0 > 200000000ull) break;
+      __nanosleep(128);
+    }
+  }
+  *abort = 1;
+  return false;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void sk_store32(uint32_t (&v)[32], OutT *__restrict__ out, long long m, int N, int nc, float wgt, bool weighted) {
+  if (weighted) {
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
+  }
+  OutT *o = out + (size_t)m * N + nc;
+  if (nc + 32 <= N && (N & 7) == 0) {
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        reinterpret_cast<float4 *>(o)[i] =
+            make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+        reinterpret_cast<uint4 *>(o)[i] = make_uint4(pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                                                     pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                                                     pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                                                     pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+      if (nc + i < N) st_act(o, i, __uint_as_float(v[i]));
+  }
+}
+
+template <typename Row, bool BF16, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const typename Row::Ctx ctx,
+                                                               const Group grp, OutT *__restrict__ out, int M, int N, int K,
+                                                               float *__restrict__ parts, unsigned *__restrict__ flags) {
+  extern __shared__ unsigned char smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sA = base, sB = base + SA * A_STAGE, sBar = sB + SB * B_STAGE;
+  const uint32_t a_full = sBar, a_empty = sBar + 8 * SA, b_full = sBar + 16 * SA, b_empty = b_full + 8 * SB, d_full = b_empty + 8 * SB,
+                 d_empty = d_full + 8, tmem_slot = d_empty + 8;
+  __shared__ int abort_flag;
+  __shared__ uint32_t tmem_base_sh;
+  __shared__ int pre[SK_MAX_E + 1];  // grouped: token tiles before expert e
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ntx = (N + BN - 1) / BN, nb = K >> 8;
+  int nty = (M + BM - 1) / BM;
+  if (grp.offsets) {
+    for (int e = threadIdx.x; e < grp.E; e += THREADS) pre[e + 1] = (grp.offsets[e + 1] - grp.offsets[e] + BM - 1) / BM;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      pre[0] = 0;
+      for (int e = 0; e < grp.E; e++) pre[e + 1] += pre[e];
+    }
+    __syncthreads();
+    nty = pre[grp.E];
+  }
+  const long long U = (long long)ntx * nty * nb;
+  const int G = gridDim.x, cta = blockIdx.x;
+  auto run_start = [&](int j) { return U * j / G; };
+  const long long pos0 = run_start(cta), pos1 = run_start(cta + 1);
+  auto tile_of = [&](long long t) {
+    SkTile T;
+    const int ty = (int)(t / ntx);
+    T.n0 = (int)(t - (long long)ty * ntx) * BN, T.expert = 0, T.m0 = ty * BM, T.m_end = M;
+    if (grp.offsets) {
+      int lo = 0, hi = grp.E - 1;  // the expert with pre[e] <= ty < pre[e + 1]
+      while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (pre[mid + 1] <= ty) lo = mid + 1;
+        else hi = mid;
+      }
+      T.expert = lo, T.m0 = grp.offsets[lo] + (ty - pre[lo]) * BM, T.m_end = grp.offsets[lo + 1];
+    }
+    T.two = T.m0 + 128 < T.m_end;
+    return T;
+  };
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int i = 0; i < SA; i++) mbar_init(a_full + 8 * i, 1), mbar_init(a_empty + 8 * i, 1);
+    for (int i = 0; i < SB; i++) mbar_init(b_full + 8 * i, NUM_DEQ_WARPS), mbar_init(b_empty + 8 * i, 1);
+    mbar_init(d_full, 1);
+    mbar_init(d_empty, NUM_DEQ_WARPS);
+    fence_barrier_init();
+  }
+  if (warp == MMA_WARP) {
+    tmem_alloc(tmem_slot, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (threadIdx.x == 0) {
+    uint32_t t;
+    asm volatile("ld.shared.u32 %0, [%1];\n" : "=r"(t) : "r"(tmem_slot));
+    tmem_base_sh = t;
+  }
+  __syncthreads();
+  const uint32_t tmem_base = tmem_base_sh;
+  volatile int *abort = &abort_flag;
+
+  if (warp == TMA_WARP) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_x);
+      int it = 0;  // k-steps issued over all segments
+      for (long long pos = pos0; pos < pos1 && !*abort;) {
+        const long long t = pos / nb;
+        const int b0 = (int)(pos - t * nb), b1 = (int)min((long long)nb, b0 + (pos1 - pos));
+        const SkTile T = tile_of(t);
+        for (int kb = b0 * 4; kb < b1 * 4; kb++, it++) {
+          const int s = it % SA;
+          if (it >= SA && !mbar_wait(a_empty + 8 * s, ((it / SA) - 1) & 1, abort)) break;
+          mbar_arrive_expect_tx(a_full + 8 * s, T.two ? A_STAGE : A_STAGE / 2);
+          tma_load_2d(sA + s * A_STAGE, &tmap_x, a_full + 8 * s, kb * BK, T.m0);
+          if (T.two) tma_load_2d(sA + s * A_STAGE + A_STAGE / 2, &tmap_x, a_full + 8 * s, kb * BK, T.m0 + 128);
+        }
+        pos += b1 - b0;
+      }
+      if (*abort)  // give the loads still in flight a bounded time to land before the CTA retires
+        for (int k = it > SA ? it - SA : 0; k < it; k++)
+          for (int i = 0; i < (1 << 14) && !mbar_try_wait(a_full + 8 * (k % SA), (k / SA) & 1); i++) {
+          }
+    }
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_f16(128, BN, BF16);
+      int it = 0, seg = 0;
+      bool ok = true;
+      for (long long pos = pos0; pos < pos1 && ok; seg++) {
+        const long long t = pos / nb;
+        const int b0 = (int)(pos - t * nb), b1 = (int)min((long long)nb, b0 + (pos1 - pos));
+        const SkTile T = tile_of(t);
+        // the accumulators of the segment before must have been read out
+        if (seg > 0 && !mbar_wait(d_empty, (seg - 1) & 1, abort)) break;
+        tc_fence_after();
+        for (int kb = 0; kb < (b1 - b0) * 4; kb++, it++) {
+          const int sa = it % SA, sb = it % SB;
+          if (!mbar_wait(a_full + 8 * sa, (it / SA) & 1, abort) || !mbar_wait(b_full + 8 * sb, (it / SB) & 1, abort)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+#pragma unroll
+          for (int k4 = 0; k4 < BK / 16; k4++) {
+            const uint64_t bd = smem_desc_sw128(sB + sb * B_STAGE + k4 * 32);
+            const uint64_t a0 = smem_desc_sw128(sA + sa * A_STAGE + k4 * 32);
+            const uint64_t a1 = smem_desc_sw128(sA + sa * A_STAGE + A_STAGE / 2 + k4 * 32);
+            const uint32_t acc = (kb | k4) ? 1u : 0u;
+            mma_f16(tmem_base, a0, bd, idesc, acc);
+            if (T.two) mma_f16(tmem_base + 256, a1, bd, idesc, acc);
+          }
+          mma_commit(a_empty + 8 * sa);
+          mma_commit(b_empty + 8 * sb);
+        }
+        if (ok) mma_commit(d_full);
+        pos += b1 - b0;
+      }
+    }
+  } else {
+    // ---- weight expansion (thread r owns row n0 + r of the segment's tile), then the segment's epilogue
+    const int r = threadIdx.x, quad = warp & 3, chalf = warp >> 2;
+    int it = 0, seg = 0;
+    bool ok = true;
+    Row cur;
+    for (long long pos = pos0; pos < pos1 && ok; seg++) {
+      const long long t = pos / nb;
+      const int b0 = (int)(pos - t * nb), b1 = (int)min((long long)nb, b0 + (pos1 - pos));
+      const SkTile T = tile_of(t);
+      const int kb0 = b0 * 4, u0 = kb0 / Row::STEPS, units = b1 * 4 / Row::STEPS;
+      cur.init(ctx, T.expert, min(T.n0 + r, N - 1), N, K);
+      cur.load(u0);
+      for (int u = u0; u < units && ok; u++) {
+        Row nxt = cur;
+        if (u + 1 < units) nxt.load(u + 1);
+#pragma unroll
+        for (int j = 0; j < Row::STEPS; j++, it++) {
+          const int s = it % SB;
+          if (it >= SB) {  // lane 0 waits for the stage to be free, the warp follows its verdict
+            int got = 1;
+            if (lane == 0) got = mbar_wait(b_empty + 8 * s, ((it / SB) - 1) & 1, abort);
+            if (!__shfl_sync(0xffffffffu, got, 0)) {
+              ok = false;
+              break;
+            }
+          }
+          cur.template step<BF16>(j, sB + s * B_STAGE, r);
+          fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(b_full + 8 * s);
+        }
+        cur = nxt;
+      }
+      pos += b1 - b0;
+      if (pos < pos1 && ok) {  // the next segment's first block of this thread's row, on its way to L2 during the epilogue
+        const SkTile Tn = tile_of(pos / nb);
+        Row nr;
+        nr.init(ctx, Tn.expert, min(Tn.n0 + r, N - 1), N, K);
+        nr.prefetch(0);
+      }
+      int done = 0;
+      if (ok && lane == 0) done = (int)mbar_wait(d_full, seg & 1, abort);
+      done = __shfl_sync(0xffffffffu, done, 0);
+      if (!done) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const bool owner = b0 == 0, whole = owner && b1 == nb;
+      const int nch = T.two ? 8 : 4;  // 32-column chunks of this warp's part of the accumulators: (token half, chunk)
+      auto chunk_addr = [&](int ch) { return tmem_base + ((uint32_t)(quad * 32) << 16) + (ch >> 2) * 256 + chalf * 128 + (ch & 3) * 32; };
+      uint32_t va[32], vb[32];
+      if (!owner) {
+        // a tail (or a middle) of a tile another CTA owns: the partial sums to this CTA's slot, then the flag
+        float *mine = parts + (size_t)cta * SK_PART_FLOATS + threadIdx.x;
+        auto put = [&](const uint32_t (&v)[32], int ch) {
+#pragma unroll
+          for (int i = 0; i < 32; i++) mine[(ch * 32 + i) * 256] = __uint_as_float(v[i]);
+        };
+        tmem_ld32(chunk_addr(0), va);
+#pragma unroll 1
+        for (int ch = 0; ch < nch; ch += 2) {  // (the next chunk leaves tensor memory while this one is stored)
+          tmem_ld_wait();
+          tmem_ld32(chunk_addr(ch + 1), vb);
+          put(va, ch);
+          tmem_ld_wait();
+          if (ch + 2 < nch) tmem_ld32(chunk_addr(ch + 2), va);
+          put(vb, ch + 1);
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 256;\n" ::: "memory");
+        if (threadIdx.x == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;\n" ::"l"(flags + cta), "r"(1u) : "memory");
+      } else {
+        // the CTAs that hold the rest of this tile's k range, in run order
+        int jlast = cta;
+        if (!whole) {
+          const long long tile_end = (t + 1) * nb;
+          while (jlast + 1 < G && run_start(jlast + 1) < tile_end) jlast++;
+          for (int j = cta + 1; j <= jlast; j++)
+            if (run_start(j + 1) > run_start(j) && !sk_wait_flag(flags + j, 1u, abort)) ok = false;
+        }
+        // this thread's token row in either half: where it goes and with what weight
+        long long mrow[2];
+        float wrow[2];
+        bool lrow[2];
+#pragma unroll
+        for (int a = 0; a < 2; a++) {
+          const int mi = T.m0 + a * 128 + quad * 32 + lane;  // row of the A operand
+          mrow[a] = mi, wrow[a] = 1.f, lrow[a] = mi < T.m_end && (a == 0 || T.two);
+          if (grp.offsets && lrow[a]) {
+            mrow[a] = grp.pairs[mi];
+            lrow[a] = mrow[a] >= 0 && mrow[a] < grp.size_m;
+            if (lrow[a] && grp.topkw) wrow[a] = grp.topkw[mrow[a]];
+          }
+        }
+        auto put = [&](uint32_t (&v)[32], int ch) {
+          const int a = ch >> 2;
+          const long long m = a ? mrow[1] : mrow[0];
+          const float wgt = a ? wrow[1] : wrow[0];
+          const bool live = a ? lrow[1] : lrow[0];
+          if (live && ok) {
+            for (int j = cta + 1; j <= jlast; j++) {
+              if (run_start(j + 1) == run_start(j)) continue;  // (an empty run wrote nothing)
+              const float *theirs = parts + (size_t)j * SK_PART_FLOATS + threadIdx.x + ch * 32 * 256;
+#pragma unroll
+              for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(theirs + i * 256));
+            }
+          }
+          const int nc = T.n0 + chalf * 128 + (ch & 3) * 32;
+          if (nc + 32 <= N && (N & 7) == 0) {
+            // Through shared memory, so that a store instruction writes whole 128-byte lines: the thread holds 32
+            // columns of ONE token row, and rows are N elements apart.  The staging area is the part of weight stage 0
+            // that this warp alone writes as an expander (its 32 rows of 128 bytes): the stage's last MMA has completed
+            // and the warp expands again only after its epilogue.  16-byte chunks are XOR-swizzled by the row.
+            constexpr int ROWB = 32 * (int)sizeof(OutT), LPR = ROWB / 16, RPI = 32 / LPR;
+            auto sw = [](int row) { return sizeof(OutT) == 4 ? (row & 7) : ((row >> 1) & 3); };
+            const uint32_t mine = sB + (uint32_t)warp * 4096;
+            if (grp.topkw) {
+#pragma unroll
+              for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
+            }
+            if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+              for (int i = 0; i < 8; i++)
+                st_chunk(mine + lane * ROWB + 16 * (i ^ sw(lane)), make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+            } else {
+#pragma unroll
+              for (int i = 0; i < 4; i++)
+                st_chunk(mine + lane * ROWB + 16 * (i ^ sw(lane)),
+                         make_uint4(pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                                    pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                                    pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                                    pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]))));
+            }
+            __syncwarp();
+#pragma unroll
+            for (int g = 0; g < 32 / RPI; g++) {
+              const int row = g * RPI + lane / LPR, q = lane % LPR;
+              const long long mr = __shfl_sync(0xffffffffu, m, row);
+              const int lr = __shfl_sync(0xffffffffu, (int)live, row);
+              const uint4 w = lds128(mine + row * ROWB + 16 * (q ^ sw(row)));
+              if (lr) *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(out + (size_t)mr * N + nc) + 16 * q) = w;
+            }
+            __syncwarp();
+          } else if (live) {
+            sk_store32<OutT>(v, out, m, N, nc, wgt, grp.topkw != nullptr);
+          }
+        };
+        tmem_ld32(chunk_addr(0), va);
+#pragma unroll 1
+        for (int ch = 0; ch < nch; ch += 2) {
+          tmem_ld_wait();
+          tmem_ld32(chunk_addr(ch + 1), vb);
+          put(va, ch);
+          tmem_ld_wait();
+          if (ch + 2 < nch) tmem_ld32(chunk_addr(ch + 2), va);
+          put(vb, ch + 1);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_empty);
+    }
+  }
+  __syncwarp();
+  if (abort_flag && threadIdx.x == 0) g_prefill_status = 1;
+  tc_fence_before();
+  __syncthreads();
+  if (warp == MMA_WARP) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 // x f32 (M, K) -> f16, clamped to the f16 range so that an outlier cannot become an infinity.
 // PERM: every four consecutive k are stored in the order 0, 2, 1, 3 (what a KPERM row expander pairs them with).
 template <bool PERM>
@@ -355,7 +719,32 @@ int make_x_map(CUtensorMap *tm, const void *x, int act_dtype, int M, int K, void
 
 template <typename Row, bool BF16, typename OutT>
 int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp, OutT *out, int M, int N, int K,
-           cudaStream_t st) {
+           cudaStream_t st, void *sk = nullptr, size_t sk_bytes = 0) {
+  // The persistent stream-K kernel when the workspace has room for its partial tiles and the split pays: each CTA needs
+  // a few K blocks to spread the cost of its two extra epilogues over (measured: five), and a grid of whole 256-token tiles
+  // that fills between three quarters and all of the SMs in one wave is already even.  A grouped launch always takes it (its
+  // tiles are uneven by nature).  LIGHT_B200_PREFILL_SK = 0: never, 2: whenever possible.
+  static int use_sk = -1;
+  if (use_sk < 0) use_sk = getenv("LIGHT_B200_PREFILL_SK") ? atoi(getenv("LIGHT_B200_PREFILL_SK")) : 1;
+  if (use_sk && sk && K % 256 == 0 && (!grp.offsets || grp.E <= SK_MAX_E)) {
+    long long G = sm_count();
+    bool pays = true;
+    if (!grp.offsets) {
+      const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM), U = tiles * (K >> 8);
+      pays = U >= 5 * G && !(M > 128 && tiles <= G && 4 * tiles >= 3 * G);
+      if (U < G) G = U;
+    }
+    if (use_sk == 1 && !pays) G = 0;
+    if (G > 0 && sk_bytes >= SK_FLAG_BYTES + (size_t)G * SK_PART_FLOATS * 4 && (size_t)G * 4 <= SK_FLAG_BYTES) {
+      auto skern = prefill_sk_kernel<Row, BF16, OutT>;
+      static DeviceOnce sk_attr;
+      cudaError_t e = sk_attr.ensure([&] { return cudaFuncSetAttribute(skern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+      if (e == cudaSuccess) e = cudaMemsetAsync(sk, 0, (size_t)G * 4, st);
+      if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
+      skern<<<(unsigned)G, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, (float *)((char *)sk + SK_FLAG_BYTES), (unsigned *)sk);
+      return launched("prefill (tcgen05, stream-K)");
+    }
+  }
   auto kern = prefill_umma_kernel<Row, BF16, OutT>;
   static DeviceOnce attr_done;
   {
@@ -445,28 +834,32 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
 // f32 activations run with f16 operands and f32 output, bf16 activations with bf16 operands and output
 template <typename Row>
 int launch_by_act(const void *x, int act_dtype, const typename Row::Ctx &ctx, void *out, int M, int N, int K, void *ws,
-                  cudaStream_t st) {
+                  size_t ws_bytes, cudaStream_t st) {
   CUtensorMap tm;
   if (Row::KPERM && act_dtype != LB200_F32)
     return fail(LB200_E_DTYPE, "light_b200: prefill: this weight format takes f32 activations only");
   if (int rc = make_x_map(&tm, x, act_dtype, M, K, ws, Row::KPERM, st)) return rc;
   const Group none{nullptr, nullptr, nullptr, 0, 0};
-  if (act_dtype == LB200_F32) return launch<Row, false, float>(tm, ctx, none, (float *)out, M, N, K, st);
-  if constexpr (!Row::KPERM) return launch<Row, true, __nv_bfloat16>(tm, ctx, none, (__nv_bfloat16 *)out, M, N, K, st);
+  // what the workspace holds beyond the f16 copy of x is the stream-K kernel's
+  const size_t x_bytes = act_dtype == LB200_F32 ? (((size_t)M * K * 2 + 1023) & ~(size_t)1023) : 0;
+  void *sk = ws && ws_bytes > x_bytes ? (char *)ws + x_bytes : nullptr;
+  const size_t sk_bytes = sk ? ws_bytes - x_bytes : 0;
+  if (act_dtype == LB200_F32) return launch<Row, false, float>(tm, ctx, none, (float *)out, M, N, K, st, sk, sk_bytes);
+  if constexpr (!Row::KPERM) return launch<Row, true, __nv_bfloat16>(tm, ctx, none, (__nv_bfloat16 *)out, M, N, K, st, sk, sk_bytes);
   return LB200_E_DTYPE;
 }
 
 // workspace for an f32 activation matrix; bf16 needs none.  Returns false if there is not enough.
-bool get_ws(int device, int act_dtype, int M, int K, void **ws) {
-  *ws = nullptr;
-  if (act_dtype != LB200_F32) return true;
+bool get_ws(int device, int act_dtype, int M, int K, void **ws, size_t *bytes) {
   std::lock_guard<std::mutex> lk(g_mu);
-  if (!g_ws[device].ptr || g_ws[device].bytes < (size_t)M * K * 2) return false;
-  *ws = g_ws[device].ptr;
-  return true;
+  *ws = g_ws[device].ptr, *bytes = g_ws[device].ptr ? g_ws[device].bytes : 0;
+  return act_dtype != LB200_F32 || (*ws && *bytes >= (size_t)M * K * 2);
 }
 
 }  // namespace
+
+// room the stream-K kernel wants after the f16 copy of x: the flags and one partial tile per SM (up to 160 of them)
+size_t prefill_sk_ws_bytes() { return SK_FLAG_BYTES + (size_t)160 * SK_PART_FLOATS * 4 + 1024; }
 
 void *workspace_ptr(int device, size_t *bytes) {
   std::lock_guard<std::mutex> lk(g_mu);
@@ -505,11 +898,12 @@ int gguf_prefill(int type, const float *x, const void *w, float *out, int M, int
     return 0;
   }
   void *ws;
-  if (!get_ws(device, LB200_F32, M, K, &ws)) return 0;
+  size_t wsb;
+  if (!get_ws(device, LB200_F32, M, K, &ws, &wsb)) return 0;
   GgufCtx ctx{(const uint8_t *)w};
-  int rc = type == LB200_Q4_K   ? launch_by_act<Q4KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st)
-           : type == LB200_Q6_K ? launch_by_act<Q6KRow>(x, LB200_F32, ctx, out, M, N, K, ws, st)
-                                : launch_by_act<Q80Row>(x, LB200_F32, ctx, out, M, N, K, ws, st);
+  int rc = type == LB200_Q4_K   ? launch_by_act<Q4KRow>(x, LB200_F32, ctx, out, M, N, K, ws, wsb, st)
+           : type == LB200_Q6_K ? launch_by_act<Q6KRow>(x, LB200_F32, ctx, out, M, N, K, ws, wsb, st)
+                                : launch_by_act<Q80Row>(x, LB200_F32, ctx, out, M, N, K, ws, wsb, st);
   return rc ? rc : 1;
 }
 
@@ -517,9 +911,10 @@ int int4_prefill(const void *x, const uint32_t *codes, const float *s, const flo
                  int K, int G, int device, cudaStream_t st) {
   if (M < PREFILL_MIN_M || K % 256 || G % 64 || ((uintptr_t)codes & 15) || ((uintptr_t)x & 15)) return 0;
   void *ws;
-  if (!get_ws(device, act_dtype, M, K, &ws)) return 0;
+  size_t wsb;
+  if (!get_ws(device, act_dtype, M, K, &ws, &wsb)) return 0;
   Int4Ctx ctx{codes, s, z, G};
-  int rc = launch_by_act<Int4Row>(x, act_dtype, ctx, y, M, N, K, ws, st);
+  int rc = launch_by_act<Int4Row>(x, act_dtype, ctx, y, M, N, K, ws, wsb, st);
   return rc ? rc : 1;
 }
 
@@ -527,9 +922,10 @@ int fp8_prefill(const void *x, const uint8_t *w, const float *scale, void *y, in
                 int bC, int device, cudaStream_t st) {
   if (M < PREFILL_MIN_M || K % 128 || bC % 64 || ((uintptr_t)w & 15) || ((uintptr_t)x & 15)) return 0;
   void *ws;
-  if (!get_ws(device, act_dtype, M, K, &ws)) return 0;
+  size_t wsb;
+  if (!get_ws(device, act_dtype, M, K, &ws, &wsb)) return 0;
   Fp8Ctx ctx{w, scale, bR, bC};
-  int rc = launch_by_act<Fp8Row>(x, act_dtype, ctx, y, M, N, K, ws, st);
+  int rc = launch_by_act<Fp8Row>(x, act_dtype, ctx, y, M, N, K, ws, wsb, st);
   return rc ? rc : 1;
 }
 
@@ -565,7 +961,7 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const TI *__restrict__
 }
 
 template <typename Row, bool BF16, typename OutT, typename TI>
-int moe_launch(const lb200_moe_args *a, const typename Row::Ctx &ctx, void *ws, cudaStream_t st) {
+int moe_launch(const lb200_moe_args *a, const typename Row::Ctx &ctx, void *ws, size_t ws_bytes, cudaStream_t st) {
   if (int rc = ensure_encode()) return rc;
   long long blocks = (a->M + 7) / 8;
   if (blocks > 148 * 32) blocks = 148 * 32;
@@ -582,7 +978,9 @@ int moe_launch(const lb200_moe_args *a, const typename Row::Ctx &ctx, void *ws, 
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(LB200_E_SHAPE, "light_b200: moe: cuTensorMapEncodeTiled failed (%d)", (int)r);
   const Group grp{a->offsets, a->sorted_pairs, a->topk_weights, a->size_m, a->E};
-  return launch<Row, BF16, OutT>(tm, ctx, grp, (OutT *)a->out, (int)a->M, a->N, a->K, st);
+  const size_t x_bytes = ((size_t)a->M * a->K * 2 + 1023) & ~(size_t)1023;
+  void *sk = ws_bytes > x_bytes ? (char *)ws + x_bytes : nullptr;
+  return launch<Row, BF16, OutT>(tm, ctx, grp, (OutT *)a->out, (int)a->M, a->N, a->K, st, sk, sk ? ws_bytes - x_bytes : 0);
 }
 
 }  // namespace
@@ -593,32 +991,33 @@ int moe_launch(const lb200_moe_args *a, const typename Row::Ctx &ctx, void *ws, 
 int moe_umma(const lb200_moe_args *a, int kind, const float *w_scale, int bR, int bC, int device, cudaStream_t st) {
   if (a->M < 256 || a->M > 0x7fffffffLL || ((uintptr_t)a->input & 15) || ((uintptr_t)a->weights & 15) || a->K % 64) return 0;
   void *ws;
+  size_t wsb;
   {
     std::lock_guard<std::mutex> lk(g_mu);
     if (!g_ws[device].ptr || g_ws[device].bytes < (size_t)a->M * a->K * 2) return 0;
-    ws = g_ws[device].ptr;
+    ws = g_ws[device].ptr, wsb = g_ws[device].bytes;
   }
   int rc = 0;
   if (kind == 0) {
     if (a->dtype != LB200_BF16) return 0;
-    rc = moe_launch<DenseRow, true, __nv_bfloat16, __nv_bfloat16>(a, DenseCtx{(const uint16_t *)a->weights}, ws, st);
+    rc = moe_launch<DenseRow, true, __nv_bfloat16, __nv_bfloat16>(a, DenseCtx{(const uint16_t *)a->weights}, ws, wsb, st);
   } else if (kind == 1) {
     if (a->K % 256) return 0;
     if (a->dtype == LB200_Q4_K)
-      rc = moe_launch<Q4KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
+      rc = moe_launch<Q4KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, wsb, st);
     else if (a->dtype == LB200_Q6_K && ((size_t)(a->K >> 8) * 210) % 4 == 0)
-      rc = moe_launch<Q6KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
+      rc = moe_launch<Q6KRow, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, wsb, st);
     else if (a->dtype == LB200_Q8_0 && !((uintptr_t)a->weights & 15))
-      rc = moe_launch<Q80Row, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, st);
+      rc = moe_launch<Q80Row, false, float, float>(a, GgufCtx{(const uint8_t *)a->weights}, ws, wsb, st);
     else
       return 0;
   } else {
     if (a->K % 128 || bC % 64 || bR <= 0 || a->N % bR || a->K % bC) return 0;
     const Fp8Ctx ctx{(const uint8_t *)a->weights, w_scale, bR, bC};
     if (a->dtype == LB200_BF16)
-      rc = moe_launch<Fp8Row, true, __nv_bfloat16, __nv_bfloat16>(a, ctx, ws, st);
+      rc = moe_launch<Fp8Row, true, __nv_bfloat16, __nv_bfloat16>(a, ctx, ws, wsb, st);
     else if (a->dtype == LB200_F32)
-      rc = moe_launch<Fp8Row, false, float, float>(a, ctx, ws, st);
+      rc = moe_launch<Fp8Row, false, float, float>(a, ctx, ws, wsb, st);
     else
       return 0;
   }

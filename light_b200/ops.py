@@ -419,9 +419,9 @@ def MatMulInt4(x: torch.Tensor, w: Int4) -> torch.Tensor:
     if w.perm is not None:  # act-order GPTQ: gather x's columns into the weight's K order (ops/int4.go:129-147)
         xc = GatherColumns(xc, w.perm)
     M, N = x.shape[0], w.N()
-    if M > 64 and x.dtype == torch.float32:  # tensor-core path: f16 copy of x in the workspace
-        ensure_workspace(dev, M * w.K() * 2)
-    elif 4 <= M <= 64 and x.dtype == torch.bfloat16:  # token tiles over activations staged once
+    if M > 64 or (4 <= M and x.dtype == torch.bfloat16):
+        # tensor-core path: f16 copy of x (f32 activations) and the persistent kernel's partial tiles; 4 to 64 bf16 rows:
+        # token tiles over activations staged once
         ensure_workspace(dev, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, w.K())))
     out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
     _lib.check(_lib.lib().light_b200_int4_gemv(_ptr(xc), _ptr(w.codes.contiguous()), _ptr(w.scales.contiguous()),
@@ -460,9 +460,7 @@ def MatMulF8Block(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, block_r
     M, K = x.shape
     N = w.shape[0]
     dev = _dev(x, "MatMulF8Block")
-    if M > 64 and x.dtype == torch.float32:
-        ensure_workspace(dev, M * K * 2)
-    elif 4 <= M <= 64 and x.dtype == torch.bfloat16:  # token tiles over activations staged once
+    if M > 64 or (4 <= M and x.dtype == torch.bfloat16):  # (as in MatMulInt4)
         ensure_workspace(dev, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, K)))
     out = torch.zeros((M, N), dtype=x.dtype, device=x.device)
     _lib.check(_lib.lib().light_b200_fp8_block_gemv(_ptr(x.contiguous()), _ptr(w.contiguous()),
@@ -579,8 +577,8 @@ def _moe_dispatch(op: str, key_dtype: int, quant: bool, inp: torch.Tensor, weigh
         raise ValueError(f"{op}: topkWeights must be F32 with {M} elements")
     dev = _dev(inp, op)
     inc = inp.contiguous()
-    if M >= 256:  # tensor-core grouped path: the token rows are gathered into the workspace in expert order
-        ensure_workspace(dev, M * K * 2)
+    if M >= 256:  # tensor-core grouped path: the token rows gathered in expert order, the persistent kernel's partial tiles
+        ensure_workspace(dev, int(_lib.lib().light_b200_matmul_q_workspace_bytes(M, K)))
     counts = torch.zeros(E, dtype=torch.int32, device=inp.device)
     offsets = torch.zeros(E + 1, dtype=torch.int32, device=inp.device)
     out = torch.zeros((M, N), dtype=out_dtype, device=inp.device)
