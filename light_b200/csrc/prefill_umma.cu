@@ -55,6 +55,76 @@ struct Group {
   int E;
 };
 
+template <typename OutT>
+__device__ __forceinline__ void sk_store32(uint32_t (&v)[32], OutT *__restrict__ out, long long m, int N, int nc, float wgt, bool weighted) {
+  if (weighted) {
+#pragma unroll
+    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
+  }
+  OutT *o = out + (size_t)m * N + nc;
+  if (nc + 32 <= N && (N & 7) == 0) {
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+      for (int i = 0; i < 8; i++)
+        reinterpret_cast<float4 *>(o)[i] =
+            make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+        reinterpret_cast<uint4 *>(o)[i] = make_uint4(pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                                                     pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                                                     pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                                                     pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 32; i++)
+      if (nc + i < N) st_act(o, i, __uint_as_float(v[i]));
+  }
+}
+
+// 32 columns of one output row per thread (row m of the thread, dead rows skipped) -> global memory.  Through shared
+// memory, so that a store instruction writes whole 128-byte lines: the thread holds 32 columns of ONE token row, and rows
+// are N elements apart.  `stage` is 4 KB of shared memory that only this warp uses during an epilogue: the part of weight
+// stage 0 that it alone writes as an expander (its 32 rows of 128 bytes; the stage's last MMA has completed, and the warp
+// expands again only after its epilogue).  16-byte chunks are XOR-swizzled by the row.  All 32 lanes must call.
+template <typename OutT>
+__device__ __forceinline__ void tile_store32(uint32_t (&v)[32], uint32_t stage, int lane, long long m, bool live, float wgt, bool weighted,
+                                             OutT *__restrict__ out, int N, int nc) {
+  if (nc + 32 <= N && (N & 7) == 0) {
+    constexpr int ROWB = 32 * (int)sizeof(OutT), LPR = ROWB / 16, RPI = 32 / LPR;
+    auto sw = [](int row) { return sizeof(OutT) == 4 ? (row & 7) : ((row >> 1) & 3); };
+    if (weighted) {
+#pragma unroll
+      for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
+    }
+    if constexpr (sizeof(OutT) == 4) {
+#pragma unroll
+      for (int i = 0; i < 8; i++) st_chunk(stage + lane * ROWB + 16 * (i ^ sw(lane)), make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; i++)
+        st_chunk(stage + lane * ROWB + 16 * (i ^ sw(lane)),
+                 make_uint4(pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
+                            pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
+                            pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
+                            pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]))));
+    }
+    __syncwarp();
+#pragma unroll
+    for (int g = 0; g < 32 / RPI; g++) {
+      const int row = g * RPI + lane / LPR, q = lane % LPR;
+      const long long mr = __shfl_sync(0xffffffffu, m, row);
+      const int lr = __shfl_sync(0xffffffffu, (int)live, row);
+      const uint4 w = lds128(stage + row * ROWB + 16 * (q ^ sw(row)));
+      if (lr) *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(out + (size_t)mr * N + nc) + 16 * q) = w;
+    }
+    __syncwarp();
+  } else if (live) {
+    sk_store32<OutT>(v, out, m, N, nc, wgt, weighted);
+  }
+}
+
 // ---- the kernel.  grid = (ceil(N / 256), ceil(M / 256)); 320 threads:
 //   warps 0-7  expand weights (thread r <-> weight row n0 + r), then run the epilogue
 //   warp  8    TMA producer of the x tiles (one lane)
@@ -237,34 +307,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_umma_kernel(const __grid_c
           uint32_t v[32];
           tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + a * 256 + chalf * 128 + c * 32, v);
           tmem_ld_wait();
-          const int nc = n0 + chalf * 128 + c * 32;
-          if (live) {
-            if (grp.topkw) {
-#pragma unroll
-              for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
-            }
-            OutT *o = out + (size_t)m * N + nc;
-            if (nc + 32 <= N && (N & 7) == 0) {
-              if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-                for (int i = 0; i < 8; i++)
-                  reinterpret_cast<float4 *>(o)[i] = make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]),
-                                                                 __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-              } else {
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                  reinterpret_cast<uint4 *>(o)[i] = make_uint4(
-                      pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
-                      pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
-                      pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
-                      pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
-              }
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; i++)
-                if (nc + i < N) st_act(o, i, __uint_as_float(v[i]));
-            }
-          }
+          tile_store32<OutT>(v, sB + (uint32_t)warp * 4096, lane, m, live, wgt, grp.topkw != nullptr, out, N, n0 + chalf * 128 + c * 32);
         }
       }
     }
@@ -327,34 +370,6 @@ __device__ __forceinline__ bool sk_wait_flag(const unsigned *flag, unsigned want
   }
   *abort = 1;
   return false;
-}
-
-template <typename OutT>
-__device__ __forceinline__ void sk_store32(uint32_t (&v)[32], OutT *__restrict__ out, long long m, int N, int nc, float wgt, bool weighted) {
-  if (weighted) {
-#pragma unroll
-    for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
-  }
-  OutT *o = out + (size_t)m * N + nc;
-  if (nc + 32 <= N && (N & 7) == 0) {
-    if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-      for (int i = 0; i < 8; i++)
-        reinterpret_cast<float4 *>(o)[i] =
-            make_float4(__uint_as_float(v[4 * i]), __uint_as_float(v[4 * i + 1]), __uint_as_float(v[4 * i + 2]), __uint_as_float(v[4 * i + 3]));
-    } else {
-#pragma unroll
-      for (int i = 0; i < 4; i++)
-        reinterpret_cast<uint4 *>(o)[i] = make_uint4(pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
-                                                     pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
-                                                     pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
-                                                     pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7])));
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 32; i++)
-      if (nc + i < N) st_act(o, i, __uint_as_float(v[i]));
-  }
 }
 
 template <typename Row, bool BF16, typename OutT>
@@ -593,45 +608,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
               for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) + __ldcg(theirs + i * 256));
             }
           }
-          const int nc = T.n0 + chalf * 128 + (ch & 3) * 32;
-          if (nc + 32 <= N && (N & 7) == 0) {
-            // Through shared memory, so that a store instruction writes whole 128-byte lines: the thread holds 32
-            // columns of ONE token row, and rows are N elements apart.  The staging area is the part of weight stage 0
-            // that this warp alone writes as an expander (its 32 rows of 128 bytes): the stage's last MMA has completed
-            // and the warp expands again only after its epilogue.  16-byte chunks are XOR-swizzled by the row.
-            constexpr int ROWB = 32 * (int)sizeof(OutT), LPR = ROWB / 16, RPI = 32 / LPR;
-            auto sw = [](int row) { return sizeof(OutT) == 4 ? (row & 7) : ((row >> 1) & 3); };
-            const uint32_t mine = sB + (uint32_t)warp * 4096;
-            if (grp.topkw) {
-#pragma unroll
-              for (int i = 0; i < 32; i++) v[i] = __float_as_uint(__uint_as_float(v[i]) * wgt);
-            }
-            if constexpr (sizeof(OutT) == 4) {
-#pragma unroll
-              for (int i = 0; i < 8; i++)
-                st_chunk(mine + lane * ROWB + 16 * (i ^ sw(lane)), make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
-            } else {
-#pragma unroll
-              for (int i = 0; i < 4; i++)
-                st_chunk(mine + lane * ROWB + 16 * (i ^ sw(lane)),
-                         make_uint4(pack2<true>(__uint_as_float(v[8 * i]), __uint_as_float(v[8 * i + 1])),
-                                    pack2<true>(__uint_as_float(v[8 * i + 2]), __uint_as_float(v[8 * i + 3])),
-                                    pack2<true>(__uint_as_float(v[8 * i + 4]), __uint_as_float(v[8 * i + 5])),
-                                    pack2<true>(__uint_as_float(v[8 * i + 6]), __uint_as_float(v[8 * i + 7]))));
-            }
-            __syncwarp();
-#pragma unroll
-            for (int g = 0; g < 32 / RPI; g++) {
-              const int row = g * RPI + lane / LPR, q = lane % LPR;
-              const long long mr = __shfl_sync(0xffffffffu, m, row);
-              const int lr = __shfl_sync(0xffffffffu, (int)live, row);
-              const uint4 w = lds128(mine + row * ROWB + 16 * (q ^ sw(row)));
-              if (lr) *reinterpret_cast<uint4 *>(reinterpret_cast<char *>(out + (size_t)mr * N + nc) + 16 * q) = w;
-            }
-            __syncwarp();
-          } else if (live) {
-            sk_store32<OutT>(v, out, m, N, nc, wgt, grp.topkw != nullptr);
-          }
+          tile_store32<OutT>(v, sB + (uint32_t)warp * 4096, lane, m, live, wgt, grp.topkw != nullptr, out, N, T.n0 + chalf * 128 + (ch & 3) * 32);
         };
         tmem_ld32(chunk_addr(0), va);
 #pragma unroll 1
