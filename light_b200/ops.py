@@ -103,6 +103,7 @@ def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
 # --------------------------------------------------------------------------- workspace
 
 _workspaces = {}  # device index -> torch uint8 buffer handed to the library
+_retired = []     # buffers that were outgrown: a captured graph may still hold their address (scratch stays valid scratch)
 
 
 def ensure_workspace(device_index: int, nbytes: int) -> None:
@@ -111,8 +112,11 @@ def ensure_workspace(device_index: int, nbytes: int) -> None:
     cur = _workspaces.get(device_index)
     if cur is not None and cur.numel() - 1024 >= nbytes:
         return
-    # 64 MB to begin with: what batched decode (22 MB) and a 2048-row prefill of the widest layer need, so that the
-    # buffer is not replaced under a captured graph that holds its address
+    # 64 MB to begin with: what batched decode (22 MB) and a 2048-row prefill of the widest layer's f16 copy need.  A
+    # buffer that is outgrown is kept, not freed: launches already captured in a CUDA graph go on using its address, and
+    # every call writes what it reads there, so they stay correct.
+    if cur is not None:
+        _retired.append(cur)
     buf = torch.empty(max(nbytes, 64 << 20) + 1024, dtype=torch.uint8, device=torch.device("cuda", device_index))
     off = (-buf.data_ptr()) % 1024
     _lib.check(_lib.lib().light_b200_set_workspace(device_index, C.c_void_p(buf.data_ptr() + off), buf.numel() - 1024))
