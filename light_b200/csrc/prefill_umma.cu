@@ -19,6 +19,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
 
 #include <vector>
 
@@ -372,14 +373,37 @@ __device__ __forceinline__ bool sk_wait_flag(const unsigned *flag, unsigned want
   return false;
 }
 
+// rows whose packed weights the persistent kernel brings in through shared memory
+template <typename Row>
+struct SkStaged : std::false_type {};
+template <>
+struct SkStaged<Fp8Row> : std::true_type {
+  static constexpr int granules = 8;  // 128 codes
+};
+// (Q4_K rows -- 9 granules, one 144-byte block -- were measured this way too: no faster at 2048 tokens, where their main
+// loop runs at the MMAs' pace, and 5-15 % slower on short runs)
+template <>
+struct SkStaged<Int4Row> : std::true_type {
+  static constexpr int granules = 8;  // 256 codes
+};
+constexpr int SK_RAW_UNIT = 256 * 144;  // one 128-code load unit of all 256 rows, 144 bytes apart
+constexpr int SK_SMEM_STAGED = 2 * A_STAGE + SB * B_STAGE + 1024 + 256 + 2 * SK_RAW_UNIT;
+
 template <typename Row, bool BF16, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const typename Row::Ctx ctx,
                                                                const Group grp, OutT *__restrict__ out, int M, int N, int K,
                                                                float *__restrict__ parts, unsigned *__restrict__ flags) {
+  // 4-bit group-quantized and block-FP8 rows come in through shared memory: a thread per row reading global memory
+  // touches 32 lines per load instruction, and with a byte per weight that made the load unit (70 % of its wavefront
+  // rate), not the MMAs, set the pace.  Each warp copies the next load unit of its 32 rows with cp.async, the lanes
+  // running along a row (4 or 5 lines per instruction), into its own part of a two-unit ring, and its threads read
+  // their rows from there (pitch 144: no bank conflicts).  The ring takes the third activation stage's room.
+  constexpr bool STAGED = SkStaged<Row>::value;
+  constexpr int SAK = STAGED ? 2 : SA;
   extern __shared__ unsigned char smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t sA = base, sB = base + SA * A_STAGE, sBar = sB + SB * B_STAGE;
-  const uint32_t a_full = sBar, a_empty = sBar + 8 * SA, b_full = sBar + 16 * SA, b_empty = b_full + 8 * SB, d_full = b_empty + 8 * SB,
+  const uint32_t sA = base, sB = base + SAK * A_STAGE, sBar = sB + SB * B_STAGE, sRaw = sBar + 256;
+  const uint32_t a_full = sBar, a_empty = sBar + 8 * SAK, b_full = sBar + 16 * SAK, b_empty = b_full + 8 * SB, d_full = b_empty + 8 * SB,
                  d_empty = d_full + 8, tmem_slot = d_empty + 8;
   __shared__ int abort_flag;
   __shared__ uint32_t tmem_base_sh;
@@ -420,7 +444,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int i = 0; i < SA; i++) mbar_init(a_full + 8 * i, 1), mbar_init(a_empty + 8 * i, 1);
+    for (int i = 0; i < SAK; i++) mbar_init(a_full + 8 * i, 1), mbar_init(a_empty + 8 * i, 1);
     for (int i = 0; i < SB; i++) mbar_init(b_full + 8 * i, NUM_DEQ_WARPS), mbar_init(b_empty + 8 * i, 1);
     mbar_init(d_full, 1);
     mbar_init(d_empty, NUM_DEQ_WARPS);
@@ -451,8 +475,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
         const int b0 = (int)(pos - t * nb), b1 = (int)min((long long)nb, b0 + (pos1 - pos));
         const SkTile T = tile_of(t);
         for (int kb = b0 * 4; kb < b1 * 4; kb++, it++) {
-          const int s = it % SA;
-          if (it >= SA && !mbar_wait(a_empty + 8 * s, ((it / SA) - 1) & 1, abort)) break;
+          const int s = it % SAK;
+          if (it >= SAK && !mbar_wait(a_empty + 8 * s, ((it / SAK) - 1) & 1, abort)) break;
           mbar_arrive_expect_tx(a_full + 8 * s, T.two ? A_STAGE : A_STAGE / 2);
           tma_load_2d(sA + s * A_STAGE, &tmap_x, a_full + 8 * s, kb * BK, T.m0);
           if (T.two) tma_load_2d(sA + s * A_STAGE + A_STAGE / 2, &tmap_x, a_full + 8 * s, kb * BK, T.m0 + 128);
@@ -460,8 +484,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
         pos += b1 - b0;
       }
       if (*abort)  // give the loads still in flight a bounded time to land before the CTA retires
-        for (int k = it > SA ? it - SA : 0; k < it; k++)
-          for (int i = 0; i < (1 << 14) && !mbar_try_wait(a_full + 8 * (k % SA), (k / SA) & 1); i++) {
+        for (int k = it > SAK ? it - SAK : 0; k < it; k++)
+          for (int i = 0; i < (1 << 14) && !mbar_try_wait(a_full + 8 * (k % SAK), (k / SAK) & 1); i++) {
           }
     }
   } else if (warp == MMA_WARP) {
@@ -477,8 +501,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
         if (seg > 0 && !mbar_wait(d_empty, (seg - 1) & 1, abort)) break;
         tc_fence_after();
         for (int kb = 0; kb < (b1 - b0) * 4; kb++, it++) {
-          const int sa = it % SA, sb = it % SB;
-          if (!mbar_wait(a_full + 8 * sa, (it / SA) & 1, abort) || !mbar_wait(b_full + 8 * sb, (it / SB) & 1, abort)) {
+          const int sa = it % SAK, sb = it % SB;
+          if (!mbar_wait(a_full + 8 * sa, (it / SAK) & 1, abort) || !mbar_wait(b_full + 8 * sb, (it / SB) & 1, abort)) {
             ok = false;
             break;
           }
@@ -511,10 +535,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
       const SkTile T = tile_of(t);
       const int kb0 = b0 * 4, u0 = kb0 / Row::STEPS, units = b1 * 4 / Row::STEPS;
       cur.init(ctx, T.expert, min(T.n0 + r, N - 1), N, K);
-      cur.load(u0);
-      for (int u = u0; u < units && ok; u++) {
-        Row nxt = cur;
-        if (u + 1 < units) nxt.load(u + 1);
+      auto steps_of = [&](Row &row) {  // the 64-k steps of the unit `row` holds
 #pragma unroll
         for (int j = 0; j < Row::STEPS; j++, it++) {
           const int s = it % SB;
@@ -526,12 +547,52 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
               break;
             }
           }
-          cur.template step<BF16>(j, sB + s * B_STAGE, r);
+          row.template step<BF16>(j, sB + s * B_STAGE, r);
           fence_proxy_async();
           __syncwarp();
           if (lane == 0) mbar_arrive(b_full + 8 * s);
         }
-        cur = nxt;
+      };
+      if constexpr (STAGED) {
+        constexpr int GR = SkStaged<Row>::granules;  // 16-byte granules of a load unit of one row
+        constexpr bool HALF = std::is_same<Row, Fp8Row>::value;  // a load unit is half of a 256-code raw block
+        const int nw = min(T.n0 + warp * 32, N - 1);              // the warp's first row, and its 31 successors (clamped)
+        Row c0;
+        c0.init(ctx, T.expert, nw, N, K);
+        const size_t rstride = Row::row_stride(ctx, K);
+        int iu = u0;
+        auto issue = [&]() {  // always closes a commit group, so that the group counts stay uniform
+          if (iu < units) {
+            const uint32_t slot = sRaw + (uint32_t)(iu & 1) * SK_RAW_UNIT + (uint32_t)warp * 32 * 144;
+            const uint8_t *src = HALF ? c0.raw_src(iu >> 1) + 128 * (iu & 1) : c0.raw_src(iu);
+#pragma unroll
+            for (int i = 0; i < GR; i++) {  // lanes run along the granules of a row, then on to the next row
+              const int q = lane + 32 * i, rr = q / GR, piece = q - rr * GR;
+              cp_async16(slot + rr * 144 + piece * 16, src + (size_t)(min(T.n0 + warp * 32 + rr, N - 1) - nw) * rstride + piece * 16);
+            }
+          }
+          iu++;
+          cp_async_commit();
+        };
+        issue();
+        issue();
+        for (int u = u0; u < units && ok; u++) {
+          cp_async_wait<1>();  // this lane's granules of unit u have landed ...
+          __syncwarp();        // ... and so have the other lanes' (the rows of a warp are copied by that warp alone)
+          cur.load_smem(sRaw + (uint32_t)(u & 1) * SK_RAW_UNIT + (uint32_t)r * 144 - (HALF ? 128u * (u & 1) : 0u), u);
+          __syncwarp();        // every row of the slot has been read: it can take unit u + 2
+          issue();
+          steps_of(cur);
+        }
+        cp_async_wait<0>();
+      } else {
+        cur.load(u0);
+        for (int u = u0; u < units && ok; u++) {
+          Row nxt = cur;
+          if (u + 1 < units) nxt.load(u + 1);
+          steps_of(cur);
+          cur = nxt;
+        }
       }
       pos += b1 - b0;
       if (pos < pos1 && ok) {  // the next segment's first block of this thread's row, on its way to L2 during the epilogue
@@ -714,11 +775,12 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
     if (use_sk == 1 && !pays) G = 0;
     if (G > 0 && sk_bytes >= SK_FLAG_BYTES + (size_t)G * SK_PART_FLOATS * 4 && (size_t)G * 4 <= SK_FLAG_BYTES) {
       auto skern = prefill_sk_kernel<Row, BF16, OutT>;
+      constexpr int sk_smem = SkStaged<Row>::value ? SK_SMEM_STAGED : SMEM_BYTES;
       static DeviceOnce sk_attr;
-      cudaError_t e = sk_attr.ensure([&] { return cudaFuncSetAttribute(skern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES); });
+      cudaError_t e = sk_attr.ensure([&] { return cudaFuncSetAttribute(skern, cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem); });
       if (e == cudaSuccess) e = cudaMemsetAsync(sk, 0, (size_t)G * 4, st);
       if (e != cudaSuccess) return fail((int)e, "light_b200: prefill: %s", cudaGetErrorString(e));
-      skern<<<(unsigned)G, THREADS, SMEM_BYTES, st>>>(tm, ctx, grp, out, M, N, K, (float *)((char *)sk + SK_FLAG_BYTES), (unsigned *)sk);
+      skern<<<(unsigned)G, THREADS, sk_smem, st>>>(tm, ctx, grp, out, M, N, K, (float *)((char *)sk + SK_FLAG_BYTES), (unsigned *)sk);
       return launched("prefill (tcgen05, stream-K)");
     }
   }
