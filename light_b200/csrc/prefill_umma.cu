@@ -375,29 +375,38 @@ __device__ __forceinline__ bool sk_wait_flag(const unsigned *flag, unsigned want
 
 // rows whose packed weights the persistent kernel brings in through shared memory
 template <typename Row>
-struct SkStaged : std::false_type {};
+struct SkStaged : std::false_type {
+  static constexpr int pitch = 0;
+};
 template <>
 struct SkStaged<Fp8Row> : std::true_type {
-  static constexpr int granules = 8;  // 128 codes
+  static constexpr int granules = 8, pitch = 144, units_per_copy = 1;  // 128 codes
+};
+template <>
+struct SkStaged<Q6KRow> : std::true_type {
+  static constexpr int granules = 14, pitch = 240, units_per_copy = 2;  // the 224 bytes that cover a 210-byte block
 };
 // (Q4_K rows -- 9 granules, one 144-byte block -- were measured this way too: no faster at 2048 tokens, where their main
 // loop runs at the MMAs' pace, and 5-15 % slower on short runs)
 template <>
 struct SkStaged<Int4Row> : std::true_type {
-  static constexpr int granules = 8;  // 256 codes
+  static constexpr int granules = 8, pitch = 144, units_per_copy = 1;  // 256 codes
 };
-constexpr int SK_RAW_UNIT = 256 * 144;  // one 128-code load unit of all 256 rows, 144 bytes apart
-constexpr int SK_SMEM_STAGED = 2 * A_STAGE + SB * B_STAGE + 1024 + 256 + 2 * SK_RAW_UNIT;
+template <typename Row>
+constexpr int sk_smem_bytes() {  // staged rows: two activation stages, and one copy slot of `pitch` bytes per weight row
+  return SkStaged<Row>::value ? 2 * A_STAGE + SB * B_STAGE + 1024 + 256 + 256 * SkStaged<Row>::pitch : SMEM_BYTES;
+}
 
 template <typename Row, bool BF16, typename OutT>
 __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_constant__ CUtensorMap tmap_x, const typename Row::Ctx ctx,
                                                                const Group grp, OutT *__restrict__ out, int M, int N, int K,
                                                                float *__restrict__ parts, unsigned *__restrict__ flags) {
-  // 4-bit group-quantized and block-FP8 rows come in through shared memory: a thread per row reading global memory
-  // touches 32 lines per load instruction, and with a byte per weight that made the load unit (70 % of its wavefront
-  // rate), not the MMAs, set the pace.  Each warp copies the next load unit of its 32 rows with cp.async, the lanes
-  // running along a row (4 or 5 lines per instruction), into its own part of a two-unit ring, and its threads read
-  // their rows from there (pitch 144: no bank conflicts).  The ring takes the third activation stage's room.
+  // Q6_K, 4-bit group-quantized and block-FP8 rows come in through shared memory: a thread per row reading global memory
+  // touches 32 lines per load instruction (Q6_K: 27 to 54 four-byte loads per 128 weights), and that made the load unit
+  // (70 % of its wavefront rate for FP8), not the MMAs, set the pace.  Each warp copies the next load unit (Q6_K: block)
+  // of its 32 rows with cp.async, the lanes running along a row (a few lines per instruction), into its own slot, and
+  // its threads read their rows from there into registers; the slot is then free for the next copy, which lands while
+  // those registers are expanded.  The slots take the third activation stage's room.
   constexpr bool STAGED = SkStaged<Row>::value;
   constexpr int SAK = STAGED ? 2 : SA;
   extern __shared__ unsigned char smem_raw[];
@@ -554,35 +563,52 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_sk_kernel(const __grid_con
         }
       };
       if constexpr (STAGED) {
-        constexpr int GR = SkStaged<Row>::granules;  // 16-byte granules of a load unit of one row
-        constexpr bool HALF = std::is_same<Row, Fp8Row>::value;  // a load unit is half of a 256-code raw block
-        const int nw = min(T.n0 + warp * 32, N - 1);              // the warp's first row, and its 31 successors (clamped)
+        using S = SkStaged<Row>;
+        constexpr int GR = S::granules, PITCH = S::pitch, CG = S::units_per_copy;
+        constexpr bool HALF = std::is_same<Row, Fp8Row>::value;    // a load unit is half of a 256-code raw block
+        constexpr bool SKEWED = std::is_same<Row, Q6KRow>::value;  // rows start on any even byte: the copy is of the
+                                                                   // 16-byte granules that cover the block
+        const int nw = min(T.n0 + warp * 32, N - 1);               // the warp's first row, and its 31 successors (clamped)
         Row c0;
         c0.init(ctx, T.expert, nw, N, K);
         const size_t rstride = Row::row_stride(ctx, K);
-        int iu = u0;
-        auto issue = [&]() {  // always closes a commit group, so that the group counts stay uniform
-          if (iu < units) {
-            const uint32_t slot = sRaw + (uint32_t)(iu & 1) * SK_RAW_UNIT + (uint32_t)warp * 32 * 144;
-            const uint8_t *src = HALF ? c0.raw_src(iu >> 1) + 128 * (iu & 1) : c0.raw_src(iu);
+        const uint32_t wslot = sRaw + (uint32_t)warp * 32 * PITCH;
+        const uint8_t *lim = c0.raw_end();
+        int ic = u0 / CG;
+        const int c_end = units / CG;
+        auto issue = [&]() {  // always closes a commit group
+          if (ic < c_end) {
 #pragma unroll
             for (int i = 0; i < GR; i++) {  // lanes run along the granules of a row, then on to the next row
               const int q = lane + 32 * i, rr = q / GR, piece = q - rr * GR;
-              cp_async16(slot + rr * 144 + piece * 16, src + (size_t)(min(T.n0 + warp * 32 + rr, N - 1) - nw) * rstride + piece * 16);
+              const size_t down = (size_t)(min(T.n0 + warp * 32 + rr, N - 1) - nw) * rstride;
+              const uint8_t *src;
+              if constexpr (HALF) src = c0.raw_src(ic >> 1) + 128 * (ic & 1) + down;
+              else if constexpr (SKEWED) src = reinterpret_cast<const uint8_t *>((uintptr_t)(c0.raw_src_unaligned(ic) + down) & ~(uintptr_t)15);
+              else src = c0.raw_src(ic) + down;
+              src += piece * 16;
+              const uint32_t dst = wslot + rr * PITCH + piece * 16;
+              if (lim == nullptr || src + 16 <= lim) cp_async16(dst, src);
+              else if (src < lim) cp_async16_part(dst, src, (uint32_t)(lim - src));
             }
           }
-          iu++;
+          ic++;
           cp_async_commit();
         };
         issue();
-        issue();
-        for (int u = u0; u < units && ok; u++) {
-          cp_async_wait<1>();  // this lane's granules of unit u have landed ...
+        for (int c = u0 / CG; c < c_end && ok; c++) {
+          cp_async_wait<0>();  // this lane's granules of copy c have landed ...
           __syncwarp();        // ... and so have the other lanes' (the rows of a warp are copied by that warp alone)
-          cur.load_smem(sRaw + (uint32_t)(u & 1) * SK_RAW_UNIT + (uint32_t)r * 144 - (HALF ? 128u * (u & 1) : 0u), u);
-          __syncwarp();        // every row of the slot has been read: it can take unit u + 2
-          issue();
-          steps_of(cur);
+#pragma unroll
+          for (int uu = 0; uu < CG; uu++) {
+            const int u = c * CG + uu;
+            cur.load_smem(sRaw + (uint32_t)r * PITCH - (HALF ? 128u * (u & 1) : 0u), u);
+            if (uu == CG - 1) {  // the rows are in registers: the slot can take the next copy while these steps run
+              __syncwarp();
+              issue();
+            }
+            steps_of(cur);
+          }
         }
         cp_async_wait<0>();
       } else {
@@ -775,7 +801,7 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
     if (use_sk == 1 && !pays) G = 0;
     if (G > 0 && sk_bytes >= SK_FLAG_BYTES + (size_t)G * SK_PART_FLOATS * 4 && (size_t)G * 4 <= SK_FLAG_BYTES) {
       auto skern = prefill_sk_kernel<Row, BF16, OutT>;
-      constexpr int sk_smem = SkStaged<Row>::value ? SK_SMEM_STAGED : SMEM_BYTES;
+      constexpr int sk_smem = sk_smem_bytes<Row>();
       static DeviceOnce sk_attr;
       cudaError_t e = sk_attr.ensure([&] { return cudaFuncSetAttribute(skern, cudaFuncAttributeMaxDynamicSharedMemorySize, sk_smem); });
       if (e == cudaSuccess) e = cudaMemsetAsync(sk, 0, (size_t)G * 4, st);

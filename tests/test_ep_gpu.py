@@ -2,8 +2,10 @@
 all-to-all to the rank that owns their experts, run through this library's grouped matmuls there
 (SwiGLU expert: gate_up, SiLU * up, down), and come back; the result must equal the same sparse block
 computed on one GPU with all experts.  Skipped on a single-GPU box."""
+import datetime
 import os
 import socket
+import time
 
 import pytest
 import torch
@@ -25,7 +27,10 @@ def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     dev = torch.device("cuda", rank)
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # (a short collective timeout: a rank that fails leaves at once, and the others then report their aborted
+    # collective instead of waiting for it)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
+    failed = False
     try:
         from light_b200 import ops, tp
 
@@ -61,11 +66,14 @@ def _worker(rank, world, port, q):
             assert err <= 1e-3, f"rank {rank} T={T} rel err {err}"
         q.put((rank, "ok"))
     except Exception as e:  # noqa: BLE001
+        failed = True
         q.put((rank, repr(e)))
     finally:
-        dist.barrier()
-        torch.cuda.synchronize(dev)
-        os._exit(0)
+        if not failed:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+        time.sleep(0.5)  # (let the queue's feeder thread send)
+        os._exit(1 if failed else 0)
 
 
 def test_expert_parallel_matches_single_gpu():
@@ -81,7 +89,16 @@ def test_expert_parallel_matches_single_gpu():
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = dict(q.get(timeout=300) for _ in procs)
+    res, deadline = {}, time.time() + 600
+    while len(res) < world and time.time() < deadline:
+        try:
+            r, msg = q.get(timeout=5)
+            res[r] = msg
+        except Exception:  # noqa: BLE001  (queue.Empty: keep waiting while any worker lives)
+            if not any(p.is_alive() for p in procs):
+                break
     for p in procs:
-        p.join(60)
+        p.join(30)
+        if p.is_alive():
+            p.terminate()
     assert res == {r: "ok" for r in range(world)}, res
