@@ -786,7 +786,8 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
            cudaStream_t st, void *sk = nullptr, size_t sk_bytes = 0) {
   // The persistent stream-K kernel when the workspace has room for its partial tiles and the split pays: each CTA needs
   // a few K blocks to spread the cost of its two extra epilogues over (measured: five), and a grid of whole 256-token tiles
-  // that fills between three quarters and all of the SMs in one wave is already even.  A grouped launch always takes it (its
+  // that fills between three quarters and all of the SMs in one wave is already even (rows that only this kernel brings
+  // in through shared memory take it there too: Q6_K down at 2048 tokens 300 against 325 us).  A grouped launch always takes it (its
   // tiles are uneven by nature).  LIGHT_B200_PREFILL_SK = 0: never, 2: whenever possible.
   static int use_sk = -1;
   if (use_sk < 0) use_sk = getenv("LIGHT_B200_PREFILL_SK") ? atoi(getenv("LIGHT_B200_PREFILL_SK")) : 1;
@@ -795,7 +796,7 @@ int launch(const CUtensorMap &tm, const typename Row::Ctx &ctx, const Group &grp
     bool pays = true;
     if (!grp.offsets) {
       const long long tiles = (long long)((N + BN - 1) / BN) * ((M + BM - 1) / BM), U = tiles * (K >> 8);
-      pays = U >= 5 * G && !(M > 128 && tiles <= G && 4 * tiles >= 3 * G);
+      pays = U >= 5 * G && (SkStaged<Row>::value || !(M > 128 && tiles <= G && 4 * tiles >= 3 * G));
       if (U < G) G = U;
     }
     if (use_sk == 1 && !pays) G = 0;
