@@ -12,6 +12,9 @@
 //   * completion is tracked with mbarriers (TMA -> MMA -> free stage), the epilogue reads the
 //     accumulators with tcgen05.ld and writes f32 rows.
 //
+// Two kernels share this pipeline: prefill_umma_kernel, one tile per CTA (optionally a cluster split of K), and
+// prefill_sk_kernel, one persistent CTA per SM over an even split of all (tile, K block) pairs; launch() picks.
+//
 // f16 (not bf16) operands: the reference multiplies f32 weights by f32 activations; rounding the
 // weights to bf16 alone costs 1.7e-3 relative L2, to f16 2e-4.
 #include <cuda.h>
