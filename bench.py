@@ -904,8 +904,6 @@ def main():
             "whole_decode_step_kv1024_tok_s": round(ex["decode_m1_full_step_kv1024"]["tok_s"], 1) if "decode_m1_full_step_kv1024" in ex else None,
             "prefill_m2048_frac_of_sustained_bf16": ex["prefill_m2048"].get("all_four", {}).get("frac_of_measured_sustained_bf16"),
         }
-    if world > 1 and not args.no_extras:
-        line["moe_fp8_deepseek_v3_layer_expert_parallel"] = moe_ep_extras(device, world, rank, barrier)
     if world > 1 and chain.peer is not None:
         # correctness of the exchange that was just timed: rank 0's logits against the NCCL-gathered chain
         graph.replay()
@@ -919,21 +917,41 @@ def main():
         dist.all_reduce(check, op=dist.ReduceOp.MAX)
         line["tp_check"] = {"rel_l2_vs_nccl_chain_max_over_ranks": float(check[0].item()), "comm_status": int(check[1].item()),
                             "finite": bool(torch.isfinite(got).all().item())}
+    peer_bad = world > 1 and chain.peer is not None and chain.peer.status() != 0  # (one status word covers both exchanges)
+    ep_stuck = False
+    if world > 1 and not args.no_extras:
+        # Last, and under a deadline on every rank: a side measurement must not be able to keep the line above from
+        # being printed (a rank that fails alone would leave the others waiting in the next all-to-all).
+        got = {}
+
+        def ep_work():
+            try:
+                torch.cuda.set_device(device)
+                got["v"] = moe_ep_extras(device, world, rank, barrier)
+            except Exception as e:  # noqa: BLE001
+                got["v"] = {"error": repr(e)[:300]}
+
+        th = threading.Thread(target=ep_work, daemon=True)
+        th.start()
+        th.join(180)
+        ep_stuck = "v" not in got
+        line["moe_fp8_deepseek_v3_layer_expert_parallel"] = got.get("v", {"error": "no result within 180 s"})
     if rank == 0:
         if world == 1 and not args.no_cpu_baseline:
             threads = os.cpu_count() or 1
             v, t_step, _, _, sample = cpu_reference(M, threads, 3, 1)
             line["cpu_baseline"] = {"value": v, "unit": unit, "cores": threads, "kind": "port", "sample": sample}
         print(json.dumps(line), flush=True)
-    if world > 1 and chain.peer is not None and chain.peer.status() != 0:  # (one status word covers both exchanges)
+    if peer_bad:
         print("[bench] a bounded wait on a peer gave up: the N-GPU number above is not valid", file=sys.stderr)
     if world > 1:
         # Graphs that captured NCCL kernels must be gone before the communicator is torn down; and a
         # communicator that will not finish tearing down must not keep the job alive.
-        del graph
-        torch.cuda.synchronize(device)
-        dist.barrier()
         sys.stdout.flush()
+        if not ep_stuck:
+            del graph
+            torch.cuda.synchronize(device)
+            dist.barrier()
         os._exit(0)
     return 0
 
