@@ -822,6 +822,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
+        os.environ.setdefault("NCCL_DEBUG", "WARN")  # (keeps NCCL's version banner off stdout: the JSON line stands alone)
         dist.init_process_group("nccl", device_id=device)
         barrier = lambda: dist.barrier()  # noqa: E731
     else:
