@@ -822,8 +822,6 @@ def main():
     if world > 1:
         import torch.distributed as dist
 
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):  # (NCCL's version banner goes to stdout: the JSON
-            os.environ["NCCL_DEBUG"] = "WARN"                            #  line is to stand alone there)
         dist.init_process_group("nccl", device_id=device)
         barrier = lambda: dist.barrier()  # noqa: E731
     else:
