@@ -1,10 +1,11 @@
-"""Expert parallelism, host logic and exchange, as two gloo ranks on CPU: each rank routes its own
+"""Expert parallelism, host logic and exchange, as two and four gloo ranks on CPU: each rank routes its own
 tokens, the pairs travel to the rank that owns their expert, a stand-in expert function (a dense matmul
 per expert in torch, the arithmetic of kernels/cpu/moe.go:51-123) runs there, and the combined output
 equals the single-rank sparse block (nn/moe.go:121-237) on the same tokens."""
 import os
 import socket
 
+import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
@@ -62,8 +63,8 @@ def _worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
-def test_expert_parallel_two_ranks():
-    world = 2
+@pytest.mark.parametrize("world", [2, 4])
+def test_expert_parallel_ranks(world):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
@@ -73,4 +74,4 @@ def test_expert_parallel_two_ranks():
     res = dict(q.get(timeout=120) for _ in procs)
     for p in procs:
         p.join(30)
-    assert res == {0: "ok", 1: "ok"}, res
+    assert res == {r: "ok" for r in range(world)}, res
